@@ -1,0 +1,101 @@
+"""Pins the CPU oracle against vectors produced by the reference's own test oracles."""
+import numpy as np
+import torch
+
+from _util import load_golden, max_abs, rel_rmse
+
+TOKENS = ("r", "w", "k", "v", "a", "b")
+
+
+def _run(oracle, g, **kw):
+    return oracle.forward(*(g[n] for n in TOKENS), state_pool=g["state_pool"], cu_seqlens=g["cu_seqlens"],
+                          state_indices=g.get("state_indices"), scale=g.get("scale", 1.0),
+                          decay_bias=g.get("decay_bias"), **kw)
+
+
+def test_recurrent_cfg0_both_accumulators(oracle):
+    g = load_golden("recurrent_cfg0")
+    for double in (True, False):
+        out = _run(oracle, g, double=double)
+        assert max_abs(out["y"], g["y"]) < 2e-4
+        assert rel_rmse(out["y"], g["y"]) < 2e-6
+        assert rel_rmse(out["state_pool"], g["final_pool"]) < 2e-6
+
+
+def test_recurrent_ragged_slots_bias_scale(oracle):
+    g = load_golden("recurrent_ragged")
+    out = _run(oracle, g)
+    assert rel_rmse(out["y"], g["y"]) < 1e-6
+    assert rel_rmse(out["state_pool"], g["final_pool"]) < 1e-6
+    inactive = [1, 3, 6, 8]
+    assert np.array_equal(out["state_pool"][inactive], g["state_pool"].numpy()[inactive])
+
+
+def test_torch_restatement_matches_reference_oracle(oracle):
+    g = load_golden("recurrent_ragged")
+    y, pool = oracle.forward_torch(*(g[n] for n in TOKENS), state_pool=g["state_pool"],
+                                   cu_seqlens=g["cu_seqlens"], state_indices=g["state_indices"],
+                                   scale=g["scale"], decay_bias=g["decay_bias"])
+    assert rel_rmse(y, g["y"]) < 1e-6
+    assert rel_rmse(pool, g["final_pool"]) < 1e-6
+
+
+def test_chunk_bf16_reference_rounds_outputs(oracle):
+    g = load_golden("chunk_bf16")
+    out = _run(oracle, g)
+    y = torch.from_numpy(out["y"]).to(torch.bfloat16)
+    # the reference oracle rounds y and the final state to bf16: allow one ulp of disagreement
+    assert rel_rmse(y.float(), g["y"].float()) < 4e-3
+    final = torch.from_numpy(out["state_pool"]).to(torch.bfloat16)
+    assert rel_rmse(final.float(), g["final_pool"].float()) < 4e-3
+
+
+def test_rl_fp16_io(oracle):
+    g = load_golden("rl_fp16")
+    out = _run(oracle, g)
+    assert max_abs(torch.from_numpy(out["y"]).half().float(), g["y"].float()) <= 2e-6
+    assert rel_rmse(out["state_pool"], g["final_pool"]) < 1e-6
+
+
+def test_statetune_outputs_and_gradients(oracle):
+    g = load_golden("statetune")
+    B = g["S0"].shape[0]
+    chunks = (g["seq_chunk_offsets"], g["chunk_starts"], g["chunk_ends"])
+    cu = torch.tensor([0, 3, 5], dtype=torch.int32)  # token ranges implied by the chunk tables
+    out = oracle.forward(*(g[n] for n in TOKENS), state_pool=g["S0"], cu_seqlens=cu,
+                         state_indices=torch.arange(B, dtype=torch.int32), scale=g["scale"],
+                         chunks=chunks, want_state_dot_a=True)
+    assert max_abs(torch.from_numpy(out["y"]).half().float(), g["y"].float()) <= 2e-7
+    assert rel_rmse(out["state_pool"], g["final_state"]) < 1e-6
+    assert rel_rmse(out["boundary"], g["boundary"]) < 1e-6
+    assert rel_rmse(out["state_dot_a"], g["state_dot_a"]) < 1e-5
+    grads = oracle.backward(*(g[n] for n in TOKENS), initial_state=g["S0"], cu_seqlens=cu,
+                            grad_output=g["grad_output"], grad_final_state=g["grad_final_state"],
+                            scale=g["scale"])
+    for ours, name in (("initial_state", "dS0"), ("r", "dr"), ("decay_logits", "dw"), ("k", "dk"),
+                       ("v", "dv"), ("a", "da"), ("b", "db")):
+        assert torch.allclose(torch.from_numpy(grads[ours]), g[name], atol=3e-6, rtol=3e-3), name
+
+
+def test_pretrain_dense_forward_and_gradients(oracle):
+    g = load_golden("pretrain")
+    Bp, Tp, C = g["r"].shape
+    H, D = C // 64, 64
+    toks = [g[n].reshape(Bp * Tp, H, D) for n in TOKENS]
+    cu = torch.arange(Bp + 1, dtype=torch.int32) * Tp
+    S0 = torch.zeros(Bp, H, D, D)
+    out = oracle.forward(*toks, state_pool=S0, cu_seqlens=cu)
+    assert rel_rmse(out["y"].reshape(Bp, Tp, C), g["y"]) < 1e-5
+    grads = oracle.backward(*toks, initial_state=S0, cu_seqlens=cu,
+                            grad_output=g["dy"].reshape(Bp * Tp, H, D))
+    for ours, name in (("r", "dr"), ("decay_logits", "dw"), ("k", "dk"), ("v", "dv"), ("a", "da"), ("b", "db")):
+        # the reference's autograd leaves are bf16, so its gradients carry one bf16 rounding
+        assert rel_rmse(grads[ours].reshape(Bp, Tp, C), g[name]) < 4e-3, name
+
+
+def test_retention_matches_exp2_form(oracle):
+    x = np.linspace(-12, 14, 4001, dtype=np.float32)
+    w = oracle.retention(x)
+    ref = np.exp2(-0.8750387749145276 / (1.0 + np.exp2(-1.4426950408889634 * x.astype(np.float64))))
+    assert np.max(np.abs(w - ref)) < 2e-7
+    assert w.min() > 0.545 and w.max() < 1.0
