@@ -1,0 +1,318 @@
+#!/usr/bin/env python
+"""Benchmark of the WKV7 time-mix hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Workload (N = 1 and every N): recurrent decode at B=256 sequences, H=32, D=64,
+bf16 tokens, fp32 state pool read and written in place.  One benchmark *step* is
+one pass over a batch of synthetic input: 256 consecutive decode steps of the 256
+sequences (65 536 tokens, 256 kernel launches).  With N GPUs every rank owns its
+own 256 sequences and state pool (weak scaling, no collective on the data path);
+`value` is the total tokens/s over all ranks using the slowest rank's time.
+
+The line printed by rank 0 carries, besides the contract keys, `roofline`
+(algorithmic bytes per launch / measured launch time against the measured HBM
+peak), `cpu_baseline` (the CPU oracle timed on the host cores) and `e2e` (the same
+metric with host buffers: pinned-host -> device copies of every decode step's six
+token tensors and a device -> host read of its output inside the timed region).
+
+`--impl reference` times the CPU port of the reference's recurrence (the oracle)
+on a bounded sample and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+B, H, D = 256, 32, 64
+DECODE_STEPS_PER_STEP = 256          # "run 256 consecutive steps"
+TOKEN_RING = 8                       # distinct pre-generated decode steps of token data
+METRIC = "WKV7 recurrent decode tokens/s (B=256,H=32,D=64, fp32 state in place)"
+# algorithmic bytes of one decode launch: per (sequence, head) 2*D*D*4 (state read + write)
+# + 7*D*2 (r,w,k,v,a,b in, y out)
+BYTES_PER_UNIT = 2 * D * D * 4 + 7 * D * 2
+BYTES_PER_LAUNCH = B * H * BYTES_PER_UNIT
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch at this size, from the ncu
+# capture summarised in profiles/ (None until a capture exists)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+FALLBACK_HBM_GBS = 6650.0
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return float(d["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the bench runs."""
+
+    def __init__(self, index: int):
+        self.samples = []
+        self.timed = False
+        self._stop = threading.Event()
+        self._thread = None
+        self.sm_max = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)
+                reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                self.samples.append((self.timed, mhz, int(reasons)))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=1.0)
+
+    def summary(self):
+        if self._nv is None or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": ["nvml unavailable"]}
+        timed = [s for s in self.samples if s[0]] or self.samples
+        nv = self._nv
+        names = {
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "hw_power_brake": getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        seen = sorted(n for n, bit in names.items() if any(s[2] & bit for s in timed))
+        return {"sm_mhz": statistics.median(s[1] for s in timed), "sm_max_mhz": self.sm_max,
+                "reasons": seen, "samples": len(timed)}
+
+
+class CpuPort:
+    """The CPU oracle (C port of the reference recurrence, OpenMP over (sequence, head))."""
+
+    def __init__(self):
+        from flashrwkv_b200 import synthetic
+        from oracle import wkv7_oracle
+
+        wkv7_oracle.build()
+        self.oracle = wkv7_oracle
+        self.cu, self.idx = synthetic.equal_length_metadata(B, 1)
+        self.pool = synthetic.state_pool(B, H, D, seed=1).numpy()
+        self.toks = [t.float().numpy() for t in synthetic.wkv7_inputs(B, H, D, seed=2)]
+        self.toks16 = synthetic.wkv7_inputs(B, H, D, seed=2)
+
+    def decode_steps(self, n: int) -> float:
+        """Run n decode steps of the batch; return the seconds they took."""
+        t0 = time.perf_counter()
+        for _ in range(n):
+            self.oracle.forward(*self.toks, state_pool=self.pool, cu_seqlens=self.cu, state_indices=self.idx,
+                                double=False, inplace=True)
+        return time.perf_counter() - t0
+
+    def pytorch_port_tokens_per_s(self, reps: int = 2) -> float:
+        """The oracle in the reference's own form: pure PyTorch, Python loop over sequences and tokens."""
+        import torch
+
+        tp = torch.from_numpy(self.pool)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            _, tp = self.oracle.forward_torch(*self.toks16, state_pool=tp, cu_seqlens=self.cu,
+                                              state_indices=self.idx)
+        return B * reps / (time.perf_counter() - t0)
+
+    def describe(self, value: float, sample: str) -> dict:
+        import torch
+
+        return {"value": value, "unit": "tokens/s", "cores": self.oracle.num_threads(), "kind": "port",
+                "sample": sample, "pytorch_port_tokens_per_s": self.pytorch_port_tokens_per_s(),
+                "pytorch_port_threads": torch.get_num_threads(), "host_cpus": os.cpu_count()}
+
+
+def _cpu_baseline(sample_decode_steps: int) -> dict:
+    port = CpuPort()
+    port.decode_steps(2)
+    dt = port.decode_steps(sample_decode_steps)
+    return port.describe(B * sample_decode_steps / dt,
+                         f"{sample_decode_steps} decode steps of the same B={B},H={H},D={D} batch; fp32 C port of "
+                         f"the reference recurrence, OpenMP over (sequence, head)")
+
+
+def run_reference(args):
+    """The CPU arm: each step is a bounded sample (16 decode steps) of the workload."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    sample = 16
+    port = CpuPort()
+    for _ in range(args.warmup):
+        port.decode_steps(sample)
+    dt = sum(port.decode_steps(sample) for _ in range(args.steps))
+    value = B * sample * args.steps / dt
+    base = port.describe(value, f"{args.steps} steps x {sample} decode steps of the B={B},H={H},D={D} batch; fp32 C "
+                                f"port of the reference recurrence, OpenMP over (sequence, head)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"recurrent decode B={B} H={H} D={D}, fp32 state, CPU port of the reference "
+                               f"recurrence; each step = {sample} decode steps (bounded sample)"},
+        "cpu_baseline": base,
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback of the product path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    cu, idx = (t.to(dev) for t in synthetic.equal_length_metadata(B, 1))
+    pool = synthetic.state_pool(B, H, D, seed=1000 + rank, device=dev)
+    ring_host = [[t.pin_memory() for t in synthetic.wkv7_inputs(B, H, D, seed=20260805 + 97 * rank + i)]
+                 for i in range(TOKEN_RING)]
+    ring = [[t.to(dev) for t in step] for step in ring_host]
+    ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=B, state_pool_size=B, max_seqlen=1)
+    kw = dict(state_pool=pool, cu_seqlens=cu, state_indices=idx, validated_metadata=ticket, max_seqlen=1)
+
+    def device_step():
+        for i in range(DECODE_STEPS_PER_STEP):
+            F.infer_recurrent_fp32io16_forward_varlen(*ring[i % TOKEN_RING], **kw)
+
+    stage = [torch.empty_like(t, device=dev) for t in ring_host[0]]
+    y_host = torch.empty((B, H, D), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        for i in range(DECODE_STEPS_PER_STEP):
+            src = ring_host[i % TOKEN_RING]
+            for d, s in zip(stage, src):
+                d.copy_(s, non_blocking=True)
+            y = F.infer_recurrent_fp32io16_forward_varlen(*stage, **kw)
+            y_host.copy_(y, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, warmup, steps, sampler=None):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if sampler:
+            sampler.timed = True
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        barrier()
+        if sampler:
+            sampler.timed = False
+        ms = start.elapsed_time(stop)
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
+    sampler.start()
+    ms = timed(device_step, args.warmup, args.steps, sampler)
+    sampler.stop()
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_ms = timed(e2e_step, 1, e2e_steps)
+
+    tokens_per_step = B * DECODE_STEPS_PER_STEP * world
+    value = tokens_per_step * args.steps / (ms * 1e-3)
+    e2e_value = tokens_per_step * e2e_steps / (e2e_ms * 1e-3)
+    launches = args.steps * DECODE_STEPS_PER_STEP
+    launch_s = ms * 1e-3 / launches
+    peak, peak_kind = _peaks()
+    achieved = BYTES_PER_LAUNCH / launch_s / 1e9
+
+    if rank == 0:
+        cpu = _cpu_baseline(32) if world == 1 else None
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"recurrent decode B={B} H={H} D={D} per GPU, bf16 tokens, fp32 state, "
+                                   f"{DECODE_STEPS_PER_STEP} consecutive decode steps per step",
+                       "global_sequences": B * world, "parallelism": f"sequences sharded over {world} GPU(s)",
+                       "l2": "no flush: per-launch working set (134 MB state + 7 MB tokens) exceeds the 126 MB L2"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "peak_source": f"of {peak_kind}", "kernel": "wkv7_recurrent_d64_kernel",
+                         "algorithmic_bytes_per_launch": BYTES_PER_LAUNCH, "us_per_launch": launch_s * 1e6},
+            "e2e": {"value": e2e_value, "unit": "tokens/s",
+                    "h2d_bytes_per_step": 6 * B * H * D * 2 * DECODE_STEPS_PER_STEP,
+                    "d2h_bytes_per_step": B * H * D * 2 * DECODE_STEPS_PER_STEP, "steps": e2e_steps},
+            "gpu_launches": launches,
+            "clocks": sampler.summary(),
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,17 @@
+"""flashrwkv_b200 -- B200 (sm_100a) implementation of the RWKV-7 WKV7 time-mix operators.
+
+The operator names, signatures and error behaviour follow the FlashRWKV2
+reference (`flashrwkv2.tmix.*`, contracts in its docs/kernel_api.md); the
+kernels are hand-written CUDA for sm_100a reached through the C ABI of
+include/frwkv_b200.h.  There is no CPU fallback.
+"""
+from .tmix.wkv7 import (
+    infer_recurrent_fp32io16_forward_varlen,
+    prepare_recurrent_metadata,
+)
+
+__all__ = [
+    "infer_recurrent_fp32io16_forward_varlen",
+    "prepare_recurrent_metadata",
+]
+__version__ = "0.1.0"

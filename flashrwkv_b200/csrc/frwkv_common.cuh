@@ -1,0 +1,93 @@
+// Shared helpers of the frwkv_b200 kernels: error reporting, 16-bit io types, the
+// retention transform, small PTX wrappers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "frwkv_b200.h"
+
+namespace frwkv {
+
+// ---- error reporting (thread-local message, negative return codes) -----------------------
+void set_error(const char* fmt, ...);
+void clear_error();
+
+inline int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  set_error("%s", buf);
+  return code;
+}
+
+inline int check_launch(const char* what) {
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    return fail(FRWKV_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
+  }
+  return FRWKV_OK;
+}
+
+#define FRWKV_REQUIRE(cond, ...)                              \
+  do {                                                        \
+    if (!(cond)) return ::frwkv::fail(FRWKV_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
+  } while (0)
+
+// ---- 16-bit io -----------------------------------------------------------------------------
+template <typename T>
+struct Io16;
+
+template <>
+struct Io16<__half> {
+  using pair = __half2;
+  static __device__ __forceinline__ float2 unpack(uint32_t bits) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&bits));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ float load(const __half* p) { return __half2float(*p); }
+  static __device__ __forceinline__ __half store(float x) { return __float2half_rn(x); }
+};
+
+template <>
+struct Io16<__nv_bfloat16> {
+  using pair = __nv_bfloat162;
+  // a bf16 is the upper half of the fp32 with the same value: unpack with shifts
+  static __device__ __forceinline__ float2 unpack(uint32_t bits) {
+    return make_float2(__uint_as_float(bits << 16), __uint_as_float(bits & 0xffff0000u));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ __nv_bfloat16 store(float x) { return __float2bfloat16_rn(x); }
+};
+
+// ---- retention transform -------------------------------------------------------------------
+// w = exp(-exp(-0.5) * sigmoid(x)), written in the reference's exp2 form
+// (csrc/sm120/tmix/wkv7/recurrent_decay.cuh:18-22 of the reference) so that both
+// implementations round the same way.
+__device__ __forceinline__ float retention(float decay_logit) {
+  return exp2f(-0.8750387749145276f / (1.0f + exp2f(-1.4426950408889634f * decay_logit)));
+}
+
+// d log(w) / dx = -exp(-0.5) * s * (1 - s), s = sigmoid(x) (recurrent_decay.cuh:27-32).
+__device__ __forceinline__ float retention_log_derivative(float decay_logit) {
+  const float s = 1.0f / (1.0f + exp2f(-1.4426950408889634f * decay_logit));
+  return -0.6065306597126334f * s * (1.0f - s);
+}
+
+__device__ __forceinline__ float quiet_nan() { return __int_as_float(0x7fffffff); }
+
+}  // namespace frwkv

@@ -1,0 +1,94 @@
+// Device-side validation of packed-sequence metadata.
+//
+// Two launches on the caller's stream: the first snapshots cu_seqlens and
+// state_indices and clears the status words; the second validates the SNAPSHOT
+// (so a caller that mutates its tensors afterwards cannot invalidate what the
+// consumers read) and ORs error bits into status[0], the longest sequence into
+// status[1].  The duplicate-slot scan is quadratic like the reference's but is
+// spread over many blocks instead of one.
+//
+// Replaces validate_recurrent_metadata_kernel of the reference
+// (csrc/validation/recurrent_metadata.cu:22-97).
+
+#include "frwkv_common.cuh"
+
+namespace frwkv {
+namespace {
+
+__global__ void snapshot_metadata_kernel(const int* __restrict__ cu, const int* __restrict__ idx, int n,
+                                         int* __restrict__ status, int* __restrict__ cu_snap,
+                                         int* __restrict__ idx_snap) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) idx_snap[i] = idx[i];
+  if (i <= n) cu_snap[i] = cu[i];
+  if (i == 0) {
+    status[0] = 0;
+    status[1] = 0;
+  }
+}
+
+__global__ void validate_metadata_kernel(const int* __restrict__ cu, const int* __restrict__ idx, int n,
+                                         int total_tokens, int pool_size, int* __restrict__ status) {
+  __shared__ int s_error;
+  __shared__ int s_maxlen;
+  if (threadIdx.x == 0) {
+    s_error = 0;
+    s_maxlen = 0;
+  }
+  __syncthreads();
+  int error = 0, maxlen = 0;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    if (i == 0 && (cu[0] != 0 || cu[n] != total_tokens)) error |= FRWKV_META_INVALID_ENDPOINT;
+    const int t0 = cu[i], t1 = cu[i + 1];
+    if (t0 < 0 || t1 <= t0 || t1 > total_tokens) {
+      error |= FRWKV_META_INVALID_RANGE;
+    } else {
+      maxlen = max(maxlen, t1 - t0);
+    }
+    const int slot = idx[i];
+    if (slot < 0 || slot >= pool_size) {
+      error |= FRWKV_META_INVALID_SLOT;
+    } else {
+      for (int e = 0; e < i; ++e) {
+        if (idx[e] == slot) {
+          error |= FRWKV_META_DUPLICATE_SLOT;
+          break;
+        }
+      }
+    }
+  }
+  if (error) atomicOr(&s_error, error);
+  atomicMax(&s_maxlen, maxlen);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (s_error) atomicOr(&status[0], s_error);
+    atomicMax(&status[1], s_maxlen);
+  }
+}
+
+}  // namespace
+}  // namespace frwkv
+
+extern "C" int frwkv_validate_recurrent_metadata(const int32_t* cu_seqlens, const int32_t* state_indices,
+                                                 int num_sequences, int total_tokens, int state_pool_size,
+                                                 int32_t* status, int32_t* cu_snapshot,
+                                                 int32_t* idx_snapshot, frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(cu_seqlens && state_indices && status && cu_snapshot && idx_snapshot,
+                "validate_recurrent_metadata: null pointer argument");
+  FRWKV_REQUIRE(num_sequences > 0 && num_sequences <= 65535,
+                "state_indices must contain at most 65535 sequences");
+  FRWKV_REQUIRE(total_tokens > 0, "total_tokens must be positive and fit in int32");
+  FRWKV_REQUIRE(state_pool_size > 0, "state_pool_size must be positive and fit in int32");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  constexpr int threads = 128;
+  const int blocks = (num_sequences + 1 + threads - 1) / threads;
+  snapshot_metadata_kernel<<<blocks, threads, 0, s>>>(cu_seqlens, state_indices, num_sequences, status,
+                                                      cu_snapshot, idx_snapshot);
+  int rc = check_launch("snapshot_metadata_kernel");
+  if (rc != FRWKV_OK) return rc;
+  validate_metadata_kernel<<<(num_sequences + threads - 1) / threads, threads, 0, s>>>(
+      cu_snapshot, idx_snapshot, num_sequences, total_tokens, state_pool_size, status);
+  return check_launch("validate_metadata_kernel");
+}

@@ -1,0 +1,234 @@
+// WKV7 recurrence over packed sequences, fp32 state pool updated in place (head size 64).
+//
+// Work decomposition.  One warp owns one half (32 value columns) of one
+// (sequence, head) state for the whole sequence; the two halves of a head never
+// exchange data, so there is no shared memory and no block-level barrier.
+// Inside the warp, lane = kg*8 + vq: the lane holds key rows [16*kg, 16*kg+16)
+// of value columns [4*vq, 4*vq+4) -- 16 float4 registers.  A row segment of the
+// eight lanes with equal kg is 128 contiguous bytes, so every state load and
+// store instruction moves four full 128-byte lines, and the 16 independent
+// 128-bit loads per lane are issued back to back before the first use.
+//
+// One sweep per token.  With S' = diag(w) S + b sa^T + k v^T,
+//     y / scale = S'^T r = S^T (w*r) + (b.r) sa + (k.r) v,
+// so both matrix-vector products (S^T a and S^T (w*r)) read the OLD state in the
+// same pass; the key-direction sums finish with two xor-shuffles (over kg), then
+// the update streams out of the registers.  A decode step (one token per
+// sequence) therefore reads and writes each state element exactly once.
+//
+// Replaces wkv_fp32_v2_kernel / wkv_fp32_v2_small_warp_kernel of the reference
+// (csrc/sm120/tmix/wkv7/infer_recurrent_fp32io16_forward_varlen.cu:90-275).
+
+#include "frwkv_common.cuh"
+
+namespace frwkv {
+namespace {
+
+constexpr int kD = 64;
+constexpr int kWarpsPerBlock = 4;
+constexpr int kThreads = kWarpsPerBlock * 32;
+
+__device__ __forceinline__ void load16(const void* p, uint32_t (&w)[8]) {
+  const uint4* q = reinterpret_cast<const uint4*>(p);
+  const uint4 lo = __ldg(q), hi = __ldg(q + 1);
+  w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w;
+  w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
+}
+
+template <typename io_t>
+__global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
+    const int* __restrict__ cu_seqlens, const int* __restrict__ state_indices,
+    const int* __restrict__ metadata_status, float* __restrict__ state_pool,
+    const io_t* __restrict__ r_ptr, const io_t* __restrict__ w_ptr, const io_t* __restrict__ k_ptr,
+    const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr, const io_t* __restrict__ b_ptr,
+    const io_t* __restrict__ bias_ptr, io_t* __restrict__ y_ptr, float* __restrict__ y32_ptr,
+    long long num_units, int num_heads, long long output_elements, float scale) {
+  using IO = Io16<io_t>;
+  if (metadata_status != nullptr && metadata_status[0] != 0) {
+    // fail closed: NaN output, state untouched
+    const io_t nan16 = IO::store(quiet_nan());
+    for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < output_elements;
+         i += (long long)gridDim.x * kThreads) {
+      y_ptr[i] = nan16;
+      if (y32_ptr != nullptr) y32_ptr[i] = quiet_nan();
+    }
+    return;
+  }
+  const int lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (unit >= num_units) return;
+  const int vhalf = (int)(unit & 1);
+  const long long seq_head = unit >> 1;
+  const int head = (int)(seq_head % num_heads);
+  const int seq = (int)(seq_head / num_heads);
+  const int kg = lane >> 3, vq = lane & 7;
+  const int row0 = kg * 16;
+  const int col0 = vhalf * 32 + vq * 4;
+
+  const int t_begin = cu_seqlens[seq];
+  const int t_end = cu_seqlens[seq + 1];
+  const int slot = state_indices[seq];
+
+  float* sbase = state_pool + ((long long)slot * num_heads + head) * (kD * kD) + row0 * kD + col0;
+  float4 s[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s[i] = *reinterpret_cast<const float4*>(sbase + i * kD);
+
+  for (int t = t_begin; t < t_end; ++t) {
+    const long long tb = ((long long)t * num_heads + head) * kD;
+    uint32_t rr[8], ww[8], kk[8], aa[8], bb[8];
+    load16(w_ptr + tb + row0, ww);
+    load16(a_ptr + tb + row0, aa);
+    load16(r_ptr + tb + row0, rr);
+    load16(b_ptr + tb + row0, bb);
+    load16(k_ptr + tb + row0, kk);
+    const uint2 vraw = __ldg(reinterpret_cast<const uint2*>(v_ptr + tb + col0));
+
+    float wv[16];
+    if (bias_ptr != nullptr) {
+      uint32_t bs[8];
+      load16(bias_ptr + head * kD + row0, bs);
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        const float2 x = IO::unpack(ww[p]), bx = IO::unpack(bs[p]);
+        wv[2 * p] = retention(x.x + bx.x);
+        wv[2 * p + 1] = retention(x.y + bx.y);
+      }
+    } else {
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        const float2 x = IO::unpack(ww[p]);
+        wv[2 * p] = retention(x.x);
+        wv[2 * p + 1] = retention(x.y);
+      }
+    }
+
+    float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f;
+    float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+    float br = 0.f, kr = 0.f;
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      const float2 a2 = IO::unpack(aa[p]), r2 = IO::unpack(rr[p]);
+      const float2 b2 = IO::unpack(bb[p]), k2 = IO::unpack(kk[p]);
+      br = fmaf(b2.x, r2.x, br);
+      br = fmaf(b2.y, r2.y, br);
+      kr = fmaf(k2.x, r2.x, kr);
+      kr = fmaf(k2.y, r2.y, kr);
+      {
+        const float4 q = s[2 * p];
+        const float wr = wv[2 * p] * r2.x;
+        sa0 = fmaf(a2.x, q.x, sa0); sa1 = fmaf(a2.x, q.y, sa1);
+        sa2 = fmaf(a2.x, q.z, sa2); sa3 = fmaf(a2.x, q.w, sa3);
+        y0 = fmaf(wr, q.x, y0); y1 = fmaf(wr, q.y, y1);
+        y2 = fmaf(wr, q.z, y2); y3 = fmaf(wr, q.w, y3);
+      }
+      {
+        const float4 q = s[2 * p + 1];
+        const float wr = wv[2 * p + 1] * r2.y;
+        sa0 = fmaf(a2.y, q.x, sa0); sa1 = fmaf(a2.y, q.y, sa1);
+        sa2 = fmaf(a2.y, q.z, sa2); sa3 = fmaf(a2.y, q.w, sa3);
+        y0 = fmaf(wr, q.x, y0); y1 = fmaf(wr, q.y, y1);
+        y2 = fmaf(wr, q.z, y2); y3 = fmaf(wr, q.w, y3);
+      }
+    }
+    // finish the key-direction sums across the four row groups (lane bits 3 and 4)
+#pragma unroll
+    for (int m = 8; m <= 16; m <<= 1) {
+      sa0 += __shfl_xor_sync(0xffffffffu, sa0, m); sa1 += __shfl_xor_sync(0xffffffffu, sa1, m);
+      sa2 += __shfl_xor_sync(0xffffffffu, sa2, m); sa3 += __shfl_xor_sync(0xffffffffu, sa3, m);
+      y0 += __shfl_xor_sync(0xffffffffu, y0, m); y1 += __shfl_xor_sync(0xffffffffu, y1, m);
+      y2 += __shfl_xor_sync(0xffffffffu, y2, m); y3 += __shfl_xor_sync(0xffffffffu, y3, m);
+      br += __shfl_xor_sync(0xffffffffu, br, m); kr += __shfl_xor_sync(0xffffffffu, kr, m);
+    }
+    const float2 v01 = IO::unpack(vraw.x), v23 = IO::unpack(vraw.y);
+
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      const float2 b2 = IO::unpack(bb[p]), k2 = IO::unpack(kk[p]);
+      {
+        float4 q = s[2 * p];
+        const float wi = wv[2 * p];
+        q.x = fmaf(wi, q.x, fmaf(b2.x, sa0, k2.x * v01.x));
+        q.y = fmaf(wi, q.y, fmaf(b2.x, sa1, k2.x * v01.y));
+        q.z = fmaf(wi, q.z, fmaf(b2.x, sa2, k2.x * v23.x));
+        q.w = fmaf(wi, q.w, fmaf(b2.x, sa3, k2.x * v23.y));
+        s[2 * p] = q;
+      }
+      {
+        float4 q = s[2 * p + 1];
+        const float wi = wv[2 * p + 1];
+        q.x = fmaf(wi, q.x, fmaf(b2.y, sa0, k2.y * v01.x));
+        q.y = fmaf(wi, q.y, fmaf(b2.y, sa1, k2.y * v01.y));
+        q.z = fmaf(wi, q.z, fmaf(b2.y, sa2, k2.y * v23.x));
+        q.w = fmaf(wi, q.w, fmaf(b2.y, sa3, k2.y * v23.y));
+        s[2 * p + 1] = q;
+      }
+    }
+    if (kg == 0) {
+      const float o0 = scale * fmaf(kr, v01.x, fmaf(br, sa0, y0));
+      const float o1 = scale * fmaf(kr, v01.y, fmaf(br, sa1, y1));
+      const float o2 = scale * fmaf(kr, v23.x, fmaf(br, sa2, y2));
+      const float o3 = scale * fmaf(kr, v23.y, fmaf(br, sa3, y3));
+      uint2 packed;
+      packed.x = IO::pack(o0, o1);
+      packed.y = IO::pack(o2, o3);
+      *reinterpret_cast<uint2*>(y_ptr + tb + col0) = packed;
+      if (y32_ptr != nullptr) {
+        *reinterpret_cast<float4*>(y32_ptr + tb + col0) = make_float4(o0, o1, o2, o3);
+      }
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < 16; ++i) *reinterpret_cast<float4*>(sbase + i * kD) = s[i];
+}
+
+template <typename io_t>
+int launch(const int* cu, const int* idx, const int* status, float* state, const void* r,
+           const void* w, const void* k, const void* v, const void* a, const void* b,
+           const void* bias, void* y, float* y32, int total_tokens, int num_sequences, int num_heads,
+           float scale, cudaStream_t stream) {
+  const long long units = (long long)num_sequences * num_heads * 2;
+  const long long blocks = (units + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  wkv7_recurrent_d64_kernel<io_t><<<(unsigned)blocks, kThreads, 0, stream>>>(
+      cu, idx, status, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w),
+      static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),
+      static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, units,
+      num_heads, (long long)total_tokens * num_heads * kD, scale);
+  return check_launch("wkv7_recurrent_d64_kernel");
+}
+
+}  // namespace
+}  // namespace frwkv
+
+extern "C" int frwkv_wkv7_recurrent_fp32io16_forward_varlen(
+    const int32_t* cu_seqlens, const int32_t* state_indices, const int32_t* metadata_status,
+    float* state_pool, const void* r, const void* decay_logits, const void* k, const void* v,
+    const void* a, const void* b, const void* decay_bias, void* y, float* y_fp32,
+    int total_tokens, int num_sequences, int num_heads, int head_size, int max_seqlen,
+    int io_dtype, float scale, frwkv_stream_t stream) {
+  using namespace frwkv;
+  (void)max_seqlen;  // one kernel serves every sequence length
+  clear_error();
+  FRWKV_REQUIRE(cu_seqlens && state_indices && state_pool && r && decay_logits && k && v && a && b && y,
+                "wkv7_recurrent: null pointer argument");
+  FRWKV_REQUIRE(total_tokens > 0 && num_heads > 0, "wkv7_recurrent: sizes must be positive");
+  FRWKV_REQUIRE(num_sequences > 0 && num_sequences <= 65535,
+                "wkv7_recurrent: state_indices must contain 1..65535 sequences");
+  if (head_size != 64) {
+    return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_recurrent: head size %d is not built (only 64)", head_size);
+  }
+  const long long blocks = ((long long)num_sequences * num_heads * 2 + 3) / 4;
+  FRWKV_REQUIRE(blocks <= 0x7fffffffLL, "wkv7_recurrent: too many (sequence, head) pairs");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (io_dtype == FRWKV_DTYPE_BF16) {
+    return launch<__nv_bfloat16>(cu_seqlens, state_indices, metadata_status, state_pool, r, decay_logits, k,
+                                 v, a, b, decay_bias, y, y_fp32, total_tokens, num_sequences, num_heads,
+                                 scale, s);
+  }
+  if (io_dtype == FRWKV_DTYPE_FP16) {
+    return launch<__half>(cu_seqlens, state_indices, metadata_status, state_pool, r, decay_logits, k, v, a,
+                          b, decay_bias, y, y_fp32, total_tokens, num_sequences, num_heads, scale, s);
+  }
+  return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_recurrent: token tensors must be float16 or bfloat16");
+}

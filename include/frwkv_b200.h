@@ -1,0 +1,90 @@
+/*
+ * frwkv_b200 -- C ABI of the B200 (sm_100a) WKV7 time-mix kernels.
+ *
+ * Every entry point takes raw device pointers and sizes, launches on the given
+ * stream and returns immediately (no synchronisation, no allocation, no
+ * exceptions).  Return value: FRWKV_OK, or a negative FRWKV_ERR_* code with a
+ * message available from frwkv_last_error() on the calling thread.  All tensors
+ * are contiguous.  "io16" tensors are fp16 or bf16 according to io_dtype.
+ *
+ * Each declaration names the interface of the FlashRWKV2 reference it replaces
+ * (paths inside the reference project).
+ */
+#ifndef FRWKV_B200_H_
+#define FRWKV_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* frwkv_stream_t; /* == cudaStream_t */
+
+enum {
+  FRWKV_DTYPE_FP16 = 0,
+  FRWKV_DTYPE_BF16 = 1,
+};
+
+enum {
+  FRWKV_OK = 0,
+  FRWKV_ERR_INVALID_ARGUMENT = -1, /* null pointer, non-positive size, size over a limit */
+  FRWKV_ERR_UNSUPPORTED = -2,      /* shape or dtype this build has no kernel for */
+  FRWKV_ERR_CUDA = -3,             /* the CUDA runtime rejected the launch */
+};
+
+/* Bits written to the metadata status word (0 = valid).  Same values as the
+ * reference's MetadataError (csrc/validation/recurrent_metadata.cu:15-20). */
+enum {
+  FRWKV_META_INVALID_ENDPOINT = 1,
+  FRWKV_META_INVALID_RANGE = 2,
+  FRWKV_META_INVALID_SLOT = 4,
+  FRWKV_META_DUPLICATE_SLOT = 8,
+};
+
+/* ABI version of this header (bumped on any signature change). */
+int frwkv_abi_version(void);
+
+/* Message of the last error returned on this thread ("" if none). */
+const char* frwkv_last_error(void);
+
+/*
+ * Validate packed-sequence metadata on the device and snapshot it.
+ * Replaces prepare_recurrent_metadata_cuda / validate_recurrent_metadata_kernel
+ * (csrc/validation/recurrent_metadata.cu:22-128).
+ *   cu_seqlens [B+1], state_indices [B] int32; 1 <= B <= 65535.
+ *   status [2] int32: status[0] = OR of FRWKV_META_* bits, status[1] = longest
+ *   sequence length found.  cu_snapshot [B+1], idx_snapshot [B] receive copies
+ *   taken before validation (the values later kernels must use).
+ */
+int frwkv_validate_recurrent_metadata(const int32_t* cu_seqlens, const int32_t* state_indices,
+                                      int num_sequences, int total_tokens, int state_pool_size,
+                                      int32_t* status, int32_t* cu_snapshot, int32_t* idx_snapshot,
+                                      frwkv_stream_t stream);
+
+/*
+ * WKV7 recurrence over packed sequences with an fp32 state pool updated in place.
+ * Replaces recurrent_fp32_from_decay_logits_cuda
+ * (csrc/sm120/tmix/wkv7/infer_recurrent_fp32io16_forward_varlen.cu:448-508).
+ *   per token:  w = exp(-exp(-0.5) * sigmoid(decay_logits + decay_bias))
+ *               sa = S^T a ; S = diag(w) S + b sa^T + k v^T ; y = scale * S^T r
+ *   r, decay_logits, k, v, a, b, y : io16 [total_tokens, H, D]
+ *   state_pool : fp32 [slots, H, D, D] (key row, value column)
+ *   decay_bias : io16 [H, D] or NULL;  y_fp32 : fp32 [total_tokens, H, D] or NULL
+ *     (the unrounded outputs, for precision checks)
+ *   metadata_status : int32 device word; when *metadata_status != 0 the kernel
+ *     fills y with NaN and leaves the state pool untouched.
+ *   head_size must be 64.
+ */
+int frwkv_wkv7_recurrent_fp32io16_forward_varlen(
+    const int32_t* cu_seqlens, const int32_t* state_indices, const int32_t* metadata_status,
+    float* state_pool, const void* r, const void* decay_logits, const void* k, const void* v,
+    const void* a, const void* b, const void* decay_bias, void* y, float* y_fp32,
+    int total_tokens, int num_sequences, int num_heads, int head_size, int max_seqlen,
+    int io_dtype, float scale, frwkv_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FRWKV_B200_H_ */

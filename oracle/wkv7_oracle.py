@@ -83,20 +83,26 @@ def retention(logits) -> np.ndarray:
 
 def forward(r, decay_logits, k, v, a, b, *, state_pool, cu_seqlens, state_indices=None,
             scale: float = 1.0, decay_bias=None, chunks=None, want_state_dot_a: bool = False,
-            double: bool = True):
+            double: bool = True, inplace: bool = False):
     """Packed varlen WKV7 forward.
 
     Returns a dict with ``y`` [N,H,D], ``state_pool`` (updated copy), and, when
     ``chunks=(seq_chunk_offsets, chunk_starts, chunk_ends)`` is given,
     ``boundary`` [Cn,H,D,D] (state before each chunk); ``state_dot_a`` [N,H,D]
-    when requested.  ``double`` selects float64 accumulation.
+    when requested.  ``double`` selects float64 accumulation.  ``inplace`` updates a
+    contiguous float32 ndarray ``state_pool`` directly instead of a copy.
     """
     lib = _load()
     r, w, k, v, a, b = (_f32(t) for t in (r, decay_logits, k, v, a, b))
     N, H, D = r.shape
     if D > 256:
         raise ValueError("oracle supports D <= 256")
-    pool = _f32(state_pool).copy()
+    if inplace:
+        pool = state_pool
+        if not (isinstance(pool, np.ndarray) and pool.dtype == np.float32 and pool.flags.c_contiguous):
+            raise TypeError("inplace needs a C-contiguous float32 ndarray state_pool")
+    else:
+        pool = _f32(state_pool).copy()
     cu = _i32(cu_seqlens)
     B = cu.size - 1
     idx = None if state_indices is None else _i32(state_indices)

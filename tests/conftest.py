@@ -12,6 +12,13 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
 
 
+def pytest_sessionstart(session):
+    """Build the native library, the host extension and the oracle if they are not there yet."""
+    from flashrwkv_b200 import build as native
+
+    native.build_all()
+
+
 @pytest.fixture(scope="session")
 def oracle():
     """The CPU oracle (test infrastructure); built on first use."""
