@@ -11,6 +11,7 @@ nvcc cross-compiles without a GPU, so the build works on a CPU-only machine.
 """
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
 import subprocess
@@ -48,11 +49,25 @@ def _host_cxx() -> str:
     return shutil.which("g++") or "g++"
 
 
-def _newer(target: Path, deps) -> bool:
-    if not target.exists():
-        return False
-    t = target.stat().st_mtime
-    return all(Path(d).stat().st_mtime <= t for d in deps)
+def _digest(paths, extra=()) -> str:
+    h = hashlib.sha256()
+    for p in sorted(str(x) for x in paths):
+        h.update(Path(p).name.encode())
+        h.update(Path(p).read_bytes())
+    for e in extra:
+        h.update(str(e).encode())
+    return h.hexdigest()
+
+
+def _up_to_date(target: Path, digest: str) -> bool:
+    """A built file is current when its stamp (a hash of its sources and flags) matches; file times
+    are not used because copies of the tree do not always keep them."""
+    stamp = target.with_suffix(target.suffix + ".stamp")
+    return target.exists() and stamp.exists() and stamp.read_text().strip() == digest
+
+
+def _write_stamp(target: Path, digest: str) -> None:
+    target.with_suffix(target.suffix + ".stamp").write_text(digest + "\n")
 
 
 def _run(cmd, verbose):
@@ -69,6 +84,9 @@ def _run(cmd, verbose):
 def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
     """Compile the kernels and the C ABI into libfrwkv_b200.so (one nvcc call per source, then link)."""
     headers = list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h"))
+    lib_digest = _digest([CSRC / n for n in CUDA_SOURCES] + headers, NVCC_FLAGS)
+    if not force and not ptxas_info and _up_to_date(LIB, lib_digest):
+        return LIB
     objdir = PKG / "build"
     objdir.mkdir(exist_ok=True)
     objs = []
@@ -76,15 +94,17 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
         src = CSRC / name
         obj = objdir / (src.stem + ".o")
         objs.append(obj)
-        if not force and _newer(obj, [src, *headers]):
+        obj_digest = _digest([src] + headers, NVCC_FLAGS)
+        if not force and not ptxas_info and _up_to_date(obj, obj_digest):
             continue
         flags = list(NVCC_FLAGS)
         if ptxas_info:
             flags += ["-Xptxas", "-v"]
         _run([_nvcc(), *flags, "-ccbin", _host_cxx(), f"-I{INCLUDE}", f"-I{CSRC}", "-c", src, "-o", obj],
              verbose or ptxas_info)
-    if force or not _newer(LIB, objs):
-        _run([_nvcc(), "-shared", "-ccbin", _host_cxx(), "-o", LIB, *objs], verbose)
+        _write_stamp(obj, obj_digest)
+    _run([_nvcc(), "-shared", "-ccbin", _host_cxx(), "-o", LIB, *objs], verbose)
+    _write_stamp(LIB, lib_digest)
     return LIB
 
 
@@ -100,7 +120,8 @@ def build_torch_ext(force: bool = False, verbose: bool = False) -> Path:
 
     out = torch_ext_path()
     src = CSRC / "torch_binding.cpp"
-    if not force and _newer(out, [src, LIB, *INCLUDE.glob("*.h")]):
+    digest = _digest([src, *INCLUDE.glob("*.h")], [torch.__version__])
+    if not force and _up_to_date(out, digest):
         return out
     cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
     includes = [*cpp_extension.include_paths(), sysconfig.get_paths()["include"], f"{cuda_home}/include",
@@ -115,6 +136,7 @@ def build_torch_ext(force: bool = False, verbose: bool = False) -> Path:
            "-ltorch", "-ltorch_python", f"-L{cuda_home}/lib64", "-lcudart",
            "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
     _run(cmd, verbose)
+    _write_stamp(out, digest)
     return out
 
 

@@ -32,10 +32,15 @@ DECAY_RATE = 0.6065306597126334  # exp(-0.5)
 
 def build(force: bool = False) -> Path:
     """Compile the C oracle next to its source (gcc, OpenMP)."""
+    import hashlib
+
     src = _HERE / "wkv7_oracle.c"
-    if force or not _LIB_PATH.exists() or _LIB_PATH.stat().st_mtime < src.stat().st_mtime:
+    digest = hashlib.sha256(src.read_bytes() + (_HERE / "Makefile").read_bytes()).hexdigest()
+    stamp = _HERE / "liboracle_wkv7.so.stamp"
+    if force or not _LIB_PATH.exists() or not stamp.exists() or stamp.read_text().strip() != digest:
         subprocess.run(["make", "-C", str(_HERE), "-B", "liboracle_wkv7.so"], check=True,
                        stdout=subprocess.DEVNULL)
+        stamp.write_text(digest + "\n")
     return _LIB_PATH
 
 
