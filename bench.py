@@ -264,7 +264,7 @@ def run_b200(args):
     ms = timed(device_step, args.warmup, args.steps, sampler)
     sampler.stop()
     e2e_steps = max(1, min(args.steps, 5))
-    e2e_ms = timed(e2e_step, 1, e2e_steps)
+    e2e_ms = timed(e2e_step, 1, e2e_steps) if not args.kernel_only else float("nan")
 
     tokens_per_step = B * DECODE_STEPS_PER_STEP * world
     value = tokens_per_step * args.steps / (ms * 1e-3)
@@ -275,7 +275,7 @@ def run_b200(args):
     achieved = BYTES_PER_LAUNCH / launch_s / 1e9
 
     if rank == 0:
-        cpu = _cpu_baseline(32) if world == 1 else None
+        cpu = _cpu_baseline(32) if world == 1 and not args.kernel_only else None
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
@@ -307,6 +307,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU-baseline legs (for profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
