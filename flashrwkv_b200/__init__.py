@@ -5,13 +5,18 @@ reference (`flashrwkv2.tmix.*`, contracts in its docs/kernel_api.md); the
 kernels are hand-written CUDA for sm_100a reached through the C ABI of
 include/frwkv_b200.h.  There is no CPU fallback.
 """
+from .rl_infctx.wkv7 import rl_infctx_chunk_fp32io16, rl_infctx_chunk_fp32io16_factor_recompute
 from .tmix.wkv7 import (
+    infer_chunk_bf16_forward_varlen,
     infer_recurrent_fp32io16_forward_varlen,
     prepare_recurrent_metadata,
 )
 
 __all__ = [
+    "infer_chunk_bf16_forward_varlen",
     "infer_recurrent_fp32io16_forward_varlen",
     "prepare_recurrent_metadata",
+    "rl_infctx_chunk_fp32io16",
+    "rl_infctx_chunk_fp32io16_factor_recompute",
 ]
 __version__ = "0.1.0"

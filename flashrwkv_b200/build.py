@@ -29,6 +29,8 @@ CUDA_SOURCES = [
     "frwkv_capi.cu",
     "metadata.cu",
     "wkv7_recurrent.cu",
+    "umma_selftest.cu",
+    "wkv7_chunk_fwd.cu",
 ]
 
 NVCC_FLAGS = [

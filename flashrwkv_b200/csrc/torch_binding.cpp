@@ -16,6 +16,7 @@
 #include <memory>
 #include <optional>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "frwkv_b200.h"
@@ -268,6 +269,109 @@ void recurrent_fp32_from_decay_logits(torch::Tensor cu, torch::Tensor idx, torch
       io_dtype_of(r), static_cast<float>(scale), current_stream(state)));
 }
 
+// ---- chunked forward ---------------------------------------------------------------------------------
+void check_chunk_tables(const torch::Tensor& sco, const torch::Tensor& cs, const torch::Tensor& ce,
+                        const torch::Tensor& ref) {
+  const std::pair<const torch::Tensor*, const char*> all[] = {
+      {&sco, "sequence_chunk_offsets"}, {&cs, "chunk_token_starts"}, {&ce, "chunk_token_ends"}};
+  for (const auto& item : all) {
+    check_cuda_contiguous(*item.first, item.second);
+    TORCH_CHECK(item.first->scalar_type() == torch::kInt32, item.second, " must be int32");
+    TORCH_CHECK(item.first->dim() == 1, item.second, " must be one-dimensional");
+    TORCH_CHECK(item.first->device() == ref.device(), item.second, " must be on the token device");
+  }
+  TORCH_CHECK(sco.numel() >= 2, "sequence_chunk_offsets must have shape [B+1]");
+  TORCH_CHECK(cs.numel() > 0 && cs.numel() == ce.numel(), "chunk_token_starts and chunk_token_ends must have shape [Cn]");
+}
+
+// Runs build + scan.  `state` [slots,H,64,64] fp32 is updated in place (slot = state_indices[s], or s when
+// state_indices is None).  Returns the device error flag (int32[1]; non-zero = a tensor-core wait ran out).
+torch::Tensor wkv7_chunk_forward(torch::Tensor sco, torch::Tensor cs, torch::Tensor ce, torch::Tensor state,
+                                 torch::Tensor r, torch::Tensor w, torch::Tensor k, torch::Tensor v, torch::Tensor a,
+                                 torch::Tensor b, torch::Tensor output, double scale,
+                                 std::optional<torch::Tensor> decay_bias, std::optional<torch::Tensor> state_indices,
+                                 std::optional<torch::Tensor> boundary, std::optional<torch::Tensor> output_fp32,
+                                 std::optional<torch::Tensor> metadata_status) {
+  check_chunk_tables(sco, cs, ce, r);
+  const std::pair<const torch::Tensor*, const char*> toks[] = {{&r, "r"}, {&w, "decay_logits"}, {&k, "k"},
+                                                               {&v, "v"}, {&a, "a"},           {&b, "b"},
+                                                               {&output, "output"}};
+  for (const auto& item : toks) {
+    check_cuda_contiguous(*item.first, item.second);
+    TORCH_CHECK(item.first->device() == r.device(), item.second, " must share r's device");
+    TORCH_CHECK(item.first->sizes() == r.sizes(), "r,decay_logits,k,v,a,b,output shape mismatch");
+    TORCH_CHECK(item.first->scalar_type() == r.scalar_type(), "r,decay_logits,k,v,a,b,output dtype mismatch");
+  }
+  TORCH_CHECK(r.scalar_type() == torch::kFloat16 || r.scalar_type() == torch::kBFloat16,
+              "token tensors must be float16 or bfloat16");
+  TORCH_CHECK(r.dim() == 3 && r.size(0) > 0 && r.size(1) > 0, "token tensors must have shape [N,H,D]");
+  TORCH_CHECK(r.size(2) == 64, "chunked WKV7 supports head size 64, got ", r.size(2));
+  TORCH_CHECK(std::isfinite(scale), "scale must be finite");
+  check_cuda_contiguous(state, "state");
+  TORCH_CHECK(state.scalar_type() == torch::kFloat32, "state must be float32");
+  TORCH_CHECK(state.dim() == 4 && state.size(1) == r.size(1) && state.size(2) == 64 && state.size(3) == 64,
+              "state must have shape [slots,H,D,D] matching the tokens");
+  TORCH_CHECK(state.device() == r.device(), "state must share r's device");
+  const int64_t B = sco.numel() - 1, Cn = cs.numel(), H = r.size(1);
+  if (state_indices.has_value()) {
+    check_cuda_contiguous(*state_indices, "state_indices");
+    TORCH_CHECK(state_indices->scalar_type() == torch::kInt32 && state_indices->dim() == 1 &&
+                    state_indices->numel() == B && state_indices->device() == r.device(),
+                "state_indices must be int32 [B] on the token device");
+  } else {
+    TORCH_CHECK(state.size(0) >= B, "state must hold one slot per sequence");
+  }
+  check_decay_bias(decay_bias, state, r);
+  if (boundary.has_value()) {
+    check_cuda_contiguous(*boundary, "boundary");
+    TORCH_CHECK(boundary->scalar_type() == torch::kFloat32 && boundary->dim() == 4 && boundary->size(0) == Cn &&
+                    boundary->size(1) == H && boundary->size(2) == 64 && boundary->size(3) == 64 &&
+                    boundary->device() == r.device(),
+                "boundary must be float32 [Cn,H,D,D] on the token device");
+  }
+  if (output_fp32.has_value()) {
+    check_cuda_contiguous(*output_fp32, "output_fp32");
+    TORCH_CHECK(output_fp32->scalar_type() == torch::kFloat32 && output_fp32->sizes() == r.sizes() &&
+                    output_fp32->device() == r.device(),
+                "output_fp32 must be a float32 tensor shaped like r");
+  }
+  if (metadata_status.has_value()) {
+    TORCH_CHECK(metadata_status->is_cuda() && metadata_status->scalar_type() == torch::kInt32 &&
+                    metadata_status->numel() >= 1 && metadata_status->device() == r.device(),
+                "metadata_status must be an int32 CUDA tensor");
+  }
+  const c10::cuda::CUDAGuard guard(r.device());
+  const size_t ws_bytes = frwkv_wkv7_chunk_workspace_bytes(static_cast<int>(Cn), static_cast<int>(H));
+  auto workspace = torch::empty({static_cast<int64_t>(ws_bytes)}, r.options().dtype(torch::kUInt8));
+  auto error_flag = torch::zeros({1}, r.options().dtype(torch::kInt32));
+  check_rc(frwkv_wkv7_chunk_fp32io16_forward(
+      sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(),
+      state_indices.has_value() ? state_indices->data_ptr<int>() : nullptr,
+      metadata_status.has_value() ? metadata_status->data_ptr<int>() : nullptr, state.data_ptr<float>(), r.data_ptr(),
+      w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
+      decay_bias.has_value() ? decay_bias->data_ptr() : nullptr, output.data_ptr(),
+      output_fp32.has_value() ? output_fp32->data_ptr<float>() : nullptr,
+      boundary.has_value() ? boundary->data_ptr<float>() : nullptr, workspace.data_ptr(), ws_bytes,
+      error_flag.data_ptr<int>(), static_cast<int>(r.size(0)), static_cast<int>(B), static_cast<int>(Cn),
+      static_cast<int>(H), 64, io_dtype_of(r), static_cast<float>(scale), current_stream(r)));
+  return error_flag;
+}
+
+// Reference-named entry (csrc/sm90/rl_infctx/wkv7/rl_infctx_chunk_fp32io16_forward.cpp:157-241 there): the
+// input state [B,H,D,D] is cloned, both strategies run the same tensor-core path.
+std::tuple<torch::Tensor, torch::Tensor> rl_infctx_chunk_fp32io16_forward(
+    torch::Tensor sco, torch::Tensor cs, torch::Tensor ce, torch::Tensor state, torch::Tensor r, torch::Tensor w,
+    torch::Tensor k, torch::Tensor v, torch::Tensor a, torch::Tensor b, int64_t strategy, double scale,
+    std::optional<torch::Tensor> decay_bias) {
+  TORCH_CHECK(strategy == 0 || strategy == 1, "strategy must be 0 (materialized) or 1 (recompute)");
+  check_cuda_contiguous(state, "state");
+  auto working = state.clone();
+  auto output = torch::empty_like(v);
+  wkv7_chunk_forward(sco, cs, ce, working, r, w, k, v, a, b, output, scale, decay_bias, std::nullopt, std::nullopt,
+                     std::nullopt, std::nullopt);
+  return {output, working};
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -289,4 +393,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("v"), py::arg("a"), py::arg("b"), py::arg("output"), py::arg("scale"),
         py::arg("decay_bias") = py::none(), py::arg("validated_metadata") = py::none(),
         py::arg("max_seqlen") = -1, py::arg("output_fp32") = py::none());
+  m.def("wkv7_chunk_forward", &wkv7_chunk_forward, py::arg("sequence_chunk_offsets"),
+        py::arg("chunk_token_starts"), py::arg("chunk_token_ends"), py::arg("state"), py::arg("r"),
+        py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"), py::arg("output"),
+        py::arg("scale") = 1.0, py::arg("decay_bias") = py::none(), py::arg("state_indices") = py::none(),
+        py::arg("boundary") = py::none(), py::arg("output_fp32") = py::none(),
+        py::arg("metadata_status") = py::none());
+  m.def("rl_infctx_chunk_fp32io16_forward", &rl_infctx_chunk_fp32io16_forward, py::arg("sequence_chunk_offsets"),
+        py::arg("chunk_token_starts"), py::arg("chunk_token_ends"), py::arg("state"), py::arg("r"),
+        py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"), py::arg("strategy") = 1,
+        py::arg("scale") = 1.0, py::arg("decay_bias") = py::none());
 }

@@ -1,0 +1,158 @@
+// Thin inline-PTX layer over the sm_100a tensor-core path: tensor memory (TMEM)
+// allocation, tcgen05.mma with shared-memory descriptors, tcgen05.ld/st, mbarriers
+// with bounded waits, and 1-D bulk copies (cp.async.bulk).
+//
+// Shared-memory operand format used throughout this library ("chunk-major tile"):
+// a logical matrix X[row][col] of fp32 values is stored as
+//     byte offset(row, col) = (col / 4) * chunk_stride + row * 16 + (col % 4) * 4
+// i.e. 16-byte column chunks, all rows of one chunk contiguous.  With no swizzle
+// this one physical format serves both operand orientations of tcgen05.mma:
+//   * contraction over col ("K-major"): 8 rows x 16 B form a core matrix, the two
+//     core matrices of one K=8 step are chunk_stride apart (leading byte offset),
+//     8-row groups are 128 B apart (stride byte offset);
+//   * contraction over row ("MN-major"): 8 rows x 16 B is again a core matrix, now
+//     8 (k) x 4 (m or n); core matrices along M/N are chunk_stride apart (stride
+//     byte offset), the next K step is 128 B further.
+// A thread that owns one row writes/reads float4 chunks; consecutive rows are
+// consecutive 16-byte words, so warp accesses are bank-conflict free.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace frwkv {
+namespace umma {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- instruction descriptor (kind::tf32, fp32 accumulate) ---------------------------------
+// bits [4,6) D format (1 = f32), [7,10) A format (2 = tf32), [10,13) B format (2 = tf32),
+// bit 15 A major (0 = K, 1 = MN), bit 16 B major, [17,23) N >> 3, [24,29) M >> 4.
+__host__ __device__ constexpr uint32_t idesc_tf32(int M, int N, int a_mn_major, int b_mn_major) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) |
+         (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+}
+
+// ---- shared-memory matrix descriptor, no swizzle -------------------------------------------
+// bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
+// [46,48) descriptor version (1 on sm_100), [61,64) swizzle mode (0 = none).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+  return uint64_t((smem_addr & 0x3ffffu) >> 4) | (uint64_t((leading_bytes >> 4) & 0x3fffu) << 16) |
+         (uint64_t((stride_bytes >> 4) & 0x3fffu) << 32) | (uint64_t(1) << 46);
+}
+// operand whose contraction index is the tile's column index
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t tile_addr, uint32_t chunk_stride) {
+  return smem_desc(tile_addr, chunk_stride, 128);
+}
+// operand whose contraction index is the tile's row index
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t tile_addr, uint32_t chunk_stride) {
+  return smem_desc(tile_addr, 128, chunk_stride);
+}
+// advance of the start address for the next K = 8 step
+__device__ __forceinline__ uint32_t kstep_k_major(uint32_t chunk_stride) { return 2 * chunk_stride; }
+__device__ __forceinline__ uint32_t kstep_mn_major() { return 128; }
+
+// ---- TMEM allocation (one warp executes these) ----------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// ---- fences -----------------------------------------------------------------------------------
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// make generic-proxy shared-memory writes visible to the async proxy (tensor core / bulk copies)
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ---- MMA (issued by ONE thread) ---------------------------------------------------------------
+// D[tmem] (+)= A[smem] * B[smem];  accumulate == 0 overwrites D.
+__device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// all MMAs issued so far by this thread arrive on the mbarrier when they complete
+__device__ __forceinline__ void mma_commit(uint64_t* mbar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mbar))
+               : "memory");
+}
+
+// ---- TMEM -> registers: this warp's 32 lanes x 32 consecutive columns ------------------------
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- mbarrier -----------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* mbar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(mbar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* mbar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(mbar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* mbar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(smem_u32(mbar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait: gives up after `limit` polls and returns false (the caller records an error and
+// carries on without touching what the barrier guards); a stuck barrier can never hang the GPU.
+__device__ __forceinline__ bool mbar_wait(uint64_t* mbar, uint32_t parity, uint32_t limit = (1u << 22)) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (mbar_try_wait(mbar, parity)) return true;
+  }
+  return false;
+}
+
+// ---- 1-D bulk copy global -> shared, completion on an mbarrier (both 16-byte aligned) --------
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* mbar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(mbar))
+               : "memory");
+}
+
+// round-to-nearest fp32 -> tf32 (kept in a 32-bit container); the tensor core would otherwise truncate
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+__device__ __forceinline__ float4 to_tf32(float4 v) {
+  return make_float4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
+}
+
+}  // namespace umma
+}  // namespace frwkv

@@ -82,3 +82,7 @@ def infer_recurrent_fp32io16_forward_varlen(r, decay_logits, k, v, a, b, *, stat
 
 
 __all__ = ["infer_recurrent_fp32io16_forward_varlen", "prepare_recurrent_metadata"]
+
+from .chunk import infer_chunk_bf16_forward_varlen, make_chunk_metadata, wkv7_chunk_forward  # noqa: E402
+
+__all__ += ["infer_chunk_bf16_forward_varlen", "wkv7_chunk_forward", "make_chunk_metadata"]

@@ -13,6 +13,7 @@
 #ifndef FRWKV_B200_H_
 #define FRWKV_B200_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -82,6 +83,43 @@ int frwkv_wkv7_recurrent_fp32io16_forward_varlen(
     const void* a, const void* b, const void* decay_bias, void* y, float* y_fp32,
     int total_tokens, int num_sequences, int num_heads, int head_size, int max_seqlen,
     int io_dtype, float scale, frwkv_stream_t stream);
+
+/*
+ * Chunked WKV7 forward on the tensor cores: same recurrence and tensors as
+ * frwkv_wkv7_recurrent_fp32io16_forward_varlen, evaluated chunk by chunk (chunk length <= 64).
+ * Replaces the reference's chunk families: infer_chunk_bf16_forward_varlen_cuda
+ * (csrc/sm120/tmix/wkv7/infer_chunk_bf16_forward_varlen.cu:268-334), rl_infctx_chunk_fp32io16_forward
+ * (csrc/sm90/rl_infctx/wkv7/rl_infctx_chunk_fp32io16_forward.cpp:157-229) and the forward of
+ * statetune_recurrent_fp32io16 (csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_forward.cu:32-130).
+ *   seq_chunk_offsets [B+1], chunk_starts [Cn], chunk_ends [Cn] int32: sequence s owns chunks
+ *     [seq_chunk_offsets[s], seq_chunk_offsets[s+1]); chunk c covers tokens [chunk_starts[c], chunk_ends[c]),
+ *     at most 64 of them, consecutive chunks of a sequence being adjacent token ranges.
+ *   state_pool fp32 [slots,H,64,64]: initial state in, final state out (in place); sequence s uses slot
+ *     state_indices[s], or slot s when state_indices is NULL.
+ *   boundary fp32 [Cn,H,64,64] or NULL: receives the state at the start of every chunk.
+ *   workspace: frwkv_wkv7_chunk_workspace_bytes(Cn, H) bytes of device memory, 128-byte aligned.
+ *   error_flag: device int32 or NULL; set non-zero if a tensor-core completion wait ran out (outputs invalid).
+ *   metadata_status / y_fp32 / decay_bias / scale: as in the recurrent entry point.
+ */
+size_t frwkv_wkv7_chunk_workspace_bytes(int num_chunks, int num_heads);
+int frwkv_wkv7_chunk_fp32io16_forward(
+    const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends,
+    const int32_t* state_indices, const int32_t* metadata_status, float* state_pool, const void* r,
+    const void* decay_logits, const void* k, const void* v, const void* a, const void* b, const void* decay_bias,
+    void* y, float* y_fp32, float* boundary, void* workspace, size_t workspace_bytes, int32_t* error_flag,
+    int total_tokens, int num_sequences, int num_chunks, int num_heads, int head_size, int io_dtype, float scale,
+    frwkv_stream_t stream);
+
+/*
+ * Diagnostic: D[128][n] = A[128][64] * B[n][64]^T through one tcgen05.mma (kind::tf32) chain, with A and B
+ * staged in shared memory in the given orientation (0 = contraction over tile columns, 1 = over tile rows)
+ * and chunk stride in bytes.  No counterpart in the reference; used by the tests to pin the descriptor
+ * encodings the chunk kernels rely on.  error_flag (device int32) is set to 1 if the MMA never completed.
+ * a_raw_shift >= 0 turns the A region into a layout probe (word i holds (i >> shift) & 2047); -1 = off.
+ */
+int frwkv_selftest_umma(const float* a, const float* b, float* d, int n, int a_mn_major, int b_mn_major,
+                        int a_chunk_stride, int b_chunk_stride, int a_raw_shift, int32_t* error_flag,
+                        frwkv_stream_t stream);
 
 #ifdef __cplusplus
 }
