@@ -5,16 +5,13 @@
 // Shared-memory operand format used throughout this library ("chunk-major tile"):
 // a logical matrix X[row][col] of fp32 values is stored as
 //     byte offset(row, col) = (col / 4) * chunk_stride + row * 16 + (col % 4) * 4
-// i.e. 16-byte column chunks, all rows of one chunk contiguous.  With no swizzle
-// this one physical format serves both operand orientations of tcgen05.mma:
-//   * contraction over col ("K-major"): 8 rows x 16 B form a core matrix, the two
-//     core matrices of one K=8 step are chunk_stride apart (leading byte offset),
-//     8-row groups are 128 B apart (stride byte offset);
-//   * contraction over row ("MN-major"): 8 rows x 16 B is again a core matrix, now
-//     8 (k) x 4 (m or n); core matrices along M/N are chunk_stride apart (stride
-//     byte offset), the next K step is 128 B further.
-// A thread that owns one row writes/reads float4 chunks; consecutive rows are
-// consecutive 16-byte words, so warp accesses are bank-conflict free.
+// i.e. 16-byte column chunks, all rows of one chunk contiguous, no swizzle.  The tensor core
+// contracts over the tile's columns ("K-major"): 8 rows x 16 B form a core matrix, the two core
+// matrices of one K = 8 step are chunk_stride apart (leading byte offset), 8-row groups are
+// 128 B apart (stride byte offset).  kind::tf32 has no unswizzled form that contracts over the
+// rows, so a producer that owns a column of the operand writes 4-byte words into the
+// transposed tile instead; a chunk stride of 16 (mod 128) bytes keeps those writes, and the
+// float4 writes of row owners, free of bank conflicts.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -30,10 +27,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 
 // ---- instruction descriptor (kind::tf32, fp32 accumulate) ---------------------------------
 // bits [4,6) D format (1 = f32), [7,10) A format (2 = tf32), [10,13) B format (2 = tf32),
-// bit 15 A major (0 = K, 1 = MN), bit 16 B major, [17,23) N >> 3, [24,29) M >> 4.
-__host__ __device__ constexpr uint32_t idesc_tf32(int M, int N, int a_mn_major, int b_mn_major) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) |
-         (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+// bits 15 / 16 A / B major (0 = K-major, used here), [17,23) N >> 3, [24,29) M >> 4.
+__host__ __device__ constexpr uint32_t idesc_tf32(int M, int N) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
 }
 
 // ---- shared-memory matrix descriptor, no swizzle -------------------------------------------
@@ -43,17 +39,11 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr, uint32_t leadi
   return uint64_t((smem_addr & 0x3ffffu) >> 4) | (uint64_t((leading_bytes >> 4) & 0x3fffu) << 16) |
          (uint64_t((stride_bytes >> 4) & 0x3fffu) << 32) | (uint64_t(1) << 46);
 }
-// operand whose contraction index is the tile's column index
 __device__ __forceinline__ uint64_t desc_k_major(uint32_t tile_addr, uint32_t chunk_stride) {
   return smem_desc(tile_addr, chunk_stride, 128);
 }
-// operand whose contraction index is the tile's row index
-__device__ __forceinline__ uint64_t desc_mn_major(uint32_t tile_addr, uint32_t chunk_stride) {
-  return smem_desc(tile_addr, 128, chunk_stride);
-}
-// advance of the start address for the next K = 8 step
+// advance of the start address for the next K = 8 step (two 16-byte chunks)
 __device__ __forceinline__ uint32_t kstep_k_major(uint32_t chunk_stride) { return 2 * chunk_stride; }
-__device__ __forceinline__ uint32_t kstep_mn_major() { return 128; }
 
 // ---- TMEM allocation (one warp executes these) ----------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {

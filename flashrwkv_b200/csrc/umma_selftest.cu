@@ -1,7 +1,6 @@
 // Diagnostic entry point: one tcgen05.mma product through the same descriptor helpers
 // and shared-memory tile formats the WKV7 chunk kernels use.  It exists so that every
-// operand orientation (K-major / MN-major, both chunk strides) can be checked against
-// a host matrix product in isolation.
+// tile size and chunk stride can be checked against a host matrix product in isolation.
 #include "frwkv_common.cuh"
 #include "umma.cuh"
 
@@ -13,8 +12,8 @@ constexpr int kK = 64;
 
 // D[m][n] = sum_k A[m][k] * B[n][k]; A is [128][64], B is [N][64], D is [128][N] (row-major, global).
 __global__ __launch_bounds__(128, 1) void umma_selftest_kernel(const float* __restrict__ A, const float* __restrict__ B,
-                                                               float* __restrict__ Dout, int N, int a_mn_major,
-                                                               int b_mn_major, int a_chunk_stride, int b_chunk_stride,
+                                                               float* __restrict__ Dout, int N,
+                                                               int a_chunk_stride, int b_chunk_stride,
                                                                int a_raw_shift, int* __restrict__ error_flag) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t mbar;
@@ -24,10 +23,9 @@ __global__ __launch_bounds__(128, 1) void umma_selftest_kernel(const float* __re
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
 
-  // place A: logical tile X[row][col]; K-major: row = m, col = k; MN-major: row = k, col = m
+  // place A as a chunk-major tile: row = m, col = k
   for (int e = tid; e < kM * kK; e += 128) {
-    const int m = e / kK, k = e % kK;
-    const int row = a_mn_major ? k : m, col = a_mn_major ? m : k;
+    const int row = e / kK, col = e % kK;
     *reinterpret_cast<float*>(a_tile + (col >> 2) * a_chunk_stride + row * 16 + (col & 3) * 4) =
         umma::to_tf32(A[e]);
   }
@@ -38,8 +36,7 @@ __global__ __launch_bounds__(128, 1) void umma_selftest_kernel(const float* __re
       reinterpret_cast<float*>(a_tile)[i] = float((i >> a_raw_shift) & 2047);
   }
   for (int e = tid; e < N * kK; e += 128) {
-    const int n = e / kK, k = e % kK;
-    const int row = b_mn_major ? k : n, col = b_mn_major ? n : k;
+    const int row = e / kK, col = e % kK;
     *reinterpret_cast<float*>(b_tile + (col >> 2) * b_chunk_stride + row * 16 + (col & 3) * 4) =
         umma::to_tf32(B[e]);
   }
@@ -55,16 +52,12 @@ __global__ __launch_bounds__(128, 1) void umma_selftest_kernel(const float* __re
   const uint32_t tmem = tmem_base_holder;
 
   if (tid == 0) {
-    const uint32_t idesc = umma::idesc_tf32(kM, N, a_mn_major, b_mn_major);
+    const uint32_t idesc = umma::idesc_tf32(kM, N);
     const uint32_t a_addr = umma::smem_u32(a_tile), b_addr = umma::smem_u32(b_tile);
-    const uint32_t a_step = a_mn_major ? umma::kstep_mn_major() : umma::kstep_k_major(a_chunk_stride);
-    const uint32_t b_step = b_mn_major ? umma::kstep_mn_major() : umma::kstep_k_major(b_chunk_stride);
     for (int ks = 0; ks < kK / 8; ++ks) {
-      const uint64_t ad = a_mn_major ? umma::desc_mn_major(a_addr + ks * a_step, a_chunk_stride)
-                                     : umma::desc_k_major(a_addr + ks * a_step, a_chunk_stride);
-      const uint64_t bd = b_mn_major ? umma::desc_mn_major(b_addr + ks * b_step, b_chunk_stride)
-                                     : umma::desc_k_major(b_addr + ks * b_step, b_chunk_stride);
-      umma::mma_tf32_ss(tmem, ad, bd, idesc, ks > 0 ? 1u : 0u);
+      umma::mma_tf32_ss(tmem, umma::desc_k_major(a_addr + ks * umma::kstep_k_major(a_chunk_stride), a_chunk_stride),
+                        umma::desc_k_major(b_addr + ks * umma::kstep_k_major(b_chunk_stride), b_chunk_stride), idesc,
+                        ks > 0 ? 1u : 0u);
     }
     umma::mma_commit(&mbar);
   }
@@ -88,23 +81,21 @@ __global__ __launch_bounds__(128, 1) void umma_selftest_kernel(const float* __re
 }  // namespace
 }  // namespace frwkv
 
-extern "C" int frwkv_selftest_umma(const float* a, const float* b, float* d, int n, int a_mn_major, int b_mn_major,
-                                   int a_chunk_stride, int b_chunk_stride, int a_raw_shift,
+extern "C" int frwkv_selftest_umma(const float* a, const float* b, float* d, int n, int a_chunk_stride,
+                                   int b_chunk_stride, int a_raw_shift,
                                    int32_t* error_flag, frwkv_stream_t stream) {
   using namespace frwkv;
   clear_error();
   FRWKV_REQUIRE(a && b && d && error_flag, "selftest_umma: null pointer argument");
   FRWKV_REQUIRE(n == 64 || n == 128, "selftest_umma: n must be 64 or 128");
-  const int a_chunks = a_mn_major ? 32 : 16, b_chunks = b_mn_major ? n / 4 : 16;
-  const int a_rows = a_mn_major ? 64 : 128, b_rows = b_mn_major ? 64 : n;
-  FRWKV_REQUIRE(a_chunk_stride % 16 == 0 && a_chunk_stride >= a_rows * 16 && a_chunks * a_chunk_stride <= 65536,
+  FRWKV_REQUIRE(a_chunk_stride % 16 == 0 && a_chunk_stride >= 128 * 16 && 16 * a_chunk_stride <= 65536,
                 "selftest_umma: bad a_chunk_stride");
-  FRWKV_REQUIRE(b_chunk_stride % 16 == 0 && b_chunk_stride >= b_rows * 16 && b_chunks * b_chunk_stride <= 32768,
+  FRWKV_REQUIRE(b_chunk_stride % 16 == 0 && b_chunk_stride >= n * 16 && 16 * b_chunk_stride <= 32768,
                 "selftest_umma: bad b_chunk_stride");
   const int smem_bytes = 65536 + 32768;
   cudaError_t err = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (err != cudaSuccess) return fail(FRWKV_ERR_CUDA, "selftest_umma: %s", cudaGetErrorString(err));
   umma_selftest_kernel<<<1, 128, smem_bytes, reinterpret_cast<cudaStream_t>(stream)>>>(
-      a, b, d, n, a_mn_major, b_mn_major, a_chunk_stride, b_chunk_stride, a_raw_shift, error_flag);
+      a, b, d, n, a_chunk_stride, b_chunk_stride, a_raw_shift, error_flag);
   return check_launch("umma_selftest_kernel");
 }

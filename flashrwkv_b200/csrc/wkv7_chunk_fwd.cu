@@ -70,7 +70,7 @@ __device__ __forceinline__ uint32_t tile_off(uint32_t cs, int row, int col) {
 // one 128 x N x 64 product: 8 K-steps of tcgen05.mma, A and B chunk-major tiles contracted over their columns
 __device__ __forceinline__ void issue_mma(uint32_t d_tmem, uint32_t a_addr, uint32_t a_cs, uint32_t b_addr,
                                           uint32_t b_cs, int n, bool accumulate_first) {
-  const uint32_t idesc = umma::idesc_tf32(128, n, 0, 0);
+  const uint32_t idesc = umma::idesc_tf32(128, n);
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks) {
     umma::mma_tf32_ss(d_tmem, umma::desc_k_major(a_addr + ks * 2 * a_cs, a_cs),

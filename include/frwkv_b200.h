@@ -111,15 +111,14 @@ int frwkv_wkv7_chunk_fp32io16_forward(
     frwkv_stream_t stream);
 
 /*
- * Diagnostic: D[128][n] = A[128][64] * B[n][64]^T through one tcgen05.mma (kind::tf32) chain, with A and B
- * staged in shared memory in the given orientation (0 = contraction over tile columns, 1 = over tile rows)
- * and chunk stride in bytes.  No counterpart in the reference; used by the tests to pin the descriptor
- * encodings the chunk kernels rely on.  error_flag (device int32) is set to 1 if the MMA never completed.
- * a_raw_shift >= 0 turns the A region into a layout probe (word i holds (i >> shift) & 2047); -1 = off.
+ * Diagnostic: D[128][n] = A[128][64] * B[n][64]^T through one tcgen05.mma (kind::tf32) chain of 8 K-steps,
+ * with A and B staged in shared memory as chunk-major tiles of the given chunk stride (bytes).  No
+ * counterpart in the reference; used by the tests to pin the descriptor encodings the chunk kernels rely on.
+ * error_flag (device int32) is set to 1 if the MMA never completed.  a_raw_shift >= 0 turns the A region
+ * into a layout probe (word i holds (i >> shift) & 2047); -1 = off.
  */
-int frwkv_selftest_umma(const float* a, const float* b, float* d, int n, int a_mn_major, int b_mn_major,
-                        int a_chunk_stride, int b_chunk_stride, int a_raw_shift, int32_t* error_flag,
-                        frwkv_stream_t stream);
+int frwkv_selftest_umma(const float* a, const float* b, float* d, int n, int a_chunk_stride, int b_chunk_stride,
+                        int a_raw_shift, int32_t* error_flag, frwkv_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -1,4 +1,4 @@
-"""Pins the tcgen05 descriptor encodings: one tensor-core product per operand orientation vs numpy."""
+"""Pins the tcgen05 descriptor encodings: one tensor-core product per tile shape and chunk stride vs numpy."""
 import ctypes
 
 import numpy as np
@@ -15,28 +15,27 @@ def _tf32(x: np.ndarray) -> np.ndarray:
 
 
 CASES = [
-    # n, a_mn, b_mn, a_stride, b_stride     (the forms used by the chunk kernels)
-    (128, 0, 0, 2048, 2048),   # [B~;K~] x [A~;R~]^T
-    (64, 1, 1, 1024, 2048),    # [A_ak;A_rk] x V  (V interleaved with another tile)
-    (64, 1, 1, 2048, 1024),    # [A~|Z]^T x T^T
-    (128, 1, 0, 1024, 2048),   # [A_rb;B^] x [P|Q]
-    (64, 0, 1, 2048, 1024),    # scan: [E;M] x S
+    # n, a_stride, b_stride     (the tile shapes used by the chunk kernels)
+    (128, 2048, 2048),   # [A~;R~] x [B~;K~]^T
+    (64, 2048, 1040),    # [A_ak;-] x V ; scan: [E;M] x S
+    (64, 2064, 1040),    # [A~^T;Z^T] x T^T ; [A_rk;K^^T] x V
+    (128, 2064, 2048),   # [A_rb;B^^T] x [P|Q]
 ]
 
 
-@pytest.mark.parametrize("n,a_mn,b_mn,a_stride,b_stride", CASES)
-def test_single_mma_matches_numpy(n, a_mn, b_mn, a_stride, b_stride):
+@pytest.mark.parametrize("n,a_stride,b_stride", CASES)
+def test_single_mma_matches_numpy(n, a_stride, b_stride):
     from flashrwkv_b200 import _ext
 
     lib = _ext.capi()
-    rng = np.random.default_rng(n + 2 * a_mn + b_mn)
+    rng = np.random.default_rng(n + a_stride + b_stride)
     A = rng.standard_normal((128, 64)).astype(np.float32)
     Bm = rng.standard_normal((n, 64)).astype(np.float32)
     a_d, b_d = torch.from_numpy(A).cuda(), torch.from_numpy(Bm).cuda()
     d_d = torch.zeros(128, n, device="cuda")
     flag = torch.zeros(1, dtype=torch.int32, device="cuda")
     p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
-    rc = lib.frwkv_selftest_umma(p(a_d), p(b_d), p(d_d), n, a_mn, b_mn, a_stride, b_stride, -1, p(flag),
+    rc = lib.frwkv_selftest_umma(p(a_d), p(b_d), p(d_d), n, a_stride, b_stride, -1, p(flag),
                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == 0, lib.frwkv_last_error()
     torch.cuda.synchronize()
