@@ -37,6 +37,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC",
+    *os.environ.get("FRWKV_EXTRA_NVCC_FLAGS", "").split(),
 ]
 
 

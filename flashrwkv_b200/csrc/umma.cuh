@@ -134,6 +134,14 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
                : "memory");
 }
 
+// ---- 16-byte asynchronous copy global -> shared (zero-fills when src_bytes == 0) --------------
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gmem_src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gmem_src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // round-to-nearest fp32 -> tf32 (kept in a 32-bit container); the tensor core would otherwise truncate
 __device__ __forceinline__ float to_tf32(float x) {
   uint32_t r;

@@ -9,7 +9,7 @@
 //     T = (I - A_ab)^-1,  P = T A~,  Q = T A_ak V
 //     E = R~ + A_rb P,  F = A_rb Q + A_rk V,  M = diag(g_L) + B^^T P,  N = B^^T Q + K^^T V.
 //
-// Kernel 1 (build, one CTA per (chunk, head), all chunks in parallel) forms [E;M] and [F;N] with five
+// Kernel 1 (build, persistent CTAs over the (chunk, head) items, all chunks independent) forms [E;M] and [F;N] with five
 // tcgen05.mma (kind::tf32, fp32 accumulate in tensor memory) products; the 64 x 64 unit-triangular inverse
 // is done in fp32 on the CUDA cores (one thread per column of T).  Operands are rounded to tf32 once, with
 // round-to-nearest, when they are written to shared memory.  Results go to a workspace laid out exactly as
@@ -78,322 +78,390 @@ __device__ __forceinline__ void issue_mma(uint32_t d_tmem, uint32_t a_addr, uint
   }
 }
 
-template <typename io_t>
-__device__ __forceinline__ void load_row_half(const io_t* p, bool valid, float (&out)[32]) {
-  // 32 consecutive 16-bit values (64 bytes) -> fp32
-  using IO = Io16<io_t>;
-  if (valid) {
-    const uint4* q = reinterpret_cast<const uint4*>(p);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint4 u = __ldg(q + i);
-      float2 f;
-      f = IO::unpack(u.x); out[8 * i + 0] = f.x; out[8 * i + 1] = f.y;
-      f = IO::unpack(u.y); out[8 * i + 2] = f.x; out[8 * i + 3] = f.y;
-      f = IO::unpack(u.z); out[8 * i + 4] = f.x; out[8 * i + 5] = f.y;
-      f = IO::unpack(u.w); out[8 * i + 6] = f.x; out[8 * i + 7] = f.y;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) out[i] = 0.f;
-  }
-}
-
-template <typename io_t>
-__device__ __forceinline__ void load_row_raw(const io_t* p, bool valid, uint32_t (&out)[32]) {
-  // 64 consecutive 16-bit values kept packed (two per register)
-  if (valid) {
-    const uint4* q = reinterpret_cast<const uint4*>(p);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint4 u = __ldg(q + i);
-      out[4 * i] = u.x; out[4 * i + 1] = u.y; out[4 * i + 2] = u.z; out[4 * i + 3] = u.w;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) out[i] = 0u;
-  }
-}
-
-template <typename io_t>
-__device__ __forceinline__ float4 unpack4(const uint32_t (&raw)[32], int kc) {
-  using IO = Io16<io_t>;
-  const float2 lo = IO::unpack(raw[2 * kc]), hi = IO::unpack(raw[2 * kc + 1]);
-  return make_float4(lo.x, lo.y, hi.x, hi.y);
-}
-
 __device__ __forceinline__ float4 mul4(float4 a, float4 b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
+
+#ifdef FRWKV_PROFILE_PHASES
+}  // namespace
+__device__ long long g_phase_clock[16];
+namespace {
+#define FRWKV_PHASE(i) do { if (blockIdx.x == 0 && tid == 0 && item == (int)(2 * gridDim.x)) g_phase_clock[i] = clock64(); } while (0)
+#else
+#define FRWKV_PHASE(i) do { } while (0)
+#endif
 
 // =================================================================================================
 // Kernel 1: build [E;M] and [F;N] for every (chunk, head)
+// Persistent: each CTA walks (chunk, head) items blockIdx.x, blockIdx.x + gridDim.x, ... so that the
+// tensor-memory allocation and the barriers are set up once per SM.  512 threads: the per-item work is a
+// chain of short phases separated by barriers, so it is latency- not throughput-bound and wants four
+// warps per scheduler.  Thread roles:
+//   operand phases : t = tid % 64 (token), part = tid / 64: hsel = part % 2 picks the tensor group
+//                    (0: a, b   1: r, k, v), quarter = part / 2 picks 16 of the 64 key channels;
+//   epilogues      : warp w reads tensor-memory lanes 32*(w%4).. (row m = 32*(w%4) + lane) and the
+//                    32 accumulator columns starting at 32*(w/4).
 // =================================================================================================
+constexpr int kBuildThreads = 512;
+
 template <typename io_t>
-__global__ __launch_bounds__(128, 1) void wkv7_chunk_build_kernel(
+__global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     const int* __restrict__ chunk_starts, const int* __restrict__ chunk_ends, const int* __restrict__ metadata_status,
     const io_t* __restrict__ r_ptr, const io_t* __restrict__ w_ptr, const io_t* __restrict__ k_ptr,
     const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr, const io_t* __restrict__ b_ptr,
-    const io_t* __restrict__ bias_ptr, unsigned char* __restrict__ workspace, int num_heads,
+    const io_t* __restrict__ bias_ptr, unsigned char* __restrict__ workspace, int num_heads, int num_items,
     int* __restrict__ error_flag) {
+  using IO = Io16<io_t>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t mbar[4];
   __shared__ uint32_t tmem_holder;
   if (metadata_status != nullptr && metadata_status[0] != 0) return;
 
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int t = tid & 63, hsel = tid >> 6;
-  const int chunk = blockIdx.x / num_heads, head = blockIdx.x % num_heads;
-  const int t0 = chunk_starts[chunk];
-  const int len = min(max(chunk_ends[chunk] - t0, 0), kL);
-  const bool valid = t < len;
-  const long long row = ((long long)(t0 + t) * num_heads + head) * kD;
-
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t = tid & 63, part = tid >> 6, hsel = part & 1, quarter = part >> 1;
+  const int m = 32 * (warp & 3) + lane;  // accumulator row of this thread
+  const int colq = warp >> 2;            // accumulator column quarter of this thread
+  const int mt = m & 63;                 // token (rows 0..63) or key channel (rows 64..127) of that row
   if (tid == 0) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) umma::mbar_init(&mbar[i], 1);
     umma::mbar_fence_init();
   }
   if (warp == 0) umma::tmem_alloc(&tmem_holder, 256);
-
-  // ---- issue the token loads early: group 0 owns a and b, group 1 owns r, k and v ---------------
-  uint32_t raw0[32], raw1[32], raw2[32];
-  if (hsel == 0) {
-    load_row_raw(a_ptr + row, valid, raw0);
-    load_row_raw(b_ptr + row, valid, raw1);
-  } else {
-    load_row_raw(r_ptr + row, valid, raw0);
-    load_row_raw(k_ptr + row, valid, raw1);
-    load_row_raw(v_ptr + row, valid, raw2);
-  }
-  // ---- per-step retention for this thread's half of the key channels ---------------------------
-  {
-    float x[32];
-    load_row_half(w_ptr + row + 32 * hsel, valid, x);
-    if (bias_ptr != nullptr) {
-      float bx[32];
-      load_row_half(bias_ptr + head * kD + 32 * hsel, true, bx);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) x[i] += bx[i];
-    }
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      float4 w4;
-      w4.x = valid ? retention(x[4 * c]) : 1.f;
-      w4.y = valid ? retention(x[4 * c + 1]) : 1.f;
-      w4.z = valid ? retention(x[4 * c + 2]) : 1.f;
-      w4.w = valid ? retention(x[4 * c + 3]) : 1.f;
-      st4(smem, kOffSC + (8 * hsel + c) * kCS64P + t * 16, w4);
-    }
-  }
-  __syncthreads();
-  // ---- cumulative decay g_t[k] down each key column (threads 0..63 own one column each) ---------
-  if (tid < 64) {
-    float col[64];
-    const uint32_t base = kOffSC + (tid >> 2) * kCS64P + (tid & 3) * 4;
-#pragma unroll
-    for (int i = 0; i < 64; ++i) col[i] = *reinterpret_cast<const float*>(smem + base + i * 16);
-    float run = 1.f;
-#pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      run *= col[i];
-      st1(smem, base + i * 16, run);
-    }
-  }
-  __syncthreads();
-  // ---- operands -------------------------------------------------------------------------------
-  float diag_gl = 0.f;  // g_L[k] for the thread that later owns row k of M
-  if (tid >= 64) diag_gl = *reinterpret_cast<const float*>(smem + kOffSC + tile_off(kCS64P, 63, tid - 64));
-#pragma unroll
-  for (int kc = 0; kc < 16; ++kc) {
-    const float4 g = ld4(smem, kOffSC + kc * kCS64P + t * 16);
-    const float4 gl = ld4(smem, kOffSC + kc * kCS64P + 63 * 16);
-    const float4 inv = make_float4(__frcp_rn(g.x), __frcp_rn(g.y), __frcp_rn(g.z), __frcp_rn(g.w));
-    const uint32_t tcol = uint32_t(t >> 2), tsub = uint32_t(t & 3) * 4;
-    if (hsel == 0) {
-      float4 gp = make_float4(1.f, 1.f, 1.f, 1.f);
-      if (t > 0) gp = ld4(smem, kOffSC + kc * kCS64P + (t - 1) * 16);
-      const float4 at = umma::to_tf32(mul4(unpack4<io_t>(raw0, kc), gp));
-      const float4 bt = mul4(unpack4<io_t>(raw1, kc), inv);
-      const float4 bh = umma::to_tf32(mul4(bt, gl));
-      st4(smem, kOffX1 + kc * kCS128 + t * 16, at);
-      st4(smem, kOffX2 + kc * kCS128 + t * 16, umma::to_tf32(bt));
-      // A~^T (rows k, col t) and B^^T (rows 64 + k, col t)
-      const uint32_t oa = kOffAZ + tcol * kCS128P + tsub + uint32_t(4 * kc) * 16;
-      st1(smem, oa, at.x); st1(smem, oa + 16, at.y); st1(smem, oa + 32, at.z); st1(smem, oa + 48, at.w);
-      const uint32_t ob = kOffRB + tcol * kCS128P + tsub + uint32_t(64 + 4 * kc) * 16;
-      st1(smem, ob, bh.x); st1(smem, ob + 16, bh.y); st1(smem, ob + 32, bh.z); st1(smem, ob + 48, bh.w);
-    } else {
-      const float4 rt = umma::to_tf32(mul4(unpack4<io_t>(raw0, kc), g));
-      const float4 kt = mul4(unpack4<io_t>(raw1, kc), inv);
-      const float4 kh = umma::to_tf32(mul4(kt, gl));
-      const float4 vv = unpack4<io_t>(raw2, kc);
-      st4(smem, kOffX1 + kc * kCS128 + (64 + t) * 16, rt);
-      st4(smem, kOffX2 + kc * kCS128 + (64 + t) * 16, umma::to_tf32(kt));
-      const uint32_t ok = kOffRK + tcol * kCS128P + tsub + uint32_t(64 + 4 * kc) * 16;
-      st1(smem, ok, kh.x); st1(smem, ok + 16, kh.y); st1(smem, ok + 32, kh.z); st1(smem, ok + 48, kh.w);
-      const uint32_t ov = kOffVT + tcol * kCS64P + tsub + uint32_t(4 * kc) * 16;
-      st1(smem, ov, vv.x); st1(smem, ov + 16, vv.y); st1(smem, ov + 32, vv.z); st1(smem, ov + 48, vv.w);
-    }
-  }
-  umma::fence_async_smem();
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
   const uint32_t tmem = tmem_holder;
   const uint32_t sbase = umma::smem_u32(smem);
-  const uint32_t lane_base = uint32_t(warp * 32) << 16;
+  const uint32_t lane_base = uint32_t(32 * (warp & 3)) << 16;
+  const uint32_t tcol = uint32_t(t >> 2), tsub = uint32_t(t & 3) * 4;
   bool ok = true;
+  uint32_t parity = 0;
 
-  // ---- MMA 1: [A~;R~] [B~;K~]^T  ->  rows t: [A_ab | A_ak], rows 64+t: [A_rb | A_rk] -----------
-  if (tid == 0) {
-    issue_mma(tmem, sbase + kOffX1, kCS128, sbase + kOffX2, kCS128, 128, false);
-    umma::mma_commit(&mbar[0]);
-  }
-  ok = umma::mbar_wait(&mbar[0], 0) && ok;
-  umma::fence_after_sync();
-  if (ok) {
+  // Stage the 16-bit token rows of an item in shared memory with cp.async (rows past the end of a short
+  // chunk are zero-filled).  The staging slots are the parts of RB / RK / AZ / TT that the item's own operands
+  // do not occupy until later phases, so the copies for the NEXT item start as soon as the last product of the
+  // current one has completed and overlap its final epilogue.  Each thread stages exactly what it consumes:
+  //   a|r : RB chunk (8*hsel + c), rows 0..63     b|k : RK chunk (8*hsel + c), rows 0..63      c = 2*quarter + {0,1}
+  //   v   : AZ chunk c, rows 64..127              w   : TT region, slot [part][t] (key channels 8*part..)
+  auto stage_item = [&](int it) {
+    const int ch = it / num_heads, hd = it % num_heads;
+    const int tt0 = chunk_starts[ch];
+    const int ln = min(max(chunk_ends[ch] - tt0, 1), kL);
+    const uint32_t nbytes = (t < ln) ? 16u : 0u;
+    const long long rw = ((long long)(tt0 + min(t, ln - 1)) * num_heads + hd) * kD;
+    const io_t* p0 = (hsel == 0 ? a_ptr : r_ptr) + rw;
+    const io_t* p1 = (hsel == 0 ? b_ptr : k_ptr) + rw;
 #pragma unroll
-    for (int c0 = 0; c0 < 128; c0 += 32) {
-      uint32_t u[32];
-      umma::tmem_ld32(tmem + lane_base + c0, u);
-      umma::tmem_ld_wait();
-      const int s0 = c0 & 63;
-      float f[32];
+    for (int cc = 0; cc < 2; ++cc) {
+      const int c = 2 * quarter + cc;
+      umma::cp_async16(sbase + kOffRB + uint32_t(8 * hsel + c) * kCS128P + t * 16, p0 + 8 * c, nbytes);
+      umma::cp_async16(sbase + kOffRK + uint32_t(8 * hsel + c) * kCS128P + t * 16, p1 + 8 * c, nbytes);
+      if (hsel == 1) umma::cp_async16(sbase + kOffAZ + uint32_t(c) * kCS128P + 1024 + t * 16, v_ptr + rw + 8 * c, nbytes);
+    }
+    umma::cp_async16(sbase + kOffTT + uint32_t(part) * 1024 + t * 16, w_ptr + rw + 8 * part, nbytes);
+    umma::cp_async_commit();
+  };
+  if ((int)blockIdx.x < num_items) stage_item(blockIdx.x);
+
+  for (int item = blockIdx.x; item < num_items; item += gridDim.x, parity ^= 1u) {
+    const int chunk = item / num_heads, head = item % num_heads;
+    const int t0 = chunk_starts[chunk];
+    const int len = min(max(chunk_ends[chunk] - t0, 1), kL);
+    const bool valid = t < len;
+
+    FRWKV_PHASE(0);
+    umma::cp_async_wait_all();  // this thread's staged rows have landed (each thread reads only its own)
+    // ---- per-step retention for key channels 8*part .. 8*part+7 -> scratch [kc][t][4] ---------------
+    {
+      float x[8];
+      if (valid) {
+        const uint4 u = *reinterpret_cast<const uint4*>(smem + kOffTT + uint32_t(part) * 1024 + t * 16);
+        float2 f;
+        f = IO::unpack(u.x); x[0] = f.x; x[1] = f.y;
+        f = IO::unpack(u.y); x[2] = f.x; x[3] = f.y;
+        f = IO::unpack(u.z); x[4] = f.x; x[5] = f.y;
+        f = IO::unpack(u.w); x[6] = f.x; x[7] = f.y;
+        if (bias_ptr != nullptr) {
+          const uint4 bu = __ldg(reinterpret_cast<const uint4*>(bias_ptr + head * kD + 8 * part));
+          f = IO::unpack(bu.x); x[0] += f.x; x[1] += f.y;
+          f = IO::unpack(bu.y); x[2] += f.x; x[3] += f.y;
+          f = IO::unpack(bu.z); x[4] += f.x; x[5] += f.y;
+          f = IO::unpack(bu.w); x[6] += f.x; x[7] += f.y;
+        }
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int s = s0 + j;
-        const bool keep = (tid < 64) ? (s < t) : (s <= t);
-        f[j] = keep ? __uint_as_float(u[j]) : 0.f;
+        for (int e = 0; e < 8; ++e) x[e] = retention(x[e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = 1.f;
       }
-      if (tid < 64 && c0 < 64) {  // A_ab -> fp32 scratch for the inverse
+      const uint32_t o = kOffSC + uint32_t(2 * part) * kCS64P + t * 16;
+      st4(smem, o, make_float4(x[0], x[1], x[2], x[3]));
+      st4(smem, o + kCS64P, make_float4(x[4], x[5], x[6], x[7]));
+    }
+    __syncthreads();
+    FRWKV_PHASE(1);
+    // ---- cumulative decay g_t[k] down each key column: 128 threads, two per column ---------------------
+    // (rows 0..31 and 32..63 are scanned separately, then the lower half is scaled by the upper total)
+    if (tid < 128) {
+      const int kcol = tid & 63, hh = tid >> 6;
+      float col[32];
+      const uint32_t base = kOffSC + (kcol >> 2) * kCS64P + (kcol & 3) * 4 + uint32_t(32 * hh) * 16;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) col[i] = *reinterpret_cast<const float*>(smem + base + i * 16);
+      float run = 1.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        run *= col[i];
+        col[i] = run;
+      }
+      if (hh == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) st1(smem, base + i * 16, col[i]);
+      }
+      // named barrier over the 128 scanning threads only
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (hh == 1) {
+        const float top = *reinterpret_cast<const float*>(smem + base - 16);  // g_31[k]
+#pragma unroll
+        for (int i = 0; i < 32; ++i) st1(smem, base + i * 16, col[i] * top);
+      }
+    }
+    __syncthreads();
+    FRWKV_PHASE(2);
+    // ---- operands (one code path for both groups), key channels 16*quarter .. 16*quarter+15 --------------
+    //   X1[64*hsel + t] = p * (hsel ? g_t : g_{t-1})      p = a | r
+    //   X2[64*hsel + t] = q / g_t                         q = b | k
+    //   (RB | RK) rows 64 + k, col t = q / g_t * g_L      (B^^T | K^^T)
+    //   group 0: AZ rows k, col t = a * g_{t-1}  (A~^T);  group 1: VT rows v, col t = v
+    float diag_gl = 0.f;  // g_L[k] for the threads that later own row k of M
+    if (m >= 64) diag_gl = *reinterpret_cast<const float*>(smem + kOffSC + tile_off(kCS64P, 63, mt));
+    {
+      const uint32_t o3 = (hsel == 0 ? kOffRB : kOffRK) + tcol * kCS128P + tsub + 64 * 16;
+      const uint32_t o4 = hsel == 0 ? kOffAZ + tcol * kCS128P + tsub : kOffVT + tcol * kCS64P + tsub;
+      const uint32_t oscale = kOffSC + uint32_t(hsel == 0 ? max(t - 1, 0) : t) * 16;
+      const bool first_row = (hsel == 0 && t == 0);
+      const uint32_t stage01 = uint32_t(8 * hsel) * kCS128P + t * 16;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int kc = 4 * quarter + i;
+        const uint32_t so = uint32_t(kc >> 1) * kCS128P + uint32_t(kc & 1) * 8;
+        const uint2 u0 = *reinterpret_cast<const uint2*>(smem + kOffRB + stage01 + so);
+        const uint2 u1 = *reinterpret_cast<const uint2*>(smem + kOffRK + stage01 + so);
+        uint2 u2 = make_uint2(0u, 0u);
+        if (hsel == 1) u2 = *reinterpret_cast<const uint2*>(smem + kOffAZ + 1024 + t * 16 + so);
+        const float4 g = ld4(smem, kOffSC + kc * kCS64P + t * 16);
+        const float4 gl = ld4(smem, kOffSC + kc * kCS64P + 63 * 16);
+        float4 sc = ld4(smem, oscale + kc * kCS64P);
+        if (first_row) sc = make_float4(1.f, 1.f, 1.f, 1.f);
+        const float4 inv = make_float4(__frcp_rn(g.x), __frcp_rn(g.y), __frcp_rn(g.z), __frcp_rn(g.w));
+        const float2 p01 = IO::unpack(u0.x), p23 = IO::unpack(u0.y);
+        const float2 q01 = IO::unpack(u1.x), q23 = IO::unpack(u1.y);
+        const float2 v01 = IO::unpack(u2.x), v23 = IO::unpack(u2.y);
+        const float4 p = umma::to_tf32(mul4(make_float4(p01.x, p01.y, p23.x, p23.y), sc));
+        const float4 q = mul4(make_float4(q01.x, q01.y, q23.x, q23.y), inv);
+        const float4 qh = umma::to_tf32(mul4(q, gl));
+        const float4 x4 = hsel == 0 ? p : make_float4(v01.x, v01.y, v23.x, v23.y);
+        st4(smem, kOffX1 + kc * kCS128 + (64 * hsel + t) * 16, p);
+        st4(smem, kOffX2 + kc * kCS128 + (64 * hsel + t) * 16, umma::to_tf32(q));
+        const uint32_t a3 = o3 + uint32_t(4 * kc) * 16, a4 = o4 + uint32_t(4 * kc) * 16;
+        st1(smem, a3, qh.x); st1(smem, a3 + 16, qh.y); st1(smem, a3 + 32, qh.z); st1(smem, a3 + 48, qh.w);
+        st1(smem, a4, x4.x); st1(smem, a4 + 16, x4.y); st1(smem, a4 + 32, x4.z); st1(smem, a4 + 48, x4.w);
+      }
+    }
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+
+    FRWKV_PHASE(3);
+    // ---- MMA 1: [A~;R~] [B~;K~]^T  ->  rows t: [A_ab | A_ak], rows 64+t: [A_rb | A_rk] -----------
+    if (tid == 0) {
+      issue_mma(tmem, sbase + kOffX1, kCS128, sbase + kOffX2, kCS128, 128, false);
+      umma::mma_commit(&mbar[0]);
+    }
+    ok = umma::mbar_wait(&mbar[0], parity) && ok;
+    umma::fence_after_sync();
+    FRWKV_PHASE(4);
+    if (ok) {
+      uint32_t u[32];
+      umma::tmem_ld32(tmem + lane_base + 32 * colq, u);
+      umma::tmem_ld_wait();
+      const int s0 = 32 * (colq & 1);
+      const int limit = (m < 64) ? mt : mt + 1;  // keep s < t (strict) or s <= t
+      if (m < 64 && colq < 2) {                  // A_ab -> fp32 scratch for the inverse
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
-          st4(smem, kOffSC + t * kAabRow + (s0 + j) * 4, make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]));
+          st4(smem, kOffSC + mt * kAabRow + (s0 + j) * 4,
+              make_float4(s0 + j < limit ? __uint_as_float(u[j]) : 0.f,
+                          s0 + j + 1 < limit ? __uint_as_float(u[j + 1]) : 0.f,
+                          s0 + j + 2 < limit ? __uint_as_float(u[j + 2]) : 0.f,
+                          s0 + j + 3 < limit ? __uint_as_float(u[j + 3]) : 0.f));
       } else {
         // A_ak -> X2 region rows t; A_rb -> RB rows t; A_rk -> RK rows t
-        const uint32_t base = (tid < 64) ? kOffX2 : (c0 < 64 ? kOffRB : kOffRK);
-        const uint32_t cs = (tid < 64) ? kCS128 : kCS128P;
+        const uint32_t base = (m < 64) ? kOffX2 : (colq < 2 ? kOffRB : kOffRK);
+        const uint32_t cs = (m < 64) ? kCS128 : kCS128P;
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
-          st4(smem, base + uint32_t((s0 + j) >> 2) * cs + t * 16,
-              umma::to_tf32(make_float4(f[j], f[j + 1], f[j + 2], f[j + 3])));
+          st4(smem, base + uint32_t((s0 + j) >> 2) * cs + mt * 16,
+              umma::to_tf32(make_float4(s0 + j < limit ? __uint_as_float(u[j]) : 0.f,
+                                        s0 + j + 1 < limit ? __uint_as_float(u[j + 1]) : 0.f,
+                                        s0 + j + 2 < limit ? __uint_as_float(u[j + 2]) : 0.f,
+                                        s0 + j + 3 < limit ? __uint_as_float(u[j + 3]) : 0.f)));
       }
     }
-  }
-  umma::fence_async_smem();
-  umma::fence_before_sync();
-  __syncthreads();
-  umma::fence_after_sync();
-
-  // ---- MMA 2: Z = A_ak V (rows 0..63 of the product; rows 64..127 of the A tile are don't-care) ----
-  if (tid == 0) {
-    issue_mma(tmem + 128, sbase + kOffX2, kCS128, sbase + kOffVT, kCS64P, 64, false);
-    umma::mma_commit(&mbar[1]);
-  }
-  if (tid >= 64) {
-    // T = (I - A_ab)^-1, one column per thread: T[t][j] = [t == j] + sum_{s<t} A_ab[t][s] T[s][j]
-    const int j = tid - 64;
-    float col[64];
-#pragma unroll
-    for (int tt = 0; tt < 64; ++tt) {
-      float acc0 = (tt == j) ? 1.f : 0.f, acc1 = 0.f;
-#pragma unroll
-      for (int s4 = 0; s4 < (tt + 3) / 4; ++s4) {
-        const float4 a4 = ld4(smem, kOffSC + tt * kAabRow + s4 * 16);
-        if (4 * s4 + 0 < tt) acc0 = fmaf(a4.x, col[4 * s4 + 0], acc0);
-        if (4 * s4 + 1 < tt) acc1 = fmaf(a4.y, col[4 * s4 + 1], acc1);
-        if (4 * s4 + 2 < tt) acc0 = fmaf(a4.z, col[4 * s4 + 2], acc0);
-        if (4 * s4 + 3 < tt) acc1 = fmaf(a4.w, col[4 * s4 + 3], acc1);
-      }
-      col[tt] = acc0 + acc1;
-    }
-    const uint32_t o = kOffTT + uint32_t(j >> 2) * kCS64P + uint32_t(j & 3) * 4;
-#pragma unroll
-    for (int tt = 0; tt < 64; ++tt) st1(smem, o + tt * 16, umma::to_tf32(col[tt]));
-  } else {
-    ok = umma::mbar_wait(&mbar[1], 0) && ok;
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
     umma::fence_after_sync();
-    if (ok) {
-      // Z^T -> AZ rows 64 + v, col t
-      const uint32_t o = kOffAZ + uint32_t(t >> 2) * kCS128P + uint32_t(t & 3) * 4 + 64 * 16;
+
+    FRWKV_PHASE(5);
+    // ---- MMA 2: Z = A_ak V (rows 0..63 of the product; rows 64..127 of the A tile are don't-care) ----
+    if (tid == 0) {
+      issue_mma(tmem + 128, sbase + kOffX2, kCS128, sbase + kOffVT, kCS64P, 64, false);
+      umma::mma_commit(&mbar[1]);
+    }
+    if (warp >= 8) {
+      // T = (I - A_ab)^-1 on the CUDA cores in fp32, 16 rows at a time (warps 8..15):
+      //   T[t][j] = [t == j] + sum_{s<t} A_ab[t][s] T[s][j].
+      // Column j is owned by four lanes of one warp (lane, +8, +16, +24).  The sum over the rows above the
+      // current block is split between them (groups of four rows, round robin) and joined by two shuffles;
+      // the triangular part inside the block is right-looking, so its dependent chain is one multiply-add
+      // per row.  Finished rows live (unrounded) in the TT tile at (row s, col j).
+      const int j = (warp - 8) * 8 + (lane & 7), helper = lane >> 3;
+      const uint32_t oT = kOffTT + uint32_t(j >> 2) * kCS64P + uint32_t(j & 3) * 4;
+#pragma unroll 1
+      for (int blk = 0; blk < 4; ++blk) {
+        const uint32_t arow = kOffSC + uint32_t(16 * blk) * kAabRow;
+        float acc[16];
 #pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
+        for (int rr = 0; rr < 16; ++rr) acc[rr] = 0.f;
+#pragma unroll 1
+        for (int s4 = helper; s4 < 4 * blk; s4 += 4) {
+          const float c0v = *reinterpret_cast<const float*>(smem + oT + (4 * s4 + 0) * 16);
+          const float c1v = *reinterpret_cast<const float*>(smem + oT + (4 * s4 + 1) * 16);
+          const float c2v = *reinterpret_cast<const float*>(smem + oT + (4 * s4 + 2) * 16);
+          const float c3v = *reinterpret_cast<const float*>(smem + oT + (4 * s4 + 3) * 16);
+#pragma unroll
+          for (int rr = 0; rr < 16; ++rr) {
+            const float4 a4 = ld4(smem, arow + rr * kAabRow + s4 * 16);
+            acc[rr] = fmaf(a4.x, c0v, fmaf(a4.y, c1v, fmaf(a4.z, c2v, fmaf(a4.w, c3v, acc[rr]))));
+          }
+        }
+#pragma unroll
+        for (int rr = 0; rr < 16; ++rr) {
+          acc[rr] += __shfl_xor_sync(0xffffffffu, acc[rr], 8);
+          acc[rr] += __shfl_xor_sync(0xffffffffu, acc[rr], 16);
+        }
+        const uint32_t ablk = arow + uint32_t(16 * blk) * 4;
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          const float xq = acc[q] + ((16 * blk + q == j) ? 1.f : 0.f);
+          if (helper == 0) st1(smem, oT + uint32_t(16 * blk + q) * 16, xq);
+#pragma unroll
+          for (int rr = q + 1; rr < 16; ++rr)
+            acc[rr] = fmaf(*reinterpret_cast<const float*>(smem + ablk + rr * kAabRow + q * 4), xq, acc[rr]);
+        }
+        __syncwarp();
+      }
+      // the tensor core truncates: round the finished column to tf32 (the four lanes share the rows)
+#pragma unroll 4
+      for (int s = helper; s < 64; s += 4) {
+        const uint32_t o = oT + s * 16;
+        st1(smem, o, umma::to_tf32(*reinterpret_cast<const float*>(smem + o)));
+      }
+    } else if (m < 64 && colq < 2) {
+      // warps 0, 1, 4, 5: Z^T -> AZ rows 64 + v, col t (32 value columns per warp)
+      ok = umma::mbar_wait(&mbar[1], parity) && ok;
+      umma::fence_after_sync();
+      if (ok) {
+        const uint32_t o = kOffAZ + uint32_t(mt >> 2) * kCS128P + uint32_t(mt & 3) * 4 + 64 * 16;
         uint32_t u[32];
-        umma::tmem_ld32(tmem + 128 + lane_base + c0, u);
+        umma::tmem_ld32(tmem + 128 + lane_base + 32 * colq, u);
         umma::tmem_ld_wait();
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) st1(smem, o + (c0 + jj) * 16, umma::to_tf32(__uint_as_float(u[jj])));
+        for (int jj = 0; jj < 32; ++jj)
+          st1(smem, o + (32 * colq + jj) * 16, umma::to_tf32(__uint_as_float(u[jj])));
       }
     }
-  }
-  umma::fence_async_smem();
-  umma::fence_before_sync();
-  __syncthreads();
-  umma::fence_after_sync();
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
 
-  // ---- MMA 3: [A~^T ; Z^T] T^T -> rows j: P[.][j] (j < 64) and Q[.][j-64], columns t -------------
-  if (tid == 0) {
-    issue_mma(tmem + 192, sbase + kOffAZ, kCS128P, sbase + kOffTT, kCS64P, 64, false);
-    umma::mma_commit(&mbar[2]);
-  }
-  ok = umma::mbar_wait(&mbar[2], 0) && ok;
-  umma::fence_after_sync();
-  if (ok) {
-#pragma unroll
-    for (int c0 = 0; c0 < 64; c0 += 32) {
+    FRWKV_PHASE(6);
+    // ---- MMA 3: [A~^T ; Z^T] T^T -> rows j: P[.][j] (j < 64) and Q[.][j-64], columns t -------------
+    if (tid == 0) {
+      issue_mma(tmem + 192, sbase + kOffAZ, kCS128P, sbase + kOffTT, kCS64P, 64, false);
+      umma::mma_commit(&mbar[2]);
+    }
+    ok = umma::mbar_wait(&mbar[2], parity) && ok;
+    umma::fence_after_sync();
+    FRWKV_PHASE(7);
+    if (ok && colq < 2) {  // warps 0..7, 32 of the 64 columns each
       uint32_t u[32];
-      umma::tmem_ld32(tmem + 192 + lane_base + c0, u);
+      umma::tmem_ld32(tmem + 192 + lane_base + 32 * colq, u);
       umma::tmem_ld_wait();
 #pragma unroll
       for (int jj = 0; jj < 32; jj += 4)
-        st4(smem, kOffX2 + uint32_t((c0 + jj) >> 2) * kCS128 + tid * 16,
+        st4(smem, kOffX2 + uint32_t((32 * colq + jj) >> 2) * kCS128 + m * 16,
             umma::to_tf32(make_float4(__uint_as_float(u[jj]), __uint_as_float(u[jj + 1]),
                                       __uint_as_float(u[jj + 2]), __uint_as_float(u[jj + 3]))));
     }
-  }
-  umma::fence_async_smem();
-  umma::fence_before_sync();
-  __syncthreads();
-  umma::fence_after_sync();
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
 
-  // ---- MMA 4 + 5: [A_rb ; B^^T] [P|Q]  (+)  [A_rk ; K^^T] V into columns 64..127 ----------------------
-  if (tid == 0) {
-    issue_mma(tmem, sbase + kOffRB, kCS128P, sbase + kOffX2, kCS128, 128, false);
-    issue_mma(tmem + 64, sbase + kOffRK, kCS128P, sbase + kOffVT, kCS64P, 64, true);
-    umma::mma_commit(&mbar[3]);
-  }
-  ok = umma::mbar_wait(&mbar[3], 0) && ok;
-  umma::fence_after_sync();
-  if (ok) {
-    unsigned char* ws = workspace + (size_t)blockIdx.x * (2 * kWsTile);
-#pragma unroll
-    for (int c0 = 0; c0 < 128; c0 += 32) {
+    FRWKV_PHASE(8);
+    // ---- MMA 4 + 5: [A_rb ; B^^T] [P|Q]  (+)  [A_rk ; K^^T] V into columns 64..127 ------------------
+    if (tid == 0) {
+      issue_mma(tmem, sbase + kOffRB, kCS128P, sbase + kOffX2, kCS128, 128, false);
+      issue_mma(tmem + 64, sbase + kOffRK, kCS128P, sbase + kOffVT, kCS64P, 64, true);
+      umma::mma_commit(&mbar[3]);
+    }
+    ok = umma::mbar_wait(&mbar[3], parity) && ok;
+    umma::fence_after_sync();
+    FRWKV_PHASE(9);
+    if (ok && item + (int)gridDim.x < num_items) stage_item(item + gridDim.x);
+    if (ok) {
+      unsigned char* ws = workspace + (size_t)item * (2 * kWsTile);
       uint32_t u[32];
-      umma::tmem_ld32(tmem + lane_base + c0, u);
+      umma::tmem_ld32(tmem + lane_base + 32 * colq, u);
       umma::tmem_ld_wait();
+      const int cb = 32 * (colq & 1);
+      if (colq < 2) {
 #pragma unroll
-      for (int jj = 0; jj < 32; jj += 4) {
-        float4 val = make_float4(__uint_as_float(u[jj]), __uint_as_float(u[jj + 1]), __uint_as_float(u[jj + 2]),
-                                 __uint_as_float(u[jj + 3]));
-        const int c = c0 + jj;
-        if (c < 64) {
-          if (tid < 64) {  // E = R~ + A_rb P
-            const float4 rt = ld4(smem, kOffX1 + uint32_t(c >> 2) * kCS128 + (64 + t) * 16);
+        for (int jj = 0; jj < 32; jj += 4) {
+          float4 val = make_float4(__uint_as_float(u[jj]), __uint_as_float(u[jj + 1]), __uint_as_float(u[jj + 2]),
+                                   __uint_as_float(u[jj + 3]));
+          const int c = cb + jj;
+          if (m < 64) {  // E = R~ + A_rb P
+            const float4 rt = ld4(smem, kOffX1 + uint32_t(c >> 2) * kCS128 + (64 + mt) * 16);
             val.x += rt.x; val.y += rt.y; val.z += rt.z; val.w += rt.w;
-          } else {         // M = diag(g_L) + B^^T P
-            const int kk = tid - 64;
-            if (kk == c) val.x += diag_gl;
-            if (kk == c + 1) val.y += diag_gl;
-            if (kk == c + 2) val.z += diag_gl;
-            if (kk == c + 3) val.w += diag_gl;
+          } else {       // M = diag(g_L) + B^^T P
+            val.x += (mt == c) ? diag_gl : 0.f;
+            val.y += (mt == c + 1) ? diag_gl : 0.f;
+            val.z += (mt == c + 2) ? diag_gl : 0.f;
+            val.w += (mt == c + 3) ? diag_gl : 0.f;
           }
-          st4(ws, uint32_t(c >> 2) * kCS128 + tid * 16, umma::to_tf32(val));
-        } else {
-          st4(ws, kWsTile + uint32_t((c - 64) >> 2) * kCS128 + tid * 16, val);
+          st4(ws, uint32_t(c >> 2) * kCS128 + m * 16, umma::to_tf32(val));
         }
+      } else {
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 4)
+          st4(ws, kWsTile + uint32_t((cb + jj) >> 2) * kCS128 + m * 16,
+              make_float4(__uint_as_float(u[jj]), __uint_as_float(u[jj + 1]), __uint_as_float(u[jj + 2]),
+                          __uint_as_float(u[jj + 3])));
       }
     }
+    FRWKV_PHASE(10);
+    // every thread is done with this item's shared memory and accumulators before the next item starts
+    umma::fence_before_sync();
+    ok = __syncthreads_and(ok) != 0;
+    umma::fence_after_sync();
+    if (!ok) break;
   }
   if (!ok && tid == 0 && error_flag != nullptr) atomicExch(error_flag, 1);
+  umma::cp_async_wait_all();
   umma::fence_before_sync();
   __syncthreads();
   if (warp == 0) umma::tmem_dealloc(tmem, 256);
@@ -578,11 +646,16 @@ int launch_chunk_forward(const int* seq_chunk_offsets, const int* chunk_starts, 
       return fail(FRWKV_ERR_CUDA, "wkv7_chunk_forward: cannot reserve shared memory: %s",
                   cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
   }
-  wkv7_chunk_build_kernel<io_t><<<(unsigned)(num_chunks * num_heads), 128, kBuildSmem, stream>>>(
+  int device = 0, sm_count = 0;
+  cudaGetDevice(&device);
+  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+  const int num_items = num_chunks * num_heads;
+  const int build_grid = sm_count > 0 && sm_count < num_items ? sm_count : num_items;
+  wkv7_chunk_build_kernel<io_t><<<(unsigned)build_grid, kBuildThreads, kBuildSmem, stream>>>(
       chunk_starts, chunk_ends, status, static_cast<const io_t*>(r), static_cast<const io_t*>(w),
       static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),
       static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<unsigned char*>(workspace), num_heads,
-      error_flag);
+      num_items, error_flag);
   int rc = check_launch("wkv7_chunk_build_kernel");
   if (rc != FRWKV_OK) return rc;
   wkv7_chunk_scan_kernel<io_t><<<(unsigned)(num_sequences * num_heads), 128, kScanSmem, stream>>>(
@@ -594,6 +667,12 @@ int launch_chunk_forward(const int* seq_chunk_offsets, const int* chunk_starts, 
 
 }  // namespace
 }  // namespace frwkv
+
+#ifdef FRWKV_PROFILE_PHASES
+extern "C" int frwkv_debug_phase_clocks(long long* out16) {
+  return (int)cudaMemcpyFromSymbol(out16, frwkv::g_phase_clock, sizeof(long long) * 16);
+}
+#endif
 
 extern "C" size_t frwkv_wkv7_chunk_workspace_bytes(int num_chunks, int num_heads) {
   if (num_chunks <= 0 || num_heads <= 0) return 0;
