@@ -31,6 +31,8 @@ CUDA_SOURCES = [
     "wkv7_recurrent.cu",
     "umma_selftest.cu",
     "wkv7_chunk_fwd.cu",
+    "tmix_elementwise.cu",
+    "tmix_linear.cu",
 ]
 
 NVCC_FLAGS = [

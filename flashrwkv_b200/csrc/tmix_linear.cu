@@ -1,0 +1,338 @@
+// TMix projections: y[M][N] = act(x)[M][K] * W[N][K]^T (+ value-residual epilogue), grouped so that the three or four
+// low-rank projections of a TMix layer (decay / a / gate / value-residual) go out in one launch.
+//
+// Two kernels, picked by the row count:
+//   * M <= 8 ("skinny", decode): weight-bandwidth bound.  x is staged once per CTA in shared memory with the
+//     activation applied; every weight element is read exactly once with 16-byte loads.  For long rows (K >= 256) a
+//     warp owns an output column and reduces with shuffles; for short rows (rank-out, K = rank) a thread owns it.
+//   * M > 8: tcgen05 tensor-core GEMM (kind::f16, fp32 accumulate in tensor memory), 128 x 64 output tile per CTA,
+//     K in blocks of 64 through a 4-stage cp.async pipeline into chunk-major tiles (see umma.cuh).
+// Weights are in the reference's "original" layout [N][K] (K contiguous).
+//
+// Replaces linear_wag[v]_rank_in_f16_kernel / linear_wag[v]_rank_out_f16_kernel
+// (csrc/sm120/tmix/linear/infer_fp16_forward_varlen.cu:916-1233), the linear_orig_* / linear_t_* GEMV-class kernels
+// (:133-786) and the cublasGemmEx / cublasLtMatmul calls (:1403-1446,1687-1777) of the reference.
+
+#include "frwkv_common.cuh"
+#include "umma.cuh"
+
+namespace frwkv {
+namespace {
+
+constexpr int kMaxProblems = 4;
+
+struct LinearProblem {
+  const void* x;        // [M][K]
+  const void* w;        // [N][K]
+  void* y;              // [M][N]
+  const void* v;        // epilogue 1: [M][N]
+  const void* v_first;  // epilogue 1: [M][N]
+  const void* v0;       // epilogue 1: [N]
+  int n, k, act, epilogue;
+};
+struct LinearGroup {
+  LinearProblem p[kMaxProblems];
+};
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  if (act == 1) return tanhf(x);
+  if (act == 2) return 1.f / (1.f + __expf(-x));
+  return x;
+}
+
+template <typename io_t>
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  using IO = Io16<io_t>;
+  float2 t;
+  t = IO::unpack(u.x); f[0] = t.x; f[1] = t.y;
+  t = IO::unpack(u.y); f[2] = t.x; f[3] = t.y;
+  t = IO::unpack(u.z); f[4] = t.x; f[5] = t.y;
+  t = IO::unpack(u.w); f[6] = t.x; f[7] = t.y;
+}
+
+template <typename io_t>
+__device__ __forceinline__ float finish(const LinearProblem& pr, float acc, int m, int n) {
+  if (pr.epilogue == 1) {  // v + (v_first - v) * sigmoid(v0 + acc)
+    const long long o = (long long)m * pr.n + n;
+    const float vv = Io16<io_t>::load(static_cast<const io_t*>(pr.v) + o);
+    const float vf = Io16<io_t>::load(static_cast<const io_t*>(pr.v_first) + o);
+    const float z = Io16<io_t>::load(static_cast<const io_t*>(pr.v0) + n) + acc;
+    return fmaf(vf - vv, 1.f / (1.f + __expf(-z)), vv);
+  }
+  return acc;
+}
+
+// ---- skinny kernel --------------------------------------------------------------------------------------
+// grid = (column blocks, problems); dynamic shared memory = M * K 16-bit values (activation applied).
+template <typename io_t, int M>
+__global__ __launch_bounds__(256) void linear_skinny_kernel(LinearGroup group) {
+  using IO = Io16<io_t>;
+  extern __shared__ __align__(16) unsigned char xs_raw[];
+  const LinearProblem& pr = group.p[blockIdx.y];
+  const int K = pr.k, N = pr.n, kv = K >> 3;
+  uint4* xs = reinterpret_cast<uint4*>(xs_raw);
+  for (int i = threadIdx.x; i < M * kv; i += blockDim.x) {
+    uint4 u = __ldg(reinterpret_cast<const uint4*>(pr.x) + i);
+    if (pr.act != 0) {
+      float f[8];
+      unpack8<io_t>(u, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = apply_act(f[e], pr.act);
+      u = make_uint4(IO::pack(f[0], f[1]), IO::pack(f[2], f[3]), IO::pack(f[4], f[5]), IO::pack(f[6], f[7]));
+    }
+    xs[i] = u;
+  }
+  __syncthreads();
+  const io_t* w = static_cast<const io_t*>(pr.w);
+  io_t* y = static_cast<io_t*>(pr.y);
+  if (K >= 256) {
+    const int lane = threadIdx.x & 31;
+    const int warps_total = gridDim.x * (blockDim.x >> 5);
+    for (int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); n < N; n += warps_total) {
+      float acc[M];
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[m] = 0.f;
+      const uint4* wrow = reinterpret_cast<const uint4*>(w + (long long)n * K);
+      for (int c = lane; c < kv; c += 32) {
+        float wf[8];
+        unpack8<io_t>(__ldg(wrow + c), wf);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          float xf[8];
+          unpack8<io_t>(xs[m * kv + c], xf);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[m] = fmaf(wf[e], xf[e], acc[m]);
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+      }
+      if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) y[(long long)m * N + n] = IO::store(finish<io_t>(pr, acc[m], m, n));
+      }
+    }
+  } else {
+    for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < N; n += gridDim.x * blockDim.x) {
+      float acc[M];
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[m] = 0.f;
+      const uint4* wrow = reinterpret_cast<const uint4*>(w + (long long)n * K);
+      for (int c = 0; c < kv; ++c) {
+        float wf[8];
+        unpack8<io_t>(__ldg(wrow + c), wf);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          float xf[8];
+          unpack8<io_t>(xs[m * kv + c], xf);  // same address for the whole warp: broadcast
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[m] = fmaf(wf[e], xf[e], acc[m]);
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < M; ++m) y[(long long)m * N + n] = IO::store(finish<io_t>(pr, acc[m], m, n));
+    }
+  }
+}
+
+// ---- tensor-core kernel -----------------------------------------------------------------------------------
+constexpr int kBM = 128, kBN = 64, kBK = 64, kStages = 4;
+constexpr uint32_t kCsA = kBM * 16 + 16;  // chunk stride of the A stage tile (128 rows), padded against bank conflicts
+constexpr uint32_t kCsB = kBN * 16 + 16;
+constexpr uint32_t kStageBytes = 8 * kCsA + 8 * kCsB;
+constexpr uint32_t kTcSmem = kStages * kStageBytes;
+
+__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <typename io_t>
+__global__ __launch_bounds__(128, 2) void linear_tc_kernel(LinearGroup group, int M, int* __restrict__ error_flag) {
+  using IO = Io16<io_t>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ uint64_t done_bar[kStages];
+  __shared__ uint32_t tmem_holder;
+  const LinearProblem& pr = group.p[blockIdx.z];
+  const int K = pr.k, N = pr.n;
+  const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
+  if (n0 >= N) return;  // problems of one group may have different widths
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < kStages; ++i) umma::mbar_init(&done_bar[i], 1);
+    umma::mbar_fence_init();
+  }
+  if (warp == 0) umma::tmem_alloc(&tmem_holder, 64);
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = tmem_holder;
+  const uint32_t sbase = umma::smem_u32(smem);
+  const io_t* x = static_cast<const io_t*>(pr.x);
+  const io_t* w = static_cast<const io_t*>(pr.w);
+  const int KB = (K + kBK - 1) / kBK;
+  constexpr bool is_bf16 = sizeof(typename IO::pair) == 4 && !__is_same(io_t, __half);
+  const uint32_t idesc = (1u << 4) | ((is_bf16 ? 1u : 0u) << 7) | ((is_bf16 ? 1u : 0u) << 10) |
+                         (uint32_t(kBN >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+
+  auto load_stage = [&](int kb) {
+    const uint32_t st = sbase + uint32_t(kb % kStages) * kStageBytes;
+    const int k0 = kb * kBK;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = i * 128 + tid, r = idx >> 3, c = idx & 7;
+      const bool in = (m0 + r < M) && (k0 + 8 * c < K);
+      const io_t* src = in ? x + (long long)(m0 + r) * K + k0 + 8 * c : x;
+      umma::cp_async16(st + uint32_t(c) * kCsA + r * 16, src, in ? 16u : 0u);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = i * 128 + tid, r = idx >> 3, c = idx & 7;
+      const bool in = (n0 + r < N) && (k0 + 8 * c < K);
+      const io_t* src = in ? w + (long long)(n0 + r) * K + k0 + 8 * c : w;
+      umma::cp_async16(st + 8 * kCsA + uint32_t(c) * kCsB + r * 16, src, in ? 16u : 0u);
+    }
+  };
+
+  bool ok = true;
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) {
+    if (s < KB) load_stage(s);
+    umma::cp_async_commit();
+  }
+  for (int kb = 0; kb < KB; ++kb) {
+    const int pre = kb + kStages - 1;
+    if (pre < KB) {
+      if (kb >= 1) ok = umma::mbar_wait(&done_bar[(kb - 1) % kStages], ((kb - 1) / kStages) & 1) && ok;
+      load_stage(pre);
+    }
+    umma::cp_async_commit();
+    asm volatile("cp.async.wait_group %0;" ::"n"(kStages - 1) : "memory");
+    unsigned char* st = smem + uint32_t(kb % kStages) * kStageBytes;
+    if (pr.act != 0) {  // activation on the A operand: each thread transforms the chunks it copied itself
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int idx = i * 128 + tid, r = idx >> 3, c = idx & 7;
+        uint4* q = reinterpret_cast<uint4*>(st + uint32_t(c) * kCsA + r * 16);
+        float f[8];
+        unpack8<io_t>(*q, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = apply_act(f[e], pr.act);
+        *q = make_uint4(IO::pack(f[0], f[1]), IO::pack(f[2], f[3]), IO::pack(f[4], f[5]), IO::pack(f[6], f[7]));
+      }
+    }
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    if (tid == 0) {
+      umma::fence_after_sync();
+      const uint32_t a_addr = sbase + uint32_t(kb % kStages) * kStageBytes, b_addr = a_addr + 8 * kCsA;
+#pragma unroll
+      for (int ks = 0; ks < kBK / 16; ++ks)
+        mma_f16_ss(tmem, umma::desc_k_major(a_addr + ks * 2 * kCsA, kCsA), umma::desc_k_major(b_addr + ks * 2 * kCsB, kCsB),
+                   idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+      umma::mma_commit(&done_bar[kb % kStages]);
+    }
+  }
+  ok = umma::mbar_wait(&done_bar[(KB - 1) % kStages], ((KB - 1) / kStages) & 1) && ok;
+  umma::fence_after_sync();
+  if (ok) {
+    const int m = m0 + warp * 32 + (tid & 31);
+    io_t* y = static_cast<io_t*>(pr.y);
+#pragma unroll 1
+    for (int c0 = 0; c0 < kBN; c0 += 32) {
+      uint32_t u[32];
+      umma::tmem_ld32(tmem + (uint32_t(warp * 32) << 16) + c0, u);
+      umma::tmem_ld_wait();
+      if (m < M) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          const int n = n0 + c0 + j;
+          if (n < N) {
+            float o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = finish<io_t>(pr, __uint_as_float(u[j + e]), m, n + e);
+            *reinterpret_cast<uint4*>(y + (long long)m * N + n) =
+                make_uint4(IO::pack(o[0], o[1]), IO::pack(o[2], o[3]), IO::pack(o[4], o[5]), IO::pack(o[6], o[7]));
+          }
+        }
+      }
+    }
+  } else if (tid == 0 && error_flag != nullptr) {
+    atomicExch(error_flag, 3);
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) umma::tmem_dealloc(tmem, 64);
+}
+
+template <typename io_t>
+int launch_linear(const LinearGroup& g, int count, int M, int max_n, int max_k, int* error_flag, cudaStream_t stream) {
+  if (M <= 8) {
+    const size_t smem = (size_t)M * max_k * 2;
+    const int blocks = max_k >= 256 ? (max_n + 7) / 8 : (max_n + 255) / 256;
+    dim3 grid(blocks < 1 ? 1 : blocks, count);
+#define FRWKV_SKINNY(MM)                                                                                      \
+  case MM: {                                                                                                  \
+    if (smem > 48 * 1024) {                                                                                   \
+      cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<io_t, MM>,                                    \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+      if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "tmix_linear: %s", cudaGetErrorString(e));            \
+    }                                                                                                         \
+    linear_skinny_kernel<io_t, MM><<<grid, 256, smem, stream>>>(g);                                           \
+    break;                                                                                                    \
+  }
+    switch (M) {
+      FRWKV_SKINNY(1) FRWKV_SKINNY(2) FRWKV_SKINNY(3) FRWKV_SKINNY(4)
+      FRWKV_SKINNY(5) FRWKV_SKINNY(6) FRWKV_SKINNY(7) FRWKV_SKINNY(8)
+    }
+#undef FRWKV_SKINNY
+    return check_launch("linear_skinny_kernel");
+  }
+  cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<io_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem);
+  if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "tmix_linear: %s", cudaGetErrorString(e));
+  dim3 grid((max_n + kBN - 1) / kBN, (M + kBM - 1) / kBM, count);
+  linear_tc_kernel<io_t><<<grid, 128, kTcSmem, stream>>>(g, M, error_flag);
+  return check_launch("linear_tc_kernel");
+}
+
+}  // namespace
+}  // namespace frwkv
+
+extern "C" int frwkv_tmix_linear_grouped(const frwkv_linear_problem* problems, int count, int m, int io_dtype,
+                                         int32_t* error_flag, frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(problems != nullptr, "tmix_linear: null pointer argument");
+  FRWKV_REQUIRE(count >= 1 && count <= kMaxProblems, "tmix_linear: 1..4 problems per call");
+  FRWKV_REQUIRE(m > 0, "tmix_linear: row count must be positive");
+  LinearGroup g;
+  int max_n = 0, max_k = 0;
+  for (int i = 0; i < count; ++i) {
+    const frwkv_linear_problem& p = problems[i];
+    FRWKV_REQUIRE(p.x && p.weight && p.y, "tmix_linear: null pointer in problem %d", i);
+    FRWKV_REQUIRE(p.n > 0 && p.k > 0 && p.n % 8 == 0 && p.k % 8 == 0,
+                  "tmix_linear: feature counts must be positive multiples of 8 (problem %d: n=%d k=%d)", i, p.n, p.k);
+    FRWKV_REQUIRE(p.act >= 0 && p.act <= 2 && p.epilogue >= 0 && p.epilogue <= 1, "tmix_linear: bad act/epilogue code");
+    if (p.epilogue == 1) FRWKV_REQUIRE(p.v && p.v_first && p.v0, "tmix_linear: value-residual epilogue needs v, v_first, v0");
+    g.p[i] = LinearProblem{p.x, p.weight, p.y, p.v, p.v_first, p.v0, p.n, p.k, p.act, p.epilogue};
+    max_n = p.n > max_n ? p.n : max_n;
+    max_k = p.k > max_k ? p.k : max_k;
+  }
+  for (int i = count; i < kMaxProblems; ++i) g.p[i] = g.p[0];
+  if (m <= 8) FRWKV_REQUIRE((size_t)m * max_k * 2 <= 200 * 1024, "tmix_linear: K too large for the small-row kernel");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (io_dtype == FRWKV_DTYPE_BF16) return launch_linear<__nv_bfloat16>(g, count, m, max_n, max_k, error_flag, s);
+  if (io_dtype == FRWKV_DTYPE_FP16) return launch_linear<__half>(g, count, m, max_n, max_k, error_flag, s);
+  return fail(FRWKV_ERR_UNSUPPORTED, "tmix_linear: tensors must be float16 or bfloat16");
+}

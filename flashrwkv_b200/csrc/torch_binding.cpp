@@ -372,6 +372,177 @@ std::tuple<torch::Tensor, torch::Tensor> rl_infctx_chunk_fp32io16_forward(
   return {output, working};
 }
 
+// ---- TMix ---------------------------------------------------------------------------------------------
+void check_io16(const torch::Tensor& t, const char* name, const torch::Tensor& ref) {
+  check_cuda_contiguous(t, name);
+  TORCH_CHECK(t.scalar_type() == torch::kFloat16 || t.scalar_type() == torch::kBFloat16, name,
+              " must be float16 or bfloat16");
+  TORCH_CHECK(t.scalar_type() == ref.scalar_type(), name, " dtype mismatch");
+  TORCH_CHECK(t.device() == ref.device(), name, " must share x's device");
+}
+
+std::vector<torch::Tensor> tmix_mix6_forward_varlen(torch::Tensor x, torch::Tensor shift_state_pool, torch::Tensor x_r,
+                                                    torch::Tensor x_w, torch::Tensor x_k, torch::Tensor x_v,
+                                                    torch::Tensor x_a, torch::Tensor x_g, torch::Tensor cu,
+                                                    torch::Tensor idx, int64_t max_seqlen,
+                                                    std::shared_ptr<MetadataTicket> ticket) {
+  check_io16(x, "x", x);
+  TORCH_CHECK(x.dim() == 2 && x.size(0) > 0 && x.size(1) > 0, "x must have packed shape [total_tokens,C]");
+  TORCH_CHECK(x.size(1) % 8 == 0, "C must be a multiple of 8");
+  const std::pair<const torch::Tensor*, const char*> vecs[] = {{&x_r, "x_r"}, {&x_w, "x_w"}, {&x_k, "x_k"},
+                                                               {&x_v, "x_v"}, {&x_a, "x_a"}, {&x_g, "x_g"}};
+  for (const auto& item : vecs) {
+    check_io16(*item.first, item.second, x);
+    TORCH_CHECK(item.first->dim() == 1 && item.first->size(0) == x.size(1), "all mix6 coefficients must have shape [C]");
+  }
+  check_io16(shift_state_pool, "shift_state_pool", x);
+  TORCH_CHECK(shift_state_pool.dim() == 2 && shift_state_pool.size(1) == x.size(1),
+              "shift_state_pool must have shape [slots,C]");
+  check_cuda_contiguous(cu, "cu_seqlens");
+  check_cuda_contiguous(idx, "state_indices");
+  TORCH_CHECK(cu.scalar_type() == torch::kInt32 && idx.scalar_type() == torch::kInt32, "recurrent metadata must be int32");
+  TORCH_CHECK(cu.dim() == 1 && idx.dim() == 1 && idx.numel() > 0 && cu.numel() == idx.numel() + 1,
+              "cu_seqlens must have shape [B+1] and state_indices shape [B]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  torch::Tensor launch_cu, launch_idx, status;
+  if (ticket) {
+    ticket->check_compatible(cu, idx, x.size(0), shift_state_pool.size(0), max_seqlen);
+    launch_cu = ticket->cu_snapshot();
+    launch_idx = ticket->idx_snapshot();
+    status = ticket->status();
+    max_seqlen = ticket->max_seqlen();
+  } else {
+    auto prepared = launch_validation(cu, idx, x.size(0), shift_state_pool.size(0));
+    launch_cu = std::move(prepared.cu);
+    launch_idx = std::move(prepared.idx);
+    status = std::move(prepared.status);
+  }
+  auto out = torch::empty({6, x.size(0), x.size(1)}, x.options());
+  check_rc(frwkv_tmix_mix6_forward_varlen(
+      x.data_ptr(), shift_state_pool.data_ptr(), x_r.data_ptr(), x_w.data_ptr(), x_k.data_ptr(), x_v.data_ptr(),
+      x_a.data_ptr(), x_g.data_ptr(), launch_cu.data_ptr<int>(), launch_idx.data_ptr<int>(), status.data_ptr<int>(),
+      out.data_ptr(), static_cast<int>(x.size(0)), static_cast<int>(idx.numel()), static_cast<int>(x.size(1)),
+      static_cast<int>(std::min<int64_t>(max_seqlen, std::numeric_limits<int>::max())), io_dtype_of(x),
+      current_stream(x)));
+  return out.unbind(0);
+}
+
+void check_rows_channels(const torch::Tensor& t, const char* name, const torch::Tensor& ref) {
+  check_io16(t, name, ref);
+  TORCH_CHECK(t.dim() == 2 && t.sizes() == ref.sizes(), name, " must have packed shape [total_tokens,C]");
+}
+void check_channel_vector(const torch::Tensor& t, const char* name, const torch::Tensor& ref) {
+  check_io16(t, name, ref);
+  TORCH_CHECK(t.dim() == 1 && t.size(0) == ref.size(1), name, " must have shape [C]");
+}
+
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> tmix_kk_a_gate_forward_varlen(
+    torch::Tensor k, torch::Tensor k_k, torch::Tensor a0, torch::Tensor a12, torch::Tensor k_a, int64_t head_size,
+    int64_t batch_size, int64_t max_seqlen) {
+  check_io16(k, "k", k);
+  TORCH_CHECK(k.dim() == 2 && k.size(0) > 0 && k.size(1) > 0, "k must have packed shape [total_tokens,C]");
+  TORCH_CHECK(head_size == 64 || head_size == 128 || head_size == 256, "head_size must be 64, 128, or 256");
+  TORCH_CHECK(k.size(1) % head_size == 0, "C must be divisible by head_size");
+  TORCH_CHECK(batch_size > 0 && max_seqlen > 0, "batch_size and max_seqlen must be positive");
+  check_rows_channels(a12, "a12", k);
+  check_channel_vector(k_k, "k_k", k);
+  check_channel_vector(a0, "a0", k);
+  check_channel_vector(k_a, "k_a", k);
+  const c10::cuda::CUDAGuard guard(k.device());
+  auto new_k = torch::empty_like(k), neg_kk = torch::empty_like(k), kka = torch::empty_like(k);
+  check_rc(frwkv_tmix_kk_a_gate_forward_varlen(k.data_ptr(), k_k.data_ptr(), a0.data_ptr(), a12.data_ptr(),
+                                               k_a.data_ptr(), new_k.data_ptr(), neg_kk.data_ptr(), kka.data_ptr(),
+                                               k.size(0), static_cast<int>(k.size(1)), static_cast<int>(head_size),
+                                               io_dtype_of(k), current_stream(k)));
+  return {new_k, neg_kk, kka};
+}
+
+torch::Tensor tmix_lnx_rkvres_xg_forward_varlen(torch::Tensor x, torch::Tensor r, torch::Tensor k, torch::Tensor v,
+                                                torch::Tensor r_k, torch::Tensor weight, torch::Tensor bias,
+                                                torch::Tensor g, int64_t head_size, int64_t batch_size,
+                                                int64_t max_seqlen) {
+  check_io16(x, "x", x);
+  TORCH_CHECK(x.dim() == 2 && x.size(0) > 0 && x.size(1) > 0, "x must have packed shape [total_tokens,C]");
+  TORCH_CHECK(head_size == 64 || head_size == 128 || head_size == 256, "head_size must be 64, 128, or 256");
+  TORCH_CHECK(x.size(1) % head_size == 0, "C must be divisible by head_size");
+  TORCH_CHECK(batch_size > 0 && max_seqlen > 0, "batch_size and max_seqlen must be positive");
+  check_rows_channels(r, "r", x);
+  check_rows_channels(k, "k", x);
+  check_rows_channels(v, "v", x);
+  check_rows_channels(g, "g", x);
+  check_channel_vector(r_k, "r_k", x);
+  check_channel_vector(weight, "weight", x);
+  check_channel_vector(bias, "bias", x);
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto out = torch::empty_like(x);
+  check_rc(frwkv_tmix_lnx_rkvres_xg_forward_varlen(x.data_ptr(), r.data_ptr(), k.data_ptr(), v.data_ptr(), r_k.data_ptr(),
+                                                   weight.data_ptr(), bias.data_ptr(), g.data_ptr(), out.data_ptr(),
+                                                   x.size(0), static_cast<int>(x.size(1)), static_cast<int>(head_size),
+                                                   64.0e-5f, io_dtype_of(x), current_stream(x)));
+  return out;
+}
+
+torch::Tensor tmix_vres_gate_forward_varlen(torch::Tensor v, torch::Tensor v_first, torch::Tensor v0, torch::Tensor v12) {
+  check_io16(v, "v", v);
+  TORCH_CHECK(v.dim() == 2 && v.size(0) > 0 && v.size(1) > 0 && v.size(1) % 8 == 0,
+              "v must have packed shape [total_tokens,C] with C a multiple of 8");
+  check_rows_channels(v_first, "v_first", v);
+  check_rows_channels(v12, "v12", v);
+  check_channel_vector(v0, "v0", v);
+  const c10::cuda::CUDAGuard guard(v.device());
+  auto out = torch::empty_like(v);
+  check_rc(frwkv_tmix_vres_gate_forward_varlen(v.data_ptr(), v_first.data_ptr(), v0.data_ptr(), v12.data_ptr(),
+                                               out.data_ptr(), v.size(0), static_cast<int>(v.size(1)), io_dtype_of(v),
+                                               current_stream(v)));
+  return out;
+}
+
+// y_i = act_i(x_i) @ weight_i^T for up to four projections sharing the row count; weights in the original [N,K]
+// layout.  `vres` = (v, v_first, v0) applies the value-residual epilogue to the LAST projection.
+std::vector<torch::Tensor> tmix_linear_grouped(std::vector<torch::Tensor> xs, std::vector<torch::Tensor> weights,
+                                               std::vector<int64_t> acts,
+                                               std::optional<std::tuple<torch::Tensor, torch::Tensor, torch::Tensor>> vres) {
+  const size_t count = xs.size();
+  TORCH_CHECK(count >= 1 && count <= 4, "between one and four projections per call");
+  TORCH_CHECK(weights.size() == count && acts.size() == count, "xs, weights and acts must have the same length");
+  const torch::Tensor& x0 = xs[0];
+  check_io16(x0, "x", x0);
+  TORCH_CHECK(x0.dim() == 2 && x0.size(0) > 0, "x must have shape [M,K]");
+  const int64_t M = x0.size(0);
+  TORCH_CHECK(M <= std::numeric_limits<int>::max(), "row count must fit in int32");
+  std::vector<frwkv_linear_problem> problems(count);
+  std::vector<torch::Tensor> outs;
+  const c10::cuda::CUDAGuard guard(x0.device());
+  for (size_t i = 0; i < count; ++i) {
+    check_io16(xs[i], "x", x0);
+    check_io16(weights[i], "weight", x0);
+    TORCH_CHECK(xs[i].dim() == 2 && xs[i].size(0) == M, "all inputs must have shape [M,K]");
+    TORCH_CHECK(weights[i].dim() == 2 && weights[i].size(1) == xs[i].size(1), "weight must have shape [N,K] matching x");
+    TORCH_CHECK(xs[i].size(1) % 8 == 0 && weights[i].size(0) % 8 == 0, "feature counts must be multiples of 8");
+    TORCH_CHECK(acts[i] >= 0 && acts[i] <= 2, "act must be 0 (none), 1 (tanh) or 2 (sigmoid)");
+    outs.push_back(torch::empty({M, weights[i].size(0)}, x0.options()));
+    problems[i] = frwkv_linear_problem{xs[i].data_ptr(), weights[i].data_ptr(), outs[i].data_ptr(),
+                                       static_cast<int>(weights[i].size(0)), static_cast<int>(xs[i].size(1)),
+                                       static_cast<int>(acts[i]), 0, nullptr, nullptr, nullptr};
+  }
+  if (vres.has_value()) {
+    const auto& [v, v_first, v0] = *vres;
+    const torch::Tensor& y = outs[count - 1];
+    check_io16(v, "v", x0);
+    check_io16(v_first, "v_first", x0);
+    check_io16(v0, "v0", x0);
+    TORCH_CHECK(v.sizes() == y.sizes() && v_first.sizes() == y.sizes(), "v and v_first must have shape [M,N]");
+    TORCH_CHECK(v0.dim() == 1 && v0.size(0) == y.size(1), "v0 must have shape [N]");
+    problems[count - 1].epilogue = 1;
+    problems[count - 1].v = v.data_ptr();
+    problems[count - 1].v_first = v_first.data_ptr();
+    problems[count - 1].v0 = v0.data_ptr();
+  }
+  check_rc(frwkv_tmix_linear_grouped(problems.data(), static_cast<int>(count), static_cast<int>(M), io_dtype_of(x0),
+                                     nullptr, current_stream(x0)));
+  return outs;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -403,4 +574,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("chunk_token_starts"), py::arg("chunk_token_ends"), py::arg("state"), py::arg("r"),
         py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"), py::arg("strategy") = 1,
         py::arg("scale") = 1.0, py::arg("decay_bias") = py::none());
+  m.def("tmix_mix6_forward_varlen", &tmix_mix6_forward_varlen, py::arg("x"), py::arg("shift_state_pool"),
+        py::arg("x_r"), py::arg("x_w"), py::arg("x_k"), py::arg("x_v"), py::arg("x_a"), py::arg("x_g"),
+        py::arg("cu_seqlens"), py::arg("state_indices"), py::arg("max_seqlen") = -1,
+        py::arg("validated_metadata") = py::none());
+  m.def("tmix_kk_a_gate_forward_varlen", &tmix_kk_a_gate_forward_varlen, py::arg("k"), py::arg("k_k"), py::arg("a0"),
+        py::arg("a12"), py::arg("k_a"), py::arg("head_size") = 64, py::arg("batch_size") = 1,
+        py::arg("max_seqlen") = 1);
+  m.def("tmix_lnx_rkvres_xg_forward_varlen", &tmix_lnx_rkvres_xg_forward_varlen, py::arg("x"), py::arg("r"),
+        py::arg("k"), py::arg("v"), py::arg("r_k"), py::arg("weight"), py::arg("bias"), py::arg("g"),
+        py::arg("head_size") = 64, py::arg("batch_size") = 1, py::arg("max_seqlen") = 1);
+  m.def("tmix_vres_gate_forward_varlen", &tmix_vres_gate_forward_varlen, py::arg("v"), py::arg("v_first"),
+        py::arg("v0"), py::arg("v12"));
+  m.def("tmix_linear_grouped", &tmix_linear_grouped, py::arg("xs"), py::arg("weights"), py::arg("acts"),
+        py::arg("vres") = py::none());
 }

@@ -1,0 +1,167 @@
+"""TMix projections: dense C x C linears and the low-rank (rank-in / rank-out) group.
+
+Mirror of the reference's `flashrwkv2/tmix/linear/__init__.py:25-482` (names, positional/keyword split, the
+`R <= 512` limit).  Every operator here is `act(x) @ W^T` with `W` in the reference's *original* layout `[N,K]`;
+groups of three or four projections go to the device in one launch.  Weights given only in the reference's
+*runtime* layout `[K,N]` are refused: the kernels read the original layout (no hidden transposes).
+fp16 as in the reference, bf16 in addition.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..._ext import extension
+from .._checks import check_io
+
+_ACT = {"none": 0, "tanh": 1, "sigmoid": 2}
+LOWRANK_LIMIT = 512
+
+
+def _check_x(x, name="x", ref=None):
+    check_io(name, x, ref)
+    if x.ndim != 2 or x.shape[0] <= 0 or x.shape[1] <= 0:
+        raise ValueError(f"{name} must have packed shape [M,K]")
+
+
+def _original(name, original, runtime, x, *, rank_dim: int | None, input_projection: bool):
+    """Pick the original-layout weight [N,K] for `x @ W^T`; validate shapes and the low-rank limit."""
+    if original is None and runtime is None:
+        raise ValueError(f"{name}: an original-layout or a runtime-layout weight is required")
+    if original is None:
+        raise ValueError(f"{name}: only a runtime-layout weight was given; this build reads the original "
+                         f"[out_features,in_features] layout")
+    check_io(name, original, x)
+    if original.ndim != 2 or original.shape[1] != x.shape[1]:
+        raise ValueError(f"{name} must have original layout [N,K] with K = {x.shape[1]}")
+    if runtime is not None:
+        check_io(f"{name}_runtime", runtime, x)
+        if runtime.shape != (original.shape[1], original.shape[0]):
+            raise ValueError(f"{name}_runtime must be the [K,N] transpose of {name}")
+    if rank_dim is not None:
+        rank = original.shape[0] if input_projection else original.shape[1]
+        if rank > rank_dim:
+            raise ValueError(f"{name}: low-rank dimension {rank} exceeds R <= {rank_dim}")
+    return original
+
+
+def _grouped(xs, weights, acts, vres=None):
+    return extension().tmix_linear_grouped(list(xs), list(weights), [_ACT[a] for a in acts], vres)
+
+
+# ---- dense linears ----------------------------------------------------------------------------------------
+def infer_tmix_linear_forward_varlen(x, weight, *, weight_is_transposed: bool = False):
+    """`x [M,K] @ weight[N,K]^T -> [M,N]`."""
+    _check_x(x)
+    if weight_is_transposed:
+        raise ValueError("weight_is_transposed=True (runtime [K,N] layout) is not built; pass weight as [N,K]")
+    w = _original("weight", weight, None, x, rank_dim=None, input_projection=True)
+    return _grouped([x], [w], ["none"])[0]
+
+
+def infer_tmix_linear_attention_c2c_forward_varlen(x, weight):
+    return infer_tmix_linear_forward_varlen(x, weight)
+
+
+def infer_tmix_linear_ffn_key_forward_varlen(x, weight):
+    return infer_tmix_linear_forward_varlen(x, weight)
+
+
+def _linear_t(x, weight_t, act):
+    _check_x(x)
+    if x.shape[0] > 65535:
+        raise ValueError("M must be at most 65535")
+    w = _original("weight_t", weight_t, None, x, rank_dim=None, input_projection=True)
+    return _grouped([x], [w], [act])[0]
+
+
+def infer_tmix_linear_t_forward_varlen(x, weight_t):
+    return _linear_t(x, weight_t, "none")
+
+
+def infer_tmix_linear_t_tanh_forward_varlen(x, weight_t):
+    return _linear_t(x, weight_t, "tanh")
+
+
+def infer_tmix_linear_t_sigmoid_forward_varlen(x, weight_t):
+    return _linear_t(x, weight_t, "sigmoid")
+
+
+def infer_tmix_linear_t_vres_forward_varlen(x, weight_t, v, v_first, v0):
+    _check_x(x)
+    w = _original("weight_t", weight_t, None, x, rank_dim=None, input_projection=True)
+    return _grouped([x], [w], ["none"], (v, v_first, v0))[0]
+
+
+# ---- single low-rank projections ----------------------------------------------------------------------------
+def _rank(x, weight, weight_t, act, input_projection):
+    _check_x(x)
+    w = _original("weight_t", weight_t, weight, x, rank_dim=LOWRANK_LIMIT, input_projection=input_projection)
+    return _grouped([x], [w], [act])[0]
+
+
+def infer_tmix_linear_rank_in_forward_varlen(x, weight=None, weight_t=None):
+    return _rank(x, weight, weight_t, "none", True)
+
+
+def infer_tmix_linear_rank_out_forward_varlen(x, weight=None, weight_t=None):
+    return _rank(x, weight, weight_t, "none", False)
+
+
+def infer_tmix_linear_rank_out_tanh_forward_varlen(x, weight=None, weight_t=None):
+    return _rank(x, weight, weight_t, "tanh", False)
+
+
+def infer_tmix_linear_rank_out_sigmoid_forward_varlen(x, weight=None, weight_t=None):
+    return _rank(x, weight, weight_t, "sigmoid", False)
+
+
+# ---- the composite low-rank group ----------------------------------------------------------------------------
+def _rows(named):
+    first = named[0][1]
+    for name, t in named:
+        _check_x(t, name, None if t is first else first)
+        if t.shape[0] != first.shape[0]:
+            raise ValueError(f"{name} must have {first.shape[0]} packed rows")
+
+
+def infer_tmix_lowrank_in_forward_varlen(x_w, x_a, x_g, w1, a1, g1, *, w1_runtime=None, a1_runtime=None,
+                                         g1_runtime=None):
+    """Rank-in for decay / a / gate: three `[M,C] @ [R,C]^T -> [M,R]` in one launch."""
+    _rows([("x_w", x_w), ("x_a", x_a), ("x_g", x_g)])
+    ws = [_original(n, o, r, x, rank_dim=LOWRANK_LIMIT, input_projection=True)
+          for n, o, r, x in (("w1", w1, w1_runtime, x_w), ("a1", a1, a1_runtime, x_a), ("g1", g1, g1_runtime, x_g))]
+    return tuple(_grouped([x_w, x_a, x_g], ws, ["none"] * 3))
+
+
+def infer_tmix_lowrank_wagv_in_forward_varlen(x_w, x_a, x_g, x_v, w1, a1, g1, v1, *, w1_runtime=None,
+                                              a1_runtime=None, g1_runtime=None, v1_runtime=None):
+    """Rank-in for decay / a / gate / value-residual in one launch."""
+    _rows([("x_w", x_w), ("x_a", x_a), ("x_g", x_g), ("x_v", x_v)])
+    ws = [_original(n, o, r, x, rank_dim=LOWRANK_LIMIT, input_projection=True)
+          for n, o, r, x in (("w1", w1, w1_runtime, x_w), ("a1", a1, a1_runtime, x_a), ("g1", g1, g1_runtime, x_g),
+                             ("v1", v1, v1_runtime, x_v))]
+    return tuple(_grouped([x_w, x_a, x_g, x_v], ws, ["none"] * 4))
+
+
+def infer_tmix_lowrank_out_forward_varlen(w1, a1, g1, w2, a2, g2, *, w2_runtime=None, a2_runtime=None,
+                                          g2_runtime=None):
+    """Rank-out: `tanh(w1) @ w2^T`, `a1 @ a2^T`, `sigmoid(g1) @ g2^T` (weights `[C,R]`) in one launch."""
+    _rows([("w1", w1), ("a1", a1), ("g1", g1)])
+    ws = [_original(n, o, r, x, rank_dim=LOWRANK_LIMIT, input_projection=False)
+          for n, o, r, x in (("w2", w2, w2_runtime, w1), ("a2", a2, a2_runtime, a1), ("g2", g2, g2_runtime, g1))]
+    return tuple(_grouped([w1, a1, g1], ws, ["tanh", "none", "sigmoid"]))
+
+
+def infer_tmix_lowrank_vres_forward_varlen(w1, a1, g1, v1, w2, a2, g2, v2, v, v_first, v0, *, w2_runtime=None,
+                                           a2_runtime=None, g2_runtime=None, v2_runtime=None):
+    """Rank-out for W/A/G plus the value path with its residual gate fused: `v + (v_first - v) * sigmoid(v0 + v1 @ v2^T)`."""
+    _rows([("w1", w1), ("a1", a1), ("g1", g1), ("v1", v1)])
+    ws = [_original(n, o, r, x, rank_dim=LOWRANK_LIMIT, input_projection=False)
+          for n, o, r, x in (("w2", w2, w2_runtime, w1), ("a2", a2, a2_runtime, a1), ("g2", g2, g2_runtime, g1),
+                             ("v2", v2, v2_runtime, v1))]
+    for name, t in (("v", v), ("v_first", v_first), ("v0", v0)):
+        check_io(name, t, w1)
+    return tuple(_grouped([w1, a1, g1, v1], ws, ["tanh", "none", "sigmoid", "none"], (v, v_first, v0)))
+
+
+__all__ = [n for n in dir() if n.startswith("infer_tmix_")]

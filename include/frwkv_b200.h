@@ -111,6 +111,59 @@ int frwkv_wkv7_chunk_fp32io16_forward(
     frwkv_stream_t stream);
 
 /*
+ * TMix token shift: out[j] = x + (prev - x) * mix_j for the six mix vectors (r, w, k, v, a, g); prev is the previous
+ * packed row, or shift_state_pool[state_indices[s]] at the first row of sequence s; afterwards that slot holds the
+ * sequence's last row.  Replaces tmix_mix6_forward_varlen_cuda (csrc/sm120/tmix/mix6/infer_fp16_forward_varlen.cu:190-303).
+ *   x io16 [rows, C]; shift_state_pool io16 [slots, C]; x_r..x_g io16 [C]; out io16 [6, rows, C]; C % 8 == 0.
+ *   max_seqlen: longest sequence if known (1 lets the kernel skip the separate slot-update launch), else <= 0.
+ */
+int frwkv_tmix_mix6_forward_varlen(const void* x, void* shift_state_pool, const void* x_r, const void* x_w,
+                                   const void* x_k, const void* x_v, const void* x_a, const void* x_g,
+                                   const int32_t* cu_seqlens, const int32_t* state_indices,
+                                   const int32_t* metadata_status, void* out, int total_rows, int num_sequences,
+                                   int channels, int max_seqlen, int io_dtype, frwkv_stream_t stream);
+
+/* (k', -kk, kk*a) with kk = normalize_head(k * k_k), a = sigmoid(a0 + a12), k' = k * (1 + (a - 1) * k_a).
+ * Replaces tmix_kk_a_gate_forward_varlen_cuda (csrc/sm120/tmix/kk_a_gate/infer_fp16_forward_varlen.cu:116-210).
+ * k, a12, outputs io16 [rows, C]; k_k, a0, k_a io16 [C]; head_size must be 64. */
+int frwkv_tmix_kk_a_gate_forward_varlen(const void* k, const void* k_k, const void* a0, const void* a12,
+                                        const void* k_a, void* new_k, void* neg_kk, void* kka, long long total_rows,
+                                        int channels, int head_size, int io_dtype, frwkv_stream_t stream);
+
+/* (GroupNorm per head of x (biased variance, eps) * weight + bias + (sum_d r k r_k) * v) * g.
+ * Replaces tmix_lnx_rkvres_xg_forward_varlen_cuda (csrc/sm120/tmix/lnx_rkvres_xg/infer_fp16_forward_varlen.cu:133-244). */
+int frwkv_tmix_lnx_rkvres_xg_forward_varlen(const void* x, const void* r, const void* k, const void* v, const void* r_k,
+                                            const void* weight, const void* bias, const void* g, void* out,
+                                            long long total_rows, int channels, int head_size, float eps, int io_dtype,
+                                            frwkv_stream_t stream);
+
+/* v + (v_first - v) * sigmoid(v0 + v12).  Replaces tmix_vres_gate_forward_varlen_cuda
+ * (csrc/sm120/tmix/vres_gate/infer_fp16_forward_varlen.cu:47-93). */
+int frwkv_tmix_vres_gate_forward_varlen(const void* v, const void* v_first, const void* v0, const void* v12, void* out,
+                                        long long total_rows, int channels, int io_dtype, frwkv_stream_t stream);
+
+/*
+ * Grouped TMix projections: for each of 1..4 problems, y[m][n] = act(x)[m][k] * weight[n][k]^T, optionally followed by
+ * the value-residual epilogue  y = v + (v_first - v) * sigmoid(v0 + y).  All problems share the row count m.
+ * Replaces tmix_lowrank_{in,wagv_in,out,vres}_forward_varlen, tmix_linear_forward_varlen and the rank_in/rank_out/
+ * linear_t family (csrc/sm120/tmix/linear/infer_fp16_forward_varlen.cu:2229-3100).  m <= 8 runs the bandwidth-bound
+ * small-row kernel, larger m the tcgen05 GEMM.  `problems` is a host array.  n and k must be multiples of 8.
+ */
+typedef struct {
+  const void* x;       /* io16 [m][k] */
+  const void* weight;  /* io16 [n][k]  (the reference's original layout) */
+  void* y;             /* io16 [m][n] */
+  int n, k;
+  int act;             /* applied to x: 0 none, 1 tanh, 2 sigmoid */
+  int epilogue;        /* 0 none, 1 value residual */
+  const void* v;       /* epilogue 1: io16 [m][n] */
+  const void* v_first; /* epilogue 1: io16 [m][n] */
+  const void* v0;      /* epilogue 1: io16 [n] */
+} frwkv_linear_problem;
+int frwkv_tmix_linear_grouped(const frwkv_linear_problem* problems, int count, int m, int io_dtype,
+                              int32_t* error_flag, frwkv_stream_t stream);
+
+/*
  * Diagnostic: D[128][n] = A[128][64] * B[n][64]^T through one tcgen05.mma (kind::tf32) chain of 8 K-steps,
  * with A and B staged in shared memory as chunk-major tiles of the given chunk stride (bytes).  No
  * counterpart in the reference; used by the tests to pin the descriptor encodings the chunk kernels rely on.

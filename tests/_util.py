@@ -15,6 +15,11 @@ _IO_DTYPE = {
     "rl_fp16": torch.float16,
     "statetune": torch.float16,
     "pretrain": torch.bfloat16,
+    "tmix_kk_a_gate": torch.float16,
+    "tmix_lnx": torch.float16,
+    "tmix_vres": torch.float16,
+    "tmix_mix6": torch.float16,
+    "tmix_lowrank": torch.float16,
 }
 
 

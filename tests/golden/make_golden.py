@@ -143,6 +143,70 @@ def main() -> None:
           dr=vals[0].grad.float(), dw=vals[1].grad.float(), dk=vals[2].grad.float(),
           dv=vals[3].grad.float(), da=vals[4].grad.float(), db=vals[5].grad.float())
 
+    # ---- TMix pieces: the expectations are the formulas the reference's tests evaluate inline
+    # (tests/tmix/kk_a_gate/test.py:62-67, tests/tmix/lnx_rkvres_xg/test.py:50-63, tests/tmix/vres_gate/test.py:15-26,
+    #  tests/tmix/mix6/test.py:263-278, tests/tmix/linear/test.py:395-424), evaluated here in fp32 on fp16 inputs
+    torch.manual_seed(17)
+    rows, heads, hs = 3, 2, 64
+    C = heads * hs
+    h16 = lambda *shape: torch.randn(*shape).to(torch.float16)  # noqa: E731
+    k, k_k, a0, a12, k_a = h16(rows, C), h16(C), h16(C), h16(rows, C), h16(C)
+    scaled = k.float().reshape(rows, heads, hs) * k_k.float().reshape(1, heads, hs)
+    norm = scaled / scaled.square().sum(-1, keepdim=True).sqrt().clamp_min(1.0e-12)
+    gate = torch.sigmoid(a0.float().reshape(1, heads, hs) + a12.float().reshape(rows, heads, hs))
+    kaf = k_a.float().reshape(1, heads, hs)
+    new_k = k.float().reshape(rows, heads, hs) * (gate * kaf + 1.0 - kaf)
+    _save("tmix_kk_a_gate", k=k, k_k=k_k, a0=a0, a12=a12, k_a=k_a, new_k=new_k.reshape(rows, C),
+          neg_kk=(-norm).reshape(rows, C), kka=(norm * gate).reshape(rows, C))
+
+    torch.manual_seed(21)
+    x, r, k, v, g = (h16(rows, C) for _ in range(5))
+    r_k, weight, bias = h16(C), h16(C), h16(C)
+    xf = x.float().reshape(rows, heads, hs)
+    mean = xf.mean(-1, keepdim=True)
+    rstd = (xf.var(-1, unbiased=False, keepdim=True) + 64.0e-5).rsqrt()
+    resid = (r.float().reshape(rows, heads, hs) * k.float().reshape(rows, heads, hs)
+             * r_k.float().reshape(1, heads, hs)).sum(-1, keepdim=True)
+    out = ((xf - mean) * rstd * weight.float().reshape(1, heads, hs) + bias.float().reshape(1, heads, hs)
+           + resid * v.float().reshape(rows, heads, hs)) * g.float().reshape(rows, heads, hs)
+    _save("tmix_lnx", x=x, r=r, k=k, v=v, g=g, r_k=r_k, weight=weight, bias=bias, out=out.reshape(rows, C))
+
+    torch.manual_seed(5)
+    v, v_first, v12, v0 = h16(4, C), h16(4, C), h16(4, C), h16(C)
+    out = v.float() + (v_first.float() - v.float()) * torch.sigmoid(v0.float() + v12.float())
+    _save("tmix_vres", v=v, v_first=v_first, v12=v12, v0=v0, out=out)
+
+    c = 8
+    lengths = (2, 3)
+    total = sum(lengths)
+    x = torch.arange(total * c, dtype=torch.float16).reshape(total, c)
+    params = [torch.full((c,), val, dtype=torch.float16) for val in (0.1, 0.2, 0.3, 0.4, 0.5, 0.6)]
+    torch.manual_seed(3)
+    initial = torch.randn(4, c).to(torch.float16)
+    slots = [1, 3]
+    expected = [[] for _ in range(6)]
+    shift = initial.clone()
+    start = 0
+    for s, length in enumerate(lengths):
+        previous = initial[slots[s]]
+        for t in range(start, start + length):
+            cur = x[t]
+            for i, p in enumerate(params):
+                expected[i].append((cur.float() + (previous.float() - cur.float()) * p.float()))
+            previous = cur
+        shift[slots[s]] = previous
+        start += length
+    _save("tmix_mix6", x=x, mix=torch.stack(params), shift_pool=initial,
+          cu_seqlens=torch.tensor([0, 2, 5], dtype=torch.int32), state_indices=torch.tensor(slots, dtype=torch.int32),
+          out=torch.stack([torch.stack(rows_) for rows_ in expected]), shift_after=shift)
+
+    torch.manual_seed(9)
+    M, Cc, R = 5, 256, 96
+    xw, w1, w2 = h16(M, Cc), (torch.randn(R, Cc) * 0.05).to(torch.float16), (torch.randn(Cc, R) * 0.05).to(torch.float16)
+    rank = (xw.float() @ w1.float().T).to(torch.float16)
+    outw = torch.tanh(rank.float()) @ w2.float().T
+    _save("tmix_lowrank", x=xw, w1=w1, w2=w2, rank=rank, out_tanh=outw)
+
 
 if __name__ == "__main__":
     main()

@@ -99,3 +99,27 @@ def test_retention_matches_exp2_form(oracle):
     ref = np.exp2(-0.8750387749145276 / (1.0 + np.exp2(-1.4426950408889634 * x.astype(np.float64))))
     assert np.max(np.abs(w - ref)) < 2e-7
     assert w.min() > 0.545 and w.max() < 1.0
+
+
+def test_tmix_pieces_match_reference_formulas(oracle):
+    g = load_golden("tmix_kk_a_gate")
+    outs = oracle.kk_a_gate(g["k"], g["k_k"], g["a0"], g["a12"], g["k_a"])
+    for ours, name in zip(outs, ("new_k", "neg_kk", "kka")):
+        assert max_abs(ours, g[name]) < 1e-5, name
+    g = load_golden("tmix_lnx")
+    out = oracle.lnx_rkvres_xg(g["x"], g["r"], g["k"], g["v"], g["r_k"], g["weight"], g["bias"], g["g"])
+    assert rel_rmse(out, g["out"]) < 1e-6
+    g = load_golden("tmix_vres")
+    assert max_abs(oracle.vres_gate(g["v"], g["v_first"], g["v0"], g["v12"]), g["out"]) < 1e-6
+    g = load_golden("tmix_mix6")
+    out, shift = oracle.mix6(g["x"], g["shift_pool"], list(g["mix"]), g["cu_seqlens"], g["state_indices"])
+    assert max_abs(out, g["out"]) < 1e-5
+    assert np.array_equal(shift, g["shift_after"].float().numpy())
+    g = load_golden("tmix_lowrank")
+    rank = oracle.linear_nt(g["x"], g["w1"])
+    assert max_abs(torch.from_numpy(rank).half().float(), g["rank"].float()) < 2e-3
+    assert rel_rmse(oracle.linear_nt(g["rank"], g["w2"], act="tanh"), g["out_tanh"]) < 1e-6
+    # closed-form answer pinned by the reference (tests/tmix/kk_a_gate/test.py:45-47): all-ones inputs, C = 4096
+    ones = np.ones((2, 4096), np.float32)
+    new_k, neg_kk, kka = oracle.kk_a_gate(ones, ones[0], 0 * ones[0], 0 * ones, ones[0])
+    assert np.allclose(new_k, 0.5) and np.allclose(neg_kk, -0.125) and np.allclose(kka, 0.0625)

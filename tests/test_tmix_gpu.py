@@ -1,0 +1,156 @@
+"""Parity of the TMix kernels (token shift, per-head ops, projections) with the CPU oracle and the golden vectors.
+
+Tolerances: elementwise / per-head outputs must be the oracle's value up to one rounding of the 16-bit output
+(relative RMSE <= 1.5e-3 fp16, 4e-3 bf16); projections the same (fp32 accumulation over K <= 2048); the
+reference's own allclose(atol=rtol=0.04) bounds (tests/tmix/*/test.py) are far looser and implied.
+"""
+import numpy as np
+import pytest
+import torch
+
+from _util import load_golden, max_abs, rel_rmse
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float16: 1.5e-3, torch.bfloat16: 4e-3}
+
+
+def _c(*ts):
+    return [t.cuda() for t in ts]
+
+
+def test_golden_mix6_ticket_and_shift_update():
+    import flashrwkv_b200 as F
+
+    g = load_golden("tmix_mix6")
+    x, pool = g["x"].cuda(), g["shift_pool"].cuda().clone()
+    cu, idx = g["cu_seqlens"].cuda(), g["state_indices"].cuda()
+    ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=5, state_pool_size=4)
+    outs = F.infer_tmix_mix6_forward_varlen(x, *g["mix"].cuda().unbind(0), shift_state_pool=pool, cu_seqlens=cu,
+                                            state_indices=idx, validated_metadata=ticket)
+    torch.cuda.synchronize()
+    for j in range(6):
+        assert torch.allclose(outs[j].float().cpu(), g["out"][j], atol=0.01, rtol=0.01)
+    assert torch.equal(pool.cpu(), g["shift_after"])
+    cu[1] += 1
+    before = pool.clone()
+    with pytest.raises(RuntimeError, match="version"):
+        F.infer_tmix_mix6_forward_varlen(x, *g["mix"].cuda().unbind(0), shift_state_pool=pool, cu_seqlens=cu,
+                                         state_indices=idx, validated_metadata=ticket)
+    assert torch.equal(pool, before)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("lengths", [(1,) * 7, (3, 1, 64, 2)])
+def test_mix6_vs_oracle(oracle, dtype, lengths):
+    import flashrwkv_b200 as F
+
+    C, N = 2048, sum(lengths)
+    gen = torch.Generator().manual_seed(N)
+    x = torch.randn(N, C, generator=gen).to(dtype)
+    mixes = [torch.rand(C, generator=gen).to(dtype) for _ in range(6)]
+    pool = torch.randn(len(lengths) + 3, C, generator=gen).to(dtype)
+    cu = torch.tensor([0] + list(np.cumsum(lengths)), dtype=torch.int32)
+    idx = torch.randperm(len(lengths) + 3, generator=gen)[: len(lengths)].to(torch.int32)
+    want, want_pool = oracle.mix6(x, pool, mixes, cu, idx)
+    dpool = pool.cuda()
+    outs = F.infer_tmix_mix6_forward_varlen(x.cuda(), *_c(*mixes), shift_state_pool=dpool, cu_seqlens=cu.cuda(),
+                                            state_indices=idx.cuda(),
+                                            max_seqlen=max(lengths))
+    torch.cuda.synchronize()
+    for j in range(6):
+        assert rel_rmse(outs[j].float().cpu(), want[j]) <= TOL[dtype]
+    assert torch.equal(dpool.float().cpu(), torch.from_numpy(want_pool))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_per_head_ops_vs_oracle(oracle, dtype):
+    import flashrwkv_b200 as F
+
+    N, C = 37, 2048
+    gen = torch.Generator().manual_seed(4)
+    rn = lambda *s: torch.randn(*s, generator=gen).to(dtype)  # noqa: E731
+    k, a12, k_k, a0, k_a = rn(N, C), rn(N, C), rn(C), rn(C), rn(C)
+    got = F.infer_tmix_kk_a_gate_forward_varlen(*_c(k, k_k, a0, a12, k_a))
+    for o, w in zip(got, oracle.kk_a_gate(k, k_k, a0, a12, k_a)):
+        assert rel_rmse(o.float().cpu(), w) <= TOL[dtype]
+    x, r, kk, v, g, r_k, wt, bs = rn(N, C), rn(N, C), rn(N, C), rn(N, C), rn(N, C), rn(C), rn(C), rn(C)
+    got = F.infer_tmix_lnx_rkvres_xg_forward_varlen(*_c(x, r, kk, v, r_k, wt, bs, g))
+    assert rel_rmse(got.float().cpu(), oracle.lnx_rkvres_xg(x, r, kk, v, r_k, wt, bs, g)) <= TOL[dtype]
+    v, vf, v12, v0 = rn(N, C), rn(N, C), rn(N, C), rn(C)
+    got = F.infer_tmix_vres_gate_forward_varlen(*_c(v, vf, v0, v12))
+    assert rel_rmse(got.float().cpu(), oracle.vres_gate(v, vf, v0, v12)) <= TOL[dtype]
+
+
+def test_golden_per_head_and_known_answers():
+    import flashrwkv_b200 as F
+
+    g = load_golden("tmix_kk_a_gate")
+    outs = F.infer_tmix_kk_a_gate_forward_varlen(*_c(g["k"], g["k_k"], g["a0"], g["a12"], g["k_a"]))
+    for o, name in zip(outs, ("new_k", "neg_kk", "kka")):
+        assert torch.allclose(o.float().cpu(), g[name], atol=0.04, rtol=0.04)
+        assert rel_rmse(o.float().cpu(), g[name]) <= TOL[torch.float16]
+    g = load_golden("tmix_lnx")
+    out = F.infer_tmix_lnx_rkvres_xg_forward_varlen(*_c(g["x"], g["r"], g["k"], g["v"], g["r_k"], g["weight"],
+                                                       g["bias"], g["g"]))
+    assert rel_rmse(out.float().cpu(), g["out"]) <= TOL[torch.float16]
+    g = load_golden("tmix_vres")
+    out = F.infer_tmix_vres_gate_forward_varlen(*_c(g["v"], g["v_first"], g["v0"], g["v12"]))
+    assert rel_rmse(out.float().cpu(), g["out"]) <= TOL[torch.float16]
+    ones = torch.ones(65536, 4096, dtype=torch.float16, device="cuda")
+    vec = torch.ones(4096, dtype=torch.float16, device="cuda")
+    new_k, neg_kk, kka = F.infer_tmix_kk_a_gate_forward_varlen(ones, vec, 0 * vec, 0 * ones, vec)
+    for o, val in ((new_k, 0.5), (neg_kk, -0.125), (kka, 0.0625)):
+        assert torch.allclose(o[[0, -1]].float(), torch.full_like(o[[0, -1]].float(), val))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M", [1, 4, 5, 7, 8, 9, 130, 512])
+def test_lowrank_group_and_dense_linear_vs_oracle(oracle, dtype, M):
+    import flashrwkv_b200 as F
+
+    C, ranks = 2048, {"w": 96, "a": 96, "g": 256, "v": 64}
+    gen = torch.Generator().manual_seed(100 + M)
+    rn = lambda *s, scale=1.0: (torch.randn(*s, generator=gen) * scale).to(dtype)  # noqa: E731
+    xs = {n: rn(M, C) for n in "wagv"}
+    w1 = {n: rn(ranks[n], C, scale=0.02) for n in "wagv"}
+    w2 = {n: rn(C, ranks[n], scale=0.02) for n in "wagv"}
+    tol = TOL[dtype]
+    rank_feats = F.infer_tmix_lowrank_wagv_in_forward_varlen(*_c(*(xs[n] for n in "wagv")), *_c(*(w1[n] for n in "wagv")))
+    feats = {}
+    for n, got in zip("wagv", rank_feats):
+        assert got.shape == (M, ranks[n])
+        assert rel_rmse(got.float().cpu(), oracle.linear_nt(xs[n], w1[n])) <= tol
+        feats[n] = got.cpu()
+    three = F.infer_tmix_lowrank_in_forward_varlen(*_c(xs["w"], xs["a"], xs["g"]), *_c(w1["w"], w1["a"], w1["g"]))
+    for n, got in zip("wag", three):
+        assert torch.equal(got.cpu(), feats[n])
+    v, v_first, v0 = rn(M, C), rn(M, C), rn(C)
+    outs = F.infer_tmix_lowrank_vres_forward_varlen(*_c(*(feats[n] for n in "wagv")), *_c(*(w2[n] for n in "wagv")),
+                                                    *_c(v, v_first, v0))
+    acts = {"w": "tanh", "a": "none", "g": "sigmoid"}
+    for n, got in zip("wag", outs[:3]):
+        assert rel_rmse(got.float().cpu(), oracle.linear_nt(feats[n], w2[n], act=acts[n])) <= 2 * tol
+    v12 = oracle.linear_nt(feats["v"], w2["v"])
+    assert rel_rmse(outs[3].float().cpu(), oracle.vres_gate(v, v_first, v0, v12)) <= 2 * tol
+    plain = F.infer_tmix_lowrank_out_forward_varlen(*_c(*(feats[n] for n in "wag")), *_c(*(w2[n] for n in "wag")))
+    for got, ref in zip(plain, outs[:3]):
+        assert torch.equal(got, ref)
+    W = rn(C, C, scale=0.02)
+    y = F.infer_tmix_linear_forward_varlen(xs["w"].cuda(), W.cuda())
+    assert rel_rmse(y.float().cpu(), oracle.linear_nt(xs["w"], W)) <= tol
+    with pytest.raises(ValueError, match="R <= 512"):
+        F.infer_tmix_linear_rank_in_forward_varlen(xs["w"].cuda(), weight_t=rn(520, C).cuda())
+    with pytest.raises(ValueError, match="runtime"):
+        F.infer_tmix_linear_rank_in_forward_varlen(xs["w"].cuda(), weight=rn(C, 96).cuda())
+
+
+def test_golden_lowrank_pair():
+    import flashrwkv_b200 as F
+
+    g = load_golden("tmix_lowrank")
+    rank = F.infer_tmix_linear_rank_in_forward_varlen(g["x"].cuda(), weight_t=g["w1"].cuda())
+    assert torch.allclose(rank.float().cpu(), g["rank"].float(), atol=0.04, rtol=0.04)
+    assert rel_rmse(rank.float().cpu(), g["rank"].float()) <= TOL[torch.float16]
+    out = F.infer_tmix_linear_rank_out_tanh_forward_varlen(g["rank"].cuda(), weight_t=g["w2"].cuda())
+    assert rel_rmse(out.float().cpu(), g["out_tanh"]) <= TOL[torch.float16]
