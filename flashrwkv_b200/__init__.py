@@ -10,6 +10,8 @@ from .tmix.wkv7 import (
     infer_chunk_bf16_forward_varlen,
     infer_recurrent_fp32io16_forward_varlen,
     prepare_recurrent_metadata,
+    pretrain_recurrent_bf16,
+    statetune_recurrent_fp32io16,
 )
 
 from .tmix.kk_a_gate import infer_tmix_kk_a_gate_forward_varlen
@@ -28,6 +30,8 @@ __all__ = [
     "infer_chunk_bf16_forward_varlen",
     "infer_recurrent_fp32io16_forward_varlen",
     "prepare_recurrent_metadata",
+    "pretrain_recurrent_bf16",
+    "statetune_recurrent_fp32io16",
     "rl_infctx_chunk_fp32io16",
     "rl_infctx_chunk_fp32io16_factor_recompute",
 ]

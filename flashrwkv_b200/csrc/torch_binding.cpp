@@ -543,6 +543,69 @@ std::vector<torch::Tensor> tmix_linear_grouped(std::vector<torch::Tensor> xs, st
   return outs;
 }
 
+// ---- training side -------------------------------------------------------------------------------------
+// state_dot_a [N,H,D] and the 16-token checkpoints [Cn,3,H,D,D] for the backward pass, from the chunk boundaries
+std::tuple<torch::Tensor, torch::Tensor> wkv7_chunk_replay(torch::Tensor cs, torch::Tensor ce, torch::Tensor boundary,
+                                                          torch::Tensor r, torch::Tensor w, torch::Tensor k,
+                                                          torch::Tensor v, torch::Tensor a, torch::Tensor b,
+                                                          std::optional<torch::Tensor> decay_bias) {
+  check_cuda_contiguous(boundary, "boundary");
+  TORCH_CHECK(boundary.scalar_type() == torch::kFloat32 && boundary.dim() == 4 && boundary.size(0) == cs.numel() &&
+                  boundary.size(1) == r.size(1) && boundary.size(2) == 64 && boundary.size(3) == 64,
+              "boundary must be float32 [Cn,H,64,64]");
+  TORCH_CHECK(r.dim() == 3 && r.size(2) == 64, "token tensors must have shape [N,H,64]");
+  const c10::cuda::CUDAGuard guard(r.device());
+  auto sda = torch::empty(r.sizes(), r.options().dtype(torch::kFloat32));
+  auto ckpt = torch::empty({cs.numel(), 3, r.size(1), 64, 64}, r.options().dtype(torch::kFloat32));
+  check_rc(frwkv_wkv7_chunk_replay(cs.data_ptr<int>(), ce.data_ptr<int>(), boundary.data_ptr<float>(), r.data_ptr(),
+                                   w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
+                                   decay_bias.has_value() ? decay_bias->data_ptr() : nullptr, sda.data_ptr<float>(),
+                                   ckpt.data_ptr<float>(), static_cast<int>(cs.numel()), static_cast<int>(r.size(1)), 64,
+                                   io_dtype_of(r), current_stream(r)));
+  return {sda, ckpt};
+}
+
+std::vector<torch::Tensor> wkv7_backward(torch::Tensor sco, torch::Tensor cs, torch::Tensor ce,
+                                         torch::Tensor final_state, torch::Tensor boundary, torch::Tensor checkpoints,
+                                         torch::Tensor state_dot_a, torch::Tensor r, torch::Tensor w, torch::Tensor k,
+                                         torch::Tensor v, torch::Tensor a, torch::Tensor b,
+                                         std::optional<torch::Tensor> grad_output,
+                                         std::optional<torch::Tensor> grad_final_state, double scale) {
+  check_chunk_tables(sco, cs, ce, r);
+  for (const torch::Tensor* t : {&final_state, &boundary, &checkpoints, &state_dot_a}) {
+    check_cuda_contiguous(*t, "saved tensor");
+    TORCH_CHECK(t->scalar_type() == torch::kFloat32 && t->device() == r.device(), "saved tensors must be float32 on r's device");
+  }
+  TORCH_CHECK(r.dim() == 3 && r.size(2) == 64, "token tensors must have shape [N,H,64]");
+  const int64_t B = sco.numel() - 1, H = r.size(1);
+  TORCH_CHECK(final_state.dim() == 4 && final_state.size(0) == B && final_state.size(1) == H,
+              "final_state must have shape [B,H,64,64]");
+  TORCH_CHECK(state_dot_a.sizes() == r.sizes(), "state_dot_a must be shaped like r");
+  if (grad_output.has_value()) {
+    check_cuda_contiguous(*grad_output, "grad_output");
+    TORCH_CHECK(grad_output->sizes() == r.sizes() && grad_output->scalar_type() == r.scalar_type(),
+                "grad_output must match r");
+  }
+  if (grad_final_state.has_value()) {
+    check_cuda_contiguous(*grad_final_state, "grad_final_state");
+    TORCH_CHECK(grad_final_state->sizes() == final_state.sizes() && grad_final_state->scalar_type() == torch::kFloat32,
+                "grad_final_state must be float32 [B,H,64,64]");
+  }
+  const c10::cuda::CUDAGuard guard(r.device());
+  std::vector<torch::Tensor> g;
+  for (int i = 0; i < 6; ++i) g.push_back(torch::empty_like(r));
+  g.push_back(torch::empty_like(final_state));
+  check_rc(frwkv_wkv7_backward(
+      sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(), final_state.data_ptr<float>(),
+      boundary.data_ptr<float>(), checkpoints.data_ptr<float>(), state_dot_a.data_ptr<float>(), r.data_ptr(),
+      w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
+      grad_output.has_value() ? grad_output->data_ptr() : nullptr,
+      grad_final_state.has_value() ? grad_final_state->data_ptr<float>() : nullptr, g[0].data_ptr(), g[1].data_ptr(),
+      g[2].data_ptr(), g[3].data_ptr(), g[4].data_ptr(), g[5].data_ptr(), g[6].data_ptr<float>(), static_cast<int>(B),
+      static_cast<int>(H), 64, io_dtype_of(r), static_cast<float>(scale), current_stream(r)));
+  return g;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -586,6 +649,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("head_size") = 64, py::arg("batch_size") = 1, py::arg("max_seqlen") = 1);
   m.def("tmix_vres_gate_forward_varlen", &tmix_vres_gate_forward_varlen, py::arg("v"), py::arg("v_first"),
         py::arg("v0"), py::arg("v12"));
+  m.def("wkv7_chunk_replay", &wkv7_chunk_replay, py::arg("chunk_token_starts"), py::arg("chunk_token_ends"),
+        py::arg("boundary"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),
+        py::arg("b"), py::arg("decay_bias") = py::none());
+  m.def("wkv7_backward", &wkv7_backward, py::arg("sequence_chunk_offsets"), py::arg("chunk_token_starts"),
+        py::arg("chunk_token_ends"), py::arg("final_state"), py::arg("boundary"), py::arg("checkpoints"),
+        py::arg("state_dot_a"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),
+        py::arg("b"), py::arg("grad_output") = py::none(), py::arg("grad_final_state") = py::none(),
+        py::arg("scale") = 1.0);
   m.def("tmix_linear_grouped", &tmix_linear_grouped, py::arg("xs"), py::arg("weights"), py::arg("acts"),
         py::arg("vres") = py::none());
 }

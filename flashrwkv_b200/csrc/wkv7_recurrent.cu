@@ -35,16 +35,21 @@ __device__ __forceinline__ void load16(const void* p, uint32_t (&w)[8]) {
   w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
 }
 
-template <typename io_t>
+// kReplay = true turns the kernel into the training-side "replay": units are (chunk, head, half), the state is
+// read from the chunk-start boundary tensor and never written back, and instead of being discarded the per-token
+// S^T a vectors (state_dot_a) and the states after every 16th token of a chunk (checkpoints for the backward
+// pass) are stored.  cu_seqlens / state_indices then hold chunk_starts / chunk_ends.
+template <typename io_t, bool kReplay>
 __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
     const int* __restrict__ cu_seqlens, const int* __restrict__ state_indices,
     const int* __restrict__ metadata_status, float* __restrict__ state_pool,
     const io_t* __restrict__ r_ptr, const io_t* __restrict__ w_ptr, const io_t* __restrict__ k_ptr,
     const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr, const io_t* __restrict__ b_ptr,
     const io_t* __restrict__ bias_ptr, io_t* __restrict__ y_ptr, float* __restrict__ y32_ptr,
-    long long num_units, int num_heads, long long output_elements, float scale) {
+    float* __restrict__ sa_ptr, float* __restrict__ ckpt_ptr, long long num_units, int num_heads,
+    long long output_elements, float scale) {
   using IO = Io16<io_t>;
-  if (metadata_status != nullptr && metadata_status[0] != 0) {
+  if (!kReplay && metadata_status != nullptr && metadata_status[0] != 0) {
     // fail closed: NaN output, state untouched
     const io_t nan16 = IO::store(quiet_nan());
     for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < output_elements;
@@ -66,8 +71,8 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
   const int col0 = vhalf * 32 + vq * 4;
 
   const int t_begin = cu_seqlens[seq];
-  const int t_end = cu_seqlens[seq + 1];
-  const int slot = state_indices[seq];
+  const int t_end = kReplay ? state_indices[seq] : cu_seqlens[seq + 1];
+  const int slot = kReplay ? seq : state_indices[seq];
 
   float* sbase = state_pool + ((long long)slot * num_heads + head) * (kD * kD) + row0 * kD + col0;
   float4 s[16];
@@ -164,7 +169,16 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
         s[2 * p + 1] = q;
       }
     }
-    if (kg == 0) {
+    if (kReplay) {
+      if (kg == 0) *reinterpret_cast<float4*>(sa_ptr + tb + col0) = make_float4(sa0, sa1, sa2, sa3);
+      const int done = t - t_begin + 1;
+      if (ckpt_ptr != nullptr && (done & 15) == 0 && t + 1 < t_end) {
+        float* cbase = ckpt_ptr + (((long long)seq * 3 + (done >> 4) - 1) * num_heads + head) * (kD * kD) +
+                       row0 * kD + col0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) *reinterpret_cast<float4*>(cbase + i * kD) = s[i];
+      }
+    } else if (kg == 0) {
       const float o0 = scale * fmaf(kr, v01.x, fmaf(br, sa0, y0));
       const float o1 = scale * fmaf(kr, v01.y, fmaf(br, sa1, y1));
       const float o2 = scale * fmaf(kr, v23.x, fmaf(br, sa2, y2));
@@ -179,8 +193,10 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
     }
   }
 
+  if (!kReplay) {
 #pragma unroll
-  for (int i = 0; i < 16; ++i) *reinterpret_cast<float4*>(sbase + i * kD) = s[i];
+    for (int i = 0; i < 16; ++i) *reinterpret_cast<float4*>(sbase + i * kD) = s[i];
+  }
 }
 
 template <typename io_t>
@@ -190,12 +206,26 @@ int launch(const int* cu, const int* idx, const int* status, float* state, const
            float scale, cudaStream_t stream) {
   const long long units = (long long)num_sequences * num_heads * 2;
   const long long blocks = (units + kWarpsPerBlock - 1) / kWarpsPerBlock;
-  wkv7_recurrent_d64_kernel<io_t><<<(unsigned)blocks, kThreads, 0, stream>>>(
+  wkv7_recurrent_d64_kernel<io_t, false><<<(unsigned)blocks, kThreads, 0, stream>>>(
       cu, idx, status, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w),
       static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),
-      static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, units,
-      num_heads, (long long)total_tokens * num_heads * kD, scale);
+      static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, nullptr, nullptr,
+      units, num_heads, (long long)total_tokens * num_heads * kD, scale);
   return check_launch("wkv7_recurrent_d64_kernel");
+}
+
+template <typename io_t>
+int launch_replay(const int* chunk_starts, const int* chunk_ends, const float* boundary, const void* r, const void* w,
+                  const void* k, const void* v, const void* a, const void* b, const void* bias, float* sa, float* ckpt,
+                  int num_chunks, int num_heads, cudaStream_t stream) {
+  const long long units = (long long)num_chunks * num_heads * 2;
+  const long long blocks = (units + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  wkv7_recurrent_d64_kernel<io_t, true><<<(unsigned)blocks, kThreads, 0, stream>>>(
+      chunk_starts, chunk_ends, nullptr, const_cast<float*>(boundary), static_cast<const io_t*>(r),
+      static_cast<const io_t*>(w), static_cast<const io_t*>(k), static_cast<const io_t*>(v),
+      static_cast<const io_t*>(a), static_cast<const io_t*>(b), static_cast<const io_t*>(bias), nullptr, nullptr, sa,
+      ckpt, units, num_heads, 0, 1.0f);
+  return check_launch("wkv7_recurrent_d64_kernel<replay>");
 }
 
 }  // namespace
@@ -231,4 +261,26 @@ extern "C" int frwkv_wkv7_recurrent_fp32io16_forward_varlen(
                           b, decay_bias, y, y_fp32, total_tokens, num_sequences, num_heads, scale, s);
   }
   return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_recurrent: token tensors must be float16 or bfloat16");
+}
+
+extern "C" int frwkv_wkv7_chunk_replay(const int32_t* chunk_starts, const int32_t* chunk_ends, const float* boundary,
+                                       const void* r, const void* decay_logits, const void* k, const void* v,
+                                       const void* a, const void* b, const void* decay_bias, float* state_dot_a,
+                                       float* checkpoints, int num_chunks, int num_heads, int head_size, int io_dtype,
+                                       frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(chunk_starts && chunk_ends && boundary && r && decay_logits && k && v && a && b && state_dot_a,
+                "wkv7_chunk_replay: null pointer argument");
+  FRWKV_REQUIRE(num_chunks > 0 && num_heads > 0, "wkv7_chunk_replay: sizes must be positive");
+  if (head_size != 64) return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_chunk_replay: head size %d is not built (only 64)", head_size);
+  FRWKV_REQUIRE(((long long)num_chunks * num_heads * 2 + 3) / 4 <= 0x7fffffffLL, "wkv7_chunk_replay: too many chunks");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (io_dtype == FRWKV_DTYPE_BF16)
+    return launch_replay<__nv_bfloat16>(chunk_starts, chunk_ends, boundary, r, decay_logits, k, v, a, b, decay_bias,
+                                        state_dot_a, checkpoints, num_chunks, num_heads, s);
+  if (io_dtype == FRWKV_DTYPE_FP16)
+    return launch_replay<__half>(chunk_starts, chunk_ends, boundary, r, decay_logits, k, v, a, b, decay_bias,
+                                 state_dot_a, checkpoints, num_chunks, num_heads, s);
+  return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_chunk_replay: token tensors must be float16 or bfloat16");
 }

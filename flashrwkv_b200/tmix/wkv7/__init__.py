@@ -86,3 +86,7 @@ __all__ = ["infer_recurrent_fp32io16_forward_varlen", "prepare_recurrent_metadat
 from .chunk import infer_chunk_bf16_forward_varlen, make_chunk_metadata, wkv7_chunk_forward  # noqa: E402
 
 __all__ += ["infer_chunk_bf16_forward_varlen", "wkv7_chunk_forward", "make_chunk_metadata"]
+
+from .training import pretrain_recurrent_bf16, statetune_recurrent_fp32io16  # noqa: E402
+
+__all__ += ["pretrain_recurrent_bf16", "statetune_recurrent_fp32io16"]

@@ -1,0 +1,176 @@
+"""Training-side WKV7 operators with custom autograd: StateTune (non-zero fp32 initial state, caller-defined
+chunks, gradient of the initial state) and dense BF16 pretraining (zero initial state).
+
+Mirrors of the reference's `flashrwkv2/tmix/wkv7/statetune.py:79-236` and `pretrain.py:50-129`.  Forward = the
+tensor-core chunk kernels (output, final state, chunk-start boundaries) plus a replay pass that stores
+`state_dot_a` and 16-token state checkpoints; backward = one reverse pass that re-anchors the state from those.
+Head size 64.  Chunks handed to StateTune may hold at most 64 tokens each.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..._ext import extension
+from .chunk import MAX_CHUNK
+
+CHUNK_LEN = 16  # the reference's canonical pretraining chunk length: T must be a multiple of it
+
+
+def _forward_all(state, sco, cs, ce, r, w, k, v, a, b, scale):
+    C = extension()
+    output = torch.empty_like(v)
+    boundary = torch.empty((cs.numel(), r.shape[1], 64, 64), device=r.device, dtype=torch.float32)
+    C.wkv7_chunk_forward(sco, cs, ce, state, r, w, k, v, a, b, output, float(scale), None, None, boundary, None, None)
+    state_dot_a, checkpoints = C.wkv7_chunk_replay(cs, ce, boundary, r, w, k, v, a, b, None)
+    return output, boundary, state_dot_a, checkpoints
+
+
+class _StateTune(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, initial_state, sco, cs, ce, r, w, k, v, a, b, scale):
+        state = initial_state.detach().clone()  # the caller's initial state is never mutated
+        output, boundary, state_dot_a, checkpoints = _forward_all(state, sco, cs, ce, r.detach(), w.detach(),
+                                                                  k.detach(), v.detach(), a.detach(), b.detach(), scale)
+        ctx.save_for_backward(sco, cs, ce, state, boundary, checkpoints, state_dot_a, r, w, k, v, a, b)
+        ctx.scale = scale
+        ctx.mark_non_differentiable(boundary, state_dot_a)
+        return output, state, boundary, state_dot_a
+
+    @staticmethod
+    def backward(ctx, grad_output, grad_final_state, _grad_boundary, _grad_sda):
+        sco, cs, ce, final_state, boundary, checkpoints, state_dot_a, r, w, k, v, a, b = ctx.saved_tensors
+        go = None if grad_output is None else grad_output.contiguous()
+        gf = None if grad_final_state is None else grad_final_state.contiguous().float()
+        dr, dw, dk, dv, da, db, dS0 = extension().wkv7_backward(
+            sco, cs, ce, final_state, boundary, checkpoints, state_dot_a, r.detach(), w.detach(), k.detach(),
+            v.detach(), a.detach(), b.detach(), go, gf, ctx.scale)
+        return dS0, None, None, None, dr, dw, dk, dv, da, db, None
+
+
+def _check_cuda_contiguous(tensor, name):
+    if not isinstance(tensor, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not tensor.is_cuda or not tensor.is_contiguous():
+        raise ValueError(f"{name} must be contiguous CUDA")
+
+
+def statetune_recurrent_fp32io16(initial_state, sequence_chunk_offsets, chunk_token_starts, chunk_token_ends, r,
+                                 decay_logits, k, v, a, b, *, scale: float = 1.0):
+    """StateTune forward with gradients for r, decay_logits, k, v, a, b and the initial state.
+
+    Returns `(output [N,H,D], final_state [B,H,D,D], boundary [Cn,H,D,D], state_dot_a [N,H,D])`.
+    """
+    _check_cuda_contiguous(initial_state, "state")
+    if initial_state.dtype != torch.float32:
+        raise TypeError("state must be float32")
+    if initial_state.ndim != 4 or initial_state.shape[0] <= 0 or initial_state.shape[1] <= 0:
+        raise ValueError("state must have shape [B,H,D,D]")
+    if initial_state.shape[2] != initial_state.shape[3] or initial_state.shape[2] not in (64, 128, 256):
+        raise ValueError("state head size must be 64, 128, or 256")
+    if initial_state.shape[2] != 64:
+        raise ValueError("this build implements head size 64 only")
+    for name, tensor in (("r", r), ("decay_logits", decay_logits), ("k", k), ("v", v), ("a", a), ("b", b)):
+        _check_cuda_contiguous(tensor, name)
+        if tensor.device != initial_state.device:
+            raise ValueError(f"{name} must share the state device")
+        if tensor.dtype not in (torch.float16, torch.bfloat16):
+            raise TypeError(f"{name} must be float16 or bfloat16")
+        if tensor.shape != r.shape or tensor.dtype != r.dtype:
+            raise ValueError(f"{name} must match r shape and dtype")
+    if r.ndim != 3 or r.shape[0] <= 0 or r.shape[1:] != initial_state.shape[1:3]:
+        raise ValueError("token tensors must have shape [total_tokens,H,D]")
+    for name, tensor in (("sequence_chunk_offsets", sequence_chunk_offsets), ("chunk_token_starts", chunk_token_starts),
+                         ("chunk_token_ends", chunk_token_ends)):
+        _check_cuda_contiguous(tensor, name)
+        if tensor.dtype != torch.int32:
+            raise TypeError(f"{name} must be int32")
+        if tensor.device != initial_state.device:
+            raise ValueError(f"{name} must share the state device")
+    if sequence_chunk_offsets.ndim != 1:
+        raise ValueError("sequence_chunk_offsets must be one-dimensional")
+    if chunk_token_starts.ndim != 1 or chunk_token_ends.shape != chunk_token_starts.shape:
+        raise ValueError("chunk token metadata must have matching shape [C]")
+    if chunk_token_starts.numel() == 0:
+        raise ValueError("at least one training chunk is required")
+    if sequence_chunk_offsets.numel() != initial_state.shape[0] + 1:
+        raise ValueError("sequence_chunk_offsets must have shape [B+1]")
+    if not isinstance(scale, (int, float)) or not math.isfinite(float(scale)):
+        raise ValueError("scale must be finite")
+    if int((chunk_token_ends - chunk_token_starts).max().item()) > MAX_CHUNK:
+        raise ValueError(f"training chunks may hold at most {MAX_CHUNK} tokens")
+    return _StateTune.apply(initial_state, sequence_chunk_offsets, chunk_token_starts, chunk_token_ends, r,
+                            decay_logits, k, v, a, b, float(scale))
+
+
+_dense_tables = {}
+
+
+def _dense_chunk_tables(batch: int, tokens: int, device):
+    key = (batch, tokens, str(device))
+    if key not in _dense_tables:
+        per = (tokens + MAX_CHUNK - 1) // MAX_CHUNK
+        starts = [bi * tokens + c * MAX_CHUNK for bi in range(batch) for c in range(per)]
+        ends = [min(s + MAX_CHUNK, (s // tokens + 1) * tokens) for s in starts]
+        mk = lambda x: torch.tensor(x, device=device, dtype=torch.int32)  # noqa: E731
+        _dense_tables[key] = (mk([bi * per for bi in range(batch + 1)]), mk(starts), mk(ends))
+    return _dense_tables[key]
+
+
+class _PretrainRecurrent(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, r, w, k, v, a, b, head_size):
+        batch, tokens, channels = r.shape
+        heads = channels // head_size
+        tables = _dense_chunk_tables(batch, tokens, r.device)
+        packed = [t.detach().view(batch * tokens, heads, head_size) for t in (r, w, k, v, a, b)]
+        state = torch.zeros((batch, heads, head_size, head_size), device=r.device, dtype=torch.float32)
+        output, boundary, state_dot_a, checkpoints = _forward_all(state, *tables, *packed, 1.0)
+        ctx.save_for_backward(*tables, state, boundary, checkpoints, state_dot_a, *packed)
+        ctx.shape = r.shape
+        return output.view(r.shape)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        sco, cs, ce, final_state, boundary, checkpoints, state_dot_a, r, w, k, v, a, b = ctx.saved_tensors
+        go = grad_output.contiguous().view(r.shape)
+        grads = extension().wkv7_backward(sco, cs, ce, final_state, boundary, checkpoints, state_dot_a, r, w, k, v, a,
+                                          b, go, None, 1.0)
+        return (*(g.view(ctx.shape) for g in grads[:6]), None)
+
+
+def pretrain_recurrent_bf16(r, w, k, v, a, b, *, head_size: int = 64):
+    """Dense `[B,T,C]` BF16 WKV7 with zero initial state and gradients for all six inputs (`w` is the raw decay
+    input the retention transform is applied to)."""
+    if head_size not in {64, 128, 256}:
+        raise ValueError("head_size must be one of 64, 128, or 256")
+    if not isinstance(r, torch.Tensor):
+        raise TypeError("r must be a torch.Tensor")
+    if r.ndim != 3 or min(r.shape) <= 0:
+        raise ValueError("r must have shape [B,T,C] with nonzero dimensions")
+    if r.dtype != torch.bfloat16:
+        raise TypeError("r must be bfloat16")
+    if not r.is_cuda or not r.is_contiguous():
+        raise ValueError("r must be contiguous CUDA")
+    for name, tensor in zip(("w", "k", "v", "a", "b"), (w, k, v, a, b)):
+        if not isinstance(tensor, torch.Tensor):
+            raise TypeError(f"{name} must be a torch.Tensor")
+        if tensor.dtype != torch.bfloat16:
+            raise TypeError(f"{name} must be bfloat16")
+        if not tensor.is_cuda or not tensor.is_contiguous():
+            raise ValueError(f"{name} must be contiguous CUDA")
+        if tensor.shape != r.shape:
+            raise ValueError(f"{name} must match r shape")
+        if tensor.device != r.device:
+            raise ValueError(f"{name} must share the r device")
+    if r.shape[2] % head_size != 0:
+        raise ValueError("C must be divisible by head_size")
+    if r.shape[1] % CHUNK_LEN != 0:
+        raise ValueError("T must be divisible by the canonical chunk length 16")
+    if head_size != 64:
+        raise ValueError("this build implements head size 64 only")
+    return _PretrainRecurrent.apply(r, w, k, v, a, b, head_size)
+
+
+__all__ = ["statetune_recurrent_fp32io16", "pretrain_recurrent_bf16"]

@@ -111,6 +111,38 @@ int frwkv_wkv7_chunk_fp32io16_forward(
     frwkv_stream_t stream);
 
 /*
+ * Training-side replay: per chunk, run the recurrence from the chunk-start state boundary[c] and store
+ *   state_dot_a fp32 [N,H,64]      sa_t = S_{t-1}^T a_t for every token, and
+ *   checkpoints fp32 [Cn,3,H,64,64] the state after tokens 16, 32 and 48 of each chunk (where the chunk is longer);
+ *                                   may be NULL.
+ * Replaces the state_dot_a / checkpoint outputs of forward_kernel_preload
+ * (csrc/sm90/tmix/wkv7/pretrain_recurrent_bf16_forward.cu:32-97) and statetune_recurrent_fp32io16_forward_kernel
+ * (csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_forward.cu:32-130), and emit_outputs_kernel
+ * (csrc/sm90/rl_infctx/wkv7/rl_infctx_chunk_fp32io16_backward.cu:45-127).
+ */
+int frwkv_wkv7_chunk_replay(const int32_t* chunk_starts, const int32_t* chunk_ends, const float* boundary,
+                            const void* r, const void* decay_logits, const void* k, const void* v, const void* a,
+                            const void* b, const void* decay_bias, float* state_dot_a, float* checkpoints,
+                            int num_chunks, int num_heads, int head_size, int io_dtype, frwkv_stream_t stream);
+
+/*
+ * WKV7 backward over packed sequences with chunk tables (see frwkv_wkv7_chunk_fp32io16_forward for their meaning).
+ * Inputs: the forward's final_state [B,H,64,64], boundary [Cn,H,64,64], and the replay's checkpoints / state_dot_a;
+ * grad_output io16 [N,H,64] (NULL = zero) and grad_final_state fp32 [B,H,64,64] (NULL = zero).
+ * Outputs (each may be NULL): grad_r .. grad_b io16 [N,H,64] (grad_decay_logits is with respect to the raw decay
+ * logits), grad_initial_state fp32 [B,H,64,64].
+ * Replaces cuda_backward_v3 (csrc/sm90/tmix/wkv7/pretrain_recurrent_bf16_forward.cu:163-291) and
+ * statetune_recurrent_fp32io16_backward (csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_backward.cu:49-255).
+ */
+int frwkv_wkv7_backward(const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends,
+                        const float* final_state, const float* boundary, const float* checkpoints,
+                        const float* state_dot_a, const void* r, const void* decay_logits, const void* k, const void* v,
+                        const void* a, const void* b, const void* grad_output, const float* grad_final_state,
+                        void* grad_r, void* grad_decay_logits, void* grad_k, void* grad_v, void* grad_a, void* grad_b,
+                        float* grad_initial_state, int num_sequences, int num_heads, int head_size, int io_dtype,
+                        float scale, frwkv_stream_t stream);
+
+/*
  * TMix token shift: out[j] = x + (prev - x) * mix_j for the six mix vectors (r, w, k, v, a, g); prev is the previous
  * packed row, or shift_state_pool[state_indices[s]] at the first row of sequence s; afterwards that slot holds the
  * sequence's last row.  Replaces tmix_mix6_forward_varlen_cuda (csrc/sm120/tmix/mix6/infer_fp16_forward_varlen.cu:190-303).

@@ -1,0 +1,80 @@
+"""Training path: StateTune and dense pretraining forward outputs and gradients against the golden vectors
+(the reference's oracles + autograd) and, at larger sizes, the CPU oracle's backward.
+
+Tolerances are the reference's: StateTune outputs allclose(3e-4, 3e-4), gradients allclose(atol 3e-4, rtol 3e-3)
+(tests/tmix/wkv7/statetune/test.py:107,123); pretraining forward allclose(0.02, 0.02), gradients
+allclose(atol 0.03, rtol 0.05) (tests/tmix/wkv7/pretrain/test.py:104,126-128); plus relative RMSE <= 8e-3 on
+gradients (tests/fixtures/tolerances-v1.json:13-17).
+"""
+import pytest
+import torch
+
+from _util import load_golden, rel_rmse
+
+pytestmark = pytest.mark.gpu
+TOKENS = ("r", "w", "k", "v", "a", "b")
+
+
+def test_golden_statetune_outputs_and_seven_gradients():
+    import flashrwkv_b200 as F
+
+    g = load_golden("statetune")
+    S0 = g["S0"].cuda().requires_grad_()
+    toks = [g[n].cuda().requires_grad_() for n in TOKENS]
+    before = S0.detach().clone()
+    out = F.statetune_recurrent_fp32io16(S0, g["seq_chunk_offsets"].cuda(), g["chunk_starts"].cuda(),
+                                         g["chunk_ends"].cuda(), *toks, scale=g["scale"])
+    for got, name in zip(out, ("y", "final_state", "boundary", "state_dot_a")):
+        assert torch.allclose(got.float().cpu(), g[name].float(), atol=3e-4, rtol=3e-4), name
+    (out[0].float().square().sum() + out[1].square().sum()).backward()
+    for t, name in zip([S0, *toks], ("dS0", "dr", "dw", "dk", "dv", "da", "db")):
+        assert torch.isfinite(t.grad).all()
+        assert torch.allclose(t.grad.float().cpu(), g[name], atol=3e-4, rtol=3e-3), name
+    assert torch.equal(S0.detach(), before)
+
+
+def test_golden_pretrain_forward_and_gradients():
+    import flashrwkv_b200 as F
+
+    g = load_golden("pretrain")
+    vals = [g[n].cuda().requires_grad_() for n in TOKENS]
+    y = F.pretrain_recurrent_bf16(*vals)
+    assert y.shape == vals[0].shape and y.dtype == torch.bfloat16
+    assert torch.allclose(y.float().cpu(), g["y"], atol=0.02, rtol=0.02)
+    assert torch.equal(y, F.pretrain_recurrent_bf16(*vals))
+    y.backward(g["dy"].cuda())
+    for t, name in zip(vals, ("dr", "dw", "dk", "dv", "da", "db")):
+        assert torch.isfinite(t.grad).all()
+        assert torch.allclose(t.grad.float().cpu(), g[name], atol=0.03, rtol=0.05), name
+    with pytest.raises(ValueError, match="divisible by the canonical chunk length 16"):
+        F.pretrain_recurrent_bf16(*(v[:, :17].contiguous() for v in vals))
+    with pytest.raises(TypeError, match="bfloat16"):
+        F.pretrain_recurrent_bf16(*(v.half() for v in vals))
+
+
+@pytest.mark.parametrize("lengths", [(256, 256), (1, 17, 64, 100, 130)])
+def test_gradients_vs_oracle_backward(oracle, lengths):
+    """B200 gradients against the oracle's float64 backward at T up to 256, ragged chunking, non-zero S0,
+    upstream gradients on both the output and the final state."""
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+    from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata
+
+    H, D, B = 2, 64, len(lengths)
+    N = sum(lengths)
+    toks = synthetic.wkv7_inputs(N, H, D, seed=31 + B)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32)
+    S0 = synthetic.state_pool(B, H, D, seed=5)
+    gen = torch.Generator().manual_seed(8)
+    dy = torch.randn(N, H, D, generator=gen).to(torch.bfloat16)
+    dSf = torch.randn(B, H, D, D, generator=gen) * 0.1
+    want = oracle.backward(*toks, initial_state=S0, cu_seqlens=cu, grad_output=dy, grad_final_state=dSf, scale=0.8)
+    dS0 = S0.cuda().requires_grad_()
+    dtoks = [t.cuda().requires_grad_() for t in toks]
+    meta = make_chunk_metadata(cu.cuda(), 64)
+    out = F.statetune_recurrent_fp32io16(dS0, *meta, *dtoks, scale=0.8)
+    torch.autograd.backward([out[0], out[1]], [dy.cuda(), dSf.cuda()])
+    names = ("r", "decay_logits", "k", "v", "a", "b")
+    for t, name in zip(dtoks, names):
+        assert rel_rmse(t.grad.float().cpu(), want[name]) <= 8e-3, name
+    assert rel_rmse(dS0.grad.cpu(), want["initial_state"]) <= 8e-3
