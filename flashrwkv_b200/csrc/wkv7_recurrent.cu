@@ -20,6 +20,7 @@
 // (csrc/sm120/tmix/wkv7/infer_recurrent_fp32io16_forward_varlen.cu:90-275).
 
 #include "frwkv_common.cuh"
+#include "umma.cuh"
 
 namespace frwkv {
 namespace {
@@ -33,6 +34,117 @@ __device__ __forceinline__ void load16(const void* p, uint32_t (&w)[8]) {
   const uint4 lo = __ldg(q), hi = __ldg(q + 1);
   w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w;
   w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
+}
+
+struct StepOut {
+  float sa0, sa1, sa2, sa3;  // S_{t-1}^T a for this lane's four value columns
+  float o0, o1, o2, o3;      // scale * S_t^T r for the same columns
+};
+
+// One token of the recurrence on this lane's 16 x 4 piece of the state (rows row0.., columns col0..); tb is the
+// element offset of (token, head) in the packed token tensors.  Returns the complete (all key rows) sums.
+template <typename io_t>
+__device__ __forceinline__ StepOut token_step(float4 (&s)[16], const io_t* __restrict__ r_ptr,
+                                              const io_t* __restrict__ w_ptr, const io_t* __restrict__ k_ptr,
+                                              const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr,
+                                              const io_t* __restrict__ b_ptr, const io_t* __restrict__ bias_ptr,
+                                              long long tb, int head, int row0, int col0, float scale) {
+  using IO = Io16<io_t>;
+  uint32_t rr[8], ww[8], kk[8], aa[8], bb[8];
+  load16(w_ptr + tb + row0, ww);
+  load16(a_ptr + tb + row0, aa);
+  load16(r_ptr + tb + row0, rr);
+  load16(b_ptr + tb + row0, bb);
+  load16(k_ptr + tb + row0, kk);
+  const uint2 vraw = __ldg(reinterpret_cast<const uint2*>(v_ptr + tb + col0));
+
+  float wv[16];
+  if (bias_ptr != nullptr) {
+    uint32_t bs[8];
+    load16(bias_ptr + head * kD + row0, bs);
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      const float2 x = IO::unpack(ww[p]), bx = IO::unpack(bs[p]);
+      wv[2 * p] = retention(x.x + bx.x);
+      wv[2 * p + 1] = retention(x.y + bx.y);
+    }
+  } else {
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      const float2 x = IO::unpack(ww[p]);
+      wv[2 * p] = retention(x.x);
+      wv[2 * p + 1] = retention(x.y);
+    }
+  }
+
+  float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f;
+  float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+  float br = 0.f, kr = 0.f;
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    const float2 a2 = IO::unpack(aa[p]), r2 = IO::unpack(rr[p]);
+    const float2 b2 = IO::unpack(bb[p]), k2 = IO::unpack(kk[p]);
+    br = fmaf(b2.x, r2.x, br);
+    br = fmaf(b2.y, r2.y, br);
+    kr = fmaf(k2.x, r2.x, kr);
+    kr = fmaf(k2.y, r2.y, kr);
+    {
+      const float4 q = s[2 * p];
+      const float wr = wv[2 * p] * r2.x;
+      sa0 = fmaf(a2.x, q.x, sa0); sa1 = fmaf(a2.x, q.y, sa1);
+      sa2 = fmaf(a2.x, q.z, sa2); sa3 = fmaf(a2.x, q.w, sa3);
+      y0 = fmaf(wr, q.x, y0); y1 = fmaf(wr, q.y, y1);
+      y2 = fmaf(wr, q.z, y2); y3 = fmaf(wr, q.w, y3);
+    }
+    {
+      const float4 q = s[2 * p + 1];
+      const float wr = wv[2 * p + 1] * r2.y;
+      sa0 = fmaf(a2.y, q.x, sa0); sa1 = fmaf(a2.y, q.y, sa1);
+      sa2 = fmaf(a2.y, q.z, sa2); sa3 = fmaf(a2.y, q.w, sa3);
+      y0 = fmaf(wr, q.x, y0); y1 = fmaf(wr, q.y, y1);
+      y2 = fmaf(wr, q.z, y2); y3 = fmaf(wr, q.w, y3);
+    }
+  }
+  // finish the key-direction sums across the four row groups (lane bits 3 and 4)
+#pragma unroll
+  for (int m = 8; m <= 16; m <<= 1) {
+    sa0 += __shfl_xor_sync(0xffffffffu, sa0, m); sa1 += __shfl_xor_sync(0xffffffffu, sa1, m);
+    sa2 += __shfl_xor_sync(0xffffffffu, sa2, m); sa3 += __shfl_xor_sync(0xffffffffu, sa3, m);
+    y0 += __shfl_xor_sync(0xffffffffu, y0, m); y1 += __shfl_xor_sync(0xffffffffu, y1, m);
+    y2 += __shfl_xor_sync(0xffffffffu, y2, m); y3 += __shfl_xor_sync(0xffffffffu, y3, m);
+    br += __shfl_xor_sync(0xffffffffu, br, m); kr += __shfl_xor_sync(0xffffffffu, kr, m);
+  }
+  const float2 v01 = IO::unpack(vraw.x), v23 = IO::unpack(vraw.y);
+
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    const float2 b2 = IO::unpack(bb[p]), k2 = IO::unpack(kk[p]);
+    {
+      float4 q = s[2 * p];
+      const float wi = wv[2 * p];
+      q.x = fmaf(wi, q.x, fmaf(b2.x, sa0, k2.x * v01.x));
+      q.y = fmaf(wi, q.y, fmaf(b2.x, sa1, k2.x * v01.y));
+      q.z = fmaf(wi, q.z, fmaf(b2.x, sa2, k2.x * v23.x));
+      q.w = fmaf(wi, q.w, fmaf(b2.x, sa3, k2.x * v23.y));
+      s[2 * p] = q;
+    }
+    {
+      float4 q = s[2 * p + 1];
+      const float wi = wv[2 * p + 1];
+      q.x = fmaf(wi, q.x, fmaf(b2.y, sa0, k2.y * v01.x));
+      q.y = fmaf(wi, q.y, fmaf(b2.y, sa1, k2.y * v01.y));
+      q.z = fmaf(wi, q.z, fmaf(b2.y, sa2, k2.y * v23.x));
+      q.w = fmaf(wi, q.w, fmaf(b2.y, sa3, k2.y * v23.y));
+      s[2 * p + 1] = q;
+    }
+  }
+  StepOut out;
+  out.sa0 = sa0; out.sa1 = sa1; out.sa2 = sa2; out.sa3 = sa3;
+  out.o0 = scale * fmaf(kr, v01.x, fmaf(br, sa0, y0));
+  out.o1 = scale * fmaf(kr, v01.y, fmaf(br, sa1, y1));
+  out.o2 = scale * fmaf(kr, v23.x, fmaf(br, sa2, y2));
+  out.o3 = scale * fmaf(kr, v23.y, fmaf(br, sa3, y3));
+  return out;
 }
 
 // kReplay = true turns the kernel into the training-side "replay": units are (chunk, head, half), the state is
@@ -81,96 +193,9 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
 
   for (int t = t_begin; t < t_end; ++t) {
     const long long tb = ((long long)t * num_heads + head) * kD;
-    uint32_t rr[8], ww[8], kk[8], aa[8], bb[8];
-    load16(w_ptr + tb + row0, ww);
-    load16(a_ptr + tb + row0, aa);
-    load16(r_ptr + tb + row0, rr);
-    load16(b_ptr + tb + row0, bb);
-    load16(k_ptr + tb + row0, kk);
-    const uint2 vraw = __ldg(reinterpret_cast<const uint2*>(v_ptr + tb + col0));
-
-    float wv[16];
-    if (bias_ptr != nullptr) {
-      uint32_t bs[8];
-      load16(bias_ptr + head * kD + row0, bs);
-#pragma unroll
-      for (int p = 0; p < 8; ++p) {
-        const float2 x = IO::unpack(ww[p]), bx = IO::unpack(bs[p]);
-        wv[2 * p] = retention(x.x + bx.x);
-        wv[2 * p + 1] = retention(x.y + bx.y);
-      }
-    } else {
-#pragma unroll
-      for (int p = 0; p < 8; ++p) {
-        const float2 x = IO::unpack(ww[p]);
-        wv[2 * p] = retention(x.x);
-        wv[2 * p + 1] = retention(x.y);
-      }
-    }
-
-    float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f;
-    float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
-    float br = 0.f, kr = 0.f;
-#pragma unroll
-    for (int p = 0; p < 8; ++p) {
-      const float2 a2 = IO::unpack(aa[p]), r2 = IO::unpack(rr[p]);
-      const float2 b2 = IO::unpack(bb[p]), k2 = IO::unpack(kk[p]);
-      br = fmaf(b2.x, r2.x, br);
-      br = fmaf(b2.y, r2.y, br);
-      kr = fmaf(k2.x, r2.x, kr);
-      kr = fmaf(k2.y, r2.y, kr);
-      {
-        const float4 q = s[2 * p];
-        const float wr = wv[2 * p] * r2.x;
-        sa0 = fmaf(a2.x, q.x, sa0); sa1 = fmaf(a2.x, q.y, sa1);
-        sa2 = fmaf(a2.x, q.z, sa2); sa3 = fmaf(a2.x, q.w, sa3);
-        y0 = fmaf(wr, q.x, y0); y1 = fmaf(wr, q.y, y1);
-        y2 = fmaf(wr, q.z, y2); y3 = fmaf(wr, q.w, y3);
-      }
-      {
-        const float4 q = s[2 * p + 1];
-        const float wr = wv[2 * p + 1] * r2.y;
-        sa0 = fmaf(a2.y, q.x, sa0); sa1 = fmaf(a2.y, q.y, sa1);
-        sa2 = fmaf(a2.y, q.z, sa2); sa3 = fmaf(a2.y, q.w, sa3);
-        y0 = fmaf(wr, q.x, y0); y1 = fmaf(wr, q.y, y1);
-        y2 = fmaf(wr, q.z, y2); y3 = fmaf(wr, q.w, y3);
-      }
-    }
-    // finish the key-direction sums across the four row groups (lane bits 3 and 4)
-#pragma unroll
-    for (int m = 8; m <= 16; m <<= 1) {
-      sa0 += __shfl_xor_sync(0xffffffffu, sa0, m); sa1 += __shfl_xor_sync(0xffffffffu, sa1, m);
-      sa2 += __shfl_xor_sync(0xffffffffu, sa2, m); sa3 += __shfl_xor_sync(0xffffffffu, sa3, m);
-      y0 += __shfl_xor_sync(0xffffffffu, y0, m); y1 += __shfl_xor_sync(0xffffffffu, y1, m);
-      y2 += __shfl_xor_sync(0xffffffffu, y2, m); y3 += __shfl_xor_sync(0xffffffffu, y3, m);
-      br += __shfl_xor_sync(0xffffffffu, br, m); kr += __shfl_xor_sync(0xffffffffu, kr, m);
-    }
-    const float2 v01 = IO::unpack(vraw.x), v23 = IO::unpack(vraw.y);
-
-#pragma unroll
-    for (int p = 0; p < 8; ++p) {
-      const float2 b2 = IO::unpack(bb[p]), k2 = IO::unpack(kk[p]);
-      {
-        float4 q = s[2 * p];
-        const float wi = wv[2 * p];
-        q.x = fmaf(wi, q.x, fmaf(b2.x, sa0, k2.x * v01.x));
-        q.y = fmaf(wi, q.y, fmaf(b2.x, sa1, k2.x * v01.y));
-        q.z = fmaf(wi, q.z, fmaf(b2.x, sa2, k2.x * v23.x));
-        q.w = fmaf(wi, q.w, fmaf(b2.x, sa3, k2.x * v23.y));
-        s[2 * p] = q;
-      }
-      {
-        float4 q = s[2 * p + 1];
-        const float wi = wv[2 * p + 1];
-        q.x = fmaf(wi, q.x, fmaf(b2.y, sa0, k2.y * v01.x));
-        q.y = fmaf(wi, q.y, fmaf(b2.y, sa1, k2.y * v01.y));
-        q.z = fmaf(wi, q.z, fmaf(b2.y, sa2, k2.y * v23.x));
-        q.w = fmaf(wi, q.w, fmaf(b2.y, sa3, k2.y * v23.y));
-        s[2 * p + 1] = q;
-      }
-    }
+    const StepOut st = token_step<io_t>(s, r_ptr, w_ptr, k_ptr, v_ptr, a_ptr, b_ptr, bias_ptr, tb, head, row0, col0, scale);
     if (kReplay) {
-      if (kg == 0) *reinterpret_cast<float4*>(sa_ptr + tb + col0) = make_float4(sa0, sa1, sa2, sa3);
+      if (kg == 0) *reinterpret_cast<float4*>(sa_ptr + tb + col0) = make_float4(st.sa0, st.sa1, st.sa2, st.sa3);
       const int done = t - t_begin + 1;
       if (ckpt_ptr != nullptr && (done & 15) == 0 && t + 1 < t_end) {
         float* cbase = ckpt_ptr + (((long long)seq * 3 + (done >> 4) - 1) * num_heads + head) * (kD * kD) +
@@ -179,16 +204,12 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
         for (int i = 0; i < 16; ++i) *reinterpret_cast<float4*>(cbase + i * kD) = s[i];
       }
     } else if (kg == 0) {
-      const float o0 = scale * fmaf(kr, v01.x, fmaf(br, sa0, y0));
-      const float o1 = scale * fmaf(kr, v01.y, fmaf(br, sa1, y1));
-      const float o2 = scale * fmaf(kr, v23.x, fmaf(br, sa2, y2));
-      const float o3 = scale * fmaf(kr, v23.y, fmaf(br, sa3, y3));
       uint2 packed;
-      packed.x = IO::pack(o0, o1);
-      packed.y = IO::pack(o2, o3);
+      packed.x = IO::pack(st.o0, st.o1);
+      packed.y = IO::pack(st.o2, st.o3);
       *reinterpret_cast<uint2*>(y_ptr + tb + col0) = packed;
       if (y32_ptr != nullptr) {
-        *reinterpret_cast<float4*>(y32_ptr + tb + col0) = make_float4(o0, o1, o2, o3);
+        *reinterpret_cast<float4*>(y32_ptr + tb + col0) = make_float4(st.o0, st.o1, st.o2, st.o3);
       }
     }
   }
@@ -197,6 +218,128 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
 #pragma unroll
     for (int i = 0; i < 16; ++i) *reinterpret_cast<float4*>(sbase + i * kD) = s[i];
   }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Decode kernel (every sequence has one token): persistent CTAs that stream the 16 KB state tiles through a
+// shared-memory ring with bulk copies, so that loads and stores stay in flight independently of the arithmetic.
+//   warp 0 (one lane)  : loader  - waits for a free stage, cp.async.bulk global -> shared, completion on full[stage]
+//   warp 1 (one lane)  : storer  - waits for done[stage] (both halves updated), cp.async.bulk shared -> global,
+//                                  and hands a stage back (empty[stage]) once its store has finished reading it
+//   warps 2..9         : four pairs of consumer warps; a pair owns one tile at a time, one warp per half, and runs
+//                        the same per-token step as the register kernel on float4s read from the staged tile
+// CTA b owns the (sequence, head) tiles b, b + gridDim.x, ...; its i-th tile uses stage i % kStages.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kStages = 12;
+constexpr int kTileBytes = kD * kD * 4;
+constexpr int kConsumerPairs = 4;
+constexpr int kDecodeThreads = 32 * (2 + 2 * kConsumerPairs);
+constexpr int kDecodeSmem = kStages * kTileBytes;
+
+__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),
+               "r"(umma::smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* mbar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(umma::smem_u32(mbar)) : "memory");
+}
+
+template <typename io_t>
+__global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_decode_pipelined_kernel(
+    const int* __restrict__ state_indices, const int* __restrict__ metadata_status, float* __restrict__ state_pool,
+    const io_t* __restrict__ r_ptr, const io_t* __restrict__ w_ptr, const io_t* __restrict__ k_ptr,
+    const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr, const io_t* __restrict__ b_ptr,
+    const io_t* __restrict__ bias_ptr, io_t* __restrict__ y_ptr, float* __restrict__ y32_ptr, int num_tiles,
+    int num_heads, long long output_elements, float scale, int* __restrict__ error_flag) {
+  using IO = Io16<io_t>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ uint64_t full_bar[kStages], done_bar[kStages], empty_bar[kStages];
+  if (metadata_status != nullptr && metadata_status[0] != 0) {
+    const io_t nan16 = IO::store(quiet_nan());
+    for (long long i = (long long)blockIdx.x * kDecodeThreads + threadIdx.x; i < output_elements;
+         i += (long long)gridDim.x * kDecodeThreads) {
+      y_ptr[i] = nan16;
+      if (y32_ptr != nullptr) y32_ptr[i] = quiet_nan();
+    }
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      umma::mbar_init(&full_bar[i], 1);
+      umma::mbar_init(&done_bar[i], 2);
+      umma::mbar_init(&empty_bar[i], 1);
+    }
+    umma::mbar_fence_init();
+  }
+  __syncthreads();
+  const int my_tiles = ((int)blockIdx.x < num_tiles) ? (num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < my_tiles && ok; ++i) {
+        const int st = i % kStages;
+        if (i >= kStages) ok = umma::mbar_wait(&empty_bar[st], ((i / kStages) - 1) & 1);
+        if (!ok) break;
+        const int tile = blockIdx.x + i * gridDim.x;
+        const int seq = tile / num_heads, head = tile % num_heads;
+        const float* src = state_pool + ((long long)state_indices[seq] * num_heads + head) * (kD * kD);
+        umma::mbar_expect_tx(&full_bar[st], kTileBytes);
+        umma::bulk_g2s(smem + st * kTileBytes, src, kTileBytes, &full_bar[st]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int i = 0; i < my_tiles && ok; ++i) {
+        const int st = i % kStages;
+        ok = umma::mbar_wait(&done_bar[st], (i / kStages) & 1);
+        if (!ok) break;
+        const int tile = blockIdx.x + i * gridDim.x;
+        const int seq = tile / num_heads, head = tile % num_heads;
+        float* dst = state_pool + ((long long)state_indices[seq] * num_heads + head) * (kD * kD);
+        bulk_s2g(dst, smem + st * kTileBytes, kTileBytes);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        // at most three stores may still be reading shared memory: the stage of tile i-3 is free again
+        asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+        if (i >= 3) mbar_arrive(&empty_bar[(i - 3) % kStages]);
+      }
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      for (int i = (my_tiles > 3 ? my_tiles - 3 : 0); i < my_tiles && ok; ++i) mbar_arrive(&empty_bar[i % kStages]);
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all state writes are complete before exit
+    }
+  } else {
+    const int pair = (warp - 2) >> 1, vhalf = (warp - 2) & 1;
+    const int kg = lane >> 3, vq = lane & 7;
+    const int row0 = kg * 16, col0 = vhalf * 32 + vq * 4;
+    for (int i = pair; i < my_tiles && ok; i += kConsumerPairs) {
+      const int st = i % kStages;
+      const int tile = blockIdx.x + i * gridDim.x;
+      const int seq = tile / num_heads, head = tile % num_heads;
+      ok = umma::mbar_wait(&full_bar[st], (i / kStages) & 1);
+      if (!ok) break;
+      float* tbase = reinterpret_cast<float*>(smem + st * kTileBytes) + row0 * kD + col0;
+      float4 s[16];
+#pragma unroll
+      for (int q = 0; q < 16; ++q) s[q] = *reinterpret_cast<const float4*>(tbase + q * kD);
+      const long long tb = ((long long)seq * num_heads + head) * kD;  // one token per sequence: token == sequence
+      const StepOut o = token_step<io_t>(s, r_ptr, w_ptr, k_ptr, v_ptr, a_ptr, b_ptr, bias_ptr, tb, head, row0, col0, scale);
+#pragma unroll
+      for (int q = 0; q < 16; ++q) *reinterpret_cast<float4*>(tbase + q * kD) = s[q];
+      if (kg == 0) {
+        uint2 packed;
+        packed.x = IO::pack(o.o0, o.o1);
+        packed.y = IO::pack(o.o2, o.o3);
+        *reinterpret_cast<uint2*>(y_ptr + tb + col0) = packed;
+        if (y32_ptr != nullptr) *reinterpret_cast<float4*>(y32_ptr + tb + col0) = make_float4(o.o0, o.o1, o.o2, o.o3);
+      }
+      umma::fence_async_smem();  // the bulk store reads what this warp just wrote
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&done_bar[st]);
+    }
+  }
+  if (!ok && lane == 0 && error_flag != nullptr) atomicExch(error_flag, 4);
 }
 
 template <typename io_t>
@@ -212,6 +355,26 @@ int launch(const int* cu, const int* idx, const int* status, float* state, const
       static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, nullptr, nullptr,
       units, num_heads, (long long)total_tokens * num_heads * kD, scale);
   return check_launch("wkv7_recurrent_d64_kernel");
+}
+
+template <typename io_t>
+int launch_decode(const int* idx, const int* status, float* state, const void* r, const void* w, const void* k,
+                  const void* v, const void* a, const void* b, const void* bias, void* y, float* y32,
+                  int num_sequences, int num_heads, float scale, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(wkv7_decode_pipelined_kernel<io_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kDecodeSmem);
+  if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "wkv7_recurrent: %s", cudaGetErrorString(e));
+  int device = 0, sm_count = 0;
+  cudaGetDevice(&device);
+  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+  const int tiles = num_sequences * num_heads;
+  const int grid = sm_count > 0 && sm_count < tiles ? sm_count : tiles;
+  wkv7_decode_pipelined_kernel<io_t><<<grid, kDecodeThreads, kDecodeSmem, stream>>>(
+      idx, status, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w), static_cast<const io_t*>(k),
+      static_cast<const io_t*>(v), static_cast<const io_t*>(a), static_cast<const io_t*>(b),
+      static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, tiles, num_heads,
+      (long long)num_sequences * num_heads * kD, scale, nullptr);
+  return check_launch("wkv7_decode_pipelined_kernel");
 }
 
 template <typename io_t>
@@ -238,7 +401,6 @@ extern "C" int frwkv_wkv7_recurrent_fp32io16_forward_varlen(
     int total_tokens, int num_sequences, int num_heads, int head_size, int max_seqlen,
     int io_dtype, float scale, frwkv_stream_t stream) {
   using namespace frwkv;
-  (void)max_seqlen;  // one kernel serves every sequence length
   clear_error();
   FRWKV_REQUIRE(cu_seqlens && state_indices && state_pool && r && decay_logits && k && v && a && b && y,
                 "wkv7_recurrent: null pointer argument");
@@ -251,6 +413,16 @@ extern "C" int frwkv_wkv7_recurrent_fp32io16_forward_varlen(
   const long long blocks = ((long long)num_sequences * num_heads * 2 + 3) / 4;
   FRWKV_REQUIRE(blocks <= 0x7fffffffLL, "wkv7_recurrent: too many (sequence, head) pairs");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // decode (one token per sequence, known from the caller's validated metadata) with enough tiles to keep a
+  // persistent grid busy takes the bulk-copy pipelined kernel; everything else the register kernel
+  const bool decode = max_seqlen == 1 && total_tokens == num_sequences &&
+                      (long long)num_sequences * num_heads >= 1024 && (long long)num_sequences * num_heads <= 0x7fffffffLL;
+  if (decode && io_dtype == FRWKV_DTYPE_BF16)
+    return launch_decode<__nv_bfloat16>(state_indices, metadata_status, state_pool, r, decay_logits, k, v, a, b,
+                                        decay_bias, y, y_fp32, num_sequences, num_heads, scale, s);
+  if (decode && io_dtype == FRWKV_DTYPE_FP16)
+    return launch_decode<__half>(state_indices, metadata_status, state_pool, r, decay_logits, k, v, a, b, decay_bias,
+                                 y, y_fp32, num_sequences, num_heads, scale, s);
   if (io_dtype == FRWKV_DTYPE_BF16) {
     return launch<__nv_bfloat16>(cu_seqlens, state_indices, metadata_status, state_pool, r, decay_logits, k,
                                  v, a, b, decay_bias, y, y_fp32, total_tokens, num_sequences, num_heads,
