@@ -75,11 +75,24 @@ struct Io16<__nv_bfloat16> {
 };
 
 // ---- retention transform -------------------------------------------------------------------
-// w = exp(-exp(-0.5) * sigmoid(x)), written in the reference's exp2 form
-// (csrc/sm120/tmix/wkv7/recurrent_decay.cuh:18-22 of the reference) so that both
-// implementations round the same way.
+// w = exp(-exp(-0.5) * sigmoid(x)), in the reference's exp2 form
+// (csrc/sm120/tmix/wkv7/recurrent_decay.cuh:18-22 of the reference).  The hot kernels evaluate it 64 times per
+// (token, head), so it is six instructions: ex2.approx (relative error 2^-22), one add, rcp.approx (1 ulp) and two
+// multiplies; the result is within 3e-7 relative of the correctly rounded value, far inside every tolerance here.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float retention(float decay_logit) {
-  return exp2f(-0.8750387749145276f / (1.0f + exp2f(-1.4426950408889634f * decay_logit)));
+  // clamp keeps 1 + 2^(-x log2 e) finite for very negative logits (sigmoid -> 0, w -> 1)
+  const float e = ex2_approx(fminf(-1.4426950408889634f * decay_logit, 126.0f));
+  return ex2_approx(-0.8750387749145276f * rcp_approx(1.0f + e));
 }
 
 // d log(w) / dx = -exp(-0.5) * s * (1 - s), s = sigmoid(x) (recurrent_decay.cuh:27-32).

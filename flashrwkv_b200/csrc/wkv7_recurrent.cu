@@ -232,9 +232,11 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
 // ---------------------------------------------------------------------------------------------------------
 constexpr int kStages = 12;
 constexpr int kTileBytes = kD * kD * 4;
-constexpr int kConsumerPairs = 4;
+constexpr int kTokBytes = 6 * kD * 2;                 // r, w, k, v, a, b rows of one (token, head)
+constexpr int kStageBytes = kTileBytes + kTokBytes;   // 17,152
+constexpr int kConsumerPairs = 6;
 constexpr int kDecodeThreads = 32 * (2 + 2 * kConsumerPairs);
-constexpr int kDecodeSmem = kStages * kTileBytes;
+constexpr int kDecodeSmem = kStages * kStageBytes;
 
 __device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),
@@ -243,6 +245,90 @@ __device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, u
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* mbar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(umma::smem_u32(mbar)) : "memory");
+}
+__device__ __forceinline__ void lds16(const unsigned char* p, uint32_t (&w)[8]) {
+  const uint4 lo = *reinterpret_cast<const uint4*>(p), hi = *reinterpret_cast<const uint4*>(p + 16);
+  w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w;
+  w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
+}
+
+// One token on a staged tile: same arithmetic as token_step, but the state stays in shared memory (read twice,
+// written once) and the token vectors come from the stage's token area, so the consumer needs few registers and
+// touches no global memory except for the output.
+template <typename io_t>
+__device__ __forceinline__ StepOut tile_step_smem(float* __restrict__ tbase, const unsigned char* __restrict__ tok,
+                                                  const io_t* __restrict__ bias_ptr, int head, int row0, int col0,
+                                                  float scale) {
+  using IO = Io16<io_t>;
+  uint32_t rr[8], ww[8], kk[8], aa[8], bb[8];
+  lds16(tok + 0 * 128 + row0 * 2, rr);
+  lds16(tok + 1 * 128 + row0 * 2, ww);
+  lds16(tok + 2 * 128 + row0 * 2, kk);
+  lds16(tok + 4 * 128 + row0 * 2, aa);
+  lds16(tok + 5 * 128 + row0 * 2, bb);
+  const uint2 vraw = *reinterpret_cast<const uint2*>(tok + 3 * 128 + col0 * 2);
+  float wv[16];
+  if (bias_ptr != nullptr) {
+    uint32_t bs[8];
+    load16(bias_ptr + head * kD + row0, bs);
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      const float2 x = IO::unpack(ww[p]), bx = IO::unpack(bs[p]);
+      wv[2 * p] = retention(x.x + bx.x);
+      wv[2 * p + 1] = retention(x.y + bx.y);
+    }
+  } else {
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      const float2 x = IO::unpack(ww[p]);
+      wv[2 * p] = retention(x.x);
+      wv[2 * p + 1] = retention(x.y);
+    }
+  }
+  float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f, y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f, br = 0.f, kr = 0.f;
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    const float2 a2 = IO::unpack(aa[p]), r2 = IO::unpack(rr[p]);
+    const float2 b2 = IO::unpack(bb[p]), k2 = IO::unpack(kk[p]);
+    br = fmaf(b2.x, r2.x, fmaf(b2.y, r2.y, br));
+    kr = fmaf(k2.x, r2.x, fmaf(k2.y, r2.y, kr));
+    const float4 q0 = *reinterpret_cast<const float4*>(tbase + (2 * p) * kD);
+    const float4 q1 = *reinterpret_cast<const float4*>(tbase + (2 * p + 1) * kD);
+    const float wr0 = wv[2 * p] * r2.x, wr1 = wv[2 * p + 1] * r2.y;
+    sa0 = fmaf(a2.x, q0.x, fmaf(a2.y, q1.x, sa0)); sa1 = fmaf(a2.x, q0.y, fmaf(a2.y, q1.y, sa1));
+    sa2 = fmaf(a2.x, q0.z, fmaf(a2.y, q1.z, sa2)); sa3 = fmaf(a2.x, q0.w, fmaf(a2.y, q1.w, sa3));
+    y0 = fmaf(wr0, q0.x, fmaf(wr1, q1.x, y0)); y1 = fmaf(wr0, q0.y, fmaf(wr1, q1.y, y1));
+    y2 = fmaf(wr0, q0.z, fmaf(wr1, q1.z, y2)); y3 = fmaf(wr0, q0.w, fmaf(wr1, q1.w, y3));
+  }
+#pragma unroll
+  for (int m = 8; m <= 16; m <<= 1) {
+    sa0 += __shfl_xor_sync(0xffffffffu, sa0, m); sa1 += __shfl_xor_sync(0xffffffffu, sa1, m);
+    sa2 += __shfl_xor_sync(0xffffffffu, sa2, m); sa3 += __shfl_xor_sync(0xffffffffu, sa3, m);
+    y0 += __shfl_xor_sync(0xffffffffu, y0, m); y1 += __shfl_xor_sync(0xffffffffu, y1, m);
+    y2 += __shfl_xor_sync(0xffffffffu, y2, m); y3 += __shfl_xor_sync(0xffffffffu, y3, m);
+    br += __shfl_xor_sync(0xffffffffu, br, m); kr += __shfl_xor_sync(0xffffffffu, kr, m);
+  }
+  const float2 v01 = IO::unpack(vraw.x), v23 = IO::unpack(vraw.y);
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    const float2 b2 = IO::unpack(bb[p]), k2 = IO::unpack(kk[p]);
+    float4 q0 = *reinterpret_cast<const float4*>(tbase + (2 * p) * kD);
+    float4 q1 = *reinterpret_cast<const float4*>(tbase + (2 * p + 1) * kD);
+    const float w0 = wv[2 * p], w1 = wv[2 * p + 1];
+    q0.x = fmaf(w0, q0.x, fmaf(b2.x, sa0, k2.x * v01.x)); q0.y = fmaf(w0, q0.y, fmaf(b2.x, sa1, k2.x * v01.y));
+    q0.z = fmaf(w0, q0.z, fmaf(b2.x, sa2, k2.x * v23.x)); q0.w = fmaf(w0, q0.w, fmaf(b2.x, sa3, k2.x * v23.y));
+    q1.x = fmaf(w1, q1.x, fmaf(b2.y, sa0, k2.y * v01.x)); q1.y = fmaf(w1, q1.y, fmaf(b2.y, sa1, k2.y * v01.y));
+    q1.z = fmaf(w1, q1.z, fmaf(b2.y, sa2, k2.y * v23.x)); q1.w = fmaf(w1, q1.w, fmaf(b2.y, sa3, k2.y * v23.y));
+    *reinterpret_cast<float4*>(tbase + (2 * p) * kD) = q0;
+    *reinterpret_cast<float4*>(tbase + (2 * p + 1) * kD) = q1;
+  }
+  StepOut out;
+  out.sa0 = sa0; out.sa1 = sa1; out.sa2 = sa2; out.sa3 = sa3;
+  out.o0 = scale * fmaf(kr, v01.x, fmaf(br, sa0, y0));
+  out.o1 = scale * fmaf(kr, v01.y, fmaf(br, sa1, y1));
+  out.o2 = scale * fmaf(kr, v23.x, fmaf(br, sa2, y2));
+  out.o3 = scale * fmaf(kr, v23.y, fmaf(br, sa3, y3));
+  return out;
 }
 
 template <typename io_t>
@@ -286,8 +372,16 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_decode_pipelined_kerne
         const int tile = blockIdx.x + i * gridDim.x;
         const int seq = tile / num_heads, head = tile % num_heads;
         const float* src = state_pool + ((long long)state_indices[seq] * num_heads + head) * (kD * kD);
-        umma::mbar_expect_tx(&full_bar[st], kTileBytes);
-        umma::bulk_g2s(smem + st * kTileBytes, src, kTileBytes, &full_bar[st]);
+        const long long tb = ((long long)seq * num_heads + head) * kD;  // one token per sequence: token == sequence
+        unsigned char* stage = smem + st * kStageBytes;
+        umma::mbar_expect_tx(&full_bar[st], kStageBytes);
+        umma::bulk_g2s(stage, src, kTileBytes, &full_bar[st]);
+        umma::bulk_g2s(stage + kTileBytes + 0 * 128, r_ptr + tb, 128, &full_bar[st]);
+        umma::bulk_g2s(stage + kTileBytes + 1 * 128, w_ptr + tb, 128, &full_bar[st]);
+        umma::bulk_g2s(stage + kTileBytes + 2 * 128, k_ptr + tb, 128, &full_bar[st]);
+        umma::bulk_g2s(stage + kTileBytes + 3 * 128, v_ptr + tb, 128, &full_bar[st]);
+        umma::bulk_g2s(stage + kTileBytes + 4 * 128, a_ptr + tb, 128, &full_bar[st]);
+        umma::bulk_g2s(stage + kTileBytes + 5 * 128, b_ptr + tb, 128, &full_bar[st]);
       }
     }
   } else if (warp == 1) {
@@ -299,7 +393,7 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_decode_pipelined_kerne
         const int tile = blockIdx.x + i * gridDim.x;
         const int seq = tile / num_heads, head = tile % num_heads;
         float* dst = state_pool + ((long long)state_indices[seq] * num_heads + head) * (kD * kD);
-        bulk_s2g(dst, smem + st * kTileBytes, kTileBytes);
+        bulk_s2g(dst, smem + st * kStageBytes, kTileBytes);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         // at most three stores may still be reading shared memory: the stage of tile i-3 is free again
         asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
@@ -319,15 +413,11 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_decode_pipelined_kerne
       const int seq = tile / num_heads, head = tile % num_heads;
       ok = umma::mbar_wait(&full_bar[st], (i / kStages) & 1);
       if (!ok) break;
-      float* tbase = reinterpret_cast<float*>(smem + st * kTileBytes) + row0 * kD + col0;
-      float4 s[16];
-#pragma unroll
-      for (int q = 0; q < 16; ++q) s[q] = *reinterpret_cast<const float4*>(tbase + q * kD);
-      const long long tb = ((long long)seq * num_heads + head) * kD;  // one token per sequence: token == sequence
-      const StepOut o = token_step<io_t>(s, r_ptr, w_ptr, k_ptr, v_ptr, a_ptr, b_ptr, bias_ptr, tb, head, row0, col0, scale);
-#pragma unroll
-      for (int q = 0; q < 16; ++q) *reinterpret_cast<float4*>(tbase + q * kD) = s[q];
+      unsigned char* stage = smem + st * kStageBytes;
+      const StepOut o = tile_step_smem<io_t>(reinterpret_cast<float*>(stage) + row0 * kD + col0, stage + kTileBytes,
+                                             bias_ptr, head, row0, col0, scale);
       if (kg == 0) {
+        const long long tb = ((long long)seq * num_heads + head) * kD;
         uint2 packed;
         packed.x = IO::pack(o.o0, o.o1);
         packed.y = IO::pack(o.o2, o.o3);
