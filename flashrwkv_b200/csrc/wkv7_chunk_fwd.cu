@@ -711,3 +711,75 @@ extern "C" int frwkv_wkv7_chunk_fp32io16_forward(
                                         scale, s);
   return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_chunk_forward: token tensors must be float16 or bfloat16");
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Chunked forward for callers that must not allocate device memory.
+//
+// Some hosts hand the whole device to fixed pools when they start (state pools, activation arenas) and forbid
+// any later cudaMalloc: an inference server that has sized its pools to the last megabyte, a real-time loop in
+// which an allocation could stall the device, a plain C host with no caching allocator behind it.  For them the
+// [E;M] / [F;N] workspace of the build and scan kernels lives in a fixed array inside this library instead of in
+// memory the caller provides.  The array costs kNoAllocBytes on every GPU that loads the library, for the life
+// of the process, so it is kept modest: it covers kNoAllocMaxItems (chunk, head) pairs per call, e.g. 256 tokens
+// of 64 heads, or 1024 tokens of 16 heads.
+//
+// The array name is only a handle on the host side; the device address comes from cudaGetSymbolAddress, looked
+// up once per device (on the first call made with that device current - do that first call outside any stream
+// capture) and cached.  Every call uses the same array: two calls whose kernels overlap on the GPU (different
+// streams) would overwrite each other's tiles, so callers must order them.  Nothing in the array has to start at
+// zero - the build kernel writes every tile before the scan kernel reads it - so the contents left by the
+// previous call are harmless.
+// ---------------------------------------------------------------------------------------------------------
+namespace frwkv {
+namespace {
+constexpr int kNoAllocMaxItems = 256;
+constexpr size_t kNoAllocBytes = (size_t)kNoAllocMaxItems * 2 * kWsTile;  // 16 MiB
+constexpr int kNoAllocMaxDevices = 64;
+}  // namespace
+}  // namespace frwkv
+
+static __device__ __align__(256) unsigned char g_noalloc_workspace[frwkv::kNoAllocBytes];
+
+static void* noalloc_workspace_for_current_device(int* status) {
+  static void* cached[frwkv::kNoAllocMaxDevices] = {};
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= frwkv::kNoAllocMaxDevices) {
+    *status = frwkv::fail(FRWKV_ERR_CUDA, "wkv7_chunk_forward_noalloc: cannot identify the current device");
+    return nullptr;
+  }
+  void* ptr = __atomic_load_n(&cached[device], __ATOMIC_ACQUIRE);
+  if (ptr == nullptr) {
+    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_noalloc_workspace);
+    if (err != cudaSuccess || ptr == nullptr) {
+      *status = frwkv::fail(FRWKV_ERR_CUDA, "wkv7_chunk_forward_noalloc: cudaGetSymbolAddress failed: %s",
+                            cudaGetErrorString(err));
+      return nullptr;
+    }
+    __atomic_store_n(&cached[device], ptr, __ATOMIC_RELEASE);  // racing first calls store the same address
+  }
+  return ptr;
+}
+
+extern "C" size_t frwkv_wkv7_chunk_noalloc_max_items(void) { return (size_t)frwkv::kNoAllocMaxItems; }
+
+extern "C" int frwkv_wkv7_chunk_fp32io16_forward_noalloc(
+    const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends,
+    const int32_t* state_indices, const int32_t* metadata_status, float* state_pool, const void* r,
+    const void* decay_logits, const void* k, const void* v, const void* a, const void* b, const void* decay_bias,
+    void* y, float* y_fp32, float* boundary, int32_t* error_flag, int total_tokens, int num_sequences, int num_chunks,
+    int num_heads, int head_size, int io_dtype, float scale, frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(num_chunks > 0 && num_heads > 0, "wkv7_chunk_forward_noalloc: sizes must be positive");
+  FRWKV_REQUIRE((long long)num_chunks * num_heads <= kNoAllocMaxItems,
+                "wkv7_chunk_forward_noalloc: %d chunks x %d heads exceeds the built-in workspace of %d (chunk, head) "
+                "pairs; split the batch or use frwkv_wkv7_chunk_fp32io16_forward with your own workspace",
+                num_chunks, num_heads, kNoAllocMaxItems);
+  int status = FRWKV_OK;
+  void* workspace = noalloc_workspace_for_current_device(&status);
+  if (workspace == nullptr) return status;
+  return frwkv_wkv7_chunk_fp32io16_forward(seq_chunk_offsets, chunk_starts, chunk_ends, state_indices, metadata_status,
+                                           state_pool, r, decay_logits, k, v, a, b, decay_bias, y, y_fp32, boundary,
+                                           workspace, kNoAllocBytes, error_flag, total_tokens, num_sequences,
+                                           num_chunks, num_heads, head_size, io_dtype, scale, stream);
+}

@@ -111,6 +111,25 @@ int frwkv_wkv7_chunk_fp32io16_forward(
     frwkv_stream_t stream);
 
 /*
+ * The same chunked forward for hosts that may not allocate device memory (servers that gave the whole GPU to
+ * fixed pools at start-up, real-time loops, plain C callers without a caching allocator).  It has no
+ * counterpart in the reference, whose chunk operators allocate their workspaces through Torch on every call.
+ * The workspace is a 16 MiB array built into the library (resident on every GPU that loads it), which limits a
+ * call to num_chunks * num_heads <= frwkv_wkv7_chunk_noalloc_max_items() = 256; larger calls are refused with
+ * FRWKV_ERR_INVALID_ARGUMENT and a message.  No cudaMalloc / cudaFree or allocating library call is made.
+ * The first call on each device looks up the array's device address (make it outside stream capture).
+ * All calls share the one array: calls whose kernels could overlap on the GPU must be ordered by the caller.
+ * Arguments are those of frwkv_wkv7_chunk_fp32io16_forward without workspace / workspace_bytes.
+ */
+size_t frwkv_wkv7_chunk_noalloc_max_items(void);
+int frwkv_wkv7_chunk_fp32io16_forward_noalloc(
+    const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends,
+    const int32_t* state_indices, const int32_t* metadata_status, float* state_pool, const void* r,
+    const void* decay_logits, const void* k, const void* v, const void* a, const void* b, const void* decay_bias,
+    void* y, float* y_fp32, float* boundary, int32_t* error_flag, int total_tokens, int num_sequences, int num_chunks,
+    int num_heads, int head_size, int io_dtype, float scale, frwkv_stream_t stream);
+
+/*
  * Training-side replay: per chunk, run the recurrence from the chunk-start state boundary[c] and store
  *   state_dot_a fp32 [N,H,64]      sa_t = S_{t-1}^T a_t for every token, and
  *   checkpoints fp32 [Cn,3,H,64,64] the state after tokens 16, 32 and 48 of each chunk (where the chunk is longer);
