@@ -190,6 +190,122 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def _time_cuda(fn, warmup=2, iters=5):
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3
+
+
+def _extras(dev):
+    """Secondary workloads of the same path, timed briefly on this GPU: chunked prefill (B8 T4096 H32), training
+    forward+backward (B8 T4096 H64) and the TMix layer chain (C=2048, M in {1,4,7,512}).  Roofline fractions use
+    the algorithmic bytes / FLOPs of DESIGN.md and the measured peaks."""
+    import torch
+
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+    from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata, wkv7_chunk_forward
+
+    out = {}
+    peaks = {}
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        peaks = json.loads(pk.read_text())
+    hbm = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS)) * 1e9
+    bf16 = float(peaks.get("bf16_tflops", 1590.0)) * 1e12
+    # ---- chunked prefill
+    Bc, T, Hc = 8, 4096, 32
+    toks = [t.to(dev) for t in synthetic.wkv7_inputs(Bc * T, Hc, D, seed=11)]
+    cu, _ = synthetic.equal_length_metadata(Bc, T, device=dev)
+    meta = make_chunk_metadata(cu, 64)
+    pool = synthetic.state_pool(Bc, Hc, D, seed=12, device=dev)
+    sec = _time_cuda(lambda: wkv7_chunk_forward(*toks, state=pool, chunk_metadata=meta))
+    n_tok = Bc * T
+    alg_bytes = 7 * n_tok * Hc * D * 2 + 2 * Bc * Hc * D * D * 4
+    flops = n_tok * Hc * 98304
+    out["chunked_prefill"] = {
+        "workload": f"B={Bc} T={T} H={Hc} D={D} chunk 64, bf16 tokens, fp32 state", "tokens_per_s": n_tok / sec,
+        "ms": sec * 1e3, "hbm_frac_algorithmic": alg_bytes / sec / hbm, "tensor_frac_of_bf16_peak": flops / sec / bf16,
+        "tensor_frac_of_tf32_peak": flops / sec / (bf16 / 2), "gpu_launches_per_call": 2}
+    del toks, pool
+    # ---- training forward + backward
+    Ht = 64
+    toks = [t.to(dev).requires_grad_() for t in synthetic.wkv7_inputs(Bc * T, Ht, D, seed=13)]
+    S0 = synthetic.state_pool(Bc, Ht, D, seed=14, device=dev).requires_grad_()
+    dy = torch.randn(Bc * T, Ht, D, device=dev).to(torch.bfloat16)
+
+    def train_step():
+        res = F.statetune_recurrent_fp32io16(S0, *meta, *toks)
+        res[0].backward(dy)
+        for t in (*toks, S0):
+            t.grad = None
+
+    sec = _time_cuda(train_step, warmup=1, iters=2)
+    out["training_fwd_bwd"] = {
+        "workload": f"B={Bc} T={T} H={Ht} D={D}, forward (chunk build + scan + replay) and backward",
+        "tokens_per_s": n_tok / sec, "ms": sec * 1e3, "tensor_frac_of_bf16_peak": n_tok * Ht * 294912 / sec / bf16,
+        "gpu_launches_per_call": 5}
+    del toks, S0, dy
+    torch.cuda.empty_cache()
+    # ---- TMix layer chain, C = 2048
+    C, Hh = 2048, 32
+    g = torch.Generator().manual_seed(3)
+    wt = lambda n, k: (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(dev)  # noqa: E731
+    vec = lambda: torch.rand(C, generator=g).to(torch.bfloat16).to(dev)  # noqa: E731
+    Wr, Wk, Wv, Wo = (wt(C, C) for _ in range(4))
+    ranks = {"w": 96, "a": 96, "g": 256, "v": 64}
+    w1 = {n: wt(r, C) for n, r in ranks.items()}
+    w2 = {n: wt(C, r) for n, r in ranks.items()}
+    mixes = [vec() for _ in range(6)]
+    k_k, a0, k_a, r_k, lnw, lnb, v0 = (vec() for _ in range(7))
+    weight_bytes = 2 * (4 * C * C + 2 * C * sum(ranks.values()))
+    tmix = {}
+    for M in (1, 4, 7, 512):
+        x = torch.randn(M, C, generator=g).to(torch.bfloat16).to(dev)
+        v_first = torch.randn(M, C, generator=g).to(torch.bfloat16).to(dev)
+        shift = torch.zeros(M, C, dtype=torch.bfloat16, device=dev)
+        spool = synthetic.state_pool(M, Hh, D, seed=5, device=dev)
+        cu, idx = synthetic.equal_length_metadata(M, 1, device=dev)
+        ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=M, state_pool_size=M, max_seqlen=1)
+
+        def layer():
+            xr, xw, xk, xv, xa, xg = F.infer_tmix_mix6_forward_varlen(x, *mixes, shift_state_pool=shift, cu_seqlens=cu,
+                                                                      state_indices=idx, max_seqlen=1,
+                                                                      validated_metadata=ticket)
+            r_ = F.infer_tmix_linear_forward_varlen(xr, Wr)
+            k_ = F.infer_tmix_linear_forward_varlen(xk, Wk)
+            v_ = F.infer_tmix_linear_forward_varlen(xv, Wv)
+            fw, fa, fg, fv = F.infer_tmix_lowrank_wagv_in_forward_varlen(xw, xa, xg, xv, w1["w"], w1["a"], w1["g"], w1["v"])
+            w_, a12, g_, vres = F.infer_tmix_lowrank_vres_forward_varlen(fw, fa, fg, fv, w2["w"], w2["a"], w2["g"], w2["v"],
+                                                                        v_, v_first, v0)
+            kk_, nkk, kka = F.infer_tmix_kk_a_gate_forward_varlen(k_, k_k, a0, a12, k_a)
+            sh = (M, Hh, D)
+            y = F.infer_recurrent_fp32io16_forward_varlen(r_.view(sh), w_.view(sh), kk_.view(sh), vres.view(sh),
+                                                          nkk.view(sh), kka.view(sh), state_pool=spool, cu_seqlens=cu,
+                                                          state_indices=idx, validated_metadata=ticket, max_seqlen=1)
+            z = F.infer_tmix_lnx_rkvres_xg_forward_varlen(y.view(M, C), r_, kk_, vres, r_k, lnw, lnb, g_)
+            return F.infer_tmix_linear_forward_varlen(z, Wo)
+
+        sec = _time_cuda(layer, warmup=3, iters=20)
+        entry = {"us_per_layer": sec * 1e6, "gpu_launches_per_layer": 11}
+        if M <= 7:
+            entry["weight_hbm_frac"] = weight_bytes / sec / hbm
+        else:
+            entry["tensor_frac_of_bf16_peak"] = 2 * M * (4 * C * C + 2 * C * sum(ranks.values())) / sec / bf16
+        tmix[f"M={M}"] = entry
+    out["tmix_layer_C2048"] = tmix
+    return out
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -296,6 +412,11 @@ def run_b200(args):
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if world == 1 and not args.kernel_only and not args.no_extras:
+            try:
+                line["extras"] = _extras(dev)
+            except Exception as exc:  # the headline line must survive a failure of the secondary workloads
+                line["extras"] = {"error": f"{type(exc).__name__}: {exc}"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -307,6 +428,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads (prefill, training, TMix)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for profiler runs)")
     args = ap.parse_args()
