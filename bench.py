@@ -43,7 +43,7 @@ BYTES_PER_UNIT = 2 * D * D * 4 + 7 * D * 2
 BYTES_PER_LAUNCH = B * H * BYTES_PER_UNIT
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch at this size, from the ncu
 # capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 221_950_000
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 220_650_000
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -123,6 +123,8 @@ class CpuPort:
         from oracle import wkv7_oracle
 
         wkv7_oracle.build()
+        # launchers such as torchrun export OMP_NUM_THREADS=1: the CPU arm is meant to use every core it may run on
+        wkv7_oracle.set_num_threads(len(os.sched_getaffinity(0)))
         self.oracle = wkv7_oracle
         self.cu, self.idx = synthetic.equal_length_metadata(B, 1)
         self.pool = synthetic.state_pool(B, H, D, seed=1).numpy()
@@ -402,7 +404,7 @@ def run_b200(args):
                        "l2": "no flush: per-launch working set (134 MB state + 7 MB tokens) exceeds the 126 MB L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                         "peak_source": f"of {peak_kind}", "kernel": "wkv7_recurrent_d64_kernel",
+                         "peak_source": f"of {peak_kind}", "kernel": "wkv7_decode_pipelined_kernel",
                          "algorithmic_bytes_per_launch": BYTES_PER_LAUNCH, "us_per_launch": launch_s * 1e6},
             "e2e": {"value": e2e_value, "unit": "tokens/s",
                     "h2d_bytes_per_step": 6 * B * H * D * 2 * DECODE_STEPS_PER_STEP,

@@ -252,7 +252,7 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
         const float4 gl = ld4(smem, kOffSC + kc * kCS64P + 63 * 16);
         float4 sc = ld4(smem, oscale + kc * kCS64P);
         if (first_row) sc = make_float4(1.f, 1.f, 1.f, 1.f);
-        const float4 inv = make_float4(__frcp_rn(g.x), __frcp_rn(g.y), __frcp_rn(g.z), __frcp_rn(g.w));
+        const float4 inv = make_float4(rcp_approx(g.x), rcp_approx(g.y), rcp_approx(g.z), rcp_approx(g.w));
         const float2 p01 = IO::unpack(u0.x), p23 = IO::unpack(u0.y);
         const float2 q01 = IO::unpack(u1.x), q23 = IO::unpack(u1.y);
         const float2 v01 = IO::unpack(u2.x), v23 = IO::unpack(u2.y);
@@ -319,56 +319,82 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
       issue_mma(tmem + 128, sbase + kOffX2, kCS128, sbase + kOffVT, kCS64P, 64, false);
       umma::mma_commit(&mbar[1]);
     }
-    if (warp >= 8) {
-      // T = (I - A_ab)^-1 on the CUDA cores in fp32, 16 rows at a time (warps 8..15):
-      //   T[t][j] = [t == j] + sum_{s<t} A_ab[t][s] T[s][j].
-      // Column j is owned by four lanes of one warp (lane, +8, +16, +24).  The sum over the rows above the
-      // current block is split between them (groups of four rows, round robin) and joined by two shuffles;
-      // the triangular part inside the block is right-looking, so its dependent chain is one multiply-add
-      // per row.  Finished rows live (unrounded) in the TT tile at (row s, col j).
-      const int j = (warp - 8) * 8 + (lane & 7), helper = lane >> 3;
-      const uint32_t oT = kOffTT + uint32_t(j >> 2) * kCS64P + uint32_t(j & 3) * 4;
-#pragma unroll 1
-      for (int blk = 0; blk < 4; ++blk) {
-        const uint32_t arow = kOffSC + uint32_t(16 * blk) * kAabRow;
+    {
+      // T = (I - A_ab)^-1 on the CUDA cores in fp32, by 16 x 16 blocks (all 512 threads).  A_ab is strictly lower
+      // triangular, so T is unit lower triangular and
+      //   T_ii = (I - A_ii)^-1                                   (16 right-looking steps, one thread per column)
+      //   T_ib = T_ii * sum_{k=b..i-1} A_ik T_kb   for i > b      (small products, one block anti-diagonal at a time)
+      // T is built unrounded in the TT tile (row t, col s); the inner sums W live in the still unused Z^T half of AZ.
+      const auto tt_off = [](int row, int col) { return kOffTT + uint32_t(col >> 2) * kCS64P + uint32_t(row) * 16 + uint32_t(col & 3) * 4; };
+      const auto w_off = [](int row, int col) { return kOffAZ + uint32_t(col >> 2) * kCS128P + 1024 + uint32_t(row) * 16 + uint32_t(col & 3) * 4; };
+      if (tid < 64) {
+        const int blk = tid >> 4, jj = tid & 15;
+        const uint32_t ablk = kOffSC + uint32_t(16 * blk) * kAabRow + uint32_t(16 * blk) * 4;
         float acc[16];
 #pragma unroll
         for (int rr = 0; rr < 16; ++rr) acc[rr] = 0.f;
-#pragma unroll 1
-        for (int s4 = helper; s4 < 4 * blk; s4 += 4) {
-          const float c0v = *reinterpret_cast<const float*>(smem + oT + (4 * s4 + 0) * 16);
-          const float c1v = *reinterpret_cast<const float*>(smem + oT + (4 * s4 + 1) * 16);
-          const float c2v = *reinterpret_cast<const float*>(smem + oT + (4 * s4 + 2) * 16);
-          const float c3v = *reinterpret_cast<const float*>(smem + oT + (4 * s4 + 3) * 16);
-#pragma unroll
-          for (int rr = 0; rr < 16; ++rr) {
-            const float4 a4 = ld4(smem, arow + rr * kAabRow + s4 * 16);
-            acc[rr] = fmaf(a4.x, c0v, fmaf(a4.y, c1v, fmaf(a4.z, c2v, fmaf(a4.w, c3v, acc[rr]))));
-          }
-        }
-#pragma unroll
-        for (int rr = 0; rr < 16; ++rr) {
-          acc[rr] += __shfl_xor_sync(0xffffffffu, acc[rr], 8);
-          acc[rr] += __shfl_xor_sync(0xffffffffu, acc[rr], 16);
-        }
-        const uint32_t ablk = arow + uint32_t(16 * blk) * 4;
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
-          const float xq = acc[q] + ((16 * blk + q == j) ? 1.f : 0.f);
-          if (helper == 0) st1(smem, oT + uint32_t(16 * blk + q) * 16, xq);
+          const float xq = acc[q] + (q == jj ? 1.f : 0.f);
+          st1(smem, tt_off(16 * blk + q, 16 * blk + jj), xq);
 #pragma unroll
           for (int rr = q + 1; rr < 16; ++rr)
             acc[rr] = fmaf(*reinterpret_cast<const float*>(smem + ablk + rr * kAabRow + q * 4), xq, acc[rr]);
         }
-        __syncwarp();
+      } else {
+        // zero the six blocks above the diagonal (1536 elements over 448 threads)
+        for (int e = tid - 64; e < 6 * 256; e += kBuildThreads - 64) {
+          const int ub = e >> 8, rr = (e >> 4) & 15, cc = e & 15;
+          // ub -> (row block, col block) with col block > row block: (0,1)(0,2)(0,3)(1,2)(1,3)(2,3)
+          const int rb = ub < 3 ? 0 : (ub < 5 ? 1 : 2);
+          const int cb = ub < 3 ? ub + 1 : (ub < 5 ? ub - 1 : 3);
+          st1(smem, tt_off(16 * rb + rr, 16 * cb + cc), 0.f);
+        }
       }
-      // the tensor core truncates: round the finished column to tf32 (the four lanes share the rows)
-#pragma unroll 4
-      for (int s = helper; s < 64; s += 4) {
-        const uint32_t o = oT + s * 16;
-        st1(smem, o, umma::to_tf32(*reinterpret_cast<const float*>(smem + o)));
+      __syncthreads();
+#pragma unroll 1
+      for (int dg = 1; dg < 4; ++dg) {
+        const int nblk = 4 - dg;  // blocks (i, b) = (b + dg, b), b = 0 .. nblk-1
+        // W_ib = sum_{k=b..i-1} A_ik T_kb
+        for (int e = tid; e < nblk * 256; e += kBuildThreads) {
+          const int bb = e >> 8, rr = (e >> 4) & 15, cc = e & 15;
+          const int ib = bb + dg;
+          const uint32_t arow = kOffSC + uint32_t(16 * ib + rr) * kAabRow;
+          float acc = 0.f;
+          for (int kq = 4 * bb; kq < 4 * ib; ++kq) {  // groups of four columns of A / rows of T
+            const float4 a4 = ld4(smem, arow + kq * 16);
+            acc = fmaf(a4.x, *reinterpret_cast<const float*>(smem + tt_off(4 * kq + 0, 16 * bb + cc)), acc);
+            acc = fmaf(a4.y, *reinterpret_cast<const float*>(smem + tt_off(4 * kq + 1, 16 * bb + cc)), acc);
+            acc = fmaf(a4.z, *reinterpret_cast<const float*>(smem + tt_off(4 * kq + 2, 16 * bb + cc)), acc);
+            acc = fmaf(a4.w, *reinterpret_cast<const float*>(smem + tt_off(4 * kq + 3, 16 * bb + cc)), acc);
+          }
+          st1(smem, w_off(16 * ib + rr, 16 * bb + cc), acc);
+        }
+        __syncthreads();
+        // T_ib = T_ii W_ib
+        for (int e = tid; e < nblk * 256; e += kBuildThreads) {
+          const int bb = e >> 8, rr = (e >> 4) & 15, cc = e & 15;
+          const int ib = bb + dg;
+          float acc = 0.f;
+#pragma unroll
+          for (int q = 0; q < 16; ++q)
+            acc = fmaf(*reinterpret_cast<const float*>(smem + tt_off(16 * ib + rr, 16 * ib + q)),
+                       *reinterpret_cast<const float*>(smem + w_off(16 * ib + q, 16 * bb + cc)), acc);
+          st1(smem, tt_off(16 * ib + rr, 16 * bb + cc), acc);
+        }
+        __syncthreads();
       }
-    } else if (m < 64 && colq < 2) {
+      // the tensor core truncates: round T to tf32 (eight elements per thread)
+      {
+        const int row = tid & 63, c0 = (tid >> 6) * 8;
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          const uint32_t o = tt_off(row, c0 + cc);
+          st1(smem, o, umma::to_tf32(*reinterpret_cast<const float*>(smem + o)));
+        }
+      }
+    }
+    if (m < 64 && colq < 2) {
       // warps 0, 1, 4, 5: Z^T -> AZ rows 64 + v, col t (32 value columns per warp)
       ok = umma::mbar_wait(&mbar[1], parity) && ok;
       umma::fence_after_sync();
@@ -421,7 +447,6 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     ok = umma::mbar_wait(&mbar[3], parity) && ok;
     umma::fence_after_sync();
     FRWKV_PHASE(9);
-    if (ok && item + (int)gridDim.x < num_items) stage_item(item + gridDim.x);
     if (ok) {
       unsigned char* ws = workspace + (size_t)item * (2 * kWsTile);
       uint32_t u[32];
@@ -454,6 +479,8 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
       }
     }
     FRWKV_PHASE(10);
+    if (ok && item + (int)gridDim.x < num_items) stage_item(item + gridDim.x);
+    FRWKV_PHASE(11);
     // every thread is done with this item's shared memory and accumulators before the next item starts
     umma::fence_before_sync();
     ok = __syncthreads_and(ok) != 0;
