@@ -447,6 +447,7 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     ok = umma::mbar_wait(&mbar[3], parity) && ok;
     umma::fence_after_sync();
     FRWKV_PHASE(9);
+    if (ok && item + (int)gridDim.x < num_items) stage_item(item + gridDim.x);
     if (ok) {
       unsigned char* ws = workspace + (size_t)item * (2 * kWsTile);
       uint32_t u[32];
@@ -479,8 +480,6 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
       }
     }
     FRWKV_PHASE(10);
-    if (ok && item + (int)gridDim.x < num_items) stage_item(item + gridDim.x);
-    FRWKV_PHASE(11);
     // every thread is done with this item's shared memory and accumulators before the next item starts
     umma::fence_before_sync();
     ok = __syncthreads_and(ok) != 0;
