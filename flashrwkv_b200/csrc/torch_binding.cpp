@@ -117,6 +117,8 @@ class MetadataTicket {
                 "validated_metadata stream mismatch; prepare and consume the ticket on the same CUDA stream");
   }
 
+  // Number of launches made with this ticket so far; decode launches alternate their traversal order with it.
+  int next_launch_parity() { return static_cast<int>(launches_++ & 1); }
   const torch::Tensor& cu_snapshot() const { return prepared_.cu; }
   const torch::Tensor& idx_snapshot() const { return prepared_.idx; }
   const torch::Tensor& status() const { return prepared_.status; }
@@ -132,6 +134,7 @@ class MetadataTicket {
   int64_t total_tokens_, pool_size_, max_seqlen_;
   c10::Device device_;
   cudaStream_t stream_;
+  uint64_t launches_ = 0;
 };
 
 std::shared_ptr<MetadataTicket> prepare_recurrent_metadata(torch::Tensor cu, torch::Tensor idx,
@@ -247,8 +250,10 @@ void recurrent_fp32_from_decay_logits(torch::Tensor cu, torch::Tensor idx, torch
   }
   const c10::cuda::CUDAGuard guard(state.device());
   torch::Tensor launch_cu, launch_idx, status;
+  int flags = 0;
   if (ticket) {
     ticket->check_compatible(cu, idx, r.size(0), state.size(0), max_seqlen);
+    flags = ticket->next_launch_parity() ? FRWKV_RECURRENT_REVERSE_ORDER : 0;
     launch_cu = ticket->cu_snapshot();
     launch_idx = ticket->idx_snapshot();
     status = ticket->status();
@@ -259,14 +264,14 @@ void recurrent_fp32_from_decay_logits(torch::Tensor cu, torch::Tensor idx, torch
     launch_idx = std::move(prepared.idx);
     status = std::move(prepared.status);
   }
-  check_rc(frwkv_wkv7_recurrent_fp32io16_forward_varlen(
+  check_rc(frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex(
       launch_cu.data_ptr<int>(), launch_idx.data_ptr<int>(), status.data_ptr<int>(), state.data_ptr<float>(),
       r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
       decay_bias.has_value() ? decay_bias->data_ptr() : nullptr, output.data_ptr(),
       output_fp32.has_value() ? output_fp32->data_ptr<float>() : nullptr, static_cast<int>(r.size(0)),
       static_cast<int>(dims.B), static_cast<int>(dims.H), static_cast<int>(dims.D),
       static_cast<int>(std::min<int64_t>(std::max<int64_t>(max_seqlen, -1), std::numeric_limits<int>::max())),
-      io_dtype_of(r), static_cast<float>(scale), current_stream(state)));
+      io_dtype_of(r), static_cast<float>(scale), flags, current_stream(state)));
 }
 
 // ---- chunked forward ---------------------------------------------------------------------------------

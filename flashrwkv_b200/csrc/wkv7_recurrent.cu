@@ -337,10 +337,16 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_decode_pipelined_kerne
     const io_t* __restrict__ r_ptr, const io_t* __restrict__ w_ptr, const io_t* __restrict__ k_ptr,
     const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr, const io_t* __restrict__ b_ptr,
     const io_t* __restrict__ bias_ptr, io_t* __restrict__ y_ptr, float* __restrict__ y32_ptr, int num_tiles,
-    int num_heads, long long output_elements, float scale, int* __restrict__ error_flag) {
+    int num_heads, long long output_elements, float scale, int reverse, int* __restrict__ error_flag) {
   using IO = Io16<io_t>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full_bar[kStages], done_bar[kStages], empty_bar[kStages];
+  // i-th tile of this CTA.  `reverse` walks the pool from the other end: a caller that alternates it between
+  // consecutive decode steps finds the tiles it touched last (still in the 126 MB L2) first.
+  const auto tile_of = [&](int i) {
+    const int fwd = blockIdx.x + i * gridDim.x;
+    return reverse ? num_tiles - 1 - fwd : fwd;
+  };
   if (metadata_status != nullptr && metadata_status[0] != 0) {
     const io_t nan16 = IO::store(quiet_nan());
     for (long long i = (long long)blockIdx.x * kDecodeThreads + threadIdx.x; i < output_elements;
@@ -369,7 +375,7 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_decode_pipelined_kerne
         const int st = i % kStages;
         if (i >= kStages) ok = umma::mbar_wait(&empty_bar[st], ((i / kStages) - 1) & 1);
         if (!ok) break;
-        const int tile = blockIdx.x + i * gridDim.x;
+        const int tile = tile_of(i);
         const int seq = tile / num_heads, head = tile % num_heads;
         const float* src = state_pool + ((long long)state_indices[seq] * num_heads + head) * (kD * kD);
         const long long tb = ((long long)seq * num_heads + head) * kD;  // one token per sequence: token == sequence
@@ -390,7 +396,7 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_decode_pipelined_kerne
         const int st = i % kStages;
         ok = umma::mbar_wait(&done_bar[st], (i / kStages) & 1);
         if (!ok) break;
-        const int tile = blockIdx.x + i * gridDim.x;
+        const int tile = tile_of(i);
         const int seq = tile / num_heads, head = tile % num_heads;
         float* dst = state_pool + ((long long)state_indices[seq] * num_heads + head) * (kD * kD);
         bulk_s2g(dst, smem + st * kStageBytes, kTileBytes);
@@ -409,7 +415,7 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_decode_pipelined_kerne
     const int row0 = kg * 16, col0 = vhalf * 32 + vq * 4;
     for (int i = pair; i < my_tiles && ok; i += kConsumerPairs) {
       const int st = i % kStages;
-      const int tile = blockIdx.x + i * gridDim.x;
+      const int tile = tile_of(i);
       const int seq = tile / num_heads, head = tile % num_heads;
       ok = umma::mbar_wait(&full_bar[st], (i / kStages) & 1);
       if (!ok) break;
@@ -450,7 +456,7 @@ int launch(const int* cu, const int* idx, const int* status, float* state, const
 template <typename io_t>
 int launch_decode(const int* idx, const int* status, float* state, const void* r, const void* w, const void* k,
                   const void* v, const void* a, const void* b, const void* bias, void* y, float* y32,
-                  int num_sequences, int num_heads, float scale, cudaStream_t stream) {
+                  int num_sequences, int num_heads, float scale, int reverse, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(wkv7_decode_pipelined_kernel<io_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kDecodeSmem);
   if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "wkv7_recurrent: %s", cudaGetErrorString(e));
@@ -463,7 +469,7 @@ int launch_decode(const int* idx, const int* status, float* state, const void* r
       idx, status, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w), static_cast<const io_t*>(k),
       static_cast<const io_t*>(v), static_cast<const io_t*>(a), static_cast<const io_t*>(b),
       static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, tiles, num_heads,
-      (long long)num_sequences * num_heads * kD, scale, nullptr);
+      (long long)num_sequences * num_heads * kD, scale, reverse, nullptr);
   return check_launch("wkv7_decode_pipelined_kernel");
 }
 
@@ -490,6 +496,18 @@ extern "C" int frwkv_wkv7_recurrent_fp32io16_forward_varlen(
     const void* a, const void* b, const void* decay_bias, void* y, float* y_fp32,
     int total_tokens, int num_sequences, int num_heads, int head_size, int max_seqlen,
     int io_dtype, float scale, frwkv_stream_t stream) {
+  return frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex(cu_seqlens, state_indices, metadata_status, state_pool, r,
+                                                         decay_logits, k, v, a, b, decay_bias, y, y_fp32, total_tokens,
+                                                         num_sequences, num_heads, head_size, max_seqlen, io_dtype,
+                                                         scale, 0, stream);
+}
+
+extern "C" int frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex(
+    const int32_t* cu_seqlens, const int32_t* state_indices, const int32_t* metadata_status,
+    float* state_pool, const void* r, const void* decay_logits, const void* k, const void* v,
+    const void* a, const void* b, const void* decay_bias, void* y, float* y_fp32,
+    int total_tokens, int num_sequences, int num_heads, int head_size, int max_seqlen,
+    int io_dtype, float scale, int flags, frwkv_stream_t stream) {
   using namespace frwkv;
   clear_error();
   FRWKV_REQUIRE(cu_seqlens && state_indices && state_pool && r && decay_logits && k && v && a && b && y,
@@ -509,10 +527,10 @@ extern "C" int frwkv_wkv7_recurrent_fp32io16_forward_varlen(
                       (long long)num_sequences * num_heads >= 1024 && (long long)num_sequences * num_heads <= 0x7fffffffLL;
   if (decode && io_dtype == FRWKV_DTYPE_BF16)
     return launch_decode<__nv_bfloat16>(state_indices, metadata_status, state_pool, r, decay_logits, k, v, a, b,
-                                        decay_bias, y, y_fp32, num_sequences, num_heads, scale, s);
+                                        decay_bias, y, y_fp32, num_sequences, num_heads, scale, flags & 1, s);
   if (decode && io_dtype == FRWKV_DTYPE_FP16)
     return launch_decode<__half>(state_indices, metadata_status, state_pool, r, decay_logits, k, v, a, b, decay_bias,
-                                 y, y_fp32, num_sequences, num_heads, scale, s);
+                                 y, y_fp32, num_sequences, num_heads, scale, flags & 1, s);
   if (io_dtype == FRWKV_DTYPE_BF16) {
     return launch<__nv_bfloat16>(cu_seqlens, state_indices, metadata_status, state_pool, r, decay_logits, k,
                                  v, a, b, decay_bias, y, y_fp32, total_tokens, num_sequences, num_heads,

@@ -84,6 +84,17 @@ int frwkv_wkv7_recurrent_fp32io16_forward_varlen(
     int total_tokens, int num_sequences, int num_heads, int head_size, int max_seqlen,
     int io_dtype, float scale, frwkv_stream_t stream);
 
+/* Same, with flags: bit 0 = FRWKV_RECURRENT_REVERSE_ORDER, walk the (sequence, head) tiles from the far end of the
+ * batch.  The result does not depend on it.  A decode loop that alternates the bit between consecutive steps finds
+ * the state tiles it wrote last still in L2 (126 MB on B200) when the next step starts with them. */
+enum { FRWKV_RECURRENT_REVERSE_ORDER = 1 };
+int frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex(
+    const int32_t* cu_seqlens, const int32_t* state_indices, const int32_t* metadata_status,
+    float* state_pool, const void* r, const void* decay_logits, const void* k, const void* v,
+    const void* a, const void* b, const void* decay_bias, void* y, float* y_fp32,
+    int total_tokens, int num_sequences, int num_heads, int head_size, int max_seqlen,
+    int io_dtype, float scale, int flags, frwkv_stream_t stream);
+
 /*
  * Chunked WKV7 forward on the tensor cores: same recurrence and tensors as
  * frwkv_wkv7_recurrent_fp32io16_forward_varlen, evaluated chunk by chunk (chunk length <= 64).
