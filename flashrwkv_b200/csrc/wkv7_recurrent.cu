@@ -226,15 +226,15 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
 //   warp 0 (one lane)  : loader  - waits for a free stage, cp.async.bulk global -> shared, completion on full[stage]
 //   warp 1 (one lane)  : storer  - waits for done[stage] (both halves updated), cp.async.bulk shared -> global,
 //                                  and hands a stage back (empty[stage]) once its store has finished reading it
-//   warps 2..9         : four pairs of consumer warps; a pair owns one tile at a time, one warp per half, and runs
+//   warps 2..15        : seven pairs of consumer warps; a pair owns one tile at a time, one warp per half, and runs
 //                        the same per-token step as the register kernel on float4s read from the staged tile
 // CTA b owns the (sequence, head) tiles b, b + gridDim.x, ...; its i-th tile uses stage i % kStages.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kStages = 12;
+constexpr int kStages = 13;
 constexpr int kTileBytes = kD * kD * 4;
 constexpr int kTokBytes = 6 * kD * 2;                 // r, w, k, v, a, b rows of one (token, head)
 constexpr int kStageBytes = kTileBytes + kTokBytes;   // 17,152
-constexpr int kConsumerPairs = 6;
+constexpr int kConsumerPairs = 7;
 constexpr int kDecodeThreads = 32 * (2 + 2 * kConsumerPairs);
 constexpr int kDecodeSmem = kStages * kStageBytes;
 
@@ -260,36 +260,35 @@ __device__ __forceinline__ StepOut tile_step_smem(float* __restrict__ tbase, con
                                                   const io_t* __restrict__ bias_ptr, int head, int row0, int col0,
                                                   float scale) {
   using IO = Io16<io_t>;
-  uint32_t rr[8], ww[8], kk[8], aa[8], bb[8];
-  lds16(tok + 0 * 128 + row0 * 2, rr);
-  lds16(tok + 1 * 128 + row0 * 2, ww);
-  lds16(tok + 2 * 128 + row0 * 2, kk);
-  lds16(tok + 4 * 128 + row0 * 2, aa);
-  lds16(tok + 5 * 128 + row0 * 2, bb);
-  const uint2 vraw = *reinterpret_cast<const uint2*>(tok + 3 * 128 + col0 * 2);
+  const int lane = threadIdx.x & 31;
+  // retention of this lane group's 16 key rows: each of the 8 lanes that share the rows computes two of them and
+  // the group exchanges them by shuffle (the transform is the expensive part of the step)
   float wv[16];
-  if (bias_ptr != nullptr) {
-    uint32_t bs[8];
-    load16(bias_ptr + head * kD + row0, bs);
-#pragma unroll
-    for (int p = 0; p < 8; ++p) {
-      const float2 x = IO::unpack(ww[p]), bx = IO::unpack(bs[p]);
-      wv[2 * p] = retention(x.x + bx.x);
-      wv[2 * p + 1] = retention(x.y + bx.y);
+  {
+    const int vq = lane & 7;
+    float2 x = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 1 * 128 + (row0 + 2 * vq) * 2));
+    if (bias_ptr != nullptr) {
+      const float2 bx = IO::unpack(__ldg(reinterpret_cast<const uint32_t*>(bias_ptr + head * kD + row0 + 2 * vq)));
+      x.x += bx.x;
+      x.y += bx.y;
     }
-  } else {
+    const float w_lo = retention(x.x), w_hi = retention(x.y);
 #pragma unroll
     for (int p = 0; p < 8; ++p) {
-      const float2 x = IO::unpack(ww[p]);
-      wv[2 * p] = retention(x.x);
-      wv[2 * p + 1] = retention(x.y);
+      wv[2 * p] = __shfl_sync(0xffffffffu, w_lo, (lane & 24) + p);
+      wv[2 * p + 1] = __shfl_sync(0xffffffffu, w_hi, (lane & 24) + p);
     }
   }
+  uint32_t rr[8], aa[8];
+  lds16(tok + 0 * 128 + row0 * 2, rr);
+  lds16(tok + 4 * 128 + row0 * 2, aa);
+  const uint2 vraw = *reinterpret_cast<const uint2*>(tok + 3 * 128 + col0 * 2);
   float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f, y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f, br = 0.f, kr = 0.f;
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
     const float2 a2 = IO::unpack(aa[p]), r2 = IO::unpack(rr[p]);
-    const float2 b2 = IO::unpack(bb[p]), k2 = IO::unpack(kk[p]);
+    const float2 b2 = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 5 * 128 + (row0 + 2 * p) * 2));
+    const float2 k2 = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 2 * 128 + (row0 + 2 * p) * 2));
     br = fmaf(b2.x, r2.x, fmaf(b2.y, r2.y, br));
     kr = fmaf(k2.x, r2.x, fmaf(k2.y, r2.y, kr));
     const float4 q0 = *reinterpret_cast<const float4*>(tbase + (2 * p) * kD);
@@ -311,7 +310,8 @@ __device__ __forceinline__ StepOut tile_step_smem(float* __restrict__ tbase, con
   const float2 v01 = IO::unpack(vraw.x), v23 = IO::unpack(vraw.y);
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
-    const float2 b2 = IO::unpack(bb[p]), k2 = IO::unpack(kk[p]);
+    const float2 b2 = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 5 * 128 + (row0 + 2 * p) * 2));
+    const float2 k2 = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 2 * 128 + (row0 + 2 * p) * 2));
     float4 q0 = *reinterpret_cast<const float4*>(tbase + (2 * p) * kD);
     float4 q1 = *reinterpret_cast<const float4*>(tbase + (2 * p + 1) * kD);
     const float w0 = wv[2 * p], w1 = wv[2 * p + 1];
@@ -401,12 +401,12 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_decode_pipelined_kerne
         float* dst = state_pool + ((long long)state_indices[seq] * num_heads + head) * (kD * kD);
         bulk_s2g(dst, smem + st * kStageBytes, kTileBytes);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        // at most three stores may still be reading shared memory: the stage of tile i-3 is free again
-        asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
-        if (i >= 3) mbar_arrive(&empty_bar[(i - 3) % kStages]);
+        // at most one store may still be reading shared memory: the stage of tile i-1 is free again
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        if (i >= 1) mbar_arrive(&empty_bar[(i - 1) % kStages]);
       }
       asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-      for (int i = (my_tiles > 3 ? my_tiles - 3 : 0); i < my_tiles && ok; ++i) mbar_arrive(&empty_bar[i % kStages]);
+      if (my_tiles > 0 && ok) mbar_arrive(&empty_bar[(my_tiles - 1) % kStages]);
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all state writes are complete before exit
     }
   } else {
