@@ -298,11 +298,23 @@ def _extras(dev):
             return F.infer_tmix_linear_forward_varlen(z, Wo)
 
         sec = _time_cuda(layer, warmup=3, iters=20)
-        entry = {"us_per_layer": sec * 1e6, "gpu_launches_per_layer": 11}
+        # the same 11 launches replayed from a CUDA graph: device time without the per-call host work
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            gticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=M, state_pool_size=M, max_seqlen=1)
+            ticket = gticket
+            layer()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                layer()
+            gsec = _time_cuda(graph.replay, warmup=3, iters=50)
+        torch.cuda.current_stream().wait_stream(side)
+        entry = {"us_per_layer": sec * 1e6, "us_per_layer_cuda_graph": gsec * 1e6, "gpu_launches_per_layer": 11}
         if M <= 7:
-            entry["weight_hbm_frac"] = weight_bytes / sec / hbm
+            entry["weight_hbm_frac_cuda_graph"] = weight_bytes / gsec / hbm
         else:
-            entry["tensor_frac_of_bf16_peak"] = 2 * M * (4 * C * C + 2 * C * sum(ranks.values())) / sec / bf16
+            entry["tensor_frac_of_bf16_peak_cuda_graph"] = 2 * M * (4 * C * C + 2 * C * sum(ranks.values())) / gsec / bf16
         tmix[f"M={M}"] = entry
     out["tmix_layer_C2048"] = tmix
     return out

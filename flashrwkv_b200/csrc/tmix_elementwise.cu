@@ -180,6 +180,18 @@ __global__ void vres_gate_kernel(const io_t* __restrict__ v, const io_t* __restr
   }
 }
 
+template <typename io_t>
+__global__ void act_kernel(const io_t* __restrict__ x, io_t* __restrict__ out, long long vec_total, int act) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < vec_total;
+       i += (long long)gridDim.x * blockDim.x) {
+    float a[8];
+    unpack8<io_t>(reinterpret_cast<const uint4*>(x)[i], a);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = act == 1 ? tanhf(a[e]) : sigmoidf_(a[e]);
+    reinterpret_cast<uint4*>(out)[i] = pack8<io_t>(a);
+  }
+}
+
 }  // namespace
 }  // namespace frwkv
 
@@ -290,5 +302,22 @@ extern "C" int frwkv_tmix_vres_gate_forward_varlen(const void* v, const void* v_
         static_cast<const io_t*>(v), static_cast<const io_t*>(v_first), static_cast<const io_t*>(v0),
         static_cast<const io_t*>(v12), static_cast<io_t*>(out), vec_total, channels / 8);
     return check_launch("vres_gate_kernel");
+  })
+}
+
+extern "C" int frwkv_tmix_act_forward(const void* x, void* out, long long elements, int act, int io_dtype,
+                                      frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(x && out, "tmix_act: null pointer argument");
+  FRWKV_REQUIRE(elements > 0 && elements % 8 == 0, "tmix_act: element count must be a positive multiple of 8");
+  FRWKV_REQUIRE(act == 1 || act == 2, "tmix_act: act must be 1 (tanh) or 2 (sigmoid)");
+  const long long vec_total = elements / 8;
+  long long blocks = (vec_total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  FRWKV_DISPATCH_IO(io_dtype, "tmix_act", {
+    act_kernel<io_t><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const io_t*>(x), static_cast<io_t*>(out), vec_total, act);
+    return check_launch("act_kernel");
   })
 }

@@ -502,6 +502,16 @@ torch::Tensor tmix_vres_gate_forward_varlen(torch::Tensor v, torch::Tensor v_fir
   return out;
 }
 
+torch::Tensor tmix_act_forward(torch::Tensor x, int64_t act) {
+  check_io16(x, "x", x);
+  TORCH_CHECK(x.numel() > 0 && x.numel() % 8 == 0, "x must have a positive element count that is a multiple of 8");
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto out = torch::empty_like(x);
+  check_rc(frwkv_tmix_act_forward(x.data_ptr(), out.data_ptr(), x.numel(), static_cast<int>(act), io_dtype_of(x),
+                                  current_stream(x)));
+  return out;
+}
+
 // y_i = act_i(x_i) @ weight_i^T for up to four projections sharing the row count; weights in the original [N,K]
 // layout.  `vres` = (v, v_first, v0) applies the value-residual epilogue to the LAST projection.
 std::vector<torch::Tensor> tmix_linear_grouped(std::vector<torch::Tensor> xs, std::vector<torch::Tensor> weights,
@@ -662,6 +672,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("state_dot_a"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),
         py::arg("b"), py::arg("grad_output") = py::none(), py::arg("grad_final_state") = py::none(),
         py::arg("scale") = 1.0);
+  m.def("tmix_act_forward", &tmix_act_forward, py::arg("x"), py::arg("act"));
   m.def("tmix_linear_grouped", &tmix_linear_grouped, py::arg("xs"), py::arg("weights"), py::arg("acts"),
         py::arg("vres") = py::none());
 }

@@ -92,6 +92,23 @@ def infer_tmix_linear_t_vres_forward_varlen(x, weight_t, v, v_first, v0):
     return _grouped([x], [w], ["none"], (v, v_first, v0))[0]
 
 
+def _act(x, code):
+    _check_x(x)
+    if x.numel() % 2:
+        raise ValueError("x must have an even element count")
+    if x.numel() % 8:
+        raise ValueError("this build needs an element count that is a multiple of 8")
+    return extension().tmix_act_forward(x, code)
+
+
+def infer_tmix_linear_act_tanh_forward_varlen(x):
+    return _act(x, 1)
+
+
+def infer_tmix_linear_act_sigmoid_forward_varlen(x):
+    return _act(x, 2)
+
+
 # ---- single low-rank projections ----------------------------------------------------------------------------
 def _rank(x, weight, weight_t, act, input_projection):
     _check_x(x)

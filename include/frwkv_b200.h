@@ -204,6 +204,10 @@ int frwkv_tmix_lnx_rkvres_xg_forward_varlen(const void* x, const void* r, const 
 int frwkv_tmix_vres_gate_forward_varlen(const void* v, const void* v_first, const void* v0, const void* v12, void* out,
                                         long long total_rows, int channels, int io_dtype, frwkv_stream_t stream);
 
+/* Elementwise tanh (act = 1) or sigmoid (act = 2) of a 16-bit tensor with `elements` (multiple of 8) values.
+ * Replaces linear_act_tanh / linear_act_sigmoid (csrc/sm120/tmix/linear/infer_fp16_forward_varlen.cu:1235-1373). */
+int frwkv_tmix_act_forward(const void* x, void* out, long long elements, int act, int io_dtype, frwkv_stream_t stream);
+
 /*
  * Grouped TMix projections: for each of 1..4 problems, y[m][n] = act(x)[m][k] * weight[n][k]^T, optionally followed by
  * the value-residual epilogue  y = v + (v_first - v) * sigmoid(v0 + y).  All problems share the row count m.

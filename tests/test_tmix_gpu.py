@@ -154,3 +154,12 @@ def test_golden_lowrank_pair():
     assert rel_rmse(rank.float().cpu(), g["rank"].float()) <= TOL[torch.float16]
     out = F.infer_tmix_linear_rank_out_tanh_forward_varlen(g["rank"].cuda(), weight_t=g["w2"].cuda())
     assert rel_rmse(out.float().cpu(), g["out_tanh"]) <= TOL[torch.float16]
+
+
+def test_elementwise_activations():
+    import flashrwkv_b200 as F
+
+    x = torch.randn(37, 96, generator=torch.Generator().manual_seed(1)).half()
+    assert rel_rmse(F.infer_tmix_linear_act_tanh_forward_varlen(x.cuda()).float().cpu(), torch.tanh(x.float())) <= 1e-3
+    assert rel_rmse(F.infer_tmix_linear_act_sigmoid_forward_varlen(x.cuda()).float().cpu(),
+                    torch.sigmoid(x.float())) <= 1e-3
