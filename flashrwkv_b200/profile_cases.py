@@ -1,0 +1,82 @@
+"""Small, self-contained workloads for profiler captures: `python -m flashrwkv_b200.profile_cases <case>`.
+
+Each case holds well under a few GB on the device, uses inputs larger than the 126 MB L2 where DRAM figures
+matter, runs a handful of launches and exits, so that an `ncu` capture of one of its kernels ends by itself.
+
+  chunk   chunked forward (build + scan): B=2, T=4096, H=32  (4096 (chunk, head) items)
+  train   StateTune forward + backward: B=2, T=2048, H=32
+  tmix    one TMix layer chain at C=2048 for M in (4, 512)
+  decode  recurrent decode steps at B=256, H=32 (the benchmark's shape, 8 launches)
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+import flashrwkv_b200 as F
+from flashrwkv_b200 import synthetic
+from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata, wkv7_chunk_forward
+
+D = 64
+
+
+def case_chunk(reps: int = 3):
+    B, T, H = 2, 4096, 32
+    toks = [t.cuda() for t in synthetic.wkv7_inputs(B * T, H, D, seed=1)]
+    cu, _ = synthetic.equal_length_metadata(B, T, device="cuda")
+    pool = synthetic.state_pool(B, H, D, seed=2, device="cuda")
+    meta = make_chunk_metadata(cu, 64)
+    for _ in range(reps):
+        wkv7_chunk_forward(*toks, state=pool, chunk_metadata=meta)
+
+
+def case_train(reps: int = 2):
+    B, T, H = 2, 2048, 32
+    toks = [t.cuda().requires_grad_() for t in synthetic.wkv7_inputs(B * T, H, D, seed=3)]
+    S0 = synthetic.state_pool(B, H, D, seed=4, device="cuda").requires_grad_()
+    cu, _ = synthetic.equal_length_metadata(B, T, device="cuda")
+    meta = make_chunk_metadata(cu, 64)
+    dy = torch.randn(B * T, H, D, device="cuda").to(torch.bfloat16)
+    for _ in range(reps):
+        out = F.statetune_recurrent_fp32io16(S0, *meta, *toks)
+        out[0].backward(dy)
+
+
+def case_tmix(reps: int = 3):
+    C, H = 2048, 32
+    g = torch.Generator().manual_seed(3)
+    wt = lambda n, k: (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).cuda()  # noqa: E731
+    ranks = {"w": 96, "a": 96, "g": 256, "v": 64}
+    Wr = wt(C, C)
+    w1 = {n: wt(r, C) for n, r in ranks.items()}
+    w2 = {n: wt(C, r) for n, r in ranks.items()}
+    v0 = torch.rand(C, generator=g).to(torch.bfloat16).cuda()
+    for M in (4, 512):
+        xs = [torch.randn(M, C, generator=g).to(torch.bfloat16).cuda() for _ in range(6)]
+        for _ in range(reps):
+            F.infer_tmix_linear_forward_varlen(xs[0], Wr)
+            feats = F.infer_tmix_lowrank_wagv_in_forward_varlen(xs[1], xs[2], xs[3], xs[4], w1["w"], w1["a"], w1["g"],
+                                                                w1["v"])
+            F.infer_tmix_lowrank_vres_forward_varlen(*feats, w2["w"], w2["a"], w2["g"], w2["v"], xs[4], xs[5], v0)
+
+
+def case_decode(reps: int = 8):
+    B, H = 256, 32
+    cu, idx = synthetic.equal_length_metadata(B, 1, device="cuda")
+    pool = synthetic.state_pool(B, H, D, seed=5, device="cuda")
+    toks = [t.cuda() for t in synthetic.wkv7_inputs(B, H, D, seed=6)]
+    ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=B, state_pool_size=B, max_seqlen=1)
+    for _ in range(reps):
+        F.infer_recurrent_fp32io16_forward_varlen(*toks, state_pool=pool, cu_seqlens=cu, state_indices=idx,
+                                                  validated_metadata=ticket, max_seqlen=1)
+
+
+if __name__ == "__main__":
+    cases = {"chunk": case_chunk, "train": case_train, "tmix": case_tmix, "decode": case_decode}
+    name = sys.argv[1] if len(sys.argv) > 1 else ""
+    if name not in cases:
+        raise SystemExit(__doc__)
+    cases[name]()
+    torch.cuda.synchronize()
+    print(f"profile case {name}: done")
