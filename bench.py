@@ -43,7 +43,7 @@ BYTES_PER_UNIT = 2 * D * D * 4 + 7 * D * 2
 BYTES_PER_LAUNCH = B * H * BYTES_PER_UNIT
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch at this size, from the ncu
 # capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 220_650_000
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 221_360_000
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -351,16 +351,17 @@ def run_b200(args):
         for i in range(DECODE_STEPS_PER_STEP):
             F.infer_recurrent_fp32io16_forward_varlen(*ring[i % TOKEN_RING], **kw)
 
-    stage = [torch.empty_like(t, device=dev) for t in ring_host[0]]
-    y_host = torch.empty((B, H, D), dtype=torch.bfloat16).pin_memory()
+    # end to end: every decode step's six token tensors come from pinned host memory and its output goes back to
+    # pinned host memory, through the package's three-stream host loop (copy-in / kernel / copy-out overlap)
+    from flashrwkv_b200.host_io import HostDecodeLoop
+
+    host_loop = HostDecodeLoop(ring_host[0], **kw)
+    y_hosts = [torch.empty((B, H, D), dtype=torch.bfloat16).pin_memory() for _ in range(4)]
 
     def e2e_step():
         for i in range(DECODE_STEPS_PER_STEP):
-            src = ring_host[i % TOKEN_RING]
-            for d, s in zip(stage, src):
-                d.copy_(s, non_blocking=True)
-            y = F.infer_recurrent_fp32io16_forward_varlen(*stage, **kw)
-            y_host.copy_(y, non_blocking=True)
+            host_loop.submit(ring_host[i % TOKEN_RING], y_hosts[i % len(y_hosts)])
+        host_loop.drain()
 
     def barrier():
         if world > 1:

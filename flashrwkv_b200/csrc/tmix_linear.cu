@@ -5,62 +5,23 @@
 //   * M <= 8 ("skinny", decode): weight-bandwidth bound.  x is staged once per CTA in shared memory with the
 //     activation applied; every weight element is read exactly once with 16-byte loads.  For long rows (K >= 256) a
 //     warp owns an output column and reduces with shuffles; for short rows (rank-out, K = rank) a thread owns it.
-//   * M > 8: tcgen05 tensor-core GEMM (kind::f16, fp32 accumulate in tensor memory), 128 x 64 output tile per CTA,
-//     K in blocks of 64 through a 4-stage cp.async pipeline into chunk-major tiles (see umma.cuh).
+//   * M > 8: tcgen05 tensor-core GEMM (kind::f16, fp32 accumulate in tensor memory).  Problems without an activation
+//     on x go to the TMA-fed persistent kernel of tmix_gemm_tma.cu; the kernel here (128 x 64 output tile per CTA, K in
+//     blocks of 64 through a 4-stage cp.async pipeline into chunk-major tiles, see umma.cuh) applies tanh / sigmoid
+//     to the staged x tile and so serves the rank-out projections.
 // Weights are in the reference's "original" layout [N][K] (K contiguous).
 //
 // Replaces linear_wag[v]_rank_in_f16_kernel / linear_wag[v]_rank_out_f16_kernel
 // (csrc/sm120/tmix/linear/infer_fp16_forward_varlen.cu:916-1233), the linear_orig_* / linear_t_* GEMV-class kernels
 // (:133-786) and the cublasGemmEx / cublasLtMatmul calls (:1403-1446,1687-1777) of the reference.
 
-#include "frwkv_common.cuh"
+#include <cstdlib>
+
+#include "tmix_linear.cuh"
 #include "umma.cuh"
 
 namespace frwkv {
 namespace {
-
-constexpr int kMaxProblems = 4;
-
-struct LinearProblem {
-  const void* x;        // [M][K]
-  const void* w;        // [N][K]
-  void* y;              // [M][N]
-  const void* v;        // epilogue 1: [M][N]
-  const void* v_first;  // epilogue 1: [M][N]
-  const void* v0;       // epilogue 1: [N]
-  int n, k, act, epilogue;
-};
-struct LinearGroup {
-  LinearProblem p[kMaxProblems];
-};
-
-__device__ __forceinline__ float apply_act(float x, int act) {
-  if (act == 1) return tanhf(x);
-  if (act == 2) return 1.f / (1.f + __expf(-x));
-  return x;
-}
-
-template <typename io_t>
-__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
-  using IO = Io16<io_t>;
-  float2 t;
-  t = IO::unpack(u.x); f[0] = t.x; f[1] = t.y;
-  t = IO::unpack(u.y); f[2] = t.x; f[3] = t.y;
-  t = IO::unpack(u.z); f[4] = t.x; f[5] = t.y;
-  t = IO::unpack(u.w); f[6] = t.x; f[7] = t.y;
-}
-
-template <typename io_t>
-__device__ __forceinline__ float finish(const LinearProblem& pr, float acc, int m, int n) {
-  if (pr.epilogue == 1) {  // v + (v_first - v) * sigmoid(v0 + acc)
-    const long long o = (long long)m * pr.n + n;
-    const float vv = Io16<io_t>::load(static_cast<const io_t*>(pr.v) + o);
-    const float vf = Io16<io_t>::load(static_cast<const io_t*>(pr.v_first) + o);
-    const float z = Io16<io_t>::load(static_cast<const io_t*>(pr.v0) + n) + acc;
-    return fmaf(vf - vv, 1.f / (1.f + __expf(-z)), vv);
-  }
-  return acc;
-}
 
 // ---- skinny kernel --------------------------------------------------------------------------------------
 // grid = (column blocks, problems); dynamic shared memory = M * K 16-bit values (activation applied).
@@ -139,22 +100,13 @@ __global__ __launch_bounds__(256) void linear_skinny_kernel(LinearGroup group) {
 
 // ---- tensor-core kernel -----------------------------------------------------------------------------------
 constexpr int kBM = 128, kBN = 64, kBK = 64, kStages = 4;
+// Loads run kAhead k-blocks in front of the MMA.  A stage is refilled only once the MMA that read it has completed; with
+// kAhead = kStages - 2 that MMA is two k-blocks old, so the wait never stalls on the MMA issued just before it.
+constexpr int kAhead = kStages - 2;
 constexpr uint32_t kCsA = kBM * 16 + 16;  // chunk stride of the A stage tile (128 rows), padded against bank conflicts
 constexpr uint32_t kCsB = kBN * 16 + 16;
 constexpr uint32_t kStageBytes = 8 * kCsA + 8 * kCsB;
 constexpr uint32_t kTcSmem = kStages * kStageBytes;
-
-__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                           uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}\n" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 
 template <typename io_t>
 __global__ __launch_bounds__(128, 2) void linear_tc_kernel(LinearGroup group, int M, int* __restrict__ error_flag) {
@@ -206,18 +158,19 @@ __global__ __launch_bounds__(128, 2) void linear_tc_kernel(LinearGroup group, in
 
   bool ok = true;
 #pragma unroll
-  for (int s = 0; s < kStages - 1; ++s) {
+  for (int s = 0; s < kAhead; ++s) {
     if (s < KB) load_stage(s);
     umma::cp_async_commit();
   }
   for (int kb = 0; kb < KB; ++kb) {
-    const int pre = kb + kStages - 1;
+    const int pre = kb + kAhead;
     if (pre < KB) {
-      if (kb >= 1) ok = umma::mbar_wait(&done_bar[(kb - 1) % kStages], ((kb - 1) / kStages) & 1) && ok;
+      const int old = pre - kStages;  // k-block whose MMA last read the stage about to be refilled
+      if (old >= 0) ok = umma::mbar_wait(&done_bar[old % kStages], (old / kStages) & 1) && ok;
       load_stage(pre);
     }
     umma::cp_async_commit();
-    asm volatile("cp.async.wait_group %0;" ::"n"(kStages - 1) : "memory");
+    asm volatile("cp.async.wait_group %0;" ::"n"(kAhead) : "memory");
     unsigned char* st = smem + uint32_t(kb % kStages) * kStageBytes;
     if (pr.act != 0) {  // activation on the A operand: each thread transforms the chunks it copied itself
 #pragma unroll
@@ -332,6 +285,11 @@ extern "C" int frwkv_tmix_linear_grouped(const frwkv_linear_problem* problems, i
   for (int i = count; i < kMaxProblems; ++i) g.p[i] = g.p[0];
   if (m <= 8) FRWKV_REQUIRE((size_t)m * max_k * 2 <= 200 * 1024, "tmix_linear: K too large for the small-row kernel");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (io_dtype != FRWKV_DTYPE_BF16 && io_dtype != FRWKV_DTYPE_FP16)
+    return fail(FRWKV_ERR_UNSUPPORTED, "tmix_linear: tensors must be float16 or bfloat16");
+  // FRWKV_DISABLE_TMA_GEMM=1 keeps many-row problems on the cp.async kernel (for comparisons and tests)
+  static const bool tma_off = [] { const char* e = std::getenv("FRWKV_DISABLE_TMA_GEMM"); return e != nullptr && e[0] == '1'; }();
+  if (!tma_off && linear_tma_usable(g, count, m)) return launch_linear_tma(g, count, m, io_dtype, error_flag, s);
   if (io_dtype == FRWKV_DTYPE_BF16) return launch_linear<__nv_bfloat16>(g, count, m, max_n, max_k, error_flag, s);
   if (io_dtype == FRWKV_DTYPE_FP16) return launch_linear<__half>(g, count, m, max_n, max_k, error_flag, s);
   return fail(FRWKV_ERR_UNSUPPORTED, "tmix_linear: tensors must be float16 or bfloat16");

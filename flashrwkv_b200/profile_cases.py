@@ -5,6 +5,7 @@ matter, runs a handful of launches and exits, so that an `ncu` capture of one of
 
   chunk   chunked forward (build + scan): B=2, T=4096, H=32  (4096 (chunk, head) items)
   train   StateTune forward + backward: B=2, T=2048, H=32
+  train512  the same at B=8, T=512, H=64: 512 (sequence, head) pairs, the occupancy of the benchmark's training shape
   tmix    one TMix layer chain at C=2048 for M in (4, 512)
   decode  recurrent decode steps at B=256, H=32 (the benchmark's shape, 8 launches)
 """
@@ -31,8 +32,7 @@ def case_chunk(reps: int = 3):
         wkv7_chunk_forward(*toks, state=pool, chunk_metadata=meta)
 
 
-def case_train(reps: int = 2):
-    B, T, H = 2, 2048, 32
+def case_train(reps: int = 2, B: int = 2, T: int = 2048, H: int = 32):
     toks = [t.cuda().requires_grad_() for t in synthetic.wkv7_inputs(B * T, H, D, seed=3)]
     S0 = synthetic.state_pool(B, H, D, seed=4, device="cuda").requires_grad_()
     cu, _ = synthetic.equal_length_metadata(B, T, device="cuda")
@@ -73,7 +73,7 @@ def case_decode(reps: int = 8):
 
 
 if __name__ == "__main__":
-    cases = {"chunk": case_chunk, "train": case_train, "tmix": case_tmix, "decode": case_decode}
+    cases = {"chunk": case_chunk, "train": case_train, "train512": lambda: case_train(2, 8, 512, 64), "tmix": case_tmix, "decode": case_decode}
     name = sys.argv[1] if len(sys.argv) > 1 else ""
     if name not in cases:
         raise SystemExit(__doc__)

@@ -294,3 +294,31 @@ def test_cuda_graph_replay_with_ticket(oracle):
         ref_pool = ref["state_pool"]
     assert rel_rmse(y.float().cpu(), ref["y"]) <= REF_RMSE
     assert _state_rel(pool, ref_pool) <= STATE_REL
+
+
+def test_host_decode_loop_is_bit_identical_to_serial_decode():
+    """The three-stream host loop (pinned inputs in, pinned outputs out) gives the serial result, step by step."""
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+    from flashrwkv_b200.host_io import HostDecodeLoop
+
+    B, H, D, steps = 48, 4, 64, 9
+    cu, idx = (t.cuda() for t in synthetic.equal_length_metadata(B, 1))
+    pool_a = synthetic.state_pool(B, H, D, seed=5, device="cuda")
+    pool_b = pool_a.clone()
+    host = [[t.pin_memory() for t in synthetic.wkv7_inputs(B, H, D, seed=100 + i)] for i in range(steps)]
+    ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=B, state_pool_size=B, max_seqlen=1)
+    loop = HostDecodeLoop(host[0], state_pool=pool_a, cu_seqlens=cu, state_indices=idx, validated_metadata=ticket)
+    outs = [torch.empty((B, H, D), dtype=torch.bfloat16).pin_memory() for _ in range(steps)]
+    for i in range(steps):
+        loop.submit(host[i], outs[i])
+    loop.drain()
+    torch.cuda.synchronize()
+    for i in range(steps):
+        y = F.infer_recurrent_fp32io16_forward_varlen(*[t.cuda() for t in host[i]], state_pool=pool_b, cu_seqlens=cu,
+                                                      state_indices=idx, validated_metadata=ticket, max_seqlen=1)
+        assert torch.equal(y.cpu(), outs[i]), f"step {i}"
+    assert torch.equal(pool_a, pool_b)
+    with pytest.raises(ValueError):
+        HostDecodeLoop([t.cuda() for t in host[0]], state_pool=pool_a, cu_seqlens=cu, state_indices=idx,
+                       validated_metadata=ticket)

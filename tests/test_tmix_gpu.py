@@ -163,3 +163,20 @@ def test_elementwise_activations():
     assert rel_rmse(F.infer_tmix_linear_act_tanh_forward_varlen(x.cuda()).float().cpu(), torch.tanh(x.float())) <= 1e-3
     assert rel_rmse(F.infer_tmix_linear_act_sigmoid_forward_varlen(x.cuda()).float().cpu(),
                     torch.sigmoid(x.float())) <= 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(300, 72, 200), (129, 264, 2048), (4096, 2048, 2048), (1000, 520, 72)])
+def test_dense_linear_ragged_shapes(oracle, dtype, shape):
+    """Row, column and K counts that are not multiples of the tensor-core tile, and a many-tile case."""
+    import flashrwkv_b200 as F
+
+    M, N, K = shape
+    gen = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=gen).to(dtype)
+    W = (torch.randn(N, K, generator=gen) * 0.05).to(dtype)
+    y = F.infer_tmix_linear_forward_varlen(x.cuda(), W.cuda())
+    ref = x.double() @ W.double().T
+    assert y.shape == (M, N)
+    assert rel_rmse(y.double().cpu(), ref) <= TOL[dtype]
+    assert max_abs(y.double().cpu(), ref) <= 8 * TOL[dtype] * float(ref.abs().max())
