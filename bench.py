@@ -224,6 +224,29 @@ def _extras(dev):
         peaks = json.loads(pk.read_text())
     hbm = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS)) * 1e9
     bf16 = float(peaks.get("bf16_tflops", 1590.0)) * 1e12
+    # ---- decode on an fp16 state pool (the reference's production decode contract): same batch as the headline
+    cu1, idx1 = (t.to(dev) for t in synthetic.equal_length_metadata(B, 1))
+    pool16 = synthetic.state_pool(B, H, D, seed=21, device=dev).half()
+    elapsed = torch.zeros(B, dtype=torch.int32, device=dev)
+    ring16 = [[t.to(dev) for t in synthetic.wkv7_inputs(B, H, D, seed=700 + i)] for i in range(TOKEN_RING)]
+    ticket16 = F.prepare_recurrent_metadata(cu1, idx1, total_tokens=B, state_pool_size=B, max_seqlen=1)
+    n_steps = 128
+
+    def decode16():
+        for i in range(n_steps):
+            F.infer_recurrent_fp16_forward_varlen(*ring16[i % TOKEN_RING], state_pool=pool16,
+                                                  elapsed_state_pool=elapsed, cu_seqlens=cu1, state_indices=idx1,
+                                                  max_seqlen=1, validated_metadata=ticket16)
+            F.infer_recurrent_fp16_advance_i32(elapsed, 1)
+
+    sec = _time_cuda(decode16) / n_steps
+    bytes16 = B * H * (2 * D * D * 2 + 7 * D * 2)
+    out["decode_fp16_state"] = {
+        "workload": f"recurrent decode B={B} H={H} D={D}, bf16 tokens, fp16 state pool with dither, counters advanced "
+                    f"every step", "tokens_per_s": B / sec, "us_per_step": sec * 1e6,
+        "algorithmic_bytes_per_launch": bytes16, "hbm_frac_algorithmic": bytes16 / sec / hbm,
+        "gpu_launches_per_step": 2}
+    del pool16, ring16
     # ---- chunked prefill
     Bc, T, Hc = 8, 4096, 32
     toks = [t.to(dev) for t in synthetic.wkv7_inputs(Bc * T, Hc, D, seed=11)]

@@ -29,6 +29,7 @@ CUDA_SOURCES = [
     "frwkv_capi.cu",
     "metadata.cu",
     "wkv7_recurrent.cu",
+    "wkv7_recurrent_fp16.cu",
     "umma_selftest.cu",
     "wkv7_chunk_fwd.cu",
     "tmix_elementwise.cu",

@@ -186,7 +186,8 @@ RecurrentDims check_recurrent_layout(const torch::Tensor& cu, const torch::Tenso
                                      const torch::Tensor& state, const torch::Tensor& r,
                                      const torch::Tensor& w, const torch::Tensor& k, const torch::Tensor& v,
                                      const torch::Tensor& a, const torch::Tensor& b,
-                                     const torch::Tensor& out, double scale) {
+                                     const torch::Tensor& out, double scale,
+                                     torch::ScalarType state_type = torch::kFloat32) {
   const std::pair<const torch::Tensor*, const char*> all[] = {
       {&cu, "query_start_loc"}, {&idx, "state_indices"}, {&state, "state"}, {&r, "r"},
       {&w, "decay_logits"},     {&k, "k"},               {&v, "v"},         {&a, "a"},
@@ -201,7 +202,8 @@ RecurrentDims check_recurrent_layout(const torch::Tensor& cu, const torch::Tenso
   TORCH_CHECK(cu.dim() == 1 && cu.size(0) == B + 1, "query_start_loc must have shape [N+1]");
   TORCH_CHECK(state.dim() == 4 && state.size(0) > 0 && state.size(1) > 0 && state.size(2) == state.size(3),
               "state must have square shape [slots,H,D,D]");
-  TORCH_CHECK(state.scalar_type() == torch::kFloat32, "state must be float32");
+  TORCH_CHECK(state.scalar_type() == state_type,
+              state_type == torch::kFloat32 ? "state must be float32" : "state must be float16");
   const int64_t D = state.size(2);
   TORCH_CHECK(D == 64 || D == 128 || D == 256, "recurrent head size must be 64, 128, or 256, got ", D);
   TORCH_CHECK(state.size(0) <= std::numeric_limits<int>::max(), "state slot count must fit in int32");
@@ -272,6 +274,90 @@ void recurrent_fp32_from_decay_logits(torch::Tensor cu, torch::Tensor idx, torch
       static_cast<int>(dims.B), static_cast<int>(dims.H), static_cast<int>(dims.D),
       static_cast<int>(std::min<int64_t>(std::max<int64_t>(max_seqlen, -1), std::numeric_limits<int>::max())),
       io_dtype_of(r), static_cast<float>(scale), flags, current_stream(state)));
+}
+
+// ---- fp16-state recurrence (reference entry names and argument order:
+// csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cpp:275-301) ------------------------------------------
+void check_elapsed(const torch::Tensor& elapsed, const char* name) {
+  check_cuda_contiguous(elapsed, name);
+  TORCH_CHECK(elapsed.scalar_type() == torch::kInt32, name, " must be int32");
+  TORCH_CHECK(elapsed.numel() > 0, name, " must be non-empty");
+}
+
+void recurrent_fp16_from_decay_logits(torch::Tensor cu, torch::Tensor idx, torch::Tensor elapsed, torch::Tensor state,
+                                      torch::Tensor r, torch::Tensor w, torch::Tensor k, torch::Tensor v,
+                                      torch::Tensor a, torch::Tensor b, torch::Tensor output, double scale,
+                                      std::optional<torch::Tensor> decay_bias,
+                                      std::shared_ptr<MetadataTicket> ticket, int64_t max_seqlen) {
+  const auto dims = check_recurrent_layout(cu, idx, state, r, w, k, v, a, b, output, scale, torch::kFloat16);
+  check_decay_bias(decay_bias, state, r);
+  check_elapsed(elapsed, "elapsed_state_pool");
+  check_same_device(state, elapsed, "elapsed_state_pool");
+  TORCH_CHECK(elapsed.dim() == 1 && elapsed.size(0) == state.size(0),
+              "elapsed_state_pool must have shape [state_pool_slots]");
+  const c10::cuda::CUDAGuard guard(state.device());
+  torch::Tensor launch_cu, launch_idx, status;
+  int flags = 0;
+  if (ticket) {
+    ticket->check_compatible(cu, idx, r.size(0), state.size(0), max_seqlen);
+    flags = ticket->next_launch_parity() ? FRWKV_RECURRENT_REVERSE_ORDER : 0;
+    launch_cu = ticket->cu_snapshot();
+    launch_idx = ticket->idx_snapshot();
+    status = ticket->status();
+    max_seqlen = ticket->max_seqlen();
+  } else {
+    auto prepared = launch_validation(cu, idx, r.size(0), state.size(0));
+    launch_cu = std::move(prepared.cu);
+    launch_idx = std::move(prepared.idx);
+    status = std::move(prepared.status);
+  }
+  check_rc(frwkv_wkv7_recurrent_fp16_forward_varlen(
+      launch_cu.data_ptr<int>(), launch_idx.data_ptr<int>(), status.data_ptr<int>(), elapsed.data_ptr<int>(),
+      state.data_ptr(), r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
+      decay_bias.has_value() ? decay_bias->data_ptr() : nullptr, output.data_ptr(), static_cast<int>(r.size(0)),
+      static_cast<int>(dims.B), static_cast<int>(dims.H), static_cast<int>(dims.D),
+      static_cast<int>(std::min<int64_t>(std::max<int64_t>(max_seqlen, -1), std::numeric_limits<int>::max())),
+      io_dtype_of(r), static_cast<float>(scale), flags, current_stream(state)));
+}
+
+void recurrent_fp16_advance_i32(torch::Tensor elapsed, int64_t amount) {
+  check_elapsed(elapsed, "elapsed_state");
+  TORCH_CHECK(amount >= std::numeric_limits<int>::min() && amount <= std::numeric_limits<int>::max(),
+              "amount must fit in int32");
+  const c10::cuda::CUDAGuard guard(elapsed.device());
+  check_rc(frwkv_recurrent_fp16_advance_i32(elapsed.data_ptr<int>(), elapsed.numel(), static_cast<int>(amount),
+                                            current_stream(elapsed)));
+}
+
+void recurrent_fp16_advance_i32_varlen(torch::Tensor cu, torch::Tensor idx, torch::Tensor elapsed,
+                                       int64_t total_tokens, std::shared_ptr<MetadataTicket> ticket) {
+  check_elapsed(elapsed, "elapsed_state_pool");
+  TORCH_CHECK(elapsed.dim() == 1, "elapsed_state_pool must have shape [slots]");
+  check_cuda_contiguous(cu, "query_start_loc");
+  check_cuda_contiguous(idx, "state_indices");
+  TORCH_CHECK(cu.scalar_type() == torch::kInt32 && idx.scalar_type() == torch::kInt32,
+              "query_start_loc and state_indices must be int32");
+  TORCH_CHECK(idx.dim() == 1 && idx.numel() > 0 && cu.dim() == 1 && cu.numel() == idx.numel() + 1,
+              "query_start_loc must have shape [B+1] and state_indices shape [B]");
+  TORCH_CHECK(total_tokens > 0, "total_tokens must be positive");
+  check_same_device(elapsed, cu, "query_start_loc");
+  check_same_device(elapsed, idx, "state_indices");
+  const c10::cuda::CUDAGuard guard(elapsed.device());
+  torch::Tensor launch_cu, launch_idx, status;
+  if (ticket) {
+    ticket->check_compatible(cu, idx, total_tokens, elapsed.size(0), -1);
+    launch_cu = ticket->cu_snapshot();
+    launch_idx = ticket->idx_snapshot();
+    status = ticket->status();
+  } else {
+    auto prepared = launch_validation(cu, idx, total_tokens, elapsed.size(0));
+    launch_cu = std::move(prepared.cu);
+    launch_idx = std::move(prepared.idx);
+    status = std::move(prepared.status);
+  }
+  check_rc(frwkv_recurrent_fp16_advance_i32_varlen(elapsed.data_ptr<int>(), launch_cu.data_ptr<int>(),
+                                                   launch_idx.data_ptr<int>(), status.data_ptr<int>(),
+                                                   static_cast<int>(idx.numel()), current_stream(elapsed)));
 }
 
 // ---- chunked forward ---------------------------------------------------------------------------------
@@ -642,6 +728,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("v"), py::arg("a"), py::arg("b"), py::arg("output"), py::arg("scale"),
         py::arg("decay_bias") = py::none(), py::arg("validated_metadata") = py::none(),
         py::arg("max_seqlen") = -1, py::arg("output_fp32") = py::none());
+  m.def("recurrent_fp16_from_decay_logits", &recurrent_fp16_from_decay_logits, py::arg("query_start_loc"),
+        py::arg("state_indices"), py::arg("elapsed_state_pool"), py::arg("state"), py::arg("r"),
+        py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"), py::arg("output"),
+        py::arg("scale"), py::arg("decay_bias") = py::none(), py::arg("validated_metadata") = py::none(),
+        py::arg("max_seqlen") = -1);
+  m.def("recurrent_fp16_advance_i32", &recurrent_fp16_advance_i32, py::arg("elapsed_state"), py::arg("amount"));
+  m.def("recurrent_fp16_advance_i32_varlen", &recurrent_fp16_advance_i32_varlen, py::arg("query_start_loc"),
+        py::arg("state_indices"), py::arg("elapsed_state_pool"), py::arg("total_tokens"),
+        py::arg("validated_metadata") = py::none());
   m.def("wkv7_chunk_forward", &wkv7_chunk_forward, py::arg("sequence_chunk_offsets"),
         py::arg("chunk_token_starts"), py::arg("chunk_token_ends"), py::arg("state"), py::arg("r"),
         py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"), py::arg("output"),

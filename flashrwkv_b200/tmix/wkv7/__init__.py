@@ -81,7 +81,99 @@ def infer_recurrent_fp32io16_forward_varlen(r, decay_logits, k, v, a, b, *, stat
     return output
 
 
-__all__ = ["infer_recurrent_fp32io16_forward_varlen", "prepare_recurrent_metadata"]
+# ---- fp16 state pool (reference: flashrwkv2/tmix/wkv7/__init__.py:41-140,280-339) ---------------------------------
+def _validate_fp16_state(state) -> None:
+    if not isinstance(state, torch.Tensor):
+        raise TypeError("state_pool must be a torch.Tensor")
+    if not state.is_contiguous():
+        raise ValueError("state_pool must be contiguous")
+    if state.dtype != torch.float16:
+        raise TypeError("FP16-state state_pool must have dtype float16")
+
+
+def _validate_elapsed(elapsed, name: str) -> None:
+    if not isinstance(elapsed, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if elapsed.dtype != torch.int32:
+        raise TypeError(f"{name} must have dtype torch.int32")
+    if not elapsed.is_cuda or not elapsed.is_contiguous():
+        raise ValueError(f"{name} must be contiguous CUDA int32")
+
+
+def infer_recurrent_fp16_advance_i32(elapsed_state, amount: int) -> None:
+    """Add ``amount`` to every elapsed (dither phase) counter, in place."""
+    _validate_elapsed(elapsed_state, "elapsed_state")
+    if elapsed_state.numel() == 0:
+        raise ValueError("elapsed_state must be non-empty")
+    if not isinstance(amount, int) or isinstance(amount, bool):
+        raise TypeError("amount must be an int")
+    extension().recurrent_fp16_advance_i32(elapsed_state, amount)
+
+
+def infer_recurrent_fp16_advance_i32_varlen(elapsed_state_pool, cu_seqlens, state_indices, *, total_tokens: int,
+                                            validated_metadata=None) -> None:
+    """Advance the counters of the selected slots by their sequences' packed lengths, in place."""
+    if not isinstance(elapsed_state_pool, torch.Tensor):
+        raise TypeError("elapsed_state_pool must be a torch.Tensor")
+    if (elapsed_state_pool.dtype != torch.int32 or not elapsed_state_pool.is_cuda
+            or not elapsed_state_pool.is_contiguous() or elapsed_state_pool.ndim != 1
+            or elapsed_state_pool.numel() == 0):
+        raise ValueError("elapsed_state_pool must be non-empty contiguous CUDA int32")
+    _check_metadata_inputs(cu_seqlens, state_indices)
+    for name, t in (("cu_seqlens", cu_seqlens), ("state_indices", state_indices)):
+        if t.dtype != torch.int32 or not t.is_cuda or not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous CUDA int32")
+        if t.device != elapsed_state_pool.device:
+            raise ValueError("elapsed metadata tensors must share a CUDA device")
+    if state_indices.ndim != 1 or cu_seqlens.numel() != state_indices.numel() + 1:
+        raise ValueError("cu_seqlens must have shape [B+1] and state_indices shape [B]")
+    if not isinstance(total_tokens, int) or isinstance(total_tokens, bool) or total_tokens <= 0:
+        raise ValueError("total_tokens must be a positive integer")
+    ticket = validated_metadata
+    if ticket is None:
+        ticket = prepare_recurrent_metadata(cu_seqlens, state_indices, total_tokens=total_tokens,
+                                            state_pool_size=elapsed_state_pool.shape[0])
+    extension().recurrent_fp16_advance_i32_varlen(cu_seqlens, state_indices, elapsed_state_pool, total_tokens, ticket)
+
+
+def infer_recurrent_fp16_forward_varlen(r, decay_logits, k, v, a, b, *, state_pool, elapsed_state_pool, cu_seqlens,
+                                        state_indices, scale: float = 1.0, decay_bias=None,
+                                        max_seqlen: int | None = None, validated_metadata=None) -> torch.Tensor:
+    """Packed RWKV-7 recurrence on an fp16 ``state_pool [slots,H,64,64]``, updated in place.
+
+    The retention enters as a rounded fp16 increment with a deterministic dither whose phase comes from the int32
+    ``elapsed_state_pool [slots]`` (read, never advanced here: see the two ``advance`` operators).  Returns the
+    output shaped like ``v``.
+    """
+    packed = _validate_packed_inputs(r, decay_logits, k, v, a, b)
+    _validate_fp16_state(state_pool)
+    _validate_elapsed(elapsed_state_pool, "elapsed_state_pool")
+    if elapsed_state_pool.device != state_pool.device:
+        raise ValueError("elapsed_state_pool must share state_pool's device")
+    if elapsed_state_pool.ndim != 1 or elapsed_state_pool.shape[0] != state_pool.shape[0]:
+        raise ValueError("elapsed_state_pool must have shape [state_pool_slots]")
+    _check_metadata_inputs(cu_seqlens, state_indices)
+    if max_seqlen is None:
+        launch_max_seqlen = -1
+    else:
+        if not isinstance(max_seqlen, int) or isinstance(max_seqlen, bool) or max_seqlen <= 0:
+            raise ValueError("max_seqlen must be a positive integer")
+        launch_max_seqlen = int(max_seqlen)
+    ticket = validated_metadata
+    if ticket is None:
+        ticket = prepare_recurrent_metadata(cu_seqlens, state_indices, total_tokens=r.shape[0],
+                                            state_pool_size=state_pool.shape[0],
+                                            max_seqlen=None if launch_max_seqlen < 0 else launch_max_seqlen)
+    output = torch.empty_like(packed[3])
+    extension().recurrent_fp16_from_decay_logits(
+        cu_seqlens, state_indices, elapsed_state_pool, state_pool, *packed, output, float(scale), decay_bias, ticket,
+        launch_max_seqlen)
+    return output
+
+
+__all__ = ["infer_recurrent_fp32io16_forward_varlen", "prepare_recurrent_metadata",
+           "infer_recurrent_fp16_forward_varlen", "infer_recurrent_fp16_advance_i32",
+           "infer_recurrent_fp16_advance_i32_varlen"]
 
 from .chunk import infer_chunk_bf16_forward_varlen, make_chunk_metadata, wkv7_chunk_forward  # noqa: E402
 

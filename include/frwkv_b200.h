@@ -96,6 +96,34 @@ int frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex(
     int io_dtype, float scale, int flags, frwkv_stream_t stream);
 
 /*
+ * WKV7 recurrence with an fp16 state pool updated in place (the "Albatross" contract).
+ * Replaces recurrent_fp16_from_decay_logits of the reference
+ * (csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu; Python wrapper
+ * flashrwkv2/tmix/wkv7/__init__.py:280-339; contract restated in tests/tmix/wkv7/test.py:216-277).
+ *   per token:  delta = half(exp(-exp(-0.5) * sigmoid(decay_logits + decay_bias)) - 1 + dither)
+ *               sa = S^T a ; S = half(S + S delta + b sa^T + k v^T) ; y = scale * S^T r  (rounded new state)
+ *               dither = int32(uint32(phase) * 2654435769) * 2^-41,
+ *               phase = head * D + key channel + elapsed_state_pool[slot] + index of the token in its sequence
+ *   state_pool : fp16 [slots, H, D, D];  elapsed_state_pool : int32 [slots], read only;
+ *   the other arguments as in frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex.  head_size must be 64.
+ */
+int frwkv_wkv7_recurrent_fp16_forward_varlen(
+    const int32_t* cu_seqlens, const int32_t* state_indices, const int32_t* metadata_status,
+    const int32_t* elapsed_state_pool, void* state_pool, const void* r, const void* decay_logits, const void* k,
+    const void* v, const void* a, const void* b, const void* decay_bias, void* y, int total_tokens, int num_sequences,
+    int num_heads, int head_size, int max_seqlen, int io_dtype, float scale, int flags, frwkv_stream_t stream);
+
+/* elapsed_state[i] += amount for all `count` counters (32-bit wrap-around).
+ * Replaces recurrent_fp16_advance_i32 (flashrwkv2/tmix/wkv7/__init__.py:65-80). */
+int frwkv_recurrent_fp16_advance_i32(int32_t* elapsed_state, long long count, int amount, frwkv_stream_t stream);
+
+/* elapsed_state_pool[state_indices[i]] += cu_seqlens[i+1] - cu_seqlens[i]; nothing is touched when
+ * *metadata_status != 0.  Replaces recurrent_fp16_advance_i32_varlen (flashrwkv2/tmix/wkv7/__init__.py:83-140). */
+int frwkv_recurrent_fp16_advance_i32_varlen(int32_t* elapsed_state_pool, const int32_t* cu_seqlens,
+                                            const int32_t* state_indices, const int32_t* metadata_status,
+                                            int num_sequences, frwkv_stream_t stream);
+
+/*
  * Chunked WKV7 forward on the tensor cores: same recurrence and tensors as
  * frwkv_wkv7_recurrent_fp32io16_forward_varlen, evaluated chunk by chunk (chunk length <= 64).
  * Replaces the reference's chunk families: infer_chunk_bf16_forward_varlen_cuda

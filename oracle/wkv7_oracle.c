@@ -14,6 +14,7 @@
  * Reference locations restated here (paths inside the reference project):
  *   retention transform   csrc/sm120/tmix/wkv7/recurrent_decay.cuh:10-32
  *   forward recurrence    tests/tmix/wkv7/test.py:157-213
+ *   fp16-state recurrence tests/tmix/wkv7/test.py:216-277 (rounded retention increment, dither, elapsed phase)
  *                         tests/tmix/wkv7/statetune/test.py:39-87 (boundaries, state_dot_a)
  *   backward (adjoint)    csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_backward.cu:139-254
  *                         (checked here against autograd of the forward oracle)
@@ -164,6 +165,70 @@ void oracle_retention_f32(const float* x, float* w, int64_t n) {
 
 DEFINE_FORWARD(oracle_wkv7_forward_f32, float, retention_f)
 DEFINE_FORWARD(oracle_wkv7_forward_f64, double, retention_d)
+
+/* ------------------------------------------------------------------------- */
+/* Forward recurrence on an fp16 state pool (tests/tmix/wkv7/test.py:216-277   */
+/* of the reference), fp32 arithmetic in the reference's order of operations:  */
+/*   phase    = h*D + k + elapsed[slot] + (t - first token of the sequence)    */
+/*   dither   = (float)(int32)((uint32)phase * 2654435769) * 2^-41             */
+/*   delta[k] = half(exp(-e^-0.5 sigmoid(logit[k] + bias[k])) - 1 + dither)    */
+/*   sa[v]    = sum_k a[k] S[k][v]                                             */
+/*   S[k][v]  = half(S + S*delta[k] + b[k]*sa[v] + k[k]*v[v])                  */
+/*   y[v]     = half(scale * sum_k r[k] S[k][v])        (rounded new state)    */
+/* state_pool holds IEEE binary16 values; y receives the fp16-rounded outputs  */
+/* as floats.  The elapsed counters are read, never advanced.                  */
+/* ------------------------------------------------------------------------- */
+void oracle_wkv7_fp16_forward(const int32_t* cu_seqlens, const int32_t* state_indices,
+                              const int32_t* elapsed, int B, int H, int D, _Float16* state_pool,
+                              const float* r, const float* logits, const float* k, const float* v,
+                              const float* a, const float* b, const float* decay_bias, float scale,
+                              float* y) {
+  const int64_t DD = (int64_t)D * D;
+#pragma omp parallel for collapse(2) schedule(dynamic)
+  for (int s = 0; s < B; ++s) {
+    for (int h = 0; h < H; ++h) {
+      float* S = (float*)malloc(sizeof(float) * DD);
+      float* sa = (float*)malloc(sizeof(float) * D);
+      float* delta = (float*)malloc(sizeof(float) * D);
+      const int slot = state_indices ? state_indices[s] : s;
+      _Float16* Sg = state_pool + ((int64_t)slot * H + h) * DD;
+      for (int64_t i = 0; i < DD; ++i) S[i] = (float)Sg[i];
+      const int t0 = cu_seqlens[s], t1 = cu_seqlens[s + 1];
+      for (int t = t0; t < t1; ++t) {
+        const int64_t base = ((int64_t)t * H + h) * D;
+        for (int i = 0; i < D; ++i) {
+          float x = logits[base + i];
+          if (decay_bias) x += decay_bias[(int64_t)h * D + i];
+          const float w = expf(-(float)DECAY_RATE * (1.0f / (1.0f + expf(-x))));
+          const uint32_t phase = (uint32_t)(h * D + i) + (uint32_t)elapsed[slot] + (uint32_t)(t - t0);
+          const float dither = (float)(int32_t)(phase * 2654435769u) * 4.547473508864641e-13f;
+          delta[i] = (float)(_Float16)((w - 1.0f) + dither);
+        }
+        for (int j = 0; j < D; ++j) sa[j] = 0.f;
+        for (int i = 0; i < D; ++i) {
+          const float ai = a[base + i];
+          for (int j = 0; j < D; ++j) sa[j] += ai * S[(int64_t)i * D + j];
+        }
+        float ytmp[256];
+        for (int j = 0; j < D; ++j) ytmp[j] = 0.f;
+        for (int i = 0; i < D; ++i) {
+          float* Si = S + (int64_t)i * D;
+          const float di = delta[i], bi = b[base + i], ki = k[base + i], ri = r[base + i];
+          for (int j = 0; j < D; ++j) {
+            const float u = (float)(_Float16)(((Si[j] + Si[j] * di) + bi * sa[j]) + ki * v[base + j]);
+            Si[j] = u;
+            ytmp[j] += ri * u;
+          }
+        }
+        for (int j = 0; j < D; ++j) y[base + j] = (float)(_Float16)(scale * ytmp[j]);
+      }
+      for (int64_t i = 0; i < DD; ++i) Sg[i] = (_Float16)S[i];
+      free(S);
+      free(sa);
+      free(delta);
+    }
+  }
+}
 
 /* ------------------------------------------------------------------------- */
 /* Backward of the forward above for dense equal-length sequences             */

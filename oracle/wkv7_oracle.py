@@ -125,6 +125,32 @@ def forward(r, decay_logits, k, v, a, b, *, state_pool, cu_seqlens, state_indice
     return {"y": y, "state_pool": pool, "boundary": bnd, "state_dot_a": sda}
 
 
+def forward_fp16(r, decay_logits, k, v, a, b, *, state_pool, elapsed_state_pool, cu_seqlens, state_indices=None,
+                 scale: float = 1.0, decay_bias=None):
+    """Packed varlen WKV7 forward on an fp16 state pool (rounded retention increment with dither).
+
+    ``state_pool`` is a float16 tensor / array ``[slots,H,D,D]``.  Returns ``y`` (float32 array holding the
+    fp16-rounded outputs) and ``state_pool`` (updated float16 copy).  ``elapsed_state_pool`` int32 ``[slots]``.
+    """
+    lib = _load()
+    r, w, k, v, a, b = (_f32(t) for t in (r, decay_logits, k, v, a, b))
+    N, H, D = r.shape
+    if D > 256:
+        raise ValueError("oracle supports D <= 256")
+    if hasattr(state_pool, "detach"):
+        state_pool = state_pool.detach().cpu().numpy()
+    pool = np.ascontiguousarray(state_pool, dtype=np.float16).copy()
+    cu = _i32(cu_seqlens)
+    idx = None if state_indices is None else _i32(state_indices)
+    elapsed = _i32(elapsed_state_pool)
+    bias = None if decay_bias is None else _f32(decay_bias).reshape(H, D)
+    y = np.empty_like(r)
+    lib.oracle_wkv7_fp16_forward(_p(cu), _p(idx), _p(elapsed), ctypes.c_int(cu.size - 1), ctypes.c_int(H),
+                                 ctypes.c_int(D), _p(pool), _p(r), _p(w), _p(k), _p(v), _p(a), _p(b), _p(bias),
+                                 ctypes.c_float(scale), _p(y))
+    return {"y": y, "state_pool": pool}
+
+
 def backward(r, decay_logits, k, v, a, b, *, initial_state, cu_seqlens, grad_output,
              grad_final_state=None, scale: float = 1.0, decay_bias=None):
     """Gradients of ``forward`` (float64 accumulation); initial_state is [B,H,D,D]."""

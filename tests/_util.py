@@ -11,6 +11,7 @@ GOLDEN = Path(__file__).resolve().parent / "golden"
 # io dtype of the 16-bit arrays (stored as uint16 bit patterns) in each golden file
 _IO_DTYPE = {
     "recurrent_ragged": torch.bfloat16,
+    "recurrent_fp16state": torch.float16,
     "chunk_bf16": torch.bfloat16,
     "rl_fp16": torch.float16,
     "statetune": torch.float16,

@@ -123,3 +123,26 @@ def test_tmix_pieces_match_reference_formulas(oracle):
     ones = np.ones((2, 4096), np.float32)
     new_k, neg_kk, kka = oracle.kk_a_gate(ones, ones[0], 0 * ones[0], 0 * ones, ones[0])
     assert np.allclose(new_k, 0.5) and np.allclose(neg_kk, -0.125) and np.allclose(kka, 0.0625)
+
+
+def test_fp16_state_contract_with_dither(oracle):
+    """The fp16-state restatement follows the reference oracle through rounding: values that differ at all differ
+    by one fp16 ulp (a tie broken the other way by a last-bit difference in exp / sigmoid), and few do."""
+    g = load_golden("recurrent_fp16state")
+    out = oracle.forward_fp16(*(g[n] for n in TOKENS), state_pool=g["state_pool"],
+                              elapsed_state_pool=g["elapsed_state_pool"], cu_seqlens=g["cu_seqlens"],
+                              state_indices=g["state_indices"], scale=g["scale"], decay_bias=g["decay_bias"])
+    got_state = torch.from_numpy(out["state_pool"])
+    want_state = g["final_pool"]
+    assert got_state.dtype == torch.float16 and want_state.dtype == torch.float16
+    mismatch = (got_state != want_state).float().mean().item()
+    assert mismatch < 2e-3
+    assert rel_rmse(got_state.float(), want_state.float()) < 2e-4
+    assert rel_rmse(out["y"], g["y"].float()) < 2e-4
+    inactive = [1, 3, 6, 8]
+    assert torch.equal(got_state[inactive], g["state_pool"][inactive])
+    # the dither phase matters: other elapsed counters give a different rounded state
+    shifted = oracle.forward_fp16(*(g[n] for n in TOKENS), state_pool=g["state_pool"],
+                                  elapsed_state_pool=g["elapsed_state_pool"] + 1, cu_seqlens=g["cu_seqlens"],
+                                  state_indices=g["state_indices"], scale=g["scale"], decay_bias=g["decay_bias"])
+    assert (torch.from_numpy(shifted["state_pool"]) != want_state).float().mean().item() > 1e-2
