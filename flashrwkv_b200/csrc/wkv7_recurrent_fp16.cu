@@ -201,6 +201,7 @@ constexpr int kStageBytes = kTileBytes + kTokBytes;  // 8,960
 constexpr int kConsumerPairs = 7;
 constexpr int kDecodeThreads = 32 * (2 + 2 * kConsumerPairs);
 constexpr int kDecodeSmem = kStages * kStageBytes;   // 215,040
+constexpr int kMetaTiles = 512;                      // tiles per CTA whose metadata is staged in shared memory
 
 __device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),
@@ -222,6 +223,9 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_fp16_decode_kernel(
   using IO = Io16<io_t>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full_bar[kStages], done_bar[kStages], empty_bar[kStages];
+  // state slot and elapsed counter of this CTA's first kMetaTiles tiles, fetched by all threads before the pipeline
+  // starts: the loader, the storer and the consumers would otherwise each wait for two dependent global loads per tile
+  __shared__ int slot_s[kMetaTiles], elapsed_s[kMetaTiles];
   // i-th tile of this CTA; `reverse` walks the pool from the other end (a caller that alternates it between decode
   // steps finds the tiles it touched last, still in L2, first)
   const auto tile_of = [&](int i) {
@@ -235,36 +239,46 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_fp16_decode_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
-      umma::mbar_init(&full_bar[i], 1);
+      umma::mbar_init(&full_bar[i], 1 + 32);  // the tile's expect_tx arrival + one arrival per loader lane
       umma::mbar_init(&done_bar[i], 2);
       umma::mbar_init(&empty_bar[i], 1);
     }
     umma::mbar_fence_init();
   }
-  __syncthreads();
   const int my_tiles = ((int)blockIdx.x < num_tiles) ? (num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  for (int i = threadIdx.x; i < min(my_tiles, kMetaTiles); i += kDecodeThreads) {
+    const int slot = state_indices[tile_of(i) / num_heads];
+    slot_s[i] = slot;
+    elapsed_s[i] = elapsed_pool[slot];
+  }
+  __syncthreads();
+  const auto slot_of = [&](int i) { return i < kMetaTiles ? slot_s[i] : state_indices[tile_of(i) / num_heads]; };
   bool ok = true;
 
   if (warp == 0) {
-    if (lane == 0) {  // loader
-      for (int i = 0; i < my_tiles && ok; ++i) {
-        const int st = i % kStages;
-        if (i >= kStages) ok = umma::mbar_wait(&empty_bar[st], ((i / kStages) - 1) & 1);
-        if (!ok) break;
-        const int tile = tile_of(i);
-        const int seq = tile / num_heads, head = tile % num_heads;
-        const __half* src = state_pool + ((long long)state_indices[seq] * num_heads + head) * (kD * kD);
-        const long long tb = ((long long)seq * num_heads + head) * kD;  // one token per sequence
-        unsigned char* stage = smem + st * kStageBytes;
-        umma::mbar_expect_tx(&full_bar[st], kStageBytes);
+    // loader (whole warp).  Lane 0 brings the state tile in with one bulk copy; the six 128-byte token rows go as
+    // 48 16-byte cp.async pieces spread over the lanes (a bulk copy per row would cost the copy engine a descriptor
+    // each, and that fixed cost per tile is what bounds the pipeline).  Each lane's pieces count on the stage's
+    // "full" barrier through cp.async.mbarrier.arrive.noinc.
+    const io_t* const row_src0 = lane < 8 ? r_ptr : (lane < 16 ? w_ptr : (lane < 24 ? k_ptr : v_ptr));
+    const io_t* const row_src1 = lane < 8 ? a_ptr : b_ptr;  // second piece, lanes 0..15
+    for (int i = 0; i < my_tiles && ok; ++i) {
+      const int st = i % kStages;
+      if (i >= kStages) ok = umma::mbar_wait(&empty_bar[st], ((i / kStages) - 1) & 1);
+      if (!ok) break;
+      const int tile = tile_of(i);
+      const int seq = tile / num_heads, head = tile % num_heads;
+      const long long tb = ((long long)seq * num_heads + head) * kD;  // one token per sequence
+      unsigned char* stage = smem + st * kStageBytes;
+      if (lane == 0) {
+        const __half* src = state_pool + ((long long)slot_of(i) * num_heads + head) * (kD * kD);
+        umma::mbar_expect_tx(&full_bar[st], kTileBytes);
         umma::bulk_g2s(stage, src, kTileBytes, &full_bar[st]);
-        umma::bulk_g2s(stage + kTileBytes + 0 * 128, r_ptr + tb, 128, &full_bar[st]);
-        umma::bulk_g2s(stage + kTileBytes + 1 * 128, w_ptr + tb, 128, &full_bar[st]);
-        umma::bulk_g2s(stage + kTileBytes + 2 * 128, k_ptr + tb, 128, &full_bar[st]);
-        umma::bulk_g2s(stage + kTileBytes + 3 * 128, v_ptr + tb, 128, &full_bar[st]);
-        umma::bulk_g2s(stage + kTileBytes + 4 * 128, a_ptr + tb, 128, &full_bar[st]);
-        umma::bulk_g2s(stage + kTileBytes + 5 * 128, b_ptr + tb, 128, &full_bar[st]);
       }
+      const uint32_t rows = umma::smem_u32(stage + kTileBytes);
+      umma::cp_async16(rows + lane * 16, row_src0 + tb + 8 * (lane & 7), 16u);
+      if (lane < 16) umma::cp_async16(rows + 512 + lane * 16, row_src1 + tb + 8 * (lane & 7), 16u);
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(umma::smem_u32(&full_bar[st])) : "memory");
     }
   } else if (warp == 1) {
     if (lane == 0) {  // storer
@@ -273,8 +287,8 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_fp16_decode_kernel(
         ok = umma::mbar_wait(&done_bar[st], (i / kStages) & 1);
         if (!ok) break;
         const int tile = tile_of(i);
-        const int seq = tile / num_heads, head = tile % num_heads;
-        __half* dst = state_pool + ((long long)state_indices[seq] * num_heads + head) * (kD * kD);
+        const int head = tile % num_heads;
+        __half* dst = state_pool + ((long long)slot_of(i) * num_heads + head) * (kD * kD);
         bulk_s2g(dst, smem + st * kStageBytes, kTileBytes);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         // at most one store may still be reading shared memory: the stage of tile i-1 is free again
@@ -293,7 +307,7 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_fp16_decode_kernel(
       const int st = i % kStages;
       const int tile = tile_of(i);
       const int seq = tile / num_heads, head = tile % num_heads;
-      const uint32_t phase0 = (uint32_t)(head * kD) + (uint32_t)elapsed_pool[state_indices[seq]];
+      const uint32_t phase0 = (uint32_t)(head * kD) + (uint32_t)(i < kMetaTiles ? elapsed_s[i] : elapsed_pool[slot_of(i)]);
       ok = umma::mbar_wait(&full_bar[st], (i / kStages) & 1);
       if (!ok) break;
       unsigned char* stage = smem + st * kStageBytes;

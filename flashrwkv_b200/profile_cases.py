@@ -8,6 +8,7 @@ matter, runs a handful of launches and exits, so that an `ncu` capture of one of
   train512  the same at B=8, T=512, H=64: 512 (sequence, head) pairs, the occupancy of the benchmark's training shape
   tmix    one TMix layer chain at C=2048 for M in (4, 512)
   decode  recurrent decode steps at B=256, H=32 (the benchmark's shape, 8 launches)
+  decode16  the same on an fp16 state pool
 """
 from __future__ import annotations
 
@@ -72,8 +73,21 @@ def case_decode(reps: int = 8):
                                                   validated_metadata=ticket, max_seqlen=1)
 
 
+def case_decode16(reps: int = 8):
+    B, H = 256, 32
+    cu, idx = synthetic.equal_length_metadata(B, 1, device="cuda")
+    pool = synthetic.state_pool(B, H, D, seed=5, device="cuda").half()
+    elapsed = torch.zeros(B, dtype=torch.int32, device="cuda")
+    toks = [t.cuda() for t in synthetic.wkv7_inputs(B, H, D, seed=6)]
+    ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=B, state_pool_size=B, max_seqlen=1)
+    for _ in range(reps):
+        F.infer_recurrent_fp16_forward_varlen(*toks, state_pool=pool, elapsed_state_pool=elapsed, cu_seqlens=cu,
+                                              state_indices=idx, validated_metadata=ticket, max_seqlen=1)
+        F.infer_recurrent_fp16_advance_i32(elapsed, 1)
+
+
 if __name__ == "__main__":
-    cases = {"chunk": case_chunk, "train": case_train, "train512": lambda: case_train(2, 8, 512, 64), "tmix": case_tmix, "decode": case_decode}
+    cases = {"chunk": case_chunk, "train": case_train, "train512": lambda: case_train(2, 8, 512, 64), "tmix": case_tmix, "decode": case_decode, "decode16": case_decode16}
     name = sys.argv[1] if len(sys.argv) > 1 else ""
     if name not in cases:
         raise SystemExit(__doc__)
