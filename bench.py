@@ -229,15 +229,28 @@ def _extras(dev):
     pool16 = synthetic.state_pool(B, H, D, seed=21, device=dev).half()
     elapsed = torch.zeros(B, dtype=torch.int32, device=dev)
     ring16 = [[t.to(dev) for t in synthetic.wkv7_inputs(B, H, D, seed=700 + i)] for i in range(TOKEN_RING)]
-    ticket16 = F.prepare_recurrent_metadata(cu1, idx1, total_tokens=B, state_pool_size=B, max_seqlen=1)
     n_steps = 128
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):  # the steps as one CUDA graph, as for the headline
+        ticket16 = F.prepare_recurrent_metadata(cu1, idx1, total_tokens=B, state_pool_size=B, max_seqlen=1)
 
-    def decode16():
-        for i in range(n_steps):
-            F.infer_recurrent_fp16_forward_varlen(*ring16[i % TOKEN_RING], state_pool=pool16,
-                                                  elapsed_state_pool=elapsed, cu_seqlens=cu1, state_indices=idx1,
-                                                  max_seqlen=1, validated_metadata=ticket16)
-            F.infer_recurrent_fp16_advance_i32(elapsed, 1)
+        def decode16_steps():
+            for i in range(n_steps):
+                F.infer_recurrent_fp16_forward_varlen(*ring16[i % TOKEN_RING], state_pool=pool16,
+                                                      elapsed_state_pool=elapsed, cu_seqlens=cu1, state_indices=idx1,
+                                                      max_seqlen=1, validated_metadata=ticket16)
+                F.infer_recurrent_fp16_advance_i32(elapsed, 1)
+
+        F.infer_recurrent_fp16_forward_varlen(*ring16[0], state_pool=pool16, elapsed_state_pool=elapsed,
+                                              cu_seqlens=cu1, state_indices=idx1, max_seqlen=1,
+                                              validated_metadata=ticket16)
+        torch.cuda.synchronize(dev)
+        graph16 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph16, stream=side):
+            decode16_steps()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    decode16 = graph16.replay
 
     sec = _time_cuda(decode16) / n_steps
     bytes16 = B * H * (2 * D * D * 2 + 7 * D * 2)
@@ -245,8 +258,8 @@ def _extras(dev):
         "workload": f"recurrent decode B={B} H={H} D={D}, bf16 tokens, fp16 state pool with dither, counters advanced "
                     f"every step", "tokens_per_s": B / sec, "us_per_step": sec * 1e6,
         "algorithmic_bytes_per_launch": bytes16, "hbm_frac_algorithmic": bytes16 / sec / hbm,
-        "gpu_launches_per_step": 2}
-    del pool16, ring16
+        "gpu_launches_per_step": 2, "launch": f"one CUDA graph of {n_steps} steps"}
+    del graph16, decode16, pool16, ring16
     # ---- chunked prefill
     Bc, T, Hc = 8, 4096, 32
     toks = [t.to(dev) for t in synthetic.wkv7_inputs(Bc * T, Hc, D, seed=11)]
@@ -364,8 +377,11 @@ def run_b200(args):
 
     cu, idx = (t.to(dev) for t in synthetic.equal_length_metadata(B, 1))
     pool = synthetic.state_pool(B, H, D, seed=1000 + rank, device=dev)
-    ring_host = [[t.pin_memory() for t in synthetic.wkv7_inputs(B, H, D, seed=20260805 + 97 * rank + i)]
-                 for i in range(TOKEN_RING)]
+    # each decode step's six token tensors live in one pinned host buffer [6, B, H, D] (what a serving host's staging
+    # area looks like); ring_host[i] are views of it
+    ring_packed = [torch.stack(synthetic.wkv7_inputs(B, H, D, seed=20260805 + 97 * rank + i)).pin_memory()
+                   for i in range(TOKEN_RING)]
+    ring_host = [list(p.unbind(0)) for p in ring_packed]
     ring = [[t.to(dev) for t in step] for step in ring_host]
     ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=B, state_pool_size=B, max_seqlen=1)
     kw = dict(state_pool=pool, cu_seqlens=cu, state_indices=idx, validated_metadata=ticket, max_seqlen=1)
@@ -373,6 +389,26 @@ def run_b200(args):
     def device_step():
         for i in range(DECODE_STEPS_PER_STEP):
             F.infer_recurrent_fp32io16_forward_varlen(*ring[i % TOKEN_RING], **kw)
+
+    # The 256 decode steps of a benchmark step as ONE CUDA graph (every operator taking a prepared ticket launches
+    # without host synchronisation, so the whole step captures); --no-graph launches them one by one from Python,
+    # which at 45 us per kernel is bound by the host's launch rate.
+    launch_mode = "256 Python launches per step"
+    if not args.no_graph:
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            g_ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=B, state_pool_size=B, max_seqlen=1)
+            g_kw = dict(kw, validated_metadata=g_ticket)  # a ticket is bound to the stream it was prepared on
+            F.infer_recurrent_fp32io16_forward_varlen(*ring[0], **g_kw)
+            torch.cuda.synchronize(dev)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(DECODE_STEPS_PER_STEP):
+                    F.infer_recurrent_fp32io16_forward_varlen(*ring[i % TOKEN_RING], **g_kw)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        device_step = graph.replay
+        launch_mode = "one CUDA graph of the 256 decode launches per step"
 
     # end to end: every decode step's six token tensors come from pinned host memory and its output goes back to
     # pinned host memory, through the package's three-stream host loop (copy-in / kernel / copy-out overlap)
@@ -383,7 +419,7 @@ def run_b200(args):
 
     def e2e_step():
         for i in range(DECODE_STEPS_PER_STEP):
-            host_loop.submit(ring_host[i % TOKEN_RING], y_hosts[i % len(y_hosts)])
+            host_loop.submit(ring_packed[i % TOKEN_RING], y_hosts[i % len(y_hosts)])
         host_loop.drain()
 
     def barrier():
@@ -436,7 +472,7 @@ def run_b200(args):
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"recurrent decode B={B} H={H} D={D} per GPU, bf16 tokens, fp32 state, "
                                    f"{DECODE_STEPS_PER_STEP} consecutive decode steps per step",
-                       "global_sequences": B * world, "parallelism": f"sequences sharded over {world} GPU(s)",
+                       "launch": launch_mode, "global_sequences": B * world, "parallelism": f"sequences sharded over {world} GPU(s)",
                        "l2": "no flush: per-launch working set (134 MB state + 7 MB tokens) exceeds the 126 MB L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
@@ -467,6 +503,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("b200", "reference"), default="b200")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads (prefill, training, TMix)")
+    ap.add_argument("--no-graph", action="store_true", help="launch the decode steps from Python instead of one CUDA graph")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for profiler runs)")
     args = ap.parse_args()

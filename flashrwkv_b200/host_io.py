@@ -37,7 +37,14 @@ class HostDecodeLoop:
         self._compute = torch.cuda.current_stream(dev)
         self._copy_in = torch.cuda.Stream(dev)
         self._copy_out = torch.cuda.Stream(dev)
-        self._stage = [[torch.empty(t.shape, dtype=t.dtype, device=dev) for t in example_inputs] for _ in range(depth)]
+        # one device buffer [6, N, H, D] per slot: six separate host tensors are copied into its rows, a host
+        # buffer of the same packed shape goes over in a single copy (one DMA descriptor instead of six)
+        first = example_inputs[0]
+        for t in example_inputs:
+            if t.shape != first.shape or t.dtype != first.dtype:
+                raise ValueError("the six token tensors must have one shape and dtype")
+        self._packed = [torch.empty((6, *first.shape), dtype=first.dtype, device=dev) for _ in range(depth)]
+        self._stage = [list(p.unbind(0)) for p in self._packed]
         self._outputs = [None] * depth
         self._loaded = [torch.cuda.Event() for _ in range(depth)]
         self._computed = [torch.cuda.Event() for _ in range(depth)]
@@ -45,15 +52,22 @@ class HostDecodeLoop:
         self._steps = 0
 
     def submit(self, host_inputs, host_output) -> None:
-        """Queue one decode step: `host_inputs` (six pinned tensors) in, `host_output` (pinned) out."""
+        """Queue one decode step: `host_inputs` in, `host_output` (pinned) out.
+
+        `host_inputs` is either six pinned tensors `(r, decay_logits, k, v, a, b)` or one pinned tensor
+        `[6, N, H, D]` holding them in that order (copied with a single transfer).
+        """
         slot = self._steps % self._depth
         reused = self._steps >= self._depth
         stage = self._stage[slot]
         if reused:
             self._copy_in.wait_event(self._computed[slot])  # the kernel that read this staging slot has finished
         with torch.cuda.stream(self._copy_in):
-            for d, s in zip(stage, host_inputs):
-                d.copy_(s, non_blocking=True)
+            if isinstance(host_inputs, torch.Tensor):
+                self._packed[slot].copy_(host_inputs, non_blocking=True)
+            else:
+                for d, s in zip(stage, host_inputs):
+                    d.copy_(s, non_blocking=True)
             self._loaded[slot].record(self._copy_in)
         self._compute.wait_event(self._loaded[slot])
         if reused:

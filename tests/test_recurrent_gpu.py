@@ -311,7 +311,8 @@ def test_host_decode_loop_is_bit_identical_to_serial_decode():
     loop = HostDecodeLoop(host[0], state_pool=pool_a, cu_seqlens=cu, state_indices=idx, validated_metadata=ticket)
     outs = [torch.empty((B, H, D), dtype=torch.bfloat16).pin_memory() for _ in range(steps)]
     for i in range(steps):
-        loop.submit(host[i], outs[i])
+        # six separate pinned tensors on even steps, one packed pinned buffer on odd ones
+        loop.submit(host[i] if i % 2 == 0 else torch.stack(host[i]).pin_memory(), outs[i])
     loop.drain()
     torch.cuda.synchronize()
     for i in range(steps):
