@@ -52,6 +52,15 @@ constexpr uint32_t kOffSC = kOffVT + 16 * kCS64P;    // scratch: g[t][k] (stride
 constexpr uint32_t kScratchBytes = 64 * 272;
 constexpr uint32_t kBuildSmem = kOffSC + kScratchBytes;  // 215,296 bytes
 constexpr uint32_t kAabRow = 272;
+constexpr uint32_t kOffOutEM = kOffX2;  // output staging: [E;M] (32 KB, chunk stride 2048) over the dead P|Q tile,
+constexpr uint32_t kOffOutFN = kOffVT;  // [F;N] over V^T and the scratch area
+static_assert(kOffSC + kScratchBytes - kOffVT >= kWsTile && kOffVT % 128 == 0, "the [F;N] staging area must fit");
+
+__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),
+               "r"(umma::smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
 
 __device__ __forceinline__ float4 ld4(const unsigned char* base, uint32_t off) {
   return *reinterpret_cast<const float4*>(base + off);
@@ -134,30 +143,32 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
   const uint32_t lane_base = uint32_t(32 * (warp & 3)) << 16;
   const uint32_t tcol = uint32_t(t >> 2), tsub = uint32_t(t & 3) * 4;
   bool ok = true;
+  bool stores_in_flight = false;  // thread 0 only
   uint32_t parity = 0;
 
-  // Stage the 16-bit token rows of an item in shared memory with cp.async (rows past the end of a short
-  // chunk are zero-filled).  The staging slots are the parts of RB / RK / AZ / TT that the item's own operands
-  // do not occupy until later phases, so the copies for the NEXT item start as soon as the last product of the
-  // current one has completed and overlap its final epilogue.  Each thread stages exactly what it consumes:
-  //   a|r : RB chunk (8*hsel + c), rows 0..63     b|k : RK chunk (8*hsel + c), rows 0..63      c = 2*quarter + {0,1}
-  //   v   : AZ chunk c, rows 64..127              w   : TT region, slot [part][t] (key channels 8*part..)
+  // Stage the 16-bit token rows of an item in shared memory with cp.async (rows past the end of a short chunk are
+  // zero-filled).  The staging slots are the parts of RB / RK / AZ / TT that the item's own operands do not occupy
+  // until later phases, so the copies for the NEXT item start as soon as the last product of the current one has
+  // completed and overlap its final epilogue.  Slot of the 16-byte piece (token t, key channels 8c..8c+7):
+  //   a : RB chunk c, row t        r : RB chunk 8 + c, row t       b : RK chunk c, row t      k : RK chunk 8 + c, row t
+  //   v : AZ chunk c, row 64 + t   w : TT region, slot [c][t]
+  // Thread i copies piece (t, c) = (i / 8, i % 8) of each tensor: eight consecutive lanes fetch one whole 128-byte
+  // row, so a warp's copy instruction is four full-line requests (one piece per lane of 32 different rows would be
+  // 32 half-used sector requests, and the request rate, not bandwidth, then bounds the staging).  The consumers
+  // read other threads' pieces, behind the barrier that follows the wait.
   auto stage_item = [&](int it) {
     const int ch = it / num_heads, hd = it % num_heads;
     const int tt0 = chunk_starts[ch];
     const int ln = min(max(chunk_ends[ch] - tt0, 1), kL);
-    const uint32_t nbytes = (t < ln) ? 16u : 0u;
-    const long long rw = ((long long)(tt0 + min(t, ln - 1)) * num_heads + hd) * kD;
-    const io_t* p0 = (hsel == 0 ? a_ptr : r_ptr) + rw;
-    const io_t* p1 = (hsel == 0 ? b_ptr : k_ptr) + rw;
-#pragma unroll
-    for (int cc = 0; cc < 2; ++cc) {
-      const int c = 2 * quarter + cc;
-      umma::cp_async16(sbase + kOffRB + uint32_t(8 * hsel + c) * kCS128P + t * 16, p0 + 8 * c, nbytes);
-      umma::cp_async16(sbase + kOffRK + uint32_t(8 * hsel + c) * kCS128P + t * 16, p1 + 8 * c, nbytes);
-      if (hsel == 1) umma::cp_async16(sbase + kOffAZ + uint32_t(c) * kCS128P + 1024 + t * 16, v_ptr + rw + 8 * c, nbytes);
-    }
-    umma::cp_async16(sbase + kOffTT + uint32_t(part) * 1024 + t * 16, w_ptr + rw + 8 * part, nbytes);
+    const int st = tid >> 3, sc = tid & 7;
+    const uint32_t nbytes = (st < ln) ? 16u : 0u;
+    const long long rw = ((long long)(tt0 + min(st, ln - 1)) * num_heads + hd) * kD + 8 * sc;
+    umma::cp_async16(sbase + kOffRB + uint32_t(sc) * kCS128P + st * 16, a_ptr + rw, nbytes);
+    umma::cp_async16(sbase + kOffRB + uint32_t(8 + sc) * kCS128P + st * 16, r_ptr + rw, nbytes);
+    umma::cp_async16(sbase + kOffRK + uint32_t(sc) * kCS128P + st * 16, b_ptr + rw, nbytes);
+    umma::cp_async16(sbase + kOffRK + uint32_t(8 + sc) * kCS128P + st * 16, k_ptr + rw, nbytes);
+    umma::cp_async16(sbase + kOffAZ + uint32_t(sc) * kCS128P + 1024 + st * 16, v_ptr + rw, nbytes);
+    umma::cp_async16(sbase + kOffTT + uint32_t(sc) * 1024 + st * 16, w_ptr + rw, nbytes);
     umma::cp_async_commit();
   };
   if ((int)blockIdx.x < num_items) stage_item(blockIdx.x);
@@ -169,7 +180,11 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     const bool valid = t < len;
 
     FRWKV_PHASE(0);
-    umma::cp_async_wait_all();  // this thread's staged rows have landed (each thread reads only its own)
+    umma::cp_async_wait_all();  // this thread's share of the staged rows has landed; the barrier below covers the rest
+    // the previous item's output tiles leave shared memory by bulk copies: they must have been read before this item
+    // overwrites the scratch area (next phase) and the P|Q tile (operand phase)
+    if (tid == 0 && stores_in_flight) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    __syncthreads();
     // ---- per-step retention for key channels 8*part .. 8*part+7 -> scratch [kc][t][4] ---------------
     {
       float x[8];
@@ -199,6 +214,20 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     }
     __syncthreads();
     FRWKV_PHASE(1);
+    // Pull the NEXT item's token rows into L2 now (one 128-byte line per thread: 6 tensors x 64 rows); the cp.async
+    // staging at the end of this item then finds them there.  A cp.async that misses L2 holds its issue slot for the
+    // whole DRAM round trip, which cost the last phase of every item more than its arithmetic.
+    if (tid < 6 * kL && item + (int)gridDim.x < num_items) {
+      const int nit = item + gridDim.x, nch = nit / num_heads, nhd = nit % num_heads;
+      const int nt0 = chunk_starts[nch];
+      const int nln = min(max(chunk_ends[nch] - nt0, 1), kL);
+      const int which = tid >> 6, row = tid & 63;
+      if (row < nln) {
+        const io_t* base = which == 0 ? a_ptr : which == 1 ? r_ptr : which == 2 ? b_ptr : which == 3 ? k_ptr
+                                                                       : which == 4 ? v_ptr : w_ptr;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(base + ((long long)(nt0 + row) * num_heads + nhd) * kD));
+      }
+    }
     // ---- cumulative decay g_t[k] down each key column: 128 threads, two per column ---------------------
     // (rows 0..31 and 32..63 are scanned separately, then the lower half is scaled by the upper total)
     if (tid < 128) {
@@ -448,11 +477,15 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     umma::fence_after_sync();
     FRWKV_PHASE(9);
     if (ok && item + (int)gridDim.x < num_items) stage_item(item + gridDim.x);
+    FRWKV_PHASE(12);
     if (ok) {
-      unsigned char* ws = workspace + (size_t)item * (2 * kWsTile);
+      // [E;M] and [F;N] are laid down in shared memory exactly as the workspace wants them ([E;M] over the P|Q tile,
+      // [F;N] over V^T and the scratch area, all dead by now) and leave with two bulk copies that drain while the
+      // next item starts.
       uint32_t u[32];
       umma::tmem_ld32(tmem + lane_base + 32 * colq, u);
       umma::tmem_ld_wait();
+      FRWKV_PHASE(13);
       const int cb = 32 * (colq & 1);
       if (colq < 2) {
 #pragma unroll
@@ -469,24 +502,34 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
             val.z += (mt == c + 2) ? diag_gl : 0.f;
             val.w += (mt == c + 3) ? diag_gl : 0.f;
           }
-          st4(ws, uint32_t(c >> 2) * kCS128 + m * 16, umma::to_tf32(val));
+          st4(smem, kOffOutEM + uint32_t(c >> 2) * kCS128 + m * 16, umma::to_tf32(val));
         }
       } else {
 #pragma unroll
         for (int jj = 0; jj < 32; jj += 4)
-          st4(ws, kWsTile + uint32_t((cb + jj) >> 2) * kCS128 + m * 16,
+          st4(smem, kOffOutFN + uint32_t((cb + jj) >> 2) * kCS128 + m * 16,
               make_float4(__uint_as_float(u[jj]), __uint_as_float(u[jj + 1]), __uint_as_float(u[jj + 2]),
                           __uint_as_float(u[jj + 3])));
       }
     }
     FRWKV_PHASE(10);
     // every thread is done with this item's shared memory and accumulators before the next item starts
+    umma::fence_async_smem();
     umma::fence_before_sync();
     ok = __syncthreads_and(ok) != 0;
     umma::fence_after_sync();
+    FRWKV_PHASE(11);
     if (!ok) break;
+    if (tid == 0) {
+      unsigned char* ws = workspace + (size_t)item * (2 * kWsTile);
+      bulk_s2g(ws, smem + kOffOutEM, kWsTile);
+      bulk_s2g(ws + kWsTile, smem + kOffOutFN, kWsTile);
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      stores_in_flight = true;
+    }
   }
   if (!ok && tid == 0 && error_flag != nullptr) atomicExch(error_flag, 1);
+  if (tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // output tiles are out before shared memory goes
   umma::cp_async_wait_all();
   umma::fence_before_sync();
   __syncthreads();
