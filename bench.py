@@ -299,10 +299,13 @@ def _extras(dev):
     g = torch.Generator().manual_seed(3)
     wt = lambda n, k: (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(dev)  # noqa: E731
     vec = lambda: torch.rand(C, generator=g).to(torch.bfloat16).to(dev)  # noqa: E731
-    Wr, Wk, Wv, Wo = (wt(C, C) for _ in range(4))
     ranks = {"w": 96, "a": 96, "g": 256, "v": 64}
-    w1 = {n: wt(r, C) for n, r in ranks.items()}
-    w2 = {n: wt(C, r) for n, r in ranks.items()}
+    # Four layers' weights (4 x 37.7 MB = 151 MB > the 126 MB L2), visited in turn: every layer streams its weights
+    # from HBM as in a real model, instead of finding the one set of a single layer in L2 on every replay.
+    n_layers = 4
+    layers = [{"Wr": wt(C, C), "Wk": wt(C, C), "Wv": wt(C, C), "Wo": wt(C, C),
+               "w1": {n: wt(r, C) for n, r in ranks.items()}, "w2": {n: wt(C, r) for n, r in ranks.items()}}
+              for _ in range(n_layers)]
     mixes = [vec() for _ in range(6)]
     k_k, a0, k_a, r_k, lnw, lnb, v0 = (vec() for _ in range(7))
     weight_bytes = 2 * (4 * C * C + 2 * C * sum(ranks.values()))
@@ -315,14 +318,22 @@ def _extras(dev):
         cu, idx = synthetic.equal_length_metadata(M, 1, device=dev)
         ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=M, state_pool_size=M, max_seqlen=1)
 
-        def layer():
-            xr, xw, xk, xv, xa, xg = F.infer_tmix_mix6_forward_varlen(x, *mixes, shift_state_pool=shift, cu_seqlens=cu,
-                                                                      state_indices=idx, max_seqlen=1,
-                                                                      validated_metadata=ticket)
-            r_ = F.infer_tmix_linear_forward_varlen(xr, Wr)
-            k_ = F.infer_tmix_linear_forward_varlen(xk, Wk)
-            v_ = F.infer_tmix_linear_forward_varlen(xv, Wv)
-            fw, fa, fg, fv = F.infer_tmix_lowrank_wagv_in_forward_varlen(xw, xa, xg, xv, w1["w"], w1["a"], w1["g"], w1["v"])
+        def layer(L, fused=False):
+            w1, w2 = L["w1"], L["w2"]
+            if fused:  # token shift inside the projections: r, k, v and the four rank-in products in one launch
+                r_, k_, v_, fw, fa, fg, fv = F.infer_tmix_shift_project_forward_varlen(
+                    x, [mixes[0], mixes[2], mixes[3], mixes[1], mixes[4], mixes[5], mixes[3]],
+                    [L["Wr"], L["Wk"], L["Wv"], w1["w"], w1["a"], w1["g"], w1["v"]], shift_state_pool=shift,
+                    cu_seqlens=cu, state_indices=idx, max_seqlen=1, validated_metadata=ticket)
+            else:      # the reference's operator sequence
+                xr, xw, xk, xv, xa, xg = F.infer_tmix_mix6_forward_varlen(x, *mixes, shift_state_pool=shift,
+                                                                          cu_seqlens=cu, state_indices=idx, max_seqlen=1,
+                                                                          validated_metadata=ticket)
+                r_ = F.infer_tmix_linear_forward_varlen(xr, L["Wr"])
+                k_ = F.infer_tmix_linear_forward_varlen(xk, L["Wk"])
+                v_ = F.infer_tmix_linear_forward_varlen(xv, L["Wv"])
+                fw, fa, fg, fv = F.infer_tmix_lowrank_wagv_in_forward_varlen(xw, xa, xg, xv, w1["w"], w1["a"], w1["g"],
+                                                                            w1["v"])
             w_, a12, g_, vres = F.infer_tmix_lowrank_vres_forward_varlen(fw, fa, fg, fv, w2["w"], w2["a"], w2["g"], w2["v"],
                                                                         v_, v_first, v0)
             kk_, nkk, kka = F.infer_tmix_kk_a_gate_forward_varlen(k_, k_k, a0, a12, k_a)
@@ -331,24 +342,36 @@ def _extras(dev):
                                                           nkk.view(sh), kka.view(sh), state_pool=spool, cu_seqlens=cu,
                                                           state_indices=idx, validated_metadata=ticket, max_seqlen=1)
             z = F.infer_tmix_lnx_rkvres_xg_forward_varlen(y.view(M, C), r_, kk_, vres, r_k, lnw, lnb, g_)
-            return F.infer_tmix_linear_forward_varlen(z, Wo)
+            return F.infer_tmix_linear_forward_varlen(z, L["Wo"])
 
-        sec = _time_cuda(layer, warmup=3, iters=20)
-        # the same 11 launches replayed from a CUDA graph: device time without the per-call host work
+        def stack(fused=False):
+            for L in layers:
+                layer(L, fused)
+
+        sec = _time_cuda(stack, warmup=3, iters=10) / n_layers
+        # the same launches replayed from a CUDA graph: device time without the per-call host work
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
+        gsecs = {}
         with torch.cuda.stream(side):
             gticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=M, state_pool_size=M, max_seqlen=1)
             ticket = gticket
-            layer()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
-                layer()
-            gsec = _time_cuda(graph.replay, warmup=3, iters=50)
+            for fused in (False, True):
+                stack(fused)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    stack(fused)
+                gsecs[fused] = _time_cuda(graph.replay, warmup=3, iters=30) / n_layers
+                del graph
         torch.cuda.current_stream().wait_stream(side)
-        entry = {"us_per_layer": sec * 1e6, "us_per_layer_cuda_graph": gsec * 1e6, "gpu_launches_per_layer": 11}
+        gsec = gsecs[False]
+        entry = {"us_per_layer": sec * 1e6, "us_per_layer_cuda_graph": gsec * 1e6, "gpu_launches_per_layer": 11,
+                 "us_per_layer_fused_shift_cuda_graph": gsecs[True] * 1e6,
+                 "gpu_launches_per_layer_fused_shift": 7 if M <= 8 else 10,
+                 "l2": f"{n_layers} layers' weights ({n_layers * weight_bytes / 1e6:.0f} MB) visited in turn: larger than L2"}
         if M <= 7:
             entry["weight_hbm_frac_cuda_graph"] = weight_bytes / gsec / hbm
+            entry["weight_hbm_frac_fused_shift_cuda_graph"] = weight_bytes / gsecs[True] / hbm
         else:
             entry["tensor_frac_of_bf16_peak_cuda_graph"] = 2 * M * (4 * C * C + 2 * C * sum(ranks.values())) / gsec / bf16
         tmix[f"M={M}"] = entry

@@ -21,13 +21,14 @@ from .tmix.kk_a_gate import infer_tmix_kk_a_gate_forward_varlen
 from .tmix.linear import *  # noqa: F401,F403
 from .tmix.linear import __all__ as _linear_all
 from .tmix.lnx_rkvres_xg import infer_tmix_lnx_rkvres_xg_forward_varlen
-from .tmix.mix6 import infer_tmix_mix6_forward_varlen
+from .tmix.mix6 import infer_tmix_mix6_forward_varlen, infer_tmix_shift_project_forward_varlen
 from .tmix.vres_gate import infer_tmix_vres_gate_forward_varlen
 
 __all__ = [
     "infer_tmix_kk_a_gate_forward_varlen",
     "infer_tmix_lnx_rkvres_xg_forward_varlen",
     "infer_tmix_mix6_forward_varlen",
+    "infer_tmix_shift_project_forward_varlen",
     "infer_tmix_vres_gate_forward_varlen",
     *_linear_all,
     "infer_chunk_bf16_forward_varlen",

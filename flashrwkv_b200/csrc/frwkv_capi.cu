@@ -1,4 +1,5 @@
 // Error bookkeeping and version query of the C ABI.
+#include <cstdlib>
 #include "frwkv_common.cuh"
 
 #include <cstring>
@@ -16,6 +17,14 @@ void set_error(const char* fmt, ...) {
 }
 
 void clear_error() { g_error[0] = '\0'; }
+
+bool chained_launch_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("FRWKV_DISABLE_CHAINED_LAUNCH");
+    return !(e != nullptr && e[0] == '1');
+  }();
+  return on;
+}
 
 }  // namespace frwkv
 

@@ -103,4 +103,33 @@ __device__ __forceinline__ float retention_log_derivative(float decay_logit) {
 
 __device__ __forceinline__ float quiet_nan() { return __int_as_float(0x7fffffff); }
 
+// ---- programmatic dependent launch -------------------------------------------------------------------------------
+// The short kernels of a decode step run back to back in one stream and each is bound by launch latency rather than
+// by its work.  A kernel launched with launch_chained() may start while its predecessor is still running; it calls
+// chain_begin() first, which lets ITS successor be scheduled early and then waits until everything before it in the
+// stream has completed and is visible.  Nothing is read or written before that wait, so the overlap covers only
+// launch and scheduling latency.  Both instructions do nothing in a kernel launched the ordinary way.
+__device__ __forceinline__ void chain_begin() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+bool chained_launch_enabled();  // false when FRWKV_DISABLE_CHAINED_LAUNCH=1 (for comparisons)
+
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KernelArgs>(args)...);
+}
+
 }  // namespace frwkv

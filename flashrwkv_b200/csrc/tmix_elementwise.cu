@@ -49,6 +49,7 @@ __global__ void mix6_kernel(const io_t* __restrict__ x, io_t* __restrict__ shift
                             const int* __restrict__ cu_seqlens, const int* __restrict__ state_indices,
                             const int* __restrict__ status, io_t* __restrict__ out, int num_sequences,
                             long long total_rows, int C) {
+  chain_begin();
   const long long row = blockIdx.x;
   const int vecs = C >> 3;
   if (status != nullptr && status[0] != 0) {
@@ -97,11 +98,12 @@ __global__ void mix6_kernel(const io_t* __restrict__ x, io_t* __restrict__ shift
 template <typename io_t>
 __global__ void mix6_shift_update_kernel(const io_t* __restrict__ x, io_t* __restrict__ shift_pool,
                                          const int* __restrict__ cu_seqlens, const int* __restrict__ state_indices,
-                                         const int* __restrict__ status, int C) {
+                                         const int* __restrict__ status, int C, int min_len) {
+  chain_begin();
   if (status != nullptr && status[0] != 0) return;
   const int s = blockIdx.x;
   const int t0 = cu_seqlens[s], t1 = cu_seqlens[s + 1];
-  if (t1 - t0 <= 1) return;  // handled by mix6_kernel
+  if (t1 - t0 < min_len) return;  // after mix6_kernel (min_len = 2): it has stored the rows of one-token sequences
   const uint4* src = reinterpret_cast<const uint4*>(x + (long long)(t1 - 1) * C);
   uint4* dst = reinterpret_cast<uint4*>(shift_pool + (long long)state_indices[s] * C);
   for (int i = threadIdx.x; i < (C >> 3); i += blockDim.x) dst[i] = src[i];
@@ -112,6 +114,7 @@ template <typename io_t>
 __global__ void kk_a_gate_kernel(const io_t* __restrict__ k, const io_t* __restrict__ k_k, const io_t* __restrict__ a0,
                                  const io_t* __restrict__ a12, const io_t* __restrict__ k_a, io_t* __restrict__ new_k,
                                  io_t* __restrict__ neg_kk, io_t* __restrict__ kka, long long units, int H) {
+  chain_begin();
   using IO = Io16<io_t>;
   const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= units) return;
@@ -139,6 +142,7 @@ __global__ void lnx_rkvres_xg_kernel(const io_t* __restrict__ x, const io_t* __r
                                      const io_t* __restrict__ weight, const io_t* __restrict__ bias,
                                      const io_t* __restrict__ g, io_t* __restrict__ out, long long units, int H,
                                      float eps) {
+  chain_begin();
   using IO = Io16<io_t>;
   const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= units) return;
@@ -167,6 +171,7 @@ template <typename io_t>
 __global__ void vres_gate_kernel(const io_t* __restrict__ v, const io_t* __restrict__ v_first,
                                  const io_t* __restrict__ v0, const io_t* __restrict__ v12, io_t* __restrict__ out,
                                  long long vec_total, int vecs_per_row) {
+  chain_begin();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < vec_total;
        i += (long long)gridDim.x * blockDim.x) {
     float a[8], f[8], z[8], t[8];
@@ -182,6 +187,7 @@ __global__ void vres_gate_kernel(const io_t* __restrict__ v, const io_t* __restr
 
 template <typename io_t>
 __global__ void act_kernel(const io_t* __restrict__ x, io_t* __restrict__ out, long long vec_total, int act) {
+  chain_begin();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < vec_total;
        i += (long long)gridDim.x * blockDim.x) {
     float a[8];
@@ -206,6 +212,20 @@ __global__ void act_kernel(const io_t* __restrict__ x, io_t* __restrict__ out, l
     return ::frwkv::fail(FRWKV_ERR_UNSUPPORTED, NAME ": tensors must be float16 or bfloat16");   \
   }
 
+namespace frwkv {
+int launch_shift_state_update(const void* x, void* shift_state_pool, const int* cu_seqlens, const int* state_indices,
+                              const int* metadata_status, int num_sequences, int channels, int io_dtype,
+                              cudaStream_t s) {
+  const int threads = channels / 8 >= 256 ? 256 : (channels / 8 >= 128 ? 128 : 64);
+  FRWKV_DISPATCH_IO(io_dtype, "tmix_shift_update", {
+    launch_chained(mix6_shift_update_kernel<io_t>, dim3((unsigned)num_sequences), dim3(threads), 0, s,
+                   static_cast<const io_t*>(x), static_cast<io_t*>(shift_state_pool), cu_seqlens, state_indices,
+                   metadata_status, channels, 1);
+    return check_launch("mix6_shift_update_kernel");
+  })
+}
+}  // namespace frwkv
+
 extern "C" int frwkv_tmix_mix6_forward_varlen(const void* x, void* shift_state_pool, const void* x_r, const void* x_w,
                                               const void* x_k, const void* x_v, const void* x_a, const void* x_g,
                                               const int32_t* cu_seqlens, const int32_t* state_indices,
@@ -222,15 +242,15 @@ extern "C" int frwkv_tmix_mix6_forward_varlen(const void* x, void* shift_state_p
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int threads = channels / 8 >= 256 ? 256 : (channels / 8 >= 128 ? 128 : 64);
   FRWKV_DISPATCH_IO(io_dtype, "tmix_mix6", {
-    mix6_kernel<io_t><<<(unsigned)total_rows, threads, 0, s>>>(
+    launch_chained(mix6_kernel<io_t>, dim3((unsigned)total_rows), dim3(threads), 0, s, 
         static_cast<const io_t*>(x), static_cast<io_t*>(shift_state_pool), mix6, cu_seqlens,
         state_indices, metadata_status, static_cast<io_t*>(out), num_sequences, (long long)total_rows, channels);
     int rc = check_launch("mix6_kernel");
     if (rc != FRWKV_OK) return rc;
     if (max_seqlen != 1) {  // unknown (<= 0) or longer than one token: some slot may still need its last row
-      mix6_shift_update_kernel<io_t><<<(unsigned)num_sequences, threads, 0, s>>>(
+      launch_chained(mix6_shift_update_kernel<io_t>, dim3((unsigned)num_sequences), dim3(threads), 0, s, 
           static_cast<const io_t*>(x), static_cast<io_t*>(shift_state_pool), cu_seqlens, state_indices,
-          metadata_status, channels);
+          metadata_status, channels, 2);
       return check_launch("mix6_shift_update_kernel");
     }
     return FRWKV_OK;
@@ -253,7 +273,7 @@ extern "C" int frwkv_tmix_kk_a_gate_forward_varlen(const void* k, const void* k_
   FRWKV_REQUIRE(blocks <= 0x7fffffffLL, "tmix_kk_a_gate: too many rows");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_DISPATCH_IO(io_dtype, "tmix_kk_a_gate", {
-    kk_a_gate_kernel<io_t><<<(unsigned)blocks, 256, 0, s>>>(
+    launch_chained(kk_a_gate_kernel<io_t>, dim3((unsigned)blocks), dim3(256), 0, s, 
         static_cast<const io_t*>(k), static_cast<const io_t*>(k_k), static_cast<const io_t*>(a0),
         static_cast<const io_t*>(a12), static_cast<const io_t*>(k_a), static_cast<io_t*>(new_k),
         static_cast<io_t*>(neg_kk), static_cast<io_t*>(kka), units, H);
@@ -277,7 +297,7 @@ extern "C" int frwkv_tmix_lnx_rkvres_xg_forward_varlen(const void* x, const void
   FRWKV_REQUIRE(blocks <= 0x7fffffffLL, "tmix_lnx_rkvres_xg: too many rows");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_DISPATCH_IO(io_dtype, "tmix_lnx_rkvres_xg", {
-    lnx_rkvres_xg_kernel<io_t><<<(unsigned)blocks, 256, 0, s>>>(
+    launch_chained(lnx_rkvres_xg_kernel<io_t>, dim3((unsigned)blocks), dim3(256), 0, s, 
         static_cast<const io_t*>(x), static_cast<const io_t*>(r), static_cast<const io_t*>(k),
         static_cast<const io_t*>(v), static_cast<const io_t*>(r_k), static_cast<const io_t*>(weight),
         static_cast<const io_t*>(bias), static_cast<const io_t*>(g), static_cast<io_t*>(out), units, H, eps);
@@ -298,7 +318,7 @@ extern "C" int frwkv_tmix_vres_gate_forward_varlen(const void* v, const void* v_
   if (blocks > 148 * 16) blocks = 148 * 16;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_DISPATCH_IO(io_dtype, "tmix_vres_gate", {
-    vres_gate_kernel<io_t><<<(unsigned)blocks, 256, 0, s>>>(
+    launch_chained(vres_gate_kernel<io_t>, dim3((unsigned)blocks), dim3(256), 0, s, 
         static_cast<const io_t*>(v), static_cast<const io_t*>(v_first), static_cast<const io_t*>(v0),
         static_cast<const io_t*>(v12), static_cast<io_t*>(out), vec_total, channels / 8);
     return check_launch("vres_gate_kernel");
@@ -317,7 +337,7 @@ extern "C" int frwkv_tmix_act_forward(const void* x, void* out, long long elemen
   if (blocks > 148 * 16) blocks = 148 * 16;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_DISPATCH_IO(io_dtype, "tmix_act", {
-    act_kernel<io_t><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const io_t*>(x), static_cast<io_t*>(out), vec_total, act);
+    launch_chained(act_kernel<io_t>, dim3((unsigned)blocks), dim3(256), 0, s, static_cast<const io_t*>(x), static_cast<io_t*>(out), vec_total, act);
     return check_launch("act_kernel");
   })
 }

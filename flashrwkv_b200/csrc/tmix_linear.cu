@@ -2,9 +2,9 @@
 // low-rank projections of a TMix layer (decay / a / gate / value-residual) go out in one launch.
 //
 // Two kernels, picked by the row count:
-//   * M <= 8 ("skinny", decode): weight-bandwidth bound.  x is staged once per CTA in shared memory with the
+//   * M <= 8 ("skinny", decode): weight-bandwidth bound.  x is staged once per CTA in shared memory as fp32 with the
 //     activation applied; every weight element is read exactly once with 16-byte loads.  For long rows (K >= 256) a
-//     warp owns an output column and reduces with shuffles; for short rows (rank-out, K = rank) a thread owns it.
+//     warp owns two output columns at a time and reduces with shuffles; for short rows (rank-out) a thread owns one.
 //   * M > 8: tcgen05 tensor-core GEMM (kind::f16, fp32 accumulate in tensor memory).  Problems without an activation
 //     on x go to the TMA-fed persistent kernel of tmix_gemm_tma.cu; the kernel here (128 x 64 output tile per CTA, K in
 //     blocks of 64 through a 4-stage cp.async pipeline into chunk-major tiles, see umma.cuh) applies tanh / sigmoid
@@ -24,55 +24,74 @@ namespace frwkv {
 namespace {
 
 // ---- skinny kernel --------------------------------------------------------------------------------------
-// grid = (column blocks, problems); dynamic shared memory = M * K 16-bit values (activation applied).
+// grid = (column blocks, problems); dynamic shared memory = M * K fp32 values of x (activation applied): unpacking the
+// 16-bit x once per CTA instead of once per weight row is what keeps M = 4..8 bound by the weight stream rather than
+// by instruction issue.  Long rows (K >= 256): a warp owns two output columns at a time (two independent 16-byte
+// weight loads in flight per lane, every x value used twice) and reduces with shuffles.  Short rows (rank-out,
+// K = rank): a thread owns a column.
+constexpr int kSkinnyDepth = 8;  // 16-byte weight pieces per row and lane in flight at once
+
+// the products of one CTA: xs / xs_hi hold x as fp32 (see linear_skinny_kernel)
 template <typename io_t, int M>
-__global__ __launch_bounds__(256) void linear_skinny_kernel(LinearGroup group) {
+__device__ __forceinline__ void skinny_products(const LinearProblem& pr, const float4* xs, const float4* xs_hi) {
   using IO = Io16<io_t>;
-  extern __shared__ __align__(16) unsigned char xs_raw[];
-  const LinearProblem& pr = group.p[blockIdx.y];
   const int K = pr.k, N = pr.n, kv = K >> 3;
-  uint4* xs = reinterpret_cast<uint4*>(xs_raw);
-  for (int i = threadIdx.x; i < M * kv; i += blockDim.x) {
-    uint4 u = __ldg(reinterpret_cast<const uint4*>(pr.x) + i);
-    if (pr.act != 0) {
-      float f[8];
-      unpack8<io_t>(u, f);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = apply_act(f[e], pr.act);
-      u = make_uint4(IO::pack(f[0], f[1]), IO::pack(f[2], f[3]), IO::pack(f[4], f[5]), IO::pack(f[6], f[7]));
-    }
-    xs[i] = u;
-  }
-  __syncthreads();
   const io_t* w = static_cast<const io_t*>(pr.w);
   io_t* y = static_cast<io_t*>(pr.y);
   if (K >= 256) {
     const int lane = threadIdx.x & 31;
     const int warps_total = gridDim.x * (blockDim.x >> 5);
-    for (int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); n < N; n += warps_total) {
-      float acc[M];
+    // N is a multiple of 8, so a pair of columns (n, n + 1) with n even is always complete
+    for (int n = 2 * (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)); n < N; n += 2 * warps_total) {
+      float acc0[M], acc1[M];
 #pragma unroll
-      for (int m = 0; m < M; ++m) acc[m] = 0.f;
-      const uint4* wrow = reinterpret_cast<const uint4*>(w + (long long)n * K);
-      for (int c = lane; c < kv; c += 32) {
-        float wf[8];
-        unpack8<io_t>(__ldg(wrow + c), wf);
+      for (int m = 0; m < M; ++m) { acc0[m] = 0.f; acc1[m] = 0.f; }
+      const uint4* wrow0 = reinterpret_cast<const uint4*>(w + (long long)n * K);
+      const uint4* wrow1 = reinterpret_cast<const uint4*>(w + (long long)(n + 1) * K);
+      // All weight loads of a block of 8 x 32 sixteen-byte pieces per row are issued before the first one is used:
+      // with one or two CTAs per SM the kernel lives on the number of loads in flight, not on arithmetic.
+      for (int cb = lane; cb < kv; cb += 32 * kSkinnyDepth) {
+        uint4 q0[kSkinnyDepth], q1[kSkinnyDepth];
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-          float xf[8];
-          unpack8<io_t>(xs[m * kv + c], xf);
+        for (int j = 0; j < kSkinnyDepth; ++j) {
+          const int c = cb + 32 * j;
+          if (c < kv) {
+            q0[j] = __ldg(wrow0 + c);
+            q1[j] = __ldg(wrow1 + c);
+          }
+        }
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[m] = fmaf(wf[e], xf[e], acc[m]);
+        for (int j = 0; j < kSkinnyDepth; ++j) {
+          const int c = cb + 32 * j;
+          if (c < kv) {
+            float w0[8], w1[8];
+            unpack8<io_t>(q0[j], w0);
+            unpack8<io_t>(q1[j], w1);
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+              const float4 xa = xs[m * kv + c], xb = xs_hi[m * kv + c];
+              acc0[m] = fmaf(w0[0], xa.x, fmaf(w0[1], xa.y, fmaf(w0[2], xa.z, fmaf(w0[3], xa.w, acc0[m]))));
+              acc0[m] = fmaf(w0[4], xb.x, fmaf(w0[5], xb.y, fmaf(w0[6], xb.z, fmaf(w0[7], xb.w, acc0[m]))));
+              acc1[m] = fmaf(w1[0], xa.x, fmaf(w1[1], xa.y, fmaf(w1[2], xa.z, fmaf(w1[3], xa.w, acc1[m]))));
+              acc1[m] = fmaf(w1[4], xb.x, fmaf(w1[5], xb.y, fmaf(w1[6], xb.z, fmaf(w1[7], xb.w, acc1[m]))));
+            }
+          }
         }
       }
 #pragma unroll
       for (int m = 0; m < M; ++m) {
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+        for (int o = 16; o > 0; o >>= 1) {
+          acc0[m] += __shfl_xor_sync(0xffffffffu, acc0[m], o);
+          acc1[m] += __shfl_xor_sync(0xffffffffu, acc1[m], o);
+        }
       }
       if (lane == 0) {
 #pragma unroll
-        for (int m = 0; m < M; ++m) y[(long long)m * N + n] = IO::store(finish<io_t>(pr, acc[m], m, n));
+        for (int m = 0; m < M; ++m) {
+          const uint32_t two = IO::pack(finish<io_t>(pr, acc0[m], m, n), finish<io_t>(pr, acc1[m], m, n + 1));
+          *reinterpret_cast<uint32_t*>(y + (long long)m * N + n) = two;
+        }
       }
     }
   } else {
@@ -86,16 +105,103 @@ __global__ __launch_bounds__(256) void linear_skinny_kernel(LinearGroup group) {
         unpack8<io_t>(__ldg(wrow + c), wf);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-          float xf[8];
-          unpack8<io_t>(xs[m * kv + c], xf);  // same address for the whole warp: broadcast
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[m] = fmaf(wf[e], xf[e], acc[m]);
+          // same address for the whole warp: broadcast
+          const float4 xa = xs[m * kv + c], xb = xs_hi[m * kv + c];
+          acc[m] = fmaf(wf[0], xa.x, fmaf(wf[1], xa.y, fmaf(wf[2], xa.z, fmaf(wf[3], xa.w, acc[m]))));
+          acc[m] = fmaf(wf[4], xb.x, fmaf(wf[5], xb.y, fmaf(wf[6], xb.z, fmaf(wf[7], xb.w, acc[m]))));
         }
       }
 #pragma unroll
       for (int m = 0; m < M; ++m) y[(long long)m * N + n] = IO::store(finish<io_t>(pr, acc[m], m, n));
     }
   }
+}
+
+template <typename io_t, int M>
+__global__ __launch_bounds__(256) void linear_skinny_kernel(LinearGroup group) {
+  chain_begin();
+  using IO = Io16<io_t>;
+  extern __shared__ __align__(16) unsigned char xs_raw[];
+  const LinearProblem& pr = group.p[blockIdx.y];
+  const int kv = pr.k >> 3;
+  // fp32 x as two planes of float4: plane 0 holds elements 8c..8c+3 of row m at [m*kv + c], plane 1 elements 8c+4..8c+7
+  // (consecutive lanes then read consecutive 16-byte words: no bank conflicts)
+  float4* xs = reinterpret_cast<float4*>(xs_raw);
+  float4* xs_hi = xs + M * kv;
+  for (int i = threadIdx.x; i < M * kv; i += blockDim.x) {
+    float f[8];
+    unpack8<io_t>(__ldg(reinterpret_cast<const uint4*>(pr.x) + i), f);
+    if (pr.act != 0) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = apply_act(f[e], pr.act);
+    }
+    xs[i] = make_float4(f[0], f[1], f[2], f[3]);
+    xs_hi[i] = make_float4(f[4], f[5], f[6], f[7]);
+  }
+  __syncthreads();
+  skinny_products<io_t, M>(pr, xs, xs_hi);
+}
+
+// ---- token shift fused into the projections (decode) -------------------------------------------------------------
+// y_j = (x + (prev - x) * mix_j) W_j^T for up to eight projections of the same rows x in one launch: the six-way
+// token-shift interpolation (mix6) happens while x is staged, in fp32, instead of in a kernel of its own that writes
+// six [M, C] tensors for the projections to read back.  prev is the previous row of the same sequence, or the
+// sequence's shift state for its first row.  The shift states are updated by a separate small kernel afterwards
+// (every CTA here reads them).  grid = (column blocks, projections).
+constexpr int kMaxShiftProjections = 8;
+struct ShiftProjection {
+  const void* mix;  // [C]
+  const void* w;    // [N][C]
+  void* y;          // [M][N]
+  int n;
+};
+struct ShiftProjectGroup {
+  ShiftProjection p[kMaxShiftProjections];
+};
+
+template <typename io_t, int M>
+__global__ __launch_bounds__(256) void shift_project_kernel(ShiftProjectGroup group, const io_t* __restrict__ x,
+                                                            const io_t* __restrict__ shift_pool,
+                                                            const int* __restrict__ cu_seqlens,
+                                                            const int* __restrict__ state_indices,
+                                                            const int* __restrict__ status, int num_sequences, int C) {
+  chain_begin();
+  using IO = Io16<io_t>;
+  extern __shared__ __align__(16) unsigned char xs_raw[];
+  __shared__ const io_t* prev_row[M];
+  const ShiftProjection& sp = group.p[blockIdx.y];
+  const int kv = C >> 3;
+  io_t* y = static_cast<io_t*>(sp.y);
+  if (status != nullptr && status[0] != 0) {  // fail closed: NaN outputs
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < M * sp.n; i += gridDim.x * blockDim.x)
+      y[i] = IO::store(quiet_nan());
+    return;
+  }
+  if (threadIdx.x < M) {
+    const int row = threadIdx.x;
+    int seq = 0;
+    while (seq + 1 < num_sequences && cu_seqlens[seq + 1] <= row) ++seq;  // at most eight rows: a linear search
+    prev_row[row] = row == cu_seqlens[seq] ? shift_pool + (long long)state_indices[seq] * C
+                                           : x + (long long)(row - 1) * C;
+  }
+  __syncthreads();
+  float4* xs = reinterpret_cast<float4*>(xs_raw);
+  float4* xs_hi = xs + M * kv;
+  const uint4* mixv = reinterpret_cast<const uint4*>(sp.mix);
+  for (int i = threadIdx.x; i < M * kv; i += blockDim.x) {
+    const int m = i / kv, c = i - m * kv;
+    float xf[8], pf[8], mf[8];
+    unpack8<io_t>(__ldg(reinterpret_cast<const uint4*>(x) + i), xf);
+    unpack8<io_t>(__ldg(reinterpret_cast<const uint4*>(prev_row[m]) + c), pf);
+    unpack8<io_t>(__ldg(mixv + c), mf);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) xf[e] = fmaf(pf[e] - xf[e], mf[e], xf[e]);
+    xs[i] = make_float4(xf[0], xf[1], xf[2], xf[3]);
+    xs_hi[i] = make_float4(xf[4], xf[5], xf[6], xf[7]);
+  }
+  __syncthreads();
+  const LinearProblem pr{x, sp.w, sp.y, nullptr, nullptr, nullptr, sp.n, C, 0, 0};
+  skinny_products<io_t, M>(pr, xs, xs_hi);
 }
 
 // ---- tensor-core kernel -----------------------------------------------------------------------------------
@@ -232,8 +338,8 @@ __global__ __launch_bounds__(128, 2) void linear_tc_kernel(LinearGroup group, in
 template <typename io_t>
 int launch_linear(const LinearGroup& g, int count, int M, int max_n, int max_k, int* error_flag, cudaStream_t stream) {
   if (M <= 8) {
-    const size_t smem = (size_t)M * max_k * 2;
-    const int blocks = max_k >= 256 ? (max_n + 7) / 8 : (max_n + 255) / 256;
+    const size_t smem = (size_t)M * max_k * 4;
+    const int blocks = max_k >= 256 ? (max_n + 15) / 16 : (max_n + 255) / 256;
     dim3 grid(blocks < 1 ? 1 : blocks, count);
 #define FRWKV_SKINNY(MM)                                                                                      \
   case MM: {                                                                                                  \
@@ -242,7 +348,7 @@ int launch_linear(const LinearGroup& g, int count, int M, int max_n, int max_k, 
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
       if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "tmix_linear: %s", cudaGetErrorString(e));            \
     }                                                                                                         \
-    linear_skinny_kernel<io_t, MM><<<grid, 256, smem, stream>>>(g);                                           \
+    launch_chained(linear_skinny_kernel<io_t, MM>, grid, dim3(256), smem, stream, g);                                         \
     break;                                                                                                    \
   }
     switch (M) {
@@ -283,7 +389,7 @@ extern "C" int frwkv_tmix_linear_grouped(const frwkv_linear_problem* problems, i
     max_k = p.k > max_k ? p.k : max_k;
   }
   for (int i = count; i < kMaxProblems; ++i) g.p[i] = g.p[0];
-  if (m <= 8) FRWKV_REQUIRE((size_t)m * max_k * 2 <= 200 * 1024, "tmix_linear: K too large for the small-row kernel");
+  if (m <= 8) FRWKV_REQUIRE((size_t)m * max_k * 4 <= 200 * 1024, "tmix_linear: K too large for the small-row kernel");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (io_dtype != FRWKV_DTYPE_BF16 && io_dtype != FRWKV_DTYPE_FP16)
     return fail(FRWKV_ERR_UNSUPPORTED, "tmix_linear: tensors must be float16 or bfloat16");
@@ -293,4 +399,62 @@ extern "C" int frwkv_tmix_linear_grouped(const frwkv_linear_problem* problems, i
   if (io_dtype == FRWKV_DTYPE_BF16) return launch_linear<__nv_bfloat16>(g, count, m, max_n, max_k, error_flag, s);
   if (io_dtype == FRWKV_DTYPE_FP16) return launch_linear<__half>(g, count, m, max_n, max_k, error_flag, s);
   return fail(FRWKV_ERR_UNSUPPORTED, "tmix_linear: tensors must be float16 or bfloat16");
+}
+
+extern "C" int frwkv_tmix_shift_project_varlen(const void* x, void* shift_state_pool, const int32_t* cu_seqlens,
+                                               const int32_t* state_indices, const int32_t* metadata_status,
+                                               const frwkv_shift_projection* projections, int count, int total_rows,
+                                               int num_sequences, int channels, int io_dtype, frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(x && shift_state_pool && cu_seqlens && state_indices && projections,
+                "tmix_shift_project: null pointer argument");
+  FRWKV_REQUIRE(count >= 1 && count <= kMaxShiftProjections, "tmix_shift_project: 1..8 projections per call");
+  FRWKV_REQUIRE(total_rows >= 1 && total_rows <= 8, "tmix_shift_project: 1..8 rows (more rows: mix6, then the GEMM)");
+  FRWKV_REQUIRE(num_sequences >= 1 && num_sequences <= total_rows, "tmix_shift_project: bad sequence count");
+  FRWKV_REQUIRE(channels >= 256 && channels % 8 == 0, "tmix_shift_project: channel count must be a multiple of 8, >= 256");
+  FRWKV_REQUIRE((size_t)total_rows * channels * 4 <= 200 * 1024, "tmix_shift_project: too many channels");
+  ShiftProjectGroup g;
+  int max_n = 0;
+  for (int i = 0; i < count; ++i) {
+    const frwkv_shift_projection& p = projections[i];
+    FRWKV_REQUIRE(p.mix && p.weight && p.y, "tmix_shift_project: null pointer in projection %d", i);
+    FRWKV_REQUIRE(p.n > 0 && p.n % 8 == 0, "tmix_shift_project: output width must be a positive multiple of 8");
+    g.p[i] = ShiftProjection{p.mix, p.weight, p.y, p.n};
+    max_n = p.n > max_n ? p.n : max_n;
+  }
+  for (int i = count; i < kMaxShiftProjections; ++i) g.p[i] = g.p[0];
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)total_rows * channels * 4;
+  const dim3 grid((max_n + 15) / 16, count);
+#define FRWKV_SHIFT_PROJECT(T, MM)                                                                                 \
+  case MM: {                                                                                                       \
+    if (smem > 48 * 1024) {                                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(shift_project_kernel<T, MM>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           (int)smem);                                                             \
+      if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "tmix_shift_project: %s", cudaGetErrorString(e));          \
+    }                                                                                                              \
+    launch_chained(shift_project_kernel<T, MM>, grid, dim3(256), smem, s, g, static_cast<const T*>(x),             \
+                   static_cast<const T*>(shift_state_pool), cu_seqlens, state_indices, metadata_status,            \
+                   num_sequences, channels);                                                                       \
+    break;                                                                                                         \
+  }
+#define FRWKV_SHIFT_PROJECT_ALL(T)                                                                   \
+  switch (total_rows) {                                                                              \
+    FRWKV_SHIFT_PROJECT(T, 1) FRWKV_SHIFT_PROJECT(T, 2) FRWKV_SHIFT_PROJECT(T, 3) FRWKV_SHIFT_PROJECT(T, 4) \
+    FRWKV_SHIFT_PROJECT(T, 5) FRWKV_SHIFT_PROJECT(T, 6) FRWKV_SHIFT_PROJECT(T, 7) FRWKV_SHIFT_PROJECT(T, 8) \
+  }
+  if (io_dtype == FRWKV_DTYPE_BF16) {
+    FRWKV_SHIFT_PROJECT_ALL(__nv_bfloat16)
+  } else if (io_dtype == FRWKV_DTYPE_FP16) {
+    FRWKV_SHIFT_PROJECT_ALL(__half)
+  } else {
+    return fail(FRWKV_ERR_UNSUPPORTED, "tmix_shift_project: tensors must be float16 or bfloat16");
+  }
+#undef FRWKV_SHIFT_PROJECT_ALL
+#undef FRWKV_SHIFT_PROJECT
+  int rc = check_launch("shift_project_kernel");
+  if (rc != FRWKV_OK) return rc;
+  return launch_shift_state_update(x, shift_state_pool, cu_seqlens, state_indices, metadata_status, num_sequences,
+                                   channels, io_dtype, s);
 }

@@ -68,6 +68,11 @@ __host__ __device__ constexpr uint32_t idesc_f16(bool bf16, int M, int N) {
          (uint32_t(M >> 4) << 24);
 }
 
+// stores the last row of every sequence in its shift-state slot (tmix_elementwise.cu)
+int launch_shift_state_update(const void* x, void* shift_state_pool, const int* cu_seqlens, const int* state_indices,
+                              const int* metadata_status, int num_sequences, int channels, int io_dtype,
+                              cudaStream_t stream);
+
 // The TMA-fed GEMM takes a group whose problems all have act == 0 and 16-byte aligned x / w rows.
 // Returns FRWKV_OK, or a negative code with the message set.
 bool linear_tma_usable(const LinearGroup& g, int count, int M);

@@ -518,6 +518,60 @@ std::vector<torch::Tensor> tmix_mix6_forward_varlen(torch::Tensor x, torch::Tens
   return out.unbind(0);
 }
 
+// Token shift fused into up to eight projections (1..8 rows): outputs[j] = mix(x, prev, mixes[j]) @ weights[j]^T;
+// the shift states are updated afterwards.
+std::vector<torch::Tensor> tmix_shift_project_varlen(torch::Tensor x, torch::Tensor shift_state_pool,
+                                                     std::vector<torch::Tensor> mixes,
+                                                     std::vector<torch::Tensor> weights, torch::Tensor cu,
+                                                     torch::Tensor idx, int64_t max_seqlen,
+                                                     std::shared_ptr<MetadataTicket> ticket) {
+  check_io16(x, "x", x);
+  TORCH_CHECK(x.dim() == 2 && x.size(0) >= 1 && x.size(0) <= 8, "x must have packed shape [M,C] with 1 <= M <= 8");
+  TORCH_CHECK(x.size(1) % 8 == 0 && x.size(1) >= 256, "C must be a multiple of 8 and at least 256");
+  TORCH_CHECK(!mixes.empty() && mixes.size() <= 8 && mixes.size() == weights.size(),
+              "1..8 mix vectors and as many weights are required");
+  check_io16(shift_state_pool, "shift_state_pool", x);
+  TORCH_CHECK(shift_state_pool.dim() == 2 && shift_state_pool.size(1) == x.size(1),
+              "shift_state_pool must have shape [slots,C]");
+  check_cuda_contiguous(cu, "cu_seqlens");
+  check_cuda_contiguous(idx, "state_indices");
+  TORCH_CHECK(cu.scalar_type() == torch::kInt32 && idx.scalar_type() == torch::kInt32, "recurrent metadata must be int32");
+  TORCH_CHECK(cu.dim() == 1 && idx.dim() == 1 && idx.numel() > 0 && cu.numel() == idx.numel() + 1,
+              "cu_seqlens must have shape [B+1] and state_indices shape [B]");
+  TORCH_CHECK(idx.numel() <= x.size(0), "more sequences than rows");
+  const c10::cuda::CUDAGuard guard(x.device());
+  torch::Tensor launch_cu, launch_idx, status;
+  if (ticket) {
+    ticket->check_compatible(cu, idx, x.size(0), shift_state_pool.size(0), max_seqlen);
+    launch_cu = ticket->cu_snapshot();
+    launch_idx = ticket->idx_snapshot();
+    status = ticket->status();
+  } else {
+    auto prepared = launch_validation(cu, idx, x.size(0), shift_state_pool.size(0));
+    launch_cu = std::move(prepared.cu);
+    launch_idx = std::move(prepared.idx);
+    status = std::move(prepared.status);
+  }
+  std::vector<torch::Tensor> outs;
+  std::vector<frwkv_shift_projection> proj;
+  for (size_t j = 0; j < mixes.size(); ++j) {
+    check_io16(mixes[j], "mix", x);
+    check_io16(weights[j], "weight", x);
+    TORCH_CHECK(mixes[j].dim() == 1 && mixes[j].size(0) == x.size(1), "every mix vector must have shape [C]");
+    TORCH_CHECK(weights[j].dim() == 2 && weights[j].size(1) == x.size(1) && weights[j].size(0) % 8 == 0,
+                "every weight must have the original layout [N,C] with N a multiple of 8");
+    outs.push_back(torch::empty({x.size(0), weights[j].size(0)}, x.options()));
+    proj.push_back({mixes[j].data_ptr(), weights[j].data_ptr(), outs.back().data_ptr(),
+                    static_cast<int>(weights[j].size(0))});
+  }
+  check_rc(frwkv_tmix_shift_project_varlen(x.data_ptr(), shift_state_pool.data_ptr(), launch_cu.data_ptr<int>(),
+                                           launch_idx.data_ptr<int>(), status.data_ptr<int>(), proj.data(),
+                                           static_cast<int>(proj.size()), static_cast<int>(x.size(0)),
+                                           static_cast<int>(idx.numel()), static_cast<int>(x.size(1)), io_dtype_of(x),
+                                           current_stream(x)));
+  return outs;
+}
+
 void check_rows_channels(const torch::Tensor& t, const char* name, const torch::Tensor& ref) {
   check_io16(t, name, ref);
   TORCH_CHECK(t.dim() == 2 && t.sizes() == ref.sizes(), name, " must have packed shape [total_tokens,C]");
@@ -751,6 +805,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("x_r"), py::arg("x_w"), py::arg("x_k"), py::arg("x_v"), py::arg("x_a"), py::arg("x_g"),
         py::arg("cu_seqlens"), py::arg("state_indices"), py::arg("max_seqlen") = -1,
         py::arg("validated_metadata") = py::none());
+  m.def("tmix_shift_project_varlen", &tmix_shift_project_varlen, py::arg("x"), py::arg("shift_state_pool"),
+        py::arg("mixes"), py::arg("weights"), py::arg("cu_seqlens"), py::arg("state_indices"),
+        py::arg("max_seqlen") = -1, py::arg("validated_metadata") = py::none());
   m.def("tmix_kk_a_gate_forward_varlen", &tmix_kk_a_gate_forward_varlen, py::arg("k"), py::arg("k_k"), py::arg("a0"),
         py::arg("a12"), py::arg("k_a"), py::arg("head_size") = 64, py::arg("batch_size") = 1,
         py::arg("max_seqlen") = 1);

@@ -161,6 +161,7 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
     float* __restrict__ sa_ptr, float* __restrict__ ckpt_ptr, long long num_units, int num_heads,
     long long output_elements, float scale) {
   using IO = Io16<io_t>;
+  chain_begin();
   if (!kReplay && metadata_status != nullptr && metadata_status[0] != 0) {
     // fail closed: NaN output, state untouched
     const io_t nan16 = IO::store(quiet_nan());
@@ -445,7 +446,7 @@ int launch(const int* cu, const int* idx, const int* status, float* state, const
            float scale, cudaStream_t stream) {
   const long long units = (long long)num_sequences * num_heads * 2;
   const long long blocks = (units + kWarpsPerBlock - 1) / kWarpsPerBlock;
-  wkv7_recurrent_d64_kernel<io_t, false><<<(unsigned)blocks, kThreads, 0, stream>>>(
+  launch_chained(wkv7_recurrent_d64_kernel<io_t, false>, dim3((unsigned)blocks), dim3(kThreads), 0, stream,
       cu, idx, status, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w),
       static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),
       static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, nullptr, nullptr,

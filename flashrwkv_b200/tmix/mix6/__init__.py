@@ -37,4 +37,58 @@ def infer_tmix_mix6_forward_varlen(x, x_r, x_w, x_k, x_v, x_a, x_g, *, shift_sta
         -1 if max_seqlen is None else int(max_seqlen), validated_metadata))
 
 
-__all__ = ["infer_tmix_mix6_forward_varlen"]
+def infer_tmix_shift_project_forward_varlen(x, mixes, weights, *, shift_state_pool, cu_seqlens, state_indices,
+                                            max_seqlen: int | None = None, validated_metadata=None):
+    """Token shift fused into the projections that consume it (no counterpart in the reference, which runs
+    `infer_tmix_mix6_forward_varlen` and then the projections).
+
+    `outputs[j] = (x + (prev - x) * mixes[j]) @ weights[j]^T` for up to eight `(mix [C], weight [N_j,C])` pairs —
+    e.g. r, k, v and the four rank-in projections of a TMix layer — and each sequence's last row goes to its
+    shift-state slot.  With 1..8 rows this is one launch (plus the state update) and the interpolated rows never
+    leave the chip; with more rows it runs mix6 per distinct mix vector and the grouped GEMMs.
+    """
+    from ..linear import _grouped
+
+    mixes, weights = list(mixes), list(weights)
+    if not mixes or len(mixes) != len(weights) or len(mixes) > 8:
+        raise ValueError("1..8 mix vectors and as many weights are required")
+    check_io("x", x, None)
+    if x.ndim != 2 or x.shape[0] <= 0 or x.shape[1] <= 0:
+        raise ValueError("x must have packed shape [total_tokens,C]")
+    for name, group, shape_ok in (("mix", mixes, lambda t: t.shape == (x.shape[1],)),
+                                  ("weight", weights, lambda t: t.ndim == 2 and t.shape[1] == x.shape[1])):
+        for t in group:
+            check_io(name, t, x)
+            if not shape_ok(t):
+                raise ValueError(f"every {name} must have shape " + ("[C]" if name == "mix" else "[N,C]"))
+    if not isinstance(shift_state_pool, torch.Tensor):
+        raise TypeError("shift_state_pool must be a torch.Tensor")
+    if (shift_state_pool.dtype != x.dtype or not shift_state_pool.is_cuda or not shift_state_pool.is_contiguous()
+            or shift_state_pool.ndim != 2 or shift_state_pool.shape[1] != x.shape[1]):
+        raise ValueError("shift_state_pool must be contiguous CUDA [slots,C] of x's dtype")
+    _check_metadata_inputs(cu_seqlens, state_indices)
+    if max_seqlen is not None and (not isinstance(max_seqlen, int) or isinstance(max_seqlen, bool) or max_seqlen <= 0):
+        raise ValueError("max_seqlen must be a positive integer")
+    if x.shape[0] <= 8 and x.shape[1] >= 256:
+        return tuple(extension().tmix_shift_project_varlen(
+            x, shift_state_pool, mixes, weights, cu_seqlens, state_indices,
+            -1 if max_seqlen is None else int(max_seqlen), validated_metadata))
+    # many rows: the six-way kernel once (it also updates the shift states), then the GEMMs in groups of four
+    distinct = []
+    for m in mixes:
+        if not any(m is d for d in distinct):
+            distinct.append(m)
+    if len(distinct) > 6:
+        raise ValueError("with more than 8 rows at most six distinct mix vectors are supported")
+    padded = distinct + [distinct[0]] * (6 - len(distinct))
+    mixed = infer_tmix_mix6_forward_varlen(x, *padded, shift_state_pool=shift_state_pool, cu_seqlens=cu_seqlens,
+                                           state_indices=state_indices, max_seqlen=max_seqlen,
+                                           validated_metadata=validated_metadata)
+    xs = [mixed[[m is d for d in distinct].index(True)] for m in mixes]
+    outs = []
+    for i in range(0, len(xs), 4):
+        outs.extend(_grouped(xs[i:i + 4], weights[i:i + 4], ["none"] * len(xs[i:i + 4])))
+    return tuple(outs)
+
+
+__all__ = ["infer_tmix_mix6_forward_varlen", "infer_tmix_shift_project_forward_varlen"]

@@ -232,6 +232,28 @@ int frwkv_tmix_lnx_rkvres_xg_forward_varlen(const void* x, const void* r, const 
 int frwkv_tmix_vres_gate_forward_varlen(const void* v, const void* v_first, const void* v0, const void* v12, void* out,
                                         long long total_rows, int channels, int io_dtype, frwkv_stream_t stream);
 
+/*
+ * Token shift fused into up to eight projections of the same rows (decode, 1..8 rows):
+ *   y_j[m][n] = sum_c (x[m][c] + (prev[m][c] - x[m][c]) * mix_j[c]) * weight_j[n][c]
+ * with prev the previous row of the same sequence or, for its first row, shift_state_pool[state_indices[s]]; afterwards
+ * the last row of every sequence is stored in its shift-state slot.  One launch does what tmix_mix6_forward_varlen
+ * (csrc/sm120/tmix/mix6/infer_fp16_forward_varlen.cu:75-303) followed by tmix_lowrank_wagv_in_forward_varlen and
+ * three tmix_linear_forward_varlen calls (csrc/sm120/tmix/linear/infer_fp16_forward_varlen.cu:2229-2521,2685-2952) do
+ * in the reference; the interpolated rows stay in fp32 instead of being rounded to 16 bits in between.  There is no
+ * single reference entry point with this signature.  `projections` is a host array.  When *metadata_status != 0 the
+ * outputs are NaN and the shift states untouched.
+ */
+typedef struct {
+  const void* mix;     /* io16 [channels] */
+  const void* weight;  /* io16 [n][channels] */
+  void* y;             /* io16 [total_rows][n] */
+  int n;               /* multiple of 8 */
+} frwkv_shift_projection;
+int frwkv_tmix_shift_project_varlen(const void* x, void* shift_state_pool, const int32_t* cu_seqlens,
+                                    const int32_t* state_indices, const int32_t* metadata_status,
+                                    const frwkv_shift_projection* projections, int count, int total_rows,
+                                    int num_sequences, int channels, int io_dtype, frwkv_stream_t stream);
+
 /* Elementwise tanh (act = 1) or sigmoid (act = 2) of a 16-bit tensor with `elements` (multiple of 8) values.
  * Replaces linear_act_tanh / linear_act_sigmoid (csrc/sm120/tmix/linear/infer_fp16_forward_varlen.cu:1235-1373). */
 int frwkv_tmix_act_forward(const void* x, void* out, long long elements, int act, int io_dtype, frwkv_stream_t stream);

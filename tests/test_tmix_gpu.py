@@ -180,3 +180,40 @@ def test_dense_linear_ragged_shapes(oracle, dtype, shape):
     assert y.shape == (M, N)
     assert rel_rmse(y.double().cpu(), ref) <= TOL[dtype]
     assert max_abs(y.double().cpu(), ref) <= 8 * TOL[dtype] * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("lengths", [(1,), (1,) * 7, (3, 1, 2), (8,), (5, 30)])
+def test_shift_project_fused_vs_oracle(oracle, dtype, lengths):
+    """Token shift fused into the projections (<= 8 rows: one launch; more rows: mix6 + GEMMs) against mix6 and the
+    projection of the oracle; the shift states end up holding each sequence's last row."""
+    import flashrwkv_b200 as F
+
+    C, M, slots = 512, sum(lengths), 9
+    gen = torch.Generator().manual_seed(31 * M + len(lengths))
+    x = torch.randn(M, C, generator=gen).to(dtype)
+    pool = torch.randn(slots, C, generator=gen).to(dtype)
+    mix = [torch.rand(C, generator=gen).to(dtype) for _ in range(4)]
+    Ws = [(torch.randn(n, C, generator=gen) * 0.05).to(dtype) for n in (512, 96, 64, 256, 512)]
+    use = [0, 1, 2, 3, 2]  # the fifth projection shares the third mix vector
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lengths)]), dtype=torch.int32)
+    idx = torch.randperm(slots, generator=gen)[:len(lengths)].int()
+    d_pool = pool.cuda().clone()
+    outs = F.infer_tmix_shift_project_forward_varlen(x.cuda(), [mix[u].cuda() for u in use], [w.cuda() for w in Ws],
+                                                     shift_state_pool=d_pool, cu_seqlens=cu.cuda(),
+                                                     state_indices=idx.cuda())
+    torch.cuda.synchronize()
+    # reference: previous rows, fp32 interpolation, projection
+    prev = torch.empty(M, C)
+    for s, (a, b) in enumerate(zip(cu[:-1].tolist(), cu[1:].tolist())):
+        prev[a] = pool[idx[s]].float()
+        prev[a + 1:b] = x[a:b - 1].float()
+    for j, (u, w) in enumerate(zip(use, Ws)):
+        mixed = x.float() + (prev - x.float()) * mix[u].float()
+        ref = mixed.double() @ w.double().T
+        assert outs[j].shape == (M, w.shape[0])
+        assert rel_rmse(outs[j].double().cpu(), ref) <= 2 * TOL[dtype], f"projection {j}"
+    expect_pool = pool.clone()
+    for s, b in enumerate(cu[1:].tolist()):
+        expect_pool[idx[s]] = x[b - 1]
+    assert torch.equal(d_pool.cpu(), expect_pool)
