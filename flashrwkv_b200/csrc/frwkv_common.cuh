@@ -107,11 +107,14 @@ __device__ __forceinline__ float quiet_nan() { return __int_as_float(0x7fffffff)
 // The short kernels of a decode step run back to back in one stream and each is bound by launch latency rather than
 // by its work.  A kernel launched with launch_chained() may start while its predecessor is still running; it calls
 // chain_begin() first, which lets ITS successor be scheduled early and then waits until everything before it in the
-// stream has completed and is visible.  Nothing is read or written before that wait, so the overlap covers only
-// launch and scheduling latency.  Both instructions do nothing in a kernel launched the ordinary way.
+// stream has completed and is visible.  Nothing that a predecessor may write is read, and nothing at all is written,
+// before that wait (the projection kernels fetch weights, which are constants, between chain_release() and
+// chain_wait()).  Both instructions do nothing in a kernel launched the ordinary way.
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void chain_begin() {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  chain_release();
+  chain_wait();
 }
 
 bool chained_launch_enabled();  // false when FRWKV_DISABLE_CHAINED_LAUNCH=1 (for comparisons)

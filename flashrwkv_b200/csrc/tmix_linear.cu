@@ -4,7 +4,7 @@
 // Two kernels, picked by the row count:
 //   * M <= 8 ("skinny", decode): weight-bandwidth bound.  x is staged once per CTA in shared memory as fp32 with the
 //     activation applied; every weight element is read exactly once with 16-byte loads.  For long rows (K >= 256) a
-//     warp owns two output columns at a time and reduces with shuffles; for short rows (rank-out) a thread owns one.
+//     warp owns two output columns at a time and reduces with shuffles; for short rows (rank-out) eight lanes own one.
 //   * M > 8: tcgen05 tensor-core GEMM (kind::f16, fp32 accumulate in tensor memory).  Problems without an activation
 //     on x go to the TMA-fed persistent kernel of tmix_gemm_tma.cu; the kernel here (128 x 64 output tile per CTA, K in
 //     blocks of 64 through a 4-stage cp.async pipeline into chunk-major tiles, see umma.cuh) applies tanh / sigmoid
@@ -26,14 +26,43 @@ namespace {
 // ---- skinny kernel --------------------------------------------------------------------------------------
 // grid = (column blocks, problems); dynamic shared memory = M * K fp32 values of x (activation applied): unpacking the
 // 16-bit x once per CTA instead of once per weight row is what keeps M = 4..8 bound by the weight stream rather than
-// by instruction issue.  Long rows (K >= 256): a warp owns two output columns at a time (two independent 16-byte
-// weight loads in flight per lane, every x value used twice) and reduces with shuffles.  Short rows (rank-out,
-// K = rank): a thread owns a column.
-constexpr int kSkinnyDepth = 8;  // 16-byte weight pieces per row and lane in flight at once
+// by instruction issue.  Long rows (K >= 256): a warp owns two output columns at a time (sixteen 16-byte weight
+// loads in flight per lane, every x value used twice) and reduces with shuffles.  Short rows (rank-out,
+// K = rank): eight lanes share a column.
+// Output columns a warp works on at a time (long rows) and 16-byte weight pieces per column and lane in flight at once.
+// Two columns keep 128 CTAs busy on a 2048-wide projection; four columns halve the shared-memory reads of x but leave
+// 64 CTAs to pull the weights, and the layer took twice as long (measured): the kernel lives on SMs pulling in parallel.
+constexpr int kSkinnyCols = 2;
+constexpr int kSkinnyDepth = 8;
+
+// The first block of weight pieces of a warp's first column group.  Weights are constants, so a kernel fetches them
+// before it waits for its predecessors in the stream and before it stages x: the DRAM round trip of the weight
+// stream then overlaps the tail of the previous kernel and the staging.
+struct SkinnyPrefetch {
+  uint4 q[kSkinnyCols][kSkinnyDepth];
+};
+template <typename io_t>
+__device__ __forceinline__ void skinny_prefetch(const void* weight, int N, int K, SkinnyPrefetch& pf) {
+  if (K < 256) return;
+  const int lane = threadIdx.x & 31, kv = K >> 3;
+  const int n = kSkinnyCols * (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
+  if (n >= N) return;
+  const io_t* w = static_cast<const io_t*>(weight);
+#pragma unroll
+  for (int col = 0; col < kSkinnyCols; ++col) {
+    const uint4* wrow = reinterpret_cast<const uint4*>(w + (long long)(n + col) * K);
+#pragma unroll
+    for (int j = 0; j < kSkinnyDepth; ++j) {
+      const int c = lane + 32 * j;
+      if (c < kv) pf.q[col][j] = __ldg(wrow + c);
+    }
+  }
+}
 
 // the products of one CTA: xs / xs_hi hold x as fp32 (see linear_skinny_kernel)
 template <typename io_t, int M>
-__device__ __forceinline__ void skinny_products(const LinearProblem& pr, const float4* xs, const float4* xs_hi) {
+__device__ __forceinline__ void skinny_products(const LinearProblem& pr, const float4* xs, const float4* xs_hi,
+                                                const SkinnyPrefetch& pf) {
   using IO = Io16<io_t>;
   const int K = pr.k, N = pr.n, kv = K >> 3;
   const io_t* w = static_cast<const io_t*>(pr.w);
@@ -41,88 +70,112 @@ __device__ __forceinline__ void skinny_products(const LinearProblem& pr, const f
   if (K >= 256) {
     const int lane = threadIdx.x & 31;
     const int warps_total = gridDim.x * (blockDim.x >> 5);
-    // N is a multiple of 8, so a pair of columns (n, n + 1) with n even is always complete
-    for (int n = 2 * (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)); n < N; n += 2 * warps_total) {
-      float acc0[M], acc1[M];
+    // N is a multiple of 8, so a group of kSkinnyCols columns starting at a multiple of kSkinnyCols is always complete
+    const int n_first = kSkinnyCols * (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
+    for (int n = n_first; n < N; n += kSkinnyCols * warps_total) {
+      // accumulators as fp32 pairs (even | odd elements of a piece): one fma.rn.f32x2 per two multiply-adds
+      float2 acc[kSkinnyCols][M];
 #pragma unroll
-      for (int m = 0; m < M; ++m) { acc0[m] = 0.f; acc1[m] = 0.f; }
-      const uint4* wrow0 = reinterpret_cast<const uint4*>(w + (long long)n * K);
-      const uint4* wrow1 = reinterpret_cast<const uint4*>(w + (long long)(n + 1) * K);
-      // All weight loads of a block of 8 x 32 sixteen-byte pieces per row are issued before the first one is used:
-      // with one or two CTAs per SM the kernel lives on the number of loads in flight, not on arithmetic.
+      for (int col = 0; col < kSkinnyCols; ++col) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[col][m] = make_float2(0.f, 0.f);
+      }
+      // all weight loads of a block (kSkinnyCols x kSkinnyDepth pieces per lane) are issued before the first one is used
       for (int cb = lane; cb < kv; cb += 32 * kSkinnyDepth) {
-        uint4 q0[kSkinnyDepth], q1[kSkinnyDepth];
+        uint4 q[kSkinnyCols][kSkinnyDepth];
+        const bool fetched = (n == n_first && cb == lane);  // this block came in with skinny_prefetch
 #pragma unroll
-        for (int j = 0; j < kSkinnyDepth; ++j) {
-          const int c = cb + 32 * j;
-          if (c < kv) {
-            q0[j] = __ldg(wrow0 + c);
-            q1[j] = __ldg(wrow1 + c);
+        for (int col = 0; col < kSkinnyCols; ++col) {
+          const uint4* wrow = reinterpret_cast<const uint4*>(w + (long long)(n + col) * K);
+#pragma unroll
+          for (int j = 0; j < kSkinnyDepth; ++j) {
+            const int c = cb + 32 * j;
+            if (c < kv) q[col][j] = fetched ? pf.q[col][j] : __ldg(wrow + c);
           }
         }
 #pragma unroll
         for (int j = 0; j < kSkinnyDepth; ++j) {
           const int c = cb + 32 * j;
           if (c < kv) {
-            float w0[8], w1[8];
-            unpack8<io_t>(q0[j], w0);
-            unpack8<io_t>(q1[j], w1);
+            float2 wv[kSkinnyCols][4];
+#pragma unroll
+            for (int col = 0; col < kSkinnyCols; ++col) {
+              wv[col][0] = IO::unpack(q[col][j].x); wv[col][1] = IO::unpack(q[col][j].y);
+              wv[col][2] = IO::unpack(q[col][j].z); wv[col][3] = IO::unpack(q[col][j].w);
+            }
 #pragma unroll
             for (int m = 0; m < M; ++m) {
               const float4 xa = xs[m * kv + c], xb = xs_hi[m * kv + c];
-              acc0[m] = fmaf(w0[0], xa.x, fmaf(w0[1], xa.y, fmaf(w0[2], xa.z, fmaf(w0[3], xa.w, acc0[m]))));
-              acc0[m] = fmaf(w0[4], xb.x, fmaf(w0[5], xb.y, fmaf(w0[6], xb.z, fmaf(w0[7], xb.w, acc0[m]))));
-              acc1[m] = fmaf(w1[0], xa.x, fmaf(w1[1], xa.y, fmaf(w1[2], xa.z, fmaf(w1[3], xa.w, acc1[m]))));
-              acc1[m] = fmaf(w1[4], xb.x, fmaf(w1[5], xb.y, fmaf(w1[6], xb.z, fmaf(w1[7], xb.w, acc1[m]))));
+              const float2 x0 = make_float2(xa.x, xa.y), x1 = make_float2(xa.z, xa.w);
+              const float2 x2 = make_float2(xb.x, xb.y), x3 = make_float2(xb.z, xb.w);
+#pragma unroll
+              for (int col = 0; col < kSkinnyCols; ++col)
+                acc[col][m] = __ffma2_rn(wv[col][0], x0, __ffma2_rn(wv[col][1], x1,
+                                         __ffma2_rn(wv[col][2], x2, __ffma2_rn(wv[col][3], x3, acc[col][m]))));
             }
           }
         }
       }
 #pragma unroll
       for (int m = 0; m < M; ++m) {
+        float t[kSkinnyCols];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          acc0[m] += __shfl_xor_sync(0xffffffffu, acc0[m], o);
-          acc1[m] += __shfl_xor_sync(0xffffffffu, acc1[m], o);
+        for (int col = 0; col < kSkinnyCols; ++col) {
+          t[col] = acc[col][m].x + acc[col][m].y;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) t[col] += __shfl_xor_sync(0xffffffffu, t[col], o);
         }
-      }
-      if (lane == 0) {
+        if (lane == 0) {
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-          const uint32_t two = IO::pack(finish<io_t>(pr, acc0[m], m, n), finish<io_t>(pr, acc1[m], m, n + 1));
-          *reinterpret_cast<uint32_t*>(y + (long long)m * N + n) = two;
+          for (int col = 0; col < kSkinnyCols; col += 2)
+            *reinterpret_cast<uint32_t*>(y + (long long)m * N + n + col) =
+                IO::pack(finish<io_t>(pr, t[col], m, n + col), finish<io_t>(pr, t[col + 1], m, n + col + 1));
         }
       }
     }
   } else {
-    for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < N; n += gridDim.x * blockDim.x) {
-      float acc[M];
+    // short rows (rank-out, K = rank): eight lanes share a column, a warp works on four columns at a time
+    const int lane = threadIdx.x & 31, sub = lane & 7, grp = lane >> 3;
+    const int warps_total = gridDim.x * (blockDim.x >> 5);
+    for (int n0 = 4 * (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)); n0 < N; n0 += 4 * warps_total) {
+      const int n = n0 + grp;  // N is a multiple of 8: all four columns exist
+      float2 acc[M];
 #pragma unroll
-      for (int m = 0; m < M; ++m) acc[m] = 0.f;
+      for (int m = 0; m < M; ++m) acc[m] = make_float2(0.f, 0.f);
       const uint4* wrow = reinterpret_cast<const uint4*>(w + (long long)n * K);
-      for (int c = 0; c < kv; ++c) {
-        float wf[8];
-        unpack8<io_t>(__ldg(wrow + c), wf);
+      for (int c = sub; c < kv; c += 8) {
+        const uint4 q = __ldg(wrow + c);
+        const float2 a0 = IO::unpack(q.x), a1 = IO::unpack(q.y), a2 = IO::unpack(q.z), a3 = IO::unpack(q.w);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-          // same address for the whole warp: broadcast
           const float4 xa = xs[m * kv + c], xb = xs_hi[m * kv + c];
-          acc[m] = fmaf(wf[0], xa.x, fmaf(wf[1], xa.y, fmaf(wf[2], xa.z, fmaf(wf[3], xa.w, acc[m]))));
-          acc[m] = fmaf(wf[4], xb.x, fmaf(wf[5], xb.y, fmaf(wf[6], xb.z, fmaf(wf[7], xb.w, acc[m]))));
+          acc[m] = __ffma2_rn(a0, make_float2(xa.x, xa.y),
+                              __ffma2_rn(a1, make_float2(xa.z, xa.w),
+                                         __ffma2_rn(a2, make_float2(xb.x, xb.y),
+                                                    __ffma2_rn(a3, make_float2(xb.z, xb.w), acc[m]))));
         }
       }
 #pragma unroll
-      for (int m = 0; m < M; ++m) y[(long long)m * N + n] = IO::store(finish<io_t>(pr, acc[m], m, n));
+      for (int m = 0; m < M; ++m) {
+        float t = acc[m].x + acc[m].y;
+        t += __shfl_xor_sync(0xffffffffu, t, 1);
+        t += __shfl_xor_sync(0xffffffffu, t, 2);
+        t += __shfl_xor_sync(0xffffffffu, t, 4);
+        if (sub == 0) y[(long long)m * N + n] = IO::store(finish<io_t>(pr, t, m, n));
+      }
     }
   }
 }
 
 template <typename io_t, int M>
 __global__ __launch_bounds__(256) void linear_skinny_kernel(LinearGroup group) {
-  chain_begin();
   using IO = Io16<io_t>;
   extern __shared__ __align__(16) unsigned char xs_raw[];
   const LinearProblem& pr = group.p[blockIdx.y];
+  chain_release();
+  SkinnyPrefetch pf;
+  skinny_prefetch<io_t>(pr.w, pr.n, pr.k, pf);
+  chain_wait();
   const int kv = pr.k >> 3;
   // fp32 x as two planes of float4: plane 0 holds elements 8c..8c+3 of row m at [m*kv + c], plane 1 elements 8c+4..8c+7
   // (consecutive lanes then read consecutive 16-byte words: no bank conflicts)
@@ -139,7 +192,7 @@ __global__ __launch_bounds__(256) void linear_skinny_kernel(LinearGroup group) {
     xs_hi[i] = make_float4(f[4], f[5], f[6], f[7]);
   }
   __syncthreads();
-  skinny_products<io_t, M>(pr, xs, xs_hi);
+  skinny_products<io_t, M>(pr, xs, xs_hi, pf);
 }
 
 // ---- token shift fused into the projections (decode) -------------------------------------------------------------
@@ -165,11 +218,14 @@ __global__ __launch_bounds__(256) void shift_project_kernel(ShiftProjectGroup gr
                                                             const int* __restrict__ cu_seqlens,
                                                             const int* __restrict__ state_indices,
                                                             const int* __restrict__ status, int num_sequences, int C) {
-  chain_begin();
   using IO = Io16<io_t>;
   extern __shared__ __align__(16) unsigned char xs_raw[];
   __shared__ const io_t* prev_row[M];
   const ShiftProjection& sp = group.p[blockIdx.y];
+  chain_release();
+  SkinnyPrefetch pf;
+  skinny_prefetch<io_t>(sp.w, sp.n, C, pf);
+  chain_wait();
   const int kv = C >> 3;
   io_t* y = static_cast<io_t*>(sp.y);
   if (status != nullptr && status[0] != 0) {  // fail closed: NaN outputs
@@ -188,20 +244,30 @@ __global__ __launch_bounds__(256) void shift_project_kernel(ShiftProjectGroup gr
   float4* xs = reinterpret_cast<float4*>(xs_raw);
   float4* xs_hi = xs + M * kv;
   const uint4* mixv = reinterpret_cast<const uint4*>(sp.mix);
-  for (int i = threadIdx.x; i < M * kv; i += blockDim.x) {
-    const int m = i / kv, c = i - m * kv;
-    float xf[8], pf[8], mf[8];
-    unpack8<io_t>(__ldg(reinterpret_cast<const uint4*>(x) + i), xf);
-    unpack8<io_t>(__ldg(reinterpret_cast<const uint4*>(prev_row[m]) + c), pf);
-    unpack8<io_t>(__ldg(mixv + c), mf);
+  for (int c = threadIdx.x; c < kv; c += blockDim.x) {
+    uint4 rx[M], rp[M];
+    const uint4 rm = __ldg(mixv + c);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) xf[e] = fmaf(pf[e] - xf[e], mf[e], xf[e]);
-    xs[i] = make_float4(xf[0], xf[1], xf[2], xf[3]);
-    xs_hi[i] = make_float4(xf[4], xf[5], xf[6], xf[7]);
+    for (int m = 0; m < M; ++m) {
+      rx[m] = __ldg(reinterpret_cast<const uint4*>(x) + m * kv + c);
+      rp[m] = __ldg(reinterpret_cast<const uint4*>(prev_row[m]) + c);
+    }
+    float mf[8];
+    unpack8<io_t>(rm, mf);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      float xf[8], pf8[8];
+      unpack8<io_t>(rx[m], xf);
+      unpack8<io_t>(rp[m], pf8);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xf[e] = fmaf(pf8[e] - xf[e], mf[e], xf[e]);
+      xs[m * kv + c] = make_float4(xf[0], xf[1], xf[2], xf[3]);
+      xs_hi[m * kv + c] = make_float4(xf[4], xf[5], xf[6], xf[7]);
+    }
   }
   __syncthreads();
   const LinearProblem pr{x, sp.w, sp.y, nullptr, nullptr, nullptr, sp.n, C, 0, 0};
-  skinny_products<io_t, M>(pr, xs, xs_hi);
+  skinny_products<io_t, M>(pr, xs, xs_hi, pf);
 }
 
 // ---- tensor-core kernel -----------------------------------------------------------------------------------
@@ -339,7 +405,7 @@ template <typename io_t>
 int launch_linear(const LinearGroup& g, int count, int M, int max_n, int max_k, int* error_flag, cudaStream_t stream) {
   if (M <= 8) {
     const size_t smem = (size_t)M * max_k * 4;
-    const int blocks = max_k >= 256 ? (max_n + 15) / 16 : (max_n + 255) / 256;
+    const int blocks = max_k >= 256 ? (max_n + 8 * kSkinnyCols - 1) / (8 * kSkinnyCols) : (max_n + 31) / 32;
     dim3 grid(blocks < 1 ? 1 : blocks, count);
 #define FRWKV_SKINNY(MM)                                                                                      \
   case MM: {                                                                                                  \
@@ -426,7 +492,7 @@ extern "C" int frwkv_tmix_shift_project_varlen(const void* x, void* shift_state_
   for (int i = count; i < kMaxShiftProjections; ++i) g.p[i] = g.p[0];
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const size_t smem = (size_t)total_rows * channels * 4;
-  const dim3 grid((max_n + 15) / 16, count);
+  const dim3 grid((max_n + 8 * kSkinnyCols - 1) / (8 * kSkinnyCols), count);
 #define FRWKV_SHIFT_PROJECT(T, MM)                                                                                 \
   case MM: {                                                                                                       \
     if (smem > 48 * 1024) {                                                                                        \
