@@ -21,13 +21,21 @@ from .tmix.kk_a_gate import infer_tmix_kk_a_gate_forward_varlen
 from .tmix.linear import *  # noqa: F401,F403
 from .tmix.linear import __all__ as _linear_all
 from .tmix.lnx_rkvres_xg import infer_tmix_lnx_rkvres_xg_forward_varlen
-from .tmix.mix6 import infer_tmix_mix6_forward_varlen, infer_tmix_shift_project_forward_varlen
+from .tmix.mix6 import (
+    infer_tmix_mix6_add_layer_norm_forward_varlen,
+    infer_tmix_mix6_forward_varlen,
+    infer_tmix_shift_project_forward_varlen,
+)
+from .tmix.normalization import *  # noqa: F401,F403
+from .tmix.normalization import __all__ as _norm_all
 from .tmix.vres_gate import infer_tmix_vres_gate_forward_varlen
 
 __all__ = [
     "infer_tmix_kk_a_gate_forward_varlen",
     "infer_tmix_lnx_rkvres_xg_forward_varlen",
     "infer_tmix_mix6_forward_varlen",
+    "infer_tmix_mix6_add_layer_norm_forward_varlen",
+    *_norm_all,
     "infer_tmix_shift_project_forward_varlen",
     "infer_tmix_vres_gate_forward_varlen",
     *_linear_all,

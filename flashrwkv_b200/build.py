@@ -33,6 +33,7 @@ CUDA_SOURCES = [
     "umma_selftest.cu",
     "wkv7_chunk_fwd.cu",
     "tmix_elementwise.cu",
+    "tmix_norm.cu",
     "tmix_linear.cu",
     "tmix_gemm_tma.cu",
     "wkv7_backward.cu",

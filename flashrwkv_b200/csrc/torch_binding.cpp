@@ -518,6 +518,114 @@ std::vector<torch::Tensor> tmix_mix6_forward_varlen(torch::Tensor x, torch::Tens
   return out.unbind(0);
 }
 
+// ---- add + LayerNorm family (reference entry names: tmix_layer_norm_forward_varlen, tmix_add_layer_norm_forward_varlen,
+// tmix_add_last_layer_norm_forward_varlen, tmix_add_forward_varlen, tmix_mix6_add_layer_norm_forward_varlen) -------------
+void check_norm_inputs(const torch::Tensor& x, const torch::Tensor* residual, const torch::Tensor* weight,
+                       const torch::Tensor* bias) {
+  check_io16(x, "x", x);
+  TORCH_CHECK(x.dim() == 2 && x.size(0) > 0 && x.size(1) > 0, "x must have packed shape [total_tokens,C]");
+  TORCH_CHECK(x.size(1) % 8 == 0, "C must be a multiple of 8");
+  if (residual != nullptr) {
+    check_io16(*residual, "residual", x);
+    TORCH_CHECK(residual->sizes() == x.sizes(), "residual must have the same shape as x");
+  }
+  if (weight != nullptr) {
+    check_io16(*weight, "weight", x);
+    check_io16(*bias, "bias", x);
+    TORCH_CHECK(weight->dim() == 1 && weight->size(0) == x.size(1) && bias->sizes() == weight->sizes(),
+                "weight and bias must have shape [C]");
+  }
+}
+
+torch::Tensor tmix_layer_norm_forward_varlen(torch::Tensor x, torch::Tensor weight, torch::Tensor bias, double eps) {
+  check_norm_inputs(x, nullptr, &weight, &bias);
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto out = torch::empty_like(x);
+  check_rc(frwkv_tmix_add_layer_norm_forward(x.data_ptr(), nullptr, weight.data_ptr(), bias.data_ptr(), nullptr,
+                                             out.data_ptr(), x.size(0), static_cast<int>(x.size(1)),
+                                             static_cast<float>(eps), io_dtype_of(x), current_stream(x)));
+  return out;
+}
+
+std::tuple<torch::Tensor, torch::Tensor> tmix_add_layer_norm_forward_varlen(torch::Tensor x, torch::Tensor residual,
+                                                                            torch::Tensor weight, torch::Tensor bias,
+                                                                            double eps, int64_t batch_size) {
+  (void)batch_size;  // the reference picks between two statistics kernels with it; there is one here
+  check_norm_inputs(x, &residual, &weight, &bias);
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto sum = torch::empty_like(x), out = torch::empty_like(x);
+  check_rc(frwkv_tmix_add_layer_norm_forward(x.data_ptr(), residual.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                                             sum.data_ptr(), out.data_ptr(), x.size(0), static_cast<int>(x.size(1)),
+                                             static_cast<float>(eps), io_dtype_of(x), current_stream(x)));
+  return {sum, out};
+}
+
+torch::Tensor tmix_add_last_layer_norm_forward_varlen(torch::Tensor x, torch::Tensor residual, torch::Tensor weight,
+                                                      torch::Tensor bias, double eps) {
+  check_norm_inputs(x, &residual, &weight, &bias);
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto out = torch::empty_like(x);
+  check_rc(frwkv_tmix_add_layer_norm_forward(x.data_ptr(), residual.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                                             nullptr, out.data_ptr(), x.size(0), static_cast<int>(x.size(1)),
+                                             static_cast<float>(eps), io_dtype_of(x), current_stream(x)));
+  return out;
+}
+
+torch::Tensor tmix_add_forward_varlen(torch::Tensor x, torch::Tensor residual) {
+  check_norm_inputs(x, &residual, nullptr, nullptr);
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto sum = torch::empty_like(x);
+  check_rc(frwkv_tmix_add_layer_norm_forward(x.data_ptr(), residual.data_ptr(), nullptr, nullptr, sum.data_ptr(), nullptr,
+                                             x.size(0), static_cast<int>(x.size(1)), 1.0f, io_dtype_of(x),
+                                             current_stream(x)));
+  return sum;
+}
+
+// Fused form for batches of one-token sequences; returns (sum, x_r, x_w, x_k, x_v, x_a, x_g mixes).
+std::vector<torch::Tensor> tmix_mix6_add_layer_norm_forward_varlen(
+    torch::Tensor x, torch::Tensor residual, torch::Tensor weight, torch::Tensor bias, torch::Tensor shift_state_pool,
+    torch::Tensor x_r, torch::Tensor x_w, torch::Tensor x_k, torch::Tensor x_v, torch::Tensor x_a, torch::Tensor x_g,
+    torch::Tensor cu, torch::Tensor idx, int64_t max_seqlen, double eps, std::shared_ptr<MetadataTicket> ticket) {
+  check_norm_inputs(x, &residual, &weight, &bias);
+  const std::pair<const torch::Tensor*, const char*> vecs[] = {{&x_r, "x_r"}, {&x_w, "x_w"}, {&x_k, "x_k"},
+                                                               {&x_v, "x_v"}, {&x_a, "x_a"}, {&x_g, "x_g"}};
+  for (const auto& item : vecs) {
+    check_io16(*item.first, item.second, x);
+    TORCH_CHECK(item.first->dim() == 1 && item.first->size(0) == x.size(1), "all mix6 coefficients must have shape [C]");
+  }
+  check_io16(shift_state_pool, "shift_state_pool", x);
+  TORCH_CHECK(shift_state_pool.dim() == 2 && shift_state_pool.size(1) == x.size(1),
+              "shift_state_pool must have shape [slots,C]");
+  check_cuda_contiguous(cu, "cu_seqlens");
+  check_cuda_contiguous(idx, "state_indices");
+  TORCH_CHECK(cu.scalar_type() == torch::kInt32 && idx.scalar_type() == torch::kInt32, "recurrent metadata must be int32");
+  TORCH_CHECK(cu.dim() == 1 && idx.dim() == 1 && idx.numel() == x.size(0) && cu.numel() == idx.numel() + 1,
+              "the fused form takes one-token sequences: cu_seqlens [rows+1], state_indices [rows]");
+  TORCH_CHECK(std::isfinite(eps) && eps > 0, "eps must be finite and positive");
+  const c10::cuda::CUDAGuard guard(x.device());
+  torch::Tensor launch_idx, status;
+  if (ticket) {
+    ticket->check_compatible(cu, idx, x.size(0), shift_state_pool.size(0), max_seqlen);
+    TORCH_CHECK(ticket->max_seqlen() == 1, "the fused form takes one-token sequences");
+    launch_idx = ticket->idx_snapshot();
+    status = ticket->status();
+  } else {
+    auto prepared = launch_validation(cu, idx, x.size(0), shift_state_pool.size(0));
+    launch_idx = std::move(prepared.idx);
+    status = std::move(prepared.status);
+  }
+  auto sum = torch::empty_like(x);
+  auto mixes = torch::empty({6, x.size(0), x.size(1)}, x.options());
+  check_rc(frwkv_tmix_mix6_add_layer_norm_forward(
+      x.data_ptr(), residual.data_ptr(), weight.data_ptr(), bias.data_ptr(), x_r.data_ptr(), x_w.data_ptr(),
+      x_k.data_ptr(), x_v.data_ptr(), x_a.data_ptr(), x_g.data_ptr(), shift_state_pool.data_ptr(),
+      launch_idx.data_ptr<int>(), status.data_ptr<int>(), sum.data_ptr(), mixes.data_ptr(), static_cast<int>(x.size(0)),
+      static_cast<int>(x.size(1)), static_cast<float>(eps), io_dtype_of(x), current_stream(x)));
+  std::vector<torch::Tensor> out{sum};
+  for (auto& t : mixes.unbind(0)) out.push_back(t);
+  return out;
+}
+
 // Token shift fused into up to eight projections (1..8 rows): outputs[j] = mix(x, prev, mixes[j]) @ weights[j]^T;
 // the shift states are updated afterwards.
 std::vector<torch::Tensor> tmix_shift_project_varlen(torch::Tensor x, torch::Tensor shift_state_pool,
@@ -804,6 +912,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tmix_mix6_forward_varlen", &tmix_mix6_forward_varlen, py::arg("x"), py::arg("shift_state_pool"),
         py::arg("x_r"), py::arg("x_w"), py::arg("x_k"), py::arg("x_v"), py::arg("x_a"), py::arg("x_g"),
         py::arg("cu_seqlens"), py::arg("state_indices"), py::arg("max_seqlen") = -1,
+        py::arg("validated_metadata") = py::none());
+  m.def("tmix_layer_norm_forward_varlen", &tmix_layer_norm_forward_varlen, py::arg("x"), py::arg("weight"),
+        py::arg("bias"), py::arg("eps") = 1e-5);
+  m.def("tmix_add_layer_norm_forward_varlen", &tmix_add_layer_norm_forward_varlen, py::arg("x"), py::arg("residual"),
+        py::arg("weight"), py::arg("bias"), py::arg("eps") = 1e-5, py::arg("batch_size") = -1);
+  m.def("tmix_add_last_layer_norm_forward_varlen", &tmix_add_last_layer_norm_forward_varlen, py::arg("x"),
+        py::arg("residual"), py::arg("weight"), py::arg("bias"), py::arg("eps") = 1e-5);
+  m.def("tmix_add_forward_varlen", &tmix_add_forward_varlen, py::arg("x"), py::arg("residual"));
+  m.def("tmix_mix6_add_layer_norm_forward_varlen", &tmix_mix6_add_layer_norm_forward_varlen, py::arg("x"),
+        py::arg("residual"), py::arg("weight"), py::arg("bias"), py::arg("shift_state_pool"), py::arg("x_r"),
+        py::arg("x_w"), py::arg("x_k"), py::arg("x_v"), py::arg("x_a"), py::arg("x_g"), py::arg("cu_seqlens"),
+        py::arg("state_indices"), py::arg("max_seqlen") = -1, py::arg("eps") = 1e-5,
         py::arg("validated_metadata") = py::none());
   m.def("tmix_shift_project_varlen", &tmix_shift_project_varlen, py::arg("x"), py::arg("shift_state_pool"),
         py::arg("mixes"), py::arg("weights"), py::arg("cu_seqlens"), py::arg("state_indices"),

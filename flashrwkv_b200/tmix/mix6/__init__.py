@@ -37,6 +37,44 @@ def infer_tmix_mix6_forward_varlen(x, x_r, x_w, x_k, x_v, x_a, x_g, *, shift_sta
         -1 if max_seqlen is None else int(max_seqlen), validated_metadata))
 
 
+def infer_tmix_mix6_add_layer_norm_forward_varlen(x, residual, weight, bias, x_r, x_w, x_k, x_v, x_a, x_g, *,
+                                                  shift_state_pool, cu_seqlens, state_indices,
+                                                  max_seqlen: int | None = None, eps: float = 1.0e-5,
+                                                  validated_metadata=None):
+    """Add + LayerNorm + token shift: returns `(x + residual, six mixed tensors)` and stores the normalised last row of
+    each sequence as its shift state (reference: `flashrwkv2/tmix/mix6/__init__.py:103-199`, which takes one row of
+    4096 channels).  Batches of one-token sequences (`max_seqlen=1`) run as ONE kernel; anything else as add +
+    LayerNorm followed by `infer_tmix_mix6_forward_varlen`.
+    """
+    from ..normalization import _check_affine, _check_eps, _check_rows, infer_tmix_add_layer_norm_forward_varlen
+
+    _check_rows(x, "x")
+    _check_rows(residual, "residual", x)
+    _check_affine(x, weight, bias)
+    mixes = (x_r, x_w, x_k, x_v, x_a, x_g)
+    for name, t in zip(("x_r", "x_w", "x_k", "x_v", "x_a", "x_g"), mixes):
+        check_io(name, t, x)
+        if t.shape != (x.shape[1],):
+            raise ValueError("normalization and mix parameters must have shape [C]")
+    if not isinstance(shift_state_pool, torch.Tensor):
+        raise TypeError("shift_state_pool must be a torch.Tensor")
+    if (shift_state_pool.dtype != x.dtype or not shift_state_pool.is_cuda or not shift_state_pool.is_contiguous()
+            or shift_state_pool.ndim != 2 or shift_state_pool.shape[1] != x.shape[1]
+            or shift_state_pool.device != x.device):
+        raise ValueError("shift_state_pool must be contiguous CUDA [slots,C] of x's dtype on x's device")
+    _check_metadata_inputs(cu_seqlens, state_indices)
+    if max_seqlen is not None and (not isinstance(max_seqlen, int) or isinstance(max_seqlen, bool) or max_seqlen <= 0):
+        raise ValueError("max_seqlen must be a positive integer")
+    eps = _check_eps(eps)
+    if max_seqlen == 1 and state_indices.numel() == x.shape[0]:
+        return tuple(extension().tmix_mix6_add_layer_norm_forward_varlen(
+            x, residual, weight, bias, shift_state_pool, *mixes, cu_seqlens, state_indices, 1, eps, validated_metadata))
+    summed, normalized = infer_tmix_add_layer_norm_forward_varlen(x, residual, weight, bias, eps=eps)
+    return (summed, *infer_tmix_mix6_forward_varlen(normalized, *mixes, shift_state_pool=shift_state_pool,
+                                                    cu_seqlens=cu_seqlens, state_indices=state_indices,
+                                                    max_seqlen=max_seqlen, validated_metadata=validated_metadata))
+
+
 def infer_tmix_shift_project_forward_varlen(x, mixes, weights, *, shift_state_pool, cu_seqlens, state_indices,
                                             max_seqlen: int | None = None, validated_metadata=None):
     """Token shift fused into the projections that consume it (no counterpart in the reference, which runs
@@ -91,4 +129,5 @@ def infer_tmix_shift_project_forward_varlen(x, mixes, weights, *, shift_state_po
     return tuple(outs)
 
 
-__all__ = ["infer_tmix_mix6_forward_varlen", "infer_tmix_shift_project_forward_varlen"]
+__all__ = ["infer_tmix_mix6_forward_varlen", "infer_tmix_mix6_add_layer_norm_forward_varlen",
+           "infer_tmix_shift_project_forward_varlen"]

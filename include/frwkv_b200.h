@@ -233,6 +233,33 @@ int frwkv_tmix_vres_gate_forward_varlen(const void* v, const void* v_first, cons
                                         long long total_rows, int channels, int io_dtype, frwkv_stream_t stream);
 
 /*
+ * Add + LayerNorm over rows of `channels` 16-bit values (fp32 statistics, biased variance, of the ROUNDED sum):
+ *   sum_out = x + residual ;  norm_out = (sum - mean) * rsqrt(var + eps) * weight + bias
+ *   residual == NULL : LayerNorm of x                       (tmix_layer_norm_forward_varlen)
+ *   weight == bias == NULL : plain add into sum_out         (tmix_add_forward_varlen)
+ *   sum_out == NULL : only the normalised rows              (tmix_add_last_layer_norm_forward_varlen)
+ *   all given : both outputs                                (tmix_add_layer_norm_forward_varlen)
+ * Replaces the normalization family of the reference (flashrwkv2/tmix/normalization/__init__.py:31-90).
+ */
+int frwkv_tmix_add_layer_norm_forward(const void* x, const void* residual, const void* weight, const void* bias,
+                                      void* sum_out, void* norm_out, long long rows, int channels, float eps,
+                                      int io_dtype, frwkv_stream_t stream);
+
+/*
+ * The same followed by the six-way token shift, for batches of one-token sequences (row i is sequence i):
+ *   sum_out = x + residual ; n = LayerNorm(sum) rounded ; mix_out[j] = n + (shift[slot_i] - n) * x_j ; shift[slot_i] = n
+ * mix_out is [6][rows][channels].  When *metadata_status != 0 the outputs are NaN and the shift states untouched.
+ * Replaces tmix_mix6_add_layer_norm_forward_varlen (flashrwkv2/tmix/mix6/__init__.py:103-199), which the reference
+ * restricts to one row of 4096 channels.
+ */
+int frwkv_tmix_mix6_add_layer_norm_forward(const void* x, const void* residual, const void* weight, const void* bias,
+                                           const void* x_r, const void* x_w, const void* x_k, const void* x_v,
+                                           const void* x_a, const void* x_g, void* shift_state_pool,
+                                           const int32_t* state_indices, const int32_t* metadata_status, void* sum_out,
+                                           void* mix_out, int rows, int channels, float eps, int io_dtype,
+                                           frwkv_stream_t stream);
+
+/*
  * Token shift fused into up to eight projections of the same rows (decode, 1..8 rows):
  *   y_j[m][n] = sum_c (x[m][c] + (prev[m][c] - x[m][c]) * mix_j[c]) * weight_j[n][c]
  * with prev the previous row of the same sequence or, for its first row, shift_state_pool[state_indices[s]]; afterwards

@@ -251,3 +251,20 @@ def linear_nt(x, weight, act: str = "none"):
     _load().oracle_linear_nt(_p(x), _p(weight), ctypes.c_int64(M), ctypes.c_int(Nn),
                              ctypes.c_int(K), ctypes.c_int(code), _p(y))
     return y
+
+
+def layer_norm(x, weight, bias, eps: float = 1e-5, residual=None, io_dtype=None):
+    """`LayerNorm(x [+ residual])` over the last axis in float64 (biased variance), the formula of the reference's
+    normalization tests (tests/tmix/normalization/test.py:17-35: `F.layer_norm` of the summed rows).  With `residual`
+    returns `(sum, normalized)`; `io_dtype` rounds the sum first, as the kernels' returned sum tensor is."""
+    xs = _f32(x).astype(np.float64)
+    if residual is not None:
+        xs = xs + _f32(residual).astype(np.float64)
+        if io_dtype is not None:
+            xs = torch.from_numpy(xs).to(io_dtype).double().numpy()
+    mean = xs.mean(axis=-1, keepdims=True)
+    var = ((xs - mean) ** 2).mean(axis=-1, keepdims=True)
+    out = (xs - mean) / np.sqrt(var + eps) * _f32(weight).astype(np.float64) + _f32(bias).astype(np.float64)
+    out = out.astype(np.float32)
+    return (xs.astype(np.float32), out) if residual is not None else out
+

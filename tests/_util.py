@@ -21,6 +21,7 @@ _IO_DTYPE = {
     "tmix_vres": torch.float16,
     "tmix_mix6": torch.float16,
     "tmix_lowrank": torch.float16,
+    "tmix_norm": torch.float16,
 }
 
 

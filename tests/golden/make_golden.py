@@ -19,7 +19,7 @@ Cases (reference file:line of the oracle that produced the expectation):
   rl_fp16             tests/rl_infctx/wkv7/test.py:12-53    lengths (2,5), fp16 io, decay_bias
   statetune           tests/tmix/wkv7/statetune/test.py:39-87 + autograd (:109-124), scale 0.75
   pretrain            tests/tmix/wkv7/pretrain/test.py:49-70 + autograd (:108-128), (B,T,H)=(2,32,2)
-  tmix_*              formulas of tests/tmix/{mix6,kk_a_gate,lnx_rkvres_xg,vres_gate,linear}/test.py
+  tmix_*              formulas of tests/tmix/{mix6,kk_a_gate,lnx_rkvres_xg,vres_gate,linear,normalization}/test.py
 """
 from __future__ import annotations
 
@@ -224,6 +224,30 @@ def main() -> None:
     rank = (xw.float() @ w1.float().T).to(torch.float16)
     outw = torch.tanh(rank.float()) @ w2.float().T
     _save("tmix_lowrank", x=xw, w1=w1, w2=w2, rank=rank, out_tanh=outw)
+
+    # ---- tmix_norm: add + LayerNorm family, formulas of tests/tmix/normalization/test.py:17-35 (F.layer_norm of the
+    # rounded sum) and the fused add + LayerNorm + mix6 of tests/tmix/mix6/test.py:312-368 on three one-token rows
+    torch.manual_seed(53)
+    import torch.nn.functional as Fn
+    rows, Cn = 3, 256
+    xn = (torch.randn(rows, Cn) * 0.03).to(torch.float16)
+    rn = (torch.randn(rows, Cn) * 0.02).to(torch.float16)
+    wn = (torch.randn(Cn) * 0.1 + 1.0).to(torch.float16)
+    bn = (torch.randn(Cn) * 0.01).to(torch.float16)
+    params = [(torch.randn(Cn) * 0.1).to(torch.float16) for _ in range(6)]
+    initial = torch.randn(5, Cn).to(torch.float16)
+    slots = torch.tensor([3, 0, 4], dtype=torch.int32)
+    summed = xn + rn                                               # fp16 add, as `x + residual` in the reference test
+    ln_x = Fn.layer_norm(xn.float(), (Cn,), wn.float(), bn.float(), 1e-5)
+    ln_sum = Fn.layer_norm(summed.float(), (Cn,), wn.float(), bn.float(), 1e-5)
+    normalized = ln_sum.to(torch.float16)
+    mixed = torch.stack([(normalized.float() + (initial[slots.long()].float() - normalized.float()) * p.float())
+                         for p in params])
+    shift_after = initial.clone()
+    shift_after[slots.long()] = normalized
+    _save("tmix_norm", x=xn, residual=rn, weight=wn, bias=bn, mix=torch.stack(params), shift_pool=initial,
+          state_indices=slots, cu_seqlens=torch.arange(rows + 1, dtype=torch.int32), sum=summed, ln_x=ln_x,
+          ln_sum=ln_sum, mixed=mixed, shift_after=shift_after)
 
 
 if __name__ == "__main__":

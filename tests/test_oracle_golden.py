@@ -146,3 +146,11 @@ def test_fp16_state_contract_with_dither(oracle):
                                   elapsed_state_pool=g["elapsed_state_pool"] + 1, cu_seqlens=g["cu_seqlens"],
                                   state_indices=g["state_indices"], scale=g["scale"], decay_bias=g["decay_bias"])
     assert (torch.from_numpy(shifted["state_pool"]) != want_state).float().mean().item() > 1e-2
+
+
+def test_layer_norm_family_formulas(oracle):
+    g = load_golden("tmix_norm")
+    assert rel_rmse(oracle.layer_norm(g["x"], g["weight"], g["bias"]), g["ln_x"]) < 1e-5
+    summed, normed = oracle.layer_norm(g["x"], g["weight"], g["bias"], residual=g["residual"], io_dtype=torch.float16)
+    assert np.array_equal(summed, g["sum"].float().numpy())
+    assert rel_rmse(normed, g["ln_sum"]) < 1e-5

@@ -217,3 +217,55 @@ def test_shift_project_fused_vs_oracle(oracle, dtype, lengths):
     for s, b in enumerate(cu[1:].tolist()):
         expect_pool[idx[s]] = x[b - 1]
     assert torch.equal(d_pool.cpu(), expect_pool)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_add_layer_norm_family(oracle, dtype):
+    """add, LayerNorm, add + LayerNorm (both outputs / last only) against the oracle; the sum is the exactly rounded
+    16-bit sum (reference: tests/tmix/normalization/test.py:17-88)."""
+    import flashrwkv_b200 as F
+
+    gen = torch.Generator().manual_seed(54)
+    for rows, C in ((5, 8), (4, 4096), (193, 2048)):
+        x = torch.randn(rows, C, generator=gen).to(dtype)
+        res = torch.randn(rows, C, generator=gen).to(dtype)
+        w = torch.randn(C, generator=gen).to(dtype)
+        b = torch.randn(C, generator=gen).to(dtype)
+        dx, dr, dw, db = x.cuda(), res.cuda(), w.cuda(), b.cuda()
+        exact_sum = (x.float() + res.float()).to(dtype)
+        assert torch.equal(F.infer_tmix_add_forward_varlen(dx, dr).cpu(), exact_sum)
+        ln = F.infer_tmix_layer_norm_forward_varlen(dx, dw, db)
+        assert rel_rmse(ln.float().cpu(), oracle.layer_norm(x, w, b)) <= TOL[dtype]
+        s, n = F.infer_tmix_add_layer_norm_forward_varlen(dx, dr, dw, db, batch_size=min(2, rows))
+        ref_sum, ref_norm = oracle.layer_norm(x, w, b, residual=res, io_dtype=dtype)
+        assert torch.equal(s.cpu(), exact_sum)
+        assert rel_rmse(n.float().cpu(), ref_norm) <= TOL[dtype]
+        last = F.infer_tmix_add_last_layer_norm_forward_varlen(dx, dr, dw, db, eps=1e-5)
+        assert torch.equal(last, n)
+    with pytest.raises(ValueError, match="eps"):
+        F.infer_tmix_layer_norm_forward_varlen(dx, dw, db, eps=0.0)
+    with pytest.raises(ValueError, match="same shape"):
+        F.infer_tmix_add_forward_varlen(dx, dr[:-1])
+
+
+def test_golden_mix6_add_layer_norm_fused_and_composed():
+    """The fused one-kernel form (one-token sequences) and the composed form give the golden outputs of the
+    reference's formulas, and the shift states receive the normalised rows."""
+    import flashrwkv_b200 as F
+
+    g = load_golden("tmix_norm")
+    mix = [m.cuda() for m in g["mix"]]
+    for max_seqlen in (1, None):
+        pool = g["shift_pool"].cuda().clone()
+        outs = F.infer_tmix_mix6_add_layer_norm_forward_varlen(
+            g["x"].cuda(), g["residual"].cuda(), g["weight"].cuda(), g["bias"].cuda(), *mix, shift_state_pool=pool,
+            cu_seqlens=g["cu_seqlens"].cuda(), state_indices=g["state_indices"].cuda(), max_seqlen=max_seqlen)
+        torch.cuda.synchronize()
+        assert len(outs) == 7
+        assert torch.equal(outs[0].cpu(), g["sum"])
+        for j in range(6):
+            assert torch.allclose(outs[1 + j].float().cpu(), g["mixed"][j], atol=0.01, rtol=0.01)
+            assert rel_rmse(outs[1 + j].float().cpu(), g["mixed"][j]) <= TOL[torch.float16]
+        assert torch.allclose(pool.float().cpu(), g["shift_after"].float(), atol=0.01, rtol=0.01)
+        untouched = [1, 2]
+        assert torch.equal(pool[untouched].cpu(), g["shift_pool"][untouched])
