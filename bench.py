@@ -210,7 +210,7 @@ def _time_cuda(fn, warmup=2, iters=5):
 def _extras(dev):
     """Secondary workloads of the same path, timed briefly on this GPU: chunked prefill (B8 T4096 H32), training
     forward+backward (B8 T4096 H64) and the TMix layer chain (C=2048, M in {1,4,7,512}).  Roofline fractions use
-    the algorithmic bytes / FLOPs of DESIGN.md and the measured peaks."""
+    the algorithmic bytes / FLOPs stated beside each workload and the measured peaks."""
     import torch
 
     import flashrwkv_b200 as F

@@ -60,7 +60,7 @@ def _save(name: str, **arrays) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the FlashRWKV reference checkout")
     ref = Path(ap.parse_args().reference)
     sys.path.insert(0, str(ref))
     wkv_test = _load(ref, "tests/tmix/wkv7/test.py", "ref_wkv7_test")
