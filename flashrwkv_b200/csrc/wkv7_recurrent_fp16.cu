@@ -12,9 +12,9 @@
 // Two kernels share the per-token step:
 //   * wkv7_fp16_register_kernel: any packed batch; one warp per half (32 value columns) of a (sequence, head), state in
 //     registers as fp32 copies of the fp16 values for the whole sequence;
-//   * wkv7_fp16_decode_kernel: batches of one token per sequence; persistent CTAs stream the 8 KB state tiles through a
-//     24-stage shared-memory ring with bulk copies (loader lane, storer lane, seven pairs of consumer warps), as the
-//     fp32 decode kernel does with its 16 KB tiles.
+//   * wkv7_fp16_decode_kernel: batches of one token per sequence; persistent CTAs stream the 8 KB state tiles, two
+//     adjacent heads at a time, through a shared-memory ring with bulk copies (loader warp, storer lane, seven pairs of
+//     consumer warps), as the fp32 decode kernel does with its 16 KB tiles.
 // Lane layout in both: lane = kg*8 + vq holds key rows [16 kg, 16 kg + 16) of value columns [4 vq, 4 vq + 4) of its half.
 //
 // Replaces the reference's fp16-state family (csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu; contract
@@ -194,14 +194,21 @@ __global__ __launch_bounds__(kRegWarps * 32, 4) void wkv7_fp16_register_kernel(
 }
 
 // ---- decode: persistent CTAs, bulk-copy ring ----------------------------------------------------------------------------
-constexpr int kStages = 24;
-constexpr int kTileBytes = kD * kD * 2;              // 8 KB
-constexpr int kTokBytes = 6 * kD * 2;                // r, w, k, v, a, b rows of one (token, head)
-constexpr int kStageBytes = kTileBytes + kTokBytes;  // 8,960
+// A stage holds kT state tiles of adjacent heads of one sequence (adjacent in the pool and in the token tensors) and
+// their token rows: [kT x 8 KB tiles][6 vectors x kT x 128 B].  Two tiles per stage halve the number of bulk copies per
+// byte: with 8 KB copies the per-copy latency of the copy pipeline, not DRAM bandwidth, bounds the kernel.
+constexpr int kTileBytes = kD * kD * 2;  // 8 KB
+constexpr int kTokBytes = 6 * kD * 2;    // r, w, k, v, a, b rows of one (token, head)
 constexpr int kConsumerPairs = 7;
 constexpr int kDecodeThreads = 32 * (2 + 2 * kConsumerPairs);
-constexpr int kDecodeSmem = kStages * kStageBytes;   // 215,040
-constexpr int kMetaTiles = 512;                      // tiles per CTA whose metadata is staged in shared memory
+constexpr int kMetaUnits = 512;          // units per CTA whose metadata is staged in shared memory
+
+template <int kT>
+struct RingCfg {
+  static constexpr int kStages = 24 / kT;
+  static constexpr int kStageBytes = kT * (kTileBytes + kTokBytes);
+  static constexpr int kSmem = kStages * kStageBytes;  // 215,040
+};
 
 __device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),
@@ -212,25 +219,28 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* mbar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(umma::smem_u32(mbar)) : "memory");
 }
 
-template <typename io_t>
+template <typename io_t, int kT>
 __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_fp16_decode_kernel(
     const int* __restrict__ state_indices, const int* __restrict__ metadata_status,
     const int* __restrict__ elapsed_pool, __half* __restrict__ state_pool, const io_t* __restrict__ r_ptr,
     const io_t* __restrict__ w_ptr, const io_t* __restrict__ k_ptr, const io_t* __restrict__ v_ptr,
     const io_t* __restrict__ a_ptr, const io_t* __restrict__ b_ptr, const io_t* __restrict__ bias_ptr,
-    io_t* __restrict__ y_ptr, int num_tiles, int num_heads, long long output_elements, float scale, int reverse,
+    io_t* __restrict__ y_ptr, int num_units, int num_heads, long long output_elements, float scale, int reverse,
     int* __restrict__ error_flag) {
   using IO = Io16<io_t>;
+  using R = RingCfg<kT>;
+  constexpr int kStages = R::kStages, kStageBytes = R::kStageBytes;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full_bar[kStages], done_bar[kStages], empty_bar[kStages];
-  // state slot and elapsed counter of this CTA's first kMetaTiles tiles, fetched by all threads before the pipeline
-  // starts: the loader, the storer and the consumers would otherwise each wait for two dependent global loads per tile
-  __shared__ int slot_s[kMetaTiles], elapsed_s[kMetaTiles];
-  // i-th tile of this CTA; `reverse` walks the pool from the other end (a caller that alternates it between decode
+  // state slot and elapsed counter of this CTA's first kMetaUnits units, fetched by all threads before the pipeline
+  // starts: the loader, the storer and the consumers would otherwise each wait for two dependent global loads per unit
+  __shared__ int slot_s[kMetaUnits], elapsed_s[kMetaUnits];
+  const int units_per_seq = num_heads / kT;
+  // i-th unit of this CTA; `reverse` walks the pool from the other end (a caller that alternates it between decode
   // steps finds the tiles it touched last, still in L2, first)
-  const auto tile_of = [&](int i) {
+  const auto unit_of = [&](int i) {
     const int fwd = blockIdx.x + i * gridDim.x;
-    return reverse ? num_tiles - 1 - fwd : fwd;
+    return reverse ? num_units - 1 - fwd : fwd;
   };
   if (metadata_status != nullptr && metadata_status[0] != 0) {
     fill_nan(y_ptr, output_elements, kDecodeThreads);
@@ -239,89 +249,94 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_fp16_decode_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
-      umma::mbar_init(&full_bar[i], 1 + 32);  // the tile's expect_tx arrival + one arrival per loader lane
+      umma::mbar_init(&full_bar[i], 1 + 32);  // the tiles' expect_tx arrival + one arrival per loader lane
       umma::mbar_init(&done_bar[i], 2);
       umma::mbar_init(&empty_bar[i], 1);
     }
     umma::mbar_fence_init();
   }
-  const int my_tiles = ((int)blockIdx.x < num_tiles) ? (num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-  for (int i = threadIdx.x; i < min(my_tiles, kMetaTiles); i += kDecodeThreads) {
-    const int slot = state_indices[tile_of(i) / num_heads];
+  const int my_units = ((int)blockIdx.x < num_units) ? (num_units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  for (int i = threadIdx.x; i < min(my_units, kMetaUnits); i += kDecodeThreads) {
+    const int slot = state_indices[unit_of(i) / units_per_seq];
     slot_s[i] = slot;
     elapsed_s[i] = elapsed_pool[slot];
   }
   __syncthreads();
-  const auto slot_of = [&](int i) { return i < kMetaTiles ? slot_s[i] : state_indices[tile_of(i) / num_heads]; };
+  const auto slot_of = [&](int i) { return i < kMetaUnits ? slot_s[i] : state_indices[unit_of(i) / units_per_seq]; };
   bool ok = true;
 
   if (warp == 0) {
-    // loader (whole warp).  Lane 0 brings the state tile in with one bulk copy; the six 128-byte token rows go as
-    // 48 16-byte cp.async pieces spread over the lanes (a bulk copy per row would cost the copy engine a descriptor
-    // each, and that fixed cost per tile is what bounds the pipeline).  Each lane's pieces count on the stage's
-    // "full" barrier through cp.async.mbarrier.arrive.noinc.
-    const io_t* const row_src0 = lane < 8 ? r_ptr : (lane < 16 ? w_ptr : (lane < 24 ? k_ptr : v_ptr));
-    const io_t* const row_src1 = lane < 8 ? a_ptr : b_ptr;  // second piece, lanes 0..15
-    for (int i = 0; i < my_tiles && ok; ++i) {
+    // loader (whole warp).  Lane 0 brings the state tiles in with one bulk copy; the 6 x kT token rows of 128 bytes go
+    // as 16-byte cp.async pieces spread over the lanes (a bulk copy per row would cost the copy engine a descriptor
+    // each).  Each lane's pieces count on the stage's "full" barrier through cp.async.mbarrier.arrive.noinc.
+    for (int i = 0; i < my_units && ok; ++i) {
       const int st = i % kStages;
       if (i >= kStages) ok = umma::mbar_wait(&empty_bar[st], ((i / kStages) - 1) & 1);
       if (!ok) break;
-      const int tile = tile_of(i);
-      const int seq = tile / num_heads, head = tile % num_heads;
-      const long long tb = ((long long)seq * num_heads + head) * kD;  // one token per sequence
+      const int unit = unit_of(i);
+      const int seq = unit / units_per_seq, head0 = kT * (unit % units_per_seq);
+      const long long tb = ((long long)seq * num_heads + head0) * kD;  // one token per sequence
       unsigned char* stage = smem + st * kStageBytes;
       if (lane == 0) {
-        const __half* src = state_pool + ((long long)slot_of(i) * num_heads + head) * (kD * kD);
-        umma::mbar_expect_tx(&full_bar[st], kTileBytes);
-        umma::bulk_g2s(stage, src, kTileBytes, &full_bar[st]);
+        const __half* src = state_pool + ((long long)slot_of(i) * num_heads + head0) * (kD * kD);
+        umma::mbar_expect_tx(&full_bar[st], kT * kTileBytes);
+        umma::bulk_g2s(stage, src, kT * kTileBytes, &full_bar[st]);
       }
-      const uint32_t rows = umma::smem_u32(stage + kTileBytes);
-      umma::cp_async16(rows + lane * 16, row_src0 + tb + 8 * (lane & 7), 16u);
-      if (lane < 16) umma::cp_async16(rows + 512 + lane * 16, row_src1 + tb + 8 * (lane & 7), 16u);
+      const uint32_t rows = umma::smem_u32(stage + kT * kTileBytes);
+#pragma unroll
+      for (int p = lane; p < 48 * kT; p += 32) {  // piece p: vector p / (8 kT), 16-byte piece p % (8 kT) of its kT rows
+        const int vec = p / (8 * kT), within = p % (8 * kT);
+        const io_t* src = vec == 0 ? r_ptr : vec == 1 ? w_ptr : vec == 2 ? k_ptr : vec == 3 ? v_ptr : vec == 4 ? a_ptr : b_ptr;
+        umma::cp_async16(rows + p * 16, src + tb + 8 * within, 16u);
+      }
       asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(umma::smem_u32(&full_bar[st])) : "memory");
     }
   } else if (warp == 1) {
     if (lane == 0) {  // storer
-      for (int i = 0; i < my_tiles && ok; ++i) {
+      for (int i = 0; i < my_units && ok; ++i) {
         const int st = i % kStages;
         ok = umma::mbar_wait(&done_bar[st], (i / kStages) & 1);
         if (!ok) break;
-        const int tile = tile_of(i);
-        const int head = tile % num_heads;
-        __half* dst = state_pool + ((long long)slot_of(i) * num_heads + head) * (kD * kD);
-        bulk_s2g(dst, smem + st * kStageBytes, kTileBytes);
+        const int head0 = kT * (unit_of(i) % units_per_seq);
+        __half* dst = state_pool + ((long long)slot_of(i) * num_heads + head0) * (kD * kD);
+        bulk_s2g(dst, smem + st * kStageBytes, kT * kTileBytes);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        // at most one store may still be reading shared memory: the stage of tile i-1 is free again
+        // at most one store may still be reading shared memory: the stage of unit i-1 is free again
         asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         if (i >= 1) mbar_arrive(&empty_bar[(i - 1) % kStages]);
       }
       asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-      if (my_tiles > 0 && ok) mbar_arrive(&empty_bar[(my_tiles - 1) % kStages]);
+      if (my_units > 0 && ok) mbar_arrive(&empty_bar[(my_units - 1) % kStages]);
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all state writes are complete before exit
     }
   } else {
     const int pair = (warp - 2) >> 1, vhalf = (warp - 2) & 1;
     const int kg = lane >> 3, vq = lane & 7;
     const int row0 = kg * 16, col0 = vhalf * 32 + vq * 4;
-    for (int i = pair; i < my_tiles && ok; i += kConsumerPairs) {
+    for (int i = pair; i < my_units && ok; i += kConsumerPairs) {
       const int st = i % kStages;
-      const int tile = tile_of(i);
-      const int seq = tile / num_heads, head = tile % num_heads;
-      const uint32_t phase0 = (uint32_t)(head * kD) + (uint32_t)(i < kMetaTiles ? elapsed_s[i] : elapsed_pool[slot_of(i)]);
+      const int unit = unit_of(i);
+      const int seq = unit / units_per_seq, head0 = kT * (unit % units_per_seq);
+      const uint32_t elapsed = (uint32_t)(i < kMetaUnits ? elapsed_s[i] : elapsed_pool[slot_of(i)]);
       ok = umma::mbar_wait(&full_bar[st], (i / kStages) & 1);
       if (!ok) break;
       unsigned char* stage = smem + st * kStageBytes;
-      __half* tile_rows = reinterpret_cast<__half*>(stage) + row0 * kD + col0;
-      const io_t* tok = reinterpret_cast<const io_t*>(stage + kTileBytes);
-      float4 s[16];
+      const io_t* tok = reinterpret_cast<const io_t*>(stage + kT * kTileBytes);  // vector j of tile t at (j*kT + t)*64
+#pragma unroll 1
+      for (int t = 0; t < kT; ++t) {
+        const int head = head0 + t;
+        __half* tile_rows = reinterpret_cast<__half*>(stage + t * kTileBytes) + row0 * kD + col0;
+        float4 s[16];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) s[j] = half4_to_float4(*reinterpret_cast<const uint2*>(tile_rows + j * kD));
-      const Out4 o = token_step_fp16<io_t>(s, tile_rows, tok + 0 * kD, tok + 1 * kD, tok + 2 * kD, tok + 3 * kD, tok + 4 * kD,
-                                           tok + 5 * kD, bias_ptr != nullptr ? bias_ptr + head * kD : nullptr, phase0,
-                                           row0, col0, scale, false);
-      if (kg == 0) {
-        const long long tb = ((long long)seq * num_heads + head) * kD;
-        *reinterpret_cast<uint2*>(y_ptr + tb + col0) = make_uint2(IO::pack(o.o0, o.o1), IO::pack(o.o2, o.o3));
+        for (int j = 0; j < 16; ++j) s[j] = half4_to_float4(*reinterpret_cast<const uint2*>(tile_rows + j * kD));
+        const Out4 o = token_step_fp16<io_t>(s, tile_rows, tok + (0 * kT + t) * kD, tok + (1 * kT + t) * kD,
+                                             tok + (2 * kT + t) * kD, tok + (3 * kT + t) * kD, tok + (4 * kT + t) * kD,
+                                             tok + (5 * kT + t) * kD, bias_ptr != nullptr ? bias_ptr + head * kD : nullptr,
+                                             (uint32_t)(head * kD) + elapsed, row0, col0, scale, false);
+        if (kg == 0) {
+          const long long tb = ((long long)seq * num_heads + head) * kD;
+          *reinterpret_cast<uint2*>(y_ptr + tb + col0) = make_uint2(IO::pack(o.o0, o.o1), IO::pack(o.o2, o.o3));
+        }
       }
       umma::fence_async_smem();  // the bulk store reads what this warp just wrote
       __syncwarp();
@@ -354,18 +369,24 @@ int launch_fp16(const int* cu, const int* idx, const int* status, const int* ela
   const long long out_elems = (long long)total_tokens * num_heads * kD;
   const int tiles = num_sequences * num_heads;
   if (max_seqlen == 1 && total_tokens == num_sequences && tiles >= 1024) {
-    cudaError_t e = cudaFuncSetAttribute(wkv7_fp16_decode_kernel<io_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kDecodeSmem);
-    if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "wkv7_recurrent_fp16: %s", cudaGetErrorString(e));
     int device = 0, sm_count = 0;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-    const int grid = sm_count > 0 && sm_count < tiles ? sm_count : tiles;
-    wkv7_fp16_decode_kernel<io_t><<<grid, kDecodeThreads, kDecodeSmem, stream>>>(
-        idx, status, elapsed, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w),
-        static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),
-        static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), tiles, num_heads, out_elems,
-        scale, reverse, nullptr);
+#define FRWKV_FP16_DECODE(KT)                                                                                     \
+  {                                                                                                               \
+    cudaError_t e = cudaFuncSetAttribute(wkv7_fp16_decode_kernel<io_t, KT>,                                       \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, RingCfg<KT>::kSmem);        \
+    if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "wkv7_recurrent_fp16: %s", cudaGetErrorString(e));          \
+    const int units = tiles / KT;                                                                                 \
+    const int grid = sm_count > 0 && sm_count < units ? sm_count : units;                                         \
+    wkv7_fp16_decode_kernel<io_t, KT><<<grid, kDecodeThreads, RingCfg<KT>::kSmem, stream>>>(                      \
+        idx, status, elapsed, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w),                    \
+        static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),                    \
+        static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), units, num_heads,     \
+        out_elems, scale, reverse, nullptr);                                                                      \
+  }
+    if (num_heads % 2 == 0) FRWKV_FP16_DECODE(2) else FRWKV_FP16_DECODE(1)
+#undef FRWKV_FP16_DECODE
     return check_launch("wkv7_fp16_decode_kernel");
   }
   const long long units = (long long)tiles * 2;
