@@ -30,6 +30,7 @@ CUDA_SOURCES = [
     "metadata.cu",
     "wkv7_recurrent.cu",
     "wkv7_recurrent_fp16.cu",
+    "wkv7_recurrent_wide.cu",
     "umma_selftest.cu",
     "wkv7_chunk_fwd.cu",
     "tmix_elementwise.cu",

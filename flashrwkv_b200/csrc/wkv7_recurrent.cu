@@ -23,6 +23,11 @@
 #include "umma.cuh"
 
 namespace frwkv {
+// head sizes 128 and 256 (wkv7_recurrent_wide.cu)
+int launch_recurrent_wide(const int* cu, const int* idx, const int* status, float* state, const void* r, const void* w,
+                          const void* k, const void* v, const void* a, const void* b, const void* bias, void* y,
+                          float* y32, int total_tokens, int num_sequences, int num_heads, int head_size, int io_dtype,
+                          float scale, cudaStream_t stream);
 namespace {
 
 constexpr int kD = 64;
@@ -231,13 +236,24 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
 //                        the same per-token step as the register kernel on float4s read from the staged tile
 // CTA b owns the (sequence, head) tiles b, b + gridDim.x, ...; its i-th tile uses stage i % kStages.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kStages = 13;
+#ifndef FRWKV_DECODE_TILES_PER_STAGE
+#define FRWKV_DECODE_TILES_PER_STAGE 1
+#endif
+constexpr int kDecodeTilesPerStage = FRWKV_DECODE_TILES_PER_STAGE;
 constexpr int kTileBytes = kD * kD * 4;
-constexpr int kTokBytes = 6 * kD * 2;                 // r, w, k, v, a, b rows of one (token, head)
-constexpr int kStageBytes = kTileBytes + kTokBytes;   // 17,152
+constexpr int kTokBytes = 6 * kD * 2;  // r, w, k, v, a, b rows of one (token, head)
 constexpr int kConsumerPairs = 7;
 constexpr int kDecodeThreads = 32 * (2 + 2 * kConsumerPairs);
-constexpr int kDecodeSmem = kStages * kStageBytes;
+
+// A stage holds the state tiles of kT adjacent heads of one sequence (adjacent in the pool and in the token tensors) and
+// their token rows: [kT x 16 KB tiles][6 vectors x kT x 128 B].  Bigger bulk copies amortise the per-copy latency of
+// the copy pipeline; fewer stages remain for the same shared memory.
+template <int kT>
+struct RingCfg {
+  static constexpr int kStages = 13 / kT;
+  static constexpr int kStageBytes = kT * (kTileBytes + kTokBytes);
+  static constexpr int kSmem = kStages * kStageBytes;
+};
 
 __device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),
@@ -254,12 +270,12 @@ __device__ __forceinline__ void lds16(const unsigned char* p, uint32_t (&w)[8]) 
 }
 
 // One token on a staged tile: same arithmetic as token_step, but the state stays in shared memory (read twice,
-// written once) and the token vectors come from the stage's token area, so the consumer needs few registers and
-// touches no global memory except for the output.
+// written once) and the token vectors come from the stage's token area (vector j at tok + j * vstride bytes), so the
+// consumer needs few registers and touches no global memory except for the output.
 template <typename io_t>
 __device__ __forceinline__ StepOut tile_step_smem(float* __restrict__ tbase, const unsigned char* __restrict__ tok,
-                                                  const io_t* __restrict__ bias_ptr, int head, int row0, int col0,
-                                                  float scale) {
+                                                  int vstride, const io_t* __restrict__ bias_ptr, int head, int row0,
+                                                  int col0, float scale) {
   using IO = Io16<io_t>;
   const int lane = threadIdx.x & 31;
   // retention of this lane group's 16 key rows: each of the 8 lanes that share the rows computes two of them and
@@ -267,7 +283,7 @@ __device__ __forceinline__ StepOut tile_step_smem(float* __restrict__ tbase, con
   float wv[16];
   {
     const int vq = lane & 7;
-    float2 x = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 1 * 128 + (row0 + 2 * vq) * 2));
+    float2 x = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 1 * vstride + (row0 + 2 * vq) * 2));
     if (bias_ptr != nullptr) {
       const float2 bx = IO::unpack(__ldg(reinterpret_cast<const uint32_t*>(bias_ptr + head * kD + row0 + 2 * vq)));
       x.x += bx.x;
@@ -281,15 +297,15 @@ __device__ __forceinline__ StepOut tile_step_smem(float* __restrict__ tbase, con
     }
   }
   uint32_t rr[8], aa[8];
-  lds16(tok + 0 * 128 + row0 * 2, rr);
-  lds16(tok + 4 * 128 + row0 * 2, aa);
-  const uint2 vraw = *reinterpret_cast<const uint2*>(tok + 3 * 128 + col0 * 2);
+  lds16(tok + 0 * vstride + row0 * 2, rr);
+  lds16(tok + 4 * vstride + row0 * 2, aa);
+  const uint2 vraw = *reinterpret_cast<const uint2*>(tok + 3 * vstride + col0 * 2);
   float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f, y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f, br = 0.f, kr = 0.f;
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
     const float2 a2 = IO::unpack(aa[p]), r2 = IO::unpack(rr[p]);
-    const float2 b2 = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 5 * 128 + (row0 + 2 * p) * 2));
-    const float2 k2 = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 2 * 128 + (row0 + 2 * p) * 2));
+    const float2 b2 = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 5 * vstride + (row0 + 2 * p) * 2));
+    const float2 k2 = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 2 * vstride + (row0 + 2 * p) * 2));
     br = fmaf(b2.x, r2.x, fmaf(b2.y, r2.y, br));
     kr = fmaf(k2.x, r2.x, fmaf(k2.y, r2.y, kr));
     const float4 q0 = *reinterpret_cast<const float4*>(tbase + (2 * p) * kD);
@@ -311,8 +327,8 @@ __device__ __forceinline__ StepOut tile_step_smem(float* __restrict__ tbase, con
   const float2 v01 = IO::unpack(vraw.x), v23 = IO::unpack(vraw.y);
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
-    const float2 b2 = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 5 * 128 + (row0 + 2 * p) * 2));
-    const float2 k2 = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 2 * 128 + (row0 + 2 * p) * 2));
+    const float2 b2 = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 5 * vstride + (row0 + 2 * p) * 2));
+    const float2 k2 = IO::unpack(*reinterpret_cast<const uint32_t*>(tok + 2 * vstride + (row0 + 2 * p) * 2));
     float4 q0 = *reinterpret_cast<const float4*>(tbase + (2 * p) * kD);
     float4 q1 = *reinterpret_cast<const float4*>(tbase + (2 * p + 1) * kD);
     const float w0 = wv[2 * p], w1 = wv[2 * p + 1];
@@ -332,21 +348,24 @@ __device__ __forceinline__ StepOut tile_step_smem(float* __restrict__ tbase, con
   return out;
 }
 
-template <typename io_t>
+template <typename io_t, int kT>
 __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_decode_pipelined_kernel(
     const int* __restrict__ state_indices, const int* __restrict__ metadata_status, float* __restrict__ state_pool,
     const io_t* __restrict__ r_ptr, const io_t* __restrict__ w_ptr, const io_t* __restrict__ k_ptr,
     const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr, const io_t* __restrict__ b_ptr,
-    const io_t* __restrict__ bias_ptr, io_t* __restrict__ y_ptr, float* __restrict__ y32_ptr, int num_tiles,
+    const io_t* __restrict__ bias_ptr, io_t* __restrict__ y_ptr, float* __restrict__ y32_ptr, int num_units,
     int num_heads, long long output_elements, float scale, int reverse, int* __restrict__ error_flag) {
   using IO = Io16<io_t>;
+  using R = RingCfg<kT>;
+  constexpr int kStages = R::kStages, kStageBytes = R::kStageBytes;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full_bar[kStages], done_bar[kStages], empty_bar[kStages];
-  // i-th tile of this CTA.  `reverse` walks the pool from the other end: a caller that alternates it between
-  // consecutive decode steps finds the tiles it touched last (still in the 126 MB L2) first.
-  const auto tile_of = [&](int i) {
+  const int units_per_seq = num_heads / kT;
+  // i-th unit (kT adjacent heads of one sequence) of this CTA.  `reverse` walks the pool from the other end: a caller
+  // that alternates it between consecutive decode steps finds the tiles it touched last (still in the 126 MB L2) first.
+  const auto unit_of = [&](int i) {
     const int fwd = blockIdx.x + i * gridDim.x;
-    return reverse ? num_tiles - 1 - fwd : fwd;
+    return reverse ? num_units - 1 - fwd : fwd;
   };
   if (metadata_status != nullptr && metadata_status[0] != 0) {
     const io_t nan16 = IO::store(quiet_nan());
@@ -367,69 +386,78 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_decode_pipelined_kerne
     umma::mbar_fence_init();
   }
   __syncthreads();
-  const int my_tiles = ((int)blockIdx.x < num_tiles) ? (num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const int my_units = ((int)blockIdx.x < num_units) ? (num_units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
   bool ok = true;
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < my_tiles && ok; ++i) {
+      for (int i = 0; i < my_units && ok; ++i) {
         const int st = i % kStages;
         if (i >= kStages) ok = umma::mbar_wait(&empty_bar[st], ((i / kStages) - 1) & 1);
         if (!ok) break;
-        const int tile = tile_of(i);
-        const int seq = tile / num_heads, head = tile % num_heads;
-        const float* src = state_pool + ((long long)state_indices[seq] * num_heads + head) * (kD * kD);
-        const long long tb = ((long long)seq * num_heads + head) * kD;  // one token per sequence: token == sequence
+        const int unit = unit_of(i);
+        const int seq = unit / units_per_seq, head0 = kT * (unit % units_per_seq);
+        const float* src = state_pool + ((long long)state_indices[seq] * num_heads + head0) * (kD * kD);
+        const long long tb = ((long long)seq * num_heads + head0) * kD;  // one token per sequence: token == sequence
         unsigned char* stage = smem + st * kStageBytes;
+        unsigned char* rows = stage + kT * kTileBytes;
         umma::mbar_expect_tx(&full_bar[st], kStageBytes);
-        umma::bulk_g2s(stage, src, kTileBytes, &full_bar[st]);
-        umma::bulk_g2s(stage + kTileBytes + 0 * 128, r_ptr + tb, 128, &full_bar[st]);
-        umma::bulk_g2s(stage + kTileBytes + 1 * 128, w_ptr + tb, 128, &full_bar[st]);
-        umma::bulk_g2s(stage + kTileBytes + 2 * 128, k_ptr + tb, 128, &full_bar[st]);
-        umma::bulk_g2s(stage + kTileBytes + 3 * 128, v_ptr + tb, 128, &full_bar[st]);
-        umma::bulk_g2s(stage + kTileBytes + 4 * 128, a_ptr + tb, 128, &full_bar[st]);
-        umma::bulk_g2s(stage + kTileBytes + 5 * 128, b_ptr + tb, 128, &full_bar[st]);
+        umma::bulk_g2s(stage, src, kT * kTileBytes, &full_bar[st]);
+        umma::bulk_g2s(rows + 0 * kT * 128, r_ptr + tb, kT * 128, &full_bar[st]);
+        umma::bulk_g2s(rows + 1 * kT * 128, w_ptr + tb, kT * 128, &full_bar[st]);
+        umma::bulk_g2s(rows + 2 * kT * 128, k_ptr + tb, kT * 128, &full_bar[st]);
+        umma::bulk_g2s(rows + 3 * kT * 128, v_ptr + tb, kT * 128, &full_bar[st]);
+        umma::bulk_g2s(rows + 4 * kT * 128, a_ptr + tb, kT * 128, &full_bar[st]);
+        umma::bulk_g2s(rows + 5 * kT * 128, b_ptr + tb, kT * 128, &full_bar[st]);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      for (int i = 0; i < my_tiles && ok; ++i) {
+      for (int i = 0; i < my_units && ok; ++i) {
         const int st = i % kStages;
         ok = umma::mbar_wait(&done_bar[st], (i / kStages) & 1);
         if (!ok) break;
-        const int tile = tile_of(i);
-        const int seq = tile / num_heads, head = tile % num_heads;
-        float* dst = state_pool + ((long long)state_indices[seq] * num_heads + head) * (kD * kD);
-        bulk_s2g(dst, smem + st * kStageBytes, kTileBytes);
+        const int unit = unit_of(i);
+        const int seq = unit / units_per_seq, head0 = kT * (unit % units_per_seq);
+        float* dst = state_pool + ((long long)state_indices[seq] * num_heads + head0) * (kD * kD);
+        bulk_s2g(dst, smem + st * kStageBytes, kT * kTileBytes);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        // at most one store may still be reading shared memory: the stage of tile i-1 is free again
+        // at most one store may still be reading shared memory: the stage of unit i-1 is free again
         asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         if (i >= 1) mbar_arrive(&empty_bar[(i - 1) % kStages]);
       }
       asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-      if (my_tiles > 0 && ok) mbar_arrive(&empty_bar[(my_tiles - 1) % kStages]);
+      if (my_units > 0 && ok) mbar_arrive(&empty_bar[(my_units - 1) % kStages]);
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all state writes are complete before exit
     }
   } else {
     const int pair = (warp - 2) >> 1, vhalf = (warp - 2) & 1;
     const int kg = lane >> 3, vq = lane & 7;
     const int row0 = kg * 16, col0 = vhalf * 32 + vq * 4;
-    for (int i = pair; i < my_tiles && ok; i += kConsumerPairs) {
+    // A pair's first unit must use a stage in its first phase: a wait for the SECOND fill of a fresh barrier (parity 1)
+    // returns at once.  So no more pairs work than there are stages.
+    constexpr int kActivePairs = kStages < kConsumerPairs ? kStages : kConsumerPairs;
+    for (int i = pair < kActivePairs ? pair : my_units; i < my_units && ok; i += kActivePairs) {
       const int st = i % kStages;
-      const int tile = tile_of(i);
-      const int seq = tile / num_heads, head = tile % num_heads;
+      const int unit = unit_of(i);
+      const int seq = unit / units_per_seq, head0 = kT * (unit % units_per_seq);
       ok = umma::mbar_wait(&full_bar[st], (i / kStages) & 1);
       if (!ok) break;
       unsigned char* stage = smem + st * kStageBytes;
-      const StepOut o = tile_step_smem<io_t>(reinterpret_cast<float*>(stage) + row0 * kD + col0, stage + kTileBytes,
-                                             bias_ptr, head, row0, col0, scale);
-      if (kg == 0) {
-        const long long tb = ((long long)seq * num_heads + head) * kD;
-        uint2 packed;
-        packed.x = IO::pack(o.o0, o.o1);
-        packed.y = IO::pack(o.o2, o.o3);
-        *reinterpret_cast<uint2*>(y_ptr + tb + col0) = packed;
-        if (y32_ptr != nullptr) *reinterpret_cast<float4*>(y32_ptr + tb + col0) = make_float4(o.o0, o.o1, o.o2, o.o3);
+#pragma unroll 1
+      for (int t = 0; t < kT; ++t) {
+        const int head = head0 + t;
+        const StepOut o = tile_step_smem<io_t>(reinterpret_cast<float*>(stage + t * kTileBytes) + row0 * kD + col0,
+                                               stage + kT * kTileBytes + t * 128, kT * 128, bias_ptr, head, row0, col0,
+                                               scale);
+        if (kg == 0) {
+          const long long tb = ((long long)seq * num_heads + head) * kD;
+          uint2 packed;
+          packed.x = IO::pack(o.o0, o.o1);
+          packed.y = IO::pack(o.o2, o.o3);
+          *reinterpret_cast<uint2*>(y_ptr + tb + col0) = packed;
+          if (y32_ptr != nullptr) *reinterpret_cast<float4*>(y32_ptr + tb + col0) = make_float4(o.o0, o.o1, o.o2, o.o3);
+        }
       }
       umma::fence_async_smem();  // the bulk store reads what this warp just wrote
       __syncwarp();
@@ -458,19 +486,25 @@ template <typename io_t>
 int launch_decode(const int* idx, const int* status, float* state, const void* r, const void* w, const void* k,
                   const void* v, const void* a, const void* b, const void* bias, void* y, float* y32,
                   int num_sequences, int num_heads, float scale, int reverse, cudaStream_t stream) {
-  cudaError_t e = cudaFuncSetAttribute(wkv7_decode_pipelined_kernel<io_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kDecodeSmem);
-  if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "wkv7_recurrent: %s", cudaGetErrorString(e));
   int device = 0, sm_count = 0;
   cudaGetDevice(&device);
   cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
   const int tiles = num_sequences * num_heads;
-  const int grid = sm_count > 0 && sm_count < tiles ? sm_count : tiles;
-  wkv7_decode_pipelined_kernel<io_t><<<grid, kDecodeThreads, kDecodeSmem, stream>>>(
-      idx, status, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w), static_cast<const io_t*>(k),
-      static_cast<const io_t*>(v), static_cast<const io_t*>(a), static_cast<const io_t*>(b),
-      static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, tiles, num_heads,
-      (long long)num_sequences * num_heads * kD, scale, reverse, nullptr);
+#define FRWKV_DECODE(KT)                                                                                          \
+  {                                                                                                               \
+    cudaError_t e = cudaFuncSetAttribute(wkv7_decode_pipelined_kernel<io_t, KT>,                                  \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, RingCfg<KT>::kSmem);        \
+    if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "wkv7_recurrent: %s", cudaGetErrorString(e));               \
+    const int units = tiles / KT;                                                                                 \
+    const int grid = sm_count > 0 && sm_count < units ? sm_count : units;                                         \
+    wkv7_decode_pipelined_kernel<io_t, KT><<<grid, kDecodeThreads, RingCfg<KT>::kSmem, stream>>>(                 \
+        idx, status, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w), static_cast<const io_t*>(k), \
+        static_cast<const io_t*>(v), static_cast<const io_t*>(a), static_cast<const io_t*>(b),                    \
+        static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, units, num_heads,                             \
+        (long long)num_sequences * num_heads * kD, scale, reverse, nullptr);                                      \
+  }
+  if (kDecodeTilesPerStage == 2 && num_heads % 2 == 0) FRWKV_DECODE(2) else FRWKV_DECODE(1)
+#undef FRWKV_DECODE
   return check_launch("wkv7_decode_pipelined_kernel");
 }
 
@@ -516,8 +550,12 @@ extern "C" int frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex(
   FRWKV_REQUIRE(total_tokens > 0 && num_heads > 0, "wkv7_recurrent: sizes must be positive");
   FRWKV_REQUIRE(num_sequences > 0 && num_sequences <= 65535,
                 "wkv7_recurrent: state_indices must contain 1..65535 sequences");
+  if (head_size == 128 || head_size == 256)  // the general kernel; the tuned ones below are for head size 64
+    return launch_recurrent_wide(cu_seqlens, state_indices, metadata_status, state_pool, r, decay_logits, k, v, a, b,
+                                 decay_bias, y, y_fp32, total_tokens, num_sequences, num_heads, head_size, io_dtype,
+                                 scale, reinterpret_cast<cudaStream_t>(stream));
   if (head_size != 64) {
-    return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_recurrent: head size %d is not built (only 64)", head_size);
+    return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_recurrent: head size must be 64, 128, or 256, got %d", head_size);
   }
   const long long blocks = ((long long)num_sequences * num_heads * 2 + 3) / 4;
   FRWKV_REQUIRE(blocks <= 0x7fffffffLL, "wkv7_recurrent: too many (sequence, head) pairs");

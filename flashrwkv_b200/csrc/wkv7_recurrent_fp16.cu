@@ -208,6 +208,9 @@ struct RingCfg {
   static constexpr int kStages = 24 / kT;
   static constexpr int kStageBytes = kT * (kTileBytes + kTokBytes);
   static constexpr int kSmem = kStages * kStageBytes;  // 215,040
+  // a consumer pair's first unit must find its stage in the stage's first phase (a wait for the second fill of a
+  // fresh barrier returns at once)
+  static_assert(kStages >= 7, "no more consumer pairs than stages");
 };
 
 __device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {

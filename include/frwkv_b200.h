@@ -75,7 +75,7 @@ int frwkv_validate_recurrent_metadata(const int32_t* cu_seqlens, const int32_t* 
  *     (the unrounded outputs, for precision checks)
  *   metadata_status : int32 device word; when *metadata_status != 0 the kernel
  *     fills y with NaN and leaves the state pool untouched.
- *   head_size must be 64.
+ *   head_size 64 (tuned kernels), 128 or 256 (general kernel).
  */
 int frwkv_wkv7_recurrent_fp32io16_forward_varlen(
     const int32_t* cu_seqlens, const int32_t* state_indices, const int32_t* metadata_status,

@@ -151,7 +151,7 @@ def test_c_abi_direct_call_matches_operator():
     assert torch.equal(y, y_op) and torch.equal(pool, pool_op)
     # unsupported head size and null pointers are refused with a message, nothing is launched
     rc = lib.frwkv_wkv7_recurrent_fp32io16_forward_varlen(
-        p(cu_s), p(idx_s), p(status), p(pool), *(p(t) for t in toks), None, p(y), None, N, idx.numel(), H, 128,
+        p(cu_s), p(idx_s), p(status), p(pool), *(p(t) for t in toks), None, p(y), None, N, idx.numel(), H, 96,
         -1, 1, ctypes.c_float(1.0), stream)
     assert rc == -2 and b"head size" in lib.frwkv_last_error()
     rc = lib.frwkv_wkv7_recurrent_fp32io16_forward_varlen(
@@ -323,3 +323,32 @@ def test_host_decode_loop_is_bit_identical_to_serial_decode():
     with pytest.raises(ValueError):
         HostDecodeLoop([t.cuda() for t in host[0]], state_pool=pool_a, cu_seqlens=cu, state_indices=idx,
                        validated_metadata=ticket)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D", [128, 256])
+def test_head_sizes_128_and_256_vs_oracle(oracle, D, dtype):
+    """The general kernel for the reference's other head sizes: ragged batch, slot selection, bias, scale."""
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+
+    H, lengths, slots = 2, (1, 9, 33), 5
+    N = sum(lengths)
+    toks = [t.to(dtype) for t in synthetic.wkv7_inputs(N, H, D, seed=900 + D, dtype=torch.float32)]
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lengths)]), dtype=torch.int32)
+    idx = torch.tensor([4, 0, 2], dtype=torch.int32)
+    gen = torch.Generator().manual_seed(D)
+    pool = torch.randn(slots, H, D, D, generator=gen) * 0.05
+    bias = (torch.randn(H, D, generator=gen) * 0.2).to(dtype)
+    d_pool = pool.cuda()
+    y32 = torch.empty(N, H, D, device="cuda")
+    y = F.infer_recurrent_fp32io16_forward_varlen(*[t.cuda() for t in toks], state_pool=d_pool, cu_seqlens=cu.cuda(),
+                                                  state_indices=idx.cuda(), scale=0.5, decay_bias=bias.cuda(),
+                                                  output_fp32=y32)
+    torch.cuda.synchronize()
+    ref = oracle.forward(*toks, state_pool=pool, cu_seqlens=cu, state_indices=idx, scale=0.5, decay_bias=bias)
+    assert max_abs(y32.cpu(), ref["y"]) <= Y_MAX_ABS
+    assert rel_rmse(y.float().cpu(), ref["y"]) <= REF_RMSE
+    assert _state_rel(d_pool, ref["state_pool"]) <= STATE_REL
+    assert torch.equal(y, y32.to(dtype))
+    assert torch.equal(d_pool[[1, 3]].cpu(), pool[[1, 3]])
