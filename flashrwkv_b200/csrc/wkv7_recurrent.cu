@@ -232,12 +232,15 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
 //   warp 0 (one lane)  : loader  - waits for a free stage, cp.async.bulk global -> shared, completion on full[stage]
 //   warp 1 (one lane)  : storer  - waits for done[stage] (both halves updated), cp.async.bulk shared -> global,
 //                                  and hands a stage back (empty[stage]) once its store has finished reading it
-//   warps 2..15        : seven pairs of consumer warps; a pair owns one tile at a time, one warp per half, and runs
-//                        the same per-token step as the register kernel on float4s read from the staged tile
-// CTA b owns the (sequence, head) tiles b, b + gridDim.x, ...; its i-th tile uses stage i % kStages.
+//   warps 2..15        : seven pairs of consumer warps (as many of them work as there are stages); a pair owns one
+//                        stage at a time, one warp per half of a tile, and runs the same per-token step as the register
+//                        kernel on float4s read from the staged tile(s)
+// CTA b owns the units (kT adjacent heads of a sequence) b, b + gridDim.x, ...; its i-th unit uses stage i % kStages.
 // ---------------------------------------------------------------------------------------------------------
+// 2: six stages of two adjacent heads (32 KB bulk copies), 42.97 us per launch at 256 x 32 tiles;
+// 1: thirteen stages of one tile (16 KB copies), 45.0 us.  Odd head counts always take 1.
 #ifndef FRWKV_DECODE_TILES_PER_STAGE
-#define FRWKV_DECODE_TILES_PER_STAGE 1
+#define FRWKV_DECODE_TILES_PER_STAGE 2
 #endif
 constexpr int kDecodeTilesPerStage = FRWKV_DECODE_TILES_PER_STAGE;
 constexpr int kTileBytes = kD * kD * 4;
