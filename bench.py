@@ -43,7 +43,7 @@ BYTES_PER_UNIT = 2 * D * D * 4 + 7 * D * 2
 BYTES_PER_LAUNCH = B * H * BYTES_PER_UNIT
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch at this size, from the ncu
 # capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 221_360_000
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 222_550_000
 FALLBACK_HBM_GBS = 6650.0
 
 
