@@ -109,34 +109,47 @@ __global__ void mix6_shift_update_kernel(const io_t* __restrict__ x, io_t* __res
   for (int i = threadIdx.x; i < (C >> 3); i += blockDim.x) dst[i] = src[i];
 }
 
-// ---- per-(row, head) kernels: one warp per head of 64 channels (two per lane) ------------------------------
-template <typename io_t>
+// ---- per-(row, head) kernels: one warp per head; a lane holds P = head_size / 64 pairs of channels, pair p at
+// channels 64 p + 2 lane (every load of the warp is one contiguous 128-byte segment) ----------------------------------
+template <typename io_t, int P>
 __global__ void kk_a_gate_kernel(const io_t* __restrict__ k, const io_t* __restrict__ k_k, const io_t* __restrict__ a0,
                                  const io_t* __restrict__ a12, const io_t* __restrict__ k_a, io_t* __restrict__ new_k,
                                  io_t* __restrict__ neg_kk, io_t* __restrict__ kka, long long units, int H) {
   chain_begin();
   using IO = Io16<io_t>;
+  constexpr int kHead = 64 * P;
   const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= units) return;
   const int lane = threadIdx.x & 31;
   const int head = (int)(unit % H);
-  const long long o = unit * 64 + 2 * lane;
-  const int c = head * 64 + 2 * lane;
-  const float2 kv = IO::unpack(*reinterpret_cast<const uint32_t*>(k + o));
-  const float2 kkv = IO::unpack(*reinterpret_cast<const uint32_t*>(k_k + c));
-  const float2 a0v = IO::unpack(*reinterpret_cast<const uint32_t*>(a0 + c));
-  const float2 a12v = IO::unpack(*reinterpret_cast<const uint32_t*>(a12 + o));
-  const float2 kav = IO::unpack(*reinterpret_cast<const uint32_t*>(k_a + c));
-  const float q0 = kv.x * kkv.x, q1 = kv.y * kkv.y;
-  const float nrm = fmaxf(sqrtf(warp_sum(q0 * q0 + q1 * q1)), 1e-12f);
-  const float g0 = sigmoidf_(a0v.x + a12v.x), g1 = sigmoidf_(a0v.y + a12v.y);
-  const float n0 = q0 / nrm, n1 = q1 / nrm;
-  *reinterpret_cast<uint32_t*>(new_k + o) = IO::pack(kv.x * (1.f + (g0 - 1.f) * kav.x), kv.y * (1.f + (g1 - 1.f) * kav.y));
-  *reinterpret_cast<uint32_t*>(neg_kk + o) = IO::pack(-n0, -n1);
-  *reinterpret_cast<uint32_t*>(kka + o) = IO::pack(n0 * g0, n1 * g1);
+  float2 kv[P], q[P], g[P], kav[P];
+  float ss = 0.f;
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    const long long o = unit * kHead + 64 * p + 2 * lane;
+    const int c = head * kHead + 64 * p + 2 * lane;
+    kv[p] = IO::unpack(*reinterpret_cast<const uint32_t*>(k + o));
+    const float2 kkv = IO::unpack(*reinterpret_cast<const uint32_t*>(k_k + c));
+    const float2 a0v = IO::unpack(*reinterpret_cast<const uint32_t*>(a0 + c));
+    const float2 a12v = IO::unpack(*reinterpret_cast<const uint32_t*>(a12 + o));
+    kav[p] = IO::unpack(*reinterpret_cast<const uint32_t*>(k_a + c));
+    q[p] = make_float2(kv[p].x * kkv.x, kv[p].y * kkv.y);
+    g[p] = make_float2(sigmoidf_(a0v.x + a12v.x), sigmoidf_(a0v.y + a12v.y));
+    ss = fmaf(q[p].x, q[p].x, fmaf(q[p].y, q[p].y, ss));
+  }
+  const float nrm = fmaxf(sqrtf(warp_sum(ss)), 1e-12f);
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    const long long o = unit * kHead + 64 * p + 2 * lane;
+    const float n0 = q[p].x / nrm, n1 = q[p].y / nrm;
+    *reinterpret_cast<uint32_t*>(new_k + o) =
+        IO::pack(kv[p].x * (1.f + (g[p].x - 1.f) * kav[p].x), kv[p].y * (1.f + (g[p].y - 1.f) * kav[p].y));
+    *reinterpret_cast<uint32_t*>(neg_kk + o) = IO::pack(-n0, -n1);
+    *reinterpret_cast<uint32_t*>(kka + o) = IO::pack(n0 * g[p].x, n1 * g[p].y);
+  }
 }
 
-template <typename io_t>
+template <typename io_t, int P>
 __global__ void lnx_rkvres_xg_kernel(const io_t* __restrict__ x, const io_t* __restrict__ r, const io_t* __restrict__ k,
                                      const io_t* __restrict__ v, const io_t* __restrict__ r_k,
                                      const io_t* __restrict__ weight, const io_t* __restrict__ bias,
@@ -144,27 +157,46 @@ __global__ void lnx_rkvres_xg_kernel(const io_t* __restrict__ x, const io_t* __r
                                      float eps) {
   chain_begin();
   using IO = Io16<io_t>;
+  constexpr int kHead = 64 * P;
   const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= units) return;
   const int lane = threadIdx.x & 31;
   const int head = (int)(unit % H);
-  const long long o = unit * 64 + 2 * lane;
-  const int c = head * 64 + 2 * lane;
-  const float2 xv = IO::unpack(*reinterpret_cast<const uint32_t*>(x + o));
-  const float2 rv = IO::unpack(*reinterpret_cast<const uint32_t*>(r + o));
-  const float2 kv = IO::unpack(*reinterpret_cast<const uint32_t*>(k + o));
-  const float2 vv = IO::unpack(*reinterpret_cast<const uint32_t*>(v + o));
-  const float2 gv = IO::unpack(*reinterpret_cast<const uint32_t*>(g + o));
-  const float2 rk = IO::unpack(*reinterpret_cast<const uint32_t*>(r_k + c));
-  const float2 wv = IO::unpack(*reinterpret_cast<const uint32_t*>(weight + c));
-  const float2 bv = IO::unpack(*reinterpret_cast<const uint32_t*>(bias + c));
-  const float mean = warp_sum(xv.x + xv.y) * (1.f / 64.f);
-  const float d0 = xv.x - mean, d1 = xv.y - mean;
-  const float var = warp_sum(d0 * d0 + d1 * d1) * (1.f / 64.f);
-  const float dot = warp_sum(rv.x * kv.x * rk.x + rv.y * kv.y * rk.y);
+  float2 xv[P];
+  float sum = 0.f, dot = 0.f;
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    const long long o = unit * kHead + 64 * p + 2 * lane;
+    const int c = head * kHead + 64 * p + 2 * lane;
+    xv[p] = IO::unpack(*reinterpret_cast<const uint32_t*>(x + o));
+    const float2 rv = IO::unpack(*reinterpret_cast<const uint32_t*>(r + o));
+    const float2 kv = IO::unpack(*reinterpret_cast<const uint32_t*>(k + o));
+    const float2 rk = IO::unpack(*reinterpret_cast<const uint32_t*>(r_k + c));
+    sum += xv[p].x + xv[p].y;
+    dot = fmaf(rv.x * kv.x, rk.x, fmaf(rv.y * kv.y, rk.y, dot));
+  }
+  const float mean = warp_sum(sum) * (1.f / kHead);
+  float sq = 0.f;
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    const float d0 = xv[p].x - mean, d1 = xv[p].y - mean;
+    sq = fmaf(d0, d0, fmaf(d1, d1, sq));
+  }
+  const float var = warp_sum(sq) * (1.f / kHead);
+  dot = warp_sum(dot);
   const float rstd = rsqrtf(var + eps);
-  *reinterpret_cast<uint32_t*>(out + o) = IO::pack((d0 * rstd * wv.x + bv.x + dot * vv.x) * gv.x,
-                                                   (d1 * rstd * wv.y + bv.y + dot * vv.y) * gv.y);
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    const long long o = unit * kHead + 64 * p + 2 * lane;
+    const int c = head * kHead + 64 * p + 2 * lane;
+    const float2 vv = IO::unpack(*reinterpret_cast<const uint32_t*>(v + o));
+    const float2 gv = IO::unpack(*reinterpret_cast<const uint32_t*>(g + o));
+    const float2 wv = IO::unpack(*reinterpret_cast<const uint32_t*>(weight + c));
+    const float2 bv = IO::unpack(*reinterpret_cast<const uint32_t*>(bias + c));
+    const float d0 = xv[p].x - mean, d1 = xv[p].y - mean;
+    *reinterpret_cast<uint32_t*>(out + o) = IO::pack((d0 * rstd * wv.x + bv.x + dot * vv.x) * gv.x,
+                                                     (d1 * rstd * wv.y + bv.y + dot * vv.y) * gv.y);
+  }
 }
 
 template <typename io_t>
@@ -265,18 +297,22 @@ extern "C" int frwkv_tmix_kk_a_gate_forward_varlen(const void* k, const void* k_
   clear_error();
   FRWKV_REQUIRE(k && k_k && a0 && a12 && k_a && new_k && neg_kk && kka, "tmix_kk_a_gate: null pointer argument");
   FRWKV_REQUIRE(total_rows > 0 && channels > 0, "tmix_kk_a_gate: sizes must be positive");
-  if (head_size != 64) return fail(FRWKV_ERR_UNSUPPORTED, "tmix_kk_a_gate: head size %d is not built (only 64)", head_size);
-  FRWKV_REQUIRE(channels % 64 == 0, "tmix_kk_a_gate: channels must be a multiple of head_size");
-  const int H = channels / 64;
+  if (head_size != 64 && head_size != 128 && head_size != 256)
+    return fail(FRWKV_ERR_UNSUPPORTED, "tmix_kk_a_gate: head size must be 64, 128, or 256, got %d", head_size);
+  FRWKV_REQUIRE(channels % head_size == 0, "tmix_kk_a_gate: channels must be a multiple of head_size");
+  const int H = channels / head_size;
   const long long units = total_rows * H;
   const long long blocks = (units + 7) / 8;
   FRWKV_REQUIRE(blocks <= 0x7fffffffLL, "tmix_kk_a_gate: too many rows");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_DISPATCH_IO(io_dtype, "tmix_kk_a_gate", {
-    launch_chained(kk_a_gate_kernel<io_t>, dim3((unsigned)blocks), dim3(256), 0, s, 
-        static_cast<const io_t*>(k), static_cast<const io_t*>(k_k), static_cast<const io_t*>(a0),
-        static_cast<const io_t*>(a12), static_cast<const io_t*>(k_a), static_cast<io_t*>(new_k),
-        static_cast<io_t*>(neg_kk), static_cast<io_t*>(kka), units, H);
+    const dim3 grid((unsigned)blocks), block(256);
+    const io_t *kp = static_cast<const io_t*>(k), *kkp = static_cast<const io_t*>(k_k), *a0p = static_cast<const io_t*>(a0),
+               *a12p = static_cast<const io_t*>(a12), *kap = static_cast<const io_t*>(k_a);
+    io_t *o1 = static_cast<io_t*>(new_k), *o2 = static_cast<io_t*>(neg_kk), *o3 = static_cast<io_t*>(kka);
+    if (head_size == 64) launch_chained(kk_a_gate_kernel<io_t, 1>, grid, block, 0, s, kp, kkp, a0p, a12p, kap, o1, o2, o3, units, H);
+    else if (head_size == 128) launch_chained(kk_a_gate_kernel<io_t, 2>, grid, block, 0, s, kp, kkp, a0p, a12p, kap, o1, o2, o3, units, H);
+    else launch_chained(kk_a_gate_kernel<io_t, 4>, grid, block, 0, s, kp, kkp, a0p, a12p, kap, o1, o2, o3, units, H);
     return check_launch("kk_a_gate_kernel");
   })
 }
@@ -289,18 +325,24 @@ extern "C" int frwkv_tmix_lnx_rkvres_xg_forward_varlen(const void* x, const void
   clear_error();
   FRWKV_REQUIRE(x && r && k && v && r_k && weight && bias && g && out, "tmix_lnx_rkvres_xg: null pointer argument");
   FRWKV_REQUIRE(total_rows > 0 && channels > 0, "tmix_lnx_rkvres_xg: sizes must be positive");
-  if (head_size != 64) return fail(FRWKV_ERR_UNSUPPORTED, "tmix_lnx_rkvres_xg: head size %d is not built (only 64)", head_size);
-  FRWKV_REQUIRE(channels % 64 == 0, "tmix_lnx_rkvres_xg: channels must be a multiple of head_size");
-  const int H = channels / 64;
+  if (head_size != 64 && head_size != 128 && head_size != 256)
+    return fail(FRWKV_ERR_UNSUPPORTED, "tmix_lnx_rkvres_xg: head size must be 64, 128, or 256, got %d", head_size);
+  FRWKV_REQUIRE(channels % head_size == 0, "tmix_lnx_rkvres_xg: channels must be a multiple of head_size");
+  const int H = channels / head_size;
   const long long units = total_rows * H;
   const long long blocks = (units + 7) / 8;
   FRWKV_REQUIRE(blocks <= 0x7fffffffLL, "tmix_lnx_rkvres_xg: too many rows");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_DISPATCH_IO(io_dtype, "tmix_lnx_rkvres_xg", {
-    launch_chained(lnx_rkvres_xg_kernel<io_t>, dim3((unsigned)blocks), dim3(256), 0, s, 
-        static_cast<const io_t*>(x), static_cast<const io_t*>(r), static_cast<const io_t*>(k),
-        static_cast<const io_t*>(v), static_cast<const io_t*>(r_k), static_cast<const io_t*>(weight),
-        static_cast<const io_t*>(bias), static_cast<const io_t*>(g), static_cast<io_t*>(out), units, H, eps);
+    const dim3 grid((unsigned)blocks), block(256);
+    const io_t *xp = static_cast<const io_t*>(x), *rp = static_cast<const io_t*>(r), *kp = static_cast<const io_t*>(k),
+               *vp = static_cast<const io_t*>(v), *rkp = static_cast<const io_t*>(r_k),
+               *wp = static_cast<const io_t*>(weight), *bp = static_cast<const io_t*>(bias),
+               *gp = static_cast<const io_t*>(g);
+    io_t* op = static_cast<io_t*>(out);
+    if (head_size == 64) launch_chained(lnx_rkvres_xg_kernel<io_t, 1>, grid, block, 0, s, xp, rp, kp, vp, rkp, wp, bp, gp, op, units, H, eps);
+    else if (head_size == 128) launch_chained(lnx_rkvres_xg_kernel<io_t, 2>, grid, block, 0, s, xp, rp, kp, vp, rkp, wp, bp, gp, op, units, H, eps);
+    else launch_chained(lnx_rkvres_xg_kernel<io_t, 4>, grid, block, 0, s, xp, rp, kp, vp, rkp, wp, bp, gp, op, units, H, eps);
     return check_launch("lnx_rkvres_xg_kernel");
   })
 }

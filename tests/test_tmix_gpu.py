@@ -64,19 +64,20 @@ def test_mix6_vs_oracle(oracle, dtype, lengths):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_per_head_ops_vs_oracle(oracle, dtype):
+@pytest.mark.parametrize("head_size", [64, 128, 256])
+def test_per_head_ops_vs_oracle(oracle, dtype, head_size):
     import flashrwkv_b200 as F
 
     N, C = 37, 2048
     gen = torch.Generator().manual_seed(4)
     rn = lambda *s: torch.randn(*s, generator=gen).to(dtype)  # noqa: E731
     k, a12, k_k, a0, k_a = rn(N, C), rn(N, C), rn(C), rn(C), rn(C)
-    got = F.infer_tmix_kk_a_gate_forward_varlen(*_c(k, k_k, a0, a12, k_a))
-    for o, w in zip(got, oracle.kk_a_gate(k, k_k, a0, a12, k_a)):
+    got = F.infer_tmix_kk_a_gate_forward_varlen(*_c(k, k_k, a0, a12, k_a), head_size=head_size)
+    for o, w in zip(got, oracle.kk_a_gate(k, k_k, a0, a12, k_a, head_size=head_size)):
         assert rel_rmse(o.float().cpu(), w) <= TOL[dtype]
     x, r, kk, v, g, r_k, wt, bs = rn(N, C), rn(N, C), rn(N, C), rn(N, C), rn(N, C), rn(C), rn(C), rn(C)
-    got = F.infer_tmix_lnx_rkvres_xg_forward_varlen(*_c(x, r, kk, v, r_k, wt, bs, g))
-    assert rel_rmse(got.float().cpu(), oracle.lnx_rkvres_xg(x, r, kk, v, r_k, wt, bs, g)) <= TOL[dtype]
+    got = F.infer_tmix_lnx_rkvres_xg_forward_varlen(*_c(x, r, kk, v, r_k, wt, bs, g), head_size=head_size)
+    assert rel_rmse(got.float().cpu(), oracle.lnx_rkvres_xg(x, r, kk, v, r_k, wt, bs, g, head_size=head_size)) <= TOL[dtype]
     v, vf, v12, v0 = rn(N, C), rn(N, C), rn(N, C), rn(C)
     got = F.infer_tmix_vres_gate_forward_varlen(*_c(v, vf, v0, v12))
     assert rel_rmse(got.float().cpu(), oracle.vres_gate(v, vf, v0, v12)) <= TOL[dtype]
