@@ -17,18 +17,21 @@ from .tmix.wkv7 import (
     statetune_recurrent_fp32io16,
 )
 
+from .tmix.a_gate import pretrain_tmix_a_gate_bf16
 from .tmix.kk_a_gate import infer_tmix_kk_a_gate_forward_varlen
+from .tmix.kk_pre import pretrain_tmix_kk_pre_bf16
 from .tmix.linear import *  # noqa: F401,F403
 from .tmix.linear import __all__ as _linear_all
-from .tmix.lnx_rkvres_xg import infer_tmix_lnx_rkvres_xg_forward_varlen
+from .tmix.lnx_rkvres_xg import infer_tmix_lnx_rkvres_xg_forward_varlen, pretrain_tmix_lnx_rkvres_xg_bf16
 from .tmix.mix6 import (
     infer_tmix_mix6_add_layer_norm_forward_varlen,
     infer_tmix_mix6_forward_varlen,
     infer_tmix_shift_project_forward_varlen,
+    pretrain_tmix_mix6_bf16,
 )
 from .tmix.normalization import *  # noqa: F401,F403
 from .tmix.normalization import __all__ as _norm_all
-from .tmix.vres_gate import infer_tmix_vres_gate_forward_varlen
+from .tmix.vres_gate import infer_tmix_vres_gate_forward_varlen, pretrain_tmix_vres_gate_bf16
 
 __all__ = [
     "infer_tmix_kk_a_gate_forward_varlen",
@@ -46,6 +49,11 @@ __all__ = [
     "infer_recurrent_fp32io16_forward_varlen",
     "prepare_recurrent_metadata",
     "pretrain_recurrent_bf16",
+    "pretrain_tmix_a_gate_bf16",
+    "pretrain_tmix_kk_pre_bf16",
+    "pretrain_tmix_lnx_rkvres_xg_bf16",
+    "pretrain_tmix_mix6_bf16",
+    "pretrain_tmix_vres_gate_bf16",
     "statetune_recurrent_fp32io16",
     "rl_infctx_chunk_fp32io16",
     "rl_infctx_chunk_fp32io16_factor_recompute",

@@ -35,6 +35,7 @@ CUDA_SOURCES = [
     "wkv7_chunk_fwd.cu",
     "tmix_elementwise.cu",
     "tmix_norm.cu",
+    "tmix_train.cu",
     "tmix_linear.cu",
     "tmix_gemm_tma.cu",
     "wkv7_backward.cu",

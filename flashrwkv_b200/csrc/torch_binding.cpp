@@ -869,6 +869,247 @@ std::vector<torch::Tensor> wkv7_backward(torch::Tensor sco, torch::Tensor cs, to
   return g;
 }
 
+
+// ---- training-side TMix glue on dense [B,T,C] tensors (names and argument order of the reference's
+// pretrain_tmix_* extension functions, flashrwkv2/tmix/{a_gate,vres_gate,mix6,kk_pre,lnx_rkvres_xg}) ----------
+void check_dense(const torch::Tensor& t, const char* name, const torch::Tensor& ref) {
+  check_io16(t, name, ref);
+  TORCH_CHECK(t.dim() == 3 && t.sizes() == ref.sizes(), name, " must have shape [B,T,C]");
+}
+void check_dense_vector(const torch::Tensor& t, const char* name, const torch::Tensor& ref) {
+  check_io16(t, name, ref);
+  TORCH_CHECK(t.numel() == ref.size(2), name, " must have C elements");
+}
+void check_dense_root(const torch::Tensor& x, const char* name) {
+  check_io16(x, name, x);
+  TORCH_CHECK(x.dim() == 3 && x.numel() > 0, name, " must have non-empty shape [B,T,C]");
+  TORCH_CHECK(x.size(2) % 8 == 0, name, ": C must be a multiple of 8");
+}
+torch::Tensor reduce_workspace(const torch::Tensor& ref, int vectors) {
+  const int64_t rows = ref.size(0) * ref.size(1);
+  return torch::empty({frwkv_pretrain_workspace_floats(rows, static_cast<int>(ref.size(2)), vectors)},
+                      ref.options().dtype(torch::kFloat32));
+}
+
+torch::Tensor pretrain_tmix_a_gate_forward(torch::Tensor a0, torch::Tensor a12) {
+  check_dense_root(a12, "a12");
+  check_dense_vector(a0, "a0", a12);
+  const c10::cuda::CUDAGuard guard(a12.device());
+  auto out = torch::empty_like(a12);
+  check_rc(frwkv_pretrain_a_gate_forward(a0.data_ptr(), a12.data_ptr(), out.data_ptr(), a12.size(0) * a12.size(1),
+                                         static_cast<int>(a12.size(2)), io_dtype_of(a12), current_stream(a12)));
+  return out;
+}
+
+std::vector<torch::Tensor> pretrain_tmix_a_gate_backward(torch::Tensor grad_output, torch::Tensor a0,
+                                                         torch::Tensor a12) {
+  check_dense_root(a12, "a12");
+  check_dense_vector(a0, "a0", a12);
+  check_dense(grad_output, "grad_output", a12);
+  const c10::cuda::CUDAGuard guard(a12.device());
+  auto grad_a0 = torch::empty_like(a0);
+  auto grad_a12 = torch::empty_like(a12);
+  auto ws = reduce_workspace(a12, 1);
+  check_rc(frwkv_pretrain_a_gate_backward(grad_output.data_ptr(), a0.data_ptr(), a12.data_ptr(), grad_a0.data_ptr(),
+                                          grad_a12.data_ptr(), ws.data_ptr<float>(), ws.numel(),
+                                          a12.size(0) * a12.size(1), static_cast<int>(a12.size(2)), io_dtype_of(a12),
+                                          current_stream(a12)));
+  return {grad_a0, grad_a12};
+}
+
+torch::Tensor pretrain_tmix_vres_gate_forward(torch::Tensor v, torch::Tensor v_first, torch::Tensor v0,
+                                              torch::Tensor v12) {
+  check_dense_root(v, "value");
+  check_dense(v_first, "first_value", v);
+  check_dense(v12, "v12", v);
+  check_dense_vector(v0, "v0", v);
+  const c10::cuda::CUDAGuard guard(v.device());
+  auto out = torch::empty_like(v);
+  check_rc(frwkv_tmix_vres_gate_forward_varlen(v.data_ptr(), v_first.data_ptr(), v0.data_ptr(), v12.data_ptr(),
+                                               out.data_ptr(), v.size(0) * v.size(1), static_cast<int>(v.size(2)),
+                                               io_dtype_of(v), current_stream(v)));
+  return out;
+}
+
+std::vector<torch::Tensor> pretrain_tmix_vres_gate_backward(torch::Tensor grad_output, torch::Tensor v,
+                                                            torch::Tensor v_first, torch::Tensor v0,
+                                                            torch::Tensor v12) {
+  check_dense_root(v, "value");
+  check_dense(v_first, "first_value", v);
+  check_dense(v12, "v12", v);
+  check_dense(grad_output, "grad_output", v);
+  check_dense_vector(v0, "v0", v);
+  const c10::cuda::CUDAGuard guard(v.device());
+  auto grad_v = torch::empty_like(v), grad_vf = torch::empty_like(v), grad_v12 = torch::empty_like(v);
+  auto grad_v0 = torch::empty_like(v0);
+  auto ws = reduce_workspace(v, 1);
+  check_rc(frwkv_pretrain_vres_gate_backward(grad_output.data_ptr(), v.data_ptr(), v_first.data_ptr(), v0.data_ptr(),
+                                             v12.data_ptr(), grad_v.data_ptr(), grad_vf.data_ptr(), grad_v0.data_ptr(),
+                                             grad_v12.data_ptr(), ws.data_ptr<float>(), ws.numel(),
+                                             v.size(0) * v.size(1), static_cast<int>(v.size(2)), io_dtype_of(v),
+                                             current_stream(v)));
+  return {grad_v, grad_vf, grad_v0, grad_v12};
+}
+
+std::vector<torch::Tensor> pretrain_tmix_mix6_forward(torch::Tensor x, torch::Tensor x_r, torch::Tensor x_w,
+                                                      torch::Tensor x_k, torch::Tensor x_v, torch::Tensor x_a,
+                                                      torch::Tensor x_g) {
+  check_dense_root(x, "x");
+  const torch::Tensor mix[6] = {x_r, x_w, x_k, x_v, x_a, x_g};
+  const void* mix_ptr[6];
+  void* out_ptr[6];
+  std::vector<torch::Tensor> outs;
+  const c10::cuda::CUDAGuard guard(x.device());
+  for (int j = 0; j < 6; ++j) {
+    check_dense_vector(mix[j], "mix vector", x);
+    outs.push_back(torch::empty_like(x));
+    mix_ptr[j] = mix[j].data_ptr();
+    out_ptr[j] = outs.back().data_ptr();
+  }
+  check_rc(frwkv_pretrain_mix6_forward(x.data_ptr(), mix_ptr, out_ptr, x.size(0), static_cast<int>(x.size(1)),
+                                       static_cast<int>(x.size(2)), io_dtype_of(x), current_stream(x)));
+  return outs;
+}
+
+std::vector<torch::Tensor> pretrain_tmix_mix6_backward(torch::Tensor g_r, torch::Tensor g_w, torch::Tensor g_k,
+                                                       torch::Tensor g_v, torch::Tensor g_a, torch::Tensor g_g,
+                                                       torch::Tensor x, torch::Tensor x_r, torch::Tensor x_w,
+                                                       torch::Tensor x_k, torch::Tensor x_v, torch::Tensor x_a,
+                                                       torch::Tensor x_g) {
+  check_dense_root(x, "x");
+  const torch::Tensor grads[6] = {g_r, g_w, g_k, g_v, g_a, g_g};
+  const torch::Tensor mix[6] = {x_r, x_w, x_k, x_v, x_a, x_g};
+  const void* grad_ptr[6];
+  const void* mix_ptr[6];
+  void* gmix_ptr[6];
+  const c10::cuda::CUDAGuard guard(x.device());
+  std::vector<torch::Tensor> result{torch::empty_like(x)};
+  for (int j = 0; j < 6; ++j) {
+    check_dense(grads[j], "grad_output", x);
+    check_dense_vector(mix[j], "mix vector", x);
+    result.push_back(torch::empty_like(mix[j]));
+    grad_ptr[j] = grads[j].data_ptr();
+    mix_ptr[j] = mix[j].data_ptr();
+    gmix_ptr[j] = result.back().data_ptr();
+  }
+  auto ws = reduce_workspace(x, 6);
+  check_rc(frwkv_pretrain_mix6_backward(grad_ptr, x.data_ptr(), mix_ptr, result[0].data_ptr(), gmix_ptr,
+                                        ws.data_ptr<float>(), ws.numel(), x.size(0), static_cast<int>(x.size(1)),
+                                        static_cast<int>(x.size(2)), io_dtype_of(x), current_stream(x)));
+  return result;
+}
+
+void check_head_size(const torch::Tensor& x, int64_t head_size) {
+  TORCH_CHECK(head_size == 64 || head_size == 128 || head_size == 256, "head_size must be one of 64, 128, or 256");
+  TORCH_CHECK(x.size(2) % head_size == 0, "C must be divisible by head_size");
+}
+
+std::vector<torch::Tensor> pretrain_tmix_kk_pre_forward(torch::Tensor k, torch::Tensor k_k, torch::Tensor a,
+                                                        torch::Tensor k_a, int64_t head_size) {
+  check_dense_root(k, "key");
+  check_head_size(k, head_size);
+  check_dense(a, "learning_rate", k);
+  check_dense_vector(k_k, "key_scale", k);
+  check_dense_vector(k_a, "learning_rate_scale", k);
+  const c10::cuda::CUDAGuard guard(k.device());
+  auto new_k = torch::empty_like(k), neg_kk = torch::empty_like(k), kka = torch::empty_like(k);
+  auto inv_norm = torch::empty({k.size(0), k.size(1), k.size(2) / head_size}, k.options().dtype(torch::kFloat32));
+  check_rc(frwkv_pretrain_kk_pre_forward(k.data_ptr(), k_k.data_ptr(), a.data_ptr(), k_a.data_ptr(), new_k.data_ptr(),
+                                         neg_kk.data_ptr(), kka.data_ptr(), inv_norm.data_ptr<float>(),
+                                         k.size(0) * k.size(1), static_cast<int>(k.size(2)),
+                                         static_cast<int>(head_size), io_dtype_of(k), current_stream(k)));
+  return {new_k, neg_kk, kka, inv_norm};
+}
+
+std::vector<torch::Tensor> pretrain_tmix_kk_pre_backward(torch::Tensor g_new_k, torch::Tensor g_neg_kk,
+                                                         torch::Tensor g_kka, torch::Tensor k, torch::Tensor k_k,
+                                                         torch::Tensor a, torch::Tensor k_a, torch::Tensor inv_norm,
+                                                         int64_t head_size) {
+  check_dense_root(k, "key");
+  check_head_size(k, head_size);
+  check_dense(a, "learning_rate", k);
+  check_dense(g_new_k, "grad_new_key", k);
+  check_dense(g_neg_kk, "grad_negative_direction", k);
+  check_dense(g_kka, "grad_scaled_direction", k);
+  check_dense_vector(k_k, "key_scale", k);
+  check_dense_vector(k_a, "learning_rate_scale", k);
+  check_cuda_contiguous(inv_norm, "inverse_norm");
+  TORCH_CHECK(inv_norm.scalar_type() == torch::kFloat32 &&
+                  inv_norm.numel() == k.size(0) * k.size(1) * (k.size(2) / head_size),
+              "inverse_norm must be float32 [B,T,C/head_size]");
+  const c10::cuda::CUDAGuard guard(k.device());
+  auto grad_k = torch::empty_like(k), grad_a = torch::empty_like(a);
+  auto grad_k_k = torch::empty_like(k_k), grad_k_a = torch::empty_like(k_a);
+  auto ws = reduce_workspace(k, 2);
+  check_rc(frwkv_pretrain_kk_pre_backward(
+      g_new_k.data_ptr(), g_neg_kk.data_ptr(), g_kka.data_ptr(), k.data_ptr(), k_k.data_ptr(), a.data_ptr(),
+      k_a.data_ptr(), inv_norm.data_ptr<float>(), grad_k.data_ptr(), grad_k_k.data_ptr(), grad_a.data_ptr(),
+      grad_k_a.data_ptr(), ws.data_ptr<float>(), ws.numel(), k.size(0) * k.size(1), static_cast<int>(k.size(2)),
+      static_cast<int>(head_size), io_dtype_of(k), current_stream(k)));
+  return {grad_k, grad_k_k, grad_a, grad_k_a};
+}
+
+std::vector<torch::Tensor> pretrain_tmix_lnx_rkvres_xg_forward(torch::Tensor x, torch::Tensor r, torch::Tensor k,
+                                                               torch::Tensor v, torch::Tensor r_k,
+                                                               torch::Tensor weight, torch::Tensor bias,
+                                                               torch::Tensor g, int64_t head_size) {
+  check_dense_root(x, "x");
+  check_head_size(x, head_size);
+  check_dense(r, "r", x);
+  check_dense(k, "k", x);
+  check_dense(v, "v", x);
+  check_dense(g, "g", x);
+  check_dense_vector(r_k, "residual_scale", x);
+  check_dense_vector(weight, "weight", x);
+  check_dense_vector(bias, "bias", x);
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto out = torch::empty_like(x);
+  auto stat_opts = x.options().dtype(torch::kFloat32);
+  auto mean = torch::empty({x.size(0), x.size(1), x.size(2) / head_size}, stat_opts);
+  auto rstd = torch::empty_like(mean);
+  check_rc(frwkv_pretrain_lnx_rkvres_xg_forward(
+      x.data_ptr(), r.data_ptr(), k.data_ptr(), v.data_ptr(), r_k.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+      g.data_ptr(), out.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), x.size(0) * x.size(1),
+      static_cast<int>(x.size(2)), static_cast<int>(head_size), io_dtype_of(x), current_stream(x)));
+  return {out, mean, rstd};
+}
+
+std::vector<torch::Tensor> pretrain_tmix_lnx_rkvres_xg_backward(torch::Tensor grad_output, torch::Tensor x,
+                                                                torch::Tensor r, torch::Tensor k, torch::Tensor v,
+                                                                torch::Tensor r_k, torch::Tensor weight,
+                                                                torch::Tensor bias, torch::Tensor g,
+                                                                torch::Tensor mean, torch::Tensor rstd,
+                                                                int64_t head_size) {
+  check_dense_root(x, "x");
+  check_head_size(x, head_size);
+  check_dense(grad_output, "grad_output", x);
+  check_dense(r, "r", x);
+  check_dense(k, "k", x);
+  check_dense(v, "v", x);
+  check_dense(g, "g", x);
+  check_dense_vector(r_k, "residual_scale", x);
+  check_dense_vector(weight, "weight", x);
+  check_dense_vector(bias, "bias", x);
+  check_cuda_contiguous(mean, "mean");
+  check_cuda_contiguous(rstd, "rstd");
+  const int64_t stats = x.size(0) * x.size(1) * (x.size(2) / head_size);
+  TORCH_CHECK(mean.scalar_type() == torch::kFloat32 && rstd.scalar_type() == torch::kFloat32 &&
+                  mean.numel() == stats && rstd.numel() == stats,
+              "mean and rstd must be float32 [B,T,C/head_size]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto gx = torch::empty_like(x), gr = torch::empty_like(x), gk = torch::empty_like(x), gv = torch::empty_like(x),
+       gg = torch::empty_like(x);
+  auto grk = torch::empty_like(r_k), gw = torch::empty_like(weight), gb = torch::empty_like(bias);
+  auto ws = reduce_workspace(x, 3);
+  check_rc(frwkv_pretrain_lnx_rkvres_xg_backward(
+      grad_output.data_ptr(), x.data_ptr(), r.data_ptr(), k.data_ptr(), v.data_ptr(), r_k.data_ptr(),
+      weight.data_ptr(), bias.data_ptr(), g.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), gx.data_ptr(),
+      gr.data_ptr(), gk.data_ptr(), gv.data_ptr(), grk.data_ptr(), gw.data_ptr(), gb.data_ptr(), gg.data_ptr(),
+      ws.data_ptr<float>(), ws.numel(), x.size(0) * x.size(1), static_cast<int>(x.size(2)),
+      static_cast<int>(head_size), io_dtype_of(x), current_stream(x)));
+  return {gx, gr, gk, gv, grk, gw, gb, gg};
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -944,6 +1185,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("state_dot_a"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),
         py::arg("b"), py::arg("grad_output") = py::none(), py::arg("grad_final_state") = py::none(),
         py::arg("scale") = 1.0);
+  m.def("pretrain_tmix_a_gate_forward", &pretrain_tmix_a_gate_forward, py::arg("a0"), py::arg("a12"));
+  m.def("pretrain_tmix_a_gate_backward", &pretrain_tmix_a_gate_backward, py::arg("grad_output"), py::arg("a0"),
+        py::arg("a12"));
+  m.def("pretrain_tmix_vres_gate_forward", &pretrain_tmix_vres_gate_forward, py::arg("value"),
+        py::arg("first_value"), py::arg("v0"), py::arg("v12"));
+  m.def("pretrain_tmix_vres_gate_backward", &pretrain_tmix_vres_gate_backward, py::arg("grad_output"),
+        py::arg("value"), py::arg("first_value"), py::arg("v0"), py::arg("v12"));
+  m.def("pretrain_tmix_mix6_forward", &pretrain_tmix_mix6_forward);
+  m.def("pretrain_tmix_mix6_backward", &pretrain_tmix_mix6_backward);
+  m.def("pretrain_tmix_kk_pre_forward", &pretrain_tmix_kk_pre_forward);
+  m.def("pretrain_tmix_kk_pre_backward", &pretrain_tmix_kk_pre_backward);
+  m.def("pretrain_tmix_lnx_rkvres_xg_forward", &pretrain_tmix_lnx_rkvres_xg_forward);
+  m.def("pretrain_tmix_lnx_rkvres_xg_backward", &pretrain_tmix_lnx_rkvres_xg_backward);
   m.def("tmix_act_forward", &tmix_act_forward, py::arg("x"), py::arg("act"));
   m.def("tmix_linear_grouped", &tmix_linear_grouped, py::arg("xs"), py::arg("weights"), py::arg("acts"),
         py::arg("vres") = py::none());

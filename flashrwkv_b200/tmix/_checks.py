@@ -18,3 +18,17 @@ def check_io(name: str, tensor, ref=None) -> None:
             raise TypeError(f"{name} must have the same dtype as the first tensor")
         if tensor.device != ref.device:
             raise ValueError(f"{name} must share the first tensor's device")
+
+
+def check_train_bf16(tensors: dict) -> None:
+    """The training-side operators take contiguous CUDA bfloat16 tensors on one device (ValueError otherwise)."""
+    first = None
+    for name, tensor in tensors.items():
+        if not isinstance(tensor, torch.Tensor):
+            raise TypeError(f"{name} must be a torch.Tensor")
+        if tensor.dtype != torch.bfloat16 or not tensor.is_cuda or not tensor.is_contiguous():
+            raise ValueError(f"{name} must be contiguous CUDA bfloat16")
+        if first is None:
+            first = tensor
+        elif tensor.device != first.device:
+            raise ValueError(f"{name} must share {next(iter(tensors))}'s device")

@@ -6,6 +6,7 @@ from __future__ import annotations
 
 from ..._ext import extension
 from .._checks import check_io
+from .pretrain import pretrain_tmix_lnx_rkvres_xg_bf16
 
 
 def infer_tmix_lnx_rkvres_xg_forward_varlen(x, r, k, v, r_k, weight, bias, g, *, head_size: int = 64,
@@ -27,4 +28,4 @@ def infer_tmix_lnx_rkvres_xg_forward_varlen(x, r, k, v, r_k, weight, bias, g, *,
                                                          int(batch_size), 1 if max_seqlen is None else int(max_seqlen))
 
 
-__all__ = ["infer_tmix_lnx_rkvres_xg_forward_varlen"]
+__all__ = ["infer_tmix_lnx_rkvres_xg_forward_varlen", "pretrain_tmix_lnx_rkvres_xg_bf16"]

@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from ..._ext import extension
-from .._checks import check_io
+from .._checks import check_io, check_train_bf16
 from ..wkv7 import _check_metadata_inputs
 
 
@@ -129,5 +129,41 @@ def infer_tmix_shift_project_forward_varlen(x, mixes, weights, *, shift_state_po
     return tuple(outs)
 
 
+class _PretrainMix6(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, x_r, x_w, x_k, x_v, x_a, x_g):
+        output = extension().pretrain_tmix_mix6_forward(x, x_r, x_w, x_k, x_v, x_a, x_g)
+        ctx.save_for_backward(x, x_r, x_w, x_k, x_v, x_a, x_g)
+        return tuple(output)
+
+    @staticmethod
+    def backward(ctx, *grad_outputs):
+        if all(g is None for g in grad_outputs):
+            return (None,) * 7
+        x = ctx.saved_tensors[0]
+        zeros = None
+        grads = []
+        for g in grad_outputs:  # an output that took no part in the loss contributes a zero gradient
+            if g is None:
+                zeros = torch.zeros_like(x) if zeros is None else zeros
+                g = zeros
+            grads.append(g.contiguous())
+        return tuple(extension().pretrain_tmix_mix6_backward(*grads, *ctx.saved_tensors))
+
+
+def pretrain_tmix_mix6_bf16(x, x_r, x_w, x_k, x_v, x_a, x_g):
+    """Training-side six-way token shift on a dense `[B,T,C]` bf16 tensor (the row before t = 0 is zero), with its
+    backward.  Mirror of `flashrwkv2/tmix/mix6/__init__.py:222-297`; the gradients of the six mix vectors are
+    fixed-order fp32 sums over the rows."""
+    check_train_bf16({"x": x})
+    if x.ndim != 3 or x.numel() == 0:
+        raise ValueError("x must have shape [B,T,C]")
+    for name, tensor in zip(("x_r", "x_w", "x_k", "x_v", "x_a", "x_g"), (x_r, x_w, x_k, x_v, x_a, x_g)):
+        if (not isinstance(tensor, torch.Tensor) or tensor.dtype != torch.bfloat16 or not tensor.is_cuda
+                or not tensor.is_contiguous() or tensor.shape != (x.shape[-1],) or tensor.device != x.device):
+            raise ValueError(f"{name} must be contiguous CUDA bfloat16 [C]")
+    return _PretrainMix6.apply(x, x_r, x_w, x_k, x_v, x_a, x_g)
+
+
 __all__ = ["infer_tmix_mix6_forward_varlen", "infer_tmix_mix6_add_layer_norm_forward_varlen",
-           "infer_tmix_shift_project_forward_varlen"]
+           "infer_tmix_shift_project_forward_varlen", "pretrain_tmix_mix6_bf16"]

@@ -307,6 +307,66 @@ int frwkv_tmix_linear_grouped(const frwkv_linear_problem* problems, int count, i
                               int32_t* error_flag, frwkv_stream_t stream);
 
 /*
+ * ---- Training-side TMix glue on dense [B, T, C] tensors (rows = B * T), forward and backward ----------------------
+ * io16 tensors are bf16 in the reference (io_dtype FRWKV_DTYPE_BF16); fp16 is accepted too.  channels must be a
+ * multiple of 8.  A backward that also returns the gradient of a [C] parameter sums it over the rows in two steps
+ * (per-slab fp32 partials in `workspace`, then a fixed-order sum), so the result is the same on every run;
+ * `workspace` holds at least frwkv_pretrain_workspace_floats(rows, channels, vectors) floats, `vectors` = the
+ * number of parameter gradients of that call (a_gate 1, vres_gate 1, mix6 6, kk_pre 2, lnx_rkvres_xg 3).
+ */
+long long frwkv_pretrain_workspace_floats(long long rows, int channels, int vectors);
+
+/* out = sigmoid(a0 + a12); a0 [C], a12 [rows][C].  Replaces tmix_a_gate forward / backward
+ * (csrc/sm90/tmix/a_gate/pretrain_bf16_forward.cu, pretrain_bf16_backward.cu). */
+int frwkv_pretrain_a_gate_forward(const void* a0, const void* a12, void* out, long long rows, int channels,
+                                  int io_dtype, frwkv_stream_t stream);
+int frwkv_pretrain_a_gate_backward(const void* grad_out, const void* a0, const void* a12, void* grad_a0,
+                                   void* grad_a12, float* workspace, long long workspace_floats, long long rows,
+                                   int channels, int io_dtype, frwkv_stream_t stream);
+
+/* Backward of v + (v_first - v) * sigmoid(v0 + v12); the forward is frwkv_tmix_vres_gate_forward_varlen with
+ * total_rows = rows.  Replaces csrc/sm90/tmix/vres_gate/pretrain_bf16_backward.cu. */
+int frwkv_pretrain_vres_gate_backward(const void* grad_out, const void* v, const void* v_first, const void* v0,
+                                      const void* v12, void* grad_v, void* grad_v_first, void* grad_v0,
+                                      void* grad_v12, float* workspace, long long workspace_floats, long long rows,
+                                      int channels, int io_dtype, frwkv_stream_t stream);
+
+/* out[j] = x + (x[t-1] - x) * mix[j], j = r, w, k, v, a, g; x [batch][seq_len][C], x[-1] = 0; mix, out, grad_out and
+ * grad_mix are arrays of six pointers.  Replaces csrc/sm90/tmix/mix6/pretrain_bf16_{forward,backward}.cu. */
+int frwkv_pretrain_mix6_forward(const void* x, const void* const* mix, void* const* out, long long batch, int seq_len,
+                                int channels, int io_dtype, frwkv_stream_t stream);
+int frwkv_pretrain_mix6_backward(const void* const* grad_out, const void* x, const void* const* mix, void* grad_x,
+                                 void* const* grad_mix, float* workspace, long long workspace_floats, long long batch,
+                                 int seq_len, int channels, int io_dtype, frwkv_stream_t stream);
+
+/* kk = normalize(k * k_k) per head (eps 1e-12); new_k = k * (1 + (a - 1) * k_a), neg_kk = -kk, kka = kk * a;
+ * inv_norm fp32 [rows][C / head_size] is saved for the backward.  head_size 64, 128 or 256.
+ * Replaces csrc/sm90/tmix/kk_pre/pretrain_bf16_{forward,backward}.cu. */
+int frwkv_pretrain_kk_pre_forward(const void* k, const void* k_k, const void* a, const void* k_a, void* new_k,
+                                  void* neg_kk, void* kka, float* inv_norm, long long rows, int channels,
+                                  int head_size, int io_dtype, frwkv_stream_t stream);
+int frwkv_pretrain_kk_pre_backward(const void* grad_new_k, const void* grad_neg_kk, const void* grad_kka,
+                                   const void* k, const void* k_k, const void* a, const void* k_a,
+                                   const float* inv_norm, void* grad_k, void* grad_k_k, void* grad_a, void* grad_k_a,
+                                   float* workspace, long long workspace_floats, long long rows, int channels,
+                                   int head_size, int io_dtype, frwkv_stream_t stream);
+
+/* out = (LayerNorm per head of x (biased variance, eps 64e-5) * weight + bias + (sum_head r k r_k) * v) * g; mean and
+ * rstd fp32 [rows][C / head_size] are saved for the backward.
+ * Replaces csrc/sm90/tmix/lnx_rkvres_xg/pretrain_bf16_{forward,backward}.cu. */
+int frwkv_pretrain_lnx_rkvres_xg_forward(const void* x, const void* r, const void* k, const void* v, const void* r_k,
+                                         const void* weight, const void* bias, const void* g, void* out, float* mean,
+                                         float* rstd, long long rows, int channels, int head_size, int io_dtype,
+                                         frwkv_stream_t stream);
+int frwkv_pretrain_lnx_rkvres_xg_backward(const void* grad_out, const void* x, const void* r, const void* k,
+                                          const void* v, const void* r_k, const void* weight, const void* bias,
+                                          const void* g, const float* mean, const float* rstd, void* grad_x,
+                                          void* grad_r, void* grad_k, void* grad_v, void* grad_r_k, void* grad_weight,
+                                          void* grad_bias, void* grad_g, float* workspace, long long workspace_floats,
+                                          long long rows, int channels, int head_size, int io_dtype,
+                                          frwkv_stream_t stream);
+
+/*
  * Diagnostic: D[128][n] = A[128][64] * B[n][64]^T through one tcgen05.mma (kind::tf32) chain of 8 K-steps,
  * with A and B staged in shared memory as chunk-major tiles of the given chunk stride (bytes).  No
  * counterpart in the reference; used by the tests to pin the descriptor encodings the chunk kernels rely on.

@@ -1,0 +1,100 @@
+"""CPU pin of the training-side TMix oracle: its analytic backward functions against torch autograd (float64) of the
+torch formulas the reference's own tests use (tests/tmix/mix6/test.py:72-77, tests/tmix/lnx_rkvres_xg/test.py:42-60,
+and the one-line definitions of a_gate, vres_gate and kk_pre)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import tmix_train_oracle as O
+
+
+def _rn(gen, *shape, scale=1.0):
+    return (torch.randn(*shape, generator=gen, dtype=torch.float64) * scale).requires_grad_()
+
+
+def _close(got, want, tol=1e-10):
+    want = want.detach().numpy()
+    assert np.abs(np.asarray(got) - want).max() <= tol * max(1.0, np.abs(want).max())
+
+
+def test_a_gate_and_vres_gate_backward_match_autograd():
+    gen = torch.Generator().manual_seed(1)
+    a0, a12, go = _rn(gen, 16), _rn(gen, 2, 5, 16), _rn(gen, 2, 5, 16)
+    y = torch.sigmoid(a0 + a12)
+    _close(O.a_gate(a0, a12), y)
+    want = torch.autograd.grad(y, [a0, a12], go)
+    for g, w in zip(O.a_gate_backward(go, a0, a12), want):
+        _close(g, w)
+    v, vf, v0, v12 = _rn(gen, 2, 5, 16), _rn(gen, 2, 5, 16), _rn(gen, 16), _rn(gen, 2, 5, 16)
+    y = v + (vf - v) * torch.sigmoid(v0 + v12)
+    _close(O.vres_gate(v, vf, v0, v12), y)
+    want = torch.autograd.grad(y, [v, vf, v0, v12], go)
+    for g, w in zip(O.vres_gate_backward(go, v, vf, v0, v12), want):
+        _close(g, w)
+
+
+def test_mix6_backward_matches_autograd():
+    gen = torch.Generator().manual_seed(2)
+    x = _rn(gen, 3, 7, 8)
+    mixes = [_rn(gen, 8) for _ in range(6)]
+    gos = [_rn(gen, 3, 7, 8) for _ in range(6)]
+    prev = torch.cat((torch.zeros_like(x[:, :1]), x[:, :-1]), dim=1)
+    outs = [x + (prev - x) * m for m in mixes]
+    for got, want in zip(O.mix6(x, mixes), outs):
+        _close(got, want)
+    want = torch.autograd.grad(outs, [x, *mixes], gos)
+    gx, gm = O.mix6_backward(gos, x, mixes)
+    _close(gx, want[0])
+    for g, w in zip(gm, want[1:]):
+        _close(g, w)
+
+
+@pytest.mark.parametrize("head_size", [64, 128])
+def test_kk_pre_backward_matches_autograd(head_size):
+    gen = torch.Generator().manual_seed(3)
+    B, T, C = 2, 3, 2 * head_size
+    k, k_k, a, k_a = _rn(gen, B, T, C), _rn(gen, C), _rn(gen, B, T, C), _rn(gen, C)
+    gos = [_rn(gen, B, T, C) for _ in range(3)]
+    kk = torch.nn.functional.normalize((k * k_k).view(B, T, -1, head_size), dim=-1, p=2.0, eps=1e-12).view(B, T, C)
+    outs = [k * (1 + (a - 1) * k_a), -kk, kk * a]
+    got = O.kk_pre(k, k_k, a, k_a, head_size)
+    for g, w in zip(got[:3], outs):
+        _close(g, w)
+    want = torch.autograd.grad(outs, [k, k_k, a, k_a], gos)
+    for g, w in zip(O.kk_pre_backward(*gos, k, k_k, a, k_a, head_size), want):
+        _close(g, w)
+
+
+def test_kk_pre_zero_key_has_no_projection_term():
+    """A zero key row sits below the eps clamp: kk = u / eps and the gradient is the plain scaled one."""
+    C = 64
+    k = torch.zeros(1, 1, C, dtype=torch.float64)
+    k_k = torch.ones(C, dtype=torch.float64)
+    a = torch.full((1, 1, C), 0.5, dtype=torch.float64)
+    g = torch.ones(1, 1, C, dtype=torch.float64)
+    gk, gks, ga, gka = O.kk_pre_backward(0 * g, g, 0 * g, k, k_k, a, k_k, 64)
+    assert np.allclose(gk, -1.0 / O.NORMALIZE_EPS) and np.all(gks == 0) and np.all(ga == 0) and np.all(gka == 0)
+
+
+@pytest.mark.parametrize("head_size", [64, 256])
+def test_lnx_backward_matches_autograd(head_size):
+    gen = torch.Generator().manual_seed(4)
+    B, T, H = 2, 3, 2
+    C = H * head_size
+    x, r, k, v, g = (_rn(gen, B, T, C) for _ in range(5))
+    r_k, weight, bias = _rn(gen, H, head_size), _rn(gen, C), _rn(gen, C)
+    go = _rn(gen, B, T, C)
+    xf = x.view(B, T, H, head_size)
+    mean = xf.mean(-1, keepdim=True)
+    rstd = (xf.var(-1, unbiased=False, keepdim=True) + 64.0e-5).rsqrt()
+    residual = (r.view(B, T, H, head_size) * k.view(B, T, H, head_size) * r_k.view(1, 1, H, head_size)).sum(
+        -1, keepdim=True)
+    y = (((xf - mean) * rstd * weight.view(1, 1, H, head_size) + bias.view(1, 1, H, head_size)
+          + residual * v.view(B, T, H, head_size)) * g.view(B, T, H, head_size)).reshape(B, T, C)
+    out, mean_o, rstd_o = O.lnx_rkvres_xg(x, r, k, v, r_k, weight, bias, g, head_size)
+    _close(out, y)
+    _close(mean_o, mean[..., 0])
+    _close(rstd_o, rstd[..., 0])
+    want = torch.autograd.grad(y, [x, r, k, v, r_k, weight, bias, g], go)
+    for got, w in zip(O.lnx_rkvres_xg_backward(go, x, r, k, v, r_k, weight, bias, g, head_size), want):
+        _close(got, w, tol=1e-9)
