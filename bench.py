@@ -376,6 +376,39 @@ def _extras(dev):
             entry["tensor_frac_of_bf16_peak_cuda_graph"] = 2 * M * (4 * C * C + 2 * C * sum(ranks.values())) / gsec / bf16
         tmix[f"M={M}"] = entry
     out["tmix_layer_C2048"] = tmix
+    del layers
+    torch.cuda.empty_cache()
+    # ---- training-side TMix glue on the training configuration's activations: B=8, T=4096, C=4096 (268 MB per tensor,
+    # larger than L2).  Algorithmic bytes per element = 2 x the tensors read or written.
+    from flashrwkv_b200 import _ext
+
+    ext = _ext.extension()
+    Bt, Tt, Ct = 8, 4096, 4096
+    gen = torch.Generator(device=dev).manual_seed(9)
+    acts = [torch.randn(Bt, Tt, Ct, device=dev, generator=gen).to(torch.bfloat16) for _ in range(7)]
+    x, r, k, v, gg, go, aa = acts
+    vecs = [torch.rand(Ct, device=dev, generator=gen).to(torch.bfloat16) for _ in range(6)]
+    inv = ext.pretrain_tmix_kk_pre_forward(x, vecs[0], r, vecs[1], 64)[3]
+    stats = ext.pretrain_tmix_lnx_rkvres_xg_forward(x, r, k, v, vecs[0], vecs[1], vecs[2], gg, 64)[1:]
+    cases = {
+        "a_gate_forward": (4, lambda: ext.pretrain_tmix_a_gate_forward(vecs[0], x)),
+        "a_gate_backward": (6, lambda: ext.pretrain_tmix_a_gate_backward(go, vecs[0], x)),
+        "vres_gate_backward": (14, lambda: ext.pretrain_tmix_vres_gate_backward(go, x, r, vecs[0], k)),
+        "mix6_forward": (14, lambda: ext.pretrain_tmix_mix6_forward(x, *vecs)),
+        "mix6_backward": (16, lambda: ext.pretrain_tmix_mix6_backward(x, r, k, v, gg, go, aa, *vecs)),
+        "kk_pre_forward": (10, lambda: ext.pretrain_tmix_kk_pre_forward(x, vecs[0], r, vecs[1], 64)),
+        "kk_pre_backward": (14, lambda: ext.pretrain_tmix_kk_pre_backward(k, v, gg, x, vecs[0], r, vecs[1], inv, 64)),
+        "lnx_rkvres_xg_forward": (12, lambda: ext.pretrain_tmix_lnx_rkvres_xg_forward(x, r, k, v, vecs[0], vecs[1],
+                                                                                      vecs[2], gg, 64)),
+        "lnx_rkvres_xg_backward": (22, lambda: ext.pretrain_tmix_lnx_rkvres_xg_backward(
+            go, x, r, k, v, vecs[0], vecs[1], vecs[2], gg, stats[0], stats[1], 64)),
+    }
+    glue = {"workload": f"B={Bt} T={Tt} C={Ct} bf16, head size 64; every tensor larger than L2"}
+    for name, (bytes_per_elem, fn) in cases.items():
+        sec = _time_cuda(fn, warmup=2, iters=5)
+        alg = Bt * Tt * Ct * bytes_per_elem
+        glue[name] = {"us": sec * 1e6, "algorithmic_gbs": alg / sec / 1e9, "hbm_frac": alg / sec / hbm}
+    out["tmix_train_glue"] = glue
     return out
 
 
