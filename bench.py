@@ -207,6 +207,43 @@ def _time_cuda(fn, warmup=2, iters=5):
     return e0.elapsed_time(e1) / iters * 1e-3
 
 
+def _extras_glue(dev, hbm):
+    """Training-side TMix glue kernels, each timed alone; hbm = the peak in bytes/s the fractions are quoted against."""
+    import torch
+
+    # ---- training-side TMix glue on the training configuration's activations: B=8, T=4096, C=4096 (268 MB per tensor,
+    # larger than L2).  Algorithmic bytes per element = 2 x the tensors read or written.
+    from flashrwkv_b200 import _ext
+
+    ext = _ext.extension()
+    Bt, Tt, Ct = 8, 4096, 4096
+    gen = torch.Generator(device=dev).manual_seed(9)
+    acts = [torch.randn(Bt, Tt, Ct, device=dev, generator=gen).to(torch.bfloat16) for _ in range(7)]
+    x, r, k, v, gg, go, aa = acts
+    vecs = [torch.rand(Ct, device=dev, generator=gen).to(torch.bfloat16) for _ in range(6)]
+    inv = ext.pretrain_tmix_kk_pre_forward(x, vecs[0], r, vecs[1], 64)[3]
+    stats = ext.pretrain_tmix_lnx_rkvres_xg_forward(x, r, k, v, vecs[0], vecs[1], vecs[2], gg, 64)[1:]
+    cases = {
+        "a_gate_forward": (4, lambda: ext.pretrain_tmix_a_gate_forward(vecs[0], x)),
+        "a_gate_backward": (6, lambda: ext.pretrain_tmix_a_gate_backward(go, vecs[0], x)),
+        "vres_gate_backward": (14, lambda: ext.pretrain_tmix_vres_gate_backward(go, x, r, vecs[0], k)),
+        "mix6_forward": (14, lambda: ext.pretrain_tmix_mix6_forward(x, *vecs)),
+        "mix6_backward": (16, lambda: ext.pretrain_tmix_mix6_backward(x, r, k, v, gg, go, aa, *vecs)),
+        "kk_pre_forward": (10, lambda: ext.pretrain_tmix_kk_pre_forward(x, vecs[0], r, vecs[1], 64)),
+        "kk_pre_backward": (14, lambda: ext.pretrain_tmix_kk_pre_backward(k, v, gg, x, vecs[0], r, vecs[1], inv, 64)),
+        "lnx_rkvres_xg_forward": (12, lambda: ext.pretrain_tmix_lnx_rkvres_xg_forward(x, r, k, v, vecs[0], vecs[1],
+                                                                                      vecs[2], gg, 64)),
+        "lnx_rkvres_xg_backward": (22, lambda: ext.pretrain_tmix_lnx_rkvres_xg_backward(
+            go, x, r, k, v, vecs[0], vecs[1], vecs[2], gg, stats[0], stats[1], 64)),
+    }
+    glue = {"workload": f"B={Bt} T={Tt} C={Ct} bf16, head size 64; every tensor larger than L2"}
+    for name, (bytes_per_elem, fn) in cases.items():
+        sec = _time_cuda(fn, warmup=2, iters=5)
+        alg = Bt * Tt * Ct * bytes_per_elem
+        glue[name] = {"us": sec * 1e6, "algorithmic_gbs": alg / sec / 1e9, "hbm_frac": alg / sec / hbm}
+    return glue
+
+
 def _extras(dev):
     """Secondary workloads of the same path, timed briefly on this GPU: chunked prefill (B8 T4096 H32), training
     forward+backward (B8 T4096 H64) and the TMix layer chain (C=2048, M in {1,4,7,512}).  Roofline fractions use
@@ -378,37 +415,7 @@ def _extras(dev):
     out["tmix_layer_C2048"] = tmix
     del layers
     torch.cuda.empty_cache()
-    # ---- training-side TMix glue on the training configuration's activations: B=8, T=4096, C=4096 (268 MB per tensor,
-    # larger than L2).  Algorithmic bytes per element = 2 x the tensors read or written.
-    from flashrwkv_b200 import _ext
-
-    ext = _ext.extension()
-    Bt, Tt, Ct = 8, 4096, 4096
-    gen = torch.Generator(device=dev).manual_seed(9)
-    acts = [torch.randn(Bt, Tt, Ct, device=dev, generator=gen).to(torch.bfloat16) for _ in range(7)]
-    x, r, k, v, gg, go, aa = acts
-    vecs = [torch.rand(Ct, device=dev, generator=gen).to(torch.bfloat16) for _ in range(6)]
-    inv = ext.pretrain_tmix_kk_pre_forward(x, vecs[0], r, vecs[1], 64)[3]
-    stats = ext.pretrain_tmix_lnx_rkvres_xg_forward(x, r, k, v, vecs[0], vecs[1], vecs[2], gg, 64)[1:]
-    cases = {
-        "a_gate_forward": (4, lambda: ext.pretrain_tmix_a_gate_forward(vecs[0], x)),
-        "a_gate_backward": (6, lambda: ext.pretrain_tmix_a_gate_backward(go, vecs[0], x)),
-        "vres_gate_backward": (14, lambda: ext.pretrain_tmix_vres_gate_backward(go, x, r, vecs[0], k)),
-        "mix6_forward": (14, lambda: ext.pretrain_tmix_mix6_forward(x, *vecs)),
-        "mix6_backward": (16, lambda: ext.pretrain_tmix_mix6_backward(x, r, k, v, gg, go, aa, *vecs)),
-        "kk_pre_forward": (10, lambda: ext.pretrain_tmix_kk_pre_forward(x, vecs[0], r, vecs[1], 64)),
-        "kk_pre_backward": (14, lambda: ext.pretrain_tmix_kk_pre_backward(k, v, gg, x, vecs[0], r, vecs[1], inv, 64)),
-        "lnx_rkvres_xg_forward": (12, lambda: ext.pretrain_tmix_lnx_rkvres_xg_forward(x, r, k, v, vecs[0], vecs[1],
-                                                                                      vecs[2], gg, 64)),
-        "lnx_rkvres_xg_backward": (22, lambda: ext.pretrain_tmix_lnx_rkvres_xg_backward(
-            go, x, r, k, v, vecs[0], vecs[1], vecs[2], gg, stats[0], stats[1], 64)),
-    }
-    glue = {"workload": f"B={Bt} T={Tt} C={Ct} bf16, head size 64; every tensor larger than L2"}
-    for name, (bytes_per_elem, fn) in cases.items():
-        sec = _time_cuda(fn, warmup=2, iters=5)
-        alg = Bt * Tt * Ct * bytes_per_elem
-        glue[name] = {"us": sec * 1e6, "algorithmic_gbs": alg / sec / 1e9, "hbm_frac": alg / sec / hbm}
-    out["tmix_train_glue"] = glue
+    out["tmix_train_glue"] = _extras_glue(dev, hbm)
     return out
 
 

@@ -8,14 +8,17 @@
 //
 // Every pass is bound by HBM traffic, so the kernels are organised around 16-byte accesses: a thread owns eight
 // adjacent channels, a head of D channels is D / 8 adjacent lanes of one warp (per-head sums are xor-shuffles inside
-// that lane group), a CTA of 128 threads covers 1024 channels.  The passes that also produce a gradient of a [C]
-// parameter (a sum over all B * T rows) cut the rows into contiguous slabs, one CTA per (channel tile, slab): a
-// thread walks its slab row by row with the column sums in registers and writes one fp32 partial per slab, and
-// reduce_partials_kernel adds the slabs in a fixed order.  The parameter gradients are therefore bit-reproducible;
-// the reference accumulates them with fp32 atomics.  Walking contiguous rows also hands mix6 its previous row in
-// registers, so x is read once.
+// that lane group), a warp covers 256 channels (512 contiguous bytes per row and tensor).  The rows are cut into
+// contiguous slabs, one CTA of four warps per (channel tile of 256, slab); each warp walks its own quarter of the slab
+// row by row.  The passes that also produce a gradient of a [C] parameter (a sum over all B * T rows) keep the column
+// sums in registers along the walk, add the four warps in shared memory in a fixed order and write one fp32 partial
+// per CTA; reduce_partials_kernel adds the slabs in a fixed order.  The parameter gradients are therefore
+// bit-reproducible; the reference accumulates them with fp32 atomics.  Walking contiguous rows also hands mix6 its
+// previous row in registers, so x is read once.
 //
 // Replaces csrc/sm90/tmix/{a_gate,vres_gate,mix6,kk_pre,lnx_rkvres_xg}/pretrain_bf16_{forward,backward}.cu.
+
+#include <cstdlib>
 
 #include "frwkv_common.cuh"
 
@@ -23,11 +26,16 @@ namespace frwkv {
 namespace {
 
 constexpr int kThreads = 128;
-constexpr int kTileCols = kThreads * 8;
+constexpr int kWarps = kThreads / 32;
+constexpr int kTileCols = 32 * 8;  // channels of one CTA: every warp covers all of them, for its own rows
 constexpr float kNormalizeEps = 1.0e-12f;
 constexpr float kLnxEps = 64e-5f;
 
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+// ex2.approx and rcp.approx (relative error about 2^-22 each): four instructions instead of the two dozen of an exact
+// division, which would make the sigmoid passes instruction-bound; the result is rounded to 16 bits anyway.
+__device__ __forceinline__ float sigmoidf_(float x) {
+  return rcp_approx(1.f + ex2_approx(fminf(-1.4426950408889634f * x, 126.0f)));
+}
 
 template <typename io_t>
 __device__ __forceinline__ void load8(const io_t* p, float (&f)[8]) {
@@ -64,24 +72,49 @@ __device__ __forceinline__ float head_sum(float v) {
   return v;
 }
 
-// The slab of rows and the eight channels of this thread in a (channel tile, slab) grid.
+// The rows of this warp and the eight channels of this lane in a (channel tile, slab) grid.  row_begin >= row_end for
+// a warp past the last row.
 struct Walk {
   long long row_begin, row_end;
   int col;
   bool active;
 };
-__device__ __forceinline__ Walk my_walk(long long rows, int channels, int rows_per_slab) {
+__device__ __forceinline__ Walk my_walk(long long rows, int channels, int rows_per_warp) {
   Walk w;
-  w.col = (blockIdx.x * kThreads + threadIdx.x) * 8;
+  w.col = (blockIdx.x * 32 + (threadIdx.x & 31)) * 8;
   w.active = w.col < channels;
-  w.row_begin = (long long)blockIdx.y * rows_per_slab;
-  w.row_end = w.row_begin + rows_per_slab < rows ? w.row_begin + rows_per_slab : rows;
+  w.row_begin = ((long long)blockIdx.y * kWarps + (threadIdx.x >> 5)) * rows_per_warp;
+  w.row_end = w.row_begin + rows_per_warp < rows ? w.row_begin + rows_per_warp : rows;
   return w;
 }
-__device__ __forceinline__ void store_partial(float* workspace, int vec, int channels, int col, const float (&f)[8]) {
-  float* p = workspace + ((long long)vec * gridDim.y + blockIdx.y) * channels + col;
-  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
-  *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+
+// Adds the column sums of the CTA's four warps (warp 0 + 1 + 2 + 3, in that order) and writes the CTA's partial:
+// workspace[v][slab][channel].  Every thread of the CTA calls it.
+template <int V>
+__device__ __forceinline__ void store_partials(float* workspace, int channels, const Walk& w, float (&acc)[V][8]) {
+  __shared__ float4 buf[kWarps - 1][2 * V][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp > 0) {
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      buf[warp - 1][2 * v][lane] = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+      buf[warp - 1][2 * v + 1][lane] = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+    }
+  }
+  __syncthreads();
+  if (warp != 0 || !w.active) return;
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+#pragma unroll
+    for (int j = 0; j < kWarps - 1; ++j) {
+      const float4 lo = buf[j][2 * v][lane], hi = buf[j][2 * v + 1][lane];
+      acc[v][0] += lo.x; acc[v][1] += lo.y; acc[v][2] += lo.z; acc[v][3] += lo.w;
+      acc[v][4] += hi.x; acc[v][5] += hi.y; acc[v][6] += hi.z; acc[v][7] += hi.w;
+    }
+    float* p = workspace + ((long long)v * gridDim.y + blockIdx.y) * channels + w.col;
+    *reinterpret_cast<float4*>(p) = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+  }
 }
 
 struct ReduceTargets {
@@ -114,16 +147,26 @@ __global__ __launch_bounds__(256) void reduce_partials_kernel(const float* __res
 
 // ---- a_gate --------------------------------------------------------------------------------------------------------
 template <typename io_t>
-__global__ __launch_bounds__(256) void a_gate_forward_kernel(const io_t* __restrict__ a0, const io_t* __restrict__ a12,
-                                                             io_t* __restrict__ out, long long vec_total,
-                                                             int vec_per_row) {
-  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < vec_total; i += (long long)gridDim.x * 256) {
-    float z[8], t[8];
-    load8(a0 + (i % vec_per_row) * 8, z);
-    load8(a12 + i * 8, t);
+__global__ __launch_bounds__(kThreads) void a_gate_forward_kernel(const io_t* __restrict__ a0,
+                                                                  const io_t* __restrict__ a12, io_t* __restrict__ out,
+                                                                  long long rows, int channels, int rows_per_warp) {
+  const Walk w = my_walk(rows, channels, rows_per_warp);
+  if (!w.active) return;
+  float z0[8];
+  load8(a0 + w.col, z0);
+  for (long long row = w.row_begin; row < w.row_end; row += 2) {  // two rows' loads in flight together
+    const long long at = row * channels + w.col;
+    const bool second = row + 1 < w.row_end;
+    float t[2][8];
+    load8(a12 + at, t[0]);
+    if (second) load8(a12 + at + channels, t[1]);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) t[e] = sigmoidf_(z[e] + t[e]);
-    store8(out + i * 8, t);
+    for (int u = 0; u < 2; ++u) {
+      if (u == 1 && !second) break;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) t[u][e] = sigmoidf_(z0[e] + t[u][e]);
+      store8(out + at + u * (long long)channels, t[u]);
+    }
   }
 }
 
@@ -133,27 +176,37 @@ __global__ __launch_bounds__(kThreads) void a_gate_backward_kernel(const io_t* _
                                                                    const io_t* __restrict__ a12,
                                                                    io_t* __restrict__ grad_a12,
                                                                    float* __restrict__ workspace, long long rows,
-                                                                   int channels, int rows_per_slab) {
-  const Walk w = my_walk(rows, channels, rows_per_slab);
-  if (!w.active) return;
-  float z0[8], acc[8];
-  load8(a0 + w.col, z0);
-  zero8(acc);
-#pragma unroll 2
-  for (long long row = w.row_begin; row < w.row_end; ++row) {
-    const long long at = row * channels + w.col;
-    float z[8], g[8];
-    load8(a12 + at, z);
-    load8(grad_out + at, g);
+                                                                   int channels, int rows_per_warp) {
+  const Walk w = my_walk(rows, channels, rows_per_warp);
+  float acc[1][8];
+  zero8(acc[0]);
+  if (w.active) {
+    float z0[8];
+    load8(a0 + w.col, z0);
+    for (long long row = w.row_begin; row < w.row_end; row += 2) {  // two rows' loads in flight together
+      const long long at = row * channels + w.col;
+      const bool second = row + 1 < w.row_end;
+      float z[2][8], g[2][8];
+      load8(a12 + at, z[0]);
+      load8(grad_out + at, g[0]);
+      if (second) {
+        load8(a12 + at + channels, z[1]);
+        load8(grad_out + at + channels, g[1]);
+      }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float y = sigmoidf_(z0[e] + z[e]);
-      g[e] *= y * (1.f - y);
-      acc[e] += g[e];
+      for (int u = 0; u < 2; ++u) {
+        if (u == 1 && !second) break;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float y = sigmoidf_(z0[e] + z[u][e]);
+          g[u][e] *= y * (1.f - y);
+          acc[0][e] += g[u][e];
+        }
+        store8(grad_a12 + at + u * (long long)channels, g[u]);
+      }
     }
-    store8(grad_a12 + at, g);
   }
-  store_partial(workspace, 0, channels, w.col, acc);
+  store_partials<1>(workspace, channels, w, acc);
 }
 
 // ---- vres_gate -----------------------------------------------------------------------------------------------------
@@ -162,33 +215,46 @@ __global__ __launch_bounds__(kThreads) void vres_gate_backward_kernel(
     const io_t* __restrict__ grad_out, const io_t* __restrict__ v, const io_t* __restrict__ v_first,
     const io_t* __restrict__ v0, const io_t* __restrict__ v12, io_t* __restrict__ grad_v,
     io_t* __restrict__ grad_v_first, io_t* __restrict__ grad_v12, float* __restrict__ workspace, long long rows,
-    int channels, int rows_per_slab) {
-  const Walk w = my_walk(rows, channels, rows_per_slab);
-  if (!w.active) return;
-  float z0[8], acc[8];
-  load8(v0 + w.col, z0);
-  zero8(acc);
-#pragma unroll 2
-  for (long long row = w.row_begin; row < w.row_end; ++row) {
-    const long long at = row * channels + w.col;
-    float g[8], a[8], f[8], z[8], gz[8];
-    load8(grad_out + at, g);
-    load8(v + at, a);
-    load8(v_first + at, f);
-    load8(v12 + at, z);
+    int channels, int rows_per_warp) {
+  const Walk w = my_walk(rows, channels, rows_per_warp);
+  float acc[1][8];
+  zero8(acc[0]);
+  if (w.active) {
+    float z0[8];
+    load8(v0 + w.col, z0);
+    for (long long row = w.row_begin; row < w.row_end; row += 2) {  // two rows' loads in flight together
+      const long long at = row * channels + w.col;
+      const bool second = row + 1 < w.row_end;
+      float g[2][8], a[2][8], f[2][8], z[2][8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float s = sigmoidf_(z0[e] + z[e]);
-      gz[e] = g[e] * (f[e] - a[e]) * s * (1.f - s);
-      acc[e] += gz[e];
-      f[e] = g[e] * s;         // grad of v_first
-      a[e] = g[e] - f[e];      // grad of v
+      for (int u = 0; u < 2; ++u) {
+        if (u == 1 && !second) break;
+        const long long au = at + u * (long long)channels;
+        load8(grad_out + au, g[u]);
+        load8(v + au, a[u]);
+        load8(v_first + au, f[u]);
+        load8(v12 + au, z[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (u == 1 && !second) break;
+        const long long au = at + u * (long long)channels;
+        float gz[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float sg = sigmoidf_(z0[e] + z[u][e]);
+          gz[e] = g[u][e] * (f[u][e] - a[u][e]) * sg * (1.f - sg);
+          acc[0][e] += gz[e];
+          f[u][e] = g[u][e] * sg;          // grad of v_first
+          a[u][e] = g[u][e] - f[u][e];     // grad of v
+        }
+        store8(grad_v + au, a[u]);
+        store8(grad_v_first + au, f[u]);
+        store8(grad_v12 + au, gz);
+      }
     }
-    store8(grad_v + at, a);
-    store8(grad_v_first + at, f);
-    store8(grad_v12 + at, gz);
   }
-  store_partial(workspace, 0, channels, w.col, acc);
+  store_partials<1>(workspace, channels, w, acc);
 }
 
 // ---- mix6 ----------------------------------------------------------------------------------------------------------
@@ -197,32 +263,69 @@ struct Six {
   void* out[6];
 };
 
-// Rows are b * T + t; a slab may cross sequence boundaries, the row before t = 0 is zero.
+// The six mix vectors of the CTA's 256 channels as fp32 in shared memory (all four warps walk the same channels; a
+// lane reads its own eight values, no bank conflict).  Every thread of the CTA calls it.
+using MixTable = float4[6][2][32];
+template <typename io_t>
+__device__ __forceinline__ void stage_mix(MixTable& table, const void* const* vectors, const Walk& w) {
+  if (threadIdx.x < 32 && w.active) {
+#pragma unroll
+    for (int j = 0; j < 6; ++j) {
+      float f[8];
+      load8(static_cast<const io_t*>(vectors[j]) + w.col, f);
+      table[j][0][threadIdx.x] = make_float4(f[0], f[1], f[2], f[3]);
+      table[j][1][threadIdx.x] = make_float4(f[4], f[5], f[6], f[7]);
+    }
+  }
+  __syncthreads();
+}
+// volatile: the compiler would otherwise keep all 48 loop-invariant values in registers, which is what the table is
+// there to avoid
+__device__ __forceinline__ float4 lds_volatile(const float4* p) {
+  float4 v;
+  asm volatile("ld.volatile.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"((unsigned)__cvta_generic_to_shared(p)));
+  return v;
+}
+__device__ __forceinline__ void read_mix(const MixTable& table, int j, float (&m)[8]) {
+  const float4 lo = lds_volatile(&table[j][0][threadIdx.x & 31]), hi = lds_volatile(&table[j][1][threadIdx.x & 31]);
+  m[0] = lo.x; m[1] = lo.y; m[2] = lo.z; m[3] = lo.w;
+  m[4] = hi.x; m[5] = hi.y; m[6] = hi.z; m[7] = hi.w;
+}
+
+// Rows are b * T + t; a slab may cross sequence boundaries, the row before t = 0 is zero.  The next row's x is
+// requested before the current row's six stores, so that a warp always has a read in flight.
 template <typename io_t>
 __global__ __launch_bounds__(kThreads) void mix6_forward_kernel(const io_t* __restrict__ x, Six mix, long long rows,
-                                                                int seq_len, int channels, int rows_per_slab) {
-  const Walk w = my_walk(rows, channels, rows_per_slab);
+                                                                int seq_len, int channels, int rows_per_warp) {
+  __shared__ MixTable m_s;
+  const Walk w = my_walk(rows, channels, rows_per_warp);
+  stage_mix<io_t>(m_s, mix.in, w);
   if (!w.active || w.row_begin >= w.row_end) return;
-  float m[6][8], prev[8];
-#pragma unroll
-  for (int j = 0; j < 6; ++j) load8(static_cast<const io_t*>(mix.in[j]) + w.col, m[j]);
+  float prev[8], cur[8], next[8];
   int t = (int)(w.row_begin % seq_len);
   if (t != 0) load8(x + (w.row_begin - 1) * channels + w.col, prev);
+  load8(x + w.row_begin * channels + w.col, cur);
   for (long long row = w.row_begin; row < w.row_end; ++row) {
     const long long at = row * channels + w.col;
-    float cur[8], xx[8];
-    load8(x + at, cur);
+    if (row + 1 < w.row_end) load8(x + at + channels, next);
+    float xx[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) xx[e] = (t != 0 ? prev[e] : 0.f) - cur[e];
 #pragma unroll
     for (int j = 0; j < 6; ++j) {
-      float y[8];
+      float y[8], m[8];
+      read_mix(m_s, j, m);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = fmaf(xx[e], m[j][e], cur[e]);
+      for (int e = 0; e < 8; ++e) y[e] = fmaf(xx[e], m[e], cur[e]);
       store8(static_cast<io_t*>(mix.out[j]) + at, y);
     }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) prev[e] = cur[e];
+    for (int e = 0; e < 8; ++e) {
+      prev[e] = cur[e];
+      cur[e] = next[e];
+    }
     if (++t == seq_len) t = 0;
   }
 }
@@ -230,18 +333,10 @@ __global__ __launch_bounds__(kThreads) void mix6_forward_kernel(const io_t* __re
 // grad_x[t] = sum_j g_j[t] (1 - m_j) + sum_j g_j[t+1] m_j (second term only inside the sequence);
 // grad_m_j = sum_rows g_j (x[t-1] - x[t]).  mix.in = the six upstream gradients, mix.out = the six mix vectors.
 template <typename io_t>
-__global__ __launch_bounds__(kThreads) void mix6_backward_kernel(const io_t* __restrict__ x, Six mix,
-                                                                 io_t* __restrict__ grad_x,
-                                                                 float* __restrict__ workspace, long long rows,
-                                                                 int seq_len, int channels, int rows_per_slab) {
-  const Walk w = my_walk(rows, channels, rows_per_slab);
-  if (!w.active || w.row_begin >= w.row_end) return;
-  float m[6][8], dm[6][8], prev[8], carry[8];
-#pragma unroll
-  for (int j = 0; j < 6; ++j) {
-    load8(static_cast<const io_t*>(mix.out[j]) + w.col, m[j]);
-    zero8(dm[j]);
-  }
+__device__ __forceinline__ void mix6_backward_walk(const io_t* __restrict__ x, const Six& mix,
+                                                   io_t* __restrict__ grad_x, float (&dm)[6][8], const Walk& w,
+                                                   const MixTable& m_s, long long rows, int seq_len, int channels) {
+  float prev[8], carry[8];
   int t = (int)(w.row_begin % seq_len);
   if (t != 0) load8(x + (w.row_begin - 1) * channels + w.col, prev);
   zero8(carry);
@@ -255,12 +350,13 @@ __global__ __launch_bounds__(kThreads) void mix6_backward_kernel(const io_t* __r
     for (int e = 0; e < 8; ++e) xx[e] = (t != 0 ? prev[e] : 0.f) - cur[e];
 #pragma unroll
     for (int j = 0; j < 6; ++j) {
-      float g[8];
+      float g[8], m[8];
       load8(static_cast<const io_t*>(mix.in[j]) + at, g);
+      read_mix(m_s, j, m);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         dm[j][e] = fmaf(g[e], xx[e], dm[j][e]);
-        shifted[e] = fmaf(g[e], m[j][e], shifted[e]);
+        shifted[e] = fmaf(g[e], m[e], shifted[e]);
         direct[e] += g[e];
       }
     }
@@ -280,31 +376,42 @@ __global__ __launch_bounds__(kThreads) void mix6_backward_kernel(const io_t* __r
     const long long at = w.row_end * channels + w.col;
 #pragma unroll
     for (int j = 0; j < 6; ++j) {
-      float g[8];
+      float g[8], m[8];
       load8(static_cast<const io_t*>(mix.in[j]) + at, g);
+      read_mix(m_s, j, m);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) carry[e] = fmaf(g[e], m[j][e], carry[e]);
+      for (int e = 0; e < 8; ++e) carry[e] = fmaf(g[e], m[e], carry[e]);
     }
   }
   store8(grad_x + (w.row_end - 1) * channels + w.col, carry);
+}
+
+template <typename io_t, int kMinCtas>
+__global__ __launch_bounds__(kThreads, kMinCtas) void mix6_backward_kernel(const io_t* __restrict__ x, Six mix,
+                                                                 io_t* __restrict__ grad_x,
+                                                                 float* __restrict__ workspace, long long rows,
+                                                                 int seq_len, int channels, int rows_per_warp) {
+  __shared__ MixTable m_s;
+  const Walk w = my_walk(rows, channels, rows_per_warp);
+  stage_mix<io_t>(m_s, mix.out, w);
+  float dm[6][8];
 #pragma unroll
-  for (int j = 0; j < 6; ++j) store_partial(workspace, j, channels, w.col, dm[j]);
+  for (int j = 0; j < 6; ++j) zero8(dm[j]);
+  if (w.active && w.row_begin < w.row_end)
+    mix6_backward_walk<io_t>(x, mix, grad_x, dm, w, m_s, rows, seq_len, channels);
+  store_partials<6>(workspace, channels, w, dm);
 }
 
 // ---- kk_pre --------------------------------------------------------------------------------------------------------
 // A head is kLanes = D / 8 adjacent lanes.  Lanes past the last channel keep running the row loop with their loads and
-// stores switched off so that the full-mask shuffles stay converged; a warp with no channel at all leaves at once.
-__device__ __forceinline__ bool warp_has_channels(int channels) {
-  return (blockIdx.x * kThreads + (threadIdx.x & ~31)) * 8 < channels;
-}
+// stores switched off so that the full-mask shuffles stay converged.
 
 template <typename io_t, int kLanes>
 __global__ __launch_bounds__(kThreads) void kk_pre_forward_kernel(
     const io_t* __restrict__ k, const io_t* __restrict__ k_k, const io_t* __restrict__ a, const io_t* __restrict__ k_a,
     io_t* __restrict__ new_k, io_t* __restrict__ neg_kk, io_t* __restrict__ kka, float* __restrict__ inv_norm,
-    long long rows, int channels, int rows_per_slab) {
-  const Walk w = my_walk(rows, channels, rows_per_slab);
-  if (!warp_has_channels(channels)) return;
+    long long rows, int channels, int rows_per_warp) {
+  const Walk w = my_walk(rows, channels, rows_per_warp);
   const int heads = channels / (kLanes * 8), head = w.col / (kLanes * 8);
   float ks[8], ka[8];
   zero8(ks);
@@ -351,15 +458,14 @@ __global__ __launch_bounds__(kThreads) void kk_pre_backward_kernel(
     const io_t* __restrict__ g_new_k, const io_t* __restrict__ g_neg_kk, const io_t* __restrict__ g_kka,
     const io_t* __restrict__ k, const io_t* __restrict__ k_k, const io_t* __restrict__ a, const io_t* __restrict__ k_a,
     const float* __restrict__ inv_norm, io_t* __restrict__ grad_k, io_t* __restrict__ grad_a,
-    float* __restrict__ workspace, long long rows, int channels, int rows_per_slab) {
-  const Walk w = my_walk(rows, channels, rows_per_slab);
-  if (!warp_has_channels(channels)) return;
+    float* __restrict__ workspace, long long rows, int channels, int rows_per_warp) {
+  const Walk w = my_walk(rows, channels, rows_per_warp);
   const int heads = channels / (kLanes * 8), head = w.col / (kLanes * 8);
-  float ks[8], ka[8], dks[8], dka[8];
+  float ks[8], ka[8], acc[2][8];  // acc: d k_k, d k_a
   zero8(ks);
   zero8(ka);
-  zero8(dks);
-  zero8(dka);
+  zero8(acc[0]);
+  zero8(acc[1]);
   if (w.active) {
     load8(k_k + w.col, ks);
     load8(k_a + w.col, ka);
@@ -397,16 +503,13 @@ __global__ __launch_bounds__(kThreads) void kk_pre_backward_kernel(
       const float gu = inv * fmaf(-kk[e], dot, gkk[e]);
       gk[e] = fmaf(gn[e], fmaf(av[e], ka[e], 1.f - ka[e]), gu * ks[e]);
       ga[e] = fmaf(gn[e] * kv[e], ka[e], gka[e] * kk[e]);
-      dks[e] = fmaf(gu, kv[e], dks[e]);
-      dka[e] = fmaf(gn[e] * kv[e], av[e] - 1.f, dka[e]);
+      acc[0][e] = fmaf(gu, kv[e], acc[0][e]);
+      acc[1][e] = fmaf(gn[e] * kv[e], av[e] - 1.f, acc[1][e]);
     }
     store8(grad_k + at, gk);
     store8(grad_a + at, ga);
   }
-  if (w.active) {
-    store_partial(workspace, 0, channels, w.col, dks);
-    store_partial(workspace, 1, channels, w.col, dka);
-  }
+  store_partials<2>(workspace, channels, w, acc);
 }
 
 // ---- lnx_rkvres_xg -------------------------------------------------------------------------------------------------
@@ -415,10 +518,9 @@ __global__ __launch_bounds__(kThreads) void lnx_forward_kernel(
     const io_t* __restrict__ x, const io_t* __restrict__ r, const io_t* __restrict__ k, const io_t* __restrict__ v,
     const io_t* __restrict__ r_k, const io_t* __restrict__ weight, const io_t* __restrict__ bias,
     const io_t* __restrict__ g, io_t* __restrict__ out, float* __restrict__ mean_out, float* __restrict__ rstd_out,
-    long long rows, int channels, int rows_per_slab) {
+    long long rows, int channels, int rows_per_warp) {
   constexpr float kInvD = 1.f / (kLanes * 8);
-  const Walk w = my_walk(rows, channels, rows_per_slab);
-  if (!warp_has_channels(channels)) return;
+  const Walk w = my_walk(rows, channels, rows_per_warp);
   const int heads = channels / (kLanes * 8), head = w.col / (kLanes * 8);
   float rk[8], wt[8], bs[8];
   zero8(rk);
@@ -474,18 +576,17 @@ __global__ __launch_bounds__(kThreads) void lnx_backward_kernel(
     const io_t* __restrict__ weight, const io_t* __restrict__ bias, const io_t* __restrict__ g,
     const float* __restrict__ mean_in, const float* __restrict__ rstd_in, io_t* __restrict__ grad_x,
     io_t* __restrict__ grad_r, io_t* __restrict__ grad_k, io_t* __restrict__ grad_v, io_t* __restrict__ grad_g,
-    float* __restrict__ workspace, long long rows, int channels, int rows_per_slab) {
+    float* __restrict__ workspace, long long rows, int channels, int rows_per_warp) {
   constexpr float kInvD = 1.f / (kLanes * 8);
-  const Walk w = my_walk(rows, channels, rows_per_slab);
-  if (!warp_has_channels(channels)) return;
+  const Walk w = my_walk(rows, channels, rows_per_warp);
   const int heads = channels / (kLanes * 8), head = w.col / (kLanes * 8);
-  float rk[8], wt[8], bs[8], drk[8], dwt[8], dbs[8];
+  float rk[8], wt[8], bs[8], acc[3][8];  // acc: d r_k, d weight, d bias
   zero8(rk);
   zero8(wt);
   zero8(bs);
-  zero8(drk);
-  zero8(dwt);
-  zero8(dbs);
+  zero8(acc[0]);
+  zero8(acc[1]);
+  zero8(acc[2]);
   if (w.active) {
     load8(r_k + w.col, rk);
     load8(weight + w.col, wt);
@@ -532,9 +633,9 @@ __global__ __launch_bounds__(kThreads) void lnx_backward_kernel(
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       o[e] = go[e] * (fmaf(xh[e], wt[e], bs[e]) + s * vv[e]);  // grad of g
-      dwt[e] = fmaf(gy[e], xh[e], dwt[e]);
-      dbs[e] += gy[e];
-      drk[e] = fmaf(gs * rv[e], kv[e], drk[e]);
+      acc[1][e] = fmaf(gy[e], xh[e], acc[1][e]);
+      acc[2][e] += gy[e];
+      acc[0][e] = fmaf(gs * rv[e], kv[e], acc[0][e]);
     }
     store8(grad_g + at, o);
 #pragma unroll
@@ -550,27 +651,51 @@ __global__ __launch_bounds__(kThreads) void lnx_backward_kernel(
     for (int e = 0; e < 8; ++e) o[e] = gy[e] * s;
     store8(grad_v + at, o);
   }
-  if (w.active) {
-    store_partial(workspace, 0, channels, w.col, drk);
-    store_partial(workspace, 1, channels, w.col, dwt);
-    store_partial(workspace, 2, channels, w.col, dbs);
-  }
+  store_partials<3>(workspace, channels, w, acc);
 }
 
 // ---- host side -----------------------------------------------------------------------------------------------------
 struct Plan {
-  int col_tiles, slabs, rows_per_slab;
+  int col_tiles, slabs, rows_per_warp;
 };
-// About eight CTAs of 128 threads per SM; every slab holds at least one row.
-Plan make_plan(long long rows, int channels) {
+// One wave: as many CTAs as are resident at once (ctas_per_sm of this kernel on every SM), so that no second, partly
+// filled wave follows; a slab is four warps' rows and holds at least one row.
+Plan make_plan(long long rows, int channels, int ctas_per_sm, int sms) {
   Plan p;
   p.col_tiles = (channels + kTileCols - 1) / kTileCols;
-  long long slabs = (148 * 8 + p.col_tiles - 1) / p.col_tiles;
-  if (slabs > rows) slabs = rows;
+  long long slabs = (long long)sms * ctas_per_sm / p.col_tiles;
+  const long long most = (rows + kWarps - 1) / kWarps;
+  if (slabs > most) slabs = most;
   if (slabs < 1) slabs = 1;
-  p.rows_per_slab = (int)((rows + slabs - 1) / slabs);
-  p.slabs = (int)((rows + p.rows_per_slab - 1) / p.rows_per_slab);
+  p.rows_per_warp = (int)((rows + slabs * kWarps - 1) / (slabs * kWarps));
+  p.slabs = (int)((rows + (long long)p.rows_per_warp * kWarps - 1) / ((long long)p.rows_per_warp * kWarps));
   return p;
+}
+constexpr int kMaxCtasPerSm = 16;  // 2048 threads
+int sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        n <= 0)
+      n = 148;
+    sms = n;
+  }
+  return sms;
+}
+// the slab count never exceeds this one, whatever the kernel
+long long max_slabs(long long rows, int channels) { return make_plan(rows, channels, kMaxCtasPerSm, sm_count()).slabs; }
+
+// Launches a row-walking kernel (its last parameter is rows_per_warp) on one wave of CTAs and returns the plan used.
+template <typename... KArgs, typename... Args>
+Plan launch_walk(void (*kernel)(KArgs...), long long rows, int channels, cudaStream_t s, Args... args) {
+  int resident = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, kThreads, 0) != cudaSuccess || resident < 1)
+    resident = 4;
+  if (resident > kMaxCtasPerSm) resident = kMaxCtasPerSm;
+  const Plan plan = make_plan(rows, channels, resident, sm_count());
+  kernel<<<dim3(plan.col_tiles, plan.slabs), kThreads, 0, s>>>(args..., plan.rows_per_warp);
+  return plan;
 }
 
 template <typename io_t>
@@ -586,7 +711,7 @@ int check_dense(const char* name, long long rows, int channels, long long worksp
   if (rows <= 0 || channels <= 0) return fail(FRWKV_ERR_INVALID_ARGUMENT, "%s: sizes must be positive", name);
   if (channels % 8 != 0) return fail(FRWKV_ERR_INVALID_ARGUMENT, "%s: channel count must be a multiple of 8", name);
   if (rows > 0x7fffffffLL) return fail(FRWKV_ERR_INVALID_ARGUMENT, "%s: too many rows", name);
-  if (vectors > 0 && workspace_floats < (long long)vectors * make_plan(rows, channels).slabs * channels)
+  if (vectors > 0 && workspace_floats < (long long)vectors * max_slabs(rows, channels) * channels)
     return fail(FRWKV_ERR_INVALID_ARGUMENT, "%s: workspace is smaller than frwkv_pretrain_workspace_floats", name);
   return FRWKV_OK;
 }
@@ -629,7 +754,7 @@ int check_heads(const char* name, int channels, int head_size) {
 
 extern "C" long long frwkv_pretrain_workspace_floats(long long rows, int channels, int vectors) {
   if (rows <= 0 || channels <= 0 || vectors <= 0) return 0;
-  return (long long)vectors * frwkv::make_plan(rows, channels).slabs * channels;
+  return (long long)vectors * frwkv::max_slabs(rows, channels) * channels;
 }
 
 extern "C" int frwkv_pretrain_a_gate_forward(const void* a0, const void* a12, void* out, long long rows, int channels,
@@ -638,13 +763,10 @@ extern "C" int frwkv_pretrain_a_gate_forward(const void* a0, const void* a12, vo
   clear_error();
   FRWKV_REQUIRE(a0 && a12 && out, "pretrain_a_gate: null pointer argument");
   if (int rc = check_dense("pretrain_a_gate", rows, channels, 0, 0)) return rc;
-  const long long vec_total = rows * (channels / 8);
-  long long blocks = (vec_total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_TRAIN_IO(io_dtype, "pretrain_a_gate", {
-    a_gate_forward_kernel<io_t><<<(unsigned)blocks, 256, 0, s>>>(CP(io_t, a0), CP(io_t, a12), P(io_t, out), vec_total,
-                                                                 channels / 8);
+    launch_walk(a_gate_forward_kernel<io_t>, rows, channels, s, CP(io_t, a0), CP(io_t, a12), P(io_t, out), rows,
+                channels);
     return check_launch("a_gate_forward_kernel");
   })
 }
@@ -656,13 +778,12 @@ extern "C" int frwkv_pretrain_a_gate_backward(const void* grad_out, const void* 
   clear_error();
   FRWKV_REQUIRE(grad_out && a0 && a12 && grad_a0 && grad_a12 && workspace, "pretrain_a_gate: null pointer argument");
   if (int rc = check_dense("pretrain_a_gate", rows, channels, workspace_floats, 1)) return rc;
-  const Plan plan = make_plan(rows, channels);
+  Plan plan;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   ReduceTargets targets{{grad_a0}};
   FRWKV_TRAIN_IO(io_dtype, "pretrain_a_gate", {
-    a_gate_backward_kernel<io_t><<<dim3(plan.col_tiles, plan.slabs), kThreads, 0, s>>>(
-        CP(io_t, grad_out), CP(io_t, a0), CP(io_t, a12), P(io_t, grad_a12), workspace, rows, channels,
-        plan.rows_per_slab);
+    plan = launch_walk(a_gate_backward_kernel<io_t>, rows, channels, s, 
+        CP(io_t, grad_out), CP(io_t, a0), CP(io_t, a12), P(io_t, grad_a12), workspace, rows, channels);
     if (int rc = check_launch("a_gate_backward_kernel")) return rc;
     return reduce_partials<io_t>(workspace, targets, plan, channels, 1, s);
   })
@@ -678,13 +799,13 @@ extern "C" int frwkv_pretrain_vres_gate_backward(const void* grad_out, const voi
   FRWKV_REQUIRE(grad_out && v && v_first && v0 && v12 && grad_v && grad_v_first && grad_v0 && grad_v12 && workspace,
                 "pretrain_vres_gate: null pointer argument");
   if (int rc = check_dense("pretrain_vres_gate", rows, channels, workspace_floats, 1)) return rc;
-  const Plan plan = make_plan(rows, channels);
+  Plan plan;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   ReduceTargets targets{{grad_v0}};
   FRWKV_TRAIN_IO(io_dtype, "pretrain_vres_gate", {
-    vres_gate_backward_kernel<io_t><<<dim3(plan.col_tiles, plan.slabs), kThreads, 0, s>>>(
+    plan = launch_walk(vres_gate_backward_kernel<io_t>, rows, channels, s, 
         CP(io_t, grad_out), CP(io_t, v), CP(io_t, v_first), CP(io_t, v0), CP(io_t, v12), P(io_t, grad_v),
-        P(io_t, grad_v_first), P(io_t, grad_v12), workspace, rows, channels, plan.rows_per_slab);
+        P(io_t, grad_v_first), P(io_t, grad_v12), workspace, rows, channels);
     if (int rc = check_launch("vres_gate_backward_kernel")) return rc;
     return reduce_partials<io_t>(workspace, targets, plan, channels, 1, s);
   })
@@ -704,11 +825,10 @@ extern "C" int frwkv_pretrain_mix6_forward(const void* x, const void* const* mix
     six.in[j] = mix[j];
     six.out[j] = out[j];
   }
-  const Plan plan = make_plan(rows, channels);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_TRAIN_IO(io_dtype, "pretrain_mix6", {
-    mix6_forward_kernel<io_t><<<dim3(plan.col_tiles, plan.slabs), kThreads, 0, s>>>(CP(io_t, x), six, rows, seq_len,
-                                                                                   channels, plan.rows_per_slab);
+    launch_walk(mix6_forward_kernel<io_t>, rows, channels, s, CP(io_t, x), six, rows, seq_len,
+                                                                                   channels);
     return check_launch("mix6_forward_kernel");
   })
 }
@@ -731,11 +851,18 @@ extern "C" int frwkv_pretrain_mix6_backward(const void* const* grad_out, const v
     six.out[j] = const_cast<void*>(mix[j]);
     targets.out[j] = grad_mix[j];
   }
-  const Plan plan = make_plan(rows, channels);
+  Plan plan;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_TRAIN_IO(io_dtype, "pretrain_mix6", {
-    mix6_backward_kernel<io_t><<<dim3(plan.col_tiles, plan.slabs), kThreads, 0, s>>>(
-        CP(io_t, x), six, P(io_t, grad_x), workspace, rows, seq_len, channels, plan.rows_per_slab);
+    // register budget of the walk: 3 CTAs per SM (168 registers, a few spilled words) or 2 (no spill); diagnostic
+    // switch FRWKV_MIX6_BWD_CTAS=2
+    static const bool two = [] { const char* e = getenv("FRWKV_MIX6_BWD_CTAS"); return e && e[0] == '2'; }();
+    if (two)
+      plan = launch_walk(mix6_backward_kernel<io_t, 2>, rows, channels, s, 
+        CP(io_t, x), six, P(io_t, grad_x), workspace, rows, seq_len, channels);
+    else
+      plan = launch_walk(mix6_backward_kernel<io_t, 3>, rows, channels, s, 
+        CP(io_t, x), six, P(io_t, grad_x), workspace, rows, seq_len, channels);
     if (int rc = check_launch("mix6_backward_kernel")) return rc;
     return reduce_partials<io_t>(workspace, targets, plan, channels, 6, s);
   })
@@ -749,13 +876,12 @@ extern "C" int frwkv_pretrain_kk_pre_forward(const void* k, const void* k_k, con
   FRWKV_REQUIRE(k && k_k && a && k_a && new_k && neg_kk && kka && inv_norm, "pretrain_kk_pre: null pointer argument");
   if (int rc = check_dense("pretrain_kk_pre", rows, channels, 0, 0)) return rc;
   if (int rc = check_heads("pretrain_kk_pre", channels, head_size)) return rc;
-  const Plan plan = make_plan(rows, channels);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_TRAIN_IO(io_dtype, "pretrain_kk_pre", {
     FRWKV_TRAIN_LANES(head_size, {
-      kk_pre_forward_kernel<io_t, kLanes><<<dim3(plan.col_tiles, plan.slabs), kThreads, 0, s>>>(
+      launch_walk(kk_pre_forward_kernel<io_t, kLanes>, rows, channels, s, 
           CP(io_t, k), CP(io_t, k_k), CP(io_t, a), CP(io_t, k_a), P(io_t, new_k), P(io_t, neg_kk), P(io_t, kka),
-          inv_norm, rows, channels, plan.rows_per_slab);
+          inv_norm, rows, channels);
     })
     return check_launch("kk_pre_forward_kernel");
   })
@@ -774,14 +900,14 @@ extern "C" int frwkv_pretrain_kk_pre_backward(const void* grad_new_k, const void
                 "pretrain_kk_pre: null pointer argument");
   if (int rc = check_dense("pretrain_kk_pre", rows, channels, workspace_floats, 2)) return rc;
   if (int rc = check_heads("pretrain_kk_pre", channels, head_size)) return rc;
-  const Plan plan = make_plan(rows, channels);
+  Plan plan;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   ReduceTargets targets{{grad_k_k, grad_k_a}};
   FRWKV_TRAIN_IO(io_dtype, "pretrain_kk_pre", {
     FRWKV_TRAIN_LANES(head_size, {
-      kk_pre_backward_kernel<io_t, kLanes><<<dim3(plan.col_tiles, plan.slabs), kThreads, 0, s>>>(
+      plan = launch_walk(kk_pre_backward_kernel<io_t, kLanes>, rows, channels, s, 
           CP(io_t, grad_new_k), CP(io_t, grad_neg_kk), CP(io_t, grad_kka), CP(io_t, k), CP(io_t, k_k), CP(io_t, a),
-          CP(io_t, k_a), inv_norm, P(io_t, grad_k), P(io_t, grad_a), workspace, rows, channels, plan.rows_per_slab);
+          CP(io_t, k_a), inv_norm, P(io_t, grad_k), P(io_t, grad_a), workspace, rows, channels);
     })
     if (int rc = check_launch("kk_pre_backward_kernel")) return rc;
     return reduce_partials<io_t>(workspace, targets, plan, channels, 2, s);
@@ -799,13 +925,12 @@ extern "C" int frwkv_pretrain_lnx_rkvres_xg_forward(const void* x, const void* r
                 "pretrain_lnx_rkvres_xg: null pointer argument");
   if (int rc = check_dense("pretrain_lnx_rkvres_xg", rows, channels, 0, 0)) return rc;
   if (int rc = check_heads("pretrain_lnx_rkvres_xg", channels, head_size)) return rc;
-  const Plan plan = make_plan(rows, channels);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_TRAIN_IO(io_dtype, "pretrain_lnx_rkvres_xg", {
     FRWKV_TRAIN_LANES(head_size, {
-      lnx_forward_kernel<io_t, kLanes><<<dim3(plan.col_tiles, plan.slabs), kThreads, 0, s>>>(
+      launch_walk(lnx_forward_kernel<io_t, kLanes>, rows, channels, s, 
           CP(io_t, x), CP(io_t, r), CP(io_t, k), CP(io_t, v), CP(io_t, r_k), CP(io_t, weight), CP(io_t, bias),
-          CP(io_t, g), P(io_t, out), mean, rstd, rows, channels, plan.rows_per_slab);
+          CP(io_t, g), P(io_t, out), mean, rstd, rows, channels);
     })
     return check_launch("lnx_forward_kernel");
   })
@@ -824,15 +949,15 @@ extern "C" int frwkv_pretrain_lnx_rkvres_xg_backward(
                 "pretrain_lnx_rkvres_xg: null pointer argument");
   if (int rc = check_dense("pretrain_lnx_rkvres_xg", rows, channels, workspace_floats, 3)) return rc;
   if (int rc = check_heads("pretrain_lnx_rkvres_xg", channels, head_size)) return rc;
-  const Plan plan = make_plan(rows, channels);
+  Plan plan;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   ReduceTargets targets{{grad_r_k, grad_weight, grad_bias}};
   FRWKV_TRAIN_IO(io_dtype, "pretrain_lnx_rkvres_xg", {
     FRWKV_TRAIN_LANES(head_size, {
-      lnx_backward_kernel<io_t, kLanes><<<dim3(plan.col_tiles, plan.slabs), kThreads, 0, s>>>(
+      plan = launch_walk(lnx_backward_kernel<io_t, kLanes>, rows, channels, s, 
           CP(io_t, grad_out), CP(io_t, x), CP(io_t, r), CP(io_t, k), CP(io_t, v), CP(io_t, r_k), CP(io_t, weight),
           CP(io_t, bias), CP(io_t, g), mean, rstd, P(io_t, grad_x), P(io_t, grad_r), P(io_t, grad_k), P(io_t, grad_v),
-          P(io_t, grad_g), workspace, rows, channels, plan.rows_per_slab);
+          P(io_t, grad_g), workspace, rows, channels);
     })
     if (int rc = check_launch("lnx_backward_kernel")) return rc;
     return reduce_partials<io_t>(workspace, targets, plan, channels, 3, s);

@@ -9,6 +9,7 @@ matter, runs a handful of launches and exits, so that an `ncu` capture of one of
   tmix    one TMix layer chain at C=2048 for M in (4, 512)
   decode  recurrent decode steps at B=256, H=32 (the benchmark's shape, 8 launches)
   decode16  the same on an fp16 state pool
+  glue    training-side TMix glue, forward + backward of the five operators: B=2, T=4096, C=4096 (67 MB per tensor)
 """
 from __future__ import annotations
 
@@ -86,8 +87,24 @@ def case_decode16(reps: int = 8):
         F.infer_recurrent_fp16_advance_i32(elapsed, 1)
 
 
+def case_glue(reps: int = 2):
+    B, T, C = 2, 4096, 4096
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=gen).to(torch.bfloat16).requires_grad_()  # noqa: E731
+    x, r, k, v, g = (rn(B, T, C) for _ in range(5))
+    vecs = [rn(C) for _ in range(6)]
+    r_k = rn(C // D, D)
+    go = [torch.randn(B, T, C, device="cuda", generator=gen).to(torch.bfloat16) for _ in range(6)]
+    for _ in range(reps):
+        outs = [F.pretrain_tmix_a_gate_bf16(vecs[0], x), F.pretrain_tmix_vres_gate_bf16(x, r, vecs[0], k),
+                *F.pretrain_tmix_kk_pre_bf16(x, vecs[0], r, vecs[1]),
+                F.pretrain_tmix_lnx_rkvres_xg_bf16(x, r, k, v, r_k, vecs[1], vecs[2], g)]
+        torch.autograd.backward(outs, go[:len(outs)])
+        torch.autograd.backward(F.pretrain_tmix_mix6_bf16(x, *vecs), go)
+
+
 if __name__ == "__main__":
-    cases = {"chunk": case_chunk, "train": case_train, "train512": lambda: case_train(2, 8, 512, 64), "tmix": case_tmix, "decode": case_decode, "decode16": case_decode16}
+    cases = {"glue": case_glue, "chunk": case_chunk, "train": case_train, "train512": lambda: case_train(2, 8, 512, 64), "tmix": case_tmix, "decode": case_decode, "decode16": case_decode16}
     name = sys.argv[1] if len(sys.argv) > 1 else ""
     if name not in cases:
         raise SystemExit(__doc__)
