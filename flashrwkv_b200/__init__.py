@@ -28,6 +28,7 @@ from .tmix.mix6 import (
     infer_tmix_mix6_forward_varlen,
     infer_tmix_shift_project_forward_varlen,
     pretrain_tmix_mix6_bf16,
+    statetune_tmix_mix6_bf16,
 )
 from .tmix.normalization import *  # noqa: F401,F403
 from .tmix.normalization import __all__ as _norm_all
@@ -55,6 +56,7 @@ __all__ = [
     "pretrain_tmix_mix6_bf16",
     "pretrain_tmix_vres_gate_bf16",
     "statetune_recurrent_fp32io16",
+    "statetune_tmix_mix6_bf16",
     "rl_infctx_chunk_fp32io16",
     "rl_infctx_chunk_fp32io16_factor_recompute",
 ]

@@ -261,6 +261,13 @@ __global__ __launch_bounds__(kThreads) void vres_gate_backward_kernel(
 struct Six {
   const void* in[6];
   void* out[6];
+  // StateTune form (all null in the pretrain form): the row before t = 0 is initial[b] instead of zero, the last row
+  // of every sequence is also written to final_shift[b]; in the backward grad_final[b] joins the gradient of that last
+  // row and grad_initial[b] receives the shifted term of row t = 0.  All [B][C].
+  const void* initial = nullptr;
+  void* final_shift = nullptr;
+  const void* grad_final = nullptr;
+  void* grad_initial = nullptr;
 };
 
 // The six mix vectors of the CTA's 256 channels as fp32 in shared memory (all four warps walk the same channels; a
@@ -305,14 +312,21 @@ __global__ __launch_bounds__(kThreads) void mix6_forward_kernel(const io_t* __re
   if (!w.active || w.row_begin >= w.row_end) return;
   float prev[8], cur[8], next[8];
   int t = (int)(w.row_begin % seq_len);
+  long long b = w.row_begin / seq_len;
+  const io_t* initial = static_cast<const io_t*>(mix.initial);
+  io_t* final_shift = static_cast<io_t*>(mix.final_shift);
   if (t != 0) load8(x + (w.row_begin - 1) * channels + w.col, prev);
   load8(x + w.row_begin * channels + w.col, cur);
   for (long long row = w.row_begin; row < w.row_end; ++row) {
     const long long at = row * channels + w.col;
     if (row + 1 < w.row_end) load8(x + at + channels, next);
+    if (t == 0) {
+      if (initial != nullptr) load8(initial + b * channels + w.col, prev);
+      else zero8(prev);
+    }
     float xx[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) xx[e] = (t != 0 ? prev[e] : 0.f) - cur[e];
+    for (int e = 0; e < 8; ++e) xx[e] = prev[e] - cur[e];
 #pragma unroll
     for (int j = 0; j < 6; ++j) {
       float y[8], m[8];
@@ -321,12 +335,16 @@ __global__ __launch_bounds__(kThreads) void mix6_forward_kernel(const io_t* __re
       for (int e = 0; e < 8; ++e) y[e] = fmaf(xx[e], m[e], cur[e]);
       store8(static_cast<io_t*>(mix.out[j]) + at, y);
     }
+    if (t == seq_len - 1 && final_shift != nullptr) store8(final_shift + b * channels + w.col, cur);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       prev[e] = cur[e];
       cur[e] = next[e];
     }
-    if (++t == seq_len) t = 0;
+    if (++t == seq_len) {
+      t = 0;
+      ++b;
+    }
   }
 }
 
@@ -338,6 +356,10 @@ __device__ __forceinline__ void mix6_backward_walk(const io_t* __restrict__ x, c
                                                    const MixTable& m_s, long long rows, int seq_len, int channels) {
   float prev[8], carry[8];
   int t = (int)(w.row_begin % seq_len);
+  long long b = w.row_begin / seq_len;
+  const io_t* initial = static_cast<const io_t*>(mix.initial);
+  const io_t* grad_final = static_cast<const io_t*>(mix.grad_final);
+  io_t* grad_initial = static_cast<io_t*>(mix.grad_initial);
   if (t != 0) load8(x + (w.row_begin - 1) * channels + w.col, prev);
   zero8(carry);
   for (long long row = w.row_begin; row < w.row_end; ++row) {
@@ -346,8 +368,13 @@ __device__ __forceinline__ void mix6_backward_walk(const io_t* __restrict__ x, c
     load8(x + at, cur);
     zero8(direct);
     zero8(shifted);
+    if (t == 0) {
+      if (initial != nullptr) load8(initial + b * channels + w.col, prev);
+      else zero8(prev);
+    }
+    if (t == seq_len - 1 && grad_final != nullptr) load8(grad_final + b * channels + w.col, direct);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) xx[e] = (t != 0 ? prev[e] : 0.f) - cur[e];
+    for (int e = 0; e < 8; ++e) xx[e] = prev[e] - cur[e];
 #pragma unroll
     for (int j = 0; j < 6; ++j) {
       float g[8], m[8];
@@ -365,12 +392,16 @@ __device__ __forceinline__ void mix6_backward_walk(const io_t* __restrict__ x, c
       for (int e = 0; e < 8; ++e) carry[e] += t != 0 ? shifted[e] : 0.f;
       store8(grad_x + at - channels, carry);
     }
+    if (t == 0 && grad_initial != nullptr) store8(grad_initial + b * channels + w.col, shifted);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       carry[e] = direct[e] - shifted[e];
       prev[e] = cur[e];
     }
-    if (++t == seq_len) t = 0;
+    if (++t == seq_len) {
+      t = 0;
+      ++b;
+    }
   }
   if (w.row_end < rows && t != 0) {  // the slab's last row takes its shifted term from the next slab's first row
     const long long at = w.row_end * channels + w.col;
@@ -811,10 +842,10 @@ extern "C" int frwkv_pretrain_vres_gate_backward(const void* grad_out, const voi
   })
 }
 
-extern "C" int frwkv_pretrain_mix6_forward(const void* x, const void* const* mix, void* const* out, long long batch,
-                                           int seq_len, int channels, int io_dtype, frwkv_stream_t stream) {
+static int mix6_forward_impl(const void* x, const void* initial, const void* const* mix, void* const* out,
+                             void* final_shift, long long batch, int seq_len, int channels, int io_dtype,
+                             frwkv_stream_t stream) {
   using namespace frwkv;
-  clear_error();
   FRWKV_REQUIRE(x && mix && out, "pretrain_mix6: null pointer argument");
   FRWKV_REQUIRE(batch > 0 && seq_len > 0, "pretrain_mix6: sizes must be positive");
   const long long rows = batch * seq_len;
@@ -825,6 +856,8 @@ extern "C" int frwkv_pretrain_mix6_forward(const void* x, const void* const* mix
     six.in[j] = mix[j];
     six.out[j] = out[j];
   }
+  six.initial = initial;
+  six.final_shift = final_shift;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_TRAIN_IO(io_dtype, "pretrain_mix6", {
     launch_walk(mix6_forward_kernel<io_t>, rows, channels, s, CP(io_t, x), six, rows, seq_len,
@@ -833,12 +866,26 @@ extern "C" int frwkv_pretrain_mix6_forward(const void* x, const void* const* mix
   })
 }
 
-extern "C" int frwkv_pretrain_mix6_backward(const void* const* grad_out, const void* x, const void* const* mix,
-                                            void* grad_x, void* const* grad_mix, float* workspace,
-                                            long long workspace_floats, long long batch, int seq_len, int channels,
-                                            int io_dtype, frwkv_stream_t stream) {
+extern "C" int frwkv_pretrain_mix6_forward(const void* x, const void* const* mix, void* const* out, long long batch,
+                                           int seq_len, int channels, int io_dtype, frwkv_stream_t stream) {
+  frwkv::clear_error();
+  return mix6_forward_impl(x, nullptr, mix, out, nullptr, batch, seq_len, channels, io_dtype, stream);
+}
+
+extern "C" int frwkv_statetune_mix6_forward(const void* x, const void* initial_shift, const void* const* mix,
+                                            void* const* out, void* final_shift, long long batch, int seq_len,
+                                            int channels, int io_dtype, frwkv_stream_t stream) {
   using namespace frwkv;
   clear_error();
+  FRWKV_REQUIRE(initial_shift && final_shift, "statetune_mix6: null pointer argument");
+  return mix6_forward_impl(x, initial_shift, mix, out, final_shift, batch, seq_len, channels, io_dtype, stream);
+}
+
+static int mix6_backward_impl(const void* const* grad_out, const void* grad_final, const void* x, const void* initial,
+                              const void* const* mix, void* grad_x, void* grad_initial, void* const* grad_mix,
+                              float* workspace, long long workspace_floats, long long batch, int seq_len,
+                              int channels, int io_dtype, frwkv_stream_t stream) {
+  using namespace frwkv;
   FRWKV_REQUIRE(grad_out && x && mix && grad_x && grad_mix && workspace, "pretrain_mix6: null pointer argument");
   FRWKV_REQUIRE(batch > 0 && seq_len > 0, "pretrain_mix6: sizes must be positive");
   const long long rows = batch * seq_len;
@@ -851,6 +898,9 @@ extern "C" int frwkv_pretrain_mix6_backward(const void* const* grad_out, const v
     six.out[j] = const_cast<void*>(mix[j]);
     targets.out[j] = grad_mix[j];
   }
+  six.initial = initial;
+  six.grad_final = grad_final;
+  six.grad_initial = grad_initial;
   Plan plan;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_TRAIN_IO(io_dtype, "pretrain_mix6", {
@@ -866,6 +916,27 @@ extern "C" int frwkv_pretrain_mix6_backward(const void* const* grad_out, const v
     if (int rc = check_launch("mix6_backward_kernel")) return rc;
     return reduce_partials<io_t>(workspace, targets, plan, channels, 6, s);
   })
+}
+
+extern "C" int frwkv_pretrain_mix6_backward(const void* const* grad_out, const void* x, const void* const* mix,
+                                            void* grad_x, void* const* grad_mix, float* workspace,
+                                            long long workspace_floats, long long batch, int seq_len, int channels,
+                                            int io_dtype, frwkv_stream_t stream) {
+  frwkv::clear_error();
+  return mix6_backward_impl(grad_out, nullptr, x, nullptr, mix, grad_x, nullptr, grad_mix, workspace, workspace_floats,
+                            batch, seq_len, channels, io_dtype, stream);
+}
+
+extern "C" int frwkv_statetune_mix6_backward(const void* const* grad_out, const void* grad_final_shift, const void* x,
+                                             const void* initial_shift, const void* const* mix, void* grad_x,
+                                             void* grad_initial_shift, void* const* grad_mix, float* workspace,
+                                             long long workspace_floats, long long batch, int seq_len, int channels,
+                                             int io_dtype, frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(grad_final_shift && initial_shift && grad_initial_shift, "statetune_mix6: null pointer argument");
+  return mix6_backward_impl(grad_out, grad_final_shift, x, initial_shift, mix, grad_x, grad_initial_shift, grad_mix,
+                            workspace, workspace_floats, batch, seq_len, channels, io_dtype, stream);
 }
 
 extern "C" int frwkv_pretrain_kk_pre_forward(const void* k, const void* k_k, const void* a, const void* k_a,

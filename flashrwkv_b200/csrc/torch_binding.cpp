@@ -999,6 +999,68 @@ std::vector<torch::Tensor> pretrain_tmix_mix6_backward(torch::Tensor g_r, torch:
   return result;
 }
 
+void check_shift_rows(const torch::Tensor& t, const char* name, const torch::Tensor& x) {
+  check_io16(t, name, x);
+  TORCH_CHECK(t.dim() == 2 && t.size(0) == x.size(0) && t.size(1) == x.size(2), name, " must have shape [B,C]");
+}
+
+// returns the six mixed tensors and the final shift state x[:, -1, :]
+std::vector<torch::Tensor> statetune_tmix_mix6_forward(torch::Tensor x, torch::Tensor initial_shift,
+                                                       torch::Tensor x_r, torch::Tensor x_w, torch::Tensor x_k,
+                                                       torch::Tensor x_v, torch::Tensor x_a, torch::Tensor x_g) {
+  check_dense_root(x, "x");
+  check_shift_rows(initial_shift, "initial_shift", x);
+  const torch::Tensor mix[6] = {x_r, x_w, x_k, x_v, x_a, x_g};
+  const void* mix_ptr[6];
+  void* out_ptr[6];
+  std::vector<torch::Tensor> outs;
+  const c10::cuda::CUDAGuard guard(x.device());
+  for (int j = 0; j < 6; ++j) {
+    check_dense_vector(mix[j], "mix vector", x);
+    outs.push_back(torch::empty_like(x));
+    mix_ptr[j] = mix[j].data_ptr();
+    out_ptr[j] = outs.back().data_ptr();
+  }
+  outs.push_back(torch::empty_like(initial_shift));
+  check_rc(frwkv_statetune_mix6_forward(x.data_ptr(), initial_shift.data_ptr(), mix_ptr, out_ptr,
+                                        outs.back().data_ptr(), x.size(0), static_cast<int>(x.size(1)),
+                                        static_cast<int>(x.size(2)), io_dtype_of(x), current_stream(x)));
+  return outs;
+}
+
+// gradients of (x, initial_shift, x_r, x_w, x_k, x_v, x_a, x_g)
+std::vector<torch::Tensor> statetune_tmix_mix6_backward(torch::Tensor g_r, torch::Tensor g_w, torch::Tensor g_k,
+                                                        torch::Tensor g_v, torch::Tensor g_a, torch::Tensor g_g,
+                                                        torch::Tensor g_final, torch::Tensor x,
+                                                        torch::Tensor initial_shift, torch::Tensor x_r,
+                                                        torch::Tensor x_w, torch::Tensor x_k, torch::Tensor x_v,
+                                                        torch::Tensor x_a, torch::Tensor x_g) {
+  check_dense_root(x, "x");
+  check_shift_rows(initial_shift, "initial_shift", x);
+  check_shift_rows(g_final, "grad of the final shift", x);
+  const torch::Tensor grads[6] = {g_r, g_w, g_k, g_v, g_a, g_g};
+  const torch::Tensor mix[6] = {x_r, x_w, x_k, x_v, x_a, x_g};
+  const void* grad_ptr[6];
+  const void* mix_ptr[6];
+  void* gmix_ptr[6];
+  const c10::cuda::CUDAGuard guard(x.device());
+  std::vector<torch::Tensor> result{torch::empty_like(x), torch::empty_like(initial_shift)};
+  for (int j = 0; j < 6; ++j) {
+    check_dense(grads[j], "grad_output", x);
+    check_dense_vector(mix[j], "mix vector", x);
+    result.push_back(torch::empty_like(mix[j]));
+    grad_ptr[j] = grads[j].data_ptr();
+    mix_ptr[j] = mix[j].data_ptr();
+    gmix_ptr[j] = result.back().data_ptr();
+  }
+  auto ws = reduce_workspace(x, 6);
+  check_rc(frwkv_statetune_mix6_backward(grad_ptr, g_final.data_ptr(), x.data_ptr(), initial_shift.data_ptr(), mix_ptr,
+                                         result[0].data_ptr(), result[1].data_ptr(), gmix_ptr, ws.data_ptr<float>(),
+                                         ws.numel(), x.size(0), static_cast<int>(x.size(1)),
+                                         static_cast<int>(x.size(2)), io_dtype_of(x), current_stream(x)));
+  return result;
+}
+
 void check_head_size(const torch::Tensor& x, int64_t head_size) {
   TORCH_CHECK(head_size == 64 || head_size == 128 || head_size == 256, "head_size must be one of 64, 128, or 256");
   TORCH_CHECK(x.size(2) % head_size == 0, "C must be divisible by head_size");
@@ -1194,6 +1256,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("value"), py::arg("first_value"), py::arg("v0"), py::arg("v12"));
   m.def("pretrain_tmix_mix6_forward", &pretrain_tmix_mix6_forward);
   m.def("pretrain_tmix_mix6_backward", &pretrain_tmix_mix6_backward);
+  m.def("statetune_tmix_mix6_forward", &statetune_tmix_mix6_forward);
+  m.def("statetune_tmix_mix6_backward", &statetune_tmix_mix6_backward);
   m.def("pretrain_tmix_kk_pre_forward", &pretrain_tmix_kk_pre_forward);
   m.def("pretrain_tmix_kk_pre_backward", &pretrain_tmix_kk_pre_backward);
   m.def("pretrain_tmix_lnx_rkvres_xg_forward", &pretrain_tmix_lnx_rkvres_xg_forward);

@@ -165,5 +165,52 @@ def pretrain_tmix_mix6_bf16(x, x_r, x_w, x_k, x_v, x_a, x_g):
     return _PretrainMix6.apply(x, x_r, x_w, x_k, x_v, x_a, x_g)
 
 
+class _StatetuneMix6(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, initial_shift, x_r, x_w, x_k, x_v, x_a, x_g):
+        outputs = tuple(extension().statetune_tmix_mix6_forward(x, initial_shift, x_r, x_w, x_k, x_v, x_a, x_g))
+        ctx.save_for_backward(x, initial_shift, x_r, x_w, x_k, x_v, x_a, x_g)
+        return outputs
+
+    @staticmethod
+    def backward(ctx, *grad_outputs):
+        x, initial_shift = ctx.saved_tensors[:2]
+        grads = []
+        for g, like in zip(grad_outputs, (x,) * 6 + (initial_shift,)):
+            grads.append(torch.zeros_like(like) if g is None else g.contiguous())
+        return tuple(extension().statetune_tmix_mix6_backward(*grads, *ctx.saved_tensors))
+
+
+def statetune_tmix_mix6_bf16(x, initial_shift, x_r, x_w, x_k, x_v, x_a, x_g):
+    """Six-way token shift with a differentiable chunk-boundary shift state: the row before t = 0 is
+    `initial_shift[b]`; returns the six mixed tensors and the final shift state `x[:, -1, :]`.  Mirror of
+    `flashrwkv2/tmix/mix6/__init__.py:244-343` (there C must be even, here a multiple of 8)."""
+    if not isinstance(x, torch.Tensor):
+        raise TypeError("x must be a torch.Tensor")
+    if x.dtype != torch.bfloat16:
+        raise TypeError("x must have dtype torch.bfloat16")
+    if not x.is_cuda or not x.is_contiguous():
+        raise ValueError("x must be contiguous CUDA bfloat16 [B,T,C]")
+    if x.ndim != 3 or any(size <= 0 for size in x.shape):
+        raise ValueError("x must have non-empty shape [B,T,C]")
+    if x.shape[2] % 8:
+        raise ValueError("x channel dimension C must be divisible by 8")
+    tensors = (initial_shift, x_r, x_w, x_k, x_v, x_a, x_g)
+    names = ("initial_shift", "x_r", "x_w", "x_k", "x_v", "x_a", "x_g")
+    shapes = ((x.shape[0], x.shape[2]),) + ((x.shape[2],),) * 6
+    for name, tensor, shape in zip(names, tensors, shapes):
+        if not isinstance(tensor, torch.Tensor):
+            raise TypeError(f"{name} must be a torch.Tensor")
+        if tensor.dtype != torch.bfloat16:
+            raise TypeError(f"{name} must have dtype torch.bfloat16")
+        if not tensor.is_cuda or not tensor.is_contiguous():
+            raise ValueError(f"{name} must be contiguous CUDA bfloat16")
+        if tensor.shape != shape:
+            raise ValueError(f"{name} must have shape {shape}")
+        if tensor.device != x.device:
+            raise ValueError(f"{name} must share x's device")
+    return _StatetuneMix6.apply(x, *tensors)
+
+
 __all__ = ["infer_tmix_mix6_forward_varlen", "infer_tmix_mix6_add_layer_norm_forward_varlen",
-           "infer_tmix_shift_project_forward_varlen", "pretrain_tmix_mix6_bf16"]
+           "infer_tmix_shift_project_forward_varlen", "pretrain_tmix_mix6_bf16", "statetune_tmix_mix6_bf16"]

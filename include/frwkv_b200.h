@@ -339,6 +339,18 @@ int frwkv_pretrain_mix6_backward(const void* const* grad_out, const void* x, con
                                  void* const* grad_mix, float* workspace, long long workspace_floats, long long batch,
                                  int seq_len, int channels, int io_dtype, frwkv_stream_t stream);
 
+/* StateTune form of mix6: the row before t = 0 is initial_shift[b] ([batch][C]) and the last row of every sequence
+ * is also returned as final_shift[b]; the backward takes the gradient of final_shift and returns that of
+ * initial_shift.  Replaces statetune_tmix_mix6_forward / backward (flashrwkv2/tmix/mix6/__init__.py:244-262). */
+int frwkv_statetune_mix6_forward(const void* x, const void* initial_shift, const void* const* mix, void* const* out,
+                                 void* final_shift, long long batch, int seq_len, int channels, int io_dtype,
+                                 frwkv_stream_t stream);
+int frwkv_statetune_mix6_backward(const void* const* grad_out, const void* grad_final_shift, const void* x,
+                                  const void* initial_shift, const void* const* mix, void* grad_x,
+                                  void* grad_initial_shift, void* const* grad_mix, float* workspace,
+                                  long long workspace_floats, long long batch, int seq_len, int channels, int io_dtype,
+                                  frwkv_stream_t stream);
+
 /* kk = normalize(k * k_k) per head (eps 1e-12); new_k = k * (1 + (a - 1) * k_a), neg_kk = -kk, kka = kk * a;
  * inv_norm fp32 [rows][C / head_size] is saved for the backward.  head_size 64, 128 or 256.
  * Replaces csrc/sm90/tmix/kk_pre/pretrain_bf16_{forward,backward}.cu. */

@@ -8,7 +8,8 @@ float; here float64, so that the CUDA result can be judged against an exact valu
   a_gate         csrc/sm90/tmix/a_gate/pretrain_bf16_forward.cu, pretrain_bf16_backward.cu
   vres_gate      csrc/sm90/tmix/vres_gate/pretrain_bf16_forward.cu, pretrain_bf16_backward.cu
   mix6           csrc/sm90/tmix/mix6/pretrain_bf16_forward.cu, pretrain_bf16_backward.cu
-                 (the torch formula of tests/tmix/mix6/test.py:72-77)
+                 (the torch formula of tests/tmix/mix6/test.py:72-77; StateTune form with an initial and a final
+                 shift state: tests/tmix/mix6/test.py:114-118)
   kk_pre         csrc/sm90/tmix/kk_pre/pretrain_bf16_forward.cu:66-117 (eps 1e-12, clamp of the norm) and
                  pretrain_bf16_backward.cu (projection term only while the norm is above eps)
   lnx_rkvres_xg  csrc/sm90/tmix/lnx_rkvres_xg/pretrain_bf16_forward.cu:64-124 (eps 64e-5, biased variance; the
@@ -62,29 +63,37 @@ def vres_gate_backward(grad_out, v, v_first, v0, v12):
     return g * (1.0 - s), g * s, _rows(dz).sum(0), dz
 
 
-def _shifted(x):
+def _shifted(x, initial=None):
     prev = np.zeros_like(x)
     prev[:, 1:] = x[:, :-1]
+    if initial is not None:
+        prev[:, 0] = _f64(initial)
     return prev
 
 
-def mix6(x, mixes):
+def mix6(x, mixes, initial=None):
+    """`initial` = the StateTune form's shift state [B,C] (the row before t = 0); None = zero (pretrain form)."""
     x = _f64(x)
-    xx = _shifted(x) - x
+    xx = _shifted(x, initial) - x
     return [x + xx * _f64(m) for m in mixes]
 
 
-def mix6_backward(grad_outs, x, mixes):
+def mix6_backward(grad_outs, x, mixes, initial=None, grad_final=None):
+    """Returns (grad_x, [grad_mix] * 6, grad_initial); grad_final = the gradient of the final shift state x[:, -1]."""
     x = _f64(x)
-    xx = _shifted(x) - x
+    xx = _shifted(x, initial) - x
     gx = np.zeros_like(x)
+    ginit = np.zeros_like(x[:, 0])
     gm = []
     for g, m in zip(grad_outs, mixes):
         g, m = _f64(g), _f64(m)
         gx += g * (1.0 - m)
         gx[:, :-1] += (g * m)[:, 1:]
+        ginit += (g * m)[:, 0]
         gm.append(_rows(g * xx).sum(0))
-    return gx, gm
+    if grad_final is not None:
+        gx[:, -1] += _f64(grad_final)
+    return gx, gm, ginit
 
 
 def _heads(t, head_size):

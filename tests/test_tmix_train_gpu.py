@@ -60,10 +60,64 @@ def test_mix6(B, T, C):
     for j, (got, want) in enumerate(zip(outs, O.mix6(x, mixes))):
         _check(got, want, f"mix6 out {j}")
     torch.autograd.backward(outs, gos)
-    gx, gm = O.mix6_backward(gos, x, mixes)
+    gx, gm, _ = O.mix6_backward(gos, x, mixes)
     _check(x.grad, gx, "d x")
     for j in range(6):
         _check(mixes[j].grad, gm[j], f"d mix {j}")
+
+
+@pytest.mark.parametrize("B,T,C", [(1, 1, 128), (2, 7, 128), (2, 31, 128), (3, 131, 2048)])
+@pytest.mark.parametrize("zero_shift", [False, True])
+def test_statetune_mix6(B, T, C, zero_shift):
+    """Shapes of the reference's test (tests/tmix/mix6/test.py:88-135) plus one with many slabs; with a zero shift
+    state the six outputs are bit-identical to the pretrain form's."""
+    import flashrwkv_b200 as F
+    from oracle import tmix_train_oracle as O
+
+    gen = torch.Generator().manual_seed(1000 + B * 100 + T)
+    x = _rn(gen, B, T, C, scale=0.05)
+    initial = _rn(gen, B, C, scale=0.0 if zero_shift else 0.05)
+    mixes = [_rn(gen, C, scale=0.1) for _ in range(6)]
+    gos = [_rn(gen, B, T, C) for _ in range(6)] + [_rn(gen, B, C)]
+    outs = F.statetune_tmix_mix6_bf16(x, initial, *mixes)
+    assert len(outs) == 7
+    for j, (got, want) in enumerate(zip(outs[:6], O.mix6(x, mixes, initial))):
+        _check(got, want, f"mix6 out {j}")
+    assert torch.equal(outs[6], x[:, -1, :])
+    grads = torch.autograd.grad(outs, [x, initial, *mixes], gos)
+    gx, gm, ginit = O.mix6_backward(gos[:6], x, mixes, initial, gos[6])
+    _check(grads[0], gx, "d x")
+    _check(grads[1], ginit, "d initial_shift")
+    for j in range(6):
+        _check(grads[2 + j], gm[j], f"d mix {j}")
+    if zero_shift:
+        for a, b in zip(outs[:6], F.pretrain_tmix_mix6_bf16(x.detach(), *(m.detach() for m in mixes))):
+            assert torch.equal(a, b)
+
+
+def test_statetune_mix6_chunk_composition():
+    """Two chunks chained through the shift state give the whole sequence's outputs and gradients
+    (tests/tmix/mix6/test.py:138-185)."""
+    import flashrwkv_b200 as F
+
+    gen = torch.Generator().manual_seed(23)
+    B, T, C, split = 2, 7, 128, 3
+    x, initial = _rn(gen, B, T, C), _rn(gen, B, C)
+    mixes = [_rn(gen, C) for _ in range(6)]
+    whole = F.statetune_tmix_mix6_bf16(x, initial, *mixes)
+    ups = [_rn(gen, B, T, C).detach() for _ in range(6)] + [_rn(gen, B, C).detach()]
+    whole_grads = torch.autograd.grad(whole, [x, initial, *mixes], ups)
+    x2, init2 = x.detach().clone().requires_grad_(), initial.detach().clone().requires_grad_()
+    mixes2 = [m.detach().clone().requires_grad_() for m in mixes]
+    first = F.statetune_tmix_mix6_bf16(x2[:, :split].contiguous(), init2, *mixes2)
+    second = F.statetune_tmix_mix6_bf16(x2[:, split:].contiguous(), first[6], *mixes2)
+    for j in range(6):
+        assert torch.equal(torch.cat((first[j], second[j]), dim=1), whole[j])
+    assert torch.equal(second[6], whole[6])
+    chained = [torch.cat((first[j], second[j]), dim=1) for j in range(6)] + [second[6]]
+    grads2 = torch.autograd.grad(chained, [x2, init2, *mixes2], ups)
+    for a, b in zip(whole_grads, grads2):
+        assert torch.allclose(a.float(), b.float(), atol=0.03, rtol=0.03)
 
 
 @pytest.mark.parametrize("head_size", [64, 128, 256])

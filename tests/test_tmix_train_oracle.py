@@ -43,9 +43,28 @@ def test_mix6_backward_matches_autograd():
     for got, want in zip(O.mix6(x, mixes), outs):
         _close(got, want)
     want = torch.autograd.grad(outs, [x, *mixes], gos)
-    gx, gm = O.mix6_backward(gos, x, mixes)
+    gx, gm, _ = O.mix6_backward(gos, x, mixes)
     _close(gx, want[0])
     for g, w in zip(gm, want[1:]):
+        _close(g, w)
+
+
+def test_statetune_mix6_backward_matches_autograd():
+    """The formula of the reference's StateTune mix6 test (tests/tmix/mix6/test.py:114-118)."""
+    gen = torch.Generator().manual_seed(7)
+    x, initial = _rn(gen, 2, 5, 8), _rn(gen, 2, 8)
+    mixes = [_rn(gen, 8) for _ in range(6)]
+    gos = [_rn(gen, 2, 5, 8) for _ in range(6)]
+    gfinal = _rn(gen, 2, 8)
+    prev = torch.cat((initial[:, None, :], x[:, :-1]), dim=1)
+    outs = [x + (prev - x) * m for m in mixes] + [x[:, -1, :].contiguous()]
+    for got, want in zip(O.mix6(x, mixes, initial), outs[:6]):
+        _close(got, want)
+    want = torch.autograd.grad(outs, [x, initial, *mixes], [*gos, gfinal])
+    gx, gm, ginit = O.mix6_backward(gos, x, mixes, initial, gfinal)
+    _close(gx, want[0])
+    _close(ginit, want[1])
+    for g, w in zip(gm, want[2:]):
         _close(g, w)
 
 
