@@ -101,6 +101,14 @@ __device__ __forceinline__ float retention_log_derivative(float decay_logit) {
   return -0.6065306597126334f * s * (1.0f - s);
 }
 
+// fp16-state contract: the rounded retention increment half(w - 1 + dither) of one key channel; the dither is the
+// signed 32-bit product phase * 2654435769 scaled by 2^-41 (tests/tmix/wkv7/test.py:249-258 of the reference).
+__device__ __forceinline__ float delta_of(float logit, uint32_t phase) {
+  const float w = retention(logit);
+  const float dither = __int2float_rn((int)(phase * 2654435769u)) * 4.547473508864641e-13f;
+  return __half2float(__float2half_rn((w - 1.0f) + dither));
+}
+
 __device__ __forceinline__ float quiet_nan() { return __int_as_float(0x7fffffff); }
 
 // ---- programmatic dependent launch -------------------------------------------------------------------------------

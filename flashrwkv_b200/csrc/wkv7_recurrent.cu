@@ -24,10 +24,10 @@
 
 namespace frwkv {
 // head sizes 128 and 256 (wkv7_recurrent_wide.cu)
-int launch_recurrent_wide(const int* cu, const int* idx, const int* status, float* state, const void* r, const void* w,
-                          const void* k, const void* v, const void* a, const void* b, const void* bias, void* y,
-                          float* y32, int total_tokens, int num_sequences, int num_heads, int head_size, int io_dtype,
-                          float scale, cudaStream_t stream);
+int launch_recurrent_wide(const int* cu, const int* idx, const int* status, const int* elapsed, void* state,
+                          const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                          const void* bias, void* y, float* y32, int total_tokens, int num_sequences, int num_heads,
+                          int head_size, int io_dtype, float scale, cudaStream_t stream);
 namespace {
 
 constexpr int kD = 64;
@@ -554,7 +554,7 @@ extern "C" int frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex(
   FRWKV_REQUIRE(num_sequences > 0 && num_sequences <= 65535,
                 "wkv7_recurrent: state_indices must contain 1..65535 sequences");
   if (head_size == 128 || head_size == 256)  // the general kernel; the tuned ones below are for head size 64
-    return launch_recurrent_wide(cu_seqlens, state_indices, metadata_status, state_pool, r, decay_logits, k, v, a, b,
+    return launch_recurrent_wide(cu_seqlens, state_indices, metadata_status, nullptr, state_pool, r, decay_logits, k, v, a, b,
                                  decay_bias, y, y_fp32, total_tokens, num_sequences, num_heads, head_size, io_dtype,
                                  scale, reinterpret_cast<cudaStream_t>(stream));
   if (head_size != 64) {

@@ -24,6 +24,11 @@
 #include "umma.cuh"
 
 namespace frwkv {
+// head sizes 128 and 256 (wkv7_recurrent_wide.cu); elapsed != nullptr selects the fp16 pool
+int launch_recurrent_wide(const int* cu, const int* idx, const int* status, const int* elapsed, void* state,
+                          const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                          const void* bias, void* y, float* y32, int total_tokens, int num_sequences, int num_heads,
+                          int head_size, int io_dtype, float scale, cudaStream_t stream);
 namespace {
 
 constexpr int kD = 64;
@@ -48,12 +53,6 @@ __device__ __forceinline__ uint2 round_half4(float4& q) {
   u.x = *reinterpret_cast<const uint32_t*>(&lo);
   u.y = *reinterpret_cast<const uint32_t*>(&hi);
   return u;
-}
-// the rounded retention increment of one key channel
-__device__ __forceinline__ float delta_of(float logit, uint32_t phase) {
-  const float w = retention(logit);
-  const float dither = __int2float_rn((int)(phase * 2654435769u)) * 4.547473508864641e-13f;
-  return __half2float(__float2half_rn((w - 1.0f) + dither));
 }
 
 struct Out4 {
@@ -416,8 +415,12 @@ extern "C" int frwkv_wkv7_recurrent_fp16_forward_varlen(
                 "wkv7_recurrent_fp16: null pointer argument");
   FRWKV_REQUIRE(total_tokens > 0 && num_sequences > 0 && num_heads > 0, "wkv7_recurrent_fp16: sizes must be positive");
   FRWKV_REQUIRE(num_sequences <= 65535, "wkv7_recurrent_fp16: at most 65535 sequences per call");
+  if (head_size == 128 || head_size == 256)  // the general kernel; the kernels of this file are the tuned head-size-64 ones
+    return launch_recurrent_wide(cu_seqlens, state_indices, metadata_status, elapsed_state_pool, state_pool, r,
+                                 decay_logits, k, v, a, b, decay_bias, y, nullptr, total_tokens, num_sequences, num_heads,
+                                 head_size, io_dtype, scale, reinterpret_cast<cudaStream_t>(stream));
   if (head_size != 64)
-    return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_recurrent_fp16: head size %d is not built (only 64)", head_size);
+    return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_recurrent_fp16: head size must be 64, 128, or 256, got %d", head_size);
   FRWKV_REQUIRE((long long)num_sequences * num_heads * 2 <= 0x7fffffffLL, "wkv7_recurrent_fp16: too many units");
   FRWKV_REQUIRE(scale == scale && scale - scale == 0.f, "wkv7_recurrent_fp16: scale must be finite");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

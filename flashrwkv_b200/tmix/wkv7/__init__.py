@@ -139,7 +139,7 @@ def infer_recurrent_fp16_advance_i32_varlen(elapsed_state_pool, cu_seqlens, stat
 def infer_recurrent_fp16_forward_varlen(r, decay_logits, k, v, a, b, *, state_pool, elapsed_state_pool, cu_seqlens,
                                         state_indices, scale: float = 1.0, decay_bias=None,
                                         max_seqlen: int | None = None, validated_metadata=None) -> torch.Tensor:
-    """Packed RWKV-7 recurrence on an fp16 ``state_pool [slots,H,64,64]``, updated in place.
+    """Packed RWKV-7 recurrence on an fp16 ``state_pool [slots,H,D,D]`` (D = 64, 128 or 256), updated in place.
 
     The retention enters as a rounded fp16 increment with a deterministic dither whose phase comes from the int32
     ``elapsed_state_pool [slots]`` (read, never advanced here: see the two ``advance`` operators).  Returns the

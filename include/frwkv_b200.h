@@ -105,7 +105,7 @@ int frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex(
  *               dither = int32(uint32(phase) * 2654435769) * 2^-41,
  *               phase = head * D + key channel + elapsed_state_pool[slot] + index of the token in its sequence
  *   state_pool : fp16 [slots, H, D, D];  elapsed_state_pool : int32 [slots], read only;
- *   the other arguments as in frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex.  head_size must be 64.
+ *   the other arguments as in frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex.  head_size 64 (tuned kernels), 128 or 256 (general kernel).
  */
 int frwkv_wkv7_recurrent_fp16_forward_varlen(
     const int32_t* cu_seqlens, const int32_t* state_indices, const int32_t* metadata_status,

@@ -12,6 +12,7 @@ GOLDEN = Path(__file__).resolve().parent / "golden"
 _IO_DTYPE = {
     "recurrent_ragged": torch.bfloat16,
     "recurrent_fp16state": torch.float16,
+    "recurrent_fp16state_d128": torch.float16,
     "chunk_bf16": torch.bfloat16,
     "rl_fp16": torch.float16,
     "statetune": torch.float16,

@@ -15,6 +15,7 @@ Cases (reference file:line of the oracle that produced the expectation):
                       scales of tests/tmix/wkv7/test.py:417-477, bf16 io, with decay_bias
   recurrent_fp16state tests/tmix/wkv7/test.py:216-277   fp16 state pool with dither; lengths (1,2,4,8,19), slots
                       [5,0,7,2,4], elapsed = 11 * slot, value scales of tests/tmix/wkv7/test.py:417-477, fp16 io, bias
+  recurrent_fp16state_d128  the same at head size 128: lengths (1,2,4), slots [3,0,2]
   chunk_bf16          tests/tmix/wkv7/chunk/test.py:18-49   lengths (1,9,17), scale 0.5, bf16 state
   rl_fp16             tests/rl_infctx/wkv7/test.py:12-53    lengths (2,5), fp16 io, decay_bias
   statetune           tests/tmix/wkv7/statetune/test.py:39-87 + autograd (:109-124), scale 0.75
@@ -108,6 +109,22 @@ def main() -> None:
     y, final = wkv_test.rwkv7_fp16_reference(r, w, k, v, a, b, state_pool=pool, elapsed_state_pool=elapsed,
                                              cu_seqlens=cu, state_indices=idx, scale=0.5, decay_bias=bias)
     _save("recurrent_fp16state", r=r, w=w, k=k, v=v, a=a, b=b, cu_seqlens=cu, state_indices=idx, state_pool=pool,
+          elapsed_state_pool=elapsed, decay_bias=bias, scale=0.5, y=y, final_pool=final)
+
+    # ---- recurrent_fp16state_d128: the same contract at head size 128 (phase = head * 128 + channel + ...)
+    torch.manual_seed(20260804 + 128 + 7)
+    lengths = (1, 2, 4)
+    N, H, D128 = sum(lengths), 2, 128
+    rnd = lambda s: (torch.randn(N, H, D128) * s).to(torch.float16)  # noqa: E731
+    r, w, k, v, a, b = rnd(0.12), rnd(3.5), rnd(0.06), rnd(0.06), rnd(0.06), rnd(0.06)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lengths)]), dtype=torch.int32)
+    idx = torch.tensor([3, 0, 2], dtype=torch.int32)
+    pool = (torch.randn(4, H, D128, D128) * 0.03).half()
+    elapsed = (torch.arange(4, dtype=torch.int32) * 11)
+    bias = (torch.randn(H, D128) * 0.2).to(torch.float16)
+    y, final = wkv_test.rwkv7_fp16_reference(r, w, k, v, a, b, state_pool=pool, elapsed_state_pool=elapsed,
+                                             cu_seqlens=cu, state_indices=idx, scale=0.5, decay_bias=bias)
+    _save("recurrent_fp16state_d128", r=r, w=w, k=k, v=v, a=a, b=b, cu_seqlens=cu, state_indices=idx, state_pool=pool,
           elapsed_state_pool=elapsed, decay_bias=bias, scale=0.5, y=y, final_pool=final)
 
     # ---- chunk_bf16: ragged tail, bf16 state pool

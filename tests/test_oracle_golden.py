@@ -148,6 +148,19 @@ def test_fp16_state_contract_with_dither(oracle):
     assert (torch.from_numpy(shifted["state_pool"]) != want_state).float().mean().item() > 1e-2
 
 
+def test_fp16_state_contract_head_size_128(oracle):
+    """The same contract at head size 128 (the dither phase runs over head * 128 + channel)."""
+    g = load_golden("recurrent_fp16state_d128")
+    out = oracle.forward_fp16(*(g[n] for n in TOKENS), state_pool=g["state_pool"],
+                              elapsed_state_pool=g["elapsed_state_pool"], cu_seqlens=g["cu_seqlens"],
+                              state_indices=g["state_indices"], scale=g["scale"], decay_bias=g["decay_bias"])
+    got_state, want_state = torch.from_numpy(out["state_pool"]), g["final_pool"]
+    assert (got_state != want_state).float().mean().item() < 2e-3
+    assert rel_rmse(got_state.float(), want_state.float()) < 2e-4
+    assert rel_rmse(out["y"], g["y"].float()) < 2e-4
+    assert torch.equal(got_state[[1]], g["state_pool"][[1]])
+
+
 def test_layer_norm_family_formulas(oracle):
     g = load_golden("tmix_norm")
     assert rel_rmse(oracle.layer_norm(g["x"], g["weight"], g["bias"]), g["ln_x"]) < 1e-5

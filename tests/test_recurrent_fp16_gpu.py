@@ -26,10 +26,11 @@ def _mismatch(actual: torch.Tensor, expected: torch.Tensor):
     return float((a != e).float().mean()), float((a - e).abs().max() / e.abs().max())
 
 
-def test_golden_vectors_from_reference_fp16_oracle():
+@pytest.mark.parametrize("name", ["recurrent_fp16state", "recurrent_fp16state_d128"])
+def test_golden_vectors_from_reference_fp16_oracle(name):
     import flashrwkv_b200 as F
 
-    g = load_golden("recurrent_fp16state")
+    g = load_golden(name)
     toks = [g[n].cuda() for n in TOKENS]
     pool = g["state_pool"].cuda().clone()
     elapsed = g["elapsed_state_pool"].cuda()
@@ -109,6 +110,41 @@ def test_ragged_sequences_vs_oracle(oracle):
     torch.cuda.synchronize()
     assert rel_rmse(y.float().cpu(), out["y"]) <= REF_RMSE
     assert rel_rmse(d_pool.float().cpu(), torch.from_numpy(out["state_pool"]).float()) <= REF_RMSE
+
+
+@pytest.mark.parametrize("head_size", [128, 256])
+@pytest.mark.parametrize("lengths", [(1,), (1, 2, 4), (8, 8), (33, 1, 7)])
+def test_wide_heads_vs_oracle(oracle, head_size, lengths):
+    """Head sizes 128 and 256 (the reference's fp16 family test runs these, tests/tmix/wkv7/test.py:1003-1060):
+    decay bias, a scale, scattered slots, non-zero elapsed counters; untouched slots stay bit-identical."""
+    import flashrwkv_b200 as F
+
+    D, H, slots = head_size, 2, len(lengths) + 2
+    N = sum(lengths)
+    gen = torch.Generator().manual_seed(500 + head_size + N)
+    rnd = lambda s: (torch.randn(N, H, D, generator=gen) * s).half()  # noqa: E731
+    toks = [rnd(0.1), rnd(3.0), rnd(0.05), rnd(0.05), rnd(0.05), rnd(0.05)]
+    bias = (torch.randn(H, D, generator=gen) * 0.5).half()
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lengths)]), dtype=torch.int32)
+    idx = torch.randperm(slots, generator=gen)[:len(lengths)].to(torch.int32)
+    pool = (torch.randn(slots, H, D, D, generator=gen) * 0.03).half()
+    elapsed = torch.arange(slots, dtype=torch.int32) * 7 + 3
+    d_pool, d_elapsed = pool.cuda(), elapsed.cuda()
+    y = F.infer_recurrent_fp16_forward_varlen(*[t.cuda() for t in toks], state_pool=d_pool,
+                                              elapsed_state_pool=d_elapsed, cu_seqlens=cu.cuda(),
+                                              state_indices=idx.cuda(), scale=0.5, decay_bias=bias.cuda())
+    out = oracle.forward_fp16(*toks, state_pool=pool, elapsed_state_pool=elapsed, cu_seqlens=cu, state_indices=idx,
+                              scale=0.5, decay_bias=bias)
+    torch.cuda.synchronize()
+    want_pool = torch.from_numpy(out["state_pool"])
+    assert torch.isfinite(y.float()).all()
+    assert rel_rmse(y.float().cpu(), out["y"]) <= REF_RMSE
+    assert rel_rmse(d_pool.float().cpu(), want_pool.float()) <= REF_RMSE
+    frac, worst = _mismatch(d_pool, want_pool)
+    assert frac <= 5e-3 and worst <= 2e-3, (frac, worst)
+    untouched = [i for i in range(slots) if i not in set(idx.tolist())]
+    assert torch.equal(d_pool[untouched].cpu(), pool[untouched])
+    assert torch.equal(d_elapsed.cpu(), elapsed)  # the counters are read only
 
 
 def test_elapsed_counter_operators_and_fail_closed():
