@@ -8,6 +8,7 @@ include/frwkv_b200.h.  There is no CPU fallback.
 from .rl_infctx.wkv7 import rl_infctx_chunk_fp32io16, rl_infctx_chunk_fp32io16_factor_recompute
 from .tmix.wkv7 import (
     infer_chunk_bf16_forward_varlen,
+    infer_recurrent_add_vec_forward_varlen,
     infer_recurrent_fp16_advance_i32,
     infer_recurrent_fp16_advance_i32_varlen,
     infer_recurrent_fp16_forward_varlen,
@@ -44,6 +45,7 @@ __all__ = [
     "infer_tmix_vres_gate_forward_varlen",
     *_linear_all,
     "infer_chunk_bf16_forward_varlen",
+    "infer_recurrent_add_vec_forward_varlen",
     "infer_recurrent_fp16_advance_i32",
     "infer_recurrent_fp16_advance_i32_varlen",
     "infer_recurrent_fp16_forward_varlen",

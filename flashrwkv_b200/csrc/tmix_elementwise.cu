@@ -199,6 +199,22 @@ __global__ void lnx_rkvres_xg_kernel(const io_t* __restrict__ x, const io_t* __r
   }
 }
 
+// out = x + vec (fp32 sum, one rounding): one 4-byte pair per thread and step, row index from the grid-stride counter
+// so that any even channel count works (the recurrence's pre-add-vector helper; replaces recurrent_add_vec_kernel,
+// csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu:83-124).
+template <typename io_t>
+__global__ void add_vec_kernel(const io_t* __restrict__ x, const io_t* __restrict__ vec, io_t* __restrict__ out,
+                               long long pair_total, int pairs_per_row) {
+  using IO = Io16<io_t>;
+  chain_begin();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < pair_total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float2 a = IO::unpack(reinterpret_cast<const uint32_t*>(x)[i]);
+    const float2 b = IO::unpack(__ldg(reinterpret_cast<const uint32_t*>(vec) + (i % pairs_per_row)));
+    reinterpret_cast<uint32_t*>(out)[i] = IO::pack(a.x + b.x, a.y + b.y);
+  }
+}
+
 template <typename io_t>
 __global__ void vres_gate_kernel(const io_t* __restrict__ v, const io_t* __restrict__ v_first,
                                  const io_t* __restrict__ v0, const io_t* __restrict__ v12, io_t* __restrict__ out,
@@ -364,6 +380,24 @@ extern "C" int frwkv_tmix_vres_gate_forward_varlen(const void* v, const void* v_
         static_cast<const io_t*>(v), static_cast<const io_t*>(v_first), static_cast<const io_t*>(v0),
         static_cast<const io_t*>(v12), static_cast<io_t*>(out), vec_total, channels / 8);
     return check_launch("vres_gate_kernel");
+  })
+}
+
+extern "C" int frwkv_recurrent_add_vec_forward(const void* x, const void* vec, void* out, long long total_rows,
+                                               int channels, int io_dtype, frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(x && vec && out, "recurrent_add_vec: null pointer argument");
+  FRWKV_REQUIRE(total_rows > 0 && channels > 0 && channels % 2 == 0,
+                "recurrent_add_vec: x must have packed shape [total_tokens,C] with even C");
+  const long long pair_total = total_rows * (channels / 2);
+  long long blocks = (pair_total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  FRWKV_DISPATCH_IO(io_dtype, "recurrent_add_vec", {
+    launch_chained(add_vec_kernel<io_t>, dim3((unsigned)blocks), dim3(256), 0, s, static_cast<const io_t*>(x),
+                   static_cast<const io_t*>(vec), static_cast<io_t*>(out), pair_total, channels / 2);
+    return check_launch("add_vec_kernel");
   })
 }
 

@@ -750,6 +750,19 @@ torch::Tensor tmix_vres_gate_forward_varlen(torch::Tensor v, torch::Tensor v_fir
   return out;
 }
 
+torch::Tensor recurrent_add_vec_forward_varlen(torch::Tensor x, torch::Tensor vec) {
+  check_io16(x, "x", x);
+  check_io16(vec, "vec", x);
+  TORCH_CHECK(x.dim() == 2 && x.size(0) > 0 && x.size(1) > 0 && (x.size(1) % 2) == 0,
+              "x must have packed shape [total_tokens,C] with even C");
+  TORCH_CHECK(vec.dim() == 1 && vec.size(0) == x.size(1), "vec must have shape [C]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto out = torch::empty_like(x);
+  check_rc(frwkv_recurrent_add_vec_forward(x.data_ptr(), vec.data_ptr(), out.data_ptr(), x.size(0),
+                                           static_cast<int>(x.size(1)), io_dtype_of(x), current_stream(x)));
+  return out;
+}
+
 torch::Tensor tmix_act_forward(torch::Tensor x, int64_t act) {
   check_io16(x, "x", x);
   TORCH_CHECK(x.numel() > 0 && x.numel() % 8 == 0, "x must have a positive element count that is a multiple of 8");
@@ -1262,6 +1275,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("pretrain_tmix_kk_pre_backward", &pretrain_tmix_kk_pre_backward);
   m.def("pretrain_tmix_lnx_rkvres_xg_forward", &pretrain_tmix_lnx_rkvres_xg_forward);
   m.def("pretrain_tmix_lnx_rkvres_xg_backward", &pretrain_tmix_lnx_rkvres_xg_backward);
+  m.def("recurrent_add_vec_forward_varlen", &recurrent_add_vec_forward_varlen, py::arg("x"), py::arg("vec"));
   m.def("tmix_act_forward", &tmix_act_forward, py::arg("x"), py::arg("act"));
   m.def("tmix_linear_grouped", &tmix_linear_grouped, py::arg("xs"), py::arg("weights"), py::arg("acts"),
         py::arg("vres") = py::none());

@@ -100,6 +100,25 @@ def _validate_elapsed(elapsed, name: str) -> None:
         raise ValueError(f"{name} must be contiguous CUDA int32")
 
 
+def infer_recurrent_add_vec_forward_varlen(x, vec):
+    """`x [total_tokens,C] + vec [C]` with one rounding (the recurrence's pre-add-vector helper).  Mirror of
+    `flashrwkv2/tmix/wkv7/__init__.py:133-151`: fp16 as there, bf16 in addition."""
+    for name, tensor in (("x", x), ("vec", vec)):
+        if not isinstance(tensor, torch.Tensor):
+            raise TypeError(f"{name} must be a torch.Tensor")
+        if tensor.dtype not in (torch.float16, torch.bfloat16) or tensor.dtype != x.dtype:
+            raise TypeError(f"{name} must have dtype torch.float16 (or both torch.bfloat16)")
+        if not tensor.is_cuda or not tensor.is_contiguous():
+            raise ValueError(f"{name} must be contiguous CUDA float16")
+        if tensor.device != x.device:
+            raise ValueError(f"{name} must share x's device")
+    if x.ndim != 2 or x.shape[0] <= 0 or x.shape[1] <= 0 or x.shape[1] % 2:
+        raise ValueError("x must have packed shape [total_tokens,C] with even C")
+    if vec.shape != (x.shape[1],):
+        raise ValueError("vec must have shape [C]")
+    return extension().recurrent_add_vec_forward_varlen(x, vec)
+
+
 def infer_recurrent_fp16_advance_i32(elapsed_state, amount: int) -> None:
     """Add ``amount`` to every elapsed (dither phase) counter, in place."""
     _validate_elapsed(elapsed_state, "elapsed_state")
@@ -173,7 +192,7 @@ def infer_recurrent_fp16_forward_varlen(r, decay_logits, k, v, a, b, *, state_po
 
 __all__ = ["infer_recurrent_fp32io16_forward_varlen", "prepare_recurrent_metadata",
            "infer_recurrent_fp16_forward_varlen", "infer_recurrent_fp16_advance_i32",
-           "infer_recurrent_fp16_advance_i32_varlen"]
+           "infer_recurrent_fp16_advance_i32_varlen", "infer_recurrent_add_vec_forward_varlen"]
 
 from .chunk import infer_chunk_bf16_forward_varlen, make_chunk_metadata, wkv7_chunk_forward  # noqa: E402
 

@@ -306,6 +306,11 @@ typedef struct {
 int frwkv_tmix_linear_grouped(const frwkv_linear_problem* problems, int count, int m, int io_dtype,
                               int32_t* error_flag, frwkv_stream_t stream);
 
+/* out = x + vec; x, out io16 [total_rows][channels], vec io16 [channels], channels even.  Replaces
+ * recurrent_add_vec_forward_varlen_cuda (csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu:1247-1290). */
+int frwkv_recurrent_add_vec_forward(const void* x, const void* vec, void* out, long long total_rows, int channels,
+                                    int io_dtype, frwkv_stream_t stream);
+
 /*
  * ---- Training-side TMix glue on dense [B, T, C] tensors (rows = B * T), forward and backward ----------------------
  * io16 tensors are bf16 in the reference (io_dtype FRWKV_DTYPE_BF16); fp16 is accepted too.  channels must be a

@@ -147,6 +147,21 @@ def test_wide_heads_vs_oracle(oracle, head_size, lengths):
     assert torch.equal(d_elapsed.cpu(), elapsed)  # the counters are read only
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_add_vec_helper_is_the_rounded_fp32_sum(dtype):
+    """Shapes of the reference's test (tests/tmix/wkv7/test.py:131-138) plus an even channel count that is not a
+    multiple of 8; bit-exact."""
+    import flashrwkv_b200 as F
+
+    for rows, channels in ((3, 8), (17, 4096), (5, 70)):
+        x = torch.randn(rows, channels, device="cuda").to(dtype)
+        vec = torch.randn(channels, device="cuda").to(dtype)
+        out = F.infer_recurrent_add_vec_forward_varlen(x, vec)
+        assert torch.equal(out, (x.float() + vec.float()).to(dtype))
+    with pytest.raises(ValueError, match="even C"):
+        F.infer_recurrent_add_vec_forward_varlen(x[:, :69].contiguous(), vec[:69].contiguous())
+
+
 def test_elapsed_counter_operators_and_fail_closed():
     import flashrwkv_b200 as F
 
