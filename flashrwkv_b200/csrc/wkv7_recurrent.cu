@@ -48,37 +48,39 @@ struct StepOut {
 
 // One token of the recurrence on this lane's 16 x 4 piece of the state (rows row0.., columns col0..); tb is the
 // element offset of (token, head) in the packed token tensors.  Returns the complete (all key rows) sums.
-template <typename io_t>
+// kNeedOutput = false (the training-side replay) leaves out r and everything that only the output needs.
+template <typename io_t, bool kNeedOutput>
 __device__ __forceinline__ StepOut token_step(float4 (&s)[16], const io_t* __restrict__ r_ptr,
                                               const io_t* __restrict__ w_ptr, const io_t* __restrict__ k_ptr,
                                               const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr,
                                               const io_t* __restrict__ b_ptr, const io_t* __restrict__ bias_ptr,
                                               long long tb, int head, int row0, int col0, float scale) {
   using IO = Io16<io_t>;
-  uint32_t rr[8], ww[8], kk[8], aa[8], bb[8];
-  load16(w_ptr + tb + row0, ww);
+  const int lane = threadIdx.x & 31;
+  uint32_t rr[8], kk[8], aa[8], bb[8];
+  // retention of this lane group's 16 key rows: each of the eight lanes that share the rows computes two of them and
+  // the group exchanges them by shuffle (three special-function instructions per value: all sixteen on every lane
+  // would make that unit, not the FMAs, the limit of the step)
+  const int vq = lane & 7;
+  float2 wx = IO::unpack(__ldg(reinterpret_cast<const uint32_t*>(w_ptr + tb + row0 + 2 * vq)));
   load16(a_ptr + tb + row0, aa);
-  load16(r_ptr + tb + row0, rr);
+  if (kNeedOutput) load16(r_ptr + tb + row0, rr);
   load16(b_ptr + tb + row0, bb);
   load16(k_ptr + tb + row0, kk);
   const uint2 vraw = __ldg(reinterpret_cast<const uint2*>(v_ptr + tb + col0));
 
   float wv[16];
-  if (bias_ptr != nullptr) {
-    uint32_t bs[8];
-    load16(bias_ptr + head * kD + row0, bs);
-#pragma unroll
-    for (int p = 0; p < 8; ++p) {
-      const float2 x = IO::unpack(ww[p]), bx = IO::unpack(bs[p]);
-      wv[2 * p] = retention(x.x + bx.x);
-      wv[2 * p + 1] = retention(x.y + bx.y);
+  {
+    if (bias_ptr != nullptr) {
+      const float2 bx = IO::unpack(__ldg(reinterpret_cast<const uint32_t*>(bias_ptr + head * kD + row0 + 2 * vq)));
+      wx.x += bx.x;
+      wx.y += bx.y;
     }
-  } else {
+    const float w_lo = retention(wx.x), w_hi = retention(wx.y);
 #pragma unroll
     for (int p = 0; p < 8; ++p) {
-      const float2 x = IO::unpack(ww[p]);
-      wv[2 * p] = retention(x.x);
-      wv[2 * p + 1] = retention(x.y);
+      wv[2 * p] = __shfl_sync(0xffffffffu, w_lo, (lane & 24) + p);
+      wv[2 * p + 1] = __shfl_sync(0xffffffffu, w_hi, (lane & 24) + p);
     }
   }
 
@@ -87,27 +89,35 @@ __device__ __forceinline__ StepOut token_step(float4 (&s)[16], const io_t* __res
   float br = 0.f, kr = 0.f;
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
-    const float2 a2 = IO::unpack(aa[p]), r2 = IO::unpack(rr[p]);
-    const float2 b2 = IO::unpack(bb[p]), k2 = IO::unpack(kk[p]);
-    br = fmaf(b2.x, r2.x, br);
-    br = fmaf(b2.y, r2.y, br);
-    kr = fmaf(k2.x, r2.x, kr);
-    kr = fmaf(k2.y, r2.y, kr);
+    const float2 a2 = IO::unpack(aa[p]);
+    float2 r2 = make_float2(0.f, 0.f);
+    if (kNeedOutput) {
+      r2 = IO::unpack(rr[p]);
+      const float2 b2 = IO::unpack(bb[p]), k2 = IO::unpack(kk[p]);
+      br = fmaf(b2.x, r2.x, br);
+      br = fmaf(b2.y, r2.y, br);
+      kr = fmaf(k2.x, r2.x, kr);
+      kr = fmaf(k2.y, r2.y, kr);
+    }
     {
       const float4 q = s[2 * p];
-      const float wr = wv[2 * p] * r2.x;
       sa0 = fmaf(a2.x, q.x, sa0); sa1 = fmaf(a2.x, q.y, sa1);
       sa2 = fmaf(a2.x, q.z, sa2); sa3 = fmaf(a2.x, q.w, sa3);
-      y0 = fmaf(wr, q.x, y0); y1 = fmaf(wr, q.y, y1);
-      y2 = fmaf(wr, q.z, y2); y3 = fmaf(wr, q.w, y3);
+      if (kNeedOutput) {
+        const float wr = wv[2 * p] * r2.x;
+        y0 = fmaf(wr, q.x, y0); y1 = fmaf(wr, q.y, y1);
+        y2 = fmaf(wr, q.z, y2); y3 = fmaf(wr, q.w, y3);
+      }
     }
     {
       const float4 q = s[2 * p + 1];
-      const float wr = wv[2 * p + 1] * r2.y;
       sa0 = fmaf(a2.y, q.x, sa0); sa1 = fmaf(a2.y, q.y, sa1);
       sa2 = fmaf(a2.y, q.z, sa2); sa3 = fmaf(a2.y, q.w, sa3);
-      y0 = fmaf(wr, q.x, y0); y1 = fmaf(wr, q.y, y1);
-      y2 = fmaf(wr, q.z, y2); y3 = fmaf(wr, q.w, y3);
+      if (kNeedOutput) {
+        const float wr = wv[2 * p + 1] * r2.y;
+        y0 = fmaf(wr, q.x, y0); y1 = fmaf(wr, q.y, y1);
+        y2 = fmaf(wr, q.z, y2); y3 = fmaf(wr, q.w, y3);
+      }
     }
   }
   // finish the key-direction sums across the four row groups (lane bits 3 and 4)
@@ -115,9 +125,11 @@ __device__ __forceinline__ StepOut token_step(float4 (&s)[16], const io_t* __res
   for (int m = 8; m <= 16; m <<= 1) {
     sa0 += __shfl_xor_sync(0xffffffffu, sa0, m); sa1 += __shfl_xor_sync(0xffffffffu, sa1, m);
     sa2 += __shfl_xor_sync(0xffffffffu, sa2, m); sa3 += __shfl_xor_sync(0xffffffffu, sa3, m);
-    y0 += __shfl_xor_sync(0xffffffffu, y0, m); y1 += __shfl_xor_sync(0xffffffffu, y1, m);
-    y2 += __shfl_xor_sync(0xffffffffu, y2, m); y3 += __shfl_xor_sync(0xffffffffu, y3, m);
-    br += __shfl_xor_sync(0xffffffffu, br, m); kr += __shfl_xor_sync(0xffffffffu, kr, m);
+    if (kNeedOutput) {
+      y0 += __shfl_xor_sync(0xffffffffu, y0, m); y1 += __shfl_xor_sync(0xffffffffu, y1, m);
+      y2 += __shfl_xor_sync(0xffffffffu, y2, m); y3 += __shfl_xor_sync(0xffffffffu, y3, m);
+      br += __shfl_xor_sync(0xffffffffu, br, m); kr += __shfl_xor_sync(0xffffffffu, kr, m);
+    }
   }
   const float2 v01 = IO::unpack(vraw.x), v23 = IO::unpack(vraw.y);
 
@@ -199,7 +211,7 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
 
   for (int t = t_begin; t < t_end; ++t) {
     const long long tb = ((long long)t * num_heads + head) * kD;
-    const StepOut st = token_step<io_t>(s, r_ptr, w_ptr, k_ptr, v_ptr, a_ptr, b_ptr, bias_ptr, tb, head, row0, col0, scale);
+    const StepOut st = token_step<io_t, !kReplay>(s, r_ptr, w_ptr, k_ptr, v_ptr, a_ptr, b_ptr, bias_ptr, tb, head, row0, col0, scale);
     if (kReplay) {
       if (kg == 0) *reinterpret_cast<float4*>(sa_ptr + tb + col0) = make_float4(st.sa0, st.sa1, st.sa2, st.sa3);
       const int done = t - t_begin + 1;
