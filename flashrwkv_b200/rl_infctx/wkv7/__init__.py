@@ -1,7 +1,8 @@
 """RL / infinite-context chunk operators (fp32 state, new pool returned, input pool untouched).
 
 Mirror of the reference's `flashrwkv2/rl_infctx/wkv7/__init__.py:66-159`.  Both strategies of the reference
-("materialized" and "recompute") are served by the same tensor-core build + scan kernels; head size 64.
+("materialized" and "recompute") are served by the same tensor-core build + scan kernels at head size 64, and by
+the general recurrence kernel at head sizes 128 and 256.
 """
 from __future__ import annotations
 
@@ -81,6 +82,16 @@ def rl_infctx_chunk_fp32io16(r, decay_logits, k, v, a, b, *, state_pool=None, cu
         raise ValueError("state_pool must have shape [slots,H,D,D]")
     if max(indices_cpu, default=-1) >= state_pool.shape[0] or min(indices_cpu, default=0) < 0:
         raise ValueError("state_indices must be within state_pool")
+    if r.shape[2] != 64:
+        # head sizes 128 and 256: the chunking is an evaluation order, not part of the result, so the general
+        # recurrence kernel on a copy of the pool gives the same (output, new pool)
+        from ...tmix.wkv7 import infer_recurrent_fp32io16_forward_varlen
+
+        final_pool = state_pool.clone()
+        output = infer_recurrent_fp32io16_forward_varlen(r, decay_logits, k, v, a, b, state_pool=final_pool,
+                                                         cu_seqlens=cu_seqlens, state_indices=state_indices,
+                                                         scale=float(scale), decay_bias=decay_bias)
+        return output, final_pool
     # the tensor-core kernels work on tiles of up to 64 tokens whatever chunk_size the caller names: the
     # chunking is an evaluation order, not part of the result
     chunk_metadata = make_chunk_metadata(cu_seqlens, 64)

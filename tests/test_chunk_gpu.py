@@ -72,6 +72,36 @@ def test_golden_rl_fp16_new_pool_returned_input_untouched():
                                    state_indices=torch.tensor([1, 1], dtype=torch.int32, device="cuda"))
 
 
+@pytest.mark.parametrize("d", [128, 256])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_rl_wide_heads_vs_oracle(oracle, d, dtype):
+    """Head sizes 128 / 256 of the RL operator (shapes and bounds of the reference's tests,
+    tests/rl_infctx/wkv7/test.py:83-135 and :138-190): ragged lengths, scattered slots, decay bias, a 65-token tail."""
+    import flashrwkv_b200 as F
+
+    gen = torch.Generator().manual_seed(37 + d)
+    for lengths, slots_of in (((2, 5), [3, 1]), ((65,), [1])):
+        total, h = sum(lengths), 1
+        toks = [(torch.randn(total, h, d, generator=gen) * 0.01).to(dtype) for _ in range(6)]
+        pool = torch.randn(4, h, d, d, generator=gen) * 0.01
+        cu = torch.tensor([0, *torch.tensor(lengths).cumsum(0).tolist()], dtype=torch.int32)
+        idx = torch.tensor(slots_of, dtype=torch.int32)
+        bias = (torch.randn(h, d, generator=gen) * 0.01).to(dtype)
+        want = oracle.forward(*toks, state_pool=pool, cu_seqlens=cu, state_indices=idx, decay_bias=bias)
+        d_pool = pool.cuda()
+        for strategy in ("materialized", "recompute"):
+            y, new_pool = F.rl_infctx_chunk_fp32io16(*[t.cuda() for t in toks], state_pool=d_pool, cu_seqlens=cu.cuda(),
+                                                     state_indices=idx.cuda(), chunk_size=16, strategy=strategy,
+                                                     decay_bias=bias.cuda())
+            torch.cuda.synchronize()
+            assert y.dtype == dtype and y.shape == toks[3].shape
+            assert torch.allclose(y.float().cpu(), torch.as_tensor(want["y"]).float(), rtol=0.0, atol=2e-3)
+            assert torch.allclose(new_pool.cpu(), torch.as_tensor(want["state_pool"]), rtol=0.0, atol=2e-3)
+            untouched = [s for s in range(4) if s not in slots_of]
+            assert torch.equal(new_pool[untouched].cpu(), pool[untouched])
+            assert torch.equal(d_pool.cpu(), pool)
+
+
 @pytest.mark.parametrize("lengths", [(512, 512), (1, 15, 16, 17, 65, 130, 64, 63)])
 def test_chunked_vs_oracle_and_recurrent(oracle, lengths):
     import flashrwkv_b200 as F
