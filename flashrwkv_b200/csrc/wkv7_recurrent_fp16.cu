@@ -20,6 +20,8 @@
 // Replaces the reference's fp16-state family (csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu; contract
 // restated by rwkv7_fp16_reference, tests/tmix/wkv7/test.py:216-277, and docs/kernel_api.md:85-91,109-123).
 
+#include <cstdlib>
+
 #include "frwkv_common.cuh"
 #include "umma.cuh"
 
@@ -208,8 +210,8 @@ struct RingCfg {
   static constexpr int kStageBytes = kT * (kTileBytes + kTokBytes);
   static constexpr int kSmem = kStages * kStageBytes;  // 215,040
   // a consumer pair's first unit must find its stage in the stage's first phase (a wait for the second fill of a
-  // fresh barrier returns at once)
-  static_assert(kStages >= 7, "no more consumer pairs than stages");
+  // fresh barrier returns at once): no more pairs work than there are stages
+  static constexpr int kActivePairs = kStages < kConsumerPairs ? kStages : kConsumerPairs;
 };
 
 __device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
@@ -315,7 +317,7 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_fp16_decode_kernel(
     const int pair = (warp - 2) >> 1, vhalf = (warp - 2) & 1;
     const int kg = lane >> 3, vq = lane & 7;
     const int row0 = kg * 16, col0 = vhalf * 32 + vq * 4;
-    for (int i = pair; i < my_units && ok; i += kConsumerPairs) {
+    for (int i = pair < R::kActivePairs ? pair : my_units; i < my_units && ok; i += R::kActivePairs) {
       const int st = i % kStages;
       const int unit = unit_of(i);
       const int seq = unit / units_per_seq, head0 = kT * (unit % units_per_seq);
@@ -387,7 +389,11 @@ int launch_fp16(const int* cu, const int* idx, const int* status, const int* ela
         static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), units, num_heads,     \
         out_elems, scale, reverse, nullptr);                                                                      \
   }
-    if (num_heads % 2 == 0) FRWKV_FP16_DECODE(2) else FRWKV_FP16_DECODE(1)
+    // diagnostic switch FRWKV_FP16_DECODE_TILES=4: four adjacent heads per stage (32 KB copies, six stages)
+    static const bool four = [] { const char* e = getenv("FRWKV_FP16_DECODE_TILES"); return e && e[0] == '4'; }();
+    if (four && num_heads % 4 == 0) FRWKV_FP16_DECODE(4)
+    else if (num_heads % 2 == 0) FRWKV_FP16_DECODE(2)
+    else FRWKV_FP16_DECODE(1)
 #undef FRWKV_FP16_DECODE
     return check_launch("wkv7_fp16_decode_kernel");
   }
