@@ -146,6 +146,13 @@ __global__ __launch_bounds__(256) void reduce_partials_kernel(const float* __res
 }
 
 // ---- a_gate --------------------------------------------------------------------------------------------------------
+// Rows whose loads a lane of the a_gate kernels keeps in flight together.  Measured at B=8, T=4096, C=4096 (forward /
+// backward): 2 rows 100 / 162 us, 4 rows 100 / 213 us (the registers of four rows cost the backward three of its seven
+// CTAs per SM).
+#ifndef FRWKV_GATE_ROWS
+#define FRWKV_GATE_ROWS 2
+#endif
+constexpr int kGateRows = FRWKV_GATE_ROWS;
 template <typename io_t>
 __global__ __launch_bounds__(kThreads) void a_gate_forward_kernel(const io_t* __restrict__ a0,
                                                                   const io_t* __restrict__ a12, io_t* __restrict__ out,
@@ -154,18 +161,19 @@ __global__ __launch_bounds__(kThreads) void a_gate_forward_kernel(const io_t* __
   if (!w.active) return;
   float z0[8];
   load8(a0 + w.col, z0);
-  for (long long row = w.row_begin; row < w.row_end; row += 2) {  // two rows' loads in flight together
+  for (long long row = w.row_begin; row < w.row_end; row += kGateRows) {  // kGateRows rows' loads in flight together
     const long long at = row * channels + w.col;
-    const bool second = row + 1 < w.row_end;
-    float t[2][8];
-    load8(a12 + at, t[0]);
-    if (second) load8(a12 + at + channels, t[1]);
+    float t[kGateRows][8];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      if (u == 1 && !second) break;
+    for (int u = 0; u < kGateRows; ++u)
+      if (row + u < w.row_end) load8(a12 + at + u * (long long)channels, t[u]);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) t[u][e] = sigmoidf_(z0[e] + t[u][e]);
-      store8(out + at + u * (long long)channels, t[u]);
+    for (int u = 0; u < kGateRows; ++u) {
+      if (row + u < w.row_end) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) t[u][e] = sigmoidf_(z0[e] + t[u][e]);
+        store8(out + at + u * (long long)channels, t[u]);
+      }
     }
   }
 }
@@ -183,26 +191,27 @@ __global__ __launch_bounds__(kThreads) void a_gate_backward_kernel(const io_t* _
   if (w.active) {
     float z0[8];
     load8(a0 + w.col, z0);
-    for (long long row = w.row_begin; row < w.row_end; row += 2) {  // two rows' loads in flight together
+    for (long long row = w.row_begin; row < w.row_end; row += kGateRows) {  // kGateRows rows' loads in flight together
       const long long at = row * channels + w.col;
-      const bool second = row + 1 < w.row_end;
-      float z[2][8], g[2][8];
-      load8(a12 + at, z[0]);
-      load8(grad_out + at, g[0]);
-      if (second) {
-        load8(a12 + at + channels, z[1]);
-        load8(grad_out + at + channels, g[1]);
+      float z[kGateRows][8], g[kGateRows][8];
+#pragma unroll
+      for (int u = 0; u < kGateRows; ++u) {
+        if (row + u < w.row_end) {
+          load8(a12 + at + u * (long long)channels, z[u]);
+          load8(grad_out + at + u * (long long)channels, g[u]);
+        }
       }
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        if (u == 1 && !second) break;
+      for (int u = 0; u < kGateRows; ++u) {
+        if (row + u < w.row_end) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float y = sigmoidf_(z0[e] + z[u][e]);
-          g[u][e] *= y * (1.f - y);
-          acc[0][e] += g[u][e];
+          for (int e = 0; e < 8; ++e) {
+            const float y = sigmoidf_(z0[e] + z[u][e]);
+            g[u][e] *= y * (1.f - y);
+            acc[0][e] += g[u][e];
+          }
+          store8(grad_a12 + at + u * (long long)channels, g[u]);
         }
-        store8(grad_a12 + at + u * (long long)channels, g[u]);
       }
     }
   }
@@ -350,16 +359,18 @@ __global__ __launch_bounds__(kThreads) void mix6_forward_kernel(const io_t* __re
 
 // grad_x[t] = sum_j g_j[t] (1 - m_j) + sum_j g_j[t+1] m_j (second term only inside the sequence);
 // grad_m_j = sum_rows g_j (x[t-1] - x[t]).  mix.in = the six upstream gradients, mix.out = the six mix vectors.
-template <typename io_t>
+// kShift = false (pretrain form) compiles the shift-state pointers away: with them the walk spills and runs a quarter
+// slower.
+template <typename io_t, bool kShift>
 __device__ __forceinline__ void mix6_backward_walk(const io_t* __restrict__ x, const Six& mix,
                                                    io_t* __restrict__ grad_x, float (&dm)[6][8], const Walk& w,
                                                    const MixTable& m_s, long long rows, int seq_len, int channels) {
   float prev[8], carry[8];
   int t = (int)(w.row_begin % seq_len);
   long long b = w.row_begin / seq_len;
-  const io_t* initial = static_cast<const io_t*>(mix.initial);
-  const io_t* grad_final = static_cast<const io_t*>(mix.grad_final);
-  io_t* grad_initial = static_cast<io_t*>(mix.grad_initial);
+  const io_t* initial = kShift ? static_cast<const io_t*>(mix.initial) : nullptr;
+  const io_t* grad_final = kShift ? static_cast<const io_t*>(mix.grad_final) : nullptr;
+  io_t* grad_initial = kShift ? static_cast<io_t*>(mix.grad_initial) : nullptr;
   if (t != 0) load8(x + (w.row_begin - 1) * channels + w.col, prev);
   zero8(carry);
   for (long long row = w.row_begin; row < w.row_end; ++row) {
@@ -417,7 +428,7 @@ __device__ __forceinline__ void mix6_backward_walk(const io_t* __restrict__ x, c
   store8(grad_x + (w.row_end - 1) * channels + w.col, carry);
 }
 
-template <typename io_t, int kMinCtas>
+template <typename io_t, int kMinCtas, bool kShift>
 __global__ __launch_bounds__(kThreads, kMinCtas) void mix6_backward_kernel(const io_t* __restrict__ x, Six mix,
                                                                  io_t* __restrict__ grad_x,
                                                                  float* __restrict__ workspace, long long rows,
@@ -429,7 +440,7 @@ __global__ __launch_bounds__(kThreads, kMinCtas) void mix6_backward_kernel(const
 #pragma unroll
   for (int j = 0; j < 6; ++j) zero8(dm[j]);
   if (w.active && w.row_begin < w.row_end)
-    mix6_backward_walk<io_t>(x, mix, grad_x, dm, w, m_s, rows, seq_len, channels);
+    mix6_backward_walk<io_t, kShift>(x, mix, grad_x, dm, w, m_s, rows, seq_len, channels);
   store_partials<6>(workspace, channels, w, dm);
 }
 
@@ -907,12 +918,19 @@ static int mix6_backward_impl(const void* const* grad_out, const void* grad_fina
     // register budget of the walk: 3 CTAs per SM (168 registers, a few spilled words) or 2 (no spill); diagnostic
     // switch FRWKV_MIX6_BWD_CTAS=2
     static const bool two = [] { const char* e = getenv("FRWKV_MIX6_BWD_CTAS"); return e && e[0] == '2'; }();
-    if (two)
-      plan = launch_walk(mix6_backward_kernel<io_t, 2>, rows, channels, s, 
-        CP(io_t, x), six, P(io_t, grad_x), workspace, rows, seq_len, channels);
+    const bool shift = initial != nullptr;  // StateTune form
+    if (two && shift)
+      plan = launch_walk(mix6_backward_kernel<io_t, 2, true>, rows, channels, s, CP(io_t, x), six, P(io_t, grad_x),
+                         workspace, rows, seq_len, channels);
+    else if (two)
+      plan = launch_walk(mix6_backward_kernel<io_t, 2, false>, rows, channels, s, CP(io_t, x), six, P(io_t, grad_x),
+                         workspace, rows, seq_len, channels);
+    else if (shift)
+      plan = launch_walk(mix6_backward_kernel<io_t, 3, true>, rows, channels, s, CP(io_t, x), six, P(io_t, grad_x),
+                         workspace, rows, seq_len, channels);
     else
-      plan = launch_walk(mix6_backward_kernel<io_t, 3>, rows, channels, s, 
-        CP(io_t, x), six, P(io_t, grad_x), workspace, rows, seq_len, channels);
+      plan = launch_walk(mix6_backward_kernel<io_t, 3, false>, rows, channels, s, CP(io_t, x), six, P(io_t, grad_x),
+                         workspace, rows, seq_len, channels);
     if (int rc = check_launch("mix6_backward_kernel")) return rc;
     return reduce_partials<io_t>(workspace, targets, plan, channels, 6, s);
   })
