@@ -31,8 +31,8 @@ CUDA_SOURCES = [
     "wkv7_recurrent.cu",
     "wkv7_recurrent_fp16.cu",
     "wkv7_recurrent_wide.cu",
-    "umma_selftest.cu",
     "wkv7_chunk_fwd.cu",
+    "wkv7_chunk_fused.cu",
     "tmix_elementwise.cu",
     "tmix_norm.cu",
     "tmix_train.cu",

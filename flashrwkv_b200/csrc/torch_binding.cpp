@@ -375,14 +375,18 @@ void check_chunk_tables(const torch::Tensor& sco, const torch::Tensor& cs, const
   TORCH_CHECK(cs.numel() > 0 && cs.numel() == ce.numel(), "chunk_token_starts and chunk_token_ends must have shape [Cn]");
 }
 
-// Runs build + scan.  `state` [slots,H,64,64] fp32 is updated in place (slot = state_indices[s], or s when
+// Chunked forward.  `state` [slots,H,64,64] fp32 is updated in place (slot = state_indices[s], or s when
 // state_indices is None).  Returns the device error flag (int32[1]; non-zero = a tensor-core wait ran out).
+// `path`: 0 = build + scan kernels with a workspace, 1 = the fused single kernel, -1 = whichever
+// frwkv_wkv7_chunk_prefers_fused picks for the batch.  `state_dot_a` (fp32 [N,H,64]) is written by the fused
+// kernel only, so asking for it selects that kernel.
 torch::Tensor wkv7_chunk_forward(torch::Tensor sco, torch::Tensor cs, torch::Tensor ce, torch::Tensor state,
                                  torch::Tensor r, torch::Tensor w, torch::Tensor k, torch::Tensor v, torch::Tensor a,
                                  torch::Tensor b, torch::Tensor output, double scale,
                                  std::optional<torch::Tensor> decay_bias, std::optional<torch::Tensor> state_indices,
                                  std::optional<torch::Tensor> boundary, std::optional<torch::Tensor> output_fp32,
-                                 std::optional<torch::Tensor> metadata_status) {
+                                 std::optional<torch::Tensor> metadata_status,
+                                 std::optional<torch::Tensor> state_dot_a, int64_t path) {
   check_chunk_tables(sco, cs, ce, r);
   const std::pair<const torch::Tensor*, const char*> toks[] = {{&r, "r"}, {&w, "decay_logits"}, {&k, "k"},
                                                                {&v, "v"}, {&a, "a"},           {&b, "b"},
@@ -431,10 +435,34 @@ torch::Tensor wkv7_chunk_forward(torch::Tensor sco, torch::Tensor cs, torch::Ten
                     metadata_status->numel() >= 1 && metadata_status->device() == r.device(),
                 "metadata_status must be an int32 CUDA tensor");
   }
+  if (state_dot_a.has_value()) {
+    check_cuda_contiguous(*state_dot_a, "state_dot_a");
+    TORCH_CHECK(state_dot_a->scalar_type() == torch::kFloat32 && state_dot_a->sizes() == r.sizes() &&
+                    state_dot_a->device() == r.device(),
+                "state_dot_a must be a float32 tensor shaped like r");
+  }
+  TORCH_CHECK(path >= -1 && path <= 1, "path must be -1 (automatic), 0 (build + scan) or 1 (fused)");
+  TORCH_CHECK(!(state_dot_a.has_value() && path == 0), "state_dot_a is produced by the fused kernel only");
   const c10::cuda::CUDAGuard guard(r.device());
+  auto error_flag = torch::zeros({1}, r.options().dtype(torch::kInt32));
+  const bool fused = path == 1 || state_dot_a.has_value() ||
+                     (path == -1 && frwkv_wkv7_chunk_prefers_fused(static_cast<int>(B), static_cast<int>(H)) != 0);
+  if (fused) {
+    check_rc(frwkv_wkv7_chunk_fused_fp32io16_forward(
+        sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(),
+        state_indices.has_value() ? state_indices->data_ptr<int>() : nullptr,
+        metadata_status.has_value() ? metadata_status->data_ptr<int>() : nullptr, state.data_ptr<float>(),
+        r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
+        decay_bias.has_value() ? decay_bias->data_ptr() : nullptr, output.data_ptr(),
+        output_fp32.has_value() ? output_fp32->data_ptr<float>() : nullptr,
+        boundary.has_value() ? boundary->data_ptr<float>() : nullptr,
+        state_dot_a.has_value() ? state_dot_a->data_ptr<float>() : nullptr, error_flag.data_ptr<int>(),
+        static_cast<int>(r.size(0)), static_cast<int>(B), static_cast<int>(Cn), static_cast<int>(H), 64,
+        io_dtype_of(r), static_cast<float>(scale), current_stream(r)));
+    return error_flag;
+  }
   const size_t ws_bytes = frwkv_wkv7_chunk_workspace_bytes(static_cast<int>(Cn), static_cast<int>(H));
   auto workspace = torch::empty({static_cast<int64_t>(ws_bytes)}, r.options().dtype(torch::kUInt8));
-  auto error_flag = torch::zeros({1}, r.options().dtype(torch::kInt32));
   check_rc(frwkv_wkv7_chunk_fp32io16_forward(
       sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(),
       state_indices.has_value() ? state_indices->data_ptr<int>() : nullptr,
@@ -459,7 +487,7 @@ std::tuple<torch::Tensor, torch::Tensor> rl_infctx_chunk_fp32io16_forward(
   auto working = state.clone();
   auto output = torch::empty_like(v);
   wkv7_chunk_forward(sco, cs, ce, working, r, w, k, v, a, b, output, scale, decay_bias, std::nullopt, std::nullopt,
-                     std::nullopt, std::nullopt);
+                     std::nullopt, std::nullopt, std::nullopt, -1);
   return {output, working};
 }
 
@@ -1220,7 +1248,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"), py::arg("output"),
         py::arg("scale") = 1.0, py::arg("decay_bias") = py::none(), py::arg("state_indices") = py::none(),
         py::arg("boundary") = py::none(), py::arg("output_fp32") = py::none(),
-        py::arg("metadata_status") = py::none());
+        py::arg("metadata_status") = py::none(), py::arg("state_dot_a") = py::none(), py::arg("path") = -1);
   m.def("rl_infctx_chunk_fp32io16_forward", &rl_infctx_chunk_fp32io16_forward, py::arg("sequence_chunk_offsets"),
         py::arg("chunk_token_starts"), py::arg("chunk_token_ends"), py::arg("state"), py::arg("r"),
         py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"), py::arg("strategy") = 1,

@@ -1,0 +1,704 @@
+// Chunked WKV7 forward as ONE kernel: a CTA owns a (sequence, head) pair, keeps its fp32 state on chip and walks
+// the sequence's chunks (<= 64 tokens, head size 64) in order.  Nothing but the token rows, the outputs and the
+// optional per-chunk boundary states / state_dot_a rows touches HBM: no per-chunk workspace.
+//
+// Per chunk with start state S0 (K x V), tokens t = 0..L-1, cumulative decay g_t = prod_{s<=t} w_s (g_{-1} = 1):
+//     A~ = a*g_{t-1}   R~ = r*g_t   B~ = b/g_t   K~ = k/g_t   B^ = B~*g_L   K^ = K~*g_L              (L x K)
+//     [A_ab | A_ak ; A_rb | A_rk] = [A~ ; R~] [B~ ; K~]^T, masked (strictly lower for A_a*, lower for A_r*)
+//     T  = (I - A_ab)^-1 = I + T'
+//     X  = A~ S0 + A_ak V          U = X + T' X   (rows u_t = S_{t-1}^T a_t, the reference's state_dot_a)
+//     Y  = scale * (R~ S0 + A_rk V + A_rb U)
+//     S' = diag(g_L) (S0 + B~^T U + K~^T V)
+//
+// Tensor memory carries the operands from one product to the next (row i of a matrix = lane i):
+//     XA  (64 columns)  lanes 0..63 A~, lanes 64..127 R~            written with tcgen05.st, operand A of MMA 1 and 2
+//     D1  (128 columns) result of MMA 1; masked and rounded in place; the A_ab block (needed only by the inverse)
+//                       is replaced by B~^T, after MMA 2 the A_ak block by K~^T and the A_rk block by zeros, so that
+//                       D1 as a whole is operand A of MMA 4:  [B~^T | K~^T ; A_rb | 0] [U ; V].  B~^T and K~^T are
+//                       columns of the [B~;K~] tile read back from shared memory by the thread that owns the lane.
+//     DA  (64 columns)  MMA 2: XA S0 + D1[:,64:128] V  = [X ; R~ S0 + A_rk V];  MMA 3 adds [T' ; 0] X  ->  [U ; .]
+//     DC  (= XA's columns, free by then)  MMA 4:  [B~^T U + K~^T V ; A_rb U]
+// All products are tcgen05.mma kind::tf32 with fp32 accumulation; operands are rounded to tf32 (nearest) once.  The
+// B operands contract over tokens or keys that their producers own as rows, so they are written transposed with
+// 4-byte stores into 64-row tiles whose chunk stride (1040 bytes) keeps those stores free of bank conflicts.  The
+// 64 x 64 unit-triangular inverse runs in fp32 on the CUDA cores (16 x 16 blocks, 2 x 4 register tiles).  The state
+// stays in fp32 registers; only its rounded copy is an operand.
+//
+// 256 threads, 105 KB of shared memory and 256 tensor-memory columns per CTA: two CTAs share an SM, so one CTA's
+// barrier-separated phases overlap the other's.  The loop body is kept small on purpose (rolled loops, 16-column
+// tensor-memory transfers): a first version whose body was 170 KB of unrolled code ran five times slower, bound by
+// instruction fetch.
+//
+// Replaces the same reference kernels as wkv7_chunk_fwd.cu (which remains the path for batches with too few
+// (sequence, head) pairs to fill the GPU this way): csrc/sm120/tmix/wkv7/infer_chunk_bf16_forward_varlen.cu:42-266,
+// csrc/sm90/rl_infctx/wkv7/rl_infctx_chunk_fp32io16_forward.cu:317-538, and the forward halves of
+// csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_forward.cu:32-130 (boundary and state_dot_a outputs).
+
+#include "frwkv_common.cuh"
+#include "umma.cuh"
+
+namespace frwkv {
+namespace {
+
+constexpr int kL = 64;
+constexpr int kD = 64;
+constexpr int kThreads = 256;
+constexpr uint32_t kCSB = 2064;   // chunk stride of [B~;K~]  (128 rows, written row-wise, read back column-wise)
+constexpr uint32_t kCST = 2064;   // ... of [T';0]            (128 rows, written column-wise)
+constexpr uint32_t kCS64 = 1040;  // ... of the 64-row transposed tiles and of g
+
+constexpr uint32_t kOffG = 0;                        // g[t][k], chunk-major, 16 x 1040
+constexpr uint32_t kOffX2 = kOffG + 16 * kCS64;      // [B~;K~], later [T';0]
+constexpr uint32_t kOffUV = kOffX2 + 16 * kCST;      // [U^T | V^T]: 32 chunks x 1040; the U half first holds A_ab
+constexpr uint32_t kOffS = kOffUV + 32 * kCS64;      // S0^T
+constexpr uint32_t kOffW = kOffS + 16 * kCS64;       // the chunk's decay logits as they are in HBM: [64][64] 16-bit
+constexpr uint32_t kFusedSmem = kOffW + kL * kD * 2; // 107,776 bytes
+static_assert(kOffX2 % 128 == 0 && kOffUV % 128 == 0 && kOffS % 128 == 0 && kOffW % 128 == 0,
+              "tile bases must stay 128-byte aligned");
+static_assert(64 * 256 <= 16 * kCS64, "the A_ab scratch must fit the U half");
+static_assert(2 * (kFusedSmem + 1024) <= 233472, "two CTAs must fit one SM");
+
+constexpr uint32_t kColXA = 0, kColD1 = 64, kColDA = 192, kColDC = 0, kTmemCols = 256;
+
+__device__ __forceinline__ float4 ld4(const unsigned char* base, uint32_t off) {
+  return *reinterpret_cast<const float4*>(base + off);
+}
+__device__ __forceinline__ float ld1(const unsigned char* base, uint32_t off) {
+  return *reinterpret_cast<const float*>(base + off);
+}
+__device__ __forceinline__ void st4(unsigned char* base, uint32_t off, float4 v) {
+  *reinterpret_cast<float4*>(base + off) = v;
+}
+__device__ __forceinline__ void st1(unsigned char* base, uint32_t off, float v) {
+  *reinterpret_cast<float*>(base + off) = v;
+}
+__device__ __forceinline__ uint32_t tile_off(uint32_t cs, int row, int col) {
+  return uint32_t(col >> 2) * cs + uint32_t(row) * 16 + uint32_t(col & 3) * 4;
+}
+// A_ab scratch: row t is 256 bytes; its 16-byte pieces are permuted by the row pair so that the inverse's threads,
+// which read the same piece of eight different row pairs at once, hit different banks.
+__device__ __forceinline__ uint32_t aab_off(int t, int s4) { return kOffUV + uint32_t(t) * 256 + uint32_t((s4 ^ ((t >> 1) & 7)) * 16); }
+__device__ __forceinline__ float aab(const unsigned char* smem, int t, int s) { return ld1(smem, aab_off(t, s >> 2) + (s & 3) * 4); }
+// T (then T') and the inverse's scratch W share the [T';0] tile: T in rows 0..63, W in rows 64..127
+__device__ __forceinline__ uint32_t t_off(int row, int col) { return kOffX2 + tile_off(kCST, row, col); }
+__device__ __forceinline__ uint32_t w_off(int row, int col) { return kOffX2 + tile_off(kCST, 64 + row, col); }
+
+__device__ __forceinline__ uint32_t tf32_bits(float x) { return __float_as_uint(umma::to_tf32(x)); }
+
+// Bounded wait with one answer per warp: the tensor-memory loads and stores that follow are warp-collective, so a
+// warp either does its epilogue as a whole or skips it as a whole.  Once a wait has run out no later one is tried.
+__device__ __forceinline__ bool wait_warp(uint64_t* mbar, uint32_t parity, bool ok) {
+  if (ok) ok = umma::mbar_wait_suspended(mbar, parity);
+  return __all_sync(0xffffffffu, ok) != 0;
+}
+
+// T' = (I - A)^-1 - I for the strictly lower triangular 64 x 64 A in the scratch, in fp32, by 16 x 16 blocks:
+// T_ii = (I - A_ii)^-1 (one thread per column, 16 right-looking steps), then one block anti-diagonal at a time
+// T_ib = T_ii * sum_{k=b..i-1} A_ik T_kb.  A block product is done by 32 threads with 2 x 4 register tiles and
+// 16-byte operand reads (rows of A and of T_ii, four adjacent columns of T and W).  Ends with T' rounded to tf32 in
+// rows 0..63 of the tile and zeros in rows 64..127 (the second operand half of MMA 3).  Contains barriers: every
+// thread calls it.
+__device__ __forceinline__ void fma_2x4(float (&acc)[2][4], const float4& a0, const float4& a1, const float4& t0,
+                                        const float4& t1, const float4& t2, const float4& t3) {
+  const float a[2][4] = {{a0.x, a0.y, a0.z, a0.w}, {a1.x, a1.y, a1.z, a1.w}};
+  const float t[4][4] = {{t0.x, t0.y, t0.z, t0.w}, {t1.x, t1.y, t1.z, t1.w}, {t2.x, t2.y, t2.z, t2.w},
+                         {t3.x, t3.y, t3.z, t3.w}};
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) acc[r][cc] = fmaf(a[r][k], t[k][cc], acc[r][cc]);
+}
+
+__device__ __forceinline__ void inverse_blocked(unsigned char* smem, int tid) {
+  if (tid < 64) {
+    const int blk = tid >> 4, jj = tid & 15;
+    float acc[16];
+#pragma unroll
+    for (int rr = 0; rr < 16; ++rr) acc[rr] = 0.f;
+#pragma unroll
+    for (int q = 0; q < 16; ++q) {
+      const float xq = acc[q] + (q == jj ? 1.f : 0.f);
+      st1(smem, t_off(16 * blk + q, 16 * blk + jj), xq);
+#pragma unroll
+      for (int rr = q + 1; rr < 16; ++rr) acc[rr] = fmaf(aab(smem, 16 * blk + rr, 16 * blk + q), xq, acc[rr]);
+    }
+  }
+  __syncthreads();
+  const int warp = tid >> 5, sub = tid & 31;
+  const int rp = sub >> 2, cq = sub & 3;  // rows 2 rp, 2 rp + 1 and columns 4 cq .. 4 cq + 3 of a block
+#pragma unroll 1
+  for (int dg = 1; dg < 4; ++dg) {
+    // Block (ib, bb) of this anti-diagonal needs sum_{kb = bb .. ib-1} A_{ib,kb} T_{kb,bb}: one warp per (block, kb)
+    // term (3, 4 and 3 warps for dg = 1, 2, 3); the term goes to W rows 16 (kb + 1) .., columns of block bb.
+    int bb = -1, kb = 0;
+    if (dg == 1) { if (warp < 3) { bb = warp; kb = warp; } }
+    else if (dg == 2) { if (warp < 4) { bb = warp >> 1; kb = bb + (warp & 1); } }
+    else { if (warp < 3) { bb = 0; kb = warp; } }
+    if (bb >= 0) {
+      const int ib = bb + dg, row = 16 * ib + 2 * rp, col = 16 * bb + 4 * cq;
+      float acc[2][4] = {};
+#pragma unroll 2
+      for (int kq = 4 * kb; kq < 4 * kb + 4; ++kq)  // four columns of A / rows of T at a time
+        fma_2x4(acc, ld4(smem, aab_off(row, kq)), ld4(smem, aab_off(row + 1, kq)), ld4(smem, t_off(4 * kq, col)),
+                ld4(smem, t_off(4 * kq + 1, col)), ld4(smem, t_off(4 * kq + 2, col)), ld4(smem, t_off(4 * kq + 3, col)));
+      st4(smem, w_off(16 * (kb + 1) + 2 * rp, col), make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]));
+      st4(smem, w_off(16 * (kb + 1) + 2 * rp + 1, col), make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]));
+    }
+    __syncthreads();
+    // T_ib = T_ii (sum of the dg terms): one warp per block
+    if (warp < 4 - dg) {
+      const int b2 = warp, ib = b2 + dg, row = 16 * ib + 2 * rp, col = 16 * b2 + 4 * cq;
+      float acc[2][4] = {};
+#pragma unroll 1
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float4 w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) w[e] = ld4(smem, w_off(16 * (b2 + 1) + 4 * q4 + e, col));
+        for (int term = 1; term < dg; ++term) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float4 x = ld4(smem, w_off(16 * (b2 + term + 1) + 4 * q4 + e, col));
+            w[e].x += x.x; w[e].y += x.y; w[e].z += x.z; w[e].w += x.w;
+          }
+        }
+        const int q = 16 * ib + 4 * q4;
+        fma_2x4(acc, ld4(smem, t_off(row, q)), ld4(smem, t_off(row + 1, q)), w[0], w[1], w[2], w[3]);
+      }
+      st4(smem, t_off(row, col), make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]));
+      st4(smem, t_off(row + 1, col), make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]));
+    }
+    __syncthreads();
+  }
+  {
+    // T' = T - I, rounded; everything on and above the diagonal is zero (the blocks above it were never written)
+    const int row = tid & 63, c4 = tid >> 6;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int col = 16 * c4 + 4 * i;
+      const uint32_t o = t_off(row, col);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (col < row) {
+        v = umma::to_tf32(ld4(smem, o));
+        if (col + 1 >= row) v.y = 0.f;
+        if (col + 2 >= row) v.z = 0.f;
+        if (col + 3 >= row) v.w = 0.f;
+      }
+      st4(smem, o, v);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int piece = tid + i * kThreads;  // 16 chunks x 64 rows of 16 bytes
+      st4(smem, kOffX2 + uint32_t(piece >> 6) * kCST + 1024 + uint32_t(piece & 63) * 16, make_float4(0.f, 0.f, 0.f, 0.f));
+    }
+  }
+}
+
+template <typename io_t>
+__device__ __forceinline__ void unpack8(uint4 u, float (&f)[8]) {
+  using IO = Io16<io_t>;
+  float2 p;
+  p = IO::unpack(u.x); f[0] = p.x; f[1] = p.y;
+  p = IO::unpack(u.y); f[2] = p.x; f[3] = p.y;
+  p = IO::unpack(u.z); f[4] = p.x; f[5] = p.y;
+  p = IO::unpack(u.w); f[6] = p.x; f[7] = p.y;
+}
+
+template <typename io_t>
+__global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
+    const int* __restrict__ seq_chunk_offsets, const int* __restrict__ chunk_starts, const int* __restrict__ chunk_ends,
+    const int* __restrict__ state_indices, const int* __restrict__ metadata_status, float* __restrict__ state_pool,
+    const io_t* __restrict__ r_ptr, const io_t* __restrict__ w_ptr, const io_t* __restrict__ k_ptr,
+    const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr, const io_t* __restrict__ b_ptr,
+    const io_t* __restrict__ bias_ptr, io_t* __restrict__ y_ptr, float* __restrict__ y32_ptr,
+    float* __restrict__ boundary, float* __restrict__ sda_ptr, int num_heads, int num_units,
+    long long output_elements, float scale, int* __restrict__ error_flag) {
+  using IO = Io16<io_t>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ uint64_t mbar[4];
+  __shared__ uint32_t tmem_holder;
+  __shared__ float seg_total[4][64];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (metadata_status != nullptr && metadata_status[0] != 0) {
+    const io_t nan16 = IO::store(quiet_nan());
+    for (long long i = (long long)blockIdx.x * kThreads + tid; i < output_elements; i += (long long)gridDim.x * kThreads) {
+      y_ptr[i] = nan16;
+      if (y32_ptr != nullptr) y32_ptr[i] = quiet_nan();
+    }
+    return;
+  }
+  const int m = 32 * (warp & 3) + lane;  // tensor-memory lane / operand row of this thread
+  const int half = warp >> 2;            // which 32 of 64 columns (64 of 128) this thread handles
+  const int mt = m & 63;                 // token (or key channel) of that row
+  const bool low = m < 64;               // lanes 0..63: A~ / B~ rows, later key rows; lanes 64..127: R~ / K~ / V, Y rows
+  const int c0 = 32 * half;
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) umma::mbar_init(&mbar[i], 1);
+    umma::mbar_fence_init();
+  }
+  if (warp == 0) umma::tmem_alloc(&tmem_holder, kTmemCols);
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = tmem_holder;
+  const uint32_t sbase = umma::smem_u32(smem);
+  const uint32_t lane_base = uint32_t(32 * (warp & 3)) << 16;
+  const uint32_t idesc128 = umma::idesc_tf32(128, 128), idesc64 = umma::idesc_tf32(128, 64);
+  const long long row_stride = (long long)num_heads * kD;
+  bool ok = true;
+  uint32_t parity = 0;
+
+  // the decay logits of a chunk travel by cp.async one chunk ahead (two 16-byte pieces per thread; rows past the
+  // end of a short chunk are zero-filled and not used)
+  auto stage_w = [&](int chunk, long long head_off) {
+    const int tt0 = chunk_starts[chunk];
+    const int ln = min(max(chunk_ends[chunk] - tt0, 1), kL);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int piece = tid + i * kThreads, rowi = piece >> 3, part = piece & 7;
+      umma::cp_async16(sbase + kOffW + piece * 16,
+                       w_ptr + (long long)(tt0 + min(rowi, ln - 1)) * row_stride + head_off + 8 * part,
+                       rowi < ln ? 16u : 0u);
+    }
+    umma::cp_async_commit();
+  };
+
+  // g[t][k] of a chunk: (1) thread (token, 16 channels): retention of the staged logits, row-wise into the g tile;
+  // (2) thread (key channel, 16-token segment): running product down the column, segment totals, prefix fix-up.
+  // Runs one chunk ahead of its use (while the tensor core does MMA 1 of the previous chunk) and starts the copy of
+  // the logits of the chunk after.  Contains barriers: every thread calls it.
+  auto compute_g = [&](int chunk, int last_chunk, long long head_off) {
+    const int ln = min(max(chunk_ends[chunk] - chunk_starts[chunk], 1), kL);
+    umma::cp_async_wait_all();
+    __syncthreads();
+    {
+      const int t = tid >> 2, q = tid & 3;
+      float x[16];
+      unpack8<io_t>(*reinterpret_cast<const uint4*>(smem + kOffW + t * 128 + q * 32), *reinterpret_cast<float(*)[8]>(&x[0]));
+      unpack8<io_t>(*reinterpret_cast<const uint4*>(smem + kOffW + t * 128 + q * 32 + 16), *reinterpret_cast<float(*)[8]>(&x[8]));
+      if (bias_ptr != nullptr) {
+        float bz[16];
+        unpack8<io_t>(__ldg(reinterpret_cast<const uint4*>(bias_ptr + head_off + 16 * q)), *reinterpret_cast<float(*)[8]>(&bz[0]));
+        unpack8<io_t>(__ldg(reinterpret_cast<const uint4*>(bias_ptr + head_off + 16 * q + 8)), *reinterpret_cast<float(*)[8]>(&bz[8]));
+#pragma unroll
+        for (int e = 0; e < 16; ++e) x[e] += bz[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 16; ++e) x[e] = t < ln ? retention(x[e]) : 1.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        st4(smem, kOffG + (4 * q + i) * kCS64 + t * 16, make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]));
+    }
+    __syncthreads();
+    if (chunk + 1 < last_chunk) stage_w(chunk + 1, head_off);  // everybody has read this chunk's logits
+    {
+      const int kcol = tid & 63, seg = tid >> 6;
+      const uint32_t gcol = kOffG + uint32_t(kcol >> 2) * kCS64 + uint32_t(kcol & 3) * 4 + uint32_t(16 * seg) * 16;
+      float pr[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) pr[i] = ld1(smem, gcol + i * 16);
+#pragma unroll
+      for (int i = 1; i < 16; ++i) pr[i] *= pr[i - 1];
+      seg_total[seg][kcol] = pr[15];
+      __syncthreads();
+      float mult = 1.f;
+      if (seg > 0) mult = seg_total[0][kcol];
+      if (seg > 1) mult *= seg_total[1][kcol];
+      if (seg > 2) mult *= seg_total[2][kcol];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) st1(smem, gcol + i * 16, pr[i] * mult);
+    }
+    __syncthreads();
+  };
+
+  for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+    const int seq = unit / num_heads, head = unit % num_heads;
+    const int c_begin = seq_chunk_offsets[seq], c_end = seq_chunk_offsets[seq + 1];
+    if (c_begin >= c_end) continue;
+    const int slot = state_indices != nullptr ? state_indices[seq] : seq;
+    float* state = state_pool + ((long long)slot * num_heads + head) * (kD * kD);
+    const long long head_off = (long long)head * kD;
+    stage_w(c_begin, head_off);
+
+    // ---- this unit's state: row mt, columns c0..c0+31 in registers (fp32) and, transposed and rounded, in S0^T ----
+    float S[32];
+    if (low) {
+      float* bnd = boundary != nullptr ? boundary + ((long long)c_begin * num_heads + head) * (kD * kD) + mt * kD + c0
+                                       : nullptr;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 s = *reinterpret_cast<const float4*>(state + mt * kD + c0 + j);
+        if (bnd != nullptr) *reinterpret_cast<float4*>(bnd + j) = s;
+        S[j] = s.x; S[j + 1] = s.y; S[j + 2] = s.z; S[j + 3] = s.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) st1(smem, kOffS + tile_off(kCS64, c0 + j, mt), umma::to_tf32(S[j]));
+    }
+    compute_g(c_begin, c_end, head_off);
+
+    int next_t0 = chunk_starts[c_begin], next_end = chunk_ends[c_begin];
+    for (int c = c_begin; c < c_end; ++c, parity ^= 1u) {
+      const int t0 = next_t0;
+      const int len = min(max(next_end - t0, 1), kL);
+      if (c + 1 < c_end) {  // the next chunk's bounds are on their way while this one is worked on
+        next_t0 = chunk_starts[c + 1];
+        next_end = chunk_ends[c + 1];
+      }
+      // ---- this thread's operand rows leave HBM / L2 now and are used after the decay scan ----------------------
+      const bool valid = mt < len;
+      uint4 praw[4], qraw[4], vraw[4];
+      {
+        const long long row = (long long)(t0 + min(mt, len - 1)) * row_stride + head_off + c0;
+        const uint4* pp = reinterpret_cast<const uint4*>((low ? a_ptr : r_ptr) + row);
+        const uint4* qp = reinterpret_cast<const uint4*>((low ? b_ptr : k_ptr) + row);
+        const uint4* vp = reinterpret_cast<const uint4*>(v_ptr + row);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+          praw[i] = valid ? __ldg(pp + i) : zero;
+          qraw[i] = valid ? __ldg(qp + i) : zero;
+          vraw[i] = (valid && !low) ? __ldg(vp + i) : zero;
+        }
+      }
+
+      // ---- operands: XA -> tensor memory, [B~;K~] and V^T -> shared memory -------------------------------------
+      const float g_last = low ? ld1(smem, kOffG + tile_off(kCS64, 63, mt)) : 0.f;  // g_L of key row mt
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float pf[8], qf[8];
+        unpack8<io_t>(praw[i], pf);
+        unpack8<io_t>(qraw[i], qf);
+        uint32_t xa[8];
+#pragma unroll
+        for (int hq = 0; hq < 2; ++hq) {
+          const int kc = (c0 >> 2) + 2 * i + hq;  // 16-byte column chunk of g / of the tiles
+          const float4 g = ld4(smem, kOffG + kc * kCS64 + mt * 16);
+          float4 sc = g;                          // R~ = r * g_t
+          if (low) sc = mt > 0 ? ld4(smem, kOffG + kc * kCS64 + (mt - 1) * 16) : make_float4(1.f, 1.f, 1.f, 1.f);
+          const int e = 4 * hq;
+          xa[e + 0] = tf32_bits(pf[e + 0] * sc.x);  // rows past the end of a short chunk were loaded as zeros
+          xa[e + 1] = tf32_bits(pf[e + 1] * sc.y);
+          xa[e + 2] = tf32_bits(pf[e + 2] * sc.z);
+          xa[e + 3] = tf32_bits(pf[e + 3] * sc.w);
+          st4(smem, kOffX2 + kc * kCSB + m * 16,
+              umma::to_tf32(make_float4(qf[e + 0] * rcp_approx(g.x), qf[e + 1] * rcp_approx(g.y),
+                                        qf[e + 2] * rcp_approx(g.z), qf[e + 3] * rcp_approx(g.w))));
+        }
+        umma::tmem_st8(tmem + kColXA + lane_base + c0 + 8 * i, xa);
+        if (!low) {
+          float vf[8];
+          unpack8<io_t>(vraw[i], vf);
+          const uint32_t o = kOffUV + uint32_t(16 + (mt >> 2)) * kCS64 + uint32_t(mt & 3) * 4 + (c0 + 8 * i) * 16;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) st1(smem, o + e * 16, vf[e]);
+        }
+      }
+      umma::tmem_st_wait();
+      // pull the next chunk's operand rows into L2 (its decay logits are already on their way to shared memory)
+      if (c + 1 < c_end) {
+        const int nt0 = next_t0, nlen = next_end - nt0;
+        for (int e = tid; e < 5 * kL; e += kThreads) {
+          const int which = e >> 6, rowi = e & 63;
+          if (rowi < nlen) {
+            const io_t* base = which == 0 ? a_ptr : which == 1 ? r_ptr : which == 2 ? b_ptr : which == 3 ? k_ptr : v_ptr;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(base + (long long)(nt0 + rowi) * row_stride + head_off));
+          }
+        }
+      }
+      umma::fence_async_smem();
+      umma::fence_before_sync();
+      __syncthreads();
+      umma::fence_after_sync();
+
+      // ---- MMA 1: D1 = XA [B~;K~]^T ------------------------------------------------------------------------------
+      if (tid == 0) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma::mma_tf32_ts(tmem + kColD1, tmem + kColXA + 8 * ks,
+                            umma::desc_k_major(sbase + kOffX2 + ks * 2 * kCSB, kCSB), idesc128, ks > 0 ? 1u : 0u);
+        umma::mma_commit(&mbar[0]);
+      }
+      if (c + 1 < c_end) compute_g(c + 1, c_end, head_off);  // g of this chunk has been consumed (barrier above)
+      ok = wait_warp(&mbar[0], parity, ok);
+      umma::fence_after_sync();
+      // ---- epilogue 1: mask; A_ab -> fp32 scratch, the other three blocks rounded in place -----------------------
+      if (ok) {
+        const int limit = low ? mt : mt + 1;  // keep s < t (strict) or s <= t
+#pragma unroll 1
+        for (int hb = 0; hb < 4; ++hb) {
+          uint32_t u[16];
+          const uint32_t taddr = tmem + kColD1 + lane_base + 64 * half + 16 * hb;
+          umma::tmem_ld16(taddr, u);
+          umma::tmem_ld_wait();
+          const int s0 = 16 * hb;
+          if (low && half == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4)
+              st4(smem, aab_off(mt, (s0 + j) >> 2),
+                  make_float4(s0 + j < limit ? __uint_as_float(u[j]) : 0.f,
+                              s0 + j + 1 < limit ? __uint_as_float(u[j + 1]) : 0.f,
+                              s0 + j + 2 < limit ? __uint_as_float(u[j + 2]) : 0.f,
+                              s0 + j + 3 < limit ? __uint_as_float(u[j + 3]) : 0.f));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) u[j] = s0 + j < limit ? tf32_bits(__uint_as_float(u[j])) : 0u;
+            umma::tmem_st16(taddr, u);
+          }
+        }
+        umma::tmem_st_wait();
+      }
+      umma::fence_before_sync();
+      __syncthreads();
+      umma::fence_after_sync();
+
+      // ---- MMA 2: DA = XA S0 + D1[:,64:128] V ------------------------------------------------------------------
+      if (tid == 0) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma::mma_tf32_ts(tmem + kColDA, tmem + kColXA + 8 * ks,
+                            umma::desc_k_major(sbase + kOffS + ks * 2 * kCS64, kCS64), idesc64, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma::mma_tf32_ts(tmem + kColDA, tmem + kColD1 + 64 + 8 * ks,
+                            umma::desc_k_major(sbase + kOffUV + (16 + 2 * ks) * kCS64, kCS64), idesc64, 1u);
+        umma::mma_commit(&mbar[1]);
+      }
+      // Meanwhile the key rows of MMA 4's operand: lane k gets column k of the [B~;K~] tile.  B~^T goes over the A_ab
+      // block at once (every reader of that block passed the barrier above); K~^T waits in registers for MMA 2,
+      // which still reads the A_ak block it will replace.
+      uint32_t kt[32];
+      if (low) {
+        const uint32_t colk = kOffX2 + uint32_t(mt >> 2) * kCSB + uint32_t(mt & 3) * 4;
+#pragma unroll 1
+        for (int hb = 0; hb < 2; ++hb) {
+          uint32_t bt[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) bt[j] = __float_as_uint(ld1(smem, colk + (c0 + 16 * hb + j) * 16));
+          umma::tmem_st16(tmem + kColD1 + lane_base + c0 + 16 * hb, bt);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) kt[j] = __float_as_uint(ld1(smem, colk + (64 + c0 + j) * 16));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) kt[j] = 0u;  // lanes 64..127: zeros over A_rk (A_rk V is already part of DA)
+      }
+      ok = wait_warp(&mbar[1], parity, ok);
+      umma::fence_after_sync();
+      umma::tmem_st32(tmem + kColD1 + 64 + lane_base + c0, kt);
+      umma::tmem_st_wait();
+      umma::fence_before_sync();
+      __syncthreads();  // the [B~;K~] tile has been read: the inverse may build T' over it
+      inverse_blocked(smem, tid);
+      __syncthreads();
+      // ---- epilogue 2: X^T -> shared memory (over the A_ab scratch, which the inverse has consumed) -----------------
+      umma::fence_after_sync();
+      if (ok && low) {
+#pragma unroll 1
+        for (int hb = 0; hb < 2; ++hb) {
+          uint32_t u[16];
+          umma::tmem_ld16(tmem + kColDA + lane_base + c0 + 16 * hb, u);
+          umma::tmem_ld_wait();
+          const uint32_t o = kOffUV + uint32_t(mt >> 2) * kCS64 + uint32_t(mt & 3) * 4 + (c0 + 16 * hb) * 16;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) st1(smem, o + j * 16, umma::to_tf32(__uint_as_float(u[j])));
+        }
+      }
+      umma::fence_async_smem();
+      umma::fence_before_sync();
+      __syncthreads();
+      umma::fence_after_sync();
+
+      // ---- MMA 3: DA += [T';0] X ----------------------------------------------------------------------------------
+      if (tid == 0) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma::mma_tf32_ss(tmem + kColDA, umma::desc_k_major(sbase + kOffX2 + ks * 2 * kCST, kCST),
+                            umma::desc_k_major(sbase + kOffUV + ks * 2 * kCS64, kCS64), idesc64, 1u);
+        umma::mma_commit(&mbar[2]);
+      }
+      ok = wait_warp(&mbar[2], parity, ok);
+      umma::fence_after_sync();
+      // ---- epilogue 3: U -> state_dot_a (optional) and U^T over X^T ----------------------------------------------
+      if (ok && low) {
+#pragma unroll 1
+        for (int hb = 0; hb < 2; ++hb) {
+          uint32_t u[16];
+          umma::tmem_ld16(tmem + kColDA + lane_base + c0 + 16 * hb, u);
+          umma::tmem_ld_wait();
+          if (sda_ptr != nullptr && valid) {
+            float* dst = sda_ptr + (long long)(t0 + mt) * row_stride + head_off + c0 + 16 * hb;
+#pragma unroll
+            for (int j = 0; j < 16; j += 4)
+              *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(u[j]), __uint_as_float(u[j + 1]),
+                                                                __uint_as_float(u[j + 2]), __uint_as_float(u[j + 3]));
+          }
+          const uint32_t o = kOffUV + uint32_t(mt >> 2) * kCS64 + uint32_t(mt & 3) * 4 + (c0 + 16 * hb) * 16;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) st1(smem, o + j * 16, umma::to_tf32(__uint_as_float(u[j])));
+        }
+      }
+      umma::fence_async_smem();
+      umma::fence_before_sync();
+      __syncthreads();
+      umma::fence_after_sync();
+
+      // ---- MMA 4: DC = D1 [U ; V] ---------------------------------------------------------------------------------
+      if (tid == 0) {
+#pragma unroll
+        for (int ks = 0; ks < 16; ++ks)
+          umma::mma_tf32_ts(tmem + kColDC, tmem + kColD1 + 8 * ks,
+                            umma::desc_k_major(sbase + kOffUV + ks * 2 * kCS64, kCS64), idesc64, ks > 0 ? 1u : 0u);
+        umma::mma_commit(&mbar[3]);
+      }
+      ok = wait_warp(&mbar[3], parity, ok);
+      umma::fence_after_sync();
+      // ---- epilogue 4: Y rows out; S' = g_L (S + DC) -> registers, S0^T, boundary / state pool ----------------------
+      if (ok) {
+        uint32_t u[32];
+        umma::tmem_ld32(tmem + kColDC + lane_base + c0, u);
+        if (low) {
+          umma::tmem_ld_wait();
+          const bool last = (c + 1 == c_end);
+          float* dst = last ? state + mt * kD + c0
+                            : (boundary != nullptr
+                                   ? boundary + ((long long)(c + 1) * num_heads + head) * (kD * kD) + mt * kD + c0
+                                   : nullptr);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) S[j] = g_last * (S[j] + __uint_as_float(u[j]));
+          if (dst != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+          }
+          if (!last) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) st1(smem, kOffS + tile_off(kCS64, c0 + j, mt), umma::to_tf32(S[j]));
+          }
+        } else {
+          uint32_t u2[32];
+          umma::tmem_ld32(tmem + kColDA + lane_base + c0, u2);
+          umma::tmem_ld_wait();
+          if (valid) {
+            const long long row = (long long)(t0 + mt) * row_stride + head_off + c0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float o[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o[e] = scale * (__uint_as_float(u[j + e]) + __uint_as_float(u2[j + e]));
+              uint4 packed;
+              packed.x = IO::pack(o[0], o[1]); packed.y = IO::pack(o[2], o[3]);
+              packed.z = IO::pack(o[4], o[5]); packed.w = IO::pack(o[6], o[7]);
+              *reinterpret_cast<uint4*>(y_ptr + row + j) = packed;
+              if (y32_ptr != nullptr) {
+                *reinterpret_cast<float4*>(y32_ptr + row + j) = make_float4(o[0], o[1], o[2], o[3]);
+                *reinterpret_cast<float4*>(y32_ptr + row + j + 4) = make_float4(o[4], o[5], o[6], o[7]);
+              }
+            }
+          }
+        }
+      }
+      umma::fence_async_smem();
+      umma::fence_before_sync();
+      ok = __syncthreads_and(ok ? 1 : 0) != 0;  // one verdict for the whole CTA: nobody walks on alone
+      umma::fence_after_sync();
+      if (!ok) {
+        // fail closed: the rows of this (sequence, head) read as NaN, its state slot keeps the value it had
+        const io_t nan16 = IO::store(quiet_nan());
+        const int tb = chunk_starts[c_begin], te = chunk_ends[c_end - 1];
+        for (long long e = (long long)tb * kD + tid; e < (long long)te * kD; e += kThreads) {
+          const long long at = (e / kD) * row_stride + head_off + (e % kD);
+          y_ptr[at] = nan16;
+          if (y32_ptr != nullptr) y32_ptr[at] = quiet_nan();
+        }
+        break;
+      }
+    }
+  }
+  if (!ok && tid == 0 && error_flag != nullptr) atomicExch(error_flag, 3);
+  umma::cp_async_wait_all();
+  umma::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) umma::tmem_dealloc(tmem, kTmemCols);
+}
+
+struct DeviceInfo {
+  int sm_count = 0;
+  bool attr_set[2] = {false, false};
+};
+
+DeviceInfo* device_info() {
+  static DeviceInfo info[64];
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+  DeviceInfo* d = &info[device];
+  if (d->sm_count == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) return nullptr;
+    d->sm_count = n;
+  }
+  return d;
+}
+
+template <typename io_t>
+int launch_fused(const int* sco, const int* cs, const int* ce, const int* state_indices, const int* status,
+                 float* state_pool, const void* r, const void* w, const void* k, const void* v, const void* a,
+                 const void* b, const void* bias, void* y, float* y32, float* boundary, float* sda, int* error_flag,
+                 int total_tokens, int num_sequences, int num_heads, float scale, int which, cudaStream_t stream) {
+  DeviceInfo* info = device_info();
+  if (info == nullptr) return fail(FRWKV_ERR_CUDA, "wkv7_chunk_fused_forward: cannot query the current device");
+  if (!info->attr_set[which]) {
+    cudaError_t e = cudaFuncSetAttribute(wkv7_chunk_fused_kernel<io_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kFusedSmem);
+    if (e != cudaSuccess)
+      return fail(FRWKV_ERR_CUDA, "wkv7_chunk_fused_forward: cannot reserve shared memory: %s", cudaGetErrorString(e));
+    info->attr_set[which] = true;
+  }
+  const int units = num_sequences * num_heads;
+  const int grid = units < 2 * info->sm_count ? units : 2 * info->sm_count;
+  wkv7_chunk_fused_kernel<io_t><<<(unsigned)grid, kThreads, kFusedSmem, stream>>>(
+      sco, cs, ce, state_indices, status, state_pool, static_cast<const io_t*>(r), static_cast<const io_t*>(w),
+      static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),
+      static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, boundary, sda,
+      num_heads, units, (long long)total_tokens * num_heads * kD, scale, error_flag);
+  return check_launch("wkv7_chunk_fused_kernel");
+}
+
+}  // namespace
+}  // namespace frwkv
+
+// The fused form runs one CTA per (sequence, head): below this many pairs the two-kernel form, which spreads the
+// chunks of one sequence over the GPU, is the faster one.
+extern "C" int frwkv_wkv7_chunk_prefers_fused(int num_sequences, int num_heads) {
+  return (long long)num_sequences * num_heads >= 144 ? 1 : 0;
+}
+
+extern "C" int frwkv_wkv7_chunk_fused_fp32io16_forward(
+    const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends,
+    const int32_t* state_indices, const int32_t* metadata_status, float* state_pool, const void* r,
+    const void* decay_logits, const void* k, const void* v, const void* a, const void* b, const void* decay_bias,
+    void* y, float* y_fp32, float* boundary, float* state_dot_a, int32_t* error_flag, int total_tokens,
+    int num_sequences, int num_chunks, int num_heads, int head_size, int io_dtype, float scale,
+    frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(seq_chunk_offsets && chunk_starts && chunk_ends && state_pool && r && decay_logits && k && v && a &&
+                    b && y,
+                "wkv7_chunk_fused_forward: null pointer argument");
+  FRWKV_REQUIRE(total_tokens > 0 && num_sequences > 0 && num_chunks > 0 && num_heads > 0,
+                "wkv7_chunk_fused_forward: sizes must be positive");
+  if (head_size != 64)
+    return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_chunk_fused_forward: head size %d is not built (only 64)", head_size);
+  FRWKV_REQUIRE((long long)num_sequences * num_heads <= 0x7fffffffLL,
+                "wkv7_chunk_fused_forward: too many (sequence, head) pairs");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (io_dtype == FRWKV_DTYPE_BF16)
+    return launch_fused<__nv_bfloat16>(seq_chunk_offsets, chunk_starts, chunk_ends, state_indices, metadata_status,
+                                       state_pool, r, decay_logits, k, v, a, b, decay_bias, y, y_fp32, boundary,
+                                       state_dot_a, error_flag, total_tokens, num_sequences, num_heads, scale, 0, s);
+  if (io_dtype == FRWKV_DTYPE_FP16)
+    return launch_fused<__half>(seq_chunk_offsets, chunk_starts, chunk_ends, state_indices, metadata_status,
+                                state_pool, r, decay_logits, k, v, a, b, decay_bias, y, y_fp32, boundary, state_dot_a,
+                                error_flag, total_tokens, num_sequences, num_heads, scale, 1, s);
+  return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_chunk_fused_forward: token tensors must be float16 or bfloat16");
+}

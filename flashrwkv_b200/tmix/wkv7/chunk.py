@@ -43,10 +43,14 @@ def make_chunk_metadata(cu_seqlens: torch.Tensor, chunk_size: int = MAX_CHUNK):
 
 def wkv7_chunk_forward(r, decay_logits, k, v, a, b, *, state, chunk_metadata, state_indices=None,
                        scale: float = 1.0, decay_bias=None, want_boundary: bool = False,
-                       output_fp32: torch.Tensor | None = None, metadata_status=None):
+                       output_fp32: torch.Tensor | None = None, metadata_status=None,
+                       state_dot_a: torch.Tensor | None = None, path: int = -1):
     """Chunked forward with an fp32 state `[slots,H,64,64]` updated in place.
 
     Returns `(output, boundary_or_None, error_flag)`; `boundary[c]` is the state at the start of chunk `c`.
+    `path` picks the kernels: 0 = build + scan through a workspace (spreads the chunks of few sequences over the
+    GPU), 1 = one fused kernel per (sequence, head) without a workspace, -1 = chosen from the batch.  A float32
+    `state_dot_a` tensor shaped like `r`, if given, receives `S_{t-1}^T a_t` per token (fused kernel).
     """
     sco, cs, ce = chunk_metadata
     output = torch.empty_like(v)
@@ -54,7 +58,8 @@ def wkv7_chunk_forward(r, decay_logits, k, v, a, b, *, state, chunk_metadata, st
     if want_boundary:
         boundary = torch.empty((cs.numel(), r.shape[1], 64, 64), device=r.device, dtype=torch.float32)
     flag = extension().wkv7_chunk_forward(sco, cs, ce, state, r, decay_logits, k, v, a, b, output, float(scale),
-                                          decay_bias, state_indices, boundary, output_fp32, metadata_status)
+                                          decay_bias, state_indices, boundary, output_fp32, metadata_status,
+                                          state_dot_a, int(path))
     return output, boundary, flag
 
 

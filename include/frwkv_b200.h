@@ -150,6 +150,27 @@ int frwkv_wkv7_chunk_fp32io16_forward(
     frwkv_stream_t stream);
 
 /*
+ * The same chunked forward as ONE kernel without a workspace: a CTA owns a (sequence, head) pair, keeps the
+ * fp32 state on chip and walks that sequence's chunks in order, so only token rows, outputs and the optional
+ * boundary / state_dot_a tensors cross HBM.  It needs enough (sequence, head) pairs to fill the GPU (two per
+ * SM); frwkv_wkv7_chunk_prefers_fused() says which of the two forms is expected to be faster for a batch.
+ * Replaces the same reference kernels as frwkv_wkv7_chunk_fp32io16_forward, and for training the forward of
+ * statetune_recurrent_fp32io16 (csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_forward.cu:32-130), whose
+ * state_dot_a output it produces directly:
+ *   state_dot_a fp32 [N,H,64] or NULL: sa_t = S_{t-1}^T a_t for every token.
+ * On a failed wait the rows of the affected (sequence, head) pairs are NaN, their state slots untouched, and
+ * *error_flag is non-zero.  Other arguments as in frwkv_wkv7_chunk_fp32io16_forward.
+ */
+int frwkv_wkv7_chunk_prefers_fused(int num_sequences, int num_heads);
+int frwkv_wkv7_chunk_fused_fp32io16_forward(
+    const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends,
+    const int32_t* state_indices, const int32_t* metadata_status, float* state_pool, const void* r,
+    const void* decay_logits, const void* k, const void* v, const void* a, const void* b, const void* decay_bias,
+    void* y, float* y_fp32, float* boundary, float* state_dot_a, int32_t* error_flag, int total_tokens,
+    int num_sequences, int num_chunks, int num_heads, int head_size, int io_dtype, float scale,
+    frwkv_stream_t stream);
+
+/*
  * The same chunked forward for hosts that may not allocate device memory (servers that gave the whole GPU to
  * fixed pools at start-up, real-time loops, plain C callers without a caching allocator).  It has no
  * counterpart in the reference, whose chunk operators allocate their workspaces through Torch on every call.
@@ -382,16 +403,6 @@ int frwkv_pretrain_lnx_rkvres_xg_backward(const void* grad_out, const void* x, c
                                           void* grad_bias, void* grad_g, float* workspace, long long workspace_floats,
                                           long long rows, int channels, int head_size, int io_dtype,
                                           frwkv_stream_t stream);
-
-/*
- * Diagnostic: D[128][n] = A[128][64] * B[n][64]^T through one tcgen05.mma (kind::tf32) chain of 8 K-steps,
- * with A and B staged in shared memory as chunk-major tiles of the given chunk stride (bytes).  No
- * counterpart in the reference; used by the tests to pin the descriptor encodings the chunk kernels rely on.
- * error_flag (device int32) is set to 1 if the MMA never completed.  a_raw_shift >= 0 turns the A region
- * into a layout probe (word i holds (i >> shift) & 2047); -1 = off.
- */
-int frwkv_selftest_umma(const float* a, const float* b, float* d, int n, int a_chunk_stride, int b_chunk_stride,
-                        int a_raw_shift, int32_t* error_flag, frwkv_stream_t stream);
 
 #ifdef __cplusplus
 }

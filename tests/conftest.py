@@ -17,6 +17,9 @@ def pytest_sessionstart(session):
     from flashrwkv_b200 import build as native
 
     native.build_all()
+    from tests.native import build_probe
+
+    build_probe.build()
 
 
 @pytest.fixture(scope="session")

@@ -102,8 +102,9 @@ def test_rl_wide_heads_vs_oracle(oracle, d, dtype):
             assert torch.equal(d_pool.cpu(), pool)
 
 
+@pytest.mark.parametrize("path", [0, 1], ids=["build_scan", "fused"])
 @pytest.mark.parametrize("lengths", [(512, 512), (1, 15, 16, 17, 65, 130, 64, 63)])
-def test_chunked_vs_oracle_and_recurrent(oracle, lengths):
+def test_chunked_vs_oracle_and_recurrent(oracle, lengths, path):
     import flashrwkv_b200 as F
     from flashrwkv_b200 import synthetic
     from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata, wkv7_chunk_forward
@@ -121,10 +122,16 @@ def test_chunked_vs_oracle_and_recurrent(oracle, lengths):
     pool = pool0.cuda()
     y32 = torch.empty((N, H, D), device="cuda")
     meta = make_chunk_metadata(cu.cuda(), 64)
+    sda = torch.full((N, H, D), float("nan"), device="cuda") if path == 1 else None
     y, boundary, flag = wkv7_chunk_forward(*dtoks, state=pool, chunk_metadata=meta, state_indices=slots.cuda(),
-                                           scale=0.7, decay_bias=bias.cuda(), want_boundary=True, output_fp32=y32)
+                                           scale=0.7, decay_bias=bias.cuda(), want_boundary=True, output_fp32=y32,
+                                           state_dot_a=sda, path=path)
     torch.cuda.synchronize()
     assert int(flag.item()) == 0
+    if sda is not None:  # S_{t-1}^T a_t per token, the backward's saved tensor
+        want = oracle.forward(*toks, state_pool=pool0, cu_seqlens=cu, state_indices=slots, decay_bias=bias,
+                              want_state_dot_a=True)["state_dot_a"]
+        assert rel_rmse(sda.cpu(), want) <= 2e-3
     assert max_abs(y32.cpu(), ref["y"]) <= Y_MAX_ABS
     assert rel_rmse(y.float().cpu(), ref["y"]) <= 7e-3
     assert _state_rel(pool, ref["state_pool"]) <= STATE_REL
@@ -148,7 +155,8 @@ def test_chunked_vs_oracle_and_recurrent(oracle, lengths):
             assert torch.equal(pool[slot].cpu(), pool0[slot])
 
 
-def test_bad_metadata_status_fails_closed():
+@pytest.mark.parametrize("path", [0, 1], ids=["build_scan", "fused"])
+def test_bad_metadata_status_fails_closed(path):
     from flashrwkv_b200 import synthetic
     from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata, wkv7_chunk_forward
 
@@ -157,7 +165,38 @@ def test_bad_metadata_status_fails_closed():
     pool = synthetic.state_pool(1, 2, 64, seed=2, device="cuda")
     before = pool.clone()
     status = torch.tensor([4], dtype=torch.int32, device="cuda")
-    y, _, _ = wkv7_chunk_forward(*toks, state=pool, chunk_metadata=make_chunk_metadata(cu), metadata_status=status)
+    y, _, _ = wkv7_chunk_forward(*toks, state=pool, chunk_metadata=make_chunk_metadata(cu), metadata_status=status,
+                                 path=path)
     torch.cuda.synchronize()
     assert torch.isnan(y.float()).all()
     assert torch.equal(pool, before)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fused_and_two_kernel_forms_agree_many_pairs(oracle, dtype):
+    """More (sequence, head) pairs than resident CTAs of a small grid would hold, ragged lengths, fp16 and bf16:
+    the fused kernel against the build + scan pair and the oracle."""
+    from flashrwkv_b200 import synthetic
+    from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata, wkv7_chunk_forward
+
+    H, D = 8, 64
+    lengths = [64 * (1 + (i % 3)) + (i % 5) for i in range(48)]  # 384 pairs
+    N = sum(lengths)
+    toks = [t.to(dtype) for t in synthetic.wkv7_inputs(N, H, D, seed=77)]
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32)
+    pool0 = synthetic.state_pool(len(lengths), H, D, seed=78)
+    dtoks = [t.cuda() for t in toks]
+    meta = make_chunk_metadata(cu.cuda(), 64)
+    outs = []
+    for path in (0, 1):
+        pool = pool0.cuda()
+        y32 = torch.empty((N, H, D), device="cuda")
+        _, _, flag = wkv7_chunk_forward(*dtoks, state=pool, chunk_metadata=meta, output_fp32=y32, path=path)
+        torch.cuda.synchronize()
+        assert int(flag.item()) == 0
+        outs.append((y32.cpu(), pool.cpu()))
+    ref = oracle.forward(*toks, state_pool=pool0, cu_seqlens=cu)
+    for y32, pool in outs:
+        assert max_abs(y32, ref["y"]) <= Y_MAX_ABS
+        assert _state_rel(pool, ref["state_pool"]) <= STATE_REL
+    assert max_abs(outs[0][0], outs[1][0]) <= Y_MAX_ABS
