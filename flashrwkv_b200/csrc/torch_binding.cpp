@@ -911,6 +911,113 @@ std::vector<torch::Tensor> wkv7_backward(torch::Tensor sco, torch::Tensor cs, to
 }
 
 
+// ---- reference-named entries of the chunk / training families ------------------------------------------------
+// Same names, argument order and defaults as the reference's native module, so that its Python layer binds to this
+// module unchanged.  Each is a thin arrangement of the operators above.
+
+// csrc/sm120/tmix/wkv7/infer_chunk_bf16_forward_varlen.cpp:77-183 of the reference: bf16 state pool updated in
+// place at state_indices, returns (output, state_pool).  chunk_size only has to be positive: the tensor-core
+// kernels always work on 64-token tiles and the result does not depend on the split.
+std::tuple<torch::Tensor, torch::Tensor> infer_chunk_bf16_forward_varlen_native(
+    torch::Tensor r, torch::Tensor w, torch::Tensor k, torch::Tensor v, torch::Tensor a, torch::Tensor b,
+    torch::Tensor state_pool, torch::Tensor cu, torch::Tensor idx, int64_t chunk_size, int64_t max_seqlen, double scale,
+    std::optional<torch::Tensor> decay_bias) {
+  TORCH_CHECK(chunk_size > 0, "chunk_size must be positive");
+  check_cuda_contiguous(state_pool, "state_pool");
+  TORCH_CHECK(state_pool.scalar_type() == torch::kBFloat16 && state_pool.dim() == 4 && r.dim() == 3 &&
+                  state_pool.size(1) == r.size(1) && state_pool.size(2) == 64 && state_pool.size(3) == 64,
+              "state_pool must be bfloat16 [slots,H,64,64]");
+  TORCH_CHECK(r.scalar_type() == torch::kBFloat16, "token tensors must be bfloat16");
+  check_cuda_contiguous(cu, "cu_seqlens");
+  check_cuda_contiguous(idx, "state_indices");
+  TORCH_CHECK(cu.scalar_type() == torch::kInt32 && idx.scalar_type() == torch::kInt32 && cu.dim() == 1 &&
+                  idx.dim() == 1 && cu.numel() == idx.numel() + 1 && idx.numel() > 0,
+              "cu_seqlens must be int32 [B+1] and state_indices int32 [B]");
+  const c10::cuda::CUDAGuard guard(r.device());
+  auto prepared = launch_validation(cu, idx, r.size(0), state_pool.size(0));
+  // chunk tables from the sequence offsets (one host read, as the reference does for max_seqlen)
+  auto cu_host = cu.cpu();
+  const int* offs = cu_host.data_ptr<int>();
+  std::vector<int> sco{0}, cs, ce;
+  for (int64_t sq = 0; sq + 1 < cu_host.numel(); ++sq) {
+    TORCH_CHECK(offs[sq + 1] > offs[sq] && offs[sq] >= 0 && offs[sq + 1] <= r.size(0),
+                "cu_seqlens must be strictly increasing within [0, total_tokens]");
+    for (int t = offs[sq]; t < offs[sq + 1]; t += 64) {
+      cs.push_back(t);
+      ce.push_back(std::min(t + 64, offs[sq + 1]));
+    }
+    sco.push_back(static_cast<int>(cs.size()));
+  }
+  auto to_dev = [&](const std::vector<int>& x) {
+    return torch::tensor(x, torch::TensorOptions().dtype(torch::kInt32)).to(r.device());
+  };
+  auto slots = prepared.idx.to(torch::kInt64);
+  auto working = state_pool.index_select(0, slots).to(torch::kFloat32);
+  auto output = torch::empty_like(v);
+  wkv7_chunk_forward(to_dev(sco), to_dev(cs), to_dev(ce), working, r, w, k, v, a, b, output, scale, decay_bias,
+                     std::nullopt, std::nullopt, std::nullopt, prepared.status, std::nullopt, -1);
+  // a batch that failed validation produced NaN outputs and left `working` as it was: copying it back is harmless
+  state_pool.index_copy_(0, slots, working.to(torch::kBFloat16));
+  (void)max_seqlen;
+  return {output, state_pool};
+}
+
+// csrc/sm90/rl_infctx/wkv7/rl_infctx_chunk_fp32io16_backward.cpp:102-135 of the reference: recompute `output` and
+// `state_dot_a` of every chunk from its boundary state.  Each chunk is run as a sequence of its own by the fused
+// kernel on a copy of the boundaries (the kernel updates its state in place).
+void rl_infctx_chunk_fp32io16_backward_replay(torch::Tensor cs, torch::Tensor ce, torch::Tensor boundary, torch::Tensor r,
+                                              torch::Tensor w, torch::Tensor k, torch::Tensor v, torch::Tensor a,
+                                              torch::Tensor b, torch::Tensor output, torch::Tensor state_dot_a,
+                                              double scale, std::optional<torch::Tensor> decay_bias) {
+  check_cuda_contiguous(boundary, "boundary");
+  check_cuda_contiguous(cs, "chunk_token_starts");
+  TORCH_CHECK(r.dim() == 3, "token tensors must have shape [N,H,D]");
+  TORCH_CHECK(r.size(2) == 64, "this build replays head size 64 only, got ", r.size(2));
+  TORCH_CHECK(boundary.scalar_type() == torch::kFloat32 && boundary.dim() == 4 && boundary.size(0) == cs.numel() &&
+                  boundary.size(1) == r.size(1) && boundary.size(2) == 64 && boundary.size(3) == 64,
+              "boundary must be float32 [Cn,H,D,D]");
+  const c10::cuda::CUDAGuard guard(r.device());
+  auto sco = torch::arange(cs.numel() + 1, cs.options());
+  auto pool = boundary.clone();
+  wkv7_chunk_forward(sco, cs, ce, pool, r, w, k, v, a, b, output, scale, decay_bias, std::nullopt, std::nullopt,
+                     std::nullopt, std::nullopt, state_dot_a, 1);
+}
+
+// csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_forward.cpp:26-56 of the reference: `state` [B,H,D,D] is updated
+// in place to the final state; output, boundary and state_dot_a are filled.
+void statetune_recurrent_fp32io16_forward(torch::Tensor sco, torch::Tensor cs, torch::Tensor ce, torch::Tensor state,
+                                          torch::Tensor r, torch::Tensor w, torch::Tensor k, torch::Tensor v,
+                                          torch::Tensor a, torch::Tensor b, torch::Tensor output, torch::Tensor boundary,
+                                          torch::Tensor state_dot_a, double scale) {
+  TORCH_CHECK(r.dim() == 3 && r.size(2) == 64, "this build trains head size 64 only");
+  wkv7_chunk_forward(sco, cs, ce, state, r, w, k, v, a, b, output, scale, std::nullopt, std::nullopt, boundary,
+                     std::nullopt, std::nullopt, state_dot_a, 1);
+}
+
+// csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_backward.cpp:34-82 of the reference: gradients are written into
+// the tensors the caller passes (None = not wanted).
+void statetune_recurrent_fp32io16_backward(torch::Tensor sco, torch::Tensor cs, torch::Tensor ce,
+                                           torch::Tensor final_state, torch::Tensor r, torch::Tensor w, torch::Tensor k,
+                                           torch::Tensor v, torch::Tensor a, torch::Tensor b, torch::Tensor state_dot_a,
+                                           std::optional<torch::Tensor> grad_output,
+                                           std::optional<torch::Tensor> grad_final_state, torch::Tensor boundary,
+                                           std::optional<torch::Tensor> grad_r, std::optional<torch::Tensor> grad_w,
+                                           std::optional<torch::Tensor> grad_k, std::optional<torch::Tensor> grad_v,
+                                           std::optional<torch::Tensor> grad_a, std::optional<torch::Tensor> grad_b,
+                                           std::optional<torch::Tensor> grad_initial_state, double scale) {
+  TORCH_CHECK(r.dim() == 3 && r.size(2) == 64, "this build trains head size 64 only");
+  std::optional<torch::Tensor> go, gf;
+  if (grad_output.has_value()) go = grad_output->contiguous();
+  if (grad_final_state.has_value()) gf = grad_final_state->contiguous().to(torch::kFloat32);
+  auto replayed = wkv7_chunk_replay(cs, ce, boundary, r, w, k, v, a, b, std::nullopt);
+  auto g = wkv7_backward(sco, cs, ce, final_state, boundary, std::get<1>(replayed), state_dot_a, r, w, k, v, a, b, go, gf,
+                         scale);
+  const std::optional<torch::Tensor>* outs[7] = {&grad_r, &grad_w, &grad_k, &grad_v, &grad_a, &grad_b,
+                                                 &grad_initial_state};
+  for (int i = 0; i < 7; ++i)
+    if (outs[i]->has_value()) (*outs[i])->copy_(g[i]);
+}
+
 // ---- training-side TMix glue on dense [B,T,C] tensors (names and argument order of the reference's
 // pretrain_tmix_* extension functions, flashrwkv2/tmix/{a_gate,vres_gate,mix6,kk_pre,lnx_rkvres_xg}) ----------
 void check_dense(const torch::Tensor& t, const char* name, const torch::Tensor& ref) {
@@ -1280,6 +1387,24 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("head_size") = 64, py::arg("batch_size") = 1, py::arg("max_seqlen") = 1);
   m.def("tmix_vres_gate_forward_varlen", &tmix_vres_gate_forward_varlen, py::arg("v"), py::arg("v_first"),
         py::arg("v0"), py::arg("v12"));
+  m.def("infer_chunk_bf16_forward_varlen", &infer_chunk_bf16_forward_varlen_native, py::arg("r"),
+        py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"), py::arg("state_pool"),
+        py::arg("cu_seqlens"), py::arg("state_indices"), py::arg("chunk_size") = 16, py::arg("max_seqlen") = -1,
+        py::arg("scale") = 1.0, py::arg("decay_bias") = py::none());
+  m.def("rl_infctx_chunk_fp32io16_backward_replay", &rl_infctx_chunk_fp32io16_backward_replay,
+        py::arg("chunk_token_starts"), py::arg("chunk_token_ends"), py::arg("boundary"), py::arg("r"),
+        py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"), py::arg("output"),
+        py::arg("state_dot_a"), py::arg("scale") = 1.0, py::arg("decay_bias") = py::none());
+  m.def("statetune_recurrent_fp32io16_forward", &statetune_recurrent_fp32io16_forward,
+        py::arg("sequence_chunk_offsets"), py::arg("chunk_token_starts"), py::arg("chunk_token_ends"), py::arg("state"),
+        py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"), py::arg("output"),
+        py::arg("boundary"), py::arg("state_dot_a"), py::arg("scale") = 1.0);
+  m.def("statetune_recurrent_fp32io16_backward", &statetune_recurrent_fp32io16_backward,
+        py::arg("sequence_chunk_offsets"), py::arg("chunk_token_starts"), py::arg("chunk_token_ends"),
+        py::arg("final_state"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),
+        py::arg("b"), py::arg("state_dot_a"), py::arg("grad_output"), py::arg("grad_final_state"), py::arg("boundary"),
+        py::arg("grad_r"), py::arg("grad_decay_logits"), py::arg("grad_k"), py::arg("grad_v"), py::arg("grad_a"),
+        py::arg("grad_b"), py::arg("grad_initial_state"), py::arg("scale") = 1.0);
   m.def("wkv7_chunk_replay", &wkv7_chunk_replay, py::arg("chunk_token_starts"), py::arg("chunk_token_ends"),
         py::arg("boundary"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),
         py::arg("b"), py::arg("decay_bias") = py::none());

@@ -457,7 +457,23 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_decode_pipelined_kerne
       const int unit = unit_of(i);
       const int seq = unit / units_per_seq, head0 = kT * (unit % units_per_seq);
       ok = umma::mbar_wait(&full_bar[st], (i / kStages) & 1);
-      if (!ok) break;
+      if (!ok) {
+        // fail closed: this pair's remaining units read as NaN; it never reports them done, so the storer gives
+        // up as well and their state tiles keep the values they had
+        for (int j = i; j < my_units; j += kActivePairs) {
+          const int u2 = unit_of(j);
+          if (kg == 0)
+            for (int t = 0; t < kT; ++t) {
+              const long long tb = ((long long)(u2 / units_per_seq) * num_heads + kT * (u2 % units_per_seq) + t) * kD;
+              const io_t nan16 = IO::store(quiet_nan());
+              for (int e = 0; e < 4; ++e) {
+                y_ptr[tb + col0 + e] = nan16;
+                if (y32_ptr != nullptr) y32_ptr[tb + col0 + e] = quiet_nan();
+              }
+            }
+        }
+        break;
+      }
       unsigned char* stage = smem + st * kStageBytes;
 #pragma unroll 1
       for (int t = 0; t < kT; ++t) {
@@ -479,7 +495,7 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_decode_pipelined_kerne
       if (lane == 0) mbar_arrive(&done_bar[st]);
     }
   }
-  if (!ok && lane == 0 && error_flag != nullptr) atomicExch(error_flag, 4);
+  if (!ok && lane == 0 && error_flag != nullptr) atomicOr(error_flag, FRWKV_META_WAIT_TIMEOUT);
 }
 
 template <typename io_t>
@@ -501,22 +517,30 @@ template <typename io_t>
 int launch_decode(const int* idx, const int* status, float* state, const void* r, const void* w, const void* k,
                   const void* v, const void* a, const void* b, const void* bias, void* y, float* y32,
                   int num_sequences, int num_heads, float scale, int reverse, cudaStream_t stream) {
-  int device = 0, sm_count = 0;
-  cudaGetDevice(&device);
-  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+  // the SM count and the shared-memory opt-in are looked up once per device and kernel, not on every launch
+  static int sm_counts[64] = {};
+  static bool opted_in[64][2] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
+    return fail(FRWKV_ERR_CUDA, "wkv7_recurrent: cannot identify the current device");
+  if (sm_counts[device] == 0) cudaDeviceGetAttribute(&sm_counts[device], cudaDevAttrMultiProcessorCount, device);
+  const int sm_count = sm_counts[device];
   const int tiles = num_sequences * num_heads;
 #define FRWKV_DECODE(KT)                                                                                          \
   {                                                                                                               \
-    cudaError_t e = cudaFuncSetAttribute(wkv7_decode_pipelined_kernel<io_t, KT>,                                  \
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, RingCfg<KT>::kSmem);        \
-    if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "wkv7_recurrent: %s", cudaGetErrorString(e));               \
+    if (!opted_in[device][KT - 1]) {                                                                              \
+      cudaError_t e = cudaFuncSetAttribute(wkv7_decode_pipelined_kernel<io_t, KT>,                                \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, RingCfg<KT>::kSmem);      \
+      if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "wkv7_recurrent: %s", cudaGetErrorString(e));             \
+      opted_in[device][KT - 1] = true;                                                                            \
+    }                                                                                                             \
     const int units = tiles / KT;                                                                                 \
     const int grid = sm_count > 0 && sm_count < units ? sm_count : units;                                         \
     wkv7_decode_pipelined_kernel<io_t, KT><<<grid, kDecodeThreads, RingCfg<KT>::kSmem, stream>>>(                 \
         idx, status, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w), static_cast<const io_t*>(k), \
         static_cast<const io_t*>(v), static_cast<const io_t*>(a), static_cast<const io_t*>(b),                    \
         static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, units, num_heads,                             \
-        (long long)num_sequences * num_heads * kD, scale, reverse, nullptr);                                      \
+        (long long)num_sequences * num_heads * kD, scale, reverse, const_cast<int*>(status));                     \
   }
   if (kDecodeTilesPerStage == 2 && num_heads % 2 == 0) FRWKV_DECODE(2) else FRWKV_DECODE(1)
 #undef FRWKV_DECODE

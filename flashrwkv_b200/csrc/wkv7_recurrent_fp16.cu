@@ -323,7 +323,20 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_fp16_decode_kernel(
       const int seq = unit / units_per_seq, head0 = kT * (unit % units_per_seq);
       const uint32_t elapsed = (uint32_t)(i < kMetaUnits ? elapsed_s[i] : elapsed_pool[slot_of(i)]);
       ok = umma::mbar_wait(&full_bar[st], (i / kStages) & 1);
-      if (!ok) break;
+      if (!ok) {
+        // fail closed: this pair's remaining units read as NaN; it never reports them done, so the storer gives
+        // up as well and their state tiles keep the values they had
+        for (int j = i; j < my_units; j += R::kActivePairs) {
+          const int u2 = unit_of(j);
+          if (kg == 0)
+            for (int t = 0; t < kT; ++t) {
+              const long long tb = ((long long)(u2 / units_per_seq) * num_heads + kT * (u2 % units_per_seq) + t) * kD;
+              const io_t nan16 = IO::store(quiet_nan());
+              for (int e = 0; e < 4; ++e) y_ptr[tb + col0 + e] = nan16;
+            }
+        }
+        break;
+      }
       unsigned char* stage = smem + st * kStageBytes;
       const io_t* tok = reinterpret_cast<const io_t*>(stage + kT * kTileBytes);  // vector j of tile t at (j*kT + t)*64
 #pragma unroll 1
@@ -347,7 +360,7 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_fp16_decode_kernel(
       if (lane == 0) mbar_arrive(&done_bar[st]);
     }
   }
-  if (!ok && lane == 0 && error_flag != nullptr) atomicExch(error_flag, 6);
+  if (!ok && lane == 0 && error_flag != nullptr) atomicOr(error_flag, FRWKV_META_WAIT_TIMEOUT);
 }
 
 // ---- elapsed counters ---------------------------------------------------------------------------------------------------
@@ -387,13 +400,11 @@ int launch_fp16(const int* cu, const int* idx, const int* status, const int* ela
         idx, status, elapsed, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w),                    \
         static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),                    \
         static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), units, num_heads,     \
-        out_elems, scale, reverse, nullptr);                                                                      \
+        out_elems, scale, reverse, const_cast<int*>(status));                                                     \
   }
-    // diagnostic switch FRWKV_FP16_DECODE_TILES=4: four adjacent heads per stage (32 KB copies, six stages);
-    // measured slower at 256 x 32 tiles, 29.8 us per launch against 24.4 us with two heads per stage and twelve stages
-    static const bool four = [] { const char* e = getenv("FRWKV_FP16_DECODE_TILES"); return e && e[0] == '4'; }();
-    if (four && num_heads % 4 == 0) FRWKV_FP16_DECODE(4)
-    else if (num_heads % 2 == 0) FRWKV_FP16_DECODE(2)
+    // two adjacent heads per stage (16 KB copies, twelve stages); four per stage (32 KB copies, six stages) measured
+    // slower at 256 x 32 tiles: 29.8 us per launch against 24.4 us
+    if (num_heads % 2 == 0) FRWKV_FP16_DECODE(2)
     else FRWKV_FP16_DECODE(1)
 #undef FRWKV_FP16_DECODE
     return check_launch("wkv7_fp16_decode_kernel");

@@ -41,6 +41,10 @@ enum {
   FRWKV_META_INVALID_RANGE = 2,
   FRWKV_META_INVALID_SLOT = 4,
   FRWKV_META_DUPLICATE_SLOT = 8,
+  /* Not in the reference: set by a decode kernel of this library whose bounded wait on a copy ran out.  The
+   * sequences it could not finish read as NaN and their state tiles keep their old value; because the bit stays in
+   * the status word, every later call that is given the same word fails closed like a call with bad metadata. */
+  FRWKV_META_WAIT_TIMEOUT = 16,
 };
 
 /* ABI version of this header (bumped on any signature change). */
@@ -74,7 +78,8 @@ int frwkv_validate_recurrent_metadata(const int32_t* cu_seqlens, const int32_t* 
  *   decay_bias : io16 [H, D] or NULL;  y_fp32 : fp32 [total_tokens, H, D] or NULL
  *     (the unrounded outputs, for precision checks)
  *   metadata_status : int32 device word; when *metadata_status != 0 the kernel
- *     fills y with NaN and leaves the state pool untouched.
+ *     fills y with NaN and leaves the state pool untouched.  The kernels only read it, except that a decode
+ *     kernel whose bounded wait runs out ORs FRWKV_META_WAIT_TIMEOUT into it (hence the cast from const).
  *   head_size 64 (tuned kernels), 128 or 256 (general kernel).
  */
 int frwkv_wkv7_recurrent_fp32io16_forward_varlen(

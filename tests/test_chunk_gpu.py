@@ -200,3 +200,42 @@ def test_fused_and_two_kernel_forms_agree_many_pairs(oracle, dtype):
         assert max_abs(y32, ref["y"]) <= Y_MAX_ABS
         assert _state_rel(pool, ref["state_pool"]) <= STATE_REL
     assert max_abs(outs[0][0], outs[1][0]) <= Y_MAX_ABS
+
+
+def test_reference_named_native_chunk_entries(oracle):
+    """`_C.infer_chunk_bf16_forward_varlen` and `_C.rl_infctx_chunk_fp32io16_backward_replay` with the reference's
+    argument order (csrc/sm120/tmix/wkv7/infer_chunk_bf16_forward_varlen.cpp:173-183 and
+    csrc/sm90/rl_infctx/wkv7/rl_infctx_chunk_fp32io16_backward.cpp:102-135 there)."""
+    from flashrwkv_b200 import _ext, synthetic
+    from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata, wkv7_chunk_forward
+
+    C = _ext.extension()
+    g = load_golden("chunk_bf16")
+    toks = [g[n].cuda() for n in TOKENS]
+    pool = g["state_pool"].cuda().clone()
+    y, same_pool = C.infer_chunk_bf16_forward_varlen(*toks, pool, g["cu_seqlens"].cuda(), g["state_indices"].cuda(), 8,
+                                                    -1, g["scale"])
+    torch.cuda.synchronize()
+    assert same_pool.data_ptr() == pool.data_ptr()
+    assert rel_rmse(y.float().cpu(), g["y"].float()) <= 2e-2
+    assert rel_rmse(pool.float().cpu(), g["final_pool"].float()) <= 2e-2
+
+    # replay stage: output and state_dot_a of every chunk from its boundary state
+    H, D, lengths = 2, 64, (70, 16, 33)
+    N = sum(lengths)
+    toks = synthetic.wkv7_inputs(N, H, D, seed=91, dtype=torch.float16)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32)
+    pool0 = synthetic.state_pool(len(lengths), H, D, seed=92)
+    bias = (torch.randn(H, D) * 0.1).to(torch.float16)
+    meta = make_chunk_metadata(cu.cuda(), 32)
+    dtoks = [t.cuda() for t in toks]
+    _, boundary, _ = wkv7_chunk_forward(*dtoks, state=pool0.cuda(), chunk_metadata=meta, scale=0.6,
+                                        decay_bias=bias.cuda(), want_boundary=True)
+    out = torch.empty_like(dtoks[3])
+    sda = torch.empty(N, H, D, device="cuda")
+    C.rl_infctx_chunk_fp32io16_backward_replay(meta[1], meta[2], boundary, *dtoks, out, sda, 0.6, bias.cuda())
+    torch.cuda.synchronize()
+    want = oracle.forward(*toks, state_pool=pool0, cu_seqlens=cu, scale=0.6, decay_bias=bias, want_state_dot_a=True)
+    assert torch.allclose(out.float().cpu(), torch.as_tensor(want["y"]).float(), rtol=0.0, atol=2e-2)
+    assert rel_rmse(out.float().cpu(), want["y"]) <= 7e-3
+    assert rel_rmse(sda.cpu(), want["state_dot_a"]) <= 2e-3

@@ -352,3 +352,27 @@ def test_head_sizes_128_and_256_vs_oracle(oracle, D, dtype):
     assert _state_rel(d_pool, ref["state_pool"]) <= STATE_REL
     assert torch.equal(y, y32.to(dtype))
     assert torch.equal(d_pool[[1, 3]].cpu(), pool[[1, 3]])
+
+
+def test_wait_timeout_bit_in_the_status_word_fails_closed():
+    """A decode kernel whose bounded wait ran out leaves FRWKV_META_WAIT_TIMEOUT (16) in the ticket's status word;
+    from then on every call with that ticket must behave like a call with bad metadata: NaN outputs, pool untouched."""
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+
+    B, H, D = 48, 32, 64  # 1536 tiles: the bulk-copy ring kernel
+    toks = [t.cuda() for t in synthetic.wkv7_inputs(B, H, D, seed=3)]
+    cu, idx = (t.cuda() for t in synthetic.equal_length_metadata(B, 1))
+    pool = synthetic.state_pool(B, H, D, seed=4, device="cuda")
+    ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=B, state_pool_size=B, max_seqlen=1)
+    y = F.infer_recurrent_fp32io16_forward_varlen(*toks, state_pool=pool, cu_seqlens=cu, state_indices=idx,
+                                                  validated_metadata=ticket, max_seqlen=1)
+    torch.cuda.synchronize()
+    assert int(ticket._status().item()) == 0 and torch.isfinite(y.float()).all()
+    before = pool.clone()
+    ticket._status().fill_(16)
+    y = F.infer_recurrent_fp32io16_forward_varlen(*toks, state_pool=pool, cu_seqlens=cu, state_indices=idx,
+                                                  validated_metadata=ticket, max_seqlen=1)
+    torch.cuda.synchronize()
+    assert torch.isnan(y.float()).all()
+    assert torch.equal(pool, before)

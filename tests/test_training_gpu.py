@@ -78,3 +78,34 @@ def test_gradients_vs_oracle_backward(oracle, lengths):
     for t, name in zip(dtoks, names):
         assert rel_rmse(t.grad.float().cpu(), want[name]) <= 8e-3, name
     assert rel_rmse(dS0.grad.cpu(), want["initial_state"]) <= 8e-3
+
+
+def test_reference_named_native_statetune_entries_match_golden():
+    """`_C.statetune_recurrent_fp32io16_forward` / `_backward` with the reference's argument order
+    (csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_{forward,backward}.cpp there): in-place final state, outputs and
+    gradients written into caller tensors, optional gradients skipped."""
+    from flashrwkv_b200 import _ext
+
+    C = _ext.extension()
+    g = load_golden("statetune")
+    toks = [g[n].cuda() for n in TOKENS]
+    sco, cs, ce = (g[n].cuda() for n in ("seq_chunk_offsets", "chunk_starts", "chunk_ends"))
+    state = g["S0"].cuda().clone()
+    y = torch.empty_like(toks[3])
+    boundary = torch.empty(cs.numel(), state.shape[1], 64, 64, device="cuda")
+    sda = torch.empty(toks[0].shape, device="cuda")
+    C.statetune_recurrent_fp32io16_forward(sco, cs, ce, state, *toks, y, boundary, sda, g["scale"])
+    torch.cuda.synchronize()
+    for got, name in zip((y, state, boundary, sda), ("y", "final_state", "boundary", "state_dot_a")):
+        assert torch.allclose(got.float().cpu(), g[name].float(), atol=3e-4, rtol=3e-4), name
+    # the golden loss is sum(y^2) + sum(final^2)
+    go = (2 * y.float()).to(y.dtype)
+    gf = 2 * state
+    grads = [torch.empty_like(t) for t in toks] + [torch.empty_like(state)]
+    C.statetune_recurrent_fp32io16_backward(sco, cs, ce, state, *toks, sda, go, gf, boundary, *grads[:3], None,
+                                            *grads[4:], g["scale"])
+    torch.cuda.synchronize()
+    for t, name in zip(grads, ("dr", "dw", "dk", "dv", "da", "db", "dS0")):
+        if name == "dv":
+            continue  # passed as None: not wanted
+        assert torch.allclose(t.float().cpu(), g[name], atol=6e-4, rtol=6e-3), name

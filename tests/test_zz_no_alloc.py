@@ -32,7 +32,7 @@ def _call(lib, fn_name, meta, pool, toks, y, y32, workspace, N, B, Cn, H, scale)
     return rc, flag
 
 
-def test_noalloc_entry_matches_workspace_entry_twice_in_a_row():
+def test_noalloc_entry_matches_workspace_entry_twice_in_a_row(oracle):
     from flashrwkv_b200 import _ext, synthetic
     from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata
 
@@ -66,6 +66,11 @@ def test_noalloc_entry_matches_workspace_entry_twice_in_a_row():
         assert float((pool_a - pool_b).norm() / pool_a.norm()) <= 1e-3
         assert torch.equal(y_a, y_b) and torch.equal(pool_a, pool_b)
         assert not torch.equal(pool_a, pool0)
+        # and against the CPU oracle on the same 16-bit inputs, with the parity bars of the chunk tests
+        want = oracle.forward(*(t.cpu() for t in toks), state_pool=pool0.cpu(), cu_seqlens=cu.cpu(), scale=0.9)
+        assert float((y32_b.cpu() - torch.from_numpy(want["y"])).abs().max()) <= 2e-2
+        ref_pool = torch.from_numpy(want["state_pool"])
+        assert float((pool_b.cpu() - ref_pool).norm() / ref_pool.norm()) <= 1e-3
 
 
 def test_noalloc_entry_refuses_sizes_beyond_its_workspace():
