@@ -6,9 +6,12 @@
 Workload (N = 1 and every N): recurrent decode at B=256 sequences, H=32, D=64,
 bf16 tokens, fp32 state pool read and written in place.  One benchmark *step* is
 one pass over a batch of synthetic input: 256 consecutive decode steps of the 256
-sequences (65 536 tokens, 256 kernel launches).  With N GPUs every rank owns its
-own 256 sequences and state pool (weak scaling, no collective on the data path);
-`value` is the total tokens/s over all ranks using the slowest rank's time.
+sequences (65 536 tokens, 256 kernel launches per rank).  With N GPUs the 256
+sequences are split into contiguous blocks of 256/N per rank, each rank owning its
+slice of the state pool (strong scaling, no collective on the data path); `value`
+is the job's tokens/s using the slowest rank's time.  For N > 1 `extras` adds the
+timed all-gather of one step's outputs, the weak-scaling figure (256 sequences per
+rank) and the chunked prefill with its 8 sequences split over the ranks.
 
 The line printed by rank 0 carries, besides the contract keys, `roofline`
 (algorithmic bytes per launch / measured launch time against the measured HBM
@@ -41,9 +44,6 @@ METRIC = "WKV7 recurrent decode tokens/s (B=256,H=32,D=64, fp32 state in place)"
 # + 7*D*2 (r,w,k,v,a,b in, y out)
 BYTES_PER_UNIT = 2 * D * D * 4 + 7 * D * 2
 BYTES_PER_LAUNCH = B * H * BYTES_PER_UNIT
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch at this size, from the ncu
-# capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 222_550_000
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -182,7 +182,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"recurrent decode B={B} H={H} D={D}, fp32 state, CPU port of the reference "
                                f"recurrence; each step = {sample} decode steps (bounded sample)"},
         "cpu_baseline": base,
@@ -419,12 +419,70 @@ def _extras(dev):
     return out
 
 
+class DecodeLoop:
+    """The benchmark step on one rank: DECODE_STEPS_PER_STEP decode launches of `n_seq` sequences, replayed as one
+    CUDA graph (or launched from Python), over one state pool or over several pools visited in turn."""
+
+    def __init__(self, F, synthetic, dev, n_seq: int, seed: int, pools: int = 1, graph: bool = True, torch=None):
+        self.n_seq = n_seq
+        self.cu, self.idx = (t.to(dev) for t in synthetic.equal_length_metadata(n_seq, 1))
+        self.pools = [synthetic.state_pool(n_seq, H, D, seed=seed + 31 * j, device=dev) for j in range(pools)]
+        # each decode step's six token tensors live in one pinned host buffer [6, n_seq, H, D] (what a serving
+        # host's staging area looks like); ring_host[i] are views of it
+        self.ring_packed = [torch.stack(synthetic.wkv7_inputs(n_seq, H, D, seed=seed + 1 + i)).pin_memory()
+                            for i in range(TOKEN_RING)]
+        self.ring_host = [list(p.unbind(0)) for p in self.ring_packed]
+        ring = [[t.to(dev) for t in step] for step in self.ring_host]
+        self.ticket = F.prepare_recurrent_metadata(self.cu, self.idx, total_tokens=n_seq, state_pool_size=n_seq,
+                                                   max_seqlen=1)
+        self.kw = dict(cu_seqlens=self.cu, state_indices=self.idx, max_seqlen=1)
+
+        def steps(ticket):
+            for i in range(DECODE_STEPS_PER_STEP):
+                F.infer_recurrent_fp32io16_forward_varlen(*ring[i % TOKEN_RING], state_pool=self.pools[i % pools],
+                                                          validated_metadata=ticket, **self.kw)
+
+        self.step = lambda: steps(self.ticket)
+        self.launch_mode = f"{DECODE_STEPS_PER_STEP} Python launches per step"
+        if graph:
+            # every operator that takes a prepared ticket launches without host synchronisation, so the whole
+            # step captures; a ticket is bound to the stream it was prepared on
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                g_ticket = F.prepare_recurrent_metadata(self.cu, self.idx, total_tokens=n_seq, state_pool_size=n_seq,
+                                                        max_seqlen=1)
+                F.infer_recurrent_fp32io16_forward_varlen(*ring[0], state_pool=self.pools[0],
+                                                          validated_metadata=g_ticket, **self.kw)
+                torch.cuda.synchronize(dev)
+                self.graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.graph, stream=side):
+                    steps(g_ticket)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            self.step = self.graph.replay
+            self.launch_mode = f"one CUDA graph of the {DECODE_STEPS_PER_STEP} decode launches per step"
+
+    @property
+    def bytes_per_launch(self) -> int:
+        return self.n_seq * H * BYTES_PER_UNIT
+
+
+def _profiled_traffic():
+    """DRAM bytes per decode launch at the benchmark's full batch, from the ncu capture kept beside its summary."""
+    p = ROOT / "profiles" / "wkv7_decode_pipelined_B256_H32.json"
+    try:
+        d = json.loads(p.read_text())
+        return int(d["dram_bytes_per_launch"]), d.get("source", p.name)
+    except Exception:
+        return None, None
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
 
     import flashrwkv_b200 as F
-    from flashrwkv_b200 import synthetic
+    from flashrwkv_b200 import sharding, synthetic
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -438,51 +496,22 @@ def run_b200(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    cu, idx = (t.to(dev) for t in synthetic.equal_length_metadata(B, 1))
-    pool = synthetic.state_pool(B, H, D, seed=1000 + rank, device=dev)
-    # each decode step's six token tensors live in one pinned host buffer [6, B, H, D] (what a serving host's staging
-    # area looks like); ring_host[i] are views of it
-    ring_packed = [torch.stack(synthetic.wkv7_inputs(B, H, D, seed=20260805 + 97 * rank + i)).pin_memory()
-                   for i in range(TOKEN_RING)]
-    ring_host = [list(p.unbind(0)) for p in ring_packed]
-    ring = [[t.to(dev) for t in step] for step in ring_host]
-    ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=B, state_pool_size=B, max_seqlen=1)
-    kw = dict(state_pool=pool, cu_seqlens=cu, state_indices=idx, validated_metadata=ticket, max_seqlen=1)
-
-    def device_step():
-        for i in range(DECODE_STEPS_PER_STEP):
-            F.infer_recurrent_fp32io16_forward_varlen(*ring[i % TOKEN_RING], **kw)
-
-    # The 256 decode steps of a benchmark step as ONE CUDA graph (every operator taking a prepared ticket launches
-    # without host synchronisation, so the whole step captures); --no-graph launches them one by one from Python,
-    # which at 45 us per kernel is bound by the host's launch rate.
-    launch_mode = "256 Python launches per step"
-    if not args.no_graph:
-        side = torch.cuda.Stream(dev)
-        side.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(side):
-            g_ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=B, state_pool_size=B, max_seqlen=1)
-            g_kw = dict(kw, validated_metadata=g_ticket)  # a ticket is bound to the stream it was prepared on
-            F.infer_recurrent_fp32io16_forward_varlen(*ring[0], **g_kw)
-            torch.cuda.synchronize(dev)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
-                for i in range(DECODE_STEPS_PER_STEP):
-                    F.infer_recurrent_fp32io16_forward_varlen(*ring[i % TOKEN_RING], **g_kw)
-        torch.cuda.current_stream(dev).wait_stream(side)
-        device_step = graph.replay
-        launch_mode = "one CUDA graph of the 256 decode launches per step"
+    # the fixed batch of B sequences is split over the ranks: rank i owns a contiguous block and its state slots
+    plan = sharding.shard_plan(B, H, world, rank)
+    s0, s1 = plan["sequences"]
+    n_local = s1 - s0
+    loop = DecodeLoop(F, synthetic, dev, n_local, seed=20260805 + 1009 * rank, graph=not args.no_graph, torch=torch)
 
     # end to end: every decode step's six token tensors come from pinned host memory and its output goes back to
     # pinned host memory, through the package's three-stream host loop (copy-in / kernel / copy-out overlap)
     from flashrwkv_b200.host_io import HostDecodeLoop
 
-    host_loop = HostDecodeLoop(ring_host[0], **kw)
-    y_hosts = [torch.empty((B, H, D), dtype=torch.bfloat16).pin_memory() for _ in range(4)]
+    host_loop = HostDecodeLoop(loop.ring_host[0], state_pool=loop.pools[0], validated_metadata=loop.ticket, **loop.kw)
+    y_hosts = [torch.empty((n_local, H, D), dtype=torch.bfloat16).pin_memory() for _ in range(4)]
 
     def e2e_step():
         for i in range(DECODE_STEPS_PER_STEP):
-            host_loop.submit(ring_packed[i % TOKEN_RING], y_hosts[i % len(y_hosts)])
+            host_loop.submit(loop.ring_packed[i % TOKEN_RING], y_hosts[i % len(y_hosts)])
         host_loop.drain()
 
     def barrier():
@@ -514,33 +543,92 @@ def run_b200(args):
     sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
                            int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
     sampler.start()
-    ms = timed(device_step, args.warmup, args.steps, sampler)
+    ms = timed(loop.step, args.warmup, args.steps, sampler)
     sampler.stop()
     e2e_steps = max(1, min(args.steps, 5))
     e2e_ms = timed(e2e_step, 1, e2e_steps) if not args.kernel_only else float("nan")
 
-    tokens_per_step = B * DECODE_STEPS_PER_STEP * world
+    tokens_per_step = B * DECODE_STEPS_PER_STEP  # the whole job: all ranks together decode the B sequences
     value = tokens_per_step * args.steps / (ms * 1e-3)
     e2e_value = tokens_per_step * e2e_steps / (e2e_ms * 1e-3)
     launches = args.steps * DECODE_STEPS_PER_STEP
     launch_s = ms * 1e-3 / launches
     peak, peak_kind = _peaks()
-    achieved = BYTES_PER_LAUNCH / launch_s / 1e9
+    achieved = loop.bytes_per_launch / launch_s / 1e9
+    working_mb = n_local * H * D * D * 4 / 1e6
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "peak_source": f"of {peak_kind}", "kernel": "wkv7_decode_pipelined_kernel",
+                "algorithmic_bytes_per_launch": loop.bytes_per_launch, "us_per_launch": launch_s * 1e6,
+                "note": "achieved = algorithmic bytes / time: an effective bandwidth that counts state tiles found in L2 "
+                        "(the traversal order alternates between launches) as if they came from HBM"}
+    extras_multi = {}
+    if world == 1:
+        traffic, source = _profiled_traffic()
+        if traffic is not None:
+            roofline["traffic"] = traffic
+            roofline["traffic_source"] = source
+            roofline["frac_dram"] = traffic / launch_s / 1e9 / peak
+        if not args.kernel_only:
+            # cold-L2 companion: two pools visited in turn (2 x 134 MB), so that no state tile of a launch is still
+            # in the 126 MB L2 when its pool comes round again
+            cold = DecodeLoop(F, synthetic, dev, n_local, seed=77, pools=2, graph=not args.no_graph, torch=torch)
+            cold_ms = timed(cold.step, 2, max(2, args.steps // 4))
+            cold_s = cold_ms * 1e-3 / (max(2, args.steps // 4) * DECODE_STEPS_PER_STEP)
+            roofline["cold_l2"] = {"us_per_launch": cold_s * 1e6, "achieved": cold.bytes_per_launch / cold_s / 1e9,
+                                   "frac": cold.bytes_per_launch / cold_s / 1e9 / peak,
+                                   "how": "two state pools visited alternately: every tile comes from HBM"}
+            del cold
+    else:
+        # the optional collective: all ranks' outputs of one decode step gathered on every rank (NCCL all-gather)
+        y_local = torch.zeros((n_local, H, D), dtype=torch.bfloat16, device=dev)
+        gather = lambda: sharding.gather_shards(y_local, plan, total=B)  # noqa: E731
+        full = gather()
+        reps = 20
+        g_ms = timed(gather, 3, reps)
+        extras_multi["gather_outputs"] = {"us": g_ms / reps * 1e3, "bytes_per_rank": y_local.numel() * 2,
+                                          "gathered_shape": list(full.shape), "backend": "nccl all_gather",
+                                          "note": "reported apart from the compute time; the data path has no collective"}
+        if not args.kernel_only:
+            # weak scaling beside it: every rank decodes a full batch of B sequences of its own
+            weak = DecodeLoop(F, synthetic, dev, B, seed=555 + rank, graph=not args.no_graph, torch=torch)
+            w_steps = max(2, args.steps // 4)
+            w_ms = timed(weak.step, 2, w_steps)
+            extras_multi["weak_scaling"] = {"tokens_per_s": B * world * DECODE_STEPS_PER_STEP * w_steps / (w_ms * 1e-3),
+                                            "sequences_per_gpu": B, "global_sequences": B * world,
+                                            "ms_per_step": w_ms / w_steps}
+            del weak
+            # chunked prefill (B=8 sequences of 4096 tokens, H=32) with the sequences split over the ranks
+            from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata, wkv7_chunk_forward
+
+            Bc, T, Hc = 8, 4096, 32
+            cplan = sharding.shard_plan(Bc, Hc, world, rank)
+            nb = cplan["sequences"][1] - cplan["sequences"][0]
+            nh = cplan["heads"][1] - cplan["heads"][0]
+            toks = [t.to(dev) for t in synthetic.wkv7_inputs(nb * T, nh, D, seed=11 + rank)]
+            ccu, _ = synthetic.equal_length_metadata(nb, T, device=dev)
+            meta = make_chunk_metadata(ccu, 64)
+            cpool = synthetic.state_pool(nb, nh, D, seed=12, device=dev)
+            c_ms = timed(lambda: wkv7_chunk_forward(*toks, state=cpool, chunk_metadata=meta), 2, 5)
+            extras_multi["chunked_prefill"] = {"workload": f"B={Bc} T={T} H={Hc} split over {world} ranks by "
+                                                           f"{cplan['axis']}: {nb} sequence(s) x {nh} heads per rank",
+                                               "tokens_per_s": Bc * T * 5 / (c_ms * 1e-3), "ms": c_ms / 5}
 
     if rank == 0:
         cpu = _cpu_baseline(32) if world == 1 and not args.kernel_only else None
+        l2_note = (f"no flush: the per-launch working set ({working_mb:.0f} MB of state) exceeds the 126 MB L2"
+                   if working_mb > 126 else
+                   f"the per-rank working set ({working_mb:.0f} MB of state) fits the 126 MB L2, so this split is bound "
+                   f"by launch latency and L2, not by HBM")
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"recurrent decode B={B} H={H} D={D} per GPU, bf16 tokens, fp32 state, "
+            "config": {"workload": f"recurrent decode B={B} H={H} D={D}, bf16 tokens, fp32 state, "
                                    f"{DECODE_STEPS_PER_STEP} consecutive decode steps per step",
-                       "launch": launch_mode, "global_sequences": B * world, "parallelism": f"sequences sharded over {world} GPU(s)",
-                       "l2": "no flush: per-launch working set (134 MB state + 7 MB tokens) exceeds the 126 MB L2"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                         "peak_source": f"of {peak_kind}", "kernel": "wkv7_decode_pipelined_kernel",
-                         "algorithmic_bytes_per_launch": BYTES_PER_LAUNCH, "us_per_launch": launch_s * 1e6},
+                       "launch": loop.launch_mode, "global_sequences": B, "sequences_per_gpu": n_local,
+                       "parallelism": f"the {B} sequences split over {world} GPU(s), no collective on the data path",
+                       "l2": l2_note},
+            "roofline": roofline,
             "e2e": {"value": e2e_value, "unit": "tokens/s",
                     "h2d_bytes_per_step": 6 * B * H * D * 2 * DECODE_STEPS_PER_STEP,
                     "d2h_bytes_per_step": B * H * D * 2 * DECODE_STEPS_PER_STEP, "steps": e2e_steps},
@@ -549,6 +637,8 @@ def run_b200(args):
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if extras_multi:
+            line["extras"] = extras_multi
         if world == 1 and not args.kernel_only and not args.no_extras:
             try:
                 line["extras"] = _extras(dev)
@@ -557,6 +647,108 @@ def run_b200(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# ---- small workloads for profiler captures (python bench.py --profile-case NAME) -------------------------------
+# Each holds well under a few GB on the device, uses inputs larger than the 126 MB L2 where DRAM figures matter,
+# runs a handful of launches and exits, so that an `ncu` capture of one of its kernels ends by itself:
+#   chunk      chunked forward, fused kernel: B=8, T=1024, H=32 (256 (sequence, head) pairs, 4096 (chunk, head) items)
+#   chunk2k    chunked forward, build + scan kernels: B=2, T=4096, H=32 (4096 (chunk, head) items)
+#   train      StateTune forward + backward: B=2, T=2048, H=32
+#   train512   the same at B=8, T=512, H=64: 512 (sequence, head) pairs, as in the training configuration
+#   tmix       one TMix layer's projections at C=2048 for M in (4, 512)
+#   decode     recurrent decode steps at B=256, H=32 (the benchmark's shape, 8 launches)
+#   decode16   the same on an fp16 state pool
+#   glue       training-side TMix glue, forward + backward of the five operators: B=2, T=4096, C=4096
+def _profile_case(name: str) -> None:
+    import torch
+
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+    from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata, wkv7_chunk_forward
+
+    def case_chunk(reps: int = 3, B: int = 8, T: int = 1024, H: int = 32, path: int = 1):
+        toks = [t.cuda() for t in synthetic.wkv7_inputs(B * T, H, D, seed=1)]
+        cu, _ = synthetic.equal_length_metadata(B, T, device="cuda")
+        pool = synthetic.state_pool(B, H, D, seed=2, device="cuda")
+        meta = make_chunk_metadata(cu, 64)
+        for _ in range(reps):
+            wkv7_chunk_forward(*toks, state=pool, chunk_metadata=meta, path=path)
+
+    def case_train(reps: int = 2, B: int = 2, T: int = 2048, H: int = 32):
+        toks = [t.cuda().requires_grad_() for t in synthetic.wkv7_inputs(B * T, H, D, seed=3)]
+        S0 = synthetic.state_pool(B, H, D, seed=4, device="cuda").requires_grad_()
+        cu, _ = synthetic.equal_length_metadata(B, T, device="cuda")
+        meta = make_chunk_metadata(cu, 64)
+        dy = torch.randn(B * T, H, D, device="cuda").to(torch.bfloat16)
+        for _ in range(reps):
+            out = F.statetune_recurrent_fp32io16(S0, *meta, *toks)
+            out[0].backward(dy)
+
+
+    def case_tmix(reps: int = 3):
+        C, H = 2048, 32
+        g = torch.Generator().manual_seed(3)
+        wt = lambda n, k: (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).cuda()  # noqa: E731
+        ranks = {"w": 96, "a": 96, "g": 256, "v": 64}
+        Wr = wt(C, C)
+        w1 = {n: wt(r, C) for n, r in ranks.items()}
+        w2 = {n: wt(C, r) for n, r in ranks.items()}
+        v0 = torch.rand(C, generator=g).to(torch.bfloat16).cuda()
+        for M in (4, 512):
+            xs = [torch.randn(M, C, generator=g).to(torch.bfloat16).cuda() for _ in range(6)]
+            for _ in range(reps):
+                F.infer_tmix_linear_forward_varlen(xs[0], Wr)
+                feats = F.infer_tmix_lowrank_wagv_in_forward_varlen(xs[1], xs[2], xs[3], xs[4], w1["w"], w1["a"], w1["g"],
+                                                                    w1["v"])
+                F.infer_tmix_lowrank_vres_forward_varlen(*feats, w2["w"], w2["a"], w2["g"], w2["v"], xs[4], xs[5], v0)
+
+
+    def case_decode(reps: int = 8):
+        cu, idx = synthetic.equal_length_metadata(B, 1, device="cuda")
+        pool = synthetic.state_pool(B, H, D, seed=5, device="cuda")
+        toks = [t.cuda() for t in synthetic.wkv7_inputs(B, H, D, seed=6)]
+        ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=B, state_pool_size=B, max_seqlen=1)
+        for _ in range(reps):
+            F.infer_recurrent_fp32io16_forward_varlen(*toks, state_pool=pool, cu_seqlens=cu, state_indices=idx,
+                                                      validated_metadata=ticket, max_seqlen=1)
+
+
+    def case_decode16(reps: int = 8):
+        cu, idx = synthetic.equal_length_metadata(B, 1, device="cuda")
+        pool = synthetic.state_pool(B, H, D, seed=5, device="cuda").half()
+        elapsed = torch.zeros(B, dtype=torch.int32, device="cuda")
+        toks = [t.cuda() for t in synthetic.wkv7_inputs(B, H, D, seed=6)]
+        ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=B, state_pool_size=B, max_seqlen=1)
+        for _ in range(reps):
+            F.infer_recurrent_fp16_forward_varlen(*toks, state_pool=pool, elapsed_state_pool=elapsed, cu_seqlens=cu,
+                                                  state_indices=idx, validated_metadata=ticket, max_seqlen=1)
+            F.infer_recurrent_fp16_advance_i32(elapsed, 1)
+
+
+    def case_glue(reps: int = 2):
+        B, T, C = 2, 4096, 4096
+        gen = torch.Generator(device="cuda").manual_seed(7)
+        rn = lambda *s: torch.randn(*s, device="cuda", generator=gen).to(torch.bfloat16).requires_grad_()  # noqa: E731
+        x, r, k, v, g = (rn(B, T, C) for _ in range(5))
+        vecs = [rn(C) for _ in range(6)]
+        r_k = rn(C // D, D)
+        go = [torch.randn(B, T, C, device="cuda", generator=gen).to(torch.bfloat16) for _ in range(6)]
+        for _ in range(reps):
+            outs = [F.pretrain_tmix_a_gate_bf16(vecs[0], x), F.pretrain_tmix_vres_gate_bf16(x, r, vecs[0], k),
+                    *F.pretrain_tmix_kk_pre_bf16(x, vecs[0], r, vecs[1]),
+                    F.pretrain_tmix_lnx_rkvres_xg_bf16(x, r, k, v, r_k, vecs[1], vecs[2], g)]
+            torch.autograd.backward(outs, go[:len(outs)])
+            torch.autograd.backward(F.pretrain_tmix_mix6_bf16(x, *vecs), go)
+
+    cases = {"chunk": case_chunk, "chunk2k": lambda: case_chunk(3, 2, 4096, 32, 0), "train": case_train,
+             "train512": lambda: case_train(2, 8, 512, 64), "tmix": case_tmix, "decode": case_decode,
+             "decode16": case_decode16, "glue": case_glue}
+    if name not in cases:
+        raise SystemExit("unknown profile case; one of: " + ", ".join(sorted(cases)))
+    cases[name]()
+    torch.cuda.synchronize()
+    print(f"profile case {name}: done")
 
 
 def main():
@@ -569,7 +761,11 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch the decode steps from Python instead of one CUDA graph")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for profiler runs)")
+    ap.add_argument("--profile-case", default=None, help="run one small workload for a profiler capture and exit")
     args = ap.parse_args()
+    if args.profile_case:
+        _profile_case(args.profile_case)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

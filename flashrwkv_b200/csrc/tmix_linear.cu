@@ -459,9 +459,7 @@ extern "C" int frwkv_tmix_linear_grouped(const frwkv_linear_problem* problems, i
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (io_dtype != FRWKV_DTYPE_BF16 && io_dtype != FRWKV_DTYPE_FP16)
     return fail(FRWKV_ERR_UNSUPPORTED, "tmix_linear: tensors must be float16 or bfloat16");
-  // FRWKV_DISABLE_TMA_GEMM=1 keeps many-row problems on the cp.async kernel (for comparisons and tests)
-  static const bool tma_off = [] { const char* e = std::getenv("FRWKV_DISABLE_TMA_GEMM"); return e != nullptr && e[0] == '1'; }();
-  if (!tma_off && linear_tma_usable(g, count, m)) return launch_linear_tma(g, count, m, io_dtype, error_flag, s);
+  if (linear_tma_usable(g, count, m)) return launch_linear_tma(g, count, m, io_dtype, error_flag, s);
   if (io_dtype == FRWKV_DTYPE_BF16) return launch_linear<__nv_bfloat16>(g, count, m, max_n, max_k, error_flag, s);
   if (io_dtype == FRWKV_DTYPE_FP16) return launch_linear<__half>(g, count, m, max_n, max_k, error_flag, s);
   return fail(FRWKV_ERR_UNSUPPORTED, "tmix_linear: tensors must be float16 or bfloat16");

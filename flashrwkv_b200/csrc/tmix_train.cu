@@ -915,17 +915,10 @@ static int mix6_backward_impl(const void* const* grad_out, const void* grad_fina
   Plan plan;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   FRWKV_TRAIN_IO(io_dtype, "pretrain_mix6", {
-    // register budget of the walk: 3 CTAs per SM (168 registers, a few spilled words) or 2 (no spill); diagnostic
-    // switch FRWKV_MIX6_BWD_CTAS=2
-    static const bool two = [] { const char* e = getenv("FRWKV_MIX6_BWD_CTAS"); return e && e[0] == '2'; }();
+    // register budget of the walk: 3 CTAs per SM (168 registers, a few spilled words); 2 CTAs without spills measured
+    // slower
     const bool shift = initial != nullptr;  // StateTune form
-    if (two && shift)
-      plan = launch_walk(mix6_backward_kernel<io_t, 2, true>, rows, channels, s, CP(io_t, x), six, P(io_t, grad_x),
-                         workspace, rows, seq_len, channels);
-    else if (two)
-      plan = launch_walk(mix6_backward_kernel<io_t, 2, false>, rows, channels, s, CP(io_t, x), six, P(io_t, grad_x),
-                         workspace, rows, seq_len, channels);
-    else if (shift)
+    if (shift)
       plan = launch_walk(mix6_backward_kernel<io_t, 3, true>, rows, channels, s, CP(io_t, x), six, P(io_t, grad_x),
                          workspace, rows, seq_len, channels);
     else

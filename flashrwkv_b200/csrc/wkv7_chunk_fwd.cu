@@ -89,15 +89,6 @@ __device__ __forceinline__ void issue_mma(uint32_t d_tmem, uint32_t a_addr, uint
 
 __device__ __forceinline__ float4 mul4(float4 a, float4 b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
 
-#ifdef FRWKV_PROFILE_PHASES
-}  // namespace
-__device__ long long g_phase_clock[16];
-namespace {
-#define FRWKV_PHASE(i) do { if (blockIdx.x == 0 && tid == 0 && item == (int)(2 * gridDim.x)) g_phase_clock[i] = clock64(); } while (0)
-#else
-#define FRWKV_PHASE(i) do { } while (0)
-#endif
-
 // =================================================================================================
 // Kernel 1: build [E;M] and [F;N] for every (chunk, head)
 // Persistent: each CTA walks (chunk, head) items blockIdx.x, blockIdx.x + gridDim.x, ... so that the
@@ -179,7 +170,6 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     const int len = min(max(chunk_ends[chunk] - t0, 1), kL);
     const bool valid = t < len;
 
-    FRWKV_PHASE(0);
     umma::cp_async_wait_all();  // this thread's share of the staged rows has landed; the barrier below covers the rest
     // the previous item's output tiles leave shared memory by bulk copies: they must have been read before this item
     // overwrites the scratch area (next phase) and the P|Q tile (operand phase)
@@ -213,7 +203,6 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
       st4(smem, o + kCS64P, make_float4(x[4], x[5], x[6], x[7]));
     }
     __syncthreads();
-    FRWKV_PHASE(1);
     // Pull the NEXT item's token rows into L2 now (one 128-byte line per thread: 6 tensors x 64 rows); the cp.async
     // staging at the end of this item then finds them there.  A cp.async that misses L2 holds its issue slot for the
     // whole DRAM round trip, which cost the last phase of every item more than its arithmetic.
@@ -255,7 +244,6 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
       }
     }
     __syncthreads();
-    FRWKV_PHASE(2);
     // ---- operands (one code path for both groups), key channels 16*quarter .. 16*quarter+15 --------------
     //   X1[64*hsel + t] = p * (hsel ? g_t : g_{t-1})      p = a | r
     //   X2[64*hsel + t] = q / g_t                         q = b | k
@@ -301,7 +289,6 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     __syncthreads();
     umma::fence_after_sync();
 
-    FRWKV_PHASE(3);
     // ---- MMA 1: [A~;R~] [B~;K~]^T  ->  rows t: [A_ab | A_ak], rows 64+t: [A_rb | A_rk] -----------
     if (tid == 0) {
       issue_mma(tmem, sbase + kOffX1, kCS128, sbase + kOffX2, kCS128, 128, false);
@@ -309,7 +296,6 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     }
     ok = umma::mbar_wait(&mbar[0], parity) && ok;
     umma::fence_after_sync();
-    FRWKV_PHASE(4);
     if (ok) {
       uint32_t u[32];
       umma::tmem_ld32(tmem + lane_base + 32 * colq, u);
@@ -342,7 +328,6 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     __syncthreads();
     umma::fence_after_sync();
 
-    FRWKV_PHASE(5);
     // ---- MMA 2: Z = A_ak V (rows 0..63 of the product; rows 64..127 of the A tile are don't-care) ----
     if (tid == 0) {
       issue_mma(tmem + 128, sbase + kOffX2, kCS128, sbase + kOffVT, kCS64P, 64, false);
@@ -442,7 +427,6 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     __syncthreads();
     umma::fence_after_sync();
 
-    FRWKV_PHASE(6);
     // ---- MMA 3: [A~^T ; Z^T] T^T -> rows j: P[.][j] (j < 64) and Q[.][j-64], columns t -------------
     if (tid == 0) {
       issue_mma(tmem + 192, sbase + kOffAZ, kCS128P, sbase + kOffTT, kCS64P, 64, false);
@@ -450,7 +434,6 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     }
     ok = umma::mbar_wait(&mbar[2], parity) && ok;
     umma::fence_after_sync();
-    FRWKV_PHASE(7);
     if (ok && colq < 2) {  // warps 0..7, 32 of the 64 columns each
       uint32_t u[32];
       umma::tmem_ld32(tmem + 192 + lane_base + 32 * colq, u);
@@ -466,7 +449,6 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     __syncthreads();
     umma::fence_after_sync();
 
-    FRWKV_PHASE(8);
     // ---- MMA 4 + 5: [A_rb ; B^^T] [P|Q]  (+)  [A_rk ; K^^T] V into columns 64..127 ------------------
     if (tid == 0) {
       issue_mma(tmem, sbase + kOffRB, kCS128P, sbase + kOffX2, kCS128, 128, false);
@@ -475,9 +457,7 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     }
     ok = umma::mbar_wait(&mbar[3], parity) && ok;
     umma::fence_after_sync();
-    FRWKV_PHASE(9);
     if (ok && item + (int)gridDim.x < num_items) stage_item(item + gridDim.x);
-    FRWKV_PHASE(12);
     if (ok) {
       // [E;M] and [F;N] are laid down in shared memory exactly as the workspace wants them ([E;M] over the P|Q tile,
       // [F;N] over V^T and the scratch area, all dead by now) and leave with two bulk copies that drain while the
@@ -485,7 +465,6 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
       uint32_t u[32];
       umma::tmem_ld32(tmem + lane_base + 32 * colq, u);
       umma::tmem_ld_wait();
-      FRWKV_PHASE(13);
       const int cb = 32 * (colq & 1);
       if (colq < 2) {
 #pragma unroll
@@ -512,13 +491,11 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
                           __uint_as_float(u[jj + 3])));
       }
     }
-    FRWKV_PHASE(10);
     // every thread is done with this item's shared memory and accumulators before the next item starts
     umma::fence_async_smem();
     umma::fence_before_sync();
     ok = __syncthreads_and(ok) != 0;
     umma::fence_after_sync();
-    FRWKV_PHASE(11);
     if (!ok) break;
     if (tid == 0) {
       unsigned char* ws = workspace + (size_t)item * (2 * kWsTile);
@@ -706,7 +683,13 @@ int launch_chunk_forward(const int* seq_chunk_offsets, const int* chunk_starts, 
                          const void* k, const void* v, const void* a, const void* b, const void* bias, void* y,
                          float* y32, float* boundary, void* workspace, int* error_flag, int total_tokens,
                          int num_sequences, int num_chunks, int num_heads, float scale, cudaStream_t stream) {
-  {
+  // the shared-memory opt-in and the SM count are looked up once per device and instantiation, not on every call
+  static bool opted_in[64] = {};
+  static int sm_counts[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
+    return fail(FRWKV_ERR_CUDA, "wkv7_chunk_forward: cannot identify the current device");
+  if (!opted_in[device]) {
     cudaError_t e1 = cudaFuncSetAttribute(wkv7_chunk_build_kernel<io_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)kBuildSmem);
     cudaError_t e2 = cudaFuncSetAttribute(wkv7_chunk_scan_kernel<io_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -714,10 +697,10 @@ int launch_chunk_forward(const int* seq_chunk_offsets, const int* chunk_starts, 
     if (e1 != cudaSuccess || e2 != cudaSuccess)
       return fail(FRWKV_ERR_CUDA, "wkv7_chunk_forward: cannot reserve shared memory: %s",
                   cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    cudaDeviceGetAttribute(&sm_counts[device], cudaDevAttrMultiProcessorCount, device);
+    opted_in[device] = true;
   }
-  int device = 0, sm_count = 0;
-  cudaGetDevice(&device);
-  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+  const int sm_count = sm_counts[device];
   const int num_items = num_chunks * num_heads;
   const int build_grid = sm_count > 0 && sm_count < num_items ? sm_count : num_items;
   wkv7_chunk_build_kernel<io_t><<<(unsigned)build_grid, kBuildThreads, kBuildSmem, stream>>>(
@@ -736,12 +719,6 @@ int launch_chunk_forward(const int* seq_chunk_offsets, const int* chunk_starts, 
 
 }  // namespace
 }  // namespace frwkv
-
-#ifdef FRWKV_PROFILE_PHASES
-extern "C" int frwkv_debug_phase_clocks(long long* out16) {
-  return (int)cudaMemcpyFromSymbol(out16, frwkv::g_phase_clock, sizeof(long long) * 16);
-}
-#endif
 
 extern "C" size_t frwkv_wkv7_chunk_workspace_bytes(int num_chunks, int num_heads) {
   if (num_chunks <= 0 || num_heads <= 0) return 0;

@@ -251,10 +251,7 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
 // ---------------------------------------------------------------------------------------------------------
 // 2: six stages of two adjacent heads (32 KB bulk copies), 42.97 us per launch at 256 x 32 tiles;
 // 1: thirteen stages of one tile (16 KB copies), 45.0 us.  Odd head counts always take 1.
-#ifndef FRWKV_DECODE_TILES_PER_STAGE
-#define FRWKV_DECODE_TILES_PER_STAGE 2
-#endif
-constexpr int kDecodeTilesPerStage = FRWKV_DECODE_TILES_PER_STAGE;
+constexpr int kDecodeTilesPerStage = 2;
 constexpr int kTileBytes = kD * kD * 4;
 constexpr int kTokBytes = 6 * kD * 2;  // r, w, k, v, a, b rows of one (token, head)
 constexpr int kConsumerPairs = 7;

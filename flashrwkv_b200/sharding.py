@@ -41,16 +41,30 @@ def shard_packed(tokens: torch.Tensor, cu_seqlens: torch.Tensor, plan: dict):
     return part, local_cu
 
 
-def gather_shards(local: torch.Tensor, plan: dict, group=None) -> torch.Tensor:
+def gather_shards(local: torch.Tensor, plan: dict, group=None, total: int | None = None) -> torch.Tensor:
     """All-gather per-rank results (outputs `[n_local,H_local,D]` or states `[B_local,H_local,D,D]`) so that every
-    rank holds the full tensor.  Shards may have different sizes along the split axis."""
+    rank holds the full tensor.  Shards may have different sizes along the split axis.
+
+    `total` is the size of the split axis before sharding (sequences, or packed tokens of equal-length sequences,
+    or heads).  When it is given the shard sizes follow from `shard_range` on every rank and equal shards go
+    through one `all_gather_into_tensor`; without it the sizes are exchanged first, which costs a second
+    collective and a host synchronisation."""
     world = dist.get_world_size(group)
     if world == 1:
         return local
     dim = 0 if plan["axis"] == "sequence" else 1
-    sizes = [torch.zeros(1, dtype=torch.int64, device=local.device) for _ in range(world)]
-    dist.all_gather(sizes, torch.tensor([local.shape[dim]], dtype=torch.int64, device=local.device), group=group)
-    sizes = [int(s.item()) for s in sizes]
+    if total is not None:
+        sizes = [shard_range(total, world, r)[1] - shard_range(total, world, r)[0] for r in range(world)]
+        if sizes[dist.get_rank(group)] != local.shape[dim]:
+            raise ValueError("local shard does not match shard_range(total, world_size, rank)")
+        if dim == 0 and len(set(sizes)) == 1:
+            out = local.new_empty((total, *local.shape[1:]))
+            dist.all_gather_into_tensor(out, local.contiguous(), group=group)
+            return out
+    else:
+        sizes = [torch.zeros(1, dtype=torch.int64, device=local.device) for _ in range(world)]
+        dist.all_gather(sizes, torch.tensor([local.shape[dim]], dtype=torch.int64, device=local.device), group=group)
+        sizes = [int(s.item()) for s in sizes]
     biggest = max(sizes)
     pad_shape = list(local.shape)
     pad_shape[dim] = biggest

@@ -48,6 +48,10 @@ def _worker(rank, world, port, axis, out_dir):
     res = wkv7_oracle.forward(*local, state_pool=pool[s0:s1, h0:h1].contiguous(), cu_seqlens=local_cu)
     y = sharding.gather_shards(torch.from_numpy(res["y"]), plan)
     final = sharding.gather_shards(torch.from_numpy(res["state_pool"]), plan)
+    # with the size of the split axis known no size exchange is needed (equal shards: one collective)
+    total = B if axis == "sequence" else H
+    final2 = sharding.gather_shards(torch.from_numpy(res["state_pool"]), plan, total=total)
+    assert torch.equal(final, final2)
     if rank == 0:
         full = wkv7_oracle.forward(*toks, state_pool=pool, cu_seqlens=cu)
         np.save(os.path.join(out_dir, "err.npy"),
