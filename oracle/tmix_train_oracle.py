@@ -15,9 +15,11 @@ float; here float64, so that the CUDA result can be judged against an exact valu
   lnx_rkvres_xg  csrc/sm90/tmix/lnx_rkvres_xg/pretrain_bf16_forward.cu:64-124 (eps 64e-5, biased variance; the
                  torch formula of tests/tmix/lnx_rkvres_xg/test.py:42-60)
 
-Parity pin: the reference's tests of these operators hold no golden vectors (they check finiteness and, for mix6 and
-the inference twin of lnx, a torch formula).  The backward functions here are pinned on the CPU against torch
-autograd (float64) of those formulas (tests/test_tmix_train_oracle.py).
+Parity pin: the forwards are pinned to the formulas the reference's own tests evaluate (mix6, lnx, vres_gate, and
+kk_a_gate = a_gate followed by kk_pre), stored as fixtures by tests/golden/make_golden.py and checked in
+tests/test_tmix_train_oracle.py.  The reference's tests of the BACKWARDS hold no values (finiteness checks only), so
+the backward functions here are pinned on the CPU against torch autograd (float64) of those formulas: for the
+backward of a_gate, kk_pre and vres_gate that is all there is - parity unpinned by anything the reference holds.
 """
 from __future__ import annotations
 

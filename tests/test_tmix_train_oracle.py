@@ -117,3 +117,35 @@ def test_lnx_backward_matches_autograd(head_size):
     want = torch.autograd.grad(y, [x, r, k, v, r_k, weight, bias, g], go)
     for got, w in zip(O.lnx_rkvres_xg_backward(go, x, r, k, v, r_k, weight, bias, g, head_size), want):
         _close(got, w, tol=1e-9)
+
+
+# ---- the forwards against the formulas the reference's own tests evaluate -------------------------------------------
+# tests/golden/make_golden.py stores those formulas' values (tests/tmix/{kk_a_gate,lnx_rkvres_xg,vres_gate,mix6}/test.py
+# of the reference, evaluated on seeded fp16 inputs).  They pin the forward of every operator restated above; what
+# stays unpinned by anything the reference holds is the backward of a_gate / kk_pre / vres_gate, for which the
+# reference's tests only check finiteness (pinned here against autograd of the same formulas, above).
+def test_forwards_match_the_reference_test_formulas():
+    from _util import load_golden
+
+    g = load_golden("tmix_lnx")
+    out, _, _ = O.lnx_rkvres_xg(*(g[n][None] for n in ("x", "r", "k", "v")), g["r_k"], g["weight"], g["bias"],
+                                g["g"][None], head_size=64)
+    assert np.abs(out[0] - g["out"].double().numpy()).max() < 2e-5
+
+    g = load_golden("tmix_vres")
+    out = O.vres_gate(g["v"], g["v_first"], g["v0"], g["v12"])
+    assert np.abs(out - g["out"].double().numpy()).max() < 2e-6
+
+    g = load_golden("tmix_kk_a_gate")  # the inference operator is a_gate followed by kk_pre
+    a = O.a_gate(g["a0"], g["a12"])
+    new_k, neg_kk, kka, _ = O.kk_pre(g["k"], g["k_k"], a, g["k_a"], head_size=64)
+    for got, name in ((new_k, "new_k"), (neg_kk, "neg_kk"), (kka, "kka")):
+        assert np.abs(got - g[name].double().numpy()).max() < 2e-5, name
+
+    g = load_golden("tmix_mix6")  # packed sequences with a shift-state pool: one dense call per sequence
+    cu, idx = g["cu_seqlens"].tolist(), g["state_indices"].tolist()
+    for s, slot in enumerate(idx):
+        x = g["x"][cu[s]:cu[s + 1]][None]
+        outs = O.mix6(x, list(g["mix"]), initial=g["shift_pool"][slot][None])
+        for j, o in enumerate(outs):
+            assert np.abs(o[0] - g["out"][j, cu[s]:cu[s + 1]].double().numpy()).max() < 2e-3, (s, j)
