@@ -1018,6 +1018,35 @@ void statetune_recurrent_fp32io16_backward(torch::Tensor sco, torch::Tensor cs, 
     if (outs[i]->has_value()) (*outs[i])->copy_(g[i]);
 }
 
+// Adjoint of the state at every chunk boundary and the gradient of the initial state (first stage of the chunked
+// backward).  Returns (grad_initial_state [B,H,64,64], boundary_adjoint [Cn,H,64,64], error flag).
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> wkv7_adjoint_scan(
+    torch::Tensor sco, torch::Tensor cs, torch::Tensor ce, torch::Tensor r, torch::Tensor w, torch::Tensor a,
+    torch::Tensor b, torch::Tensor grad_output, std::optional<torch::Tensor> grad_final_state, double scale,
+    std::optional<torch::Tensor> decay_bias) {
+  check_chunk_tables(sco, cs, ce, r);
+  TORCH_CHECK(r.dim() == 3 && r.size(2) == 64, "token tensors must have shape [N,H,64]");
+  check_cuda_contiguous(grad_output, "grad_output");
+  TORCH_CHECK(grad_output.sizes() == r.sizes() && grad_output.scalar_type() == r.scalar_type(),
+              "grad_output must match r");
+  const int64_t B = sco.numel() - 1, H = r.size(1), Cn = cs.numel();
+  const c10::cuda::CUDAGuard guard(r.device());
+  auto f32 = r.options().dtype(torch::kFloat32);
+  torch::Tensor g_state = grad_final_state.has_value() ? grad_final_state->to(torch::kFloat32).contiguous().clone()
+                                                       : torch::zeros({B, H, 64, 64}, f32);
+  TORCH_CHECK(g_state.dim() == 4 && g_state.size(0) == B && g_state.size(1) == H, "grad_final_state must be [B,H,64,64]");
+  auto boundary_adjoint = torch::empty({Cn, H, 64, 64}, f32);
+  auto khat = torch::empty(r.sizes(), f32);
+  auto error_flag = torch::zeros({1}, r.options().dtype(torch::kInt32));
+  check_rc(frwkv_wkv7_adjoint_scan(sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(), r.data_ptr(), w.data_ptr(),
+                                   a.data_ptr(), b.data_ptr(), decay_bias.has_value() ? decay_bias->data_ptr() : nullptr,
+                                   grad_output.data_ptr(), g_state.data_ptr<float>(), boundary_adjoint.data_ptr<float>(),
+                                   khat.data_ptr<float>(), error_flag.data_ptr<int>(), static_cast<int>(r.size(0)),
+                                   static_cast<int>(B), static_cast<int>(Cn), static_cast<int>(H), 64, io_dtype_of(r),
+                                   static_cast<float>(scale), current_stream(r)));
+  return {g_state, boundary_adjoint, error_flag};
+}
+
 // ---- training-side TMix glue on dense [B,T,C] tensors (names and argument order of the reference's
 // pretrain_tmix_* extension functions, flashrwkv2/tmix/{a_gate,vres_gate,mix6,kk_pre,lnx_rkvres_xg}) ----------
 void check_dense(const torch::Tensor& t, const char* name, const torch::Tensor& ref) {
@@ -1405,6 +1434,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("b"), py::arg("state_dot_a"), py::arg("grad_output"), py::arg("grad_final_state"), py::arg("boundary"),
         py::arg("grad_r"), py::arg("grad_decay_logits"), py::arg("grad_k"), py::arg("grad_v"), py::arg("grad_a"),
         py::arg("grad_b"), py::arg("grad_initial_state"), py::arg("scale") = 1.0);
+  m.def("wkv7_adjoint_scan", &wkv7_adjoint_scan, py::arg("sequence_chunk_offsets"), py::arg("chunk_token_starts"),
+        py::arg("chunk_token_ends"), py::arg("r"), py::arg("decay_logits"), py::arg("a"), py::arg("b"),
+        py::arg("grad_output"), py::arg("grad_final_state") = py::none(), py::arg("scale") = 1.0,
+        py::arg("decay_bias") = py::none());
   m.def("wkv7_chunk_replay", &wkv7_chunk_replay, py::arg("chunk_token_starts"), py::arg("chunk_token_ends"),
         py::arg("boundary"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),
         py::arg("b"), py::arg("decay_bias") = py::none());

@@ -205,15 +205,22 @@ __device__ __forceinline__ void unpack8(uint4 u, float (&f)[8]) {
   p = IO::unpack(u.w); f[6] = p.x; f[7] = p.y;
 }
 
-template <typename io_t>
+// kAdj = false: the forward recurrence.  kAdj = true: the same kernel walks every sequence BACKWARDS (last chunk
+// first, last token of a chunk first) and takes its key rows from an fp32 tensor: this is how the backward pass gets
+// the adjoint of the state at every chunk boundary, because that adjoint obeys a recurrence of the same form
+//     G_{t-1} = diag(w_t) G_t + a_t (G_t^T b_t)^T + k^_t dy_t^T,      k^_t = scale (w_t * r_t + (b_t . r_t) a_t)
+// (the forward one with a and b exchanged, k^ for k, dy for v, run in reverse time).  The launcher passes b as a,
+// a as b, dy as v and k^ as khat; outputs y / state_dot_a are not produced, `boundary[c]` receives the adjoint
+// that enters chunk c from the future and the state slot ends as the gradient of the initial state.
+template <typename io_t, bool kAdj>
 __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
     const int* __restrict__ seq_chunk_offsets, const int* __restrict__ chunk_starts, const int* __restrict__ chunk_ends,
     const int* __restrict__ state_indices, const int* __restrict__ metadata_status, float* __restrict__ state_pool,
     const io_t* __restrict__ r_ptr, const io_t* __restrict__ w_ptr, const io_t* __restrict__ k_ptr,
     const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr, const io_t* __restrict__ b_ptr,
-    const io_t* __restrict__ bias_ptr, io_t* __restrict__ y_ptr, float* __restrict__ y32_ptr,
-    float* __restrict__ boundary, float* __restrict__ sda_ptr, int num_heads, int num_units,
-    long long output_elements, float scale, int* __restrict__ error_flag) {
+    const io_t* __restrict__ bias_ptr, const float* __restrict__ khat_ptr, io_t* __restrict__ y_ptr,
+    float* __restrict__ y32_ptr, float* __restrict__ boundary, float* __restrict__ sda_ptr, int num_heads,
+    int num_units, long long output_elements, float scale, int* __restrict__ error_flag) {
   using IO = Io16<io_t>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t mbar[4];
@@ -222,7 +229,8 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (metadata_status != nullptr && metadata_status[0] != 0) {
     const io_t nan16 = IO::store(quiet_nan());
-    for (long long i = (long long)blockIdx.x * kThreads + tid; i < output_elements; i += (long long)gridDim.x * kThreads) {
+    for (long long i = (long long)blockIdx.x * kThreads + tid; y_ptr != nullptr && i < output_elements;
+         i += (long long)gridDim.x * kThreads) {
       y_ptr[i] = nan16;
       if (y32_ptr != nullptr) y32_ptr[i] = quiet_nan();
     }
@@ -250,6 +258,9 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
   bool ok = true;
   uint32_t parity = 0;
 
+  // packed row of the i-th token a chunk [tt0, tt0 + ln) is walked in
+  const auto token_row = [](int tt0, int ln, int i) { return kAdj ? tt0 + ln - 1 - i : tt0 + i; };
+
   // the decay logits of a chunk travel by cp.async one chunk ahead (two 16-byte pieces per thread; rows past the
   // end of a short chunk are zero-filled and not used)
   auto stage_w = [&](int chunk, long long head_off) {
@@ -259,7 +270,7 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
     for (int i = 0; i < 2; ++i) {
       const int piece = tid + i * kThreads, rowi = piece >> 3, part = piece & 7;
       umma::cp_async16(sbase + kOffW + piece * 16,
-                       w_ptr + (long long)(tt0 + min(rowi, ln - 1)) * row_stride + head_off + 8 * part,
+                       w_ptr + (long long)token_row(tt0, ln, min(rowi, ln - 1)) * row_stride + head_off + 8 * part,
                        rowi < ln ? 16u : 0u);
     }
     umma::cp_async_commit();
@@ -269,7 +280,7 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
   // (2) thread (key channel, 16-token segment): running product down the column, segment totals, prefix fix-up.
   // Runs one chunk ahead of its use (while the tensor core does MMA 1 of the previous chunk) and starts the copy of
   // the logits of the chunk after.  Contains barriers: every thread calls it.
-  auto compute_g = [&](int chunk, int last_chunk, long long head_off) {
+  auto compute_g = [&](int chunk, int chunk_after, long long head_off) {  // chunk_after < 0: none
     const int ln = min(max(chunk_ends[chunk] - chunk_starts[chunk], 1), kL);
     umma::cp_async_wait_all();
     __syncthreads();
@@ -292,7 +303,7 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
         st4(smem, kOffG + (4 * q + i) * kCS64 + t * 16, make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]));
     }
     __syncthreads();
-    if (chunk + 1 < last_chunk) stage_w(chunk + 1, head_off);  // everybody has read this chunk's logits
+    if (chunk_after >= 0) stage_w(chunk_after, head_off);  // everybody has read this chunk's logits
     {
       const int kcol = tid & 63, seg = tid >> 6;
       const uint32_t gcol = kOffG + uint32_t(kcol >> 2) * kCS64 + uint32_t(kcol & 3) * 4 + uint32_t(16 * seg) * 16;
@@ -320,12 +331,13 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
     const int slot = state_indices != nullptr ? state_indices[seq] : seq;
     float* state = state_pool + ((long long)slot * num_heads + head) * (kD * kD);
     const long long head_off = (long long)head * kD;
-    stage_w(c_begin, head_off);
+    const int n_chunks = c_end - c_begin, c_step = kAdj ? -1 : 1, c_first = kAdj ? c_end - 1 : c_begin;
+    stage_w(c_first, head_off);
 
     // ---- this unit's state: row mt, columns c0..c0+31 in registers (fp32) and, transposed and rounded, in S0^T ----
     float S[32];
     if (low) {
-      float* bnd = boundary != nullptr ? boundary + ((long long)c_begin * num_heads + head) * (kD * kD) + mt * kD + c0
+      float* bnd = boundary != nullptr ? boundary + ((long long)c_first * num_heads + head) * (kD * kD) + mt * kD + c0
                                        : nullptr;
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
@@ -336,30 +348,37 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
 #pragma unroll
       for (int j = 0; j < 32; ++j) st1(smem, kOffS + tile_off(kCS64, c0 + j, mt), umma::to_tf32(S[j]));
     }
-    compute_g(c_begin, c_end, head_off);
+    compute_g(c_first, n_chunks > 1 ? c_first + c_step : -1, head_off);
 
-    int next_t0 = chunk_starts[c_begin], next_end = chunk_ends[c_begin];
-    for (int c = c_begin; c < c_end; ++c, parity ^= 1u) {
+    int next_t0 = chunk_starts[c_first], next_end = chunk_ends[c_first];
+    for (int nc = 0; nc < n_chunks; ++nc, parity ^= 1u) {
+      const int c = c_first + nc * c_step;
+      const bool has_next = nc + 1 < n_chunks;
       const int t0 = next_t0;
       const int len = min(max(next_end - t0, 1), kL);
-      if (c + 1 < c_end) {  // the next chunk's bounds are on their way while this one is worked on
-        next_t0 = chunk_starts[c + 1];
-        next_end = chunk_ends[c + 1];
+      if (has_next) {  // the next chunk's bounds are on their way while this one is worked on
+        next_t0 = chunk_starts[c + c_step];
+        next_end = chunk_ends[c + c_step];
       }
       // ---- this thread's operand rows leave HBM / L2 now and are used after the decay scan ----------------------
       const bool valid = mt < len;
-      uint4 praw[4], qraw[4], vraw[4];
+      uint4 praw[4], qraw[kAdj ? 8 : 4], vraw[4];
       {
-        const long long row = (long long)(t0 + min(mt, len - 1)) * row_stride + head_off + c0;
+        const long long row = (long long)token_row(t0, len, min(mt, len - 1)) * row_stride + head_off + c0;
         const uint4* pp = reinterpret_cast<const uint4*>((low ? a_ptr : r_ptr) + row);
         const uint4* qp = reinterpret_cast<const uint4*>((low ? b_ptr : k_ptr) + row);
         const uint4* vp = reinterpret_cast<const uint4*>(v_ptr + row);
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
           praw[i] = valid ? __ldg(pp + i) : zero;
-          qraw[i] = valid ? __ldg(qp + i) : zero;
+          qraw[i] = valid && (!kAdj || low) ? __ldg(qp + i) : zero;
           vraw[i] = (valid && !low) ? __ldg(vp + i) : zero;
+        }
+        if (kAdj && !low) {  // the adjoint run's key rows are fp32: 32 channels = eight 16-byte pieces
+          const uint4* kp = reinterpret_cast<const uint4*>(khat_ptr + row);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) qraw[i] = valid ? __ldg(kp + i) : zero;
         }
       }
 
@@ -370,6 +389,12 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
         float pf[8], qf[8];
         unpack8<io_t>(praw[i], pf);
         unpack8<io_t>(qraw[i], qf);
+        if (kAdj && !low) {
+          const uint4 lo4 = qraw[kAdj ? 2 * i : 0], hi4 = qraw[kAdj ? 2 * i + 1 : 0];
+          qf[0] = __uint_as_float(lo4.x); qf[1] = __uint_as_float(lo4.y); qf[2] = __uint_as_float(lo4.z);
+          qf[3] = __uint_as_float(lo4.w); qf[4] = __uint_as_float(hi4.x); qf[5] = __uint_as_float(hi4.y);
+          qf[6] = __uint_as_float(hi4.z); qf[7] = __uint_as_float(hi4.w);
+        }
         uint32_t xa[8];
 #pragma unroll
         for (int hq = 0; hq < 2; ++hq) {
@@ -397,7 +422,7 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
       }
       umma::tmem_st_wait();
       // pull the next chunk's operand rows into L2 (its decay logits are already on their way to shared memory)
-      if (c + 1 < c_end) {
+      if (has_next) {
         const int nt0 = next_t0, nlen = next_end - nt0;
         for (int e = tid; e < 5 * kL; e += kThreads) {
           const int which = e >> 6, rowi = e & 63;
@@ -420,7 +445,8 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
                             umma::desc_k_major(sbase + kOffX2 + ks * 2 * kCSB, kCSB), idesc128, ks > 0 ? 1u : 0u);
         umma::mma_commit(&mbar[0]);
       }
-      if (c + 1 < c_end) compute_g(c + 1, c_end, head_off);  // g of this chunk has been consumed (barrier above)
+      if (has_next)  // g of this chunk has been consumed (barrier above)
+        compute_g(c + c_step, nc + 2 < n_chunks ? c + 2 * c_step : -1, head_off);
       ok = wait_warp(&mbar[0], parity, ok);
       umma::fence_after_sync();
       // ---- epilogue 1: mask; A_ab -> fp32 scratch, the other three blocks rounded in place -----------------------
@@ -528,7 +554,7 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
           umma::tmem_ld16(tmem + kColDA + lane_base + c0 + 16 * hb, u);
           umma::tmem_ld_wait();
           if (sda_ptr != nullptr && valid) {
-            float* dst = sda_ptr + (long long)(t0 + mt) * row_stride + head_off + c0 + 16 * hb;
+            float* dst = sda_ptr + (long long)token_row(t0, len, mt) * row_stride + head_off + c0 + 16 * hb;
 #pragma unroll
             for (int j = 0; j < 16; j += 4)
               *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(u[j]), __uint_as_float(u[j + 1]),
@@ -560,10 +586,10 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
         umma::tmem_ld32(tmem + kColDC + lane_base + c0, u);
         if (low) {
           umma::tmem_ld_wait();
-          const bool last = (c + 1 == c_end);
+          const bool last = !has_next;
           float* dst = last ? state + mt * kD + c0
                             : (boundary != nullptr
-                                   ? boundary + ((long long)(c + 1) * num_heads + head) * (kD * kD) + mt * kD + c0
+                                   ? boundary + ((long long)(c + c_step) * num_heads + head) * (kD * kD) + mt * kD + c0
                                    : nullptr);
 #pragma unroll
           for (int j = 0; j < 32; ++j) S[j] = g_last * (S[j] + __uint_as_float(u[j]));
@@ -579,8 +605,8 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
           uint32_t u2[32];
           umma::tmem_ld32(tmem + kColDA + lane_base + c0, u2);
           umma::tmem_ld_wait();
-          if (valid) {
-            const long long row = (long long)(t0 + mt) * row_stride + head_off + c0;
+          if (valid && y_ptr != nullptr) {
+            const long long row = (long long)token_row(t0, len, mt) * row_stride + head_off + c0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               float o[8];
@@ -606,7 +632,7 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
         // fail closed: the rows of this (sequence, head) read as NaN, its state slot keeps the value it had
         const io_t nan16 = IO::store(quiet_nan());
         const int tb = chunk_starts[c_begin], te = chunk_ends[c_end - 1];
-        for (long long e = (long long)tb * kD + tid; e < (long long)te * kD; e += kThreads) {
+        for (long long e = (long long)tb * kD + tid; y_ptr != nullptr && e < (long long)te * kD; e += kThreads) {
           const long long at = (e / kD) * row_stride + head_off + (e % kD);
           y_ptr[at] = nan16;
           if (y32_ptr != nullptr) y32_ptr[at] = quiet_nan();
@@ -624,7 +650,7 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
 
 struct DeviceInfo {
   int sm_count = 0;
-  bool attr_set[2] = {false, false};
+  bool attr_set[4] = {false, false, false, false};
 };
 
 DeviceInfo* device_info() {
@@ -640,15 +666,16 @@ DeviceInfo* device_info() {
   return d;
 }
 
-template <typename io_t>
+template <typename io_t, bool kAdj>
 int launch_fused(const int* sco, const int* cs, const int* ce, const int* state_indices, const int* status,
                  float* state_pool, const void* r, const void* w, const void* k, const void* v, const void* a,
-                 const void* b, const void* bias, void* y, float* y32, float* boundary, float* sda, int* error_flag,
-                 int total_tokens, int num_sequences, int num_heads, float scale, int which, cudaStream_t stream) {
+                 const void* b, const void* bias, const float* khat, void* y, float* y32, float* boundary, float* sda,
+                 int* error_flag, int total_tokens, int num_sequences, int num_heads, float scale, int which,
+                 cudaStream_t stream) {
   DeviceInfo* info = device_info();
   if (info == nullptr) return fail(FRWKV_ERR_CUDA, "wkv7_chunk_fused_forward: cannot query the current device");
   if (!info->attr_set[which]) {
-    cudaError_t e = cudaFuncSetAttribute(wkv7_chunk_fused_kernel<io_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(wkv7_chunk_fused_kernel<io_t, kAdj>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)kFusedSmem);
     if (e != cudaSuccess)
       return fail(FRWKV_ERR_CUDA, "wkv7_chunk_fused_forward: cannot reserve shared memory: %s", cudaGetErrorString(e));
@@ -656,10 +683,10 @@ int launch_fused(const int* sco, const int* cs, const int* ce, const int* state_
   }
   const int units = num_sequences * num_heads;
   const int grid = units < 2 * info->sm_count ? units : 2 * info->sm_count;
-  wkv7_chunk_fused_kernel<io_t><<<(unsigned)grid, kThreads, kFusedSmem, stream>>>(
+  wkv7_chunk_fused_kernel<io_t, kAdj><<<(unsigned)grid, kThreads, kFusedSmem, stream>>>(
       sco, cs, ce, state_indices, status, state_pool, static_cast<const io_t*>(r), static_cast<const io_t*>(w),
       static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),
-      static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, boundary, sda,
+      static_cast<const io_t*>(b), static_cast<const io_t*>(bias), khat, static_cast<io_t*>(y), y32, boundary, sda,
       num_heads, units, (long long)total_tokens * num_heads * kD, scale, error_flag);
   return check_launch("wkv7_chunk_fused_kernel");
 }
@@ -693,12 +720,91 @@ extern "C" int frwkv_wkv7_chunk_fused_fp32io16_forward(
                 "wkv7_chunk_fused_forward: too many (sequence, head) pairs");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (io_dtype == FRWKV_DTYPE_BF16)
-    return launch_fused<__nv_bfloat16>(seq_chunk_offsets, chunk_starts, chunk_ends, state_indices, metadata_status,
-                                       state_pool, r, decay_logits, k, v, a, b, decay_bias, y, y_fp32, boundary,
-                                       state_dot_a, error_flag, total_tokens, num_sequences, num_heads, scale, 0, s);
+    return launch_fused<__nv_bfloat16, false>(seq_chunk_offsets, chunk_starts, chunk_ends, state_indices,
+                                              metadata_status, state_pool, r, decay_logits, k, v, a, b, decay_bias,
+                                              nullptr, y, y_fp32, boundary, state_dot_a, error_flag, total_tokens,
+                                              num_sequences, num_heads, scale, 0, s);
   if (io_dtype == FRWKV_DTYPE_FP16)
-    return launch_fused<__half>(seq_chunk_offsets, chunk_starts, chunk_ends, state_indices, metadata_status,
-                                state_pool, r, decay_logits, k, v, a, b, decay_bias, y, y_fp32, boundary, state_dot_a,
-                                error_flag, total_tokens, num_sequences, num_heads, scale, 1, s);
+    return launch_fused<__half, false>(seq_chunk_offsets, chunk_starts, chunk_ends, state_indices, metadata_status,
+                                       state_pool, r, decay_logits, k, v, a, b, decay_bias, nullptr, y, y_fp32,
+                                       boundary, state_dot_a, error_flag, total_tokens, num_sequences, num_heads,
+                                       scale, 1, s);
   return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_chunk_fused_forward: token tensors must be float16 or bfloat16");
+}
+
+// ---- adjoint of the state at every chunk boundary (first stage of the chunked backward) -----------------------------
+namespace frwkv {
+namespace {
+
+// k^_t = scale * (w_t * r_t + (b_t . r_t) a_t) per (token, head), fp32: one warp per row, two channels per lane
+template <typename io_t>
+__global__ void adjoint_key_kernel(const io_t* __restrict__ r, const io_t* __restrict__ w, const io_t* __restrict__ a,
+                                   const io_t* __restrict__ b, const io_t* __restrict__ bias, float* __restrict__ khat,
+                                   long long rows, int num_heads, float scale) {
+  using IO = Io16<io_t>;
+  const int lane = threadIdx.x & 31;
+  for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+       row += (long long)gridDim.x * (blockDim.x >> 5)) {
+    const long long at = row * kD + 2 * lane;
+    const float2 rv = IO::unpack(*reinterpret_cast<const uint32_t*>(r + at));
+    const float2 av = IO::unpack(*reinterpret_cast<const uint32_t*>(a + at));
+    const float2 bv = IO::unpack(*reinterpret_cast<const uint32_t*>(b + at));
+    float2 wl = IO::unpack(*reinterpret_cast<const uint32_t*>(w + at));
+    if (bias != nullptr) {
+      const float2 bz = IO::unpack(*reinterpret_cast<const uint32_t*>(bias + (row % num_heads) * kD + 2 * lane));
+      wl.x += bz.x;
+      wl.y += bz.y;
+    }
+    float dot = bv.x * rv.x + bv.y * rv.y;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    *reinterpret_cast<float2*>(khat + at) = make_float2(scale * fmaf(dot, av.x, retention(wl.x) * rv.x),
+                                                        scale * fmaf(dot, av.y, retention(wl.y) * rv.y));
+  }
+}
+
+}  // namespace
+}  // namespace frwkv
+
+extern "C" int frwkv_wkv7_adjoint_scan(const int32_t* seq_chunk_offsets, const int32_t* chunk_starts,
+                                       const int32_t* chunk_ends, const void* r, const void* decay_logits,
+                                       const void* a, const void* b, const void* decay_bias, const void* grad_output,
+                                       float* grad_state, float* boundary_adjoint, float* khat, int32_t* error_flag,
+                                       int total_tokens, int num_sequences, int num_chunks, int num_heads,
+                                       int head_size, int io_dtype, float scale, frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(seq_chunk_offsets && chunk_starts && chunk_ends && r && decay_logits && a && b && grad_output &&
+                    grad_state && boundary_adjoint && khat,
+                "wkv7_adjoint_scan: null pointer argument");
+  FRWKV_REQUIRE(total_tokens > 0 && num_sequences > 0 && num_chunks > 0 && num_heads > 0,
+                "wkv7_adjoint_scan: sizes must be positive");
+  if (head_size != 64)
+    return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_adjoint_scan: head size %d is not built (only 64)", head_size);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const long long rows = (long long)total_tokens * num_heads;
+  const unsigned blocks = (unsigned)((rows + 7) / 8 < 148 * 16 ? (rows + 7) / 8 : 148 * 16);
+  if (io_dtype == FRWKV_DTYPE_BF16) {
+    using T = __nv_bfloat16;
+    adjoint_key_kernel<T><<<blocks, 256, 0, s>>>(static_cast<const T*>(r), static_cast<const T*>(decay_logits),
+                                                 static_cast<const T*>(a), static_cast<const T*>(b),
+                                                 static_cast<const T*>(decay_bias), khat, rows, num_heads, scale);
+    if (int rc = check_launch("adjoint_key_kernel")) return rc;
+    return launch_fused<T, true>(seq_chunk_offsets, chunk_starts, chunk_ends, nullptr, nullptr, grad_state, r,
+                                 decay_logits, /*k: unused*/ r, grad_output, /*a=*/b, /*b=*/a, decay_bias, khat, nullptr,
+                                 nullptr, boundary_adjoint, nullptr, error_flag, total_tokens, num_sequences, num_heads,
+                                 1.0f, 2, s);
+  }
+  if (io_dtype == FRWKV_DTYPE_FP16) {
+    using T = __half;
+    adjoint_key_kernel<T><<<blocks, 256, 0, s>>>(static_cast<const T*>(r), static_cast<const T*>(decay_logits),
+                                                 static_cast<const T*>(a), static_cast<const T*>(b),
+                                                 static_cast<const T*>(decay_bias), khat, rows, num_heads, scale);
+    if (int rc = check_launch("adjoint_key_kernel")) return rc;
+    return launch_fused<T, true>(seq_chunk_offsets, chunk_starts, chunk_ends, nullptr, nullptr, grad_state, r,
+                                 decay_logits, /*k: unused*/ r, grad_output, /*a=*/b, /*b=*/a, decay_bias, khat, nullptr,
+                                 nullptr, boundary_adjoint, nullptr, error_flag, total_tokens, num_sequences, num_heads,
+                                 1.0f, 3, s);
+  }
+  return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_adjoint_scan: token tensors must be float16 or bfloat16");
 }

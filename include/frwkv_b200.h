@@ -176,6 +176,24 @@ int frwkv_wkv7_chunk_fused_fp32io16_forward(
     frwkv_stream_t stream);
 
 /*
+ * First stage of the chunked backward: the adjoint of the state at every chunk boundary, and the gradient of the
+ * initial state.  The adjoint obeys a recurrence of the forward's own form (a and b exchanged, a modified key, the
+ * upstream gradient in place of v, time reversed), so it is computed by the fused forward kernel walking every
+ * sequence backwards.  Replaces the state-adjoint part of the reference's serial backward kernels
+ * (csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_backward.cu:139-254,
+ * csrc/sm90/tmix/wkv7/pretrain_recurrent_bf16_forward.cu:222-282).
+ *   grad_output io16 [N,H,64]; grad_state fp32 [B,H,64,64]: in = gradient of the final state (zeros if none), out =
+ *   gradient of the initial state;  boundary_adjoint fp32 [Cn,H,64,64]: receives dL/dS at the END of every chunk;
+ *   khat fp32 [N,H,64]: scratch for the modified keys scale * (w * r + (b . r) a).
+ */
+int frwkv_wkv7_adjoint_scan(const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends,
+                            const void* r, const void* decay_logits, const void* a, const void* b,
+                            const void* decay_bias, const void* grad_output, float* grad_state,
+                            float* boundary_adjoint, float* khat, int32_t* error_flag, int total_tokens,
+                            int num_sequences, int num_chunks, int num_heads, int head_size, int io_dtype, float scale,
+                            frwkv_stream_t stream);
+
+/*
  * The same chunked forward for hosts that may not allocate device memory (servers that gave the whole GPU to
  * fixed pools at start-up, real-time loops, plain C callers without a caching allocator).  It has no
  * counterpart in the reference, whose chunk operators allocate their workspaces through Torch on every call.
