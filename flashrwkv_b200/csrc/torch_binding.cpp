@@ -994,6 +994,13 @@ void statetune_recurrent_fp32io16_forward(torch::Tensor sco, torch::Tensor cs, t
                      std::nullopt, std::nullopt, state_dot_a, 1);
 }
 
+std::vector<torch::Tensor> wkv7_backward_chunked(torch::Tensor sco, torch::Tensor cs, torch::Tensor ce,
+                                                 torch::Tensor final_state, torch::Tensor boundary,
+                                                 torch::Tensor state_dot_a, torch::Tensor r, torch::Tensor w,
+                                                 torch::Tensor k, torch::Tensor v, torch::Tensor a, torch::Tensor b,
+                                                 std::optional<torch::Tensor> grad_output,
+                                                 std::optional<torch::Tensor> grad_final_state, double scale);
+
 // csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_backward.cpp:34-82 of the reference: gradients are written into
 // the tensors the caller passes (None = not wanted).
 void statetune_recurrent_fp32io16_backward(torch::Tensor sco, torch::Tensor cs, torch::Tensor ce,
@@ -1009,9 +1016,7 @@ void statetune_recurrent_fp32io16_backward(torch::Tensor sco, torch::Tensor cs, 
   std::optional<torch::Tensor> go, gf;
   if (grad_output.has_value()) go = grad_output->contiguous();
   if (grad_final_state.has_value()) gf = grad_final_state->contiguous().to(torch::kFloat32);
-  auto replayed = wkv7_chunk_replay(cs, ce, boundary, r, w, k, v, a, b, std::nullopt);
-  auto g = wkv7_backward(sco, cs, ce, final_state, boundary, std::get<1>(replayed), state_dot_a, r, w, k, v, a, b, go, gf,
-                         scale);
+  auto g = wkv7_backward_chunked(sco, cs, ce, final_state, boundary, state_dot_a, r, w, k, v, a, b, go, gf, scale);
   const std::optional<torch::Tensor>* outs[7] = {&grad_r, &grad_w, &grad_k, &grad_v, &grad_a, &grad_b,
                                                  &grad_initial_state};
   for (int i = 0; i < 7; ++i)
@@ -1045,6 +1050,45 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> wkv7_adjoint_scan(
                                    static_cast<int>(B), static_cast<int>(Cn), static_cast<int>(H), 64, io_dtype_of(r),
                                    static_cast<float>(scale), current_stream(r)));
   return {g_state, boundary_adjoint, error_flag};
+}
+
+// The chunked backward on the tensor cores: adjoint scan (boundary adjoints + gradient of the initial state), then
+// the chunk-parallel token gradients.  Needs only what the reference's backward is given: final state, boundary,
+// state_dot_a.  Returns (dr, dw, dk, dv, da, db, dS0, error flag).
+std::vector<torch::Tensor> wkv7_backward_chunked(torch::Tensor sco, torch::Tensor cs, torch::Tensor ce,
+                                                 torch::Tensor final_state, torch::Tensor boundary,
+                                                 torch::Tensor state_dot_a, torch::Tensor r, torch::Tensor w,
+                                                 torch::Tensor k, torch::Tensor v, torch::Tensor a, torch::Tensor b,
+                                                 std::optional<torch::Tensor> grad_output,
+                                                 std::optional<torch::Tensor> grad_final_state, double scale) {
+  check_chunk_tables(sco, cs, ce, r);
+  for (const torch::Tensor* t : {&final_state, &boundary, &state_dot_a}) {
+    check_cuda_contiguous(*t, "saved tensor");
+    TORCH_CHECK(t->scalar_type() == torch::kFloat32 && t->device() == r.device(), "saved tensors must be float32 on r's device");
+  }
+  TORCH_CHECK(r.dim() == 3 && r.size(2) == 64, "token tensors must have shape [N,H,64]");
+  const int64_t B = sco.numel() - 1, H = r.size(1), Cn = cs.numel();
+  TORCH_CHECK(final_state.dim() == 4 && final_state.size(0) == B && final_state.size(1) == H,
+              "final_state must have shape [B,H,64,64]");
+  TORCH_CHECK(boundary.dim() == 4 && boundary.size(0) == Cn && boundary.size(1) == H, "boundary must be [Cn,H,64,64]");
+  TORCH_CHECK(state_dot_a.sizes() == r.sizes(), "state_dot_a must be shaped like r");
+  const c10::cuda::CUDAGuard guard(r.device());
+  torch::Tensor go = grad_output.has_value() ? grad_output->contiguous() : torch::zeros_like(r);
+  TORCH_CHECK(go.sizes() == r.sizes() && go.scalar_type() == r.scalar_type(), "grad_output must match r");
+  auto scanned = wkv7_adjoint_scan(sco, cs, ce, r, w, a, b, go, grad_final_state, scale, std::nullopt);
+  std::vector<torch::Tensor> g;
+  for (int i = 0; i < 6; ++i) g.push_back(torch::empty_like(r));
+  auto error_flag = std::get<2>(scanned);
+  check_rc(frwkv_wkv7_chunk_backward(
+      sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(), final_state.data_ptr<float>(),
+      boundary.data_ptr<float>(), std::get<1>(scanned).data_ptr<float>(), state_dot_a.data_ptr<float>(), r.data_ptr(),
+      w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(), nullptr, go.data_ptr(), g[0].data_ptr(),
+      g[1].data_ptr(), g[2].data_ptr(), g[3].data_ptr(), g[4].data_ptr(), g[5].data_ptr(), error_flag.data_ptr<int>(),
+      static_cast<int>(B), static_cast<int>(Cn), static_cast<int>(H), 64, io_dtype_of(r), static_cast<float>(scale),
+      current_stream(r)));
+  g.push_back(std::get<0>(scanned));
+  g.push_back(error_flag);
+  return g;
 }
 
 // ---- training-side TMix glue on dense [B,T,C] tensors (names and argument order of the reference's
@@ -1438,6 +1482,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("chunk_token_ends"), py::arg("r"), py::arg("decay_logits"), py::arg("a"), py::arg("b"),
         py::arg("grad_output"), py::arg("grad_final_state") = py::none(), py::arg("scale") = 1.0,
         py::arg("decay_bias") = py::none());
+  m.def("wkv7_backward_chunked", &wkv7_backward_chunked, py::arg("sequence_chunk_offsets"),
+        py::arg("chunk_token_starts"), py::arg("chunk_token_ends"), py::arg("final_state"), py::arg("boundary"),
+        py::arg("state_dot_a"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),
+        py::arg("b"), py::arg("grad_output") = py::none(), py::arg("grad_final_state") = py::none(),
+        py::arg("scale") = 1.0);
   m.def("wkv7_chunk_replay", &wkv7_chunk_replay, py::arg("chunk_token_starts"), py::arg("chunk_token_ends"),
         py::arg("boundary"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),
         py::arg("b"), py::arg("decay_bias") = py::none());

@@ -1,0 +1,706 @@
+// Chunk-parallel WKV7 backward on the tcgen05 tensor cores (head size 64, chunks of <= 64 tokens).
+//
+// Second stage of the chunked backward.  The first stage (frwkv_wkv7_adjoint_scan) has left, for every chunk, the
+// adjoint G = dL/dS at the chunk's END; the forward has left the chunk-start state S0 (boundary) and the rows
+// U = state_dot_a.  With those every (chunk, head) is independent: a persistent CTA takes one at a time and produces
+// the six token gradients of its rows.  With the forward's quantities per chunk (g_t cumulative decay, g_L its last row)
+//     A~ = a*g_{t-1}  R~ = r*g_t  B~ = b/g_t  K~ = k/g_t,   [A_ab|A_ak ; A_rb|A_rk] = mask([A~;R~][B~;K~]^T),
+//     T = (I - A_ab)^-1,   X = A~ S0 + A_ak V,  U = T X,  Y' = R~ S0 + A_rk V + A_rb U,  S_L = g_L (S0 + B~^T U + K~^T V)
+// and dY' = scale * dy, G^ = g_L * G (rows scaled), the adjoints are
+//     dU = A_rb^T dY' + B~ G^            dX = T^T dU            dV = A_rk^T dY' + K~ G^ + A_ak^T dX
+//     [dA_ab|dA_ak ; dA_rb|dA_rk] = mask([dX;dY'] [U;V]^T)                                       =: DD
+//     [dA~ ; dR~] = [dX;dY'] S0^T + DD [B~;K~]          [dB~ ; dK~] = mask(DD^T) [A~;R~] + [U;V] G^^T
+//     da = dA~ g_{t-1}   dr = dR~ g_t   db = dB~ / g_t   dk = dK~ / g_t
+//     dlog w_s = sum_{t>=s} ( dr_t r_t - db_t b_t - dk_t k_t + da_{t+1} a_{t+1} ) + sum_v G S_L     (per key channel)
+//     dlogit = dlog w * retention_log_derivative(logit).
+// Every contraction is a tcgen05.mma kind::tf32 with fp32 accumulation.  Token x token matrices come straight from
+// row tiles ([x;y][u;v]^T needs no transposition) and stay in tensor memory, masked in place, as the A operand of
+// the next product; contractions over tokens take their B operand from tiles written transposed ([feature][token]).
+// Transposed token x token matrices are not transposed but computed: D1T = [B~;K~][A~;R~]^T, DDT = [U;V][dX;dY']^T.
+// T^T comes from the same blocked inverse as in the forward, written transposed at the end.
+//
+// Tensor-memory columns (512):  XA [A~;R~] -> [U;V]   |  XB [B~;K~] -> OUT1 [dA~;dR~]  |  D1 (A_ab) -> DD
+//                               D1T -> DDT            |  DUV [dU;dV] -> OUT2 [dB~;dK~] |  DXY [dX;dY']
+// 512 threads (warp w: lanes 32 (w % 4).., column group w / 4), one CTA per SM, ~221 KB of shared memory.
+//
+// Replaces the reference's serial backward kernels: csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_backward.cu:49-255
+// and cuda_backward_v3 of csrc/sm90/tmix/wkv7/pretrain_recurrent_bf16_forward.cu:163-291.
+
+#include "wkv7_chunk_common.cuh"
+
+namespace frwkv {
+namespace {
+
+using namespace chunk;
+
+constexpr int kL = 64;
+constexpr int kD = 64;
+constexpr int kBwdThreads = 512;
+constexpr uint32_t kCS128 = 2064;  // chunk stride of the 128-row tiles
+constexpr uint32_t kCS64 = 1040;   // ... of the 64-row tiles
+
+constexpr uint32_t kOffGT = 0;                         // g[t][k]
+constexpr uint32_t kOffRA = kOffGT + 16 * kCS64;       // [B~;K~] rows -> inverse tile (T | W) -> [T'^T;0] -> [U;V] rows
+constexpr uint32_t kOffRB = kOffRA + 16 * kCS128;      // [A~;R~] rows -> A_ab scratch -> [dX;dY'] rows
+constexpr uint32_t kOffTBK = kOffRB + 16 * kCS128;     // [B~^T | K~^T]  rows k, columns (s | 64 + s)
+constexpr uint32_t kOffTAR = kOffTBK + 32 * kCS64;     // [A~^T | R~^T]
+constexpr uint32_t kOffTDY = kOffTAR + 32 * kCS64;     // dY'^T [v][t] -> dU^T -> dX^T; at the end  db * b
+constexpr uint32_t kOffTG = kOffTDY + 16 * kCS64;      // G^^T [v][k];                 at the end  dr * r, then dlogit
+constexpr uint32_t kOffNG = kOffTG + 16 * kCS64;       // G^ [k][v];                   at the end  dk * k
+constexpr uint32_t kOffNS = kOffNG + 16 * kCS64;       // S0 [k][v];                   at the end  da * a
+constexpr uint32_t kOffW = kOffNS + 16 * kCS64;        // the chunk's decay logits [64][64] 16-bit
+constexpr uint32_t kBwdSmem = kOffW + kL * kD * 2;
+static_assert(kOffRA % 128 == 0 && kOffRB % 128 == 0 && kOffTBK % 128 == 0 && kOffTAR % 128 == 0 && kOffTDY % 128 == 0 &&
+                  kOffTG % 128 == 0 && kOffNG % 128 == 0 && kOffNS % 128 == 0 && kOffW % 128 == 0,
+              "tile bases must stay 128-byte aligned");
+static_assert(kBwdSmem + 2048 <= 232448, "the CTA must fit one SM's shared memory");
+
+constexpr uint32_t kColXA = 0, kColXB = 64, kColD1 = 128, kColD1T = 256, kColDUV = 384, kColDXY = 448;
+constexpr uint32_t kColUV = kColXA, kColOUT1 = kColXB, kColDD = kColD1, kColDDT = kColD1T, kColOUT2 = kColDUV;
+
+template <typename io_t>
+__global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
+    const int* __restrict__ seq_chunk_offsets, const int* __restrict__ chunk_starts, const int* __restrict__ chunk_ends,
+    const float* __restrict__ final_state, const float* __restrict__ boundary, const float* __restrict__ adjoint,
+    const float* __restrict__ sda_ptr, const io_t* __restrict__ r_ptr, const io_t* __restrict__ w_ptr,
+    const io_t* __restrict__ k_ptr, const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr,
+    const io_t* __restrict__ b_ptr, const io_t* __restrict__ bias_ptr, const io_t* __restrict__ dy_ptr,
+    io_t* __restrict__ dr_ptr, io_t* __restrict__ dw_ptr, io_t* __restrict__ dk_ptr, io_t* __restrict__ dv_ptr,
+    io_t* __restrict__ da_ptr, io_t* __restrict__ db_ptr, int num_sequences, int num_heads, int num_items, float scale,
+    int* __restrict__ error_flag) {
+  using IO = Io16<io_t>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ uint64_t mbar[6];
+  __shared__ uint32_t tmem_holder;
+  __shared__ float seg_total[8][64];
+  __shared__ float end_term[64];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m = 32 * (warp & 3) + lane;  // tensor-memory lane / operand row of this thread
+  const int cg = warp >> 2;              // column group: 16 of 64 columns, 32 of 128
+  const int mt = m & 63;                 // token of that row
+  const bool low = m < 64;               // lanes 0..63: a / b / dX / U rows; lanes 64..127: r / k / dY' / V rows
+  const int ch0 = 16 * cg;               // this thread's 16 channels
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < 6; ++i) umma::mbar_init(&mbar[i], 1);
+    umma::mbar_fence_init();
+  }
+  if (warp == 0) umma::tmem_alloc(&tmem_holder, 512);
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = tmem_holder;
+  const uint32_t sbase = umma::smem_u32(smem);
+  const uint32_t lane_base = uint32_t(32 * (warp & 3)) << 16;
+  const uint32_t idesc128 = umma::idesc_tf32(128, 128), idesc64 = umma::idesc_tf32(128, 64);
+  const long long row_stride = (long long)num_heads * kD;
+  bool ok = true;
+  uint32_t parity = 0;
+
+  // the decay logits of an item travel by cp.async one item ahead (one 16-byte piece per thread)
+  auto stage_w = [&](int item) {
+    const int ch = item / num_heads, hd = item % num_heads;
+    const int tt0 = chunk_starts[ch];
+    const int ln = min(max(chunk_ends[ch] - tt0, 1), kL);
+    const int rowi = tid >> 3, part = tid & 7;
+    umma::cp_async16(sbase + kOffW + tid * 16,
+                     w_ptr + (long long)(tt0 + min(rowi, ln - 1)) * row_stride + (long long)hd * kD + 8 * part,
+                     rowi < ln ? 16u : 0u);
+    umma::cp_async_commit();
+  };
+  if ((int)blockIdx.x < num_items) stage_w(blockIdx.x);
+
+  for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, parity ^= 1u) {
+    const int chunk = item / num_heads, head = item % num_heads;
+    const int t0 = chunk_starts[chunk];
+    const int len = min(max(chunk_ends[chunk] - t0, 1), kL);
+    const long long head_off = (long long)head * kD;
+    const bool valid = mt < len;
+    // the sequence this chunk belongs to: its last chunk ends in the final state, the others in the next boundary
+    int seq = 0;
+    {
+      int lo = 0, hi = num_sequences;  // largest s with seq_chunk_offsets[s] <= chunk
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (seq_chunk_offsets[mid] <= chunk) lo = mid; else hi = mid;
+      }
+      seq = lo;
+    }
+    const bool last_of_seq = chunk + 1 == seq_chunk_offsets[seq + 1];
+    const float* s_end = last_of_seq ? final_state + ((long long)seq * num_heads + head) * (kD * kD)
+                                     : boundary + ((long long)(chunk + 1) * num_heads + head) * (kD * kD);
+    const float* s_start = boundary + ((long long)chunk * num_heads + head) * (kD * kD);
+    const float* g_end = adjoint + ((long long)chunk * num_heads + head) * (kD * kD);
+    const long long row = (long long)(t0 + min(mt, len - 1)) * row_stride + head_off + ch0;
+
+    // ---- this thread's rows: 16 channels of (a, b) or (r, k, dy) ------------------------------------------------
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    uint4 praw[2], qraw[2], draw[2];
+    {
+      const uint4* pp = reinterpret_cast<const uint4*>((low ? a_ptr : r_ptr) + row);
+      const uint4* qp = reinterpret_cast<const uint4*>((low ? b_ptr : k_ptr) + row);
+      const uint4* dp = reinterpret_cast<const uint4*>(dy_ptr + row);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        praw[i] = valid ? __ldg(pp + i) : zero4;
+        qraw[i] = valid ? __ldg(qp + i) : zero4;
+        draw[i] = (valid && !low) ? __ldg(dp + i) : zero4;
+      }
+    }
+    if (tid < 64) end_term[tid] = 0.f;
+
+    // ---- g[t][k] (as in the forward kernel; threads 0..255 work) ------------------------------------------------
+    umma::cp_async_wait_all();
+    __syncthreads();
+    if (tid < 256) {
+      const int t = tid >> 2, q = tid & 3;
+      float x[16];
+      unpack8<io_t>(*reinterpret_cast<const uint4*>(smem + kOffW + t * 128 + q * 32), *reinterpret_cast<float(*)[8]>(&x[0]));
+      unpack8<io_t>(*reinterpret_cast<const uint4*>(smem + kOffW + t * 128 + q * 32 + 16), *reinterpret_cast<float(*)[8]>(&x[8]));
+      if (bias_ptr != nullptr) {
+        float bz[16];
+        unpack8<io_t>(__ldg(reinterpret_cast<const uint4*>(bias_ptr + head_off + 16 * q)), *reinterpret_cast<float(*)[8]>(&bz[0]));
+        unpack8<io_t>(__ldg(reinterpret_cast<const uint4*>(bias_ptr + head_off + 16 * q + 8)), *reinterpret_cast<float(*)[8]>(&bz[8]));
+#pragma unroll
+        for (int e = 0; e < 16; ++e) x[e] += bz[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 16; ++e) x[e] = t < len ? retention(x[e]) : 1.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        st4(smem, kOffGT + (4 * q + i) * kCS64 + t * 16, make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]));
+    }
+    __syncthreads();
+    {
+      const int kcol = tid & 63, seg = (tid >> 6) & 3;
+      const uint32_t gcol = kOffGT + uint32_t(kcol >> 2) * kCS64 + uint32_t(kcol & 3) * 4 + uint32_t(16 * seg) * 16;
+      float pr[16];
+      if (tid < 256) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pr[i] = ld1(smem, gcol + i * 16);
+#pragma unroll
+        for (int i = 1; i < 16; ++i) pr[i] *= pr[i - 1];
+        seg_total[seg][kcol] = pr[15];
+      }
+      __syncthreads();
+      if (tid < 256) {
+        float mult = 1.f;
+        if (seg > 0) mult = seg_total[0][kcol];
+        if (seg > 1) mult *= seg_total[1][kcol];
+        if (seg > 2) mult *= seg_total[2][kcol];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) st1(smem, gcol + i * 16, pr[i] * mult);
+      }
+    }
+    __syncthreads();
+
+    // ---- operands: A forms to tensor memory, row tiles and transposed tiles to shared memory --------------------
+    float dyv[16];  // dY' of this thread's row and channels (lanes 64..127), kept for the [dX;dY'] row tile
+    {
+      float pf[16], qf[16];
+      unpack8<io_t>(praw[0], *reinterpret_cast<float(*)[8]>(&pf[0]));
+      unpack8<io_t>(praw[1], *reinterpret_cast<float(*)[8]>(&pf[8]));
+      unpack8<io_t>(qraw[0], *reinterpret_cast<float(*)[8]>(&qf[0]));
+      unpack8<io_t>(qraw[1], *reinterpret_cast<float(*)[8]>(&qf[8]));
+      unpack8<io_t>(draw[0], *reinterpret_cast<float(*)[8]>(&dyv[0]));
+      unpack8<io_t>(draw[1], *reinterpret_cast<float(*)[8]>(&dyv[8]));
+      uint32_t xa[16], xb[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kc = 4 * cg + j;  // 16-byte column chunk (4 channels)
+        const float4 g = ld4(smem, kOffGT + kc * kCS64 + mt * 16);
+        float4 sc = g;              // R~ = r * g_t
+        if (low) sc = mt > 0 ? ld4(smem, kOffGT + kc * kCS64 + (mt - 1) * 16) : make_float4(1.f, 1.f, 1.f, 1.f);
+        const float4 p4 = umma::to_tf32(make_float4(pf[4 * j] * sc.x, pf[4 * j + 1] * sc.y, pf[4 * j + 2] * sc.z,
+                                                    pf[4 * j + 3] * sc.w));
+        const float4 q4 = umma::to_tf32(make_float4(qf[4 * j] * rcp_approx(g.x), qf[4 * j + 1] * rcp_approx(g.y),
+                                                    qf[4 * j + 2] * rcp_approx(g.z), qf[4 * j + 3] * rcp_approx(g.w)));
+        xa[4 * j] = __float_as_uint(p4.x); xa[4 * j + 1] = __float_as_uint(p4.y);
+        xa[4 * j + 2] = __float_as_uint(p4.z); xa[4 * j + 3] = __float_as_uint(p4.w);
+        xb[4 * j] = __float_as_uint(q4.x); xb[4 * j + 1] = __float_as_uint(q4.y);
+        xb[4 * j + 2] = __float_as_uint(q4.z); xb[4 * j + 3] = __float_as_uint(q4.w);
+        st4(smem, kOffRB + kc * kCS128 + m * 16, p4);           // [A~;R~] rows (B operand of D1T)
+        if (low) st4(smem, kOffRA + kc * kCS128 + m * 16, q4);  // B~ rows (B operand of D1)
+        // transposed: row = channel, column = this thread's token (second half of the columns for lanes 64..127)
+        const uint32_t tcol = uint32_t(m >> 2) * kCS64 + uint32_t(m & 3) * 4 + uint32_t(4 * kc) * 16;
+        st1(smem, kOffTAR + tcol, p4.x); st1(smem, kOffTAR + tcol + 16, p4.y);
+        st1(smem, kOffTAR + tcol + 32, p4.z); st1(smem, kOffTAR + tcol + 48, p4.w);
+        st1(smem, kOffTBK + tcol, q4.x); st1(smem, kOffTBK + tcol + 16, q4.y);
+        st1(smem, kOffTBK + tcol + 32, q4.z); st1(smem, kOffTBK + tcol + 48, q4.w);
+      }
+      umma::tmem_st16(tmem + kColXA + lane_base + ch0, xa);
+      umma::tmem_st16(tmem + kColXB + lane_base + ch0, xb);
+      if (!low) {
+        uint32_t dq[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          dyv[e] = umma::to_tf32(scale * dyv[e]);
+          dq[e] = __float_as_uint(dyv[e]);
+          st1(smem, kOffTDY + tile_off(kCS64, ch0 + e, mt), dyv[e]);  // dY'^T [v][t]
+        }
+        umma::tmem_st16(tmem + kColDXY + lane_base + ch0, dq);
+      }
+    }
+    // G^ = g_L * G in both orientations, S0, and the end term sum_v G S_L: thread (key k, eight value columns)
+    {
+      const int kk = tid & 63, v0 = 8 * (tid >> 6);
+      const float gl = ld1(smem, kOffGT + tile_off(kCS64, 63, kk));
+      const float4 ga = __ldg(reinterpret_cast<const float4*>(g_end + kk * kD + v0));
+      const float4 gb = __ldg(reinterpret_cast<const float4*>(g_end + kk * kD + v0 + 4));
+      const float4 sa = __ldg(reinterpret_cast<const float4*>(s_end + kk * kD + v0));
+      const float4 sb = __ldg(reinterpret_cast<const float4*>(s_end + kk * kD + v0 + 4));
+      const float4 za = __ldg(reinterpret_cast<const float4*>(s_start + kk * kD + v0));
+      const float4 zb = __ldg(reinterpret_cast<const float4*>(s_start + kk * kD + v0 + 4));
+      atomicAdd(&end_term[kk], ga.x * sa.x + ga.y * sa.y + ga.z * sa.z + ga.w * sa.w + gb.x * sb.x + gb.y * sb.y +
+                                   gb.z * sb.z + gb.w * sb.w);
+      const float4 ha = umma::to_tf32(make_float4(gl * ga.x, gl * ga.y, gl * ga.z, gl * ga.w));
+      const float4 hb = umma::to_tf32(make_float4(gl * gb.x, gl * gb.y, gl * gb.z, gl * gb.w));
+      st4(smem, kOffNG + uint32_t(v0 >> 2) * kCS64 + kk * 16, ha);
+      st4(smem, kOffNG + uint32_t((v0 >> 2) + 1) * kCS64 + kk * 16, hb);
+      st4(smem, kOffNS + uint32_t(v0 >> 2) * kCS64 + kk * 16, umma::to_tf32(za));
+      st4(smem, kOffNS + uint32_t((v0 >> 2) + 1) * kCS64 + kk * 16, umma::to_tf32(zb));
+      const uint32_t tg = kOffTG + uint32_t(kk >> 2) * kCS64 + uint32_t(kk & 3) * 4 + uint32_t(v0) * 16;
+      st1(smem, tg, ha.x); st1(smem, tg + 16, ha.y); st1(smem, tg + 32, ha.z); st1(smem, tg + 48, ha.w);
+      st1(smem, tg + 64, hb.x); st1(smem, tg + 80, hb.y); st1(smem, tg + 96, hb.z); st1(smem, tg + 112, hb.w);
+    }
+    // pull the next item's rows into L2
+    if (item + (int)gridDim.x < num_items) {
+      const int nit = item + gridDim.x, nch = nit / num_heads, nhd = nit % num_heads;
+      const int nt0 = chunk_starts[nch], nlen = chunk_ends[nch] - nt0;
+      for (int e = tid; e < 8 * kL; e += kBwdThreads) {
+        const int which = e >> 6, rowi = e & 63;
+        if (rowi < nlen) {
+          const long long at = (long long)(nt0 + rowi) * row_stride + (long long)nhd * kD;
+          if (which < 7) {
+            const io_t* base = which == 0 ? a_ptr : which == 1 ? r_ptr : which == 2 ? b_ptr : which == 3 ? k_ptr
+                               : which == 4 ? v_ptr : which == 5 ? dy_ptr : w_ptr;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(base + at));
+          } else {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(sda_ptr + at));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(sda_ptr + at + 32));
+          }
+        }
+      }
+    }
+    umma::tmem_st_wait();
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+
+    // ---- D1 = XA B~^T (only its A_ab block is used) and D1T = XB [A~;R~]^T ---------------------------------------
+    if (tid == 0) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ts(tmem + kColD1, tmem + kColXA + 8 * ks,
+                          umma::desc_k_major(sbase + kOffRA + ks * 2 * kCS128, kCS128), idesc64, ks > 0 ? 1u : 0u);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ts(tmem + kColD1T, tmem + kColXB + 8 * ks,
+                          umma::desc_k_major(sbase + kOffRB + ks * 2 * kCS128, kCS128), idesc128, ks > 0 ? 1u : 0u);
+      umma::mma_commit(&mbar[0]);
+    }
+    ok = wait_warp(&mbar[0], parity, ok);
+    umma::fence_after_sync();
+    // A_ab -> fp32 scratch (over the [A~;R~] row tile, which both products have consumed); D1T masked in place:
+    // its element [s][t] is kept for t > s (columns 0..63: products with A~) or t >= s (columns 64..127: with R~)
+    if (ok) {
+      if (low) {
+        uint32_t u[16];
+        umma::tmem_ld16(tmem + kColD1 + lane_base + ch0, u);
+        umma::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          const int s = ch0 + j;
+          const uint32_t o = kOffRB + uint32_t(mt) * 256 + uint32_t((((s >> 2)) ^ ((mt >> 1) & 7)) * 16);
+          st4(smem, o, make_float4(s < mt ? __uint_as_float(u[j]) : 0.f, s + 1 < mt ? __uint_as_float(u[j + 1]) : 0.f,
+                                   s + 2 < mt ? __uint_as_float(u[j + 2]) : 0.f, s + 3 < mt ? __uint_as_float(u[j + 3]) : 0.f));
+        }
+      }
+      if (!low || cg >= 2) {  // the A_ab^T block (lanes 0..63, columns 0..63) is never used
+        uint32_t u[32];
+        const uint32_t taddr = tmem + kColD1T + lane_base + 32 * cg;
+        umma::tmem_ld32(taddr, u);
+        umma::tmem_ld_wait();
+        const int tbase = (32 * cg) & 63;
+        const int first = cg >= 2 ? mt : mt + 1;  // smallest kept t
+#pragma unroll
+        for (int j = 0; j < 32; ++j) u[j] = tbase + j >= first ? tf32_bits(__uint_as_float(u[j])) : 0u;
+        umma::tmem_st32(taddr, u);
+        umma::tmem_st_wait();
+      }
+    }
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+
+    // ---- DUV = D1T[:,64:128] dY' + XB G^  ->  [dU ; A_rk^T dY' + K~ G^]   (runs while the CUDA cores invert) -------
+    if (tid == 0) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ts(tmem + kColDUV, tmem + kColD1T + 64 + 8 * ks,
+                          umma::desc_k_major(sbase + kOffTDY + ks * 2 * kCS64, kCS64), idesc64, ks > 0 ? 1u : 0u);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ts(tmem + kColDUV, tmem + kColXB + 8 * ks,
+                          umma::desc_k_major(sbase + kOffTG + ks * 2 * kCS64, kCS64), idesc64, 1u);
+      umma::mma_commit(&mbar[1]);
+    }
+    inverse_blocked<kOffRB, kOffRA, kCS128, true>(smem, tid);  // T'^T, rows 64..127 of the tile zero
+    __syncthreads();
+    ok = wait_warp(&mbar[1], parity, ok);
+    umma::fence_after_sync();
+    // ---- dU^T -> shared memory (over dY'^T, consumed) ------------------------------------------------------------
+    if (ok && low) {
+      uint32_t u[16];
+      umma::tmem_ld16(tmem + kColDUV + lane_base + ch0, u);
+      umma::tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 16; ++e) st1(smem, kOffTDY + tile_off(kCS64, ch0 + e, mt), umma::to_tf32(__uint_as_float(u[e])));
+    }
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    // ---- dX = dU + T'^T dU: DUV += [T'^T;0] dU ---------------------------------------------------------------------
+    if (tid == 0) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ss(tmem + kColDUV, umma::desc_k_major(sbase + kOffRA + ks * 2 * kCS128, kCS128),
+                          umma::desc_k_major(sbase + kOffTDY + ks * 2 * kCS64, kCS64), idesc64, 1u);
+      umma::mma_commit(&mbar[2]);
+    }
+    // meanwhile: this thread's 16 channels of its U row (fp32) or V row
+    float uv[16];
+    {
+      if (low) {
+        const float4* up = reinterpret_cast<const float4*>(sda_ptr + row);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 x = valid ? __ldg(up + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+          uv[4 * i] = x.x; uv[4 * i + 1] = x.y; uv[4 * i + 2] = x.z; uv[4 * i + 3] = x.w;
+        }
+      } else {
+        const uint4* vp = reinterpret_cast<const uint4*>(v_ptr + row);
+        unpack8<io_t>(valid ? __ldg(vp) : zero4, *reinterpret_cast<float(*)[8]>(&uv[0]));
+        unpack8<io_t>(valid ? __ldg(vp + 1) : zero4, *reinterpret_cast<float(*)[8]>(&uv[8]));
+      }
+#pragma unroll
+      for (int e = 0; e < 16; ++e) uv[e] = umma::to_tf32(uv[e]);
+    }
+    ok = wait_warp(&mbar[2], parity, ok);
+    umma::fence_after_sync();
+    // ---- dX: A form (tensor memory), dX^T (over dU^T), [dX;dY'] rows (over the A_ab scratch); [U;V]: A form and rows
+    //      (over [T'^T;0], consumed) ------------------------------------------------------------------------------
+    if (ok) {
+      float dx[16];
+      if (low) {
+        uint32_t u[16];
+        umma::tmem_ld16(tmem + kColDUV + lane_base + ch0, u);
+        umma::tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          dx[e] = umma::to_tf32(__uint_as_float(u[e]));
+          u[e] = __float_as_uint(dx[e]);
+          st1(smem, kOffTDY + tile_off(kCS64, ch0 + e, mt), dx[e]);
+        }
+        umma::tmem_st16(tmem + kColDXY + lane_base + ch0, u);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) dx[e] = dyv[e];
+      }
+      uint32_t uq[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kc = 4 * cg + j;
+        st4(smem, kOffRB + kc * kCS128 + m * 16, make_float4(dx[4 * j], dx[4 * j + 1], dx[4 * j + 2], dx[4 * j + 3]));
+        st4(smem, kOffRA + kc * kCS128 + m * 16, make_float4(uv[4 * j], uv[4 * j + 1], uv[4 * j + 2], uv[4 * j + 3]));
+      }
+#pragma unroll
+      for (int e = 0; e < 16; ++e) uq[e] = __float_as_uint(uv[e]);
+      umma::tmem_st16(tmem + kColUV + lane_base + ch0, uq);
+      umma::tmem_st_wait();
+    }
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    // ---- dV: DUV += D1T[:,0:64] dX;   DD = [dX;dY'] [U;V]^T ---------------------------------------------------------
+    if (tid == 0) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ts(tmem + kColDUV, tmem + kColD1T + 8 * ks,
+                          umma::desc_k_major(sbase + kOffTDY + ks * 2 * kCS64, kCS64), idesc64, 1u);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ts(tmem + kColDD, tmem + kColDXY + 8 * ks,
+                          umma::desc_k_major(sbase + kOffRA + ks * 2 * kCS128, kCS128), idesc128, ks > 0 ? 1u : 0u);
+      umma::mma_commit(&mbar[3]);
+    }
+    ok = wait_warp(&mbar[3], parity, ok);
+    umma::fence_after_sync();
+    if (ok) {
+      if (!low) {  // dV rows out
+        uint32_t u[16];
+        umma::tmem_ld16(tmem + kColDUV + lane_base + ch0, u);
+        umma::tmem_ld_wait();
+        if (valid) {
+          uint4 p0, p1;
+          p0.x = IO::pack(__uint_as_float(u[0]), __uint_as_float(u[1])); p0.y = IO::pack(__uint_as_float(u[2]), __uint_as_float(u[3]));
+          p0.z = IO::pack(__uint_as_float(u[4]), __uint_as_float(u[5])); p0.w = IO::pack(__uint_as_float(u[6]), __uint_as_float(u[7]));
+          p1.x = IO::pack(__uint_as_float(u[8]), __uint_as_float(u[9])); p1.y = IO::pack(__uint_as_float(u[10]), __uint_as_float(u[11]));
+          p1.z = IO::pack(__uint_as_float(u[12]), __uint_as_float(u[13])); p1.w = IO::pack(__uint_as_float(u[14]), __uint_as_float(u[15]));
+          uint4* dst = reinterpret_cast<uint4*>(dv_ptr + row);
+          dst[0] = p0;
+          dst[1] = p1;
+        }
+      }
+      // DD masked in place: element [t][s] kept for s < t (rows of dX) or s <= t (rows of dY')
+      {
+        uint32_t u[32];
+        const uint32_t taddr = tmem + kColDD + lane_base + 32 * cg;
+        umma::tmem_ld32(taddr, u);
+        umma::tmem_ld_wait();
+        const int sbase_col = (32 * cg) & 63;
+        const int limit = low ? mt : mt + 1;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) u[j] = sbase_col + j < limit ? tf32_bits(__uint_as_float(u[j])) : 0u;
+        umma::tmem_st32(taddr, u);
+        umma::tmem_st_wait();
+      }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    // ---- DDT = [U;V] [dX;dY']^T;   OUT1 = [dX;dY'] S0^T + DD [B~;K~]  ->  [dA~ ; dR~] --------------------------------
+    if (tid == 0) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ts(tmem + kColDDT, tmem + kColUV + 8 * ks,
+                          umma::desc_k_major(sbase + kOffRB + ks * 2 * kCS128, kCS128), idesc128, ks > 0 ? 1u : 0u);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ts(tmem + kColOUT1, tmem + kColDXY + 8 * ks,
+                          umma::desc_k_major(sbase + kOffNS + ks * 2 * kCS64, kCS64), idesc64, ks > 0 ? 1u : 0u);
+#pragma unroll
+      for (int ks = 0; ks < 16; ++ks)
+        umma::mma_tf32_ts(tmem + kColOUT1, tmem + kColDD + 8 * ks,
+                          umma::desc_k_major(sbase + kOffTBK + ks * 2 * kCS64, kCS64), idesc64, 1u);
+      umma::mma_commit(&mbar[4]);
+    }
+    ok = wait_warp(&mbar[4], parity, ok);
+    umma::fence_after_sync();
+    // ---- DDT masked in place ([s][t] kept for t > s in the dX columns, t >= s in the dY' columns); da, dr out ------
+    if (ok) {
+      {
+        uint32_t u[32];
+        const uint32_t taddr = tmem + kColDDT + lane_base + 32 * cg;
+        umma::tmem_ld32(taddr, u);
+        umma::tmem_ld_wait();
+        const int tbase = (32 * cg) & 63;
+        const int first = cg >= 2 ? mt : mt + 1;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) u[j] = tbase + j >= first ? tf32_bits(__uint_as_float(u[j])) : 0u;
+        umma::tmem_st32(taddr, u);
+        umma::tmem_st_wait();
+      }
+      // lanes 0..63: da = dA~ g_{t-1}; lanes 64..127: dr = dR~ g_t; the products da * a and dr * r go to shared memory
+      // for the decay gradient, over the S0 tile and the G^^T tile (both read only by products that have completed)
+      uint32_t u[16];
+      umma::tmem_ld16(tmem + kColOUT1 + lane_base + ch0, u);
+      umma::tmem_ld_wait();
+      float pf[16];
+      unpack8<io_t>(praw[0], *reinterpret_cast<float(*)[8]>(&pf[0]));
+      unpack8<io_t>(praw[1], *reinterpret_cast<float(*)[8]>(&pf[8]));
+      float gr[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kc = 4 * cg + j;
+        float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (!low) sc = ld4(smem, kOffGT + kc * kCS64 + mt * 16);
+        else if (mt > 0) sc = ld4(smem, kOffGT + kc * kCS64 + (mt - 1) * 16);
+        gr[4 * j] = __uint_as_float(u[4 * j]) * sc.x; gr[4 * j + 1] = __uint_as_float(u[4 * j + 1]) * sc.y;
+        gr[4 * j + 2] = __uint_as_float(u[4 * j + 2]) * sc.z; gr[4 * j + 3] = __uint_as_float(u[4 * j + 3]) * sc.w;
+        st4(smem, (low ? kOffNS : kOffTG) + kc * kCS64 + mt * 16,
+            make_float4(gr[4 * j] * pf[4 * j], gr[4 * j + 1] * pf[4 * j + 1], gr[4 * j + 2] * pf[4 * j + 2],
+                        gr[4 * j + 3] * pf[4 * j + 3]));
+      }
+      if (valid) {
+        uint4 p0, p1;
+        p0.x = IO::pack(gr[0], gr[1]); p0.y = IO::pack(gr[2], gr[3]); p0.z = IO::pack(gr[4], gr[5]); p0.w = IO::pack(gr[6], gr[7]);
+        p1.x = IO::pack(gr[8], gr[9]); p1.y = IO::pack(gr[10], gr[11]); p1.z = IO::pack(gr[12], gr[13]); p1.w = IO::pack(gr[14], gr[15]);
+        uint4* dst = reinterpret_cast<uint4*>((low ? da_ptr : dr_ptr) + row);
+        dst[0] = p0;
+        dst[1] = p1;
+      }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    // ---- OUT2 = DDT [A~;R~] + [U;V] G^^T  ->  [dB~ ; dK~] --------------------------------------------------------------
+    if (tid == 0) {
+#pragma unroll
+      for (int ks = 0; ks < 16; ++ks)
+        umma::mma_tf32_ts(tmem + kColOUT2, tmem + kColDDT + 8 * ks,
+                          umma::desc_k_major(sbase + kOffTAR + ks * 2 * kCS64, kCS64), idesc64, ks > 0 ? 1u : 0u);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ts(tmem + kColOUT2, tmem + kColUV + 8 * ks,
+                          umma::desc_k_major(sbase + kOffNG + ks * 2 * kCS64, kCS64), idesc64, 1u);
+      umma::mma_commit(&mbar[5]);
+    }
+    ok = wait_warp(&mbar[5], parity, ok);
+    umma::fence_after_sync();
+    // lanes 0..63: db = dB~ / g_s; lanes 64..127: dk = dK~ / g_s; products db * b, dk * k to shared memory
+    if (ok) {
+      uint32_t u[16];
+      umma::tmem_ld16(tmem + kColOUT2 + lane_base + ch0, u);
+      umma::tmem_ld_wait();
+      float qf[16];
+      unpack8<io_t>(qraw[0], *reinterpret_cast<float(*)[8]>(&qf[0]));
+      unpack8<io_t>(qraw[1], *reinterpret_cast<float(*)[8]>(&qf[8]));
+      float gr[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kc = 4 * cg + j;
+        const float4 g = ld4(smem, kOffGT + kc * kCS64 + mt * 16);
+        gr[4 * j] = __uint_as_float(u[4 * j]) * rcp_approx(g.x); gr[4 * j + 1] = __uint_as_float(u[4 * j + 1]) * rcp_approx(g.y);
+        gr[4 * j + 2] = __uint_as_float(u[4 * j + 2]) * rcp_approx(g.z); gr[4 * j + 3] = __uint_as_float(u[4 * j + 3]) * rcp_approx(g.w);
+        st4(smem, (low ? kOffTDY : kOffNG) + kc * kCS64 + mt * 16,
+            make_float4(gr[4 * j] * qf[4 * j], gr[4 * j + 1] * qf[4 * j + 1], gr[4 * j + 2] * qf[4 * j + 2],
+                        gr[4 * j + 3] * qf[4 * j + 3]));
+      }
+      if (valid) {
+        uint4 p0, p1;
+        p0.x = IO::pack(gr[0], gr[1]); p0.y = IO::pack(gr[2], gr[3]); p0.z = IO::pack(gr[4], gr[5]); p0.w = IO::pack(gr[6], gr[7]);
+        p1.x = IO::pack(gr[8], gr[9]); p1.y = IO::pack(gr[10], gr[11]); p1.z = IO::pack(gr[12], gr[13]); p1.w = IO::pack(gr[14], gr[15]);
+        uint4* dst = reinterpret_cast<uint4*>((low ? db_ptr : dk_ptr) + row);
+        dst[0] = p0;
+        dst[1] = p1;
+      }
+    }
+    __syncthreads();
+    // ---- decay gradient: thread (key channel, 8-token segment): D_t = dr r - db b - dk k + (da a)_{t+1}, plus the end
+    //      term at the chunk's last token; suffix sums over t; times dlog w / dlogit -----------------------------------
+    {
+      const int kcol = tid & 63, seg = tid >> 6;
+      const uint32_t col = uint32_t(kcol >> 2) * kCS64 + uint32_t(kcol & 3) * 4;
+      float dsum[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int t = 8 * seg + i;
+        float d = ld1(smem, kOffTG + col + t * 16) - ld1(smem, kOffTDY + col + t * 16) - ld1(smem, kOffNG + col + t * 16);
+        if (t + 1 < kL) d += ld1(smem, kOffNS + col + (t + 1) * 16);
+        if (t == len - 1) d += end_term[kcol];
+        dsum[i] = t < len ? d : 0.f;
+      }
+#pragma unroll
+      for (int i = 6; i >= 0; --i) dsum[i] += dsum[i + 1];
+      seg_total[seg][kcol] = dsum[0];
+      __syncthreads();
+      float later = 0.f;
+      for (int s2 = seg + 1; s2 < 8; ++s2) later += seg_total[s2][kcol];
+      const float bias = bias_ptr != nullptr ? IO::load(bias_ptr + head_off + kcol) : 0.f;
+      const io_t* wraw = reinterpret_cast<const io_t*>(smem + kOffW) + kcol;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int t = 8 * seg + i;
+        st1(smem, kOffTG + col + t * 16, (dsum[i] + later) * retention_log_derivative(IO::load(wraw + t * kD) + bias));
+      }
+    }
+    __syncthreads();
+    {
+      // dlogit rows out: thread (token, 8 channels)
+      const int t = tid >> 3, c8 = tid & 7;
+      if (t < len) {
+        const float4 x0 = ld4(smem, kOffTG + (2 * c8) * kCS64 + t * 16), x1 = ld4(smem, kOffTG + (2 * c8 + 1) * kCS64 + t * 16);
+        uint4 pk;
+        pk.x = IO::pack(x0.x, x0.y); pk.y = IO::pack(x0.z, x0.w); pk.z = IO::pack(x1.x, x1.y); pk.w = IO::pack(x1.z, x1.w);
+        *reinterpret_cast<uint4*>(dw_ptr + (long long)(t0 + t) * row_stride + head_off + 8 * c8) = pk;
+      }
+    }
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    umma::fence_after_sync();
+    if (ok && item + (int)gridDim.x < num_items) stage_w(item + gridDim.x);  // the logits have been read
+    if (!ok) {
+      // fail closed: the gradients of this item's rows read as NaN
+      const io_t nan16 = IO::store(quiet_nan());
+      io_t* outs[6] = {dr_ptr, dw_ptr, dk_ptr, dv_ptr, da_ptr, db_ptr};
+      for (int e = tid; e < len * kD; e += kBwdThreads)
+        for (int o = 0; o < 6; ++o) outs[o][(long long)(t0 + e / kD) * row_stride + head_off + e % kD] = nan16;
+    }
+  }
+  if (!ok && tid == 0 && error_flag != nullptr) atomicExch(error_flag, 5);
+  umma::cp_async_wait_all();
+  umma::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) umma::tmem_dealloc(tmem, 512);
+}
+
+template <typename io_t>
+int launch_chunk_backward(const int* sco, const int* cs, const int* ce, const float* final_state, const float* boundary,
+                          const float* adjoint, const float* sda, const void* r, const void* w, const void* k,
+                          const void* v, const void* a, const void* b, const void* bias, const void* dy, void* dr,
+                          void* dw, void* dk, void* dv, void* da, void* db, int num_sequences, int num_chunks,
+                          int num_heads, float scale, int* error_flag, int which, cudaStream_t stream) {
+  static bool opted_in[64][2] = {};
+  static int sm_counts[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
+    return fail(FRWKV_ERR_CUDA, "wkv7_chunk_backward: cannot identify the current device");
+  if (!opted_in[device][which]) {
+    cudaError_t e = cudaFuncSetAttribute(wkv7_chunk_backward_kernel<io_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kBwdSmem);
+    if (e != cudaSuccess)
+      return fail(FRWKV_ERR_CUDA, "wkv7_chunk_backward: cannot reserve shared memory: %s", cudaGetErrorString(e));
+    cudaDeviceGetAttribute(&sm_counts[device], cudaDevAttrMultiProcessorCount, device);
+    opted_in[device][which] = true;
+  }
+  const int items = num_chunks * num_heads;
+  const int grid = sm_counts[device] > 0 && sm_counts[device] < items ? sm_counts[device] : items;
+  using T = io_t;
+  wkv7_chunk_backward_kernel<T><<<(unsigned)grid, kBwdThreads, kBwdSmem, stream>>>(
+      sco, cs, ce, final_state, boundary, adjoint, sda, static_cast<const T*>(r), static_cast<const T*>(w),
+      static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const T*>(a), static_cast<const T*>(b),
+      static_cast<const T*>(bias), static_cast<const T*>(dy), static_cast<T*>(dr), static_cast<T*>(dw),
+      static_cast<T*>(dk), static_cast<T*>(dv), static_cast<T*>(da), static_cast<T*>(db), num_sequences, num_heads, items,
+      scale, error_flag);
+  return check_launch("wkv7_chunk_backward_kernel");
+}
+
+}  // namespace
+}  // namespace frwkv
+
+extern "C" int frwkv_wkv7_chunk_backward(
+    const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends, const float* final_state,
+    const float* boundary, const float* boundary_adjoint, const float* state_dot_a, const void* r,
+    const void* decay_logits, const void* k, const void* v, const void* a, const void* b, const void* decay_bias,
+    const void* grad_output, void* grad_r, void* grad_decay_logits, void* grad_k, void* grad_v, void* grad_a, void* grad_b,
+    int32_t* error_flag, int num_sequences, int num_chunks, int num_heads, int head_size, int io_dtype, float scale,
+    frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(seq_chunk_offsets && chunk_starts && chunk_ends && final_state && boundary && boundary_adjoint &&
+                    state_dot_a && r && decay_logits && k && v && a && b && grad_output && grad_r && grad_decay_logits &&
+                    grad_k && grad_v && grad_a && grad_b,
+                "wkv7_chunk_backward: null pointer argument");
+  FRWKV_REQUIRE(num_sequences > 0 && num_chunks > 0 && num_heads > 0, "wkv7_chunk_backward: sizes must be positive");
+  if (head_size != 64)
+    return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_chunk_backward: head size %d is not built (only 64)", head_size);
+  FRWKV_REQUIRE((long long)num_chunks * num_heads <= 0x7fffffffLL, "wkv7_chunk_backward: too many (chunk, head) pairs");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (io_dtype == FRWKV_DTYPE_BF16)
+    return launch_chunk_backward<__nv_bfloat16>(seq_chunk_offsets, chunk_starts, chunk_ends, final_state, boundary,
+                                                boundary_adjoint, state_dot_a, r, decay_logits, k, v, a, b, decay_bias,
+                                                grad_output, grad_r, grad_decay_logits, grad_k, grad_v, grad_a, grad_b,
+                                                num_sequences, num_chunks, num_heads, scale, error_flag, 0, s);
+  if (io_dtype == FRWKV_DTYPE_FP16)
+    return launch_chunk_backward<__half>(seq_chunk_offsets, chunk_starts, chunk_ends, final_state, boundary,
+                                         boundary_adjoint, state_dot_a, r, decay_logits, k, v, a, b, decay_bias,
+                                         grad_output, grad_r, grad_decay_logits, grad_k, grad_v, grad_a, grad_b,
+                                         num_sequences, num_chunks, num_heads, scale, error_flag, 1, s);
+  return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_chunk_backward: token tensors must be float16 or bfloat16");
+}

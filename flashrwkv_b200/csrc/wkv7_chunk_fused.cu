@@ -34,11 +34,12 @@
 // csrc/sm90/rl_infctx/wkv7/rl_infctx_chunk_fp32io16_forward.cu:317-538, and the forward halves of
 // csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_forward.cu:32-130 (boundary and state_dot_a outputs).
 
-#include "frwkv_common.cuh"
-#include "umma.cuh"
+#include "wkv7_chunk_common.cuh"
 
 namespace frwkv {
 namespace {
+
+using namespace chunk;
 
 constexpr int kL = 64;
 constexpr int kD = 64;
@@ -60,150 +61,9 @@ static_assert(2 * (kFusedSmem + 1024) <= 233472, "two CTAs must fit one SM");
 
 constexpr uint32_t kColXA = 0, kColD1 = 64, kColDA = 192, kColDC = 0, kTmemCols = 256;
 
-__device__ __forceinline__ float4 ld4(const unsigned char* base, uint32_t off) {
-  return *reinterpret_cast<const float4*>(base + off);
-}
-__device__ __forceinline__ float ld1(const unsigned char* base, uint32_t off) {
-  return *reinterpret_cast<const float*>(base + off);
-}
-__device__ __forceinline__ void st4(unsigned char* base, uint32_t off, float4 v) {
-  *reinterpret_cast<float4*>(base + off) = v;
-}
-__device__ __forceinline__ void st1(unsigned char* base, uint32_t off, float v) {
-  *reinterpret_cast<float*>(base + off) = v;
-}
-__device__ __forceinline__ uint32_t tile_off(uint32_t cs, int row, int col) {
-  return uint32_t(col >> 2) * cs + uint32_t(row) * 16 + uint32_t(col & 3) * 4;
-}
 // A_ab scratch: row t is 256 bytes; its 16-byte pieces are permuted by the row pair so that the inverse's threads,
 // which read the same piece of eight different row pairs at once, hit different banks.
 __device__ __forceinline__ uint32_t aab_off(int t, int s4) { return kOffUV + uint32_t(t) * 256 + uint32_t((s4 ^ ((t >> 1) & 7)) * 16); }
-__device__ __forceinline__ float aab(const unsigned char* smem, int t, int s) { return ld1(smem, aab_off(t, s >> 2) + (s & 3) * 4); }
-// T (then T') and the inverse's scratch W share the [T';0] tile: T in rows 0..63, W in rows 64..127
-__device__ __forceinline__ uint32_t t_off(int row, int col) { return kOffX2 + tile_off(kCST, row, col); }
-__device__ __forceinline__ uint32_t w_off(int row, int col) { return kOffX2 + tile_off(kCST, 64 + row, col); }
-
-__device__ __forceinline__ uint32_t tf32_bits(float x) { return __float_as_uint(umma::to_tf32(x)); }
-
-// Bounded wait with one answer per warp: the tensor-memory loads and stores that follow are warp-collective, so a
-// warp either does its epilogue as a whole or skips it as a whole.  Once a wait has run out no later one is tried.
-__device__ __forceinline__ bool wait_warp(uint64_t* mbar, uint32_t parity, bool ok) {
-  if (ok) ok = umma::mbar_wait_suspended(mbar, parity);
-  return __all_sync(0xffffffffu, ok) != 0;
-}
-
-// T' = (I - A)^-1 - I for the strictly lower triangular 64 x 64 A in the scratch, in fp32, by 16 x 16 blocks:
-// T_ii = (I - A_ii)^-1 (one thread per column, 16 right-looking steps), then one block anti-diagonal at a time
-// T_ib = T_ii * sum_{k=b..i-1} A_ik T_kb.  A block product is done by 32 threads with 2 x 4 register tiles and
-// 16-byte operand reads (rows of A and of T_ii, four adjacent columns of T and W).  Ends with T' rounded to tf32 in
-// rows 0..63 of the tile and zeros in rows 64..127 (the second operand half of MMA 3).  Contains barriers: every
-// thread calls it.
-__device__ __forceinline__ void fma_2x4(float (&acc)[2][4], const float4& a0, const float4& a1, const float4& t0,
-                                        const float4& t1, const float4& t2, const float4& t3) {
-  const float a[2][4] = {{a0.x, a0.y, a0.z, a0.w}, {a1.x, a1.y, a1.z, a1.w}};
-  const float t[4][4] = {{t0.x, t0.y, t0.z, t0.w}, {t1.x, t1.y, t1.z, t1.w}, {t2.x, t2.y, t2.z, t2.w},
-                         {t3.x, t3.y, t3.z, t3.w}};
-#pragma unroll
-  for (int r = 0; r < 2; ++r)
-#pragma unroll
-    for (int k = 0; k < 4; ++k)
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) acc[r][cc] = fmaf(a[r][k], t[k][cc], acc[r][cc]);
-}
-
-__device__ __forceinline__ void inverse_blocked(unsigned char* smem, int tid) {
-  if (tid < 64) {
-    const int blk = tid >> 4, jj = tid & 15;
-    float acc[16];
-#pragma unroll
-    for (int rr = 0; rr < 16; ++rr) acc[rr] = 0.f;
-#pragma unroll
-    for (int q = 0; q < 16; ++q) {
-      const float xq = acc[q] + (q == jj ? 1.f : 0.f);
-      st1(smem, t_off(16 * blk + q, 16 * blk + jj), xq);
-#pragma unroll
-      for (int rr = q + 1; rr < 16; ++rr) acc[rr] = fmaf(aab(smem, 16 * blk + rr, 16 * blk + q), xq, acc[rr]);
-    }
-  }
-  __syncthreads();
-  const int warp = tid >> 5, sub = tid & 31;
-  const int rp = sub >> 2, cq = sub & 3;  // rows 2 rp, 2 rp + 1 and columns 4 cq .. 4 cq + 3 of a block
-#pragma unroll 1
-  for (int dg = 1; dg < 4; ++dg) {
-    // Block (ib, bb) of this anti-diagonal needs sum_{kb = bb .. ib-1} A_{ib,kb} T_{kb,bb}: one warp per (block, kb)
-    // term (3, 4 and 3 warps for dg = 1, 2, 3); the term goes to W rows 16 (kb + 1) .., columns of block bb.
-    int bb = -1, kb = 0;
-    if (dg == 1) { if (warp < 3) { bb = warp; kb = warp; } }
-    else if (dg == 2) { if (warp < 4) { bb = warp >> 1; kb = bb + (warp & 1); } }
-    else { if (warp < 3) { bb = 0; kb = warp; } }
-    if (bb >= 0) {
-      const int ib = bb + dg, row = 16 * ib + 2 * rp, col = 16 * bb + 4 * cq;
-      float acc[2][4] = {};
-#pragma unroll 2
-      for (int kq = 4 * kb; kq < 4 * kb + 4; ++kq)  // four columns of A / rows of T at a time
-        fma_2x4(acc, ld4(smem, aab_off(row, kq)), ld4(smem, aab_off(row + 1, kq)), ld4(smem, t_off(4 * kq, col)),
-                ld4(smem, t_off(4 * kq + 1, col)), ld4(smem, t_off(4 * kq + 2, col)), ld4(smem, t_off(4 * kq + 3, col)));
-      st4(smem, w_off(16 * (kb + 1) + 2 * rp, col), make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]));
-      st4(smem, w_off(16 * (kb + 1) + 2 * rp + 1, col), make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]));
-    }
-    __syncthreads();
-    // T_ib = T_ii (sum of the dg terms): one warp per block
-    if (warp < 4 - dg) {
-      const int b2 = warp, ib = b2 + dg, row = 16 * ib + 2 * rp, col = 16 * b2 + 4 * cq;
-      float acc[2][4] = {};
-#pragma unroll 1
-      for (int q4 = 0; q4 < 4; ++q4) {
-        float4 w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) w[e] = ld4(smem, w_off(16 * (b2 + 1) + 4 * q4 + e, col));
-        for (int term = 1; term < dg; ++term) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float4 x = ld4(smem, w_off(16 * (b2 + term + 1) + 4 * q4 + e, col));
-            w[e].x += x.x; w[e].y += x.y; w[e].z += x.z; w[e].w += x.w;
-          }
-        }
-        const int q = 16 * ib + 4 * q4;
-        fma_2x4(acc, ld4(smem, t_off(row, q)), ld4(smem, t_off(row + 1, q)), w[0], w[1], w[2], w[3]);
-      }
-      st4(smem, t_off(row, col), make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]));
-      st4(smem, t_off(row + 1, col), make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]));
-    }
-    __syncthreads();
-  }
-  {
-    // T' = T - I, rounded; everything on and above the diagonal is zero (the blocks above it were never written)
-    const int row = tid & 63, c4 = tid >> 6;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int col = 16 * c4 + 4 * i;
-      const uint32_t o = t_off(row, col);
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (col < row) {
-        v = umma::to_tf32(ld4(smem, o));
-        if (col + 1 >= row) v.y = 0.f;
-        if (col + 2 >= row) v.z = 0.f;
-        if (col + 3 >= row) v.w = 0.f;
-      }
-      st4(smem, o, v);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int piece = tid + i * kThreads;  // 16 chunks x 64 rows of 16 bytes
-      st4(smem, kOffX2 + uint32_t(piece >> 6) * kCST + 1024 + uint32_t(piece & 63) * 16, make_float4(0.f, 0.f, 0.f, 0.f));
-    }
-  }
-}
-
-template <typename io_t>
-__device__ __forceinline__ void unpack8(uint4 u, float (&f)[8]) {
-  using IO = Io16<io_t>;
-  float2 p;
-  p = IO::unpack(u.x); f[0] = p.x; f[1] = p.y;
-  p = IO::unpack(u.y); f[2] = p.x; f[3] = p.y;
-  p = IO::unpack(u.z); f[4] = p.x; f[5] = p.y;
-  p = IO::unpack(u.w); f[6] = p.x; f[7] = p.y;
-}
 
 // kAdj = false: the forward recurrence.  kAdj = true: the same kernel walks every sequence BACKWARDS (last chunk
 // first, last token of a chunk first) and takes its key rows from an fp32 tensor: this is how the backward pass gets
@@ -516,7 +376,7 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
       umma::tmem_st_wait();
       umma::fence_before_sync();
       __syncthreads();  // the [B~;K~] tile has been read: the inverse may build T' over it
-      inverse_blocked(smem, tid);
+      inverse_blocked<kOffUV, kOffX2, kCST, false>(smem, tid);
       __syncthreads();
       // ---- epilogue 2: X^T -> shared memory (over the A_ab scratch, which the inverse has consumed) -----------------
       umma::fence_after_sync();

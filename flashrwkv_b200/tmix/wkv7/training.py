@@ -2,9 +2,10 @@
 chunks, gradient of the initial state) and dense BF16 pretraining (zero initial state).
 
 Mirrors of the reference's `flashrwkv2/tmix/wkv7/statetune.py:79-236` and `pretrain.py:50-129`.  Forward = the
-tensor-core chunk kernels (output, final state, chunk-start boundaries) plus a replay pass that stores
-`state_dot_a` and 16-token state checkpoints; backward = one reverse pass that re-anchors the state from those.
-Head size 64.  Chunks handed to StateTune may hold at most 64 tokens each.
+fused tensor-core chunk kernel, which also writes the chunk-start boundary states and `state_dot_a`.  Backward, on
+the tensor cores as well: the adjoint of the state at every chunk boundary (the same fused kernel walking the
+sequences backwards: the adjoint obeys a recurrence of the forward's form), then the token gradients of all
+(chunk, head) pairs in parallel.  Head size 64.  Chunks handed to StateTune may hold at most 64 tokens each.
 """
 from __future__ import annotations
 
@@ -18,34 +19,60 @@ from .chunk import MAX_CHUNK
 CHUNK_LEN = 16  # the reference's canonical pretraining chunk length: T must be a multiple of it
 
 
+_last_flags = {}
+
+
+def device_error_flags() -> dict:
+    """Device error words (int32[1] tensors) of the most recent training forward and backward launched from this
+    process.  A kernel whose bounded wait ran out has poisoned its outputs with NaN and left a non-zero value here;
+    reading a flag synchronises, so the operators themselves never do."""
+    return dict(_last_flags)
+
+
+def check_device_error_flags() -> None:
+    """Raise if the most recent training forward or backward reported a run-out wait (synchronises)."""
+    for stage, flag in _last_flags.items():
+        if int(flag.item()) != 0:
+            raise RuntimeError(f"WKV7 training {stage}: a tensor-core completion wait ran out "
+                               f"(device error flag {int(flag.item())}); its outputs are NaN")
+
+
 def _forward_all(state, sco, cs, ce, r, w, k, v, a, b, scale):
-    C = extension()
     output = torch.empty_like(v)
     boundary = torch.empty((cs.numel(), r.shape[1], 64, 64), device=r.device, dtype=torch.float32)
-    C.wkv7_chunk_forward(sco, cs, ce, state, r, w, k, v, a, b, output, float(scale), None, None, boundary, None, None)
-    state_dot_a, checkpoints = C.wkv7_chunk_replay(cs, ce, boundary, r, w, k, v, a, b, None)
-    return output, boundary, state_dot_a, checkpoints
+    state_dot_a = torch.empty(r.shape, device=r.device, dtype=torch.float32)
+    flag = extension().wkv7_chunk_forward(sco, cs, ce, state, r, w, k, v, a, b, output, float(scale), None, None,
+                                          boundary, None, None, state_dot_a, 1)
+    _last_flags["forward"] = flag
+    return output, boundary, state_dot_a, flag
+
+
+def _backward_all(sco, cs, ce, final_state, boundary, state_dot_a, r, w, k, v, a, b, go, gf, scale):
+    *grads, flag = extension().wkv7_backward_chunked(sco, cs, ce, final_state, boundary, state_dot_a, r, w, k, v, a, b,
+                                                     go, gf, float(scale))
+    _last_flags["backward"] = flag
+    return grads, flag
 
 
 class _StateTune(torch.autograd.Function):
     @staticmethod
     def forward(ctx, initial_state, sco, cs, ce, r, w, k, v, a, b, scale):
         state = initial_state.detach().clone()  # the caller's initial state is never mutated
-        output, boundary, state_dot_a, checkpoints = _forward_all(state, sco, cs, ce, r.detach(), w.detach(),
-                                                                  k.detach(), v.detach(), a.detach(), b.detach(), scale)
-        ctx.save_for_backward(sco, cs, ce, state, boundary, checkpoints, state_dot_a, r, w, k, v, a, b)
+        output, boundary, state_dot_a, flag = _forward_all(state, sco, cs, ce, r.detach(), w.detach(), k.detach(),
+                                                           v.detach(), a.detach(), b.detach(), scale)
+        ctx.save_for_backward(sco, cs, ce, state, boundary, state_dot_a, r, w, k, v, a, b, flag)
         ctx.scale = scale
         ctx.mark_non_differentiable(boundary, state_dot_a)
         return output, state, boundary, state_dot_a
 
     @staticmethod
     def backward(ctx, grad_output, grad_final_state, _grad_boundary, _grad_sda):
-        sco, cs, ce, final_state, boundary, checkpoints, state_dot_a, r, w, k, v, a, b = ctx.saved_tensors
+        sco, cs, ce, final_state, boundary, state_dot_a, r, w, k, v, a, b, _flag = ctx.saved_tensors
         go = None if grad_output is None else grad_output.contiguous()
         gf = None if grad_final_state is None else grad_final_state.contiguous().float()
-        dr, dw, dk, dv, da, db, dS0 = extension().wkv7_backward(
-            sco, cs, ce, final_state, boundary, checkpoints, state_dot_a, r.detach(), w.detach(), k.detach(),
-            v.detach(), a.detach(), b.detach(), go, gf, ctx.scale)
+        (dr, dw, dk, dv, da, db, dS0), _ = _backward_all(sco, cs, ce, final_state, boundary, state_dot_a, r.detach(),
+                                                         w.detach(), k.detach(), v.detach(), a.detach(), b.detach(),
+                                                         go, gf, ctx.scale)
         return dS0, None, None, None, dr, dw, dk, dv, da, db, None
 
 
@@ -126,17 +153,16 @@ class _PretrainRecurrent(torch.autograd.Function):
         tables = _dense_chunk_tables(batch, tokens, r.device)
         packed = [t.detach().view(batch * tokens, heads, head_size) for t in (r, w, k, v, a, b)]
         state = torch.zeros((batch, heads, head_size, head_size), device=r.device, dtype=torch.float32)
-        output, boundary, state_dot_a, checkpoints = _forward_all(state, *tables, *packed, 1.0)
-        ctx.save_for_backward(*tables, state, boundary, checkpoints, state_dot_a, *packed)
+        output, boundary, state_dot_a, flag = _forward_all(state, *tables, *packed, 1.0)
+        ctx.save_for_backward(*tables, state, boundary, state_dot_a, *packed, flag)
         ctx.shape = r.shape
         return output.view(r.shape)
 
     @staticmethod
     def backward(ctx, grad_output):
-        sco, cs, ce, final_state, boundary, checkpoints, state_dot_a, r, w, k, v, a, b = ctx.saved_tensors
+        sco, cs, ce, final_state, boundary, state_dot_a, r, w, k, v, a, b, _flag = ctx.saved_tensors
         go = grad_output.contiguous().view(r.shape)
-        grads = extension().wkv7_backward(sco, cs, ce, final_state, boundary, checkpoints, state_dot_a, r, w, k, v, a,
-                                          b, go, None, 1.0)
+        grads, _ = _backward_all(sco, cs, ce, final_state, boundary, state_dot_a, r, w, k, v, a, b, go, None, 1.0)
         return (*(g.view(ctx.shape) for g in grads[:6]), None)
 
 
@@ -173,4 +199,4 @@ def pretrain_recurrent_bf16(r, w, k, v, a, b, *, head_size: int = 64):
     return _PretrainRecurrent.apply(r, w, k, v, a, b, head_size)
 
 
-__all__ = ["statetune_recurrent_fp32io16", "pretrain_recurrent_bf16"]
+__all__ = ["statetune_recurrent_fp32io16", "pretrain_recurrent_bf16", "device_error_flags", "check_device_error_flags"]

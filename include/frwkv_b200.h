@@ -194,6 +194,25 @@ int frwkv_wkv7_adjoint_scan(const int32_t* seq_chunk_offsets, const int32_t* chu
                             frwkv_stream_t stream);
 
 /*
+ * Second stage of the chunked backward: the six token gradients of every (chunk, head), chunk-parallel on the tensor
+ * cores, from the forward's boundary states and state_dot_a rows and the first stage's boundary adjoints.
+ * Replaces the token-gradient part of the reference's serial backward kernels
+ * (csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_backward.cu:49-255; cuda_backward_v3 of
+ * csrc/sm90/tmix/wkv7/pretrain_recurrent_bf16_forward.cu:163-291).
+ *   final_state fp32 [B,H,64,64], boundary fp32 [Cn,H,64,64], state_dot_a fp32 [N,H,64]: outputs of the forward;
+ *   boundary_adjoint fp32 [Cn,H,64,64]: output of frwkv_wkv7_adjoint_scan; grad_output io16 [N,H,64];
+ *   grad_r .. grad_b io16 [N,H,64] (grad_decay_logits is with respect to the raw decay logits).
+ * On a failed wait the gradients of the affected chunks are NaN and *error_flag is non-zero.
+ */
+int frwkv_wkv7_chunk_backward(
+    const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends, const float* final_state,
+    const float* boundary, const float* boundary_adjoint, const float* state_dot_a, const void* r,
+    const void* decay_logits, const void* k, const void* v, const void* a, const void* b, const void* decay_bias,
+    const void* grad_output, void* grad_r, void* grad_decay_logits, void* grad_k, void* grad_v, void* grad_a, void* grad_b,
+    int32_t* error_flag, int num_sequences, int num_chunks, int num_heads, int head_size, int io_dtype, float scale,
+    frwkv_stream_t stream);
+
+/*
  * The same chunked forward for hosts that may not allocate device memory (servers that gave the whole GPU to
  * fixed pools at start-up, real-time loops, plain C callers without a caching allocator).  It has no
  * counterpart in the reference, whose chunk operators allocate their workspaces through Torch on every call.
