@@ -15,6 +15,10 @@
 // of K) at byte offset 128 r, its 16-byte pieces XOR-permuted by (r mod 8).  The matching shared-memory descriptor is
 // "K-major, 128-byte swizzle": stride byte offset 1024 (eight rows), start address advanced by 32 bytes per K = 16.
 //
+// A weight in the runtime layout [K][N] is loaded as it lies: per stage BN / 64 boxes of 64 (N) x 64 (K), i.e. tiles whose
+// 128-byte rows run along N and are indexed by k.  That is the "MN-major, 128-byte swizzle" operand form: eight k rows
+// (1024 bytes) per group, 64-column groups one box (8192 bytes) apart, start address advanced by 16 rows per K = 16.
+//
 // Replaces the cublasGemmEx / cublasLtMatmul calls of the reference's projections
 // (csrc/sm120/tmix/linear/infer_fp16_forward_varlen.cu:1403-1446,1687-1777,2817-2900).
 
@@ -53,6 +57,13 @@ struct GemmParams {
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t addr) {
   return uint64_t((addr & 0x3ffffu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
          (uint64_t(2) << 61);
+}
+
+// MN-major operand tile with 128-byte swizzle (rows = contraction index, 64 N values per row): leading offset = the
+// distance between 64-column groups (one box), stride offset = eight rows
+__device__ __forceinline__ uint64_t desc_mn_sw128(uint32_t addr) {
+  return uint64_t((addr & 0x3ffffu) >> 4) | (uint64_t(8192 >> 4) << 16) | (uint64_t(1024 >> 4) << 32) |
+         (uint64_t(1) << 46) | (uint64_t(2) << 61);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, uint64_t* mbar) {
@@ -118,19 +129,25 @@ __global__ __launch_bounds__(kGemmThreads, 1) void linear_tma_kernel(const __gri
           umma::mbar_expect_tx(&full_bar[s], C::kStageBytes);
           const uint32_t a_dst = tiles_base + s * C::kStageBytes;
           tma_load_2d(a_dst, &prm.map_x[z], kb * kBK, m0, &full_bar[s]);
-          tma_load_2d(a_dst + kABytes, &prm.map_w[z], kb * kBK, n0, &full_bar[s]);
+          if (prm.group.p[z].w_kn) {
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(a_dst + kABytes + j * 8192, &prm.map_w[z], n0 + 64 * j, kb * kBK, &full_bar[s]);
+          } else {
+            tma_load_2d(a_dst + kABytes, &prm.map_w[z], kb * kBK, n0, &full_bar[s]);
+          }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr bool is_bf16 = !__is_same(io_t, __half);
-      constexpr uint32_t idesc = idesc_f16(is_bf16, kBM, BN);
       uint32_t it = 0, t = 0;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
         int z, m0, n0;
         locate(tile, z, m0, n0);
         const int KB = (prm.group.p[z].k + kBK - 1) / kBK;
+        const bool w_kn = prm.group.p[z].w_kn != 0;
+        const uint32_t idesc = idesc_f16(is_bf16, kBM, BN, w_kn);
         const uint32_t acc = t & 1u, aph = (t >> 1) & 1u;
         if (!umma::mbar_wait(&acc_empty[acc], aph ^ 1u)) { ok = false; break; }
         umma::fence_after_sync();
@@ -142,7 +159,8 @@ __global__ __launch_bounds__(kGemmThreads, 1) void linear_tma_kernel(const __gri
           const uint32_t a_addr = tiles_base + s * C::kStageBytes, b_addr = a_addr + kABytes;
 #pragma unroll
           for (int ks = 0; ks < kBK / 16; ++ks)
-            mma_f16_ss(d_tmem, desc_sw128(a_addr + ks * 32), desc_sw128(b_addr + ks * 32), idesc,
+            mma_f16_ss(d_tmem, desc_sw128(a_addr + ks * 32),
+                       w_kn ? desc_mn_sw128(b_addr + ks * 2048) : desc_sw128(b_addr + ks * 32), idesc,
                        (kb > 0 || ks > 0) ? 1u : 0u);
           umma::mma_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
         }
@@ -226,6 +244,18 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// [K][N] 16-bit matrix (runtime-layout weight), boxes of 64 (N) x 64 (K), 128-byte swizzle, zero fill outside
+bool make_map_kn(CUtensorMap* map, const void* base, int K, int N, bool bf16) {
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)K};
+  const cuuint64_t strides[1] = {(cuuint64_t)N * 2};
+  const cuuint32_t box[2] = {64u, (cuuint32_t)kBK};
+  const cuuint32_t elem[2] = {1, 1};
+  return encode_tiled()(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                        const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <typename io_t, int BN>
 int launch_bn(GemmParams& prm, bool bf16, int sm_count, int* error_flag, cudaStream_t stream) {
   int tiles = 0;
@@ -233,7 +263,9 @@ int launch_bn(GemmParams& prm, bool bf16, int sm_count, int* error_flag, cudaStr
     const LinearProblem& p = prm.group.p[z];
     prm.tile_begin[z] = tiles;
     tiles += prm.tiles_m * ((p.n + BN - 1) / BN);
-    if (!make_map(&prm.map_x[z], p.x, prm.M, p.k, kBM, bf16) || !make_map(&prm.map_w[z], p.w, p.n, p.k, BN, bf16))
+    const bool w_ok = p.w_kn ? make_map_kn(&prm.map_w[z], p.w, p.k, p.n, bf16)
+                             : make_map(&prm.map_w[z], p.w, p.n, p.k, BN, bf16);
+    if (!make_map(&prm.map_x[z], p.x, prm.M, p.k, kBM, bf16) || !w_ok)
       return fail(FRWKV_ERR_CUDA, "tmix_linear: cuTensorMapEncodeTiled failed (problem %d)", z);
   }
   for (int z = prm.count; z <= kMaxProblems; ++z) prm.tile_begin[z] = tiles;

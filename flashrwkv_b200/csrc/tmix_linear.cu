@@ -401,6 +401,76 @@ __global__ __launch_bounds__(128, 2) void linear_tc_kernel(LinearGroup group, in
   if (warp == 0) umma::tmem_dealloc(tmem, 64);
 }
 
+// ---- small-row kernel for a weight in the runtime layout [K][N] ---------------------------------------------------
+// A CTA owns 64 output columns: lane l of every warp the columns 2 l, 2 l + 1 (one 128-byte row segment per warp and
+// k), the eight warps split K (k = warp, warp + 8, ...) and their partial sums meet in shared memory.  x is staged
+// as fp32 with the activation applied, as in the kernel above.  Fewer CTAs pull the weights than in the original
+// layout (N / 64), which is the price of reading this layout in place.
+template <typename io_t, int M>
+__global__ __launch_bounds__(256) void linear_kn_skinny_kernel(const LinearProblem pr) {
+  using IO = Io16<io_t>;
+  extern __shared__ float xs_kn[];           // [M][K]
+  __shared__ float2 part[8][M][32];
+  const int K = pr.k, N = pr.n, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const io_t* x = static_cast<const io_t*>(pr.x);
+  for (int e = tid; e < M * K; e += 256) xs_kn[e] = apply_act(IO::load(x + e), pr.act);
+  __syncthreads();
+  const int n = 64 * blockIdx.x + 2 * lane;
+  const io_t* w = static_cast<const io_t*>(pr.w);
+  float2 acc[M];
+#pragma unroll
+  for (int m = 0; m < M; ++m) acc[m] = make_float2(0.f, 0.f);
+  if (n < N) {
+#pragma unroll 4
+    for (int k = warp; k < K; k += 8) {
+      const float2 wv = IO::unpack(__ldg(reinterpret_cast<const uint32_t*>(w + (long long)k * N + n)));
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        const float xv = xs_kn[m * K + k];
+        acc[m].x = fmaf(xv, wv.x, acc[m].x);
+        acc[m].y = fmaf(xv, wv.y, acc[m].y);
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < M; ++m) part[warp][m][lane] = acc[m];
+  __syncthreads();
+  for (int e = tid; e < M * 32; e += 256) {
+    const int m = e >> 5, l = e & 31, col = 64 * blockIdx.x + 2 * l;
+    if (col < N) {
+      float2 t = part[0][m][l];
+#pragma unroll
+      for (int wv = 1; wv < 8; ++wv) {
+        t.x += part[wv][m][l].x;
+        t.y += part[wv][m][l].y;
+      }
+      *reinterpret_cast<uint32_t*>(static_cast<io_t*>(pr.y) + (long long)m * N + col) =
+          IO::pack(finish<io_t>(pr, t.x, m, col), finish<io_t>(pr, t.y, m, col + 1));
+    }
+  }
+}
+
+template <typename io_t>
+int launch_linear_kn_skinny(const LinearProblem& pr, int M, cudaStream_t stream) {
+  const size_t smem = (size_t)M * pr.k * 4;
+  const dim3 grid((pr.n + 63) / 64);
+#define FRWKV_KN(MM)                                                                                          \
+  case MM: {                                                                                                  \
+    if (smem > 24 * 1024) { /* the static partial-sum array takes up to 16 KB of the default 48 KB */        \
+      cudaError_t e = cudaFuncSetAttribute(linear_kn_skinny_kernel<io_t, MM>,                                 \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+      if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "tmix_linear: %s", cudaGetErrorString(e));            \
+    }                                                                                                         \
+    linear_kn_skinny_kernel<io_t, MM><<<grid, 256, smem, stream>>>(pr);                                       \
+    break;                                                                                                    \
+  }
+  switch (M) {
+    FRWKV_KN(1) FRWKV_KN(2) FRWKV_KN(3) FRWKV_KN(4) FRWKV_KN(5) FRWKV_KN(6) FRWKV_KN(7) FRWKV_KN(8)
+  }
+#undef FRWKV_KN
+  return check_launch("linear_kn_skinny_kernel");
+}
+
 template <typename io_t>
 int launch_linear(const LinearGroup& g, int count, int M, int max_n, int max_k, int* error_flag, cudaStream_t stream) {
   if (M <= 8) {
@@ -521,4 +591,35 @@ extern "C" int frwkv_tmix_shift_project_varlen(const void* x, void* shift_state_
   if (rc != FRWKV_OK) return rc;
   return launch_shift_state_update(x, shift_state_pool, cu_seqlens, state_indices, metadata_status, num_sequences,
                                    channels, io_dtype, s);
+}
+
+// One projection with the weight in the reference's runtime layout [k][n] (read in place: the small-row kernel above
+// for m <= 8, the TMA-fed GEMM with an MN-major B operand for more rows; there the activation must be 0).
+extern "C" int frwkv_tmix_linear_runtime_layout(const frwkv_linear_problem* problem, int m, int io_dtype,
+                                                int32_t* error_flag, frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(problem != nullptr && problem->x && problem->weight && problem->y, "tmix_linear: null pointer argument");
+  const frwkv_linear_problem& p = *problem;
+  FRWKV_REQUIRE(m > 0 && p.n > 0 && p.k > 0 && p.n % 8 == 0 && p.k % 8 == 0,
+                "tmix_linear: sizes must be positive, feature counts multiples of 8");
+  FRWKV_REQUIRE(p.act >= 0 && p.act <= 2 && p.epilogue >= 0 && p.epilogue <= 1, "tmix_linear: bad act/epilogue code");
+  if (p.epilogue == 1) FRWKV_REQUIRE(p.v && p.v_first && p.v0, "tmix_linear: value-residual epilogue needs v, v_first, v0");
+  LinearGroup g;
+  g.p[0] = LinearProblem{p.x, p.weight, p.y, p.v, p.v_first, p.v0, p.n, p.k, p.act, p.epilogue, 1};
+  for (int i = 1; i < kMaxProblems; ++i) g.p[i] = g.p[0];
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (io_dtype != FRWKV_DTYPE_BF16 && io_dtype != FRWKV_DTYPE_FP16)
+    return fail(FRWKV_ERR_UNSUPPORTED, "tmix_linear: tensors must be float16 or bfloat16");
+  if (m <= 8 && ((size_t)m * p.k * 4 <= 200 * 1024 || p.act != 0)) {
+    FRWKV_REQUIRE((size_t)m * p.k * 4 <= 200 * 1024, "tmix_linear: K too large for the small-row kernel");
+    return io_dtype == FRWKV_DTYPE_BF16 ? launch_linear_kn_skinny<__nv_bfloat16>(g.p[0], m, s)
+                                        : launch_linear_kn_skinny<__half>(g.p[0], m, s);
+  }
+  if (p.act != 0)
+    return fail(FRWKV_ERR_UNSUPPORTED, "tmix_linear: a runtime-layout weight with more than 8 rows takes no activation "
+                                       "(apply it to x first)");
+  if (!linear_tma_usable(g, 1, m))
+    return fail(FRWKV_ERR_UNSUPPORTED, "tmix_linear: runtime-layout weights need 16-byte aligned tensors");
+  return launch_linear_tma(g, 1, m, io_dtype, error_flag, s);
 }

@@ -10,12 +10,13 @@ constexpr int kMaxProblems = 4;
 
 struct LinearProblem {
   const void* x;        // [M][K]
-  const void* w;        // [N][K]
+  const void* w;        // [N][K] (w_kn == 0, the reference's original layout) or [K][N] (w_kn == 1, its runtime layout)
   void* y;              // [M][N]
   const void* v;        // epilogue 1: [M][N]
   const void* v_first;  // epilogue 1: [M][N]
   const void* v0;       // epilogue 1: [N]
   int n, k, act, epilogue;
+  int w_kn = 0;
 };
 struct LinearGroup {
   LinearProblem p[kMaxProblems];
@@ -62,10 +63,11 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// instruction descriptor of kind::f16: fp32 accumulate, both operands K-major, fp16 (0) or bf16 (1) inputs
-__host__ __device__ constexpr uint32_t idesc_f16(bool bf16, int M, int N) {
-  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (uint32_t(N >> 3) << 17) |
-         (uint32_t(M >> 4) << 24);
+// instruction descriptor of kind::f16: fp32 accumulate, A K-major, fp16 (0) or bf16 (1) inputs; bit 16 set = the B
+// operand is MN-major (its tile holds rows of the contraction index: a [K][N] weight as it lies in memory)
+__host__ __device__ constexpr uint32_t idesc_f16(bool bf16, int M, int N, bool b_mn_major = false) {
+  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+         (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
 }
 
 // stores the last row of every sequence in its shift-state slot (tmix_elementwise.cu)

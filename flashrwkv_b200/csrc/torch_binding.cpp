@@ -847,6 +847,128 @@ std::vector<torch::Tensor> tmix_linear_grouped(std::vector<torch::Tensor> xs, st
   return outs;
 }
 
+// ---- the reference's native projection names (csrc/sm120/tmix/linear/infer_fp16_forward_varlen.cpp:399-472 there) ----
+// Every one is `act(x) @ W` with W given in the original layout [N,K] (`weight`, `*_t`) and / or the runtime layout
+// [K,N] (`weight_is_transposed`, the un-suffixed low-rank arguments).  The original layout is used when it is
+// given; a weight given only in the runtime layout is read in place (frwkv_tmix_linear_runtime_layout).
+using OptTensor = std::optional<torch::Tensor>;
+using Vres = std::optional<std::tuple<torch::Tensor, torch::Tensor, torch::Tensor>>;
+
+torch::Tensor linear_runtime_layout(torch::Tensor x, const torch::Tensor& w_kn, int64_t act, const Vres& vres) {
+  check_io16(x, "x", x);
+  check_io16(w_kn, "weight", x);
+  TORCH_CHECK(x.dim() == 2 && x.size(0) > 0 && w_kn.dim() == 2 && w_kn.size(0) == x.size(1),
+              "runtime-layout weight must have shape [K,N] matching x [M,K]");
+  TORCH_CHECK(x.size(1) % 8 == 0 && w_kn.size(1) % 8 == 0, "feature counts must be multiples of 8");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t M = x.size(0);
+  if (M > 8 && act != 0) {  // the many-row kernel for this layout has no activation stage
+    x = tmix_act_forward(x, act);
+    act = 0;
+  }
+  auto y = torch::empty({M, w_kn.size(1)}, x.options());
+  frwkv_linear_problem p{x.data_ptr(), w_kn.data_ptr(), y.data_ptr(), static_cast<int>(w_kn.size(1)),
+                         static_cast<int>(x.size(1)), static_cast<int>(act), 0, nullptr, nullptr, nullptr};
+  if (vres.has_value()) {
+    const auto& [v, v_first, v0] = *vres;
+    check_io16(v, "v", x);
+    check_io16(v_first, "v_first", x);
+    check_io16(v0, "v0", x);
+    TORCH_CHECK(v.sizes() == y.sizes() && v_first.sizes() == y.sizes(), "v and v_first must have shape [M,N]");
+    TORCH_CHECK(v0.dim() == 1 && v0.size(0) == y.size(1), "v0 must have shape [N]");
+    p.epilogue = 1;
+    p.v = v.data_ptr();
+    p.v_first = v_first.data_ptr();
+    p.v0 = v0.data_ptr();
+  }
+  check_rc(frwkv_tmix_linear_runtime_layout(&p, static_cast<int>(M), io_dtype_of(x), nullptr, current_stream(x)));
+  return y;
+}
+
+// a group of projections, each with its weight in either layout: one launch when all are original-layout
+std::vector<torch::Tensor> linear_any_group(std::vector<torch::Tensor> xs, const std::vector<OptTensor>& originals,
+                                            const std::vector<OptTensor>& runtimes, std::vector<int64_t> acts,
+                                            const Vres& vres) {
+  bool all_original = true;
+  for (size_t i = 0; i < xs.size(); ++i) {
+    TORCH_CHECK(originals[i].has_value() || runtimes[i].has_value(), "one of weight or weight_t must be provided");
+    all_original = all_original && originals[i].has_value();
+  }
+  if (all_original) {
+    std::vector<torch::Tensor> ws;
+    for (const auto& w : originals) ws.push_back(*w);
+    return tmix_linear_grouped(std::move(xs), std::move(ws), std::move(acts), vres);
+  }
+  std::vector<torch::Tensor> outs;
+  for (size_t i = 0; i < xs.size(); ++i) {
+    const Vres one = (vres.has_value() && i + 1 == xs.size()) ? vres : Vres();
+    if (originals[i].has_value()) outs.push_back(tmix_linear_grouped({xs[i]}, {*originals[i]}, {acts[i]}, one)[0]);
+    else outs.push_back(linear_runtime_layout(xs[i], *runtimes[i], acts[i], one));
+  }
+  return outs;
+}
+
+torch::Tensor ref_linear_forward(torch::Tensor x, torch::Tensor weight, bool weight_is_transposed) {
+  if (weight_is_transposed) return linear_runtime_layout(x, weight, 0, Vres());
+  return tmix_linear_grouped({x}, {weight}, {0}, Vres())[0];
+}
+torch::Tensor ref_linear_c2c(torch::Tensor x, torch::Tensor weight) { return ref_linear_forward(x, weight, false); }
+torch::Tensor ref_linear_t(torch::Tensor x, torch::Tensor weight_t) {
+  TORCH_CHECK(x.dim() == 2 && x.size(0) <= 65535, "TMix linear_t supports at most 65535 packed rows");
+  return tmix_linear_grouped({x}, {weight_t}, {0}, Vres())[0];
+}
+torch::Tensor ref_linear_t_tanh(torch::Tensor x, torch::Tensor weight_t) {
+  TORCH_CHECK(x.dim() == 2 && x.size(0) <= 65535, "TMix linear_t supports at most 65535 packed rows");
+  return tmix_linear_grouped({x}, {weight_t}, {1}, Vres())[0];
+}
+torch::Tensor ref_linear_t_sigmoid(torch::Tensor x, torch::Tensor weight_t) {
+  TORCH_CHECK(x.dim() == 2 && x.size(0) <= 65535, "TMix linear_t supports at most 65535 packed rows");
+  return tmix_linear_grouped({x}, {weight_t}, {2}, Vres())[0];
+}
+torch::Tensor ref_act_tanh(torch::Tensor x) { return tmix_act_forward(x, 1); }
+torch::Tensor ref_act_sigmoid(torch::Tensor x) { return tmix_act_forward(x, 2); }
+torch::Tensor ref_linear_t_vres(torch::Tensor x, torch::Tensor weight_t, torch::Tensor v, torch::Tensor v_first,
+                                torch::Tensor v0) {
+  TORCH_CHECK(x.dim() == 2 && x.size(0) <= 65535, "TMix linear_t supports at most 65535 packed rows");
+  return tmix_linear_grouped({x}, {weight_t}, {0}, std::make_tuple(v, v_first, v0))[0];
+}
+void check_rank(const torch::Tensor& x, const OptTensor& weight, const OptTensor& weight_t, bool input_projection) {
+  TORCH_CHECK(weight.has_value() || weight_t.has_value(), "one of weight or weight_t must be provided");
+  const int64_t rank = weight.has_value() ? (input_projection ? weight->size(1) : weight->size(0))
+                                          : (input_projection ? weight_t->size(0) : weight_t->size(1));
+  TORCH_CHECK(rank <= 512, "low-rank projection requires R<=512");
+  (void)x;
+}
+torch::Tensor ref_rank_dispatch(torch::Tensor x, OptTensor weight, OptTensor weight_t) {
+  return linear_any_group({x}, {weight_t}, {weight}, {0}, Vres())[0];
+}
+std::vector<torch::Tensor> ref_lowrank_in(torch::Tensor x_w, torch::Tensor x_a, torch::Tensor x_g, OptTensor w1_t,
+                                          OptTensor a1_t, OptTensor g1_t, OptTensor w1, OptTensor a1, OptTensor g1) {
+  check_rank(x_w, w1, w1_t, true); check_rank(x_a, a1, a1_t, true); check_rank(x_g, g1, g1_t, true);
+  return linear_any_group({x_w, x_a, x_g}, {w1_t, a1_t, g1_t}, {w1, a1, g1}, {0, 0, 0}, Vres());
+}
+std::vector<torch::Tensor> ref_lowrank_wagv_in(torch::Tensor x_w, torch::Tensor x_a, torch::Tensor x_g, torch::Tensor x_v,
+                                               OptTensor w1_t, OptTensor a1_t, OptTensor g1_t, OptTensor v1_t,
+                                               OptTensor w1, OptTensor a1, OptTensor g1, OptTensor v1) {
+  check_rank(x_w, w1, w1_t, true); check_rank(x_a, a1, a1_t, true); check_rank(x_g, g1, g1_t, true);
+  check_rank(x_v, v1, v1_t, true);
+  return linear_any_group({x_w, x_a, x_g, x_v}, {w1_t, a1_t, g1_t, v1_t}, {w1, a1, g1, v1}, {0, 0, 0, 0}, Vres());
+}
+std::vector<torch::Tensor> ref_lowrank_out(torch::Tensor w1, torch::Tensor a1, torch::Tensor g1, OptTensor w2_t,
+                                           OptTensor a2_t, OptTensor g2_t, OptTensor w2, OptTensor a2, OptTensor g2) {
+  check_rank(w1, w2, w2_t, false); check_rank(a1, a2, a2_t, false); check_rank(g1, g2, g2_t, false);
+  return linear_any_group({w1, a1, g1}, {w2_t, a2_t, g2_t}, {w2, a2, g2}, {1, 0, 2}, Vres());
+}
+std::vector<torch::Tensor> ref_lowrank_vres(torch::Tensor w1, torch::Tensor a1, torch::Tensor g1, torch::Tensor v1,
+                                            OptTensor w2_t, OptTensor a2_t, OptTensor g2_t, OptTensor v2_t, OptTensor w2,
+                                            OptTensor a2, OptTensor g2, OptTensor v2, torch::Tensor v,
+                                            torch::Tensor v_first, torch::Tensor v0) {
+  check_rank(w1, w2, w2_t, false); check_rank(a1, a2, a2_t, false); check_rank(g1, g2, g2_t, false);
+  check_rank(v1, v2, v2_t, false);
+  return linear_any_group({w1, a1, g1, v1}, {w2_t, a2_t, g2_t, v2_t}, {w2, a2, g2, v2}, {1, 0, 2, 0},
+                          std::make_tuple(v, v_first, v0));
+}
+
 // ---- training side -------------------------------------------------------------------------------------
 // state_dot_a [N,H,D] and the 16-token checkpoints [Cn,3,H,D,D] for the backward pass, from the chunk boundaries
 std::tuple<torch::Tensor, torch::Tensor> wkv7_chunk_replay(torch::Tensor cs, torch::Tensor ce, torch::Tensor boundary,
@@ -999,7 +1121,8 @@ std::vector<torch::Tensor> wkv7_backward_chunked(torch::Tensor sco, torch::Tenso
                                                  torch::Tensor state_dot_a, torch::Tensor r, torch::Tensor w,
                                                  torch::Tensor k, torch::Tensor v, torch::Tensor a, torch::Tensor b,
                                                  std::optional<torch::Tensor> grad_output,
-                                                 std::optional<torch::Tensor> grad_final_state, double scale);
+                                                 std::optional<torch::Tensor> grad_final_state, double scale,
+                                                 std::vector<torch::Tensor> into = {});
 
 // csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_backward.cpp:34-82 of the reference: gradients are written into
 // the tensors the caller passes (None = not wanted).
@@ -1060,7 +1183,8 @@ std::vector<torch::Tensor> wkv7_backward_chunked(torch::Tensor sco, torch::Tenso
                                                  torch::Tensor state_dot_a, torch::Tensor r, torch::Tensor w,
                                                  torch::Tensor k, torch::Tensor v, torch::Tensor a, torch::Tensor b,
                                                  std::optional<torch::Tensor> grad_output,
-                                                 std::optional<torch::Tensor> grad_final_state, double scale) {
+                                                 std::optional<torch::Tensor> grad_final_state, double scale,
+                                                 std::vector<torch::Tensor> into) {
   check_chunk_tables(sco, cs, ce, r);
   for (const torch::Tensor* t : {&final_state, &boundary, &state_dot_a}) {
     check_cuda_contiguous(*t, "saved tensor");
@@ -1076,8 +1200,14 @@ std::vector<torch::Tensor> wkv7_backward_chunked(torch::Tensor sco, torch::Tenso
   torch::Tensor go = grad_output.has_value() ? grad_output->contiguous() : torch::zeros_like(r);
   TORCH_CHECK(go.sizes() == r.sizes() && go.scalar_type() == r.scalar_type(), "grad_output must match r");
   auto scanned = wkv7_adjoint_scan(sco, cs, ce, r, w, a, b, go, grad_final_state, scale, std::nullopt);
-  std::vector<torch::Tensor> g;
-  for (int i = 0; i < 6; ++i) g.push_back(torch::empty_like(r));
+  std::vector<torch::Tensor> g = std::move(into);  // the caller's six gradient tensors, or none: allocate
+  if (g.empty())
+    for (int i = 0; i < 6; ++i) g.push_back(torch::empty_like(r));
+  TORCH_CHECK(g.size() == 6, "six gradient tensors are expected");
+  for (const auto& t : g) {
+    check_cuda_contiguous(t, "gradient tensor");
+    TORCH_CHECK(t.numel() == r.numel() && t.scalar_type() == r.scalar_type(), "gradient tensors must match r");
+  }
   auto error_flag = std::get<2>(scanned);
   check_rc(frwkv_wkv7_chunk_backward(
       sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(), final_state.data_ptr<float>(),
@@ -1089,6 +1219,108 @@ std::vector<torch::Tensor> wkv7_backward_chunked(torch::Tensor sco, torch::Tenso
   g.push_back(std::get<0>(scanned));
   g.push_back(error_flag);
   return g;
+}
+
+// ---- the dense pretraining operator library: torch.ops.rwkv7_clampw_v3.{forward,backward} ------------------------
+// Same two schemas as csrc/sm90/tmix/wkv7/pretrain_recurrent_bf16_forward.cpp:20-53 of the reference (the Python
+// wrapper flashrwkv2/tmix/wkv7/pretrain.py:50-113 calls them with tensors it allocated):
+//   forward(r, w, k, v, a, b, y, s, sa, head_size):  r..b, y io16 [B,T,H,D]; s fp32 [B,H,T/16,D,D] receives the state
+//     (key row, value column) after every 16 tokens; sa fp32 [B,T,H,D] receives S_{t-1}^T a_t.
+//   backward(r, w, k, v, a, b, dy, s, sa, dr, dw, dk, dv, da, db, head_size): the six gradients, dw with respect to
+//     the raw `w` input (the retention transform included).
+// Here the forward is the fused 64-token chunk kernel (y, sa, state at every 64-token boundary) followed by the
+// element-wise checkpoint kernel that fills `s`; the backward takes every fourth checkpoint as its chunk boundary.
+// Unlike the reference's launches (legacy default stream) everything runs on the current Torch stream.
+struct DenseTables {
+  torch::Tensor sco, cs, ce;
+  int64_t per;
+};
+DenseTables dense_tables(int64_t B, int64_t T, const torch::Tensor& like) {
+  const int64_t per = (T + 63) / 64;
+  auto opt = like.options().dtype(torch::kInt32);
+  auto idx = torch::arange(B * per, opt);
+  auto bi = torch::floor_divide(idx, per);
+  auto cs = bi * T + (idx - bi * per) * 64;
+  auto ce = torch::minimum(cs + 64, (bi + 1) * T);
+  return {(torch::arange(B + 1, opt) * per).to(torch::kInt32).contiguous(), cs.to(torch::kInt32).contiguous(),
+          ce.to(torch::kInt32).contiguous(), per};
+}
+torch::Tensor g_clampw_flags[2];  // device error flags of the last forward / backward (read on request only)
+
+std::vector<torch::Tensor> clampw_error_flags() {
+  std::vector<torch::Tensor> out;
+  for (const auto& f : g_clampw_flags)
+    if (f.defined()) out.push_back(f);
+  return out;
+}
+
+void clampw_check(const torch::Tensor& r, const torch::Tensor& t, const char* name) {
+  check_cuda_contiguous(t, name);
+  TORCH_CHECK(t.scalar_type() == r.scalar_type() && t.device() == r.device() && t.sizes() == r.sizes(), name,
+              " must match r in dtype, device and shape");
+}
+void clampw_check_saved(const torch::Tensor& r, const torch::Tensor& s, const torch::Tensor& sa) {
+  const int64_t B = r.size(0), T = r.size(1), H = r.size(2);
+  check_cuda_contiguous(s, "s");
+  check_cuda_contiguous(sa, "sa");
+  TORCH_CHECK(s.scalar_type() == torch::kFloat32 && sa.scalar_type() == torch::kFloat32 && s.device() == r.device() &&
+                  sa.device() == r.device(),
+              "s and sa must be float32 on r's device");
+  TORCH_CHECK(s.numel() == B * H * (T / 16) * 64 * 64, "s must have shape [B,H,T/16,64,64]");
+  TORCH_CHECK(sa.numel() == r.numel(), "sa must have shape [B,T,H,64]");
+}
+void clampw_check_head(const torch::Tensor& r, int64_t head_size) {
+  TORCH_CHECK(head_size == 64 || head_size == 128 || head_size == 256, "head_size must be one of 64, 128, or 256");
+  TORCH_CHECK(r.dim() == 4 && r.size(3) == head_size, "input head dimension must equal head_size");
+  TORCH_CHECK(head_size == 64, "this build trains head size 64 only");
+  TORCH_CHECK(r.scalar_type() == torch::kBFloat16 || r.scalar_type() == torch::kFloat16, "r must be bfloat16 or float16");
+  check_cuda_contiguous(r, "r");
+  TORCH_CHECK(r.numel() > 0 && r.size(1) % 16 == 0, "T must be a positive multiple of 16");
+}
+
+void clampw_forward(torch::Tensor& r, torch::Tensor& w, torch::Tensor& k, torch::Tensor& v, torch::Tensor& a,
+                    torch::Tensor& b, torch::Tensor& y, torch::Tensor& s, torch::Tensor& sa, int64_t head_size) {
+  clampw_check_head(r, head_size);
+  const torch::Tensor* named[] = {&w, &k, &v, &a, &b, &y};
+  const char* names[] = {"w", "k", "v", "a", "b", "y"};
+  for (int i = 0; i < 6; ++i) clampw_check(r, *named[i], names[i]);
+  clampw_check_saved(r, s, sa);
+  const int64_t B = r.size(0), T = r.size(1), H = r.size(2);
+  const c10::cuda::CUDAGuard guard(r.device());
+  const DenseTables tab = dense_tables(B, T, r);
+  auto state = torch::zeros({B, H, 64, 64}, r.options().dtype(torch::kFloat32));
+  auto boundary = torch::empty({B * tab.per, H, 64, 64}, state.options());
+  auto flat = [&](const torch::Tensor& t) { return t.view({B * T, H, 64}); };
+  g_clampw_flags[0] = wkv7_chunk_forward(tab.sco, tab.cs, tab.ce, state, flat(r), flat(w), flat(k), flat(v), flat(a),
+                                         flat(b), flat(y), 1.0, std::nullopt, std::nullopt, boundary, std::nullopt,
+                                         std::nullopt, flat(sa), 1);
+  check_rc(frwkv_wkv7_dense_checkpoints(boundary.data_ptr<float>(), sa.data_ptr<float>(), w.data_ptr(), k.data_ptr(),
+                                        v.data_ptr(), b.data_ptr(), s.data_ptr<float>(), static_cast<int>(B),
+                                        static_cast<int>(T), static_cast<int>(H), 64, io_dtype_of(r), current_stream(r)));
+}
+
+void clampw_backward(torch::Tensor& r, torch::Tensor& w, torch::Tensor& k, torch::Tensor& v, torch::Tensor& a,
+                     torch::Tensor& b, torch::Tensor& dy, torch::Tensor& s, torch::Tensor& sa, torch::Tensor& dr,
+                     torch::Tensor& dw, torch::Tensor& dk, torch::Tensor& dv, torch::Tensor& da, torch::Tensor& db,
+                     int64_t head_size) {
+  clampw_check_head(r, head_size);
+  const torch::Tensor* named[] = {&w, &k, &v, &a, &b, &dy, &dr, &dw, &dk, &dv, &da, &db};
+  const char* names[] = {"w", "k", "v", "a", "b", "dy", "dr", "dw", "dk", "dv", "da", "db"};
+  for (int i = 0; i < 12; ++i) clampw_check(r, *named[i], names[i]);
+  clampw_check_saved(r, s, sa);
+  const int64_t B = r.size(0), T = r.size(1), H = r.size(2), G = T / 16;
+  const c10::cuda::CUDAGuard guard(r.device());
+  const DenseTables tab = dense_tables(B, T, r);
+  auto s5 = s.view({B, H, G, 64, 64});
+  auto final_state = s5.select(2, G - 1).contiguous();
+  // chunk c starts from the checkpoint after token 64 c, i.e. s[:, :, 4 c - 1]; chunk 0 from the zero state
+  auto boundary = torch::zeros({B, tab.per, H, 64, 64}, s.options());
+  if (tab.per > 1) boundary.slice(1, 1).copy_(s5.slice(2, 3, 4 * (tab.per - 1), 4).permute({0, 2, 1, 3, 4}));
+  auto flat = [&](const torch::Tensor& t) { return t.view({B * T, H, 64}); };
+  auto g = wkv7_backward_chunked(tab.sco, tab.cs, tab.ce, final_state, boundary.view({B * tab.per, H, 64, 64}), flat(sa),
+                                 flat(r), flat(w), flat(k), flat(v), flat(a), flat(b), flat(dy), std::nullopt, 1.0,
+                                 {flat(dr), flat(dw), flat(dk), flat(dv), flat(da), flat(db)});
+  g_clampw_flags[1] = g.back();
 }
 
 // ---- training-side TMix glue on dense [B,T,C] tensors (names and argument order of the reference's
@@ -1486,7 +1718,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("chunk_token_starts"), py::arg("chunk_token_ends"), py::arg("final_state"), py::arg("boundary"),
         py::arg("state_dot_a"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),
         py::arg("b"), py::arg("grad_output") = py::none(), py::arg("grad_final_state") = py::none(),
-        py::arg("scale") = 1.0);
+        py::arg("scale") = 1.0, py::arg("into") = std::vector<torch::Tensor>{});
+  m.def("rwkv7_clampw_v3_error_flags", &clampw_error_flags);
   m.def("wkv7_chunk_replay", &wkv7_chunk_replay, py::arg("chunk_token_starts"), py::arg("chunk_token_ends"),
         py::arg("boundary"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),
         py::arg("b"), py::arg("decay_bias") = py::none());
@@ -1512,6 +1745,41 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("pretrain_tmix_lnx_rkvres_xg_backward", &pretrain_tmix_lnx_rkvres_xg_backward);
   m.def("recurrent_add_vec_forward_varlen", &recurrent_add_vec_forward_varlen, py::arg("x"), py::arg("vec"));
   m.def("tmix_act_forward", &tmix_act_forward, py::arg("x"), py::arg("act"));
+  m.def("tmix_linear_runtime_layout", &linear_runtime_layout, py::arg("x"), py::arg("weight_kn"), py::arg("act") = 0,
+        py::arg("vres") = py::none());
+  m.def("tmix_linear_forward_varlen", &ref_linear_forward, py::arg("x"), py::arg("weight"),
+        py::arg("weight_is_transposed") = false);
+  m.def("tmix_linear_attention_c2c_forward_varlen", &ref_linear_c2c, py::arg("x"), py::arg("weight"));
+  m.def("tmix_linear_ffn_key_forward_varlen", &ref_linear_c2c, py::arg("x"), py::arg("weight"));
+  m.def("tmix_linear_t_forward_varlen", &ref_linear_t, py::arg("x"), py::arg("weight_t"));
+  m.def("tmix_linear_t_tanh_forward_varlen", &ref_linear_t_tanh, py::arg("x"), py::arg("weight_t"));
+  m.def("tmix_linear_t_sigmoid_forward_varlen", &ref_linear_t_sigmoid, py::arg("x"), py::arg("weight_t"));
+  m.def("tmix_linear_act_tanh_forward_varlen", &ref_act_tanh, py::arg("x"));
+  m.def("tmix_linear_act_sigmoid_forward_varlen", &ref_act_sigmoid, py::arg("x"));
+  m.def("tmix_linear_t_vres_forward_varlen", &ref_linear_t_vres, py::arg("x"), py::arg("weight_t"), py::arg("v"),
+        py::arg("v_first"), py::arg("v0"));
+  m.def("tmix_linear_rank_in_dispatch_forward_varlen", &ref_rank_dispatch, py::arg("x"), py::arg("weight") = py::none(),
+        py::arg("weight_t") = py::none());
+  m.def("tmix_linear_rank_out_dispatch_forward_varlen", &ref_rank_dispatch, py::arg("x"), py::arg("weight") = py::none(),
+        py::arg("weight_t") = py::none());
+  m.def("tmix_lowrank_in_forward_varlen", &ref_lowrank_in, py::arg("x_w"), py::arg("x_a"), py::arg("x_g"),
+        py::arg("w1_t") = py::none(), py::arg("a1_t") = py::none(), py::arg("g1_t") = py::none(),
+        py::arg("w1") = py::none(), py::arg("a1") = py::none(), py::arg("g1") = py::none());
+  m.def("tmix_lowrank_wagv_in_forward_varlen", &ref_lowrank_wagv_in, py::arg("x_w"), py::arg("x_a"), py::arg("x_g"),
+        py::arg("x_v"), py::arg("w1_t") = py::none(), py::arg("a1_t") = py::none(), py::arg("g1_t") = py::none(),
+        py::arg("v1_t") = py::none(), py::arg("w1") = py::none(), py::arg("a1") = py::none(),
+        py::arg("g1") = py::none(), py::arg("v1") = py::none());
+  m.def("tmix_lowrank_out_forward_varlen", &ref_lowrank_out, py::arg("w1"), py::arg("a1"), py::arg("g1"),
+        py::arg("w2_t") = py::none(), py::arg("a2_t") = py::none(), py::arg("g2_t") = py::none(),
+        py::arg("w2") = py::none(), py::arg("a2") = py::none(), py::arg("g2") = py::none());
+  m.def("tmix_lowrank_vres_forward_varlen", &ref_lowrank_vres, py::arg("w1"), py::arg("a1"), py::arg("g1"),
+        py::arg("v1"), py::arg("w2_t"), py::arg("a2_t"), py::arg("g2_t"), py::arg("v2_t"), py::arg("w2"), py::arg("a2"),
+        py::arg("g2"), py::arg("v2"), py::arg("v"), py::arg("v_first"), py::arg("v0"));
   m.def("tmix_linear_grouped", &tmix_linear_grouped, py::arg("xs"), py::arg("weights"), py::arg("acts"),
         py::arg("vres") = py::none());
+}
+
+TORCH_LIBRARY(rwkv7_clampw_v3, m) {
+  m.def("forward", clampw_forward);
+  m.def("backward", clampw_backward);
 }

@@ -2,8 +2,9 @@
 
 Mirror of the reference's `flashrwkv2/tmix/linear/__init__.py:25-482` (names, positional/keyword split, the
 `R <= 512` limit).  Every operator here is `act(x) @ W^T` with `W` in the reference's *original* layout `[N,K]`;
-groups of three or four projections go to the device in one launch.  Weights given only in the reference's
-*runtime* layout `[K,N]` are refused: the kernels read the original layout (no hidden transposes).
+groups of three or four projections go to the device in one launch.  A weight given only in the reference's
+*runtime* layout `[K,N]` (`weight_is_transposed=True`, the `*_runtime` arguments) is read in place by kernels of
+its own (a small-row kernel, and the TMA GEMM with an MN-major operand): no transposed copy is made.
 fp16 as in the reference, bf16 in addition.
 """
 from __future__ import annotations
@@ -24,37 +25,55 @@ def _check_x(x, name="x", ref=None):
 
 
 def _original(name, original, runtime, x, *, rank_dim: int | None, input_projection: bool):
-    """Pick the original-layout weight [N,K] for `x @ W^T`; validate shapes and the low-rank limit."""
+    """Validate the weight(s) of `x @ W^T`; returns `(original [N,K] or None, runtime [K,N] or None)`."""
     if original is None and runtime is None:
         raise ValueError(f"{name}: an original-layout or a runtime-layout weight is required")
-    if original is None:
-        raise ValueError(f"{name}: only a runtime-layout weight was given; this build reads the original "
-                         f"[out_features,in_features] layout")
-    check_io(name, original, x)
-    if original.ndim != 2 or original.shape[1] != x.shape[1]:
-        raise ValueError(f"{name} must have original layout [N,K] with K = {x.shape[1]}")
+    if original is not None:
+        check_io(name, original, x)
+        if original.ndim != 2 or original.shape[1] != x.shape[1]:
+            raise ValueError(f"{name} must have original layout [N,K] with K = {x.shape[1]}")
     if runtime is not None:
         check_io(f"{name}_runtime", runtime, x)
-        if runtime.shape != (original.shape[1], original.shape[0]):
+        if runtime.ndim != 2 or runtime.shape[0] != x.shape[1]:
+            raise ValueError(f"{name}_runtime must have runtime layout [K,N] with K = {x.shape[1]}")
+        if original is not None and runtime.shape != (original.shape[1], original.shape[0]):
             raise ValueError(f"{name}_runtime must be the [K,N] transpose of {name}")
     if rank_dim is not None:
-        rank = original.shape[0] if input_projection else original.shape[1]
+        if original is not None:
+            rank = original.shape[0] if input_projection else original.shape[1]
+        else:
+            rank = runtime.shape[1] if input_projection else runtime.shape[0]
         if rank > rank_dim:
             raise ValueError(f"{name}: low-rank dimension {rank} exceeds R <= {rank_dim}")
-    return original
+    return original, runtime
 
 
 def _grouped(xs, weights, acts, vres=None):
-    return extension().tmix_linear_grouped(list(xs), list(weights), [_ACT[a] for a in acts], vres)
+    """`weights`: one `(original, runtime)` pair (or a plain original-layout tensor) per projection.  All-original groups leave in one launch; a
+    projection that has only the runtime layout takes the kernels that read `[K,N]` in place."""
+    C = extension()
+    codes = [_ACT[a] for a in acts]
+    weights = [w if isinstance(w, tuple) else (w, None) for w in weights]
+    if all(o is not None for o, _ in weights):
+        return C.tmix_linear_grouped(list(xs), [o for o, _ in weights], codes, vres)
+    outs = []
+    for i, (x, (o, r)) in enumerate(zip(xs, weights)):
+        one = vres if i + 1 == len(xs) else None
+        if o is not None:
+            outs.append(C.tmix_linear_grouped([x], [o], [codes[i]], one)[0])
+        else:
+            outs.append(C.tmix_linear_runtime_layout(x, r, codes[i], one))
+    return outs
 
 
 # ---- dense linears ----------------------------------------------------------------------------------------
 def infer_tmix_linear_forward_varlen(x, weight, *, weight_is_transposed: bool = False):
-    """`x [M,K] @ weight[N,K]^T -> [M,N]`."""
+    """`x [M,K] @ weight[N,K]^T -> [M,N]`; with `weight_is_transposed` the weight is `[K,N]` and `x @ weight`."""
     _check_x(x)
     if weight_is_transposed:
-        raise ValueError("weight_is_transposed=True (runtime [K,N] layout) is not built; pass weight as [N,K]")
-    w = _original("weight", weight, None, x, rank_dim=None, input_projection=True)
+        w = _original("weight", None, weight, x, rank_dim=None, input_projection=True)
+    else:
+        w = _original("weight", weight, None, x, rank_dim=None, input_projection=True)
     return _grouped([x], [w], ["none"])[0]
 
 

@@ -247,6 +247,17 @@ int frwkv_wkv7_chunk_replay(const int32_t* chunk_starts, const int32_t* chunk_en
                             int num_chunks, int num_heads, int head_size, int io_dtype, frwkv_stream_t stream);
 
 /*
+ * Dense training layout [B,T,H,64]: fills checkpoints fp32 [B,H,T/16,64,64] with the state (key row, value column)
+ * after every 16 tokens, from the state at the start of every 64-token chunk (boundary fp32 [B*ceil(T/64),H,64,64],
+ * chunks of one sequence consecutive) and the rows state_dot_a fp32 [B,T,H,64] that the chunk forward wrote.
+ * T must be a multiple of 16.  Replaces the `s_` checkpoint stores of forward_kernel_preload
+ * (csrc/sm90/tmix/wkv7/pretrain_recurrent_bf16_forward.cu:85-92).
+ */
+int frwkv_wkv7_dense_checkpoints(const float* boundary, const float* state_dot_a, const void* decay_logits,
+                                 const void* k, const void* v, const void* b, float* checkpoints, int batch,
+                                 int tokens, int num_heads, int head_size, int io_dtype, frwkv_stream_t stream);
+
+/*
  * WKV7 backward over packed sequences with chunk tables (see frwkv_wkv7_chunk_fp32io16_forward for their meaning).
  * Inputs: the forward's final_state [B,H,64,64], boundary [Cn,H,64,64], and the replay's checkpoints / state_dot_a;
  * grad_output io16 [N,H,64] (NULL = zero) and grad_final_state fp32 [B,H,64,64] (NULL = zero).
@@ -368,6 +379,11 @@ typedef struct {
 } frwkv_linear_problem;
 int frwkv_tmix_linear_grouped(const frwkv_linear_problem* problems, int count, int m, int io_dtype,
                               int32_t* error_flag, frwkv_stream_t stream);
+/* One projection whose `weight` is in the reference's RUNTIME layout [k][n] (weight_is_transposed=True, the `w1` /
+ * `w2` arguments of the low-rank operators: flashrwkv2/tmix/linear/__init__.py:25-56,279-320 and
+ * csrc/sm120/tmix/linear/infer_fp16_forward_varlen.cpp:289-308), read in place.  With m > 8 `act` must be 0. */
+int frwkv_tmix_linear_runtime_layout(const frwkv_linear_problem* problem, int m, int io_dtype, int32_t* error_flag,
+                                     frwkv_stream_t stream);
 
 /* out = x + vec; x, out io16 [total_rows][channels], vec io16 [channels], channels even.  Replaces
  * recurrent_add_vec_forward_varlen_cuda (csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu:1247-1290). */

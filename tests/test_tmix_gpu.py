@@ -142,8 +142,21 @@ def test_lowrank_group_and_dense_linear_vs_oracle(oracle, dtype, M):
     assert rel_rmse(y.float().cpu(), oracle.linear_nt(xs["w"], W)) <= tol
     with pytest.raises(ValueError, match="R <= 512"):
         F.infer_tmix_linear_rank_in_forward_varlen(xs["w"].cuda(), weight_t=rn(520, C).cuda())
-    with pytest.raises(ValueError, match="runtime"):
-        F.infer_tmix_linear_rank_in_forward_varlen(xs["w"].cuda(), weight=rn(C, 96).cuda())
+    with pytest.raises(ValueError, match="runtime layout"):
+        F.infer_tmix_linear_rank_in_forward_varlen(xs["w"].cuda(), weight=rn(C + 8, 96).cuda())
+    # the same projections from weights held only in the runtime layout [K,N]
+    kn = {n: w1[n].t().contiguous().cuda() for n in "wagv"}
+    rt = F.infer_tmix_lowrank_wagv_in_forward_varlen(*_c(*(xs[n] for n in "wagv")), None, None, None, None,
+                                                     **{f"{n}1_runtime": kn[n] for n in "wagv"})
+    for n, got in zip("wagv", rt):
+        assert rel_rmse(got.float().cpu(), oracle.linear_nt(xs[n], w1[n])) <= tol
+    kn2 = {n: w2[n].t().contiguous().cuda() for n in "wagv"}
+    rt2 = F.infer_tmix_lowrank_vres_forward_varlen(*_c(*(feats[n] for n in "wagv")), None, None, None, None,
+                                                   *_c(v, v_first, v0), **{f"{n}2_runtime": kn2[n] for n in "wagv"})
+    for got, ref in zip(rt2, outs):
+        assert rel_rmse(got.float().cpu(), ref.float().cpu()) <= tol
+    one = F.infer_tmix_linear_rank_out_tanh_forward_varlen(feats["w"].cuda(), weight=kn2["w"])
+    assert rel_rmse(one.float().cpu(), outs[0].float().cpu()) <= tol
 
 
 def test_golden_lowrank_pair():
@@ -181,6 +194,11 @@ def test_dense_linear_ragged_shapes(oracle, dtype, shape):
     assert y.shape == (M, N)
     assert rel_rmse(y.double().cpu(), ref) <= TOL[dtype]
     assert max_abs(y.double().cpu(), ref) <= 8 * TOL[dtype] * float(ref.abs().max())
+    if N % 8 == 0:  # the runtime layout [K,N] read in place (rows of N must be 16-byte aligned)
+        y_kn = F.infer_tmix_linear_forward_varlen(x.cuda(), W.t().contiguous().cuda(), weight_is_transposed=True)
+        assert y_kn.shape == (M, N)
+        assert rel_rmse(y_kn.double().cpu(), ref) <= TOL[dtype]
+        assert max_abs(y_kn.double().cpu(), ref) <= 8 * TOL[dtype] * float(ref.abs().max())
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])

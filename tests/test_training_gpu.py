@@ -9,7 +9,7 @@ gradients (tests/fixtures/tolerances-v1.json:13-17).
 import pytest
 import torch
 
-from _util import load_golden, rel_rmse
+from _util import load_golden, max_abs, rel_rmse
 
 pytestmark = pytest.mark.gpu
 TOKENS = ("r", "w", "k", "v", "a", "b")
@@ -109,3 +109,44 @@ def test_reference_named_native_statetune_entries_match_golden():
         if name == "dv":
             continue  # passed as None: not wanted
         assert torch.allclose(t.float().cpu(), g[name], atol=6e-4, rtol=6e-3), name
+
+
+def test_dense_op_library_checkpoints_and_gradients(oracle):
+    """torch.ops.rwkv7_clampw_v3 at T = 208 (three full 64-token chunks and a 16-token tail): `s` holds the oracle's
+    state after every 16 tokens, `sa` its state_dot_a rows, and the backward (which takes every fourth checkpoint
+    as a chunk boundary) gives the gradients of the oracle's float64 backward."""
+    import flashrwkv_b200
+    from flashrwkv_b200._ext import extension
+
+    native = extension()  # loading the native module registers the op library
+    B, T, H = 2, 208, 2
+    gen = torch.Generator().manual_seed(20260806)
+    four = [(torch.randn(B, T, H, 64, generator=gen) * sc).to(torch.bfloat16).cuda()
+            for sc in (0.12, 2.0, 0.1, 0.1, 0.1, 0.1)]
+    dy = (torch.randn(B, T, H, 64, generator=gen) * 0.5).to(torch.bfloat16).cuda()
+    y = torch.empty_like(four[3])
+    s = torch.full((B, H, T // 16, 64, 64), float("nan"), device="cuda")
+    sa = torch.full((B, T, H, 64), float("nan"), device="cuda")
+    torch.ops.rwkv7_clampw_v3.forward(*four, y, s, sa, 64)
+    grads = [torch.full_like(four[0], float("nan")) for _ in range(6)]
+    torch.ops.rwkv7_clampw_v3.backward(*four, dy, s, sa, *grads, 64)
+    torch.cuda.synchronize()
+    G = T // 16
+    cs = torch.arange(G, dtype=torch.int32) * 16
+    cu = torch.tensor([0, T], dtype=torch.int32)
+    for bi in range(B):
+        packed = [t[bi].float().cpu() for t in four]
+        want = oracle.forward(*packed, state_pool=torch.zeros(1, H, 64, 64), cu_seqlens=cu,
+                              chunks=(torch.tensor([0, G], dtype=torch.int32), cs, cs + 16), want_state_dot_a=True)
+        assert rel_rmse(y[bi].float().cpu(), want["y"]) <= 8e-3
+        assert rel_rmse(sa[bi].cpu(), want["state_dot_a"]) <= 3e-3
+        for c in range(G):
+            after = want["boundary"][c + 1] if c + 1 < G else want["state_pool"][0]
+            assert rel_rmse(s[bi, :, c].cpu(), after) <= 3e-3, (bi, c)
+            assert max_abs(s[bi, :, c].cpu(), after) <= 3e-3 * float(abs(after).max()) + 1e-5, (bi, c)
+        back = oracle.backward(*packed, initial_state=torch.zeros(1, H, 64, 64), cu_seqlens=cu,
+                               grad_output=dy[bi].float().cpu())
+        for got, name in zip(grads, ("r", "decay_logits", "k", "v", "a", "b")):
+            assert torch.isfinite(got).all()
+            assert rel_rmse(got[bi].float().cpu(), back[name]) <= 1.5e-2, name
+    assert all(int(f.item()) == 0 for f in native.rwkv7_clampw_v3_error_flags())
