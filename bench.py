@@ -310,7 +310,8 @@ def _extras(dev):
     out["chunked_prefill"] = {
         "workload": f"B={Bc} T={T} H={Hc} D={D} chunk 64, bf16 tokens, fp32 state", "tokens_per_s": n_tok / sec,
         "ms": sec * 1e3, "hbm_frac_algorithmic": alg_bytes / sec / hbm, "tensor_frac_of_bf16_peak": flops / sec / bf16,
-        "tensor_frac_of_tf32_peak": flops / sec / (bf16 / 2), "gpu_launches_per_call": 2}
+        "tensor_frac_of_tf32_peak": flops / sec / (bf16 / 2), "gpu_launches_per_call": 1,
+        "kernel": "wkv7_chunk_fused_kernel"}
     del toks, pool
     # ---- training forward + backward
     Ht = 64
@@ -326,9 +327,12 @@ def _extras(dev):
 
     sec = _time_cuda(train_step, warmup=1, iters=2)
     out["training_fwd_bwd"] = {
-        "workload": f"B={Bc} T={T} H={Ht} D={D}, forward (chunk build + scan + replay) and backward",
+        "workload": f"B={Bc} T={T} H={Ht} D={D}, forward (fused chunk kernel: y, boundary states, state_dot_a) and "
+                    "backward (adjoint scan + chunk-parallel tensor-core backward)",
         "tokens_per_s": n_tok / sec, "ms": sec * 1e3, "tensor_frac_of_bf16_peak": n_tok * Ht * 294912 / sec / bf16,
-        "gpu_launches_per_call": 5}
+        "gpu_launches_per_call": 4,
+        "kernels": "wkv7_chunk_fused_kernel, adjoint_key_kernel, wkv7_chunk_fused_kernel<adjoint>, "
+                   "wkv7_chunk_backward_kernel"}
     del toks, S0, dy
     torch.cuda.empty_cache()
     # ---- TMix layer chain, C = 2048

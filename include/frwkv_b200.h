@@ -219,7 +219,9 @@ int frwkv_wkv7_chunk_backward(
  * The workspace is a 16 MiB array built into the library (resident on every GPU that loads it), which limits a
  * call to num_chunks * num_heads <= frwkv_wkv7_chunk_noalloc_max_items() = 256; larger calls are refused with
  * FRWKV_ERR_INVALID_ARGUMENT and a message.  No cudaMalloc / cudaFree or allocating library call is made.
- * The first call on each device looks up the array's device address (make it outside stream capture).
+ * The first call on each device looks up the array's device address and, if nothing of this library ran there
+ * before, makes the CUDA runtime load the library's module onto that device (a one-time, driver-side set-up that
+ * may itself allocate): make that call at start-up, outside stream capture, before the no-allocation phase begins.
  * All calls share the one array: calls whose kernels could overlap on the GPU must be ordered by the caller.
  * Arguments are those of frwkv_wkv7_chunk_fp32io16_forward without workspace / workspace_bytes.
  */
