@@ -1105,13 +1105,125 @@ void rl_infctx_chunk_fp32io16_backward_replay(torch::Tensor cs, torch::Tensor ce
                      std::nullopt, std::nullopt, state_dot_a, 1);
 }
 
+// ---- head sizes 128 / 256: the plain-recurrence training kernels (csrc/wkv7_train_wide.cu) -------------------------
+void check_wide_tokens(const torch::Tensor& r, const std::vector<const torch::Tensor*>& others) {
+  check_cuda_contiguous(r, "r");
+  TORCH_CHECK(r.dim() == 3 && (r.size(2) == 128 || r.size(2) == 256), "token tensors must have shape [N,H,128] or [N,H,256]");
+  TORCH_CHECK(r.scalar_type() == torch::kBFloat16 || r.scalar_type() == torch::kFloat16,
+              "token tensors must be float16 or bfloat16");
+  for (const torch::Tensor* t : others) {
+    check_cuda_contiguous(*t, "token tensor");
+    TORCH_CHECK(t->scalar_type() == r.scalar_type() && t->device() == r.device() && t->numel() == r.numel(),
+                "token tensors must match r in dtype, device and size");
+  }
+}
+
+void wkv7_train_wide_forward(torch::Tensor sco, torch::Tensor cs, torch::Tensor ce, torch::Tensor state, torch::Tensor r,
+                             torch::Tensor w, torch::Tensor k, torch::Tensor v, torch::Tensor a, torch::Tensor b,
+                             torch::Tensor output, std::optional<torch::Tensor> boundary,
+                             std::optional<torch::Tensor> state_dot_a, double scale,
+                             std::optional<torch::Tensor> dense_checkpoints) {
+  check_chunk_tables(sco, cs, ce, r);
+  check_wide_tokens(r, {&w, &k, &v, &a, &b, &output});
+  const int64_t B = sco.numel() - 1, H = r.size(1), D = r.size(2), Cn = cs.numel();
+  check_cuda_contiguous(state, "state");
+  TORCH_CHECK(state.scalar_type() == torch::kFloat32 && state.device() == r.device() && state.numel() == B * H * D * D,
+              "state must be float32 [B,H,D,D] on the token device");
+  float* bnd = nullptr;
+  float* sda = nullptr;
+  float* dense = nullptr;
+  int dense_groups = 0;
+  if (boundary.has_value()) {
+    check_cuda_contiguous(*boundary, "boundary");
+    TORCH_CHECK(boundary->scalar_type() == torch::kFloat32 && boundary->numel() == Cn * H * D * D, "boundary must be float32 [Cn,H,D,D]");
+    bnd = boundary->data_ptr<float>();
+  }
+  if (state_dot_a.has_value()) {
+    check_cuda_contiguous(*state_dot_a, "state_dot_a");
+    TORCH_CHECK(state_dot_a->scalar_type() == torch::kFloat32 && state_dot_a->numel() == r.numel(), "state_dot_a must be float32 [N,H,D]");
+    sda = state_dot_a->data_ptr<float>();
+  }
+  if (dense_checkpoints.has_value()) {
+    check_cuda_contiguous(*dense_checkpoints, "dense_checkpoints");
+    TORCH_CHECK(dense_checkpoints->scalar_type() == torch::kFloat32 && dense_checkpoints->dim() == 5 &&
+                    dense_checkpoints->size(0) == B && dense_checkpoints->size(1) == H,
+                "dense_checkpoints must be float32 [B,H,T/16,D,D]");
+    dense = dense_checkpoints->data_ptr<float>();
+    dense_groups = static_cast<int>(dense_checkpoints->size(2));
+  }
+  const c10::cuda::CUDAGuard guard(r.device());
+  check_rc(frwkv_wkv7_train_wide_forward(sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(),
+                                         state.data_ptr<float>(), r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                         a.data_ptr(), b.data_ptr(), output.data_ptr(), bnd, sda, dense, dense_groups,
+                                         static_cast<int>(B), static_cast<int>(H), static_cast<int>(D), io_dtype_of(r),
+                                         static_cast<float>(scale), current_stream(r)));
+}
+
+// returns (grad_r, grad_decay_logits, grad_k, grad_v, grad_a, grad_b, grad_initial_state)
+std::vector<torch::Tensor> wkv7_train_wide_backward(torch::Tensor sco, torch::Tensor cs, torch::Tensor ce,
+                                                    torch::Tensor final_state, torch::Tensor boundary,
+                                                    torch::Tensor state_dot_a, torch::Tensor r, torch::Tensor w,
+                                                    torch::Tensor k, torch::Tensor v, torch::Tensor a, torch::Tensor b,
+                                                    std::optional<torch::Tensor> grad_output,
+                                                    std::optional<torch::Tensor> grad_final_state, double scale,
+                                                    std::vector<torch::Tensor> into) {
+  check_chunk_tables(sco, cs, ce, r);
+  check_wide_tokens(r, {&w, &k, &v, &a, &b});
+  const int64_t B = sco.numel() - 1, N = r.size(0), H = r.size(1), D = r.size(2), Cn = cs.numel();
+  for (const torch::Tensor* t : {&final_state, &boundary, &state_dot_a}) {
+    check_cuda_contiguous(*t, "saved tensor");
+    TORCH_CHECK(t->scalar_type() == torch::kFloat32 && t->device() == r.device(), "saved tensors must be float32 on r's device");
+  }
+  TORCH_CHECK(final_state.numel() == B * H * D * D, "final_state must have shape [B,H,D,D]");
+  TORCH_CHECK(boundary.numel() == Cn * H * D * D, "boundary must have shape [Cn,H,D,D]");
+  TORCH_CHECK(state_dot_a.numel() == r.numel(), "state_dot_a must be shaped like r");
+  const c10::cuda::CUDAGuard guard(r.device());
+  const void* go = nullptr;
+  torch::Tensor go_t, gf_t;
+  if (grad_output.has_value()) {
+    go_t = grad_output->contiguous();
+    TORCH_CHECK(go_t.numel() == r.numel() && go_t.scalar_type() == r.scalar_type(), "grad_output must match r");
+    go = go_t.data_ptr();
+  }
+  const float* gf = nullptr;
+  if (grad_final_state.has_value()) {
+    gf_t = grad_final_state->contiguous().to(torch::kFloat32);
+    TORCH_CHECK(gf_t.numel() == final_state.numel(), "grad_final_state must match final_state");
+    gf = gf_t.data_ptr<float>();
+  }
+  std::vector<torch::Tensor> g = std::move(into);
+  if (g.empty())
+    for (int i = 0; i < 6; ++i) g.push_back(torch::empty_like(r));
+  TORCH_CHECK(g.size() == 6, "six gradient tensors are expected");
+  for (const auto& t : g) {
+    check_cuda_contiguous(t, "gradient tensor");
+    TORCH_CHECK(t.numel() == r.numel() && t.scalar_type() == r.scalar_type(), "gradient tensors must match r");
+  }
+  auto dS0 = torch::empty_like(final_state);
+  const size_t floats = frwkv_wkv7_train_wide_workspace_floats(N, static_cast<int>(Cn), static_cast<int>(H), static_cast<int>(D));
+  auto workspace = torch::empty({static_cast<int64_t>(floats)}, final_state.options());
+  check_rc(frwkv_wkv7_train_wide_backward(
+      sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(), final_state.data_ptr<float>(),
+      boundary.data_ptr<float>(), state_dot_a.data_ptr<float>(), r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(),
+      a.data_ptr(), b.data_ptr(), go, gf, g[0].data_ptr(), g[1].data_ptr(), g[2].data_ptr(), g[3].data_ptr(),
+      g[4].data_ptr(), g[5].data_ptr(), dS0.data_ptr<float>(), workspace.data_ptr<float>(), N, static_cast<int>(B),
+      static_cast<int>(Cn), static_cast<int>(H), static_cast<int>(D), io_dtype_of(r), static_cast<float>(scale),
+      current_stream(r)));
+  g.push_back(dS0);
+  return g;
+}
+
 // csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_forward.cpp:26-56 of the reference: `state` [B,H,D,D] is updated
 // in place to the final state; output, boundary and state_dot_a are filled.
 void statetune_recurrent_fp32io16_forward(torch::Tensor sco, torch::Tensor cs, torch::Tensor ce, torch::Tensor state,
                                           torch::Tensor r, torch::Tensor w, torch::Tensor k, torch::Tensor v,
                                           torch::Tensor a, torch::Tensor b, torch::Tensor output, torch::Tensor boundary,
                                           torch::Tensor state_dot_a, double scale) {
-  TORCH_CHECK(r.dim() == 3 && r.size(2) == 64, "this build trains head size 64 only");
+  TORCH_CHECK(r.dim() == 3, "token tensors must have shape [N,H,D]");
+  if (r.size(2) != 64) {  // head sizes 128 / 256: the plain-recurrence kernels
+    wkv7_train_wide_forward(sco, cs, ce, state, r, w, k, v, a, b, output, boundary, state_dot_a, scale, std::nullopt);
+    return;
+  }
   wkv7_chunk_forward(sco, cs, ce, state, r, w, k, v, a, b, output, scale, std::nullopt, std::nullopt, boundary,
                      std::nullopt, std::nullopt, state_dot_a, 1);
 }
@@ -1135,11 +1247,14 @@ void statetune_recurrent_fp32io16_backward(torch::Tensor sco, torch::Tensor cs, 
                                            std::optional<torch::Tensor> grad_k, std::optional<torch::Tensor> grad_v,
                                            std::optional<torch::Tensor> grad_a, std::optional<torch::Tensor> grad_b,
                                            std::optional<torch::Tensor> grad_initial_state, double scale) {
-  TORCH_CHECK(r.dim() == 3 && r.size(2) == 64, "this build trains head size 64 only");
+  TORCH_CHECK(r.dim() == 3, "token tensors must have shape [N,H,D]");
   std::optional<torch::Tensor> go, gf;
   if (grad_output.has_value()) go = grad_output->contiguous();
   if (grad_final_state.has_value()) gf = grad_final_state->contiguous().to(torch::kFloat32);
-  auto g = wkv7_backward_chunked(sco, cs, ce, final_state, boundary, state_dot_a, r, w, k, v, a, b, go, gf, scale);
+  auto g = r.size(2) == 64
+               ? wkv7_backward_chunked(sco, cs, ce, final_state, boundary, state_dot_a, r, w, k, v, a, b, go, gf, scale)
+               : wkv7_train_wide_backward(sco, cs, ce, final_state, boundary, state_dot_a, r, w, k, v, a, b, go, gf,
+                                          scale, {});
   const std::optional<torch::Tensor>* outs[7] = {&grad_r, &grad_w, &grad_k, &grad_v, &grad_a, &grad_b,
                                                  &grad_initial_state};
   for (int i = 0; i < 7; ++i)
@@ -1260,19 +1375,18 @@ void clampw_check(const torch::Tensor& r, const torch::Tensor& t, const char* na
               " must match r in dtype, device and shape");
 }
 void clampw_check_saved(const torch::Tensor& r, const torch::Tensor& s, const torch::Tensor& sa) {
-  const int64_t B = r.size(0), T = r.size(1), H = r.size(2);
+  const int64_t B = r.size(0), T = r.size(1), H = r.size(2), D = r.size(3);
   check_cuda_contiguous(s, "s");
   check_cuda_contiguous(sa, "sa");
   TORCH_CHECK(s.scalar_type() == torch::kFloat32 && sa.scalar_type() == torch::kFloat32 && s.device() == r.device() &&
                   sa.device() == r.device(),
               "s and sa must be float32 on r's device");
-  TORCH_CHECK(s.numel() == B * H * (T / 16) * 64 * 64, "s must have shape [B,H,T/16,64,64]");
-  TORCH_CHECK(sa.numel() == r.numel(), "sa must have shape [B,T,H,64]");
+  TORCH_CHECK(s.numel() == B * H * (T / 16) * D * D, "s must have shape [B,H,T/16,D,D]");
+  TORCH_CHECK(sa.numel() == r.numel(), "sa must have shape [B,T,H,D]");
 }
 void clampw_check_head(const torch::Tensor& r, int64_t head_size) {
   TORCH_CHECK(head_size == 64 || head_size == 128 || head_size == 256, "head_size must be one of 64, 128, or 256");
   TORCH_CHECK(r.dim() == 4 && r.size(3) == head_size, "input head dimension must equal head_size");
-  TORCH_CHECK(head_size == 64, "this build trains head size 64 only");
   TORCH_CHECK(r.scalar_type() == torch::kBFloat16 || r.scalar_type() == torch::kFloat16, "r must be bfloat16 or float16");
   check_cuda_contiguous(r, "r");
   TORCH_CHECK(r.numel() > 0 && r.size(1) % 16 == 0, "T must be a positive multiple of 16");
@@ -1285,12 +1399,17 @@ void clampw_forward(torch::Tensor& r, torch::Tensor& w, torch::Tensor& k, torch:
   const char* names[] = {"w", "k", "v", "a", "b", "y"};
   for (int i = 0; i < 6; ++i) clampw_check(r, *named[i], names[i]);
   clampw_check_saved(r, s, sa);
-  const int64_t B = r.size(0), T = r.size(1), H = r.size(2);
+  const int64_t B = r.size(0), T = r.size(1), H = r.size(2), D = head_size;
   const c10::cuda::CUDAGuard guard(r.device());
   const DenseTables tab = dense_tables(B, T, r);
-  auto state = torch::zeros({B, H, 64, 64}, r.options().dtype(torch::kFloat32));
+  auto state = torch::zeros({B, H, D, D}, r.options().dtype(torch::kFloat32));
+  auto flat = [&](const torch::Tensor& t) { return t.view({B * T, H, D}); };
+  if (D != 64) {  // head sizes 128 / 256: the plain recurrence writes the 16-token states itself
+    wkv7_train_wide_forward(tab.sco, tab.cs, tab.ce, state, flat(r), flat(w), flat(k), flat(v), flat(a), flat(b), flat(y),
+                            std::nullopt, flat(sa), 1.0, s.view({B, H, T / 16, D, D}));
+    return;
+  }
   auto boundary = torch::empty({B * tab.per, H, 64, 64}, state.options());
-  auto flat = [&](const torch::Tensor& t) { return t.view({B * T, H, 64}); };
   g_clampw_flags[0] = wkv7_chunk_forward(tab.sco, tab.cs, tab.ce, state, flat(r), flat(w), flat(k), flat(v), flat(a),
                                          flat(b), flat(y), 1.0, std::nullopt, std::nullopt, boundary, std::nullopt,
                                          std::nullopt, flat(sa), 1);
@@ -1308,15 +1427,21 @@ void clampw_backward(torch::Tensor& r, torch::Tensor& w, torch::Tensor& k, torch
   const char* names[] = {"w", "k", "v", "a", "b", "dy", "dr", "dw", "dk", "dv", "da", "db"};
   for (int i = 0; i < 12; ++i) clampw_check(r, *named[i], names[i]);
   clampw_check_saved(r, s, sa);
-  const int64_t B = r.size(0), T = r.size(1), H = r.size(2), G = T / 16;
+  const int64_t B = r.size(0), T = r.size(1), H = r.size(2), G = T / 16, D = head_size;
   const c10::cuda::CUDAGuard guard(r.device());
   const DenseTables tab = dense_tables(B, T, r);
-  auto s5 = s.view({B, H, G, 64, 64});
+  auto s5 = s.view({B, H, G, D, D});
   auto final_state = s5.select(2, G - 1).contiguous();
   // chunk c starts from the checkpoint after token 64 c, i.e. s[:, :, 4 c - 1]; chunk 0 from the zero state
-  auto boundary = torch::zeros({B, tab.per, H, 64, 64}, s.options());
+  auto boundary = torch::zeros({B, tab.per, H, D, D}, s.options());
   if (tab.per > 1) boundary.slice(1, 1).copy_(s5.slice(2, 3, 4 * (tab.per - 1), 4).permute({0, 2, 1, 3, 4}));
-  auto flat = [&](const torch::Tensor& t) { return t.view({B * T, H, 64}); };
+  auto flat = [&](const torch::Tensor& t) { return t.view({B * T, H, D}); };
+  if (D != 64) {
+    wkv7_train_wide_backward(tab.sco, tab.cs, tab.ce, final_state, boundary.view({B * tab.per, H, D, D}), flat(sa),
+                             flat(r), flat(w), flat(k), flat(v), flat(a), flat(b), flat(dy), std::nullopt, 1.0,
+                             {flat(dr), flat(dw), flat(dk), flat(dv), flat(da), flat(db)});
+    return;
+  }
   auto g = wkv7_backward_chunked(tab.sco, tab.cs, tab.ce, final_state, boundary.view({B * tab.per, H, 64, 64}), flat(sa),
                                  flat(r), flat(w), flat(k), flat(v), flat(a), flat(b), flat(dy), std::nullopt, 1.0,
                                  {flat(dr), flat(dw), flat(dk), flat(dv), flat(da), flat(db)});
@@ -1720,6 +1845,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("b"), py::arg("grad_output") = py::none(), py::arg("grad_final_state") = py::none(),
         py::arg("scale") = 1.0, py::arg("into") = std::vector<torch::Tensor>{});
   m.def("rwkv7_clampw_v3_error_flags", &clampw_error_flags);
+  m.def("wkv7_train_wide_forward", &wkv7_train_wide_forward, py::arg("sequence_chunk_offsets"),
+        py::arg("chunk_token_starts"), py::arg("chunk_token_ends"), py::arg("state"), py::arg("r"),
+        py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"), py::arg("output"),
+        py::arg("boundary") = py::none(), py::arg("state_dot_a") = py::none(), py::arg("scale") = 1.0,
+        py::arg("dense_checkpoints") = py::none());
+  m.def("wkv7_train_wide_backward", &wkv7_train_wide_backward, py::arg("sequence_chunk_offsets"),
+        py::arg("chunk_token_starts"), py::arg("chunk_token_ends"), py::arg("final_state"), py::arg("boundary"),
+        py::arg("state_dot_a"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),
+        py::arg("b"), py::arg("grad_output") = py::none(), py::arg("grad_final_state") = py::none(),
+        py::arg("scale") = 1.0, py::arg("into") = std::vector<torch::Tensor>{});
   m.def("wkv7_chunk_replay", &wkv7_chunk_replay, py::arg("chunk_token_starts"), py::arg("chunk_token_ends"),
         py::arg("boundary"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),
         py::arg("b"), py::arg("decay_bias") = py::none());

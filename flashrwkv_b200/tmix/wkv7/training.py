@@ -39,8 +39,13 @@ def check_device_error_flags() -> None:
 
 def _forward_all(state, sco, cs, ce, r, w, k, v, a, b, scale):
     output = torch.empty_like(v)
-    boundary = torch.empty((cs.numel(), r.shape[1], 64, 64), device=r.device, dtype=torch.float32)
+    D = r.shape[2]
+    boundary = torch.empty((cs.numel(), r.shape[1], D, D), device=r.device, dtype=torch.float32)
     state_dot_a = torch.empty(r.shape, device=r.device, dtype=torch.float32)
+    if D != 64:  # head sizes 128 / 256: the plain-recurrence kernels (no tensor-core waits, hence no flag)
+        extension().wkv7_train_wide_forward(sco, cs, ce, state, r, w, k, v, a, b, output, boundary, state_dot_a,
+                                            float(scale))
+        return output, boundary, state_dot_a, torch.zeros(1, dtype=torch.int32, device=r.device)
     flag = extension().wkv7_chunk_forward(sco, cs, ce, state, r, w, k, v, a, b, output, float(scale), None, None,
                                           boundary, None, None, state_dot_a, 1)
     _last_flags["forward"] = flag
@@ -48,6 +53,10 @@ def _forward_all(state, sco, cs, ce, r, w, k, v, a, b, scale):
 
 
 def _backward_all(sco, cs, ce, final_state, boundary, state_dot_a, r, w, k, v, a, b, go, gf, scale):
+    if r.shape[2] != 64:
+        grads = extension().wkv7_train_wide_backward(sco, cs, ce, final_state, boundary, state_dot_a, r, w, k, v, a, b,
+                                                     go, gf, float(scale))
+        return grads, None
     *grads, flag = extension().wkv7_backward_chunked(sco, cs, ce, final_state, boundary, state_dot_a, r, w, k, v, a, b,
                                                      go, gf, float(scale))
     _last_flags["backward"] = flag
@@ -76,6 +85,30 @@ class _StateTune(torch.autograd.Function):
         return dS0, None, None, None, dr, dw, dk, dv, da, db, None
 
 
+def _validate_chunk_tables(sco, cs, ce, total_tokens: int) -> None:
+    """One device-to-host read for every property the kernels rely on: chunk bounds inside [0, N], at most MAX_CHUNK
+    tokens per chunk, chunks of a sequence contiguous and in order, offsets monotone from 0 to the chunk count.  A
+    table that fails would drive out-of-range reads and writes on the device, so it is refused here."""
+    cn = cs.numel()
+    lens = ce - cs
+    starts = torch.zeros(cn + 1, dtype=torch.bool, device=cs.device)
+    starts[sco.clamp(0, cn).long()] = True
+    code = ((lens > MAX_CHUNK).any().int() | (lens < 0).any().int() * 2 | (cs < 0).any().int() * 4
+            | (ce > total_tokens).any().int() * 8 | (sco[0] != 0).int() * 16 | (sco[-1] != cn).int() * 32
+            | (sco[1:] < sco[:-1]).any().int() * 64)
+    if cn > 1:
+        code = code | ((cs[1:] != ce[:-1]) & ~starts[1:cn]).any().int() * 128
+    code = int(code.item())
+    if code & 1:
+        raise ValueError(f"training chunks may hold at most {MAX_CHUNK} tokens")
+    if code & (2 | 4 | 8):
+        raise ValueError("chunk token bounds must satisfy 0 <= start <= end <= total_tokens")
+    if code & (16 | 32 | 64):
+        raise ValueError("sequence_chunk_offsets must rise from 0 to the number of chunks")
+    if code & 128:
+        raise ValueError("the chunks of a sequence must be contiguous and in token order")
+
+
 def _check_cuda_contiguous(tensor, name):
     if not isinstance(tensor, torch.Tensor):
         raise TypeError(f"{name} must be a torch.Tensor")
@@ -96,8 +129,6 @@ def statetune_recurrent_fp32io16(initial_state, sequence_chunk_offsets, chunk_to
         raise ValueError("state must have shape [B,H,D,D]")
     if initial_state.shape[2] != initial_state.shape[3] or initial_state.shape[2] not in (64, 128, 256):
         raise ValueError("state head size must be 64, 128, or 256")
-    if initial_state.shape[2] != 64:
-        raise ValueError("this build implements head size 64 only")
     for name, tensor in (("r", r), ("decay_logits", decay_logits), ("k", k), ("v", v), ("a", a), ("b", b)):
         _check_cuda_contiguous(tensor, name)
         if tensor.device != initial_state.device:
@@ -125,8 +156,7 @@ def statetune_recurrent_fp32io16(initial_state, sequence_chunk_offsets, chunk_to
         raise ValueError("sequence_chunk_offsets must have shape [B+1]")
     if not isinstance(scale, (int, float)) or not math.isfinite(float(scale)):
         raise ValueError("scale must be finite")
-    if int((chunk_token_ends - chunk_token_starts).max().item()) > MAX_CHUNK:
-        raise ValueError(f"training chunks may hold at most {MAX_CHUNK} tokens")
+    _validate_chunk_tables(sequence_chunk_offsets, chunk_token_starts, chunk_token_ends, r.shape[0])
     return _StateTune.apply(initial_state, sequence_chunk_offsets, chunk_token_starts, chunk_token_ends, r,
                             decay_logits, k, v, a, b, float(scale))
 
@@ -152,7 +182,7 @@ class _PretrainRecurrent(torch.autograd.Function):
         heads = channels // head_size
         tables = _dense_chunk_tables(batch, tokens, r.device)
         packed = [t.detach().view(batch * tokens, heads, head_size) for t in (r, w, k, v, a, b)]
-        state = torch.zeros((batch, heads, head_size, head_size), device=r.device, dtype=torch.float32)
+        state = torch.zeros((batch, heads, head_size, head_size), device=r.device, dtype=torch.float32)  # S0 = 0
         output, boundary, state_dot_a, flag = _forward_all(state, *tables, *packed, 1.0)
         ctx.save_for_backward(*tables, state, boundary, state_dot_a, *packed, flag)
         ctx.shape = r.shape
@@ -194,8 +224,6 @@ def pretrain_recurrent_bf16(r, w, k, v, a, b, *, head_size: int = 64):
         raise ValueError("C must be divisible by head_size")
     if r.shape[1] % CHUNK_LEN != 0:
         raise ValueError("T must be divisible by the canonical chunk length 16")
-    if head_size != 64:
-        raise ValueError("this build implements head size 64 only")
     return _PretrainRecurrent.apply(r, w, k, v, a, b, head_size)
 
 

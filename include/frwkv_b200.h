@@ -277,6 +277,36 @@ int frwkv_wkv7_backward(const int32_t* seq_chunk_offsets, const int32_t* chunk_s
                         float scale, frwkv_stream_t stream);
 
 /*
+ * WKV7 training at head sizes 128 and 256 (the plain recurrence; head size 64 has the chunked tensor-core entries
+ * above).  Chunk tables as in frwkv_wkv7_chunk_fp32io16_forward, chunks of at most 64 tokens; tensors [N,H,D] 16-bit,
+ * states [B,H,D,D] fp32 (key row, value column).
+ *   forward: `state` holds the initial states and receives the final ones; y io16 [N,H,D]; boundary fp32
+ *     [Cn,H,D,D] (state at the start of every chunk, may be NULL); state_dot_a fp32 [N,H,D] (may be NULL);
+ *     dense_checkpoints fp32 [B,H,dense_groups,D,D] or NULL: the state after every 16 tokens of each sequence
+ *     (dense_groups = tokens per sequence / 16), the `s` tensor of the reference's dense pretraining operator.
+ *   backward: gradients of r, decay logits (raw), k, v, a, b (io16 [N,H,D], each may be NULL) and of the initial
+ *     state (fp32 [B,H,D,D], may be NULL) from the forward's final_state, boundary and state_dot_a; grad_output
+ *     io16 [N,H,D] (NULL = zero), grad_final_state fp32 [B,H,D,D] (NULL = zero); workspace of
+ *     frwkv_wkv7_train_wide_workspace_floats(...) floats (16-token checkpoints and per-column-block partial sums).
+ * Replace forward_kernel_split64 / backward_kernel_split64 / the tiled D = 256 backward
+ * (csrc/sm90/tmix/wkv7/pretrain_recurrent_bf16_forward.cu:110-150,293-478) and the D = 128 / 256 instantiations of
+ * the StateTune kernels (csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_backward.cu:317-502).
+ */
+int frwkv_wkv7_train_wide_forward(const int32_t* seq_chunk_offsets, const int32_t* chunk_starts,
+                                  const int32_t* chunk_ends, float* state, const void* r, const void* decay_logits,
+                                  const void* k, const void* v, const void* a, const void* b, void* y, float* boundary,
+                                  float* state_dot_a, float* dense_checkpoints, int dense_groups, int num_sequences,
+                                  int num_heads, int head_size, int io_dtype, float scale, frwkv_stream_t stream);
+size_t frwkv_wkv7_train_wide_workspace_floats(long long total_tokens, int num_chunks, int num_heads, int head_size);
+int frwkv_wkv7_train_wide_backward(
+    const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends, const float* final_state,
+    const float* boundary, const float* state_dot_a, const void* r, const void* decay_logits, const void* k,
+    const void* v, const void* a, const void* b, const void* grad_output, const float* grad_final_state, void* grad_r,
+    void* grad_decay_logits, void* grad_k, void* grad_v, void* grad_a, void* grad_b, float* grad_initial_state,
+    float* workspace, long long total_tokens, int num_sequences, int num_chunks, int num_heads, int head_size,
+    int io_dtype, float scale, frwkv_stream_t stream);
+
+/*
  * TMix token shift: out[j] = x + (prev - x) * mix_j for the six mix vectors (r, w, k, v, a, g); prev is the previous
  * packed row, or shift_state_pool[state_indices[s]] at the first row of sequence s; afterwards that slot holds the
  * sequence's last row.  Replaces tmix_mix6_forward_varlen_cuda (csrc/sm120/tmix/mix6/infer_fp16_forward_varlen.cu:190-303).

@@ -162,6 +162,43 @@ def test_pretrain_through_reference_autograd_and_op_library(ref, oracle):
             assert max_abs(s[bi, :, c].cpu(), after) <= 3e-4
 
 
+@pytest.mark.parametrize("head_size", [128, 256])
+def test_wide_head_training_through_reference_wrappers(ref, head_size):
+    """Head sizes 128 / 256: the reference's pretrain and StateTune autograd wrappers over this module give the
+    bits of this package's own wrappers (which tests/test_training_gpu.py checks against the oracle)."""
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+    from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata
+
+    B, T, H, D = 1, 48, 1, head_size
+    gen = torch.Generator().manual_seed(D)
+    base = [(torch.randn(B, T, H * D, generator=gen) * sc).to(torch.bfloat16).cuda()
+            for sc in (0.12, 2.0, 0.1, 0.1, 0.1, 0.1)]
+    dy = torch.randn(B, T, H * D, generator=gen).to(torch.bfloat16).cuda()
+    grads = []
+    for impl in (ref, F):
+        vals = [t.clone().requires_grad_() for t in base]
+        y = impl.pretrain_recurrent_bf16(*vals, head_size=D)
+        y.backward(dy)
+        grads.append([y.detach()] + [v.grad for v in vals])
+    for a, b in zip(*grads):
+        assert torch.isfinite(a).all() and torch.equal(a, b)
+    lengths = (20, 33)
+    cu = torch.tensor([0, 20, 53], dtype=torch.int32, device="cuda")
+    meta = make_chunk_metadata(cu, 32)
+    toks = [t.cuda() for t in synthetic.wkv7_inputs(sum(lengths), H, D, seed=D)]
+    S0 = synthetic.state_pool(2, H, D, seed=2, device="cuda")
+    outs = []
+    for impl in (ref, F):
+        s0 = S0.clone().requires_grad_()
+        leaves = [t.clone().requires_grad_() for t in toks]
+        res = impl.statetune_recurrent_fp32io16(s0, *meta, *leaves, scale=0.9)
+        (res[0].float().sum() + res[1].sum()).backward()
+        outs.append([r.detach() for r in res] + [s0.grad] + [t.grad for t in leaves])
+    for a, b in zip(*outs):
+        assert torch.isfinite(a).all() and torch.equal(a, b)
+
+
 def test_projections_through_reference_wrappers_both_layouts(ref):
     gen = torch.Generator().manual_seed(11)
     M, C, R = 9, 256, 64

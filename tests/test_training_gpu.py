@@ -150,3 +150,110 @@ def test_dense_op_library_checkpoints_and_gradients(oracle):
             assert torch.isfinite(got).all()
             assert rel_rmse(got[bi].float().cpu(), back[name]) <= 1.5e-2, name
     assert all(int(f.item()) == 0 for f in native.rwkv7_clampw_v3_error_flags())
+
+
+@pytest.mark.parametrize("head_size", [128, 256])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_wide_head_statetune_vs_oracle(oracle, head_size, dtype):
+    """Head sizes 128 and 256: outputs, saved tensors and all seven gradients against the oracle's float64 forward
+    and backward; ragged chunks (a 16-token multiple, a tail of 1, chunks that need one, two and three checkpoints),
+    non-zero initial state, upstream gradients on the output and on the final state."""
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+    from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata
+
+    lengths = (81, 1, 48)
+    H, D, B, N = 2, head_size, len(lengths), sum(lengths)
+    toks = [t.to(dtype) for t in synthetic.wkv7_inputs(N, H, D, seed=41 + D, dtype=torch.float32)]
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32)
+    S0 = synthetic.state_pool(B, H, D, seed=6)
+    gen = torch.Generator().manual_seed(9)
+    dy = torch.randn(N, H, D, generator=gen).to(dtype)
+    dSf = torch.randn(B, H, D, D, generator=gen) * 0.1
+    meta = make_chunk_metadata(cu.cuda(), 64)
+    fwd = oracle.forward(*toks, state_pool=S0, cu_seqlens=cu, scale=0.8, chunks=tuple(m.cpu() for m in meta),
+                         want_state_dot_a=True)
+    want = oracle.backward(*toks, initial_state=S0, cu_seqlens=cu, grad_output=dy, grad_final_state=dSf, scale=0.8)
+    dS0 = S0.cuda().requires_grad_()
+    dtoks = [t.cuda().requires_grad_() for t in toks]
+    out = F.statetune_recurrent_fp32io16(dS0, *meta, *dtoks, scale=0.8)
+    tol = 8e-3 if dtype == torch.bfloat16 else 2e-3
+    assert rel_rmse(out[0].detach().float().cpu(), fwd["y"]) <= tol
+    assert rel_rmse(out[1].detach().cpu(), fwd["state_pool"]) <= 1e-4
+    assert rel_rmse(out[2].detach().cpu(), fwd["boundary"]) <= 1e-4
+    assert rel_rmse(out[3].detach().cpu(), fwd["state_dot_a"]) <= 1e-4
+    torch.autograd.backward([out[0], out[1]], [dy.cuda(), dSf.cuda()])
+    for t, name in zip(dtoks, ("r", "decay_logits", "k", "v", "a", "b")):
+        assert torch.isfinite(t.grad).all()
+        assert rel_rmse(t.grad.float().cpu(), want[name]) <= tol, name
+    assert rel_rmse(dS0.grad.cpu(), want["initial_state"]) <= 1e-3
+    # bit-identical on a second run (fixed-order sums over the column blocks)
+    dtoks2 = [t.detach().clone().requires_grad_() for t in dtoks]
+    dS02 = S0.cuda().requires_grad_()
+    out2 = F.statetune_recurrent_fp32io16(dS02, *meta, *dtoks2, scale=0.8)
+    torch.autograd.backward([out2[0], out2[1]], [dy.cuda(), dSf.cuda()])
+    for t, t2 in zip(dtoks, dtoks2):
+        assert torch.equal(t.grad, t2.grad)
+
+
+@pytest.mark.parametrize("head_size", [128, 256])
+def test_wide_head_pretrain_and_op_library(oracle, head_size):
+    """The dense pretraining operator at head sizes 128 / 256 through this package's wrapper and through
+    torch.ops.rwkv7_clampw_v3 (16-token checkpoints, sa, gradients written into the caller's tensors)."""
+    import flashrwkv_b200 as F
+
+    B, T, H, D = 2, 80, 1, head_size
+    gen = torch.Generator().manual_seed(20260806 + D)
+    vals = [(torch.randn(B, T, H * D, generator=gen) * sc).to(torch.bfloat16).cuda().requires_grad_()
+            for sc in (0.12, 2.0, 0.1, 0.1, 0.1, 0.1)]
+    dy = (torch.randn(B, T, H * D, generator=gen) * 0.5).to(torch.bfloat16).cuda()
+    y = F.pretrain_recurrent_bf16(*vals, head_size=D)
+    y.backward(dy)
+    four = [v.detach().view(B, T, H, D) for v in vals]
+    out = torch.empty_like(four[3])
+    s = torch.full((B, H, T // 16, D, D), float("nan"), device="cuda")
+    sa = torch.full((B, T, H, D), float("nan"), device="cuda")
+    torch.ops.rwkv7_clampw_v3.forward(*four, out, s, sa, D)
+    grads = [torch.full_like(four[0], float("nan")) for _ in range(6)]
+    torch.ops.rwkv7_clampw_v3.backward(*four, dy.view(B, T, H, D), s, sa, *grads, D)
+    assert torch.equal(out.view(B, T, H * D), y.detach())
+    G = T // 16
+    cs = torch.arange(G, dtype=torch.int32) * 16
+    cu = torch.tensor([0, T], dtype=torch.int32)
+    for bi in range(B):
+        packed = [t[bi].float().cpu() for t in four]
+        want = oracle.forward(*packed, state_pool=torch.zeros(1, H, D, D), cu_seqlens=cu,
+                              chunks=(torch.tensor([0, G], dtype=torch.int32), cs, cs + 16), want_state_dot_a=True)
+        assert rel_rmse(out[bi].float().cpu(), want["y"]) <= 8e-3
+        assert rel_rmse(sa[bi].cpu(), want["state_dot_a"]) <= 1e-4
+        for c in range(G):
+            after = want["boundary"][c + 1] if c + 1 < G else want["state_pool"][0]
+            assert rel_rmse(s[bi, :, c].cpu(), after) <= 1e-4, (bi, c)
+        back = oracle.backward(*packed, initial_state=torch.zeros(1, H, D, D), cu_seqlens=cu,
+                               grad_output=dy.view(B, T, H, D)[bi].float().cpu())
+        for got, v, name in zip(grads, vals, ("r", "decay_logits", "k", "v", "a", "b")):
+            assert rel_rmse(got[bi].float().cpu(), back[name]) <= 8e-3, name
+            assert torch.equal(got.view(B, T, H * D), v.grad), name
+
+
+def test_chunk_tables_are_validated_before_any_launch():
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+
+    H, D, N = 1, 64, 40
+    toks = [t.cuda() for t in synthetic.wkv7_inputs(N, H, D, seed=3)]
+    S0 = torch.zeros(2, H, D, D, device="cuda")
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")  # noqa: E731
+    good = (i32([0, 1, 2]), i32([0, 30]), i32([30, 40]))
+    F.statetune_recurrent_fp32io16(S0, *good, *toks)
+    bad = {
+        "at most 64": (i32([0, 1, 2]), i32([0, 0]), i32([0, 70])),
+        "0 <= start <= end <= total_tokens": (i32([0, 1, 2]), i32([0, 30]), i32([30, 41])),
+        "0 <= start <= end": (i32([0, 1, 2]), i32([5, 30]), i32([3, 40])),
+        "rise from 0": (i32([0, 2, 1]), i32([0, 30]), i32([30, 40])),
+        "number of chunks": (i32([0, 1, 3]), i32([0, 30]), i32([30, 40])),
+        "contiguous": (i32([0, 2, 2]), i32([0, 31]), i32([30, 40])),
+    }
+    for match, tables in bad.items():
+        with pytest.raises(ValueError, match=match):
+            F.statetune_recurrent_fp32io16(S0, *tables, *toks)
