@@ -266,6 +266,7 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
     // pull the next item's rows into L2
     if (item + (int)gridDim.x < num_items) {
       const int nit = item + gridDim.x, nch = nit / num_heads, nhd = nit % num_heads;
+      const int num_chunks_total = num_items / num_heads;
       const int nt0 = chunk_starts[nch], nlen = chunk_ends[nch] - nt0;
       for (int e = tid; e < 8 * kL; e += kBwdThreads) {
         const int which = e >> 6, rowi = e & 63;
@@ -280,6 +281,16 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
             asm volatile("prefetch.global.L2 [%0];" ::"l"(sda_ptr + at + 32));
           }
         }
+      }
+      // ... and its three 16 KB state tiles (chunk-start state, chunk-end adjoint; the chunk-end state is the next
+      // boundary or the final state, found by the same search the item does): 128 lines of 128 bytes each
+      if (tid < 384) {
+        const int which = tid >> 7, line = tid & 127;
+        const float* base = nullptr;
+        if (which == 0) base = boundary + ((long long)nch * num_heads + nhd) * (kD * kD);
+        if (which == 1) base = adjoint + ((long long)nch * num_heads + nhd) * (kD * kD);
+        if (which == 2 && nch + 1 < num_chunks_total) base = boundary + ((long long)(nch + 1) * num_heads + nhd) * (kD * kD);
+        if (base != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + 32 * line));
       }
     }
     umma::tmem_st_wait();
@@ -347,6 +358,14 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
                           umma::desc_k_major(sbase + kOffTG + ks * 2 * kCS64, kCS64), idesc64, 1u);
       umma::mma_commit(&mbar[1]);
     }
+    // this thread's 16 channels of its U row (fp32, four pieces) or V row (16-bit, two pieces): requested now, used
+    // after the inverse
+    uint4 uvraw[4];
+    {
+      const uint4* up = low ? reinterpret_cast<const uint4*>(sda_ptr + row) : reinterpret_cast<const uint4*>(v_ptr + row);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) uvraw[i] = (valid && (low || i < 2)) ? __ldg(up + i) : zero4;
+    }
     inverse_blocked<kOffRB, kOffRA, kCS128, true>(smem, tid);  // T'^T, rows 64..127 of the tile zero
     __syncthreads();
     ok = wait_warp(&mbar[1], parity, ok);
@@ -371,20 +390,18 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
                           umma::desc_k_major(sbase + kOffTDY + ks * 2 * kCS64, kCS64), idesc64, 1u);
       umma::mma_commit(&mbar[2]);
     }
-    // meanwhile: this thread's 16 channels of its U row (fp32) or V row
+    // meanwhile: this thread's 16 channels of its U row or V row, rounded as operands
     float uv[16];
     {
       if (low) {
-        const float4* up = reinterpret_cast<const float4*>(sda_ptr + row);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float4 x = valid ? __ldg(up + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-          uv[4 * i] = x.x; uv[4 * i + 1] = x.y; uv[4 * i + 2] = x.z; uv[4 * i + 3] = x.w;
+          uv[4 * i] = __uint_as_float(uvraw[i].x); uv[4 * i + 1] = __uint_as_float(uvraw[i].y);
+          uv[4 * i + 2] = __uint_as_float(uvraw[i].z); uv[4 * i + 3] = __uint_as_float(uvraw[i].w);
         }
       } else {
-        const uint4* vp = reinterpret_cast<const uint4*>(v_ptr + row);
-        unpack8<io_t>(valid ? __ldg(vp) : zero4, *reinterpret_cast<float(*)[8]>(&uv[0]));
-        unpack8<io_t>(valid ? __ldg(vp + 1) : zero4, *reinterpret_cast<float(*)[8]>(&uv[8]));
+        unpack8<io_t>(uvraw[0], *reinterpret_cast<float(*)[8]>(&uv[0]));
+        unpack8<io_t>(uvraw[1], *reinterpret_cast<float(*)[8]>(&uv[8]));
       }
 #pragma unroll
       for (int e = 0; e < 16; ++e) uv[e] = umma::to_tf32(uv[e]);
