@@ -349,6 +349,9 @@ def _extras(dev):
               for _ in range(n_layers)]
     mixes = [vec() for _ in range(6)]
     k_k, a0, k_a, r_k, lnw, lnb, v0 = (vec() for _ in range(7))
+    for L in layers:
+        L["packed"] = F.TMixLayerWeights(*mixes, L["Wr"], L["Wk"], L["Wv"], L["Wo"], L["w1"], L["w2"], k_k, a0, k_a, r_k,
+                                         lnw, lnb, v0)
     weight_bytes = 2 * (4 * C * C + 2 * C * sum(ranks.values()))
     tmix = {}
     for M in (1, 4, 7, 512):
@@ -385,9 +388,17 @@ def _extras(dev):
             z = F.infer_tmix_lnx_rkvres_xg_forward_varlen(y.view(M, C), r_, kk_, vres, r_k, lnw, lnb, g_)
             return F.infer_tmix_linear_forward_varlen(z, L["Wo"])
 
+        def one_launch(L):  # the whole layer as one persistent kernel (decode batches of at most 8 rows)
+            return F.infer_tmix_decode_layer_forward_varlen(x, v_first, L["packed"], shift_state_pool=shift,
+                                                            state_pool=spool, cu_seqlens=cu, state_indices=idx,
+                                                            validated_metadata=ticket)
+
         def stack(fused=False):
             for L in layers:
-                layer(L, fused)
+                if fused == "one_launch":
+                    one_launch(L)
+                else:
+                    layer(L, fused)
 
         sec = _time_cuda(stack, warmup=3, iters=10) / n_layers
         # the same launches replayed from a CUDA graph: device time without the per-call host work
@@ -397,7 +408,7 @@ def _extras(dev):
         with torch.cuda.stream(side):
             gticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=M, state_pool_size=M, max_seqlen=1)
             ticket = gticket
-            for fused in (False, True):
+            for fused in (False, True) + (("one_launch",) if M <= 8 else ()):
                 stack(fused)
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=side):
@@ -413,6 +424,9 @@ def _extras(dev):
         if M <= 7:
             entry["weight_hbm_frac_cuda_graph"] = weight_bytes / gsec / hbm
             entry["weight_hbm_frac_fused_shift_cuda_graph"] = weight_bytes / gsecs[True] / hbm
+            entry["us_per_layer_one_launch_cuda_graph"] = gsecs["one_launch"] * 1e6
+            entry["gpu_launches_per_layer_one_launch"] = 1
+            entry["weight_hbm_frac_one_launch_cuda_graph"] = weight_bytes / gsecs["one_launch"] / hbm
         else:
             entry["tensor_frac_of_bf16_peak_cuda_graph"] = 2 * M * (4 * C * C + 2 * C * sum(ranks.values())) / gsec / bf16
         tmix[f"M={M}"] = entry
@@ -745,7 +759,27 @@ def _profile_case(name: str) -> None:
             torch.autograd.backward(outs, go[:len(outs)])
             torch.autograd.backward(F.pretrain_tmix_mix6_bf16(x, *vecs), go)
 
-    cases = {"chunk": case_chunk, "chunk2k": lambda: case_chunk(3, 2, 4096, 32, 0), "train": case_train,
+    def case_layer(reps: int = 3, M: int = 4):
+        C = 2048
+        g = torch.Generator().manual_seed(3)
+        wt = lambda n, k: (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).cuda()  # noqa: E731
+        vec = lambda: torch.rand(C, generator=g).to(torch.bfloat16).cuda()  # noqa: E731
+        ranks = {"w": 96, "a": 96, "g": 256, "v": 64}
+        layers = [F.TMixLayerWeights(vec(), vec(), vec(), vec(), vec(), vec(), wt(C, C), wt(C, C), wt(C, C), wt(C, C),
+                                     {n: wt(r, C) for n, r in ranks.items()}, {n: wt(C, r) for n, r in ranks.items()},
+                                     vec(), vec(), vec(), vec(), vec(), vec(), vec()) for _ in range(4)]
+        x = torch.randn(M, C, generator=g).to(torch.bfloat16).cuda()
+        v_first = torch.randn(M, C, generator=g).to(torch.bfloat16).cuda()
+        shift = torch.zeros(M, C, dtype=torch.bfloat16, device="cuda")
+        pool = synthetic.state_pool(M, C // D, D, seed=5, device="cuda")
+        cu, idx = synthetic.equal_length_metadata(M, 1, device="cuda")
+        ticket = F.prepare_recurrent_metadata(cu, idx, total_tokens=M, state_pool_size=M, max_seqlen=1)
+        for _ in range(reps):
+            for L in layers:  # four layers' weights in turn (151 MB): every launch streams its weights from HBM
+                F.infer_tmix_decode_layer_forward_varlen(x, v_first, L, shift_state_pool=shift, state_pool=pool,
+                                                         cu_seqlens=cu, state_indices=idx, validated_metadata=ticket)
+
+    cases = {"layer": case_layer, "layer1": lambda: case_layer(3, 1), "chunk": case_chunk, "chunk2k": lambda: case_chunk(3, 2, 4096, 32, 0), "train": case_train,
              "train512": lambda: case_train(2, 8, 512, 64), "tmix": case_tmix, "decode": case_decode,
              "decode16": case_decode16, "glue": case_glue}
     if name not in cases:

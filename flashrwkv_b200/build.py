@@ -33,7 +33,7 @@ CUDA_SOURCES = [
     "wkv7_recurrent_wide.cu",
     "wkv7_chunk_fwd.cu",
     "wkv7_chunk_fused.cu",
-    "wkv7_chunk_bwd.cu", "wkv7_checkpoints.cu", "wkv7_train_wide.cu",
+    "wkv7_chunk_bwd.cu", "wkv7_checkpoints.cu", "wkv7_train_wide.cu", "tmix_decode_layer.cu",
     "tmix_elementwise.cu",
     "tmix_norm.cu",
     "tmix_train.cu",

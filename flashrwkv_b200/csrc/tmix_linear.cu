@@ -23,150 +23,6 @@
 namespace frwkv {
 namespace {
 
-// ---- skinny kernel --------------------------------------------------------------------------------------
-// grid = (column blocks, problems); dynamic shared memory = M * K fp32 values of x (activation applied): unpacking the
-// 16-bit x once per CTA instead of once per weight row is what keeps M = 4..8 bound by the weight stream rather than
-// by instruction issue.  Long rows (K >= 256): a warp owns two output columns at a time (sixteen 16-byte weight
-// loads in flight per lane, every x value used twice) and reduces with shuffles.  Short rows (rank-out,
-// K = rank): eight lanes share a column.
-// Output columns a warp works on at a time (long rows) and 16-byte weight pieces per column and lane in flight at once.
-// Two columns keep 128 CTAs busy on a 2048-wide projection; four columns halve the shared-memory reads of x but leave
-// 64 CTAs to pull the weights, and the layer took twice as long (measured): the kernel lives on SMs pulling in parallel.
-constexpr int kSkinnyCols = 2;
-constexpr int kSkinnyDepth = 8;
-
-// The first block of weight pieces of a warp's first column group.  Weights are constants, so a kernel fetches them
-// before it waits for its predecessors in the stream and before it stages x: the DRAM round trip of the weight
-// stream then overlaps the tail of the previous kernel and the staging.
-struct SkinnyPrefetch {
-  uint4 q[kSkinnyCols][kSkinnyDepth];
-};
-template <typename io_t>
-__device__ __forceinline__ void skinny_prefetch(const void* weight, int N, int K, SkinnyPrefetch& pf) {
-  if (K < 256) return;
-  const int lane = threadIdx.x & 31, kv = K >> 3;
-  const int n = kSkinnyCols * (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
-  if (n >= N) return;
-  const io_t* w = static_cast<const io_t*>(weight);
-#pragma unroll
-  for (int col = 0; col < kSkinnyCols; ++col) {
-    const uint4* wrow = reinterpret_cast<const uint4*>(w + (long long)(n + col) * K);
-#pragma unroll
-    for (int j = 0; j < kSkinnyDepth; ++j) {
-      const int c = lane + 32 * j;
-      if (c < kv) pf.q[col][j] = __ldg(wrow + c);
-    }
-  }
-}
-
-// the products of one CTA: xs / xs_hi hold x as fp32 (see linear_skinny_kernel)
-template <typename io_t, int M>
-__device__ __forceinline__ void skinny_products(const LinearProblem& pr, const float4* xs, const float4* xs_hi,
-                                                const SkinnyPrefetch& pf) {
-  using IO = Io16<io_t>;
-  const int K = pr.k, N = pr.n, kv = K >> 3;
-  const io_t* w = static_cast<const io_t*>(pr.w);
-  io_t* y = static_cast<io_t*>(pr.y);
-  if (K >= 256) {
-    const int lane = threadIdx.x & 31;
-    const int warps_total = gridDim.x * (blockDim.x >> 5);
-    // N is a multiple of 8, so a group of kSkinnyCols columns starting at a multiple of kSkinnyCols is always complete
-    const int n_first = kSkinnyCols * (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
-    for (int n = n_first; n < N; n += kSkinnyCols * warps_total) {
-      // accumulators as fp32 pairs (even | odd elements of a piece): one fma.rn.f32x2 per two multiply-adds
-      float2 acc[kSkinnyCols][M];
-#pragma unroll
-      for (int col = 0; col < kSkinnyCols; ++col) {
-#pragma unroll
-        for (int m = 0; m < M; ++m) acc[col][m] = make_float2(0.f, 0.f);
-      }
-      // all weight loads of a block (kSkinnyCols x kSkinnyDepth pieces per lane) are issued before the first one is used
-      for (int cb = lane; cb < kv; cb += 32 * kSkinnyDepth) {
-        uint4 q[kSkinnyCols][kSkinnyDepth];
-        const bool fetched = (n == n_first && cb == lane);  // this block came in with skinny_prefetch
-#pragma unroll
-        for (int col = 0; col < kSkinnyCols; ++col) {
-          const uint4* wrow = reinterpret_cast<const uint4*>(w + (long long)(n + col) * K);
-#pragma unroll
-          for (int j = 0; j < kSkinnyDepth; ++j) {
-            const int c = cb + 32 * j;
-            if (c < kv) q[col][j] = fetched ? pf.q[col][j] : __ldg(wrow + c);
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < kSkinnyDepth; ++j) {
-          const int c = cb + 32 * j;
-          if (c < kv) {
-            float2 wv[kSkinnyCols][4];
-#pragma unroll
-            for (int col = 0; col < kSkinnyCols; ++col) {
-              wv[col][0] = IO::unpack(q[col][j].x); wv[col][1] = IO::unpack(q[col][j].y);
-              wv[col][2] = IO::unpack(q[col][j].z); wv[col][3] = IO::unpack(q[col][j].w);
-            }
-#pragma unroll
-            for (int m = 0; m < M; ++m) {
-              const float4 xa = xs[m * kv + c], xb = xs_hi[m * kv + c];
-              const float2 x0 = make_float2(xa.x, xa.y), x1 = make_float2(xa.z, xa.w);
-              const float2 x2 = make_float2(xb.x, xb.y), x3 = make_float2(xb.z, xb.w);
-#pragma unroll
-              for (int col = 0; col < kSkinnyCols; ++col)
-                acc[col][m] = __ffma2_rn(wv[col][0], x0, __ffma2_rn(wv[col][1], x1,
-                                         __ffma2_rn(wv[col][2], x2, __ffma2_rn(wv[col][3], x3, acc[col][m]))));
-            }
-          }
-        }
-      }
-#pragma unroll
-      for (int m = 0; m < M; ++m) {
-        float t[kSkinnyCols];
-#pragma unroll
-        for (int col = 0; col < kSkinnyCols; ++col) {
-          t[col] = acc[col][m].x + acc[col][m].y;
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) t[col] += __shfl_xor_sync(0xffffffffu, t[col], o);
-        }
-        if (lane == 0) {
-#pragma unroll
-          for (int col = 0; col < kSkinnyCols; col += 2)
-            *reinterpret_cast<uint32_t*>(y + (long long)m * N + n + col) =
-                IO::pack(finish<io_t>(pr, t[col], m, n + col), finish<io_t>(pr, t[col + 1], m, n + col + 1));
-        }
-      }
-    }
-  } else {
-    // short rows (rank-out, K = rank): eight lanes share a column, a warp works on four columns at a time
-    const int lane = threadIdx.x & 31, sub = lane & 7, grp = lane >> 3;
-    const int warps_total = gridDim.x * (blockDim.x >> 5);
-    for (int n0 = 4 * (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)); n0 < N; n0 += 4 * warps_total) {
-      const int n = n0 + grp;  // N is a multiple of 8: all four columns exist
-      float2 acc[M];
-#pragma unroll
-      for (int m = 0; m < M; ++m) acc[m] = make_float2(0.f, 0.f);
-      const uint4* wrow = reinterpret_cast<const uint4*>(w + (long long)n * K);
-      for (int c = sub; c < kv; c += 8) {
-        const uint4 q = __ldg(wrow + c);
-        const float2 a0 = IO::unpack(q.x), a1 = IO::unpack(q.y), a2 = IO::unpack(q.z), a3 = IO::unpack(q.w);
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          const float4 xa = xs[m * kv + c], xb = xs_hi[m * kv + c];
-          acc[m] = __ffma2_rn(a0, make_float2(xa.x, xa.y),
-                              __ffma2_rn(a1, make_float2(xa.z, xa.w),
-                                         __ffma2_rn(a2, make_float2(xb.x, xb.y),
-                                                    __ffma2_rn(a3, make_float2(xb.z, xb.w), acc[m]))));
-        }
-      }
-#pragma unroll
-      for (int m = 0; m < M; ++m) {
-        float t = acc[m].x + acc[m].y;
-        t += __shfl_xor_sync(0xffffffffu, t, 1);
-        t += __shfl_xor_sync(0xffffffffu, t, 2);
-        t += __shfl_xor_sync(0xffffffffu, t, 4);
-        if (sub == 0) y[(long long)m * N + n] = IO::store(finish<io_t>(pr, t, m, n));
-      }
-    }
-  }
-}
-
 template <typename io_t, int M>
 __global__ __launch_bounds__(256) void linear_skinny_kernel(LinearGroup group) {
   using IO = Io16<io_t>;
@@ -174,7 +30,7 @@ __global__ __launch_bounds__(256) void linear_skinny_kernel(LinearGroup group) {
   const LinearProblem& pr = group.p[blockIdx.y];
   chain_release();
   SkinnyPrefetch pf;
-  skinny_prefetch<io_t>(pr.w, pr.n, pr.k, pf);
+  skinny_prefetch<io_t>(pr.w, pr.n, pr.k, pf, blockIdx.x, gridDim.x);
   chain_wait();
   const int kv = pr.k >> 3;
   // fp32 x as two planes of float4: plane 0 holds elements 8c..8c+3 of row m at [m*kv + c], plane 1 elements 8c+4..8c+7
@@ -192,7 +48,7 @@ __global__ __launch_bounds__(256) void linear_skinny_kernel(LinearGroup group) {
     xs_hi[i] = make_float4(f[4], f[5], f[6], f[7]);
   }
   __syncthreads();
-  skinny_products<io_t, M>(pr, xs, xs_hi, pf);
+  skinny_products<io_t, M>(pr, xs, xs_hi, pf, blockIdx.x, gridDim.x);
 }
 
 // ---- token shift fused into the projections (decode) -------------------------------------------------------------
@@ -224,7 +80,7 @@ __global__ __launch_bounds__(256) void shift_project_kernel(ShiftProjectGroup gr
   const ShiftProjection& sp = group.p[blockIdx.y];
   chain_release();
   SkinnyPrefetch pf;
-  skinny_prefetch<io_t>(sp.w, sp.n, C, pf);
+  skinny_prefetch<io_t>(sp.w, sp.n, C, pf, blockIdx.x, gridDim.x);
   chain_wait();
   const int kv = C >> 3;
   io_t* y = static_cast<io_t*>(sp.y);
@@ -267,7 +123,7 @@ __global__ __launch_bounds__(256) void shift_project_kernel(ShiftProjectGroup gr
   }
   __syncthreads();
   const LinearProblem pr{x, sp.w, sp.y, nullptr, nullptr, nullptr, sp.n, C, 0, 0};
-  skinny_products<io_t, M>(pr, xs, xs_hi, pf);
+  skinny_products<io_t, M>(pr, xs, xs_hi, pf, blockIdx.x, gridDim.x);
 }
 
 // ---- tensor-core kernel -----------------------------------------------------------------------------------

@@ -13,6 +13,8 @@
 
 #include <cmath>
 #include <limits>
+#include <map>
+#include <mutex>
 #include <memory>
 #include <optional>
 #include <string>
@@ -706,6 +708,103 @@ std::vector<torch::Tensor> tmix_shift_project_varlen(torch::Tensor x, torch::Ten
                                            static_cast<int>(idx.numel()), static_cast<int>(x.size(1)), io_dtype_of(x),
                                            current_stream(x)));
   return outs;
+}
+
+// One TMix layer of a decode batch in a single cooperative launch (csrc/tmix_decode_layer.cu).  Row m is sequence m.
+//   mixes = x_r, x_w, x_k, x_v, x_a, x_g [C];  big = Wr, Wk, Wv, Wo [C,C];  w1 / w2 = decay, a, gate, value-residual
+//   low-rank pairs ([R,C] / [C,R]);  vecs = k_k, a0, k_a, r_k, ln_w, ln_b, v0 [C].
+// Returns (out [M,C], device words: four barrier counters and the error flag at index 7).
+std::tuple<torch::Tensor, torch::Tensor> tmix_decode_layer(torch::Tensor x, torch::Tensor v_first,
+                                                           torch::Tensor shift_state_pool, torch::Tensor state_pool,
+                                                           std::vector<torch::Tensor> mixes,
+                                                           std::vector<torch::Tensor> big, std::vector<torch::Tensor> w1,
+                                                           std::vector<torch::Tensor> w2, std::vector<torch::Tensor> vecs,
+                                                           torch::Tensor cu, torch::Tensor idx, double eps,
+                                                           std::shared_ptr<MetadataTicket> ticket) {
+  check_io16(x, "x", x);
+  TORCH_CHECK(x.dim() == 2 && x.size(0) >= 1 && x.size(0) <= 8, "x must have packed shape [M,C] with 1 <= M <= 8");
+  const int64_t M = x.size(0), C = x.size(1);
+  TORCH_CHECK(C >= 256 && C % 64 == 0, "C must be a multiple of the head size 64, at least 256");
+  check_io16(v_first, "v_first", x);
+  TORCH_CHECK(v_first.sizes() == x.sizes(), "v_first must have x's shape");
+  check_io16(shift_state_pool, "shift_state_pool", x);
+  TORCH_CHECK(shift_state_pool.dim() == 2 && shift_state_pool.size(1) == C, "shift_state_pool must have shape [slots,C]");
+  check_cuda_contiguous(state_pool, "state_pool");
+  TORCH_CHECK(state_pool.scalar_type() == torch::kFloat32 && state_pool.device() == x.device() && state_pool.dim() == 4 &&
+                  state_pool.size(1) * 64 == C && state_pool.size(2) == 64 && state_pool.size(3) == 64,
+              "state_pool must be float32 [slots,C/64,64,64] on x's device");
+  TORCH_CHECK(mixes.size() == 6 && big.size() == 4 && w1.size() == 4 && w2.size() == 4 && vecs.size() == 7,
+              "expected 6 mix vectors, 4 square weights, 4 + 4 low-rank weights and 7 channel vectors");
+  check_cuda_contiguous(cu, "cu_seqlens");
+  check_cuda_contiguous(idx, "state_indices");
+  TORCH_CHECK(cu.scalar_type() == torch::kInt32 && idx.scalar_type() == torch::kInt32, "recurrent metadata must be int32");
+  TORCH_CHECK(cu.dim() == 1 && idx.dim() == 1 && idx.numel() == M && cu.numel() == M + 1,
+              "a decode batch has one token per sequence: cu_seqlens [M+1], state_indices [M]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  torch::Tensor launch_idx, status;
+  if (ticket) {
+    TORCH_CHECK(shift_state_pool.size(0) >= state_pool.size(0),
+                "with a prepared ticket the shift-state pool needs at least as many slots as the state pool");
+    ticket->check_compatible(cu, idx, M, state_pool.size(0), 1);
+    launch_idx = ticket->idx_snapshot();
+    status = ticket->status();
+  } else {
+    auto prepared = launch_validation(cu, idx, M, std::min(shift_state_pool.size(0), state_pool.size(0)));
+    launch_idx = std::move(prepared.idx);
+    status = std::move(prepared.status);
+  }
+  frwkv_tmix_decode_layer_args a{};
+  a.x = x.data_ptr();
+  a.v_first = v_first.data_ptr();
+  a.shift_state_pool = shift_state_pool.data_ptr();
+  a.state_pool = state_pool.data_ptr<float>();
+  for (int i = 0; i < 6; ++i) {
+    check_io16(mixes[i], "mix", x);
+    TORCH_CHECK(mixes[i].dim() == 1 && mixes[i].size(0) == C, "every mix vector must have shape [C]");
+    a.mix[i] = mixes[i].data_ptr();
+  }
+  for (int i = 0; i < 4; ++i) {
+    check_io16(big[i], "weight", x);
+    TORCH_CHECK(big[i].dim() == 2 && big[i].size(0) == C && big[i].size(1) == C, "Wr, Wk, Wv, Wo must have shape [C,C]");
+    check_io16(w1[i], "rank-in weight", x);
+    check_io16(w2[i], "rank-out weight", x);
+    TORCH_CHECK(w1[i].dim() == 2 && w1[i].size(1) == C && w1[i].size(0) % 8 == 0 && w1[i].size(0) >= 8 && w1[i].size(0) <= C,
+                "rank-in weights must have shape [R,C], R a multiple of 8");
+    TORCH_CHECK(w2[i].dim() == 2 && w2[i].size(0) == C && w2[i].size(1) == w1[i].size(0),
+                "rank-out weights must have shape [C,R]");
+    a.w1[i] = w1[i].data_ptr();
+    a.w2[i] = w2[i].data_ptr();
+    a.rank[i] = static_cast<int>(w1[i].size(0));
+  }
+  a.w_r = big[0].data_ptr(); a.w_k = big[1].data_ptr(); a.w_v = big[2].data_ptr(); a.w_o = big[3].data_ptr();
+  for (int i = 0; i < 7; ++i) {
+    check_io16(vecs[i], "channel vector", x);
+    TORCH_CHECK(vecs[i].dim() == 1 && vecs[i].size(0) == C, "k_k, a0, k_a, r_k, ln_w, ln_b, v0 must have shape [C]");
+  }
+  a.k_k = vecs[0].data_ptr(); a.a0 = vecs[1].data_ptr(); a.k_a = vecs[2].data_ptr(); a.r_k = vecs[3].data_ptr();
+  a.ln_w = vecs[4].data_ptr(); a.ln_b = vecs[5].data_ptr(); a.v0 = vecs[6].data_ptr();
+  auto out = torch::empty_like(x);
+  a.out = out.data_ptr();
+  auto workspace = torch::empty(
+      {static_cast<int64_t>(frwkv_tmix_decode_layer_workspace_bytes(static_cast<int>(M), static_cast<int>(C), a.rank))},
+      x.options().dtype(torch::kUInt8));
+  a.workspace = workspace.data_ptr();
+  // barrier counters and the error flag: one set per (device, stream), zeroed once; the kernel leaves the counters zero
+  static std::mutex words_mutex;
+  static std::map<std::pair<int, void*>, torch::Tensor> words_of;
+  torch::Tensor words;
+  {
+    const std::lock_guard<std::mutex> lock(words_mutex);
+    const auto key = std::make_pair(static_cast<int>(x.device().index()), static_cast<void*>(current_stream(x)));
+    auto it = words_of.find(key);
+    if (it == words_of.end()) it = words_of.emplace(key, torch::zeros({8}, x.options().dtype(torch::kInt32))).first;
+    words = it->second;
+  }
+  a.barrier = reinterpret_cast<uint32_t*>(words.data_ptr<int>());
+  check_rc(frwkv_tmix_decode_layer_forward(&a, launch_idx.data_ptr<int>(), status.data_ptr<int>(), static_cast<int>(M),
+                                           static_cast<int>(C), static_cast<int>(C / 64), static_cast<float>(eps),
+                                           io_dtype_of(x), words.data_ptr<int>() + 7, current_stream(x)));
+  return {out, words};
 }
 
 void check_rows_channels(const torch::Tensor& t, const char* name, const torch::Tensor& ref) {
@@ -1806,6 +1905,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("x_w"), py::arg("x_k"), py::arg("x_v"), py::arg("x_a"), py::arg("x_g"), py::arg("cu_seqlens"),
         py::arg("state_indices"), py::arg("max_seqlen") = -1, py::arg("eps") = 1e-5,
         py::arg("validated_metadata") = py::none());
+  m.def("tmix_decode_layer", &tmix_decode_layer, py::arg("x"), py::arg("v_first"), py::arg("shift_state_pool"),
+        py::arg("state_pool"), py::arg("mixes"), py::arg("square_weights"), py::arg("rank_in_weights"),
+        py::arg("rank_out_weights"), py::arg("channel_vectors"), py::arg("cu_seqlens"), py::arg("state_indices"),
+        py::arg("eps") = 64e-5, py::arg("validated_metadata") = py::none());
   m.def("tmix_shift_project_varlen", &tmix_shift_project_varlen, py::arg("x"), py::arg("shift_state_pool"),
         py::arg("mixes"), py::arg("weights"), py::arg("cu_seqlens"), py::arg("state_indices"),
         py::arg("max_seqlen") = -1, py::arg("validated_metadata") = py::none());

@@ -417,6 +417,49 @@ int frwkv_tmix_linear_grouped(const frwkv_linear_problem* problems, int count, i
 int frwkv_tmix_linear_runtime_layout(const frwkv_linear_problem* problem, int m, int io_dtype, int32_t* error_flag,
                                      frwkv_stream_t stream);
 
+/*
+ * One RWKV-7 TMix layer for a decode batch (one token per sequence; rows = sequences <= 8; head size 64) as one
+ * persistent, cooperatively launched kernel: token shift, r / k / v and the four rank-in projections, rank-out
+ * projections with the value-residual gate, kk_a_gate, the WKV7 step on state_pool, lnx_rkvres_xg and the output
+ * projection, separated by grid-wide barriers (bounded waits; on a time-out error_flag is set and out is NaN).
+ * Row m belongs to sequence m: its shift state is shift_state_pool[state_indices[m]] (updated to x[m]) and its WKV7
+ * state state_pool[state_indices[m]] (fp32 [slots,H,64,64], updated in place).  mix = x_r, x_w, x_k, x_v, x_a, x_g;
+ * w1 / w2 / rank = decay, a, gate, value-residual low-rank pairs ([R,C] and [C,R]); all weights in the original
+ * layout.  workspace: frwkv_tmix_decode_layer_workspace_bytes bytes for the 16-bit intermediates; barrier: four
+ * 32-bit words that are zero before the first launch (the kernel leaves them zero; launches that may overlap on
+ * the GPU need words of their own).  metadata_status may be NULL.
+ * No single counterpart in the reference: equals the operator sequence of csrc/sm120/tmix/{mix6,linear,kk_a_gate,
+ * wkv7,lnx_rkvres_xg} up to summation order.
+ */
+typedef struct {
+  const void* x;
+  const void* v_first;
+  void* shift_state_pool;
+  float* state_pool;
+  const void* mix[6];
+  const void* w_r;
+  const void* w_k;
+  const void* w_v;
+  const void* w_o;
+  const void* w1[4];
+  const void* w2[4];
+  int rank[4];
+  const void* k_k;
+  const void* a0;
+  const void* k_a;
+  const void* r_k;
+  const void* ln_w;
+  const void* ln_b;
+  const void* v0;
+  void* out;
+  void* workspace;
+  uint32_t* barrier;
+} frwkv_tmix_decode_layer_args;
+size_t frwkv_tmix_decode_layer_workspace_bytes(int rows, int channels, const int* rank);
+int frwkv_tmix_decode_layer_forward(const frwkv_tmix_decode_layer_args* args, const int32_t* state_indices,
+                                    const int32_t* metadata_status, int rows, int channels, int num_heads, float ln_eps,
+                                    int io_dtype, int32_t* error_flag, frwkv_stream_t stream);
+
 /* out = x + vec; x, out io16 [total_rows][channels], vec io16 [channels], channels even.  Replaces
  * recurrent_add_vec_forward_varlen_cuda (csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu:1247-1290). */
 int frwkv_recurrent_add_vec_forward(const void* x, const void* vec, void* out, long long total_rows, int channels,

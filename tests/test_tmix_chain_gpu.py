@@ -133,3 +133,74 @@ def test_layer_chain_matches_oracle_chain(oracle, D, M, packing, dtype):
         assert rel_rmse(out.float().cpu(), want_out) <= bar_out, (fused, rel_rmse(out.float().cpu(), want_out))
         assert rel_rmse(pool.cpu(), want_pool) <= bar_state, (fused, rel_rmse(pool.cpu(), want_pool))
         assert torch.equal(shift.cpu().float(), torch.as_tensor(want_shift).to(dtype).float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("M", [1, 2, 4, 7, 8])
+def test_one_launch_decode_layer_matches_oracle_chain_and_operator_sequence(oracle, M, dtype):
+    """The persistent single-launch layer (grid-wide barriers between its stages) against the oracle chain, and
+    against the operator sequence it replaces: same rounding points, so the two GPU paths differ by summation order
+    only; scattered slots, untouched slots stay bit-identical, a second launch (the barrier counters must have been
+    left at zero) and a CUDA-graph replay give the first launch's bits."""
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+    from flashrwkv_b200.tmix.layer import TMixLayerWeights, decode_layer_error_flag, reference_sequence
+
+    D, H = 64, C // 64
+    W = _weights(dtype, seed=2000 + M)
+    gen = torch.Generator().manual_seed(M * 11)
+    x = torch.randn(M, C, generator=gen).to(dtype)
+    v_first = torch.randn(M, C, generator=gen).to(dtype)
+    cu = torch.arange(M + 1, dtype=torch.int32)
+    idx = torch.randperm(M + 3, generator=gen)[:M].to(torch.int32)
+    slots = M + 3
+    shift0 = torch.randn(slots, C, generator=gen).to(dtype)
+    pool0 = synthetic.state_pool(slots, H, D, seed=M)
+    want_out, want_pool, want_shift = _expected(oracle, W, x, v_first, shift0, pool0, cu, idx, D, dtype)
+    d = lambda t: t.cuda()  # noqa: E731
+    lw = TMixLayerWeights(*(d(m) for m in W["mix"]), d(W["Wr"]), d(W["Wk"]), d(W["Wv"]), d(W["Wo"]),
+                          {n: d(t) for n, t in W["w1"].items()}, {n: d(t) for n, t in W["w2"].items()}, d(W["k_k"]),
+                          d(W["a0"]), d(W["k_a"]), d(W["r_k"]), d(W["lnw"]), d(W["lnb"]), d(W["v0"]))
+    # TMixLayerWeights takes the mix vectors in the order r, w, k, v, a, g: the order of W["mix"]
+    bar_out, bar_state = (4e-3, 2e-3) if dtype == torch.float16 else (2.5e-2, 1e-2)
+    shift, pool = d(shift0).clone(), d(pool0).clone()
+    out = F.infer_tmix_decode_layer_forward_varlen(d(x), d(v_first), lw, shift_state_pool=shift, state_pool=pool,
+                                                   cu_seqlens=d(cu), state_indices=d(idx))
+    torch.cuda.synchronize()
+    assert decode_layer_error_flag() == 0
+    assert out.dtype == dtype and out.shape == (M, C)
+    assert rel_rmse(out.float().cpu(), want_out) <= bar_out
+    assert rel_rmse(pool.cpu(), want_pool) <= bar_state
+    assert torch.equal(shift.cpu().float(), torch.as_tensor(want_shift).to(dtype).float())
+    untouched = [s for s in range(slots) if s not in idx.tolist()]
+    assert torch.equal(pool[untouched].cpu(), pool0[untouched])
+    # the operator sequence on the same inputs
+    shift_b, pool_b = d(shift0).clone(), d(pool0).clone()
+    seq = reference_sequence(d(x), d(v_first), lw, shift_state_pool=shift_b, state_pool=pool_b, cu_seqlens=d(cu),
+                             state_indices=d(idx))
+    assert rel_rmse(out.float().cpu(), seq.float().cpu()) <= (2e-3 if dtype == torch.float16 else 1.2e-2)
+    assert rel_rmse(pool.cpu(), pool_b.cpu()) <= (5e-4 if dtype == torch.float16 else 4e-3)
+    assert torch.equal(shift, shift_b)
+    # again, with a prepared ticket, eagerly and from a CUDA graph: the same bits as the first launch
+    cu_d, idx_d, x_d, vf_d = d(cu), d(idx), d(x), d(v_first)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ticket = F.prepare_recurrent_metadata(cu_d, idx_d, total_tokens=M, state_pool_size=slots, max_seqlen=1)
+        shift_c, pool_c = d(shift0).clone(), d(pool0).clone()
+        run = lambda: F.infer_tmix_decode_layer_forward_varlen(  # noqa: E731
+            x_d, vf_d, lw, shift_state_pool=shift_c, state_pool=pool_c, cu_seqlens=cu_d, state_indices=idx_d,
+            validated_metadata=ticket)
+        out_c = run()
+        side.synchronize()
+        assert torch.equal(out_c, out) and torch.equal(pool_c, pool)
+        graph = torch.cuda.CUDAGraph()
+        shift_c.copy_(d(shift0)); pool_c.copy_(d(pool0))
+        with torch.cuda.graph(graph, stream=side):
+            out_g = run()
+        shift_c.copy_(d(shift0)); pool_c.copy_(d(pool0))
+        graph.replay()
+        side.synchronize()
+        assert torch.equal(out_g, out) and torch.equal(pool_c, pool)
+    torch.cuda.current_stream().wait_stream(side)
+    assert decode_layer_error_flag() == 0
