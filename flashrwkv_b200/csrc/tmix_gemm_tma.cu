@@ -34,19 +34,27 @@ constexpr int kBM = 128, kBK = 64;
 constexpr uint32_t kABytes = kBM * kBK * 2;  // 16 KB
 constexpr int kGemmThreads = 192;
 
-template <int BN>
+// kShift: the A operand is the token-shifted x, x + (prev - x) * mix, made in shared memory by four extra warps from
+// the x tile and the tile of the rows before (a second TMA load of the same map, one row up) before the MMA reads it.
+template <int BN, bool kShift>
 struct Cfg {
   static constexpr uint32_t kBBytes = BN * kBK * 2;
-  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr uint32_t kPrevBytes = kShift ? kABytes : 0;
+  static constexpr uint32_t kStageBytes = kABytes + kPrevBytes + kBBytes;
+  static constexpr int kPlain = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kStages = kShift ? (BN == 256 ? 3 : (BN == 128 ? 4 : 5)) : kPlain;
   static constexpr uint32_t kSmem = kStages * kStageBytes + 1024;  // + slack to align the tiles to 1024 bytes
   static constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators (a power of two >= 32)
+  static constexpr int kThreads = kShift ? kGemmThreads + 128 : kGemmThreads;
 };
 
 struct GemmParams {
   CUtensorMap map_x[kMaxProblems];
   CUtensorMap map_w[kMaxProblems];
   LinearGroup group;
+  const void* mix[kMaxProblems];     // kShift: the token-shift vector [K] of each problem
+  const void* shift_pool;            // kShift: [slots][K], the row before the first row of a sequence
+  const int* row_prev_slot;          // kShift: [M], the slot for a sequence's first row, -1 for every other row
   int tile_begin[kMaxProblems + 1];  // first tile index of each problem
   int tiles_m;                       // row tiles (the same for all problems)
   int count, M;
@@ -77,13 +85,13 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* mbar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(umma::smem_u32(mbar)) : "memory");
 }
 
-template <typename io_t, int BN>
-__global__ __launch_bounds__(kGemmThreads, 1) void linear_tma_kernel(const __grid_constant__ GemmParams prm,
-                                                                     int* __restrict__ error_flag) {
+template <typename io_t, int BN, bool kShift>
+__global__ __launch_bounds__(Cfg<BN, kShift>::kThreads, 1) void linear_tma_kernel(const __grid_constant__ GemmParams prm,
+                                                                                  int* __restrict__ error_flag) {
   using IO = Io16<io_t>;
-  using C = Cfg<BN>;
+  using C = Cfg<BN, kShift>;
   extern __shared__ unsigned char smem_raw[];
-  __shared__ uint64_t full_bar[C::kStages], empty_bar[C::kStages], acc_full[2], acc_empty[2];
+  __shared__ uint64_t full_bar[C::kStages], empty_bar[C::kStages], ready_bar[C::kStages], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_holder;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t tiles_base = (umma::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -92,6 +100,7 @@ __global__ __launch_bounds__(kGemmThreads, 1) void linear_tma_kernel(const __gri
     for (int i = 0; i < C::kStages; ++i) {
       umma::mbar_init(&full_bar[i], 1);
       umma::mbar_init(&empty_bar[i], 1);
+      umma::mbar_init(&ready_bar[i], 4);  // one arrival per transform warp
     }
     for (int i = 0; i < 2; ++i) {
       umma::mbar_init(&acc_full[i], 1);
@@ -129,11 +138,15 @@ __global__ __launch_bounds__(kGemmThreads, 1) void linear_tma_kernel(const __gri
           umma::mbar_expect_tx(&full_bar[s], C::kStageBytes);
           const uint32_t a_dst = tiles_base + s * C::kStageBytes;
           tma_load_2d(a_dst, &prm.map_x[z], kb * kBK, m0, &full_bar[s]);
+          // the rows before: the same map one row up (row -1 of the first tile reads as zeros and is never used:
+          // row 0 starts a sequence)
+          if (kShift) tma_load_2d(a_dst + kABytes, &prm.map_x[z], kb * kBK, m0 - 1, &full_bar[s]);
+          const uint32_t b_dst = a_dst + kABytes + C::kPrevBytes;
           if (prm.group.p[z].w_kn) {
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(a_dst + kABytes + j * 8192, &prm.map_w[z], n0 + 64 * j, kb * kBK, &full_bar[s]);
+              tma_load_2d(b_dst + j * 8192, &prm.map_w[z], n0 + 64 * j, kb * kBK, &full_bar[s]);
           } else {
-            tma_load_2d(a_dst + kABytes, &prm.map_w[z], kb * kBK, n0, &full_bar[s]);
+            tma_load_2d(b_dst, &prm.map_w[z], kb * kBK, n0, &full_bar[s]);
           }
         }
       }
@@ -154,9 +167,9 @@ __global__ __launch_bounds__(kGemmThreads, 1) void linear_tma_kernel(const __gri
         const uint32_t d_tmem = tmem + acc * BN;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
-          if (!umma::mbar_wait(&full_bar[s], ph)) { ok = false; break; }
+          if (!umma::mbar_wait(kShift ? &ready_bar[s] : &full_bar[s], ph)) { ok = false; break; }
           umma::fence_after_sync();
-          const uint32_t a_addr = tiles_base + s * C::kStageBytes, b_addr = a_addr + kABytes;
+          const uint32_t a_addr = tiles_base + s * C::kStageBytes, b_addr = a_addr + kABytes + C::kPrevBytes;
 #pragma unroll
           for (int ks = 0; ks < kBK / 16; ++ks)
             mma_f16_ss(d_tmem, desc_sw128(a_addr + ks * 32),
@@ -165,6 +178,54 @@ __global__ __launch_bounds__(kGemmThreads, 1) void linear_tma_kernel(const __gri
           umma::mma_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
         }
         if (ok) umma::mma_commit(&acc_full[acc]);
+      }
+    }
+  } else if (kShift && warp >= 6) {
+    // ---- token shift: A <- x + (prev - x) * mix, in place in the x tile ---------------------------------------------
+    // Thread t of the 128 takes the 16-byte piece at position t % 8 of rows t / 8 + 16 i (i = 0..7): consecutive lanes,
+    // consecutive pieces.  TMA's 128-byte swizzle has put the logical piece (t % 8) ^ (row % 8) there, the same for
+    // all eight rows of a thread, so its eight mix values per k-block are one 16-byte load.
+    const int t = tid - kGemmThreads, pos = t & 7, sub = t >> 3;
+    const int piece = pos ^ (sub & 7);  // logical 16-byte piece (eight k values) of these rows
+    unsigned char* tiles = smem_raw + (tiles_base - umma::smem_u32(smem_raw));
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      int z, m0, n0;
+      locate(tile, z, m0, n0);
+      const int K = prm.group.p[z].k, KB = (K + kBK - 1) / kBK;
+      const io_t* mix = static_cast<const io_t*>(prm.mix[z]);
+      int slot[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int m = m0 + sub + 16 * i;
+        slot[i] = m < prm.M ? __ldg(prm.row_prev_slot + m) : -1;
+      }
+      for (int kb = 0; kb < KB; ++kb, ++it) {
+        const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
+        if (!__all_sync(0xffffffffu, umma::mbar_wait(&full_bar[s], ph))) { ok = false; break; }
+        const int k0 = kb * kBK + 8 * piece;
+        if (k0 < K) {  // pieces beyond K are zero in x and stay zero
+          float mf[8];
+          unpack8<io_t>(__ldg(reinterpret_cast<const uint4*>(mix + k0)), mf);
+          unsigned char* a_tile = tiles + s * C::kStageBytes;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t off = uint32_t(sub + 16 * i) * 128u + uint32_t(pos) * 16u;
+            uint4* xa = reinterpret_cast<uint4*>(a_tile + off);
+            uint4 pv = *reinterpret_cast<const uint4*>(a_tile + kABytes + off);
+            if (slot[i] >= 0)
+              pv = __ldg(reinterpret_cast<const uint4*>(static_cast<const io_t*>(prm.shift_pool) + (long long)slot[i] * K + k0));
+            float xf[8], pf[8];
+            unpack8<io_t>(*xa, xf);
+            unpack8<io_t>(pv, pf);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) xf[e] = slot[i] == -2 ? quiet_nan() : fmaf(pf[e] - xf[e], mf[e], xf[e]);  // -2: bad metadata
+            *xa = make_uint4(IO::pack(xf[0], xf[1]), IO::pack(xf[2], xf[3]), IO::pack(xf[4], xf[5]), IO::pack(xf[6], xf[7]));
+          }
+        }
+        umma::fence_async_smem();  // generic writes before the tensor core's reads of the tile
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ready_bar[s]);
       }
     }
   } else {
@@ -256,7 +317,7 @@ bool make_map_kn(CUtensorMap* map, const void* base, int K, int N, bool bf16) {
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename io_t, int BN>
+template <typename io_t, int BN, bool kShift>
 int launch_bn(GemmParams& prm, bool bf16, int sm_count, int* error_flag, cudaStream_t stream) {
   int tiles = 0;
   for (int z = 0; z < prm.count; ++z) {
@@ -269,16 +330,18 @@ int launch_bn(GemmParams& prm, bool bf16, int sm_count, int* error_flag, cudaStr
       return fail(FRWKV_ERR_CUDA, "tmix_linear: cuTensorMapEncodeTiled failed (problem %d)", z);
   }
   for (int z = prm.count; z <= kMaxProblems; ++z) prm.tile_begin[z] = tiles;
-  cudaError_t e = cudaFuncSetAttribute(linear_tma_kernel<io_t, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)Cfg<BN>::kSmem);
+  using C = Cfg<BN, kShift>;
+  cudaError_t e = cudaFuncSetAttribute(linear_tma_kernel<io_t, BN, kShift>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)C::kSmem);
   if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "tmix_linear: %s", cudaGetErrorString(e));
   const int grid = tiles < sm_count ? tiles : sm_count;
-  linear_tma_kernel<io_t, BN><<<grid, kGemmThreads, Cfg<BN>::kSmem, stream>>>(prm, error_flag);
+  linear_tma_kernel<io_t, BN, kShift><<<grid, C::kThreads, C::kSmem, stream>>>(prm, error_flag);
   return check_launch("linear_tma_kernel");
 }
 
-template <typename io_t>
-int launch_typed(const LinearGroup& g, int count, int M, bool bf16, int* error_flag, cudaStream_t stream) {
+template <typename io_t, bool kShift>
+int launch_typed(const LinearGroup& g, int count, int M, bool bf16, const void* const* mix, const void* shift_pool,
+                 const int* row_prev_slot, int* error_flag, cudaStream_t stream) {
   int device = 0, sm_count = 0;
   cudaGetDevice(&device);
   cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
@@ -287,6 +350,9 @@ int launch_typed(const LinearGroup& g, int count, int M, bool bf16, int* error_f
   prm.group = g;
   prm.count = count;
   prm.M = M;
+  for (int z = 0; z < kMaxProblems; ++z) prm.mix[z] = (kShift && z < count) ? mix[z] : nullptr;
+  prm.shift_pool = shift_pool;
+  prm.row_prev_slot = row_prev_slot;
   prm.tiles_m = (M + kBM - 1) / kBM;
   // the widest tile that still gives every SM a tile (wide tiles read x fewer times)
   const auto tiles_for = [&](int bn) {
@@ -294,9 +360,9 @@ int launch_typed(const LinearGroup& g, int count, int M, bool bf16, int* error_f
     for (int z = 0; z < count; ++z) t += prm.tiles_m * ((g.p[z].n + bn - 1) / bn);
     return t;
   };
-  if (tiles_for(256) >= sm_count) return launch_bn<io_t, 256>(prm, bf16, sm_count, error_flag, stream);
-  if (tiles_for(128) >= sm_count) return launch_bn<io_t, 128>(prm, bf16, sm_count, error_flag, stream);
-  return launch_bn<io_t, 64>(prm, bf16, sm_count, error_flag, stream);
+  if (tiles_for(256) >= sm_count) return launch_bn<io_t, 256, kShift>(prm, bf16, sm_count, error_flag, stream);
+  if (tiles_for(128) >= sm_count) return launch_bn<io_t, 128, kShift>(prm, bf16, sm_count, error_flag, stream);
+  return launch_bn<io_t, 64, kShift>(prm, bf16, sm_count, error_flag, stream);
 }
 
 }  // namespace
@@ -313,8 +379,21 @@ bool linear_tma_usable(const LinearGroup& g, int count, int M) {
 }
 
 int launch_linear_tma(const LinearGroup& g, int count, int M, int io_dtype, int* error_flag, cudaStream_t stream) {
-  if (io_dtype == FRWKV_DTYPE_BF16) return launch_typed<__nv_bfloat16>(g, count, M, true, error_flag, stream);
-  if (io_dtype == FRWKV_DTYPE_FP16) return launch_typed<__half>(g, count, M, false, error_flag, stream);
+  if (io_dtype == FRWKV_DTYPE_BF16)
+    return launch_typed<__nv_bfloat16, false>(g, count, M, true, nullptr, nullptr, nullptr, error_flag, stream);
+  if (io_dtype == FRWKV_DTYPE_FP16)
+    return launch_typed<__half, false>(g, count, M, false, nullptr, nullptr, nullptr, error_flag, stream);
+  return fail(FRWKV_ERR_UNSUPPORTED, "tmix_linear: tensors must be float16 or bfloat16");
+}
+
+// y_z = (x + (prev - x) * mix_z) W_z^T for up to four projections of the same rows x: mix[z] is [K]; prev is the row
+// before, or shift_pool[row_prev_slot[m]] where row m starts a sequence (row_prev_slot[m] >= 0)
+int launch_linear_tma_shift(const LinearGroup& g, int count, int M, int io_dtype, const void* const* mix,
+                            const void* shift_pool, const int* row_prev_slot, int* error_flag, cudaStream_t stream) {
+  if (io_dtype == FRWKV_DTYPE_BF16)
+    return launch_typed<__nv_bfloat16, true>(g, count, M, true, mix, shift_pool, row_prev_slot, error_flag, stream);
+  if (io_dtype == FRWKV_DTYPE_FP16)
+    return launch_typed<__half, true>(g, count, M, false, mix, shift_pool, row_prev_slot, error_flag, stream);
   return fail(FRWKV_ERR_UNSUPPORTED, "tmix_linear: tensors must be float16 or bfloat16");
 }
 

@@ -391,6 +391,66 @@ extern "C" int frwkv_tmix_linear_grouped(const frwkv_linear_problem* problems, i
   return fail(FRWKV_ERR_UNSUPPORTED, "tmix_linear: tensors must be float16 or bfloat16");
 }
 
+// row m -> the shift-state slot that holds its predecessor when m is the first row of its sequence, else -1; -2 in
+// every row when the metadata failed validation (the consumer then writes NaN)
+namespace frwkv {
+namespace {
+__global__ void row_prev_slot_kernel(const int* __restrict__ cu_seqlens, const int* __restrict__ state_indices,
+                                     const int* __restrict__ status, int num_sequences, int total_rows,
+                                     int* __restrict__ out) {
+  const int m = blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= total_rows) return;
+  if (status != nullptr && status[0] != 0) { out[m] = -2; return; }
+  int lo = 0, hi = num_sequences;  // largest s with cu_seqlens[s] <= m
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (cu_seqlens[mid] <= m) lo = mid; else hi = mid;
+  }
+  out[m] = cu_seqlens[lo] == m ? state_indices[lo] : -1;
+}
+}  // namespace
+}  // namespace frwkv
+
+extern "C" int frwkv_tmix_shift_project_gemm(const void* x, void* shift_state_pool, const int32_t* cu_seqlens,
+                                             const int32_t* state_indices, const int32_t* metadata_status,
+                                             const frwkv_shift_projection* projections, int count, int total_rows,
+                                             int num_sequences, int channels, int io_dtype, int32_t* row_workspace,
+                                             int32_t* error_flag, frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(x && shift_state_pool && cu_seqlens && state_indices && projections && row_workspace,
+                "tmix_shift_project_gemm: null pointer argument");
+  FRWKV_REQUIRE(count >= 1 && count <= kMaxShiftProjections, "tmix_shift_project_gemm: 1..8 projections per call");
+  FRWKV_REQUIRE(total_rows > 8, "tmix_shift_project_gemm: more than 8 rows (fewer: frwkv_tmix_shift_project_varlen)");
+  FRWKV_REQUIRE(num_sequences >= 1 && num_sequences <= total_rows, "tmix_shift_project_gemm: bad sequence count");
+  FRWKV_REQUIRE(channels >= 64 && channels % 8 == 0, "tmix_shift_project_gemm: channel count must be a multiple of 8");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  row_prev_slot_kernel<<<(total_rows + 255) / 256, 256, 0, s>>>(cu_seqlens, state_indices, metadata_status, num_sequences,
+                                                                  total_rows, row_workspace);
+  int rc = check_launch("row_prev_slot_kernel");
+  if (rc != FRWKV_OK) return rc;
+  for (int first = 0; first < count; first += kMaxProblems) {
+    const int n = count - first < kMaxProblems ? count - first : kMaxProblems;
+    LinearGroup g;
+    const void* mix[kMaxProblems] = {nullptr, nullptr, nullptr, nullptr};
+    for (int i = 0; i < n; ++i) {
+      const frwkv_shift_projection& p = projections[first + i];
+      FRWKV_REQUIRE(p.mix && p.weight && p.y, "tmix_shift_project_gemm: null pointer in projection %d", first + i);
+      FRWKV_REQUIRE(p.n > 0 && p.n % 8 == 0, "tmix_shift_project_gemm: output width must be a positive multiple of 8");
+      g.p[i] = LinearProblem{x, p.weight, p.y, nullptr, nullptr, nullptr, p.n, channels, 0, 0};
+      mix[i] = p.mix;
+    }
+    for (int i = n; i < kMaxProblems; ++i) g.p[i] = g.p[0];
+    if (!linear_tma_usable(g, n, total_rows))
+      return fail(FRWKV_ERR_UNSUPPORTED, "tmix_shift_project_gemm: x, weights and mix vectors must be 16-byte aligned");
+    rc = launch_linear_tma_shift(g, n, total_rows, io_dtype, mix, shift_state_pool, row_workspace, error_flag, s);
+    if (rc != FRWKV_OK) return rc;
+  }
+  // every launch above has read the shift states: now they take each sequence's last row
+  return launch_shift_state_update(x, shift_state_pool, cu_seqlens, state_indices, metadata_status, num_sequences,
+                                   channels, io_dtype, s);
+}
+
 extern "C" int frwkv_tmix_shift_project_varlen(const void* x, void* shift_state_pool, const int32_t* cu_seqlens,
                                                const int32_t* state_indices, const int32_t* metadata_status,
                                                const frwkv_shift_projection* projections, int count, int total_rows,

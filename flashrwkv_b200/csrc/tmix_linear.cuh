@@ -228,5 +228,8 @@ int launch_shift_state_update(const void* x, void* shift_state_pool, const int* 
 // Returns FRWKV_OK, or a negative code with the message set.
 bool linear_tma_usable(const LinearGroup& g, int count, int M);
 int launch_linear_tma(const LinearGroup& g, int count, int M, int io_dtype, int* error_flag, cudaStream_t stream);
+// the same GEMM with the token shift applied to x while it is staged (tmix_gemm_tma.cu)
+int launch_linear_tma_shift(const LinearGroup& g, int count, int M, int io_dtype, const void* const* mix,
+                            const void* shift_pool, const int* row_prev_slot, int* error_flag, cudaStream_t stream);
 
 }  // namespace frwkv

@@ -664,7 +664,7 @@ std::vector<torch::Tensor> tmix_shift_project_varlen(torch::Tensor x, torch::Ten
                                                      torch::Tensor idx, int64_t max_seqlen,
                                                      std::shared_ptr<MetadataTicket> ticket) {
   check_io16(x, "x", x);
-  TORCH_CHECK(x.dim() == 2 && x.size(0) >= 1 && x.size(0) <= 8, "x must have packed shape [M,C] with 1 <= M <= 8");
+  TORCH_CHECK(x.dim() == 2 && x.size(0) >= 1, "x must have packed shape [M,C]");
   TORCH_CHECK(x.size(1) % 8 == 0 && x.size(1) >= 256, "C must be a multiple of 8 and at least 256");
   TORCH_CHECK(!mixes.empty() && mixes.size() <= 8 && mixes.size() == weights.size(),
               "1..8 mix vectors and as many weights are required");
@@ -701,6 +701,15 @@ std::vector<torch::Tensor> tmix_shift_project_varlen(torch::Tensor x, torch::Ten
     outs.push_back(torch::empty({x.size(0), weights[j].size(0)}, x.options()));
     proj.push_back({mixes[j].data_ptr(), weights[j].data_ptr(), outs.back().data_ptr(),
                     static_cast<int>(weights[j].size(0))});
+  }
+  if (x.size(0) > 8) {  // many rows: the shift happens inside the tensor-core GEMM
+    auto rows = torch::empty({x.size(0)}, x.options().dtype(torch::kInt32));
+    check_rc(frwkv_tmix_shift_project_gemm(x.data_ptr(), shift_state_pool.data_ptr(), launch_cu.data_ptr<int>(),
+                                           launch_idx.data_ptr<int>(), status.data_ptr<int>(), proj.data(),
+                                           static_cast<int>(proj.size()), static_cast<int>(x.size(0)),
+                                           static_cast<int>(idx.numel()), static_cast<int>(x.size(1)), io_dtype_of(x),
+                                           rows.data_ptr<int>(), nullptr, current_stream(x)));
+    return outs;
   }
   check_rc(frwkv_tmix_shift_project_varlen(x.data_ptr(), shift_state_pool.data_ptr(), launch_cu.data_ptr<int>(),
                                            launch_idx.data_ptr<int>(), status.data_ptr<int>(), proj.data(),

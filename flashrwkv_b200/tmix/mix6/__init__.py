@@ -76,14 +76,19 @@ def infer_tmix_mix6_add_layer_norm_forward_varlen(x, residual, weight, bias, x_r
 
 
 def infer_tmix_shift_project_forward_varlen(x, mixes, weights, *, shift_state_pool, cu_seqlens, state_indices,
-                                            max_seqlen: int | None = None, validated_metadata=None):
+                                            max_seqlen: int | None = None, validated_metadata=None,
+                                            fuse_many_rows: bool = False):
     """Token shift fused into the projections that consume it (no counterpart in the reference, which runs
     `infer_tmix_mix6_forward_varlen` and then the projections).
 
     `outputs[j] = (x + (prev - x) * mixes[j]) @ weights[j]^T` for up to eight `(mix [C], weight [N_j,C])` pairs —
     e.g. r, k, v and the four rank-in projections of a TMix layer — and each sequence's last row goes to its
     shift-state slot.  With 1..8 rows this is one launch (plus the state update) and the interpolated rows never
-    leave the chip; with more rows it runs mix6 per distinct mix vector and the grouped GEMMs.
+    leave the chip.  With more rows the default is mix6 per distinct mix vector and the grouped GEMMs;
+    `fuse_many_rows=True` does the interpolation inside the TMA-fed tensor-core GEMM instead, on its staged x tiles
+    (four projections per launch).  That form is correct and tested but measured slower on B200 (the GEMM is bound
+    by the fill of its shared-memory stages, and the extra pass over the x tile costs more than the six [M,C]
+    tensors it saves: 114 against 90 us for r, k, v and the four rank-in products at M = 512, C = 2048).
     """
     from ..linear import _grouped
 
@@ -107,7 +112,9 @@ def infer_tmix_shift_project_forward_varlen(x, mixes, weights, *, shift_state_po
     _check_metadata_inputs(cu_seqlens, state_indices)
     if max_seqlen is not None and (not isinstance(max_seqlen, int) or isinstance(max_seqlen, bool) or max_seqlen <= 0):
         raise ValueError("max_seqlen must be a positive integer")
-    if x.shape[0] <= 8 and x.shape[1] >= 256:
+    aligned = all(t.data_ptr() % 16 == 0 for t in (x, *mixes, *weights)) and all(w.shape[0] % 8 == 0 for w in weights)
+    if x.shape[1] >= 256 and x.shape[1] % 8 == 0 and (x.shape[0] <= 8 or (fuse_many_rows and aligned)):
+        # 1..8 rows: the small-row kernel; more (on request): the GEMM with the shift applied to its staged x tiles
         return tuple(extension().tmix_shift_project_varlen(
             x, shift_state_pool, mixes, weights, cu_seqlens, state_indices,
             -1 if max_seqlen is None else int(max_seqlen), validated_metadata))

@@ -387,6 +387,21 @@ int frwkv_tmix_shift_project_varlen(const void* x, void* shift_state_pool, const
                                     const frwkv_shift_projection* projections, int count, int total_rows,
                                     int num_sequences, int channels, int io_dtype, frwkv_stream_t stream);
 
+/*
+ * The same operator for more than 8 rows: the token shift happens inside the tensor-core GEMM.  Per pipeline stage TMA
+ * brings the x tile and the tile of the rows before it (the same tensor map, one row up); four warps turn the x tile
+ * into x + (prev - x) * mix in shared memory (for a sequence's first row prev comes from its shift state) before the
+ * tcgen05 products read it.  Projections go out four per launch; afterwards every sequence's last row becomes its shift
+ * state.  row_workspace: int32 [total_rows].  error_flag (may be NULL) is set if a bounded wait ran out.  Replaces
+ * tmix_mix6_forward_varlen followed by the projections' GEMMs
+ * (csrc/sm120/tmix/linear/infer_fp16_forward_varlen.cu:3058-3099 of the reference).
+ */
+int frwkv_tmix_shift_project_gemm(const void* x, void* shift_state_pool, const int32_t* cu_seqlens,
+                                  const int32_t* state_indices, const int32_t* metadata_status,
+                                  const frwkv_shift_projection* projections, int count, int total_rows,
+                                  int num_sequences, int channels, int io_dtype, int32_t* row_workspace,
+                                  int32_t* error_flag, frwkv_stream_t stream);
+
 /* Elementwise tanh (act = 1) or sigmoid (act = 2) of a 16-bit tensor with `elements` (multiple of 8) values.
  * Replaces linear_act_tanh / linear_act_sigmoid (csrc/sm120/tmix/linear/infer_fp16_forward_varlen.cu:1235-1373). */
 int frwkv_tmix_act_forward(const void* x, void* out, long long elements, int act, int io_dtype, frwkv_stream_t stream);

@@ -73,7 +73,7 @@ def _layer(F, W, x, v_first, shift, pool, cu, idx, D, fused):
         r, k, v, fw, fa, fg, fv = F.infer_tmix_shift_project_forward_varlen(
             x, [mix[0], mix[2], mix[3], mix[1], mix[4], mix[5], mix[3]],
             [W["Wr"], W["Wk"], W["Wv"], w1["w"], w1["a"], w1["g"], w1["v"]], shift_state_pool=shift, cu_seqlens=cu,
-            state_indices=idx, max_seqlen=max_len, validated_metadata=ticket)
+            state_indices=idx, max_seqlen=max_len, validated_metadata=ticket, fuse_many_rows=True)
     else:
         xr, xw, xk, xv, xa, xg = F.infer_tmix_mix6_forward_varlen(x, *mix, shift_state_pool=shift, cu_seqlens=cu,
                                                                   state_indices=idx, max_seqlen=max_len,

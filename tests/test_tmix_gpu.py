@@ -202,13 +202,17 @@ def test_dense_linear_ragged_shapes(oracle, dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("lengths", [(1,), (1,) * 7, (3, 1, 2), (8,), (5, 30)])
-def test_shift_project_fused_vs_oracle(oracle, dtype, lengths):
-    """Token shift fused into the projections (<= 8 rows: one launch; more rows: mix6 + GEMMs) against mix6 and the
-    projection of the oracle; the shift states end up holding each sequence's last row."""
+@pytest.mark.parametrize("lengths", [(1,), (1,) * 7, (3, 1, 2), (8,), (5, 30), (1,) * 130, (127, 1, 2, 129, 64, 200),
+                                     (300,)])
+@pytest.mark.parametrize("C", [512, 328])
+def test_shift_project_fused_vs_oracle(oracle, dtype, lengths, C):
+    """Token shift fused into the projections (<= 8 rows: the small-row kernel; more rows with fuse_many_rows: inside
+    the TMA-fed tensor-core GEMM, on its staged x tiles) against mix6 and the projection of the oracle; sequence starts inside,
+    at the first and at the last row of a 128-row tile, rows and channels that do not fill a tile (C = 328 leaves a
+    partial k-block); the shift states end up holding each sequence's last row."""
     import flashrwkv_b200 as F
 
-    C, M, slots = 512, sum(lengths), 9
+    M, slots = sum(lengths), len(lengths) + 3
     gen = torch.Generator().manual_seed(31 * M + len(lengths))
     x = torch.randn(M, C, generator=gen).to(dtype)
     pool = torch.randn(slots, C, generator=gen).to(dtype)
@@ -220,7 +224,7 @@ def test_shift_project_fused_vs_oracle(oracle, dtype, lengths):
     d_pool = pool.cuda().clone()
     outs = F.infer_tmix_shift_project_forward_varlen(x.cuda(), [mix[u].cuda() for u in use], [w.cuda() for w in Ws],
                                                      shift_state_pool=d_pool, cu_seqlens=cu.cuda(),
-                                                     state_indices=idx.cuda())
+                                                     state_indices=idx.cuda(), fuse_many_rows=True)
     torch.cuda.synchronize()
     # reference: previous rows, fp32 interpolation, projection
     prev = torch.empty(M, C)
@@ -236,6 +240,24 @@ def test_shift_project_fused_vs_oracle(oracle, dtype, lengths):
     for s, b in enumerate(cu[1:].tolist()):
         expect_pool[idx[s]] = x[b - 1]
     assert torch.equal(d_pool.cpu(), expect_pool)
+    if M > 8:  # the default for many rows (mix6, then the GEMMs) rounds the interpolated rows to 16 bits in between
+        d_pool3 = pool.cuda().clone()
+        outs3 = F.infer_tmix_shift_project_forward_varlen(x.cuda(), [mix[u].cuda() for u in use], [w.cuda() for w in Ws],
+                                                          shift_state_pool=d_pool3, cu_seqlens=cu.cuda(),
+                                                          state_indices=idx.cuda())
+        for a, b in zip(outs, outs3):
+            assert rel_rmse(a.double().cpu(), b.double().cpu()) <= 2 * TOL[dtype]
+        assert torch.equal(d_pool3.cpu(), expect_pool)
+    if M > 8 and len(lengths) > 1:  # bad metadata (a slot used twice) fails closed: NaN outputs, shift states untouched
+        bad = idx.clone()
+        bad[-1] = bad[0]
+        d_pool2 = pool.cuda().clone()
+        outs2 = F.infer_tmix_shift_project_forward_varlen(x.cuda(), [mix[u].cuda() for u in use], [w.cuda() for w in Ws],
+                                                          shift_state_pool=d_pool2, cu_seqlens=cu.cuda(),
+                                                          state_indices=bad.cuda(), fuse_many_rows=True)
+        torch.cuda.synchronize()
+        assert all(bool(torch.isnan(o.float()).all()) for o in outs2)
+        assert torch.equal(d_pool2.cpu(), pool)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
