@@ -35,6 +35,7 @@ from .tmix.normalization import *  # noqa: F401,F403
 from .tmix.normalization import __all__ as _norm_all
 from .tmix.vres_gate import infer_tmix_vres_gate_forward_varlen, pretrain_tmix_vres_gate_bf16
 from .tmix.layer import TMixLayerWeights, infer_tmix_decode_layer_forward_varlen
+from ._ext import check_device_error_flags, device_error_flags
 
 __all__ = [
     "infer_tmix_kk_a_gate_forward_varlen",
@@ -45,6 +46,8 @@ __all__ = [
     "infer_tmix_shift_project_forward_varlen",
     "infer_tmix_decode_layer_forward_varlen",
     "TMixLayerWeights",
+    "device_error_flags",
+    "check_device_error_flags",
     "infer_tmix_vres_gate_forward_varlen",
     *_linear_all,
     "infer_chunk_bf16_forward_varlen",

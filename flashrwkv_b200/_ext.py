@@ -46,3 +46,22 @@ def capi() -> ctypes.CDLL:
 
 def library_path() -> Path:
     return _LIB_PATH
+
+
+def device_error_flags() -> dict:
+    """The device error words of the latest launches that use bounded waits, by stage name (a host read: this
+    synchronises).  Non-zero = a tensor-core, copy or grid-barrier wait ran out in that stage and its outputs are NaN.
+    Stages: `wkv7_chunk_forward`, `wkv7_chunk_backward`, `tmix_linear` (sticky, one word per device),
+    `tmix_decode_layer` (word 7 of its eight); the recurrent decode kernels report through the metadata status word
+    (bit 16) instead."""
+    out = {}
+    for stage, words in extension().last_error_flags().items():
+        out[stage] = int(words[7].item()) if stage == "tmix_decode_layer" else int(words.flatten()[0].item())
+    return out
+
+
+def check_device_error_flags() -> None:
+    """Raise `RuntimeError` if any stage of `device_error_flags()` reports a wait that ran out."""
+    bad = {stage: flag for stage, flag in device_error_flags().items() if flag != 0}
+    if bad:
+        raise RuntimeError(f"a bounded device wait ran out (stage -> error word): {bad}; the affected outputs are NaN")

@@ -231,7 +231,8 @@ __global__ __launch_bounds__(Cfg<BN, kShift>::kThreads, 1) void linear_tma_kerne
   } else {
     const uint32_t quarter = warp & 3u;  // the tensor-memory lanes this warp may read: 32 * (warp % 4) ..
     uint32_t t = 0;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+    int tile = blockIdx.x;
+    for (; tile < total_tiles && ok; tile += gridDim.x, ++t) {
       int z, m0, n0;
       locate(tile, z, m0, n0);
       const LinearProblem& pr = prm.group.p[z];
@@ -263,6 +264,15 @@ __global__ __launch_bounds__(Cfg<BN, kShift>::kThreads, 1) void linear_tma_kerne
       umma::fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+    // a wait ran out: the tile it was for and the tiles this CTA never got to read as NaN, not as stale memory
+    for (; !ok && tile < total_tiles; tile += gridDim.x) {
+      int z, m0, n0;
+      locate(tile, z, m0, n0);
+      const LinearProblem& pr = prm.group.p[z];
+      const int m = m0 + 32 * quarter + lane;
+      io_t* y = static_cast<io_t*>(pr.y);
+      for (int n = n0; m < prm.M && n < n0 + BN && n < pr.n; ++n) y[(long long)m * pr.n + n] = IO::store(quiet_nan());
     }
   }
   if (!ok) {

@@ -249,8 +249,11 @@ __global__ __launch_bounds__(128, 2) void linear_tc_kernel(LinearGroup group, in
         }
       }
     }
-  } else if (tid == 0 && error_flag != nullptr) {
-    atomicExch(error_flag, 3);
+  } else {  // a wait ran out: the tile reads as NaN, not as stale memory
+    if (tid == 0 && error_flag != nullptr) atomicExch(error_flag, 3);
+    const int m = m0 + warp * 32 + (tid & 31);
+    io_t* y = static_cast<io_t*>(pr.y);
+    for (int n = n0; m < M && n < n0 + kBN && n < N; ++n) y[(long long)m * N + n] = IO::store(quiet_nan());
   }
   umma::fence_before_sync();
   __syncthreads();

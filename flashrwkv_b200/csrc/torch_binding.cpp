@@ -38,6 +38,33 @@ int io_dtype_of(const torch::Tensor& t) {
   return t.scalar_type() == torch::kBFloat16 ? FRWKV_DTYPE_BF16 : FRWKV_DTYPE_FP16;
 }
 
+// ---- device error words ------------------------------------------------------------------------------------------------
+// Kernels with bounded waits report a wait that ran out through an int32 word on the device (and write NaN instead of
+// results).  No operator synchronises to read it; the words of the latest launches are kept here by stage name, and
+// `last_error_flags()` hands them to Python, where reading them is the caller's decision.
+std::mutex g_flags_mutex;
+std::map<std::string, torch::Tensor> g_last_flags;
+void remember_flag(const std::string& stage, const torch::Tensor& flag) {
+  const std::lock_guard<std::mutex> lock(g_flags_mutex);
+  g_last_flags[stage] = flag;
+}
+std::map<std::string, torch::Tensor> last_error_flags() {
+  const std::lock_guard<std::mutex> lock(g_flags_mutex);
+  return g_last_flags;
+}
+// one sticky word per device for the projection kernels (tensor-core GEMMs): zero until a wait runs out
+torch::Tensor linear_flag(const torch::Tensor& like) {
+  static std::map<int, torch::Tensor> words;
+  const std::lock_guard<std::mutex> lock(g_flags_mutex);
+  const int dev = static_cast<int>(like.device().index());
+  auto it = words.find(dev);
+  if (it == words.end()) {
+    it = words.emplace(dev, torch::zeros({1}, like.options().dtype(torch::kInt32))).first;
+    g_last_flags["tmix_linear"] = it->second;
+  }
+  return it->second;
+}
+
 void check_cuda_contiguous(const torch::Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, " must be CUDA");
   TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
@@ -447,6 +474,7 @@ torch::Tensor wkv7_chunk_forward(torch::Tensor sco, torch::Tensor cs, torch::Ten
   TORCH_CHECK(!(state_dot_a.has_value() && path == 0), "state_dot_a is produced by the fused kernel only");
   const c10::cuda::CUDAGuard guard(r.device());
   auto error_flag = torch::zeros({1}, r.options().dtype(torch::kInt32));
+  remember_flag("wkv7_chunk_forward", error_flag);
   const bool fused = path == 1 || state_dot_a.has_value() ||
                      (path == -1 && frwkv_wkv7_chunk_prefers_fused(static_cast<int>(B), static_cast<int>(H)) != 0);
   if (fused) {
@@ -708,7 +736,7 @@ std::vector<torch::Tensor> tmix_shift_project_varlen(torch::Tensor x, torch::Ten
                                            launch_idx.data_ptr<int>(), status.data_ptr<int>(), proj.data(),
                                            static_cast<int>(proj.size()), static_cast<int>(x.size(0)),
                                            static_cast<int>(idx.numel()), static_cast<int>(x.size(1)), io_dtype_of(x),
-                                           rows.data_ptr<int>(), nullptr, current_stream(x)));
+                                           rows.data_ptr<int>(), linear_flag(x).data_ptr<int>(), current_stream(x)));
     return outs;
   }
   check_rc(frwkv_tmix_shift_project_varlen(x.data_ptr(), shift_state_pool.data_ptr(), launch_cu.data_ptr<int>(),
@@ -813,6 +841,7 @@ std::tuple<torch::Tensor, torch::Tensor> tmix_decode_layer(torch::Tensor x, torc
   check_rc(frwkv_tmix_decode_layer_forward(&a, launch_idx.data_ptr<int>(), status.data_ptr<int>(), static_cast<int>(M),
                                            static_cast<int>(C), static_cast<int>(C / 64), static_cast<float>(eps),
                                            io_dtype_of(x), words.data_ptr<int>() + 7, current_stream(x)));
+  remember_flag("tmix_decode_layer", words);  // index 7 is the error word
   return {out, words};
 }
 
@@ -951,7 +980,7 @@ std::vector<torch::Tensor> tmix_linear_grouped(std::vector<torch::Tensor> xs, st
     problems[count - 1].v0 = v0.data_ptr();
   }
   check_rc(frwkv_tmix_linear_grouped(problems.data(), static_cast<int>(count), static_cast<int>(M), io_dtype_of(x0),
-                                     nullptr, current_stream(x0)));
+                                     linear_flag(x0).data_ptr<int>(), current_stream(x0)));
   return outs;
 }
 
@@ -989,7 +1018,8 @@ torch::Tensor linear_runtime_layout(torch::Tensor x, const torch::Tensor& w_kn, 
     p.v_first = v_first.data_ptr();
     p.v0 = v0.data_ptr();
   }
-  check_rc(frwkv_tmix_linear_runtime_layout(&p, static_cast<int>(M), io_dtype_of(x), nullptr, current_stream(x)));
+  check_rc(frwkv_tmix_linear_runtime_layout(&p, static_cast<int>(M), io_dtype_of(x), linear_flag(x).data_ptr<int>(),
+                                            current_stream(x)));
   return y;
 }
 
@@ -1389,6 +1419,7 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> wkv7_adjoint_scan(
   auto boundary_adjoint = torch::empty({Cn, H, 64, 64}, f32);
   auto khat = torch::empty(r.sizes(), f32);
   auto error_flag = torch::zeros({1}, r.options().dtype(torch::kInt32));
+  remember_flag("wkv7_chunk_backward", error_flag);  // the scan and the token-gradient kernel share the word
   check_rc(frwkv_wkv7_adjoint_scan(sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(), r.data_ptr(), w.data_ptr(),
                                    a.data_ptr(), b.data_ptr(), decay_bias.has_value() ? decay_bias->data_ptr() : nullptr,
                                    grad_output.data_ptr(), g_state.data_ptr<float>(), boundary_adjoint.data_ptr<float>(),
@@ -1957,6 +1988,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("b"), py::arg("grad_output") = py::none(), py::arg("grad_final_state") = py::none(),
         py::arg("scale") = 1.0, py::arg("into") = std::vector<torch::Tensor>{});
   m.def("rwkv7_clampw_v3_error_flags", &clampw_error_flags);
+  m.def("last_error_flags", &last_error_flags);
   m.def("wkv7_train_wide_forward", &wkv7_train_wide_forward, py::arg("sequence_chunk_offsets"),
         py::arg("chunk_token_starts"), py::arg("chunk_token_ends"), py::arg("state"), py::arg("r"),
         py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"), py::arg("output"),

@@ -257,3 +257,26 @@ def test_chunk_tables_are_validated_before_any_launch():
     for match, tables in bad.items():
         with pytest.raises(ValueError, match=match):
             F.statetune_recurrent_fp32io16(S0, *tables, *toks)
+
+
+def test_device_error_words_are_kept_and_zero_after_clean_runs():
+    """Every stage with bounded waits leaves its error word where `device_error_flags()` finds it; clean runs read 0
+    and `check_device_error_flags()` stays silent.  (The give-up path itself is exercised on a barrier at which
+    nothing arrives: tests/test_umma_gpu.py, and by the sticky time-out bit of the decode operators.)"""
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+    from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata
+
+    H, D, T = 2, 64, 130
+    toks = [t.cuda().requires_grad_() for t in synthetic.wkv7_inputs(T, H, D, seed=2)]
+    S0 = synthetic.state_pool(1, H, D, seed=3, device="cuda").requires_grad_()
+    cu = torch.tensor([0, T], dtype=torch.int32, device="cuda")
+    out = F.statetune_recurrent_fp32io16(S0, *make_chunk_metadata(cu, 64), *toks)
+    out[0].float().sum().backward()
+    x = torch.randn(40, 256, device="cuda").to(torch.bfloat16)
+    W = torch.randn(64, 256, device="cuda").to(torch.bfloat16)
+    F.infer_tmix_linear_forward_varlen(x, W)  # more than 8 rows: the tensor-core GEMM
+    flags = F.device_error_flags()
+    for stage in ("wkv7_chunk_forward", "wkv7_chunk_backward", "tmix_linear"):
+        assert flags.get(stage) == 0, (stage, flags)
+    F.check_device_error_flags()
