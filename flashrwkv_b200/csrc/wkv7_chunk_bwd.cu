@@ -73,7 +73,7 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
   __shared__ uint64_t mbar[6];
   __shared__ uint32_t tmem_holder;
   __shared__ float seg_total[8][64];
-  __shared__ float end_term[64];
+  __shared__ float end_part[8][64];  // sum_v G S_L per key channel, one partial per block of eight value columns
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int m = 32 * (warp & 3) + lane;  // tensor-memory lane / operand row of this thread
   const int cg = warp >> 2;              // column group: 16 of 64 columns, 32 of 128
@@ -147,7 +147,6 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
         draw[i] = (valid && !low) ? __ldg(dp + i) : zero4;
       }
     }
-    if (tid < 64) end_term[tid] = 0.f;
 
     // ---- g[t][k] (as in the forward kernel; threads 0..255 work) ------------------------------------------------
     umma::cp_async_wait_all();
@@ -251,8 +250,9 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
       const float4 sb = __ldg(reinterpret_cast<const float4*>(s_end + kk * kD + v0 + 4));
       const float4 za = __ldg(reinterpret_cast<const float4*>(s_start + kk * kD + v0));
       const float4 zb = __ldg(reinterpret_cast<const float4*>(s_start + kk * kD + v0 + 4));
-      atomicAdd(&end_term[kk], ga.x * sa.x + ga.y * sa.y + ga.z * sa.z + ga.w * sa.w + gb.x * sb.x + gb.y * sb.y +
-                                   gb.z * sb.z + gb.w * sb.w);
+      // partial sums in a table, added later in a fixed order: repeated runs give the same bits
+      end_part[tid >> 6][kk] = ga.x * sa.x + ga.y * sa.y + ga.z * sa.z + ga.w * sa.w + gb.x * sb.x + gb.y * sb.y +
+                               gb.z * sb.z + gb.w * sb.w;
       const float4 ha = umma::to_tf32(make_float4(gl * ga.x, gl * ga.y, gl * ga.z, gl * ga.w));
       const float4 hb = umma::to_tf32(make_float4(gl * gb.x, gl * gb.y, gl * gb.z, gl * gb.w));
       st4(smem, kOffNG + uint32_t(v0 >> 2) * kCS64 + kk * 16, ha);
@@ -609,7 +609,12 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
         const int t = 8 * seg + i;
         float d = ld1(smem, kOffTG + col + t * 16) - ld1(smem, kOffTDY + col + t * 16) - ld1(smem, kOffNG + col + t * 16);
         if (t + 1 < kL) d += ld1(smem, kOffNS + col + (t + 1) * 16);
-        if (t == len - 1) d += end_term[kcol];
+        if (t == len - 1) {
+          float e = end_part[0][kcol];
+#pragma unroll
+          for (int vb = 1; vb < 8; ++vb) e += end_part[vb][kcol];
+          d += e;
+        }
         dsum[i] = t < len ? d : 0.f;
       }
 #pragma unroll

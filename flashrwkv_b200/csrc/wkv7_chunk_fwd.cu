@@ -294,7 +294,7 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
       issue_mma(tmem, sbase + kOffX1, kCS128, sbase + kOffX2, kCS128, 128, false);
       umma::mma_commit(&mbar[0]);
     }
-    ok = umma::mbar_wait(&mbar[0], parity) && ok;
+    ok = __all_sync(0xffffffffu, umma::mbar_wait(&mbar[0], parity) && ok) != 0;  // one answer per warp
     umma::fence_after_sync();
     if (ok) {
       uint32_t u[32];
@@ -410,7 +410,7 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
     }
     if (m < 64 && colq < 2) {
       // warps 0, 1, 4, 5: Z^T -> AZ rows 64 + v, col t (32 value columns per warp)
-      ok = umma::mbar_wait(&mbar[1], parity) && ok;
+      ok = __all_sync(0xffffffffu, umma::mbar_wait(&mbar[1], parity) && ok) != 0;  // one answer per warp
       umma::fence_after_sync();
       if (ok) {
         const uint32_t o = kOffAZ + uint32_t(mt >> 2) * kCS128P + uint32_t(mt & 3) * 4 + 64 * 16;
@@ -432,7 +432,7 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
       issue_mma(tmem + 192, sbase + kOffAZ, kCS128P, sbase + kOffTT, kCS64P, 64, false);
       umma::mma_commit(&mbar[2]);
     }
-    ok = umma::mbar_wait(&mbar[2], parity) && ok;
+    ok = __all_sync(0xffffffffu, umma::mbar_wait(&mbar[2], parity) && ok) != 0;  // one answer per warp
     umma::fence_after_sync();
     if (ok && colq < 2) {  // warps 0..7, 32 of the 64 columns each
       uint32_t u[32];
@@ -455,7 +455,7 @@ __global__ __launch_bounds__(kBuildThreads, 1) void wkv7_chunk_build_kernel(
       issue_mma(tmem + 64, sbase + kOffRK, kCS128P, sbase + kOffVT, kCS64P, 64, true);
       umma::mma_commit(&mbar[3]);
     }
-    ok = umma::mbar_wait(&mbar[3], parity) && ok;
+    ok = __all_sync(0xffffffffu, umma::mbar_wait(&mbar[3], parity) && ok) != 0;  // one answer per warp
     umma::fence_after_sync();
     if (ok && item + (int)gridDim.x < num_items) stage_item(item + gridDim.x);
     if (ok) {
@@ -590,14 +590,15 @@ __global__ __launch_bounds__(128, 1) void wkv7_chunk_scan_kernel(
     const int it = c - c_begin, stage = it & 1;
     const uint32_t acc = tmem + 64 * stage;
     unsigned char* st = smem + stage * kScanStage;
-    ok = umma::mbar_wait(&full_bar[stage], (it >> 1) & 1);
+    // one verdict for the whole CTA on every wait: nobody runs on alone into the barriers and tensor-memory loads below
+    ok = __syncthreads_and(umma::mbar_wait(&full_bar[stage], (it >> 1) & 1) ? 1 : 0) != 0;
     if (!ok) break;
     if (tid == 0) {
       umma::fence_after_sync();
       issue_mma(acc, sbase + stage * kScanStage, kCS128, sbase + kScanOffST, kCS64P, 64, false);
       umma::mma_commit(&mma_bar);
     }
-    ok = umma::mbar_wait(&mma_bar, it & 1);
+    ok = __syncthreads_and(umma::mbar_wait(&mma_bar, it & 1) ? 1 : 0) != 0;
     umma::fence_after_sync();
     if (!ok) break;
     const int t0 = chunk_starts[c];
@@ -671,7 +672,19 @@ __global__ __launch_bounds__(128, 1) void wkv7_chunk_scan_kernel(
       umma::bulk_g2s(st, src, kScanStage, &full_bar[stage]);
     }
   }
-  if (!ok && tid == 0 && error_flag != nullptr) atomicExch(error_flag, 2);
+  if (!ok) {
+    // fail closed: the rows of this (sequence, head) read as NaN; copies and products that may still be in flight get
+    // time to land before the shared and tensor memory go away
+    if (tid == 0 && error_flag != nullptr) atomicExch(error_flag, 2);
+    const io_t nan16 = IO::store(quiet_nan());
+    const int tb = chunk_starts[c_begin], te = chunk_ends[c_end - 1];
+    for (long long e = (long long)tb * kD + tid; e < (long long)te * kD; e += blockDim.x) {
+      const long long at = ((e / kD) * num_heads + head) * kD + (e % kD);
+      y_ptr[at] = nan16;
+      if (y32_ptr != nullptr) y32_ptr[at] = quiet_nan();
+    }
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
   umma::fence_before_sync();
   __syncthreads();
   if (warp == 0) umma::tmem_dealloc(tmem, 128);
