@@ -66,8 +66,50 @@ __global__ void validate_metadata_kernel(const int* __restrict__ cu, const int* 
   }
 }
 
+// Chunk tables of the training operators: status[0] receives FRWKV_META_* bits when a chunk lies outside [0, N], holds
+// more than max_chunk tokens, does not follow its predecessor in the same sequence, or the offsets do not rise from 0
+// to the chunk count.  status[0] must be zero beforehand (the launcher clears it).
+__global__ void validate_chunk_tables_kernel(const int* __restrict__ sco, const int* __restrict__ cs,
+                                             const int* __restrict__ ce, int num_sequences, int num_chunks,
+                                             int total_tokens, int max_chunk, int* __restrict__ status) {
+  int error = 0;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < num_chunks + num_sequences; i += gridDim.x * blockDim.x) {
+    if (i < num_chunks) {
+      const int a = cs[i], b = ce[i];
+      if (a < 0 || b < a || b > total_tokens || b - a > max_chunk) error |= FRWKV_META_INVALID_RANGE;
+    } else {
+      const int s = i - num_chunks;
+      const int c0 = sco[s], c1 = sco[s + 1];
+      if ((s == 0 && c0 != 0) || (s == num_sequences - 1 && c1 != num_chunks) || c0 < 0 || c1 < c0 || c1 > num_chunks) {
+        error |= FRWKV_META_INVALID_ENDPOINT;
+      } else {
+        for (int c = c0 + 1; c < c1; ++c)
+          if (cs[c] != ce[c - 1]) error |= FRWKV_META_INVALID_RANGE;
+      }
+    }
+  }
+  if (error) atomicOr(&status[0], error);
+}
+
 }  // namespace
 }  // namespace frwkv
+
+extern "C" int frwkv_validate_chunk_tables(const int32_t* seq_chunk_offsets, const int32_t* chunk_starts,
+                                           const int32_t* chunk_ends, int num_sequences, int num_chunks,
+                                           int total_tokens, int max_chunk, int32_t* status, frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(seq_chunk_offsets && chunk_starts && chunk_ends && status, "validate_chunk_tables: null pointer argument");
+  FRWKV_REQUIRE(num_sequences > 0 && num_chunks > 0 && total_tokens > 0 && max_chunk > 0,
+                "validate_chunk_tables: sizes must be positive");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int32_t), s);
+  if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "validate_chunk_tables: %s", cudaGetErrorString(e));
+  const int work = num_chunks + num_sequences;
+  validate_chunk_tables_kernel<<<(work + 255) / 256 < 1024 ? (work + 255) / 256 : 1024, 256, 0, s>>>(
+      seq_chunk_offsets, chunk_starts, chunk_ends, num_sequences, num_chunks, total_tokens, max_chunk, status);
+  return check_launch("validate_chunk_tables_kernel");
+}
 
 extern "C" int frwkv_validate_recurrent_metadata(const int32_t* cu_seqlens, const int32_t* state_indices,
                                                  int num_sequences, int total_tokens, int state_pool_size,

@@ -404,6 +404,16 @@ void check_chunk_tables(const torch::Tensor& sco, const torch::Tensor& cs, const
   TORCH_CHECK(cs.numel() > 0 && cs.numel() == ce.numel(), "chunk_token_starts and chunk_token_ends must have shape [Cn]");
 }
 
+// The device-side verdict on caller-built chunk tables (int32[1], zero = good): kernels given it fail closed
+torch::Tensor chunk_table_status(const torch::Tensor& sco, const torch::Tensor& cs, const torch::Tensor& ce,
+                                 const torch::Tensor& r) {
+  auto status = torch::empty({1}, r.options().dtype(torch::kInt32));
+  check_rc(frwkv_validate_chunk_tables(sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(),
+                                       static_cast<int>(sco.numel() - 1), static_cast<int>(cs.numel()),
+                                       static_cast<int>(r.size(0)), 64, status.data_ptr<int>(), current_stream(r)));
+  return status;
+}
+
 // Chunked forward.  `state` [slots,H,64,64] fp32 is updated in place (slot = state_indices[s], or s when
 // state_indices is None).  Returns the device error flag (int32[1]; non-zero = a tensor-core wait ran out).
 // `path`: 0 = build + scan kernels with a workspace, 1 = the fused single kernel, -1 = whichever
@@ -1290,11 +1300,14 @@ void wkv7_train_wide_forward(torch::Tensor sco, torch::Tensor cs, torch::Tensor 
     dense_groups = static_cast<int>(dense_checkpoints->size(2));
   }
   const c10::cuda::CUDAGuard guard(r.device());
+  // caller-built tables: verdict on the device; on a bad table the kernels do nothing and the output reads as NaN
+  auto status = chunk_table_status(sco, cs, ce, r);
   check_rc(frwkv_wkv7_train_wide_forward(sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(),
                                          state.data_ptr<float>(), r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(),
                                          a.data_ptr(), b.data_ptr(), output.data_ptr(), bnd, sda, dense, dense_groups,
-                                         static_cast<int>(B), static_cast<int>(H), static_cast<int>(D), io_dtype_of(r),
-                                         static_cast<float>(scale), current_stream(r)));
+                                         status.data_ptr<int>(), static_cast<int>(B), static_cast<int>(H),
+                                         static_cast<int>(D), io_dtype_of(r), static_cast<float>(scale), current_stream(r)));
+  output.masked_fill_(status.ne(0), std::numeric_limits<double>::quiet_NaN());
 }
 
 // returns (grad_r, grad_decay_logits, grad_k, grad_v, grad_a, grad_b, grad_initial_state)
@@ -1338,15 +1351,19 @@ std::vector<torch::Tensor> wkv7_train_wide_backward(torch::Tensor sco, torch::Te
     TORCH_CHECK(t.numel() == r.numel() && t.scalar_type() == r.scalar_type(), "gradient tensors must match r");
   }
   auto dS0 = torch::empty_like(final_state);
+  auto status = chunk_table_status(sco, cs, ce, r);
   const size_t floats = frwkv_wkv7_train_wide_workspace_floats(N, static_cast<int>(Cn), static_cast<int>(H), static_cast<int>(D));
   auto workspace = torch::empty({static_cast<int64_t>(floats)}, final_state.options());
   check_rc(frwkv_wkv7_train_wide_backward(
       sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(), final_state.data_ptr<float>(),
       boundary.data_ptr<float>(), state_dot_a.data_ptr<float>(), r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(),
       a.data_ptr(), b.data_ptr(), go, gf, g[0].data_ptr(), g[1].data_ptr(), g[2].data_ptr(), g[3].data_ptr(),
-      g[4].data_ptr(), g[5].data_ptr(), dS0.data_ptr<float>(), workspace.data_ptr<float>(), N, static_cast<int>(B),
-      static_cast<int>(Cn), static_cast<int>(H), static_cast<int>(D), io_dtype_of(r), static_cast<float>(scale),
-      current_stream(r)));
+      g[4].data_ptr(), g[5].data_ptr(), dS0.data_ptr<float>(), workspace.data_ptr<float>(), status.data_ptr<int>(), N,
+      static_cast<int>(B), static_cast<int>(Cn), static_cast<int>(H), static_cast<int>(D), io_dtype_of(r),
+      static_cast<float>(scale), current_stream(r)));
+  const auto bad = status.ne(0);
+  for (auto& t : g) t.masked_fill_(bad, std::numeric_limits<double>::quiet_NaN());
+  dS0.masked_fill_(bad, std::numeric_limits<double>::quiet_NaN());
   g.push_back(dS0);
   return g;
 }
@@ -1362,8 +1379,9 @@ void statetune_recurrent_fp32io16_forward(torch::Tensor sco, torch::Tensor cs, t
     wkv7_train_wide_forward(sco, cs, ce, state, r, w, k, v, a, b, output, boundary, state_dot_a, scale, std::nullopt);
     return;
   }
+  // this entry is reached with caller-built tables (the reference's wrapper checks shapes only): verdict on the device
   wkv7_chunk_forward(sco, cs, ce, state, r, w, k, v, a, b, output, scale, std::nullopt, std::nullopt, boundary,
-                     std::nullopt, std::nullopt, state_dot_a, 1);
+                     std::nullopt, chunk_table_status(sco, cs, ce, r), state_dot_a, 1);
 }
 
 std::vector<torch::Tensor> wkv7_backward_chunked(torch::Tensor sco, torch::Tensor cs, torch::Tensor ce,
@@ -1404,7 +1422,7 @@ void statetune_recurrent_fp32io16_backward(torch::Tensor sco, torch::Tensor cs, 
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> wkv7_adjoint_scan(
     torch::Tensor sco, torch::Tensor cs, torch::Tensor ce, torch::Tensor r, torch::Tensor w, torch::Tensor a,
     torch::Tensor b, torch::Tensor grad_output, std::optional<torch::Tensor> grad_final_state, double scale,
-    std::optional<torch::Tensor> decay_bias) {
+    std::optional<torch::Tensor> decay_bias, std::optional<torch::Tensor> table_status) {
   check_chunk_tables(sco, cs, ce, r);
   TORCH_CHECK(r.dim() == 3 && r.size(2) == 64, "token tensors must have shape [N,H,64]");
   check_cuda_contiguous(grad_output, "grad_output");
@@ -1423,9 +1441,10 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> wkv7_adjoint_scan(
   check_rc(frwkv_wkv7_adjoint_scan(sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(), r.data_ptr(), w.data_ptr(),
                                    a.data_ptr(), b.data_ptr(), decay_bias.has_value() ? decay_bias->data_ptr() : nullptr,
                                    grad_output.data_ptr(), g_state.data_ptr<float>(), boundary_adjoint.data_ptr<float>(),
-                                   khat.data_ptr<float>(), error_flag.data_ptr<int>(), static_cast<int>(r.size(0)),
-                                   static_cast<int>(B), static_cast<int>(Cn), static_cast<int>(H), 64, io_dtype_of(r),
-                                   static_cast<float>(scale), current_stream(r)));
+                                   khat.data_ptr<float>(), error_flag.data_ptr<int>(),
+                                   table_status.has_value() ? table_status->data_ptr<int>() : nullptr,
+                                   static_cast<int>(r.size(0)), static_cast<int>(B), static_cast<int>(Cn),
+                                   static_cast<int>(H), 64, io_dtype_of(r), static_cast<float>(scale), current_stream(r)));
   return {g_state, boundary_adjoint, error_flag};
 }
 
@@ -1453,7 +1472,8 @@ std::vector<torch::Tensor> wkv7_backward_chunked(torch::Tensor sco, torch::Tenso
   const c10::cuda::CUDAGuard guard(r.device());
   torch::Tensor go = grad_output.has_value() ? grad_output->contiguous() : torch::zeros_like(r);
   TORCH_CHECK(go.sizes() == r.sizes() && go.scalar_type() == r.scalar_type(), "grad_output must match r");
-  auto scanned = wkv7_adjoint_scan(sco, cs, ce, r, w, a, b, go, grad_final_state, scale, std::nullopt);
+  auto table_status = chunk_table_status(sco, cs, ce, r);  // bad tables: NaN gradients, no out-of-range access
+  auto scanned = wkv7_adjoint_scan(sco, cs, ce, r, w, a, b, go, grad_final_state, scale, std::nullopt, table_status);
   std::vector<torch::Tensor> g = std::move(into);  // the caller's six gradient tensors, or none: allocate
   if (g.empty())
     for (int i = 0; i < 6; ++i) g.push_back(torch::empty_like(r));
@@ -1468,8 +1488,8 @@ std::vector<torch::Tensor> wkv7_backward_chunked(torch::Tensor sco, torch::Tenso
       boundary.data_ptr<float>(), std::get<1>(scanned).data_ptr<float>(), state_dot_a.data_ptr<float>(), r.data_ptr(),
       w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(), nullptr, go.data_ptr(), g[0].data_ptr(),
       g[1].data_ptr(), g[2].data_ptr(), g[3].data_ptr(), g[4].data_ptr(), g[5].data_ptr(), error_flag.data_ptr<int>(),
-      static_cast<int>(B), static_cast<int>(Cn), static_cast<int>(H), 64, io_dtype_of(r), static_cast<float>(scale),
-      current_stream(r)));
+      table_status.data_ptr<int>(), static_cast<int>(r.size(0)), static_cast<int>(B), static_cast<int>(Cn),
+      static_cast<int>(H), 64, io_dtype_of(r), static_cast<float>(scale), current_stream(r)));
   g.push_back(std::get<0>(scanned));
   g.push_back(error_flag);
   return g;
@@ -1981,7 +2001,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wkv7_adjoint_scan", &wkv7_adjoint_scan, py::arg("sequence_chunk_offsets"), py::arg("chunk_token_starts"),
         py::arg("chunk_token_ends"), py::arg("r"), py::arg("decay_logits"), py::arg("a"), py::arg("b"),
         py::arg("grad_output"), py::arg("grad_final_state") = py::none(), py::arg("scale") = 1.0,
-        py::arg("decay_bias") = py::none());
+        py::arg("decay_bias") = py::none(), py::arg("table_status") = py::none());
   m.def("wkv7_backward_chunked", &wkv7_backward_chunked, py::arg("sequence_chunk_offsets"),
         py::arg("chunk_token_starts"), py::arg("chunk_token_ends"), py::arg("final_state"), py::arg("boundary"),
         py::arg("state_dot_a"), py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"),

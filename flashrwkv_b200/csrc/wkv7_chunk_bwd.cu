@@ -67,8 +67,16 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
     const io_t* __restrict__ b_ptr, const io_t* __restrict__ bias_ptr, const io_t* __restrict__ dy_ptr,
     io_t* __restrict__ dr_ptr, io_t* __restrict__ dw_ptr, io_t* __restrict__ dk_ptr, io_t* __restrict__ dv_ptr,
     io_t* __restrict__ da_ptr, io_t* __restrict__ db_ptr, int num_sequences, int num_heads, int num_items, float scale,
-    int* __restrict__ error_flag) {
+    int* __restrict__ error_flag, const int* __restrict__ metadata_status, long long output_elements) {
   using IO = Io16<io_t>;
+  if (metadata_status != nullptr && metadata_status[0] != 0) {  // bad chunk tables: fail closed, touch nothing else
+    const io_t nan16 = IO::store(quiet_nan());
+    for (long long i = (long long)blockIdx.x * kBwdThreads + threadIdx.x; i < output_elements;
+         i += (long long)gridDim.x * kBwdThreads) {
+      dr_ptr[i] = nan16; dw_ptr[i] = nan16; dk_ptr[i] = nan16; dv_ptr[i] = nan16; da_ptr[i] = nan16; db_ptr[i] = nan16;
+    }
+    return;
+  }
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t mbar[6];
   __shared__ uint32_t tmem_holder;
@@ -667,7 +675,8 @@ int launch_chunk_backward(const int* sco, const int* cs, const int* ce, const fl
                           const float* adjoint, const float* sda, const void* r, const void* w, const void* k,
                           const void* v, const void* a, const void* b, const void* bias, const void* dy, void* dr,
                           void* dw, void* dk, void* dv, void* da, void* db, int num_sequences, int num_chunks,
-                          int num_heads, float scale, int* error_flag, int which, cudaStream_t stream) {
+                          int num_heads, float scale, int* error_flag, const int* metadata_status, int total_tokens,
+                          int which, cudaStream_t stream) {
   static bool opted_in[64][2] = {};
   static int sm_counts[64] = {};
   int device = 0;
@@ -689,7 +698,7 @@ int launch_chunk_backward(const int* sco, const int* cs, const int* ce, const fl
       static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const T*>(a), static_cast<const T*>(b),
       static_cast<const T*>(bias), static_cast<const T*>(dy), static_cast<T*>(dr), static_cast<T*>(dw),
       static_cast<T*>(dk), static_cast<T*>(dv), static_cast<T*>(da), static_cast<T*>(db), num_sequences, num_heads, items,
-      scale, error_flag);
+      scale, error_flag, metadata_status, (long long)total_tokens * num_heads * kD);
   return check_launch("wkv7_chunk_backward_kernel");
 }
 
@@ -701,15 +710,16 @@ extern "C" int frwkv_wkv7_chunk_backward(
     const float* boundary, const float* boundary_adjoint, const float* state_dot_a, const void* r,
     const void* decay_logits, const void* k, const void* v, const void* a, const void* b, const void* decay_bias,
     const void* grad_output, void* grad_r, void* grad_decay_logits, void* grad_k, void* grad_v, void* grad_a, void* grad_b,
-    int32_t* error_flag, int num_sequences, int num_chunks, int num_heads, int head_size, int io_dtype, float scale,
-    frwkv_stream_t stream) {
+    int32_t* error_flag, const int32_t* metadata_status, int total_tokens, int num_sequences, int num_chunks,
+    int num_heads, int head_size, int io_dtype, float scale, frwkv_stream_t stream) {
   using namespace frwkv;
   clear_error();
   FRWKV_REQUIRE(seq_chunk_offsets && chunk_starts && chunk_ends && final_state && boundary && boundary_adjoint &&
                     state_dot_a && r && decay_logits && k && v && a && b && grad_output && grad_r && grad_decay_logits &&
                     grad_k && grad_v && grad_a && grad_b,
                 "wkv7_chunk_backward: null pointer argument");
-  FRWKV_REQUIRE(num_sequences > 0 && num_chunks > 0 && num_heads > 0, "wkv7_chunk_backward: sizes must be positive");
+  FRWKV_REQUIRE(num_sequences > 0 && num_chunks > 0 && num_heads > 0 && total_tokens > 0,
+                "wkv7_chunk_backward: sizes must be positive");
   if (head_size != 64)
     return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_chunk_backward: head size %d is not built (only 64)", head_size);
   FRWKV_REQUIRE((long long)num_chunks * num_heads <= 0x7fffffffLL, "wkv7_chunk_backward: too many (chunk, head) pairs");
@@ -718,11 +728,13 @@ extern "C" int frwkv_wkv7_chunk_backward(
     return launch_chunk_backward<__nv_bfloat16>(seq_chunk_offsets, chunk_starts, chunk_ends, final_state, boundary,
                                                 boundary_adjoint, state_dot_a, r, decay_logits, k, v, a, b, decay_bias,
                                                 grad_output, grad_r, grad_decay_logits, grad_k, grad_v, grad_a, grad_b,
-                                                num_sequences, num_chunks, num_heads, scale, error_flag, 0, s);
+                                                num_sequences, num_chunks, num_heads, scale, error_flag, metadata_status,
+                                                total_tokens, 0, s);
   if (io_dtype == FRWKV_DTYPE_FP16)
     return launch_chunk_backward<__half>(seq_chunk_offsets, chunk_starts, chunk_ends, final_state, boundary,
                                          boundary_adjoint, state_dot_a, r, decay_logits, k, v, a, b, decay_bias,
                                          grad_output, grad_r, grad_decay_logits, grad_k, grad_v, grad_a, grad_b,
-                                         num_sequences, num_chunks, num_heads, scale, error_flag, 1, s);
+                                         num_sequences, num_chunks, num_heads, scale, error_flag, metadata_status,
+                                         total_tokens, 1, s);
   return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_chunk_backward: token tensors must be float16 or bfloat16");
 }

@@ -630,8 +630,9 @@ extern "C" int frwkv_wkv7_adjoint_scan(const int32_t* seq_chunk_offsets, const i
                                        const int32_t* chunk_ends, const void* r, const void* decay_logits,
                                        const void* a, const void* b, const void* decay_bias, const void* grad_output,
                                        float* grad_state, float* boundary_adjoint, float* khat, int32_t* error_flag,
-                                       int total_tokens, int num_sequences, int num_chunks, int num_heads,
-                                       int head_size, int io_dtype, float scale, frwkv_stream_t stream) {
+                                       const int32_t* metadata_status, int total_tokens, int num_sequences,
+                                       int num_chunks, int num_heads, int head_size, int io_dtype, float scale,
+                                       frwkv_stream_t stream) {
   using namespace frwkv;
   clear_error();
   FRWKV_REQUIRE(seq_chunk_offsets && chunk_starts && chunk_ends && r && decay_logits && a && b && grad_output &&
@@ -650,7 +651,7 @@ extern "C" int frwkv_wkv7_adjoint_scan(const int32_t* seq_chunk_offsets, const i
                                                  static_cast<const T*>(a), static_cast<const T*>(b),
                                                  static_cast<const T*>(decay_bias), khat, rows, num_heads, scale);
     if (int rc = check_launch("adjoint_key_kernel")) return rc;
-    return launch_fused<T, true>(seq_chunk_offsets, chunk_starts, chunk_ends, nullptr, nullptr, grad_state, r,
+    return launch_fused<T, true>(seq_chunk_offsets, chunk_starts, chunk_ends, nullptr, metadata_status, grad_state, r,
                                  decay_logits, /*k: unused*/ r, grad_output, /*a=*/b, /*b=*/a, decay_bias, khat, nullptr,
                                  nullptr, boundary_adjoint, nullptr, error_flag, total_tokens, num_sequences, num_heads,
                                  1.0f, 2, s);
@@ -661,7 +662,7 @@ extern "C" int frwkv_wkv7_adjoint_scan(const int32_t* seq_chunk_offsets, const i
                                                  static_cast<const T*>(a), static_cast<const T*>(b),
                                                  static_cast<const T*>(decay_bias), khat, rows, num_heads, scale);
     if (int rc = check_launch("adjoint_key_kernel")) return rc;
-    return launch_fused<T, true>(seq_chunk_offsets, chunk_starts, chunk_ends, nullptr, nullptr, grad_state, r,
+    return launch_fused<T, true>(seq_chunk_offsets, chunk_starts, chunk_ends, nullptr, metadata_status, grad_state, r,
                                  decay_logits, /*k: unused*/ r, grad_output, /*a=*/b, /*b=*/a, decay_bias, khat, nullptr,
                                  nullptr, boundary_adjoint, nullptr, error_flag, total_tokens, num_sequences, num_heads,
                                  1.0f, 3, s);

@@ -56,11 +56,12 @@ __global__ __launch_bounds__(kFwdCols*(D / 64), 1) void train_wide_forward_kerne
     const io_t* __restrict__ k_ptr, const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr,
     const io_t* __restrict__ b_ptr, io_t* __restrict__ y_ptr, float* __restrict__ boundary,
     float* __restrict__ state_dot_a, float* __restrict__ dense_checkpoints, int dense_groups, int num_heads,
-    float scale) {
+    float scale, const int* __restrict__ status) {
   using IO = Io16<io_t>;
   constexpr int kSlabs = D / 64, kThreads = kFwdCols * kSlabs, kColBlocks = D / kFwdCols;
   __shared__ __align__(16) float vec_s[5][D];
   __shared__ float part_s[kSlabs][kFwdCols];
+  if (status != nullptr && status[0] != 0) return;  // bad chunk tables: touch nothing (the host side poisons the outputs)
   const int c = threadIdx.x % kFwdCols, q = threadIdx.x / kFwdCols;
   const int cb = blockIdx.x % kColBlocks;
   const long long seq_head = blockIdx.x / kColBlocks;
@@ -135,8 +136,10 @@ template <typename io_t, int D>
 __global__ __launch_bounds__(kFwdCols*(D / 64), 1) void train_wide_checkpoints_kernel(
     const int* __restrict__ chunk_starts, const int* __restrict__ chunk_ends, const float* __restrict__ boundary,
     const float* __restrict__ state_dot_a, const io_t* __restrict__ w_ptr, const io_t* __restrict__ k_ptr,
-    const io_t* __restrict__ v_ptr, const io_t* __restrict__ b_ptr, float* __restrict__ checkpoints, int num_heads) {
+    const io_t* __restrict__ v_ptr, const io_t* __restrict__ b_ptr, float* __restrict__ checkpoints, int num_heads,
+    const int* __restrict__ status) {
   using IO = Io16<io_t>;
+  if (status != nullptr && status[0] != 0) return;
   constexpr int kSlabs = D / 64, kThreads = kFwdCols * kSlabs, kColBlocks = D / kFwdCols;
   __shared__ __align__(16) float vec_s[5][D];
   const int c = threadIdx.x % kFwdCols, q = threadIdx.x / kFwdCols;
@@ -194,9 +197,10 @@ __global__ __launch_bounds__(D, 1) void train_wide_backward_kernel(
     const io_t* __restrict__ k_ptr, const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr,
     const io_t* __restrict__ b_ptr, const io_t* __restrict__ dy_ptr, const float* __restrict__ grad_final_state,
     io_t* __restrict__ dv_ptr, float* __restrict__ dS0_ptr, float* __restrict__ partials, long long elements,
-    int num_heads, float scale) {
+    int num_heads, float scale, const int* __restrict__ status) {
   using IO = Io16<io_t>;
   constexpr int kBlocks = D / kBwdCols, kRowGroups = D / 4;
+  if (status != nullptr && status[0] != 0) return;
   __shared__ __align__(16) float vec_s[5][D];                    // r, w, k, a, b of the current token
   __shared__ __align__(16) float col_s[3][kBwdCols];             // v, dy, sa of this CTA's columns
   __shared__ __align__(16) float part_dv[kRowGroups][kBwdCols + 4];
@@ -358,8 +362,10 @@ template <typename io_t, int D>
 __global__ void train_wide_reduce_kernel(const float* __restrict__ partials, long long elements,
                                          const io_t* __restrict__ w_ptr, io_t* __restrict__ dr_ptr,
                                          io_t* __restrict__ dw_ptr, io_t* __restrict__ dk_ptr,
-                                         io_t* __restrict__ da_ptr, io_t* __restrict__ db_ptr) {
+                                         io_t* __restrict__ da_ptr, io_t* __restrict__ db_ptr,
+                                         const int* __restrict__ status) {
   using IO = Io16<io_t>;
+  if (status != nullptr && status[0] != 0) return;
   constexpr int kBlocks = D / kBwdCols;
   const long long part_stride = (long long)kBlocks * elements;
   for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < elements;
@@ -387,13 +393,13 @@ template <typename io_t, int D>
 int launch_forward(const int* sco, const int* cs, const int* ce, float* state, const void* r, const void* w,
                    const void* k, const void* v, const void* a, const void* b, void* y, float* boundary, float* sda,
                    float* dense_checkpoints, int dense_groups, int num_sequences, int num_heads, float scale,
-                   cudaStream_t stream) {
+                   const int* status, cudaStream_t stream) {
   const long long blocks = (long long)num_sequences * num_heads * (D / kFwdCols);
   if (blocks > 0x7fffffffLL) return fail(FRWKV_ERR_INVALID_ARGUMENT, "wkv7_train_wide: too many (sequence, head) pairs");
   train_wide_forward_kernel<io_t, D><<<(unsigned)blocks, kFwdCols*(D / 64), 0, stream>>>(
       sco, cs, ce, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w), static_cast<const io_t*>(k),
       static_cast<const io_t*>(v), static_cast<const io_t*>(a), static_cast<const io_t*>(b), static_cast<io_t*>(y),
-      boundary, sda, dense_checkpoints, dense_groups, num_heads, scale);
+      boundary, sda, dense_checkpoints, dense_groups, num_heads, scale, status);
   return check_launch("train_wide_forward_kernel");
 }
 
@@ -402,7 +408,7 @@ int launch_backward(const int* sco, const int* cs, const int* ce, const float* f
                     const float* sda, const void* r, const void* w, const void* k, const void* v, const void* a,
                     const void* b, const void* dy, const float* grad_final_state, void* dr, void* dw, void* dk, void* dv,
                     void* da, void* db, float* dS0, float* workspace, long long total_tokens, int num_sequences,
-                    int num_chunks, int num_heads, float scale, cudaStream_t stream) {
+                    int num_chunks, int num_heads, float scale, const int* status, cudaStream_t stream) {
   const long long DD = (long long)D * D;
   const long long elements = total_tokens * num_heads * D;
   float* checkpoints = workspace;                                       // [Cn][3][H][D][D]
@@ -413,20 +419,20 @@ int launch_backward(const int* sco, const int* cs, const int* ce, const float* f
     return fail(FRWKV_ERR_INVALID_ARGUMENT, "wkv7_train_wide: too many (chunk, head) pairs");
   train_wide_checkpoints_kernel<io_t, D><<<(unsigned)cp_blocks, kFwdCols*(D / 64), 0, stream>>>(
       cs, ce, boundary, sda, static_cast<const io_t*>(w), static_cast<const io_t*>(k), static_cast<const io_t*>(v),
-      static_cast<const io_t*>(b), checkpoints, num_heads);
+      static_cast<const io_t*>(b), checkpoints, num_heads, status);
   int rc = check_launch("train_wide_checkpoints_kernel");
   if (rc != FRWKV_OK) return rc;
   train_wide_backward_kernel<io_t, D><<<(unsigned)bw_blocks, D, 0, stream>>>(
       sco, cs, ce, final_state, boundary, checkpoints, sda, static_cast<const io_t*>(r), static_cast<const io_t*>(w),
       static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),
       static_cast<const io_t*>(b), static_cast<const io_t*>(dy), grad_final_state, static_cast<io_t*>(dv), dS0, partials,
-      elements, num_heads, scale);
+      elements, num_heads, scale, status);
   rc = check_launch("train_wide_backward_kernel");
   if (rc != FRWKV_OK) return rc;
   const long long want = (elements + 255) / 256;
   train_wide_reduce_kernel<io_t, D><<<(unsigned)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>(
       partials, elements, static_cast<const io_t*>(w), static_cast<io_t*>(dr), static_cast<io_t*>(dw),
-      static_cast<io_t*>(dk), static_cast<io_t*>(da), static_cast<io_t*>(db));
+      static_cast<io_t*>(dk), static_cast<io_t*>(da), static_cast<io_t*>(db), status);
   return check_launch("train_wide_reduce_kernel");
 }
 
@@ -437,9 +443,9 @@ extern "C" int frwkv_wkv7_train_wide_forward(const int32_t* seq_chunk_offsets, c
                                              const int32_t* chunk_ends, float* state, const void* r,
                                              const void* decay_logits, const void* k, const void* v, const void* a,
                                              const void* b, void* y, float* boundary, float* state_dot_a,
-                                             float* dense_checkpoints, int dense_groups, int num_sequences,
-                                             int num_heads, int head_size, int io_dtype, float scale,
-                                             frwkv_stream_t stream) {
+                                             float* dense_checkpoints, int dense_groups,
+                                             const int32_t* metadata_status, int num_sequences, int num_heads,
+                                             int head_size, int io_dtype, float scale, frwkv_stream_t stream) {
   using namespace frwkv;
   clear_error();
   FRWKV_REQUIRE(seq_chunk_offsets && chunk_starts && chunk_ends && state && r && decay_logits && k && v && a && b && y,
@@ -449,7 +455,8 @@ extern "C" int frwkv_wkv7_train_wide_forward(const int32_t* seq_chunk_offsets, c
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define FRWKV_WF(T, DD)                                                                                               \
   return launch_forward<T, DD>(seq_chunk_offsets, chunk_starts, chunk_ends, state, r, decay_logits, k, v, a, b, y,    \
-                               boundary, state_dot_a, dense_checkpoints, dense_groups, num_sequences, num_heads, scale, s)
+                               boundary, state_dot_a, dense_checkpoints, dense_groups, num_sequences, num_heads, scale,      \
+                               metadata_status, s)
   if (io_dtype == FRWKV_DTYPE_BF16 && head_size == 128) FRWKV_WF(__nv_bfloat16, 128);
   if (io_dtype == FRWKV_DTYPE_BF16 && head_size == 256) FRWKV_WF(__nv_bfloat16, 256);
   if (io_dtype == FRWKV_DTYPE_FP16 && head_size == 128) FRWKV_WF(__half, 128);
@@ -471,8 +478,8 @@ extern "C" int frwkv_wkv7_train_wide_backward(
     const float* boundary, const float* state_dot_a, const void* r, const void* decay_logits, const void* k,
     const void* v, const void* a, const void* b, const void* grad_output, const float* grad_final_state, void* grad_r,
     void* grad_decay_logits, void* grad_k, void* grad_v, void* grad_a, void* grad_b, float* grad_initial_state,
-    float* workspace, long long total_tokens, int num_sequences, int num_chunks, int num_heads, int head_size,
-    int io_dtype, float scale, frwkv_stream_t stream) {
+    float* workspace, const int32_t* metadata_status, long long total_tokens, int num_sequences, int num_chunks,
+    int num_heads, int head_size, int io_dtype, float scale, frwkv_stream_t stream) {
   using namespace frwkv;
   clear_error();
   FRWKV_REQUIRE(seq_chunk_offsets && chunk_starts && chunk_ends && final_state && boundary && state_dot_a && r &&
@@ -485,7 +492,7 @@ extern "C" int frwkv_wkv7_train_wide_backward(
   return launch_backward<T, DD>(seq_chunk_offsets, chunk_starts, chunk_ends, final_state, boundary, state_dot_a, r,    \
                                 decay_logits, k, v, a, b, grad_output, grad_final_state, grad_r, grad_decay_logits,    \
                                 grad_k, grad_v, grad_a, grad_b, grad_initial_state, workspace, total_tokens,           \
-                                num_sequences, num_chunks, num_heads, scale, s)
+                                num_sequences, num_chunks, num_heads, scale, metadata_status, s)
   if (io_dtype == FRWKV_DTYPE_BF16 && head_size == 128) FRWKV_WB(__nv_bfloat16, 128);
   if (io_dtype == FRWKV_DTYPE_BF16 && head_size == 256) FRWKV_WB(__nv_bfloat16, 256);
   if (io_dtype == FRWKV_DTYPE_FP16 && head_size == 128) FRWKV_WB(__half, 128);

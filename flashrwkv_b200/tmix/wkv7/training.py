@@ -88,15 +88,16 @@ class _StateTune(torch.autograd.Function):
 _validated_tables: list = []
 
 
-def _validate_chunk_tables(sco, cs, ce, total_tokens: int) -> None:
-    """One device-to-host read for every property the kernels rely on: chunk bounds inside [0, N], at most MAX_CHUNK
-    tokens per chunk, chunks of a sequence contiguous and in order, offsets monotone from 0 to the chunk count.  A
-    table that fails would drive out-of-range reads and writes on the device, so it is refused here."""
+def _validate_chunk_tables(sco, cs, ce, total_tokens: int) -> bool:
+    """One device-to-host read for every property the kernels rely on: chunk bounds inside [0, N], chunks of a
+    sequence contiguous and in order, offsets monotone from 0 to the chunk count.  A table that fails would drive
+    out-of-range reads and writes on the device, so it is refused here.  Returns True when some chunk holds more
+    than MAX_CHUNK tokens (the caller then splits those chunks; the kernels work on at most MAX_CHUNK)."""
     key = (sco, cs, ce)
     stamp = (sco._version, cs._version, ce._version, int(total_tokens))
     for entry in _validated_tables:
         if all(a is b for a, b in zip(entry[0], key)) and entry[1] == stamp:
-            return  # these very tensors, unmodified since, passed before (a training loop reuses its tables)
+            return entry[2]  # these very tensors, unmodified since, passed before (a training loop reuses its tables)
     cn = cs.numel()
     lens = ce - cs
     starts = torch.zeros(cn + 1, dtype=torch.bool, device=cs.device)
@@ -107,16 +108,49 @@ def _validate_chunk_tables(sco, cs, ce, total_tokens: int) -> None:
     if cn > 1:
         code = code | ((cs[1:] != ce[:-1]) & ~starts[1:cn]).any().int() * 128
     code = int(code.item())
-    if code & 1:
-        raise ValueError(f"training chunks may hold at most {MAX_CHUNK} tokens")
     if code & (2 | 4 | 8):
         raise ValueError("chunk token bounds must satisfy 0 <= start <= end <= total_tokens")
     if code & (16 | 32 | 64):
         raise ValueError("sequence_chunk_offsets must rise from 0 to the number of chunks")
     if code & 128:
         raise ValueError("the chunks of a sequence must be contiguous and in token order")
-    _validated_tables.append((key, stamp))  # holds the tensors, so their addresses cannot be recycled meanwhile
+    _validated_tables.append((key, stamp, bool(code & 1)))  # holds the tensors: their addresses cannot be recycled
     del _validated_tables[:-8]
+    return bool(code & 1)
+
+
+_refined_tables: list = []
+
+
+def _refine_chunk_tables(sco, cs, ce):
+    """Chunk tables whose chunks hold at most MAX_CHUNK tokens: every longer chunk of the caller is cut into pieces.
+    Returns (sco, cs, ce, first) where first[c] is the index of the first piece of the caller's chunk c (the state at
+    its start is the boundary the caller asked for).  Remembered per table identity and version."""
+    key = (sco, cs, ce)
+    stamp = (sco._version, cs._version, ce._version)
+    for entry in _refined_tables:
+        if all(a is b for a, b in zip(entry[0], key)) and entry[1] == stamp:
+            return entry[2]
+    h_sco, h_cs, h_ce = (t.cpu().tolist() for t in (sco, cs, ce))
+    starts, ends, first, offsets = [], [], [], [0]
+    for s in range(len(h_sco) - 1):
+        for c in range(h_sco[s], h_sco[s + 1]):
+            first.append(len(starts))
+            a, b = h_cs[c], h_ce[c]
+            if b <= a:
+                starts.append(a)
+                ends.append(b)
+            while a < b:
+                e = min(a + MAX_CHUNK, b)
+                starts.append(a)
+                ends.append(e)
+                a = e
+        offsets.append(len(starts))
+    mk = lambda x, dt=torch.int32: torch.tensor(x, device=cs.device, dtype=dt)  # noqa: E731
+    refined = (mk(offsets), mk(starts), mk(ends), mk(first, torch.int64))
+    _refined_tables.append((key, stamp, refined))
+    del _refined_tables[:-8]
+    return refined
 
 
 def _check_cuda_contiguous(tensor, name):
@@ -166,7 +200,12 @@ def statetune_recurrent_fp32io16(initial_state, sequence_chunk_offsets, chunk_to
         raise ValueError("sequence_chunk_offsets must have shape [B+1]")
     if not isinstance(scale, (int, float)) or not math.isfinite(float(scale)):
         raise ValueError("scale must be finite")
-    _validate_chunk_tables(sequence_chunk_offsets, chunk_token_starts, chunk_token_ends, r.shape[0])
+    if _validate_chunk_tables(sequence_chunk_offsets, chunk_token_starts, chunk_token_ends, r.shape[0]):
+        # chunks longer than the kernels' 64 tokens: run on pieces, hand back the boundaries the caller's table names
+        sco, cs, ce, first = _refine_chunk_tables(sequence_chunk_offsets, chunk_token_starts, chunk_token_ends)
+        output, final_state, boundary, state_dot_a = _StateTune.apply(initial_state, sco, cs, ce, r, decay_logits, k, v,
+                                                                      a, b, float(scale))
+        return output, final_state, boundary.index_select(0, first), state_dot_a
     return _StateTune.apply(initial_state, sequence_chunk_offsets, chunk_token_starts, chunk_token_ends, r,
                             decay_logits, k, v, a, b, float(scale))
 

@@ -68,6 +68,18 @@ int frwkv_validate_recurrent_metadata(const int32_t* cu_seqlens, const int32_t* 
                                       frwkv_stream_t stream);
 
 /*
+ * Validate the chunk tables of the training operators on the device: status[0] (int32, cleared first) receives
+ * FRWKV_META_INVALID_RANGE if a chunk lies outside [0, total_tokens], holds more than max_chunk tokens or does not
+ * start where its predecessor in the same sequence ends, FRWKV_META_INVALID_ENDPOINT if the offsets do not rise from 0
+ * to num_chunks.  Kernels given this word as metadata_status fail closed (NaN outputs, states untouched), so a bad
+ * caller-built table cannot drive out-of-range accesses.  The reference validates its RL chunk tables on the host
+ * (csrc/sm90/rl_infctx/wkv7/rl_infctx_chunk_fp32io16_forward.cpp:100-133).
+ */
+int frwkv_validate_chunk_tables(const int32_t* seq_chunk_offsets, const int32_t* chunk_starts,
+                                const int32_t* chunk_ends, int num_sequences, int num_chunks, int total_tokens,
+                                int max_chunk, int32_t* status, frwkv_stream_t stream);
+
+/*
  * WKV7 recurrence over packed sequences with an fp32 state pool updated in place.
  * Replaces recurrent_fp32_from_decay_logits_cuda
  * (csrc/sm120/tmix/wkv7/infer_recurrent_fp32io16_forward_varlen.cu:448-508).
@@ -184,14 +196,15 @@ int frwkv_wkv7_chunk_fused_fp32io16_forward(
  * csrc/sm90/tmix/wkv7/pretrain_recurrent_bf16_forward.cu:222-282).
  *   grad_output io16 [N,H,64]; grad_state fp32 [B,H,64,64]: in = gradient of the final state (zeros if none), out =
  *   gradient of the initial state;  boundary_adjoint fp32 [Cn,H,64,64]: receives dL/dS at the END of every chunk;
- *   khat fp32 [N,H,64]: scratch for the modified keys scale * (w * r + (b . r) a).
+ *   khat fp32 [N,H,64]: scratch for the modified keys scale * (w * r + (b . r) a);
+ *   metadata_status (may be NULL): the word of frwkv_validate_chunk_tables; non-zero = the scan does nothing.
  */
 int frwkv_wkv7_adjoint_scan(const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends,
                             const void* r, const void* decay_logits, const void* a, const void* b,
                             const void* decay_bias, const void* grad_output, float* grad_state,
-                            float* boundary_adjoint, float* khat, int32_t* error_flag, int total_tokens,
-                            int num_sequences, int num_chunks, int num_heads, int head_size, int io_dtype, float scale,
-                            frwkv_stream_t stream);
+                            float* boundary_adjoint, float* khat, int32_t* error_flag,
+                            const int32_t* metadata_status, int total_tokens, int num_sequences, int num_chunks,
+                            int num_heads, int head_size, int io_dtype, float scale, frwkv_stream_t stream);
 
 /*
  * Second stage of the chunked backward: the six token gradients of every (chunk, head), chunk-parallel on the tensor
@@ -202,15 +215,16 @@ int frwkv_wkv7_adjoint_scan(const int32_t* seq_chunk_offsets, const int32_t* chu
  *   final_state fp32 [B,H,64,64], boundary fp32 [Cn,H,64,64], state_dot_a fp32 [N,H,64]: outputs of the forward;
  *   boundary_adjoint fp32 [Cn,H,64,64]: output of frwkv_wkv7_adjoint_scan; grad_output io16 [N,H,64];
  *   grad_r .. grad_b io16 [N,H,64] (grad_decay_logits is with respect to the raw decay logits).
- * On a failed wait the gradients of the affected chunks are NaN and *error_flag is non-zero.
+ * On a failed wait the gradients of the affected chunks are NaN and *error_flag is non-zero.  metadata_status (may be
+ * NULL): the word of frwkv_validate_chunk_tables; non-zero = all gradients NaN, nothing else touched.
  */
 int frwkv_wkv7_chunk_backward(
     const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends, const float* final_state,
     const float* boundary, const float* boundary_adjoint, const float* state_dot_a, const void* r,
     const void* decay_logits, const void* k, const void* v, const void* a, const void* b, const void* decay_bias,
     const void* grad_output, void* grad_r, void* grad_decay_logits, void* grad_k, void* grad_v, void* grad_a, void* grad_b,
-    int32_t* error_flag, int num_sequences, int num_chunks, int num_heads, int head_size, int io_dtype, float scale,
-    frwkv_stream_t stream);
+    int32_t* error_flag, const int32_t* metadata_status, int total_tokens, int num_sequences, int num_chunks,
+    int num_heads, int head_size, int io_dtype, float scale, frwkv_stream_t stream);
 
 /*
  * The same chunked forward for hosts that may not allocate device memory (servers that gave the whole GPU to
@@ -288,6 +302,8 @@ int frwkv_wkv7_backward(const int32_t* seq_chunk_offsets, const int32_t* chunk_s
  *     state (fp32 [B,H,D,D], may be NULL) from the forward's final_state, boundary and state_dot_a; grad_output
  *     io16 [N,H,D] (NULL = zero), grad_final_state fp32 [B,H,D,D] (NULL = zero); workspace of
  *     frwkv_wkv7_train_wide_workspace_floats(...) floats (16-token checkpoints and per-column-block partial sums).
+ *   metadata_status (may be NULL): the word of frwkv_validate_chunk_tables; when it is non-zero the kernels return
+ *     without reading or writing anything (outputs stay as they were: the caller poisons them).
  * Replace forward_kernel_split64 / backward_kernel_split64 / the tiled D = 256 backward
  * (csrc/sm90/tmix/wkv7/pretrain_recurrent_bf16_forward.cu:110-150,293-478) and the D = 128 / 256 instantiations of
  * the StateTune kernels (csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_backward.cu:317-502).
@@ -295,16 +311,17 @@ int frwkv_wkv7_backward(const int32_t* seq_chunk_offsets, const int32_t* chunk_s
 int frwkv_wkv7_train_wide_forward(const int32_t* seq_chunk_offsets, const int32_t* chunk_starts,
                                   const int32_t* chunk_ends, float* state, const void* r, const void* decay_logits,
                                   const void* k, const void* v, const void* a, const void* b, void* y, float* boundary,
-                                  float* state_dot_a, float* dense_checkpoints, int dense_groups, int num_sequences,
-                                  int num_heads, int head_size, int io_dtype, float scale, frwkv_stream_t stream);
+                                  float* state_dot_a, float* dense_checkpoints, int dense_groups,
+                                  const int32_t* metadata_status, int num_sequences, int num_heads, int head_size,
+                                  int io_dtype, float scale, frwkv_stream_t stream);
 size_t frwkv_wkv7_train_wide_workspace_floats(long long total_tokens, int num_chunks, int num_heads, int head_size);
 int frwkv_wkv7_train_wide_backward(
     const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends, const float* final_state,
     const float* boundary, const float* state_dot_a, const void* r, const void* decay_logits, const void* k,
     const void* v, const void* a, const void* b, const void* grad_output, const float* grad_final_state, void* grad_r,
     void* grad_decay_logits, void* grad_k, void* grad_v, void* grad_a, void* grad_b, float* grad_initial_state,
-    float* workspace, long long total_tokens, int num_sequences, int num_chunks, int num_heads, int head_size,
-    int io_dtype, float scale, frwkv_stream_t stream);
+    float* workspace, const int32_t* metadata_status, long long total_tokens, int num_sequences, int num_chunks,
+    int num_heads, int head_size, int io_dtype, float scale, frwkv_stream_t stream);
 
 /*
  * TMix token shift: out[j] = x + (prev - x) * mix_j for the six mix vectors (r, w, k, v, a, g); prev is the previous

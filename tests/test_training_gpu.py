@@ -247,7 +247,6 @@ def test_chunk_tables_are_validated_before_any_launch():
     good = (i32([0, 1, 2]), i32([0, 30]), i32([30, 40]))
     F.statetune_recurrent_fp32io16(S0, *good, *toks)
     bad = {
-        "at most 64": (i32([0, 1, 2]), i32([0, 0]), i32([0, 70])),
         "0 <= start <= end <= total_tokens": (i32([0, 1, 2]), i32([0, 30]), i32([30, 41])),
         "0 <= start <= end": (i32([0, 1, 2]), i32([5, 30]), i32([3, 40])),
         "rise from 0": (i32([0, 2, 1]), i32([0, 30]), i32([30, 40])),
@@ -280,3 +279,68 @@ def test_device_error_words_are_kept_and_zero_after_clean_runs():
     for stage in ("wkv7_chunk_forward", "wkv7_chunk_backward", "tmix_linear"):
         assert flags.get(stage) == 0, (stage, flags)
     F.check_device_error_flags()
+
+
+def test_chunks_longer_than_64_tokens_are_split_internally(oracle):
+    """Caller-built tables with chunks of 100 and 150 tokens (the reference accepts any chunk length): outputs,
+    boundaries named by the caller's table and all seven gradients against the oracle."""
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+
+    H, D = 2, 64
+    lengths = (250, 70)
+    N = sum(lengths)
+    toks = synthetic.wkv7_inputs(N, H, D, seed=77)
+    S0 = synthetic.state_pool(2, H, D, seed=78)
+    sco = torch.tensor([0, 2, 3], dtype=torch.int32)
+    cs = torch.tensor([0, 100, 250], dtype=torch.int32)
+    ce = torch.tensor([100, 250, 320], dtype=torch.int32)
+    cu = torch.tensor([0, 250, 320], dtype=torch.int32)
+    gen = torch.Generator().manual_seed(5)
+    dy = torch.randn(N, H, D, generator=gen).to(torch.bfloat16)
+    fwd = oracle.forward(*toks, state_pool=S0, cu_seqlens=cu, chunks=(sco, cs, ce), want_state_dot_a=True)
+    want = oracle.backward(*toks, initial_state=S0, cu_seqlens=cu, grad_output=dy)
+    dS0 = S0.cuda().requires_grad_()
+    dtoks = [t.cuda().requires_grad_() for t in toks]
+    out = F.statetune_recurrent_fp32io16(dS0, sco.cuda(), cs.cuda(), ce.cuda(), *dtoks)
+    assert out[2].shape == (3, H, D, D)
+    assert rel_rmse(out[0].detach().float().cpu(), fwd["y"]) <= 8e-3
+    assert rel_rmse(out[1].detach().cpu(), fwd["state_pool"]) <= 1e-3
+    assert rel_rmse(out[2].detach().cpu(), fwd["boundary"]) <= 1e-3
+    assert rel_rmse(out[3].detach().cpu(), fwd["state_dot_a"]) <= 3e-3
+    out[0].backward(dy.cuda())
+    for t, name in zip(dtoks, ("r", "decay_logits", "k", "v", "a", "b")):
+        assert rel_rmse(t.grad.float().cpu(), want[name]) <= 8e-3, name
+    assert rel_rmse(dS0.grad.cpu(), want["initial_state"]) <= 8e-3
+
+
+@pytest.mark.parametrize("head_size", [64, 128])
+def test_native_training_entries_fail_closed_on_bad_chunk_tables(head_size):
+    """The reference-named native entries are reached with caller-built tables (the reference's wrapper checks shapes
+    only).  A table with a chunk of 70 tokens, or one that ends beyond the token count, gets its verdict on the device:
+    outputs and gradients read as NaN, the state keeps its value, nothing is accessed out of range, no host sync."""
+    from flashrwkv_b200 import synthetic
+    from flashrwkv_b200._ext import extension
+
+    C_ = extension()
+    H, D, N = 1, head_size, 100
+    toks = [t.cuda() for t in synthetic.wkv7_inputs(N, H, D, seed=5)]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")  # noqa: E731
+    for cs, ce in (([0, 70], [70, 100]), ([0, 50], [50, 164])):
+        sco = i32([0, 2])
+        state = synthetic.state_pool(1, H, D, seed=6, device="cuda")
+        before = state.clone()
+        out = torch.zeros_like(toks[3])
+        boundary = torch.zeros(2, H, D, D, device="cuda")
+        sda = torch.zeros(N, H, D, device="cuda")
+        C_.statetune_recurrent_fp32io16_forward(sco, i32(cs), i32(ce), state, *toks, out, boundary, sda, 1.0)
+        torch.cuda.synchronize()
+        assert torch.isnan(out.float()).all()
+        assert torch.equal(state, before)
+        grads = [torch.zeros_like(toks[0]) for _ in range(6)]
+        dS0 = torch.zeros_like(state)
+        C_.statetune_recurrent_fp32io16_backward(sco, i32(cs), i32(ce), state, *toks, sda, torch.ones_like(toks[0]), None,
+                                                 boundary, *grads, dS0, 1.0)
+        torch.cuda.synchronize()
+        for g in grads:
+            assert torch.isnan(g.float()).all()
