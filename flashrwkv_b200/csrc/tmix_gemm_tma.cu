@@ -253,8 +253,19 @@ __global__ __launch_bounds__(Cfg<BN, kShift>::kThreads, 1) void linear_tma_kerne
             const int n = n0 + c0 + jj;
             if (n < pr.n) {  // n and N are multiples of 8
               float o[8];
+              if (pr.epilogue == 1) {  // value-residual gate, its three operands as 16-byte pieces
+                const long long at = (long long)m * pr.n + n;
+                float vv[8], vf[8], z0[8];
+                unpack8<io_t>(*reinterpret_cast<const uint4*>(static_cast<const io_t*>(pr.v) + at), vv);
+                unpack8<io_t>(*reinterpret_cast<const uint4*>(static_cast<const io_t*>(pr.v_first) + at), vf);
+                unpack8<io_t>(*reinterpret_cast<const uint4*>(static_cast<const io_t*>(pr.v0) + n), z0);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) o[e] = finish<io_t>(pr, __uint_as_float(u[jj + e]), m, n + e);
+                for (int e = 0; e < 8; ++e)
+                  o[e] = fmaf(vf[e] - vv[e], 1.f / (1.f + __expf(-(z0[e] + __uint_as_float(u[jj + e])))), vv[e]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(u[jj + e]);
+              }
               *reinterpret_cast<uint4*>(y + (long long)m * pr.n + n) =
                   make_uint4(IO::pack(o[0], o[1]), IO::pack(o[2], o[3]), IO::pack(o[4], o[5]), IO::pack(o[6], o[7]));
             }
