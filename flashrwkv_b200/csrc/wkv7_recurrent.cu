@@ -29,6 +29,13 @@ int launch_recurrent_wide(const int* cu, const int* idx, const int* status, cons
                           const void* bias, void* y, float* y32, int total_tokens, int num_sequences, int num_heads,
                           int head_size, int io_dtype, float scale, cudaStream_t stream);
 namespace {
+// Decode batches with more (sequence, head) tiles than this take the bulk-copy ring kernel, smaller ones the register
+// kernel.  Measured per launch in a CUDA graph (H = 32, register / ring): 1024 tiles 6.9 / 8.5 us, 2048 10.3 / 12.2,
+// 3072 14.4 / 16.5, 4096 20.8 / 21.2, 5120 30.5 / 27.6, 6144 38.0 / 32.4, 8192 50.1 / 43.5.  Up to 4096 tiles the
+// state (64 MB) stays in the 126 MB L2 between steps and the ring's fill and drain is pure overhead; beyond that the
+// step streams from HBM and the ring's deeper queue of copies wins.
+constexpr long long kRingMinTiles = 4608;
+
 
 constexpr int kD = 64;
 constexpr int kWarpsPerBlock = 4;
@@ -599,7 +606,7 @@ extern "C" int frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex(
   // decode (one token per sequence, known from the caller's validated metadata) with enough tiles to keep a
   // persistent grid busy takes the bulk-copy pipelined kernel; everything else the register kernel
   const bool decode = max_seqlen == 1 && total_tokens == num_sequences &&
-                      (long long)num_sequences * num_heads >= 1024 && (long long)num_sequences * num_heads <= 0x7fffffffLL;
+                      (long long)num_sequences * num_heads >= kRingMinTiles && (long long)num_sequences * num_heads <= 0x7fffffffLL;
   if (decode && io_dtype == FRWKV_DTYPE_BF16)
     return launch_decode<__nv_bfloat16>(state_indices, metadata_status, state_pool, r, decay_logits, k, v, a, b,
                                         decay_bias, y, y_fp32, num_sequences, num_heads, scale, flags & 1, s);

@@ -354,13 +354,14 @@ def test_head_sizes_128_and_256_vs_oracle(oracle, D, dtype):
     assert torch.equal(d_pool[[1, 3]].cpu(), pool[[1, 3]])
 
 
-def test_wait_timeout_bit_in_the_status_word_fails_closed():
+@pytest.mark.parametrize("B", [48, 160])  # 1536 tiles: the register kernel; 5120 tiles: the bulk-copy ring kernel
+def test_wait_timeout_bit_in_the_status_word_fails_closed(B):
     """A decode kernel whose bounded wait ran out leaves FRWKV_META_WAIT_TIMEOUT (16) in the ticket's status word;
     from then on every call with that ticket must behave like a call with bad metadata: NaN outputs, pool untouched."""
     import flashrwkv_b200 as F
     from flashrwkv_b200 import synthetic
 
-    B, H, D = 48, 32, 64  # 1536 tiles: the bulk-copy ring kernel
+    H, D = 32, 64
     toks = [t.cuda() for t in synthetic.wkv7_inputs(B, H, D, seed=3)]
     cu, idx = (t.cuda() for t in synthetic.equal_length_metadata(B, 1))
     pool = synthetic.state_pool(B, H, D, seed=4, device="cuda")
