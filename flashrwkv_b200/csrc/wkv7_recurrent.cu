@@ -186,7 +186,24 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
     long long output_elements, float scale) {
   using IO = Io16<io_t>;
   chain_begin();
-  if (!kReplay && metadata_status != nullptr && metadata_status[0] != 0) {
+  const int lane = threadIdx.x & 31;
+  const long long unit_raw = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const bool active = unit_raw < num_units;
+  const long long unit = active ? unit_raw : 0;
+  const int vhalf = (int)(unit & 1);
+  const long long seq_head = unit >> 1;
+  const int head = (int)(seq_head % num_heads);
+  const int seq = (int)(seq_head / num_heads);
+  const int kg = lane >> 3, vq = lane & 7;
+  const int row0 = kg * 16;
+  const int col0 = vhalf * 32 + vq * 4;
+  // the status word and the sequence's metadata are requested together (one round trip, not two in a row: in a decode
+  // step of a few hundred tiles the kernel is a chain of dependent loads)
+  const int status0 = (!kReplay && metadata_status != nullptr) ? metadata_status[0] : 0;
+  const int t_begin = cu_seqlens[seq];
+  const int t_end = kReplay ? state_indices[seq] : cu_seqlens[seq + 1];
+  const int slot = kReplay ? seq : state_indices[seq];
+  if (status0 != 0) {
     // fail closed: NaN output, state untouched
     const io_t nan16 = IO::store(quiet_nan());
     for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < output_elements;
@@ -196,20 +213,7 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
     }
     return;
   }
-  const int lane = threadIdx.x & 31;
-  const long long unit = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  if (unit >= num_units) return;
-  const int vhalf = (int)(unit & 1);
-  const long long seq_head = unit >> 1;
-  const int head = (int)(seq_head % num_heads);
-  const int seq = (int)(seq_head / num_heads);
-  const int kg = lane >> 3, vq = lane & 7;
-  const int row0 = kg * 16;
-  const int col0 = vhalf * 32 + vq * 4;
-
-  const int t_begin = cu_seqlens[seq];
-  const int t_end = kReplay ? state_indices[seq] : cu_seqlens[seq + 1];
-  const int slot = kReplay ? seq : state_indices[seq];
+  if (!active) return;
 
   float* sbase = state_pool + ((long long)slot * num_heads + head) * (kD * kD) + row0 * kD + col0;
   float4 s[16];
