@@ -33,10 +33,10 @@ __device__ __forceinline__ bool wait_warp(uint64_t* mbar, uint32_t parity, bool 
 }
 
 // T' = (I - A)^-1 - I for the strictly lower triangular 64 x 64 A in the scratch, in fp32, by 16 x 16 blocks:
-// T_ii = (I - A_ii)^-1 (one thread per column, 16 right-looking steps), then one block anti-diagonal at a time
-// T_ib = T_ii * sum_{k=b..i-1} A_ik T_kb.  A block product is done by 32 threads with 2 x 4 register tiles and
-// 16-byte operand reads (rows of A and of T_ii, four adjacent columns of T and W).  Ends with T' rounded to tf32 in
-// rows 0..63 of the tile and zeros in rows 64..127 (the second operand half of MMA 3).  Contains barriers: every
+// T_ii = (I - A_ii)^-1 (one thread per column, 16 right-looking steps), then the off-diagonal blocks in two levels
+// (inside the 32 x 32 halves, then the 32 x 32 block below them).  A block product is done by 32 threads with 2 x 4
+// register tiles and 16-byte operand reads (rows of A and of T, four adjacent columns of T and W).  Ends with T'
+// rounded to tf32 in rows 0..63 of the tile and zeros in rows 64..127 (the second operand half of MMA 3).  Contains barriers: every
 // thread calls it.
 __device__ __forceinline__ void fma_2x4(float (&acc)[2][4], const float4& a0, const float4& a1, const float4& t0,
                                         const float4& t1, const float4& t2, const float4& t3) {
@@ -74,50 +74,78 @@ __device__ __forceinline__ void inverse_blocked(unsigned char* smem, int tid) {
   }
   __syncthreads();
   const int warp = tid >> 5, sub = tid & 31;
-  const int rp = sub >> 2, cq = sub & 3;  // rows 2 rp, 2 rp + 1 and columns 4 cq .. 4 cq + 3 of a block
-#pragma unroll 1
-  for (int dg = 1; dg < 4; ++dg) {
-    // Block (ib, bb) of this anti-diagonal needs sum_{kb = bb .. ib-1} A_{ib,kb} T_{kb,bb}: one warp per (block, kb)
-    // term (3, 4 and 3 warps for dg = 1, 2, 3); the term goes to W rows 16 (kb + 1) .., columns of block bb.
-    int bb = -1, kb = 0;
-    if (dg == 1) { if (warp < 3) { bb = warp; kb = warp; } }
-    else if (dg == 2) { if (warp < 4) { bb = warp >> 1; kb = bb + (warp & 1); } }
-    else { if (warp < 3) { bb = 0; kb = warp; } }
-    if (bb >= 0) {
-      const int ib = bb + dg, row = 16 * ib + 2 * rp, col = 16 * bb + 4 * cq;
-      float acc[2][4] = {};
+  const int rp = sub >> 2, cq = sub & 3;  // rows 2 rp, 2 rp + 1 and columns 4 cq .. 4 cq + 3 of a 16 x 16 block
+  // One 16 x 16 x 16 block product per warp: acc += L[rows lr .. lr + 15][k] * R[k][columns rc .. rc + 15], k = 0..15.
+  // L is a block of A (scratch; lc = its first column), of T or of W (tile rows 0..63 / 64..127); R a block of T or W.
+  enum { kFromA = 0, kFromT = 1, kFromW = 2 };
+  const auto product = [&](float (&acc)[2][4], int lkind, int lr, int lc, int rkind, int rr, int rc) {
+    const int row = lr + 2 * rp, col = rc + 4 * cq;
 #pragma unroll 2
-      for (int kq = 4 * kb; kq < 4 * kb + 4; ++kq)  // four columns of A / rows of T at a time
-        fma_2x4(acc, ld4(smem, aab_off(row, kq)), ld4(smem, aab_off(row + 1, kq)), ld4(smem, t_off(4 * kq, col)),
-                ld4(smem, t_off(4 * kq + 1, col)), ld4(smem, t_off(4 * kq + 2, col)), ld4(smem, t_off(4 * kq + 3, col)));
-      st4(smem, w_off(16 * (kb + 1) + 2 * rp, col), make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]));
-      st4(smem, w_off(16 * (kb + 1) + 2 * rp + 1, col), make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]));
-    }
-    __syncthreads();
-    // T_ib = T_ii (sum of the dg terms): one warp per block
-    if (warp < 4 - dg) {
-      const int b2 = warp, ib = b2 + dg, row = 16 * ib + 2 * rp, col = 16 * b2 + 4 * cq;
-      float acc[2][4] = {};
-#pragma unroll 1
-      for (int q4 = 0; q4 < 4; ++q4) {
-        float4 w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) w[e] = ld4(smem, w_off(16 * (b2 + 1) + 4 * q4 + e, col));
-        for (int term = 1; term < dg; ++term) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float4 x = ld4(smem, w_off(16 * (b2 + term + 1) + 4 * q4 + e, col));
-            w[e].x += x.x; w[e].y += x.y; w[e].z += x.z; w[e].w += x.w;
-          }
-        }
-        const int q = 16 * ib + 4 * q4;
-        fma_2x4(acc, ld4(smem, t_off(row, q)), ld4(smem, t_off(row + 1, q)), w[0], w[1], w[2], w[3]);
+    for (int kq = 0; kq < 4; ++kq) {
+      float4 l0, l1;
+      if (lkind == kFromA) {
+        l0 = ld4(smem, aab_off(row, (lc >> 2) + kq));
+        l1 = ld4(smem, aab_off(row + 1, (lc >> 2) + kq));
+      } else {
+        const uint32_t base0 = lkind == kFromT ? t_off(row, lc + 4 * kq) : w_off(row, lc + 4 * kq);
+        l0 = ld4(smem, base0);
+        l1 = ld4(smem, base0 + 16);  // the next row of the same 16-byte column chunk
       }
-      st4(smem, t_off(row, col), make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]));
-      st4(smem, t_off(row + 1, col), make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]));
+      const uint32_t r0 = rkind == kFromT ? t_off(rr + 4 * kq, col) : w_off(rr + 4 * kq, col);
+      fma_2x4(acc, l0, l1, ld4(smem, r0), ld4(smem, r0 + 16), ld4(smem, r0 + 32), ld4(smem, r0 + 48));
     }
-    __syncthreads();
+  };
+  const auto store = [&](bool to_t, int r0, int c0, const float (&acc)[2][4]) {
+    const uint32_t o = to_t ? t_off(r0 + 2 * rp, c0 + 4 * cq) : w_off(r0 + 2 * rp, c0 + 4 * cq);
+    st4(smem, o, make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]));
+    st4(smem, o + 16, make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]));
+  };
+  // Two levels instead of one block anti-diagonal at a time: first the off-diagonal blocks inside the two 32 x 32
+  // halves, T_10 = T_11 (A_10 T_00) and T_32 = T_33 (A_32 T_22); then the 32 x 32 block below,
+  // T_lo = T22' (A21' T11') with T11' = [T_00 0; T_10 T_11], T22' = [T_22 0; T_32 T_33], one warp per 16 x 16 block.
+  // Four barrier-separated steps in place of six.  W block (i, j) lives in tile rows 64 + 16 i .., columns 16 j ...
+  // ---- step 1a: W(0,0) = A_10 T_00, W(0,1) = A_32 T_22 ----------------------------------------------------------
+  if (warp < 2) {
+    float acc[2][4] = {};
+    const int j = 32 * warp;  // block column 0 or 2
+    product(acc, kFromA, j + 16, j, kFromT, j, j);
+    store(false, 0, 16 * warp, acc);
   }
+  __syncthreads();
+  // ---- step 1b: T_10 = T_11 W(0,0), T_32 = T_33 W(0,1) -----------------------------------------------------------
+  if (warp < 2) {
+    float acc[2][4] = {};
+    const int j = 32 * warp;
+    product(acc, kFromT, j + 16, j + 16, kFromW, 0, 16 * warp);
+    store(true, j + 16, j, acc);
+  }
+  __syncthreads();
+  // ---- step 2a: W' = A21' T11': W'_p0 = A_{2+p,0} T_00 + A_{2+p,1} T_10, W'_p1 = A_{2+p,1} T_11; W'_pj in W(1+p, j) ---
+  if (warp < 4) {
+    float acc[2][4] = {};
+    const int p = warp >> 1, j = warp & 1;
+    if (j == 0) {
+      product(acc, kFromA, 32 + 16 * p, 0, kFromT, 0, 0);
+      product(acc, kFromA, 32 + 16 * p, 16, kFromT, 16, 0);
+    } else {
+      product(acc, kFromA, 32 + 16 * p, 16, kFromT, 16, 16);
+    }
+    store(false, 16 * (1 + p), 16 * j, acc);
+  }
+  __syncthreads();
+  // ---- step 2b: T_lo = T22' W': T_2j = T_22 W'_0j, T_3j = T_32 W'_0j + T_33 W'_1j ----------------------------------
+  if (warp < 4) {
+    float acc[2][4] = {};
+    const int i = warp >> 1, j = warp & 1;
+    if (i == 0) {
+      product(acc, kFromT, 32, 32, kFromW, 16, 16 * j);
+    } else {
+      product(acc, kFromT, 48, 32, kFromW, 16, 16 * j);
+      product(acc, kFromT, 48, 48, kFromW, 32, 16 * j);
+    }
+    store(true, 32 + 16 * i, 16 * j, acc);
+  }
+  __syncthreads();
   {
     // T' = T - I, rounded; everything on and above the diagonal is zero (the blocks above it were never written).
     // kTransposed: the tile ends as T'^T (rows and columns exchanged through registers, behind a barrier).
