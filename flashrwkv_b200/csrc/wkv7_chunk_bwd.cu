@@ -17,10 +17,12 @@
 // row tiles ([x;y][u;v]^T needs no transposition) and stay in tensor memory, masked in place, as the A operand of
 // the next product; contractions over tokens take their B operand from tiles written transposed ([feature][token]).
 // Transposed token x token matrices are not transposed but computed: D1T = [B~;K~][A~;R~]^T, DDT = [U;V][dX;dY']^T.
-// T^T comes from the same blocked inverse as in the forward, written transposed at the end.
+// T is never formed: dX = T^T dU is the solution of (I - A_ab)^T dX = dU, found in fp32 by blocked back substitution
+// (256 threads, one per (value column, block of 16 tokens)), which costs a third of inverting and multiplying.
+// [dX;dY'] and [U;V] enter the later products as shared-memory row tiles (both operands from shared memory).
 //
-// Tensor-memory columns (512):  XA [A~;R~] -> [U;V]   |  XB [B~;K~] -> OUT1 [dA~;dR~]  |  D1 (A_ab) -> DD
-//                               D1T -> DDT            |  DUV [dU;dV] -> OUT2 [dB~;dK~] |  DXY [dX;dY']
+// Tensor-memory columns (512):  XA [A~;R~]            |  XB [B~;K~] -> OUT1 [dA~;dR~]  |  D1 (A_ab) -> DD
+//                               D1T -> DDT            |  DUV [dU;dV] -> OUT2 [dB~;dK~]
 // 512 threads (warp w: lanes 32 (w % 4).., column group w / 4), one CTA per SM, ~221 KB of shared memory.
 //
 // Replaces the reference's serial backward kernels: csrc/sm90/tmix/wkv7/statetune_recurrent_fp32io16_backward.cu:49-255
@@ -40,8 +42,8 @@ constexpr uint32_t kCS128 = 2064;  // chunk stride of the 128-row tiles
 constexpr uint32_t kCS64 = 1040;   // ... of the 64-row tiles
 
 constexpr uint32_t kOffGT = 0;                         // g[t][k]
-constexpr uint32_t kOffRA = kOffGT + 16 * kCS64;       // [B~;K~] rows -> inverse tile (T | W) -> [T'^T;0] -> [U;V] rows
-constexpr uint32_t kOffRB = kOffRA + 16 * kCS128;      // [A~;R~] rows -> A_ab scratch -> [dX;dY'] rows
+constexpr uint32_t kOffRA = kOffGT + 16 * kCS64;       // B~ rows -> A_ab (fp32, rows 0..63) -> [U;V] rows
+constexpr uint32_t kOffRB = kOffRA + 16 * kCS128;      // [A~;R~] rows -> [dX;dY'] rows
 constexpr uint32_t kOffTBK = kOffRB + 16 * kCS128;     // [B~^T | K~^T]  rows k, columns (s | 64 + s)
 constexpr uint32_t kOffTAR = kOffTBK + 32 * kCS64;     // [A~^T | R~^T]
 constexpr uint32_t kOffTDY = kOffTAR + 32 * kCS64;     // dY'^T [v][t] -> dU^T -> dX^T; at the end  db * b
@@ -55,8 +57,8 @@ static_assert(kOffRA % 128 == 0 && kOffRB % 128 == 0 && kOffTBK % 128 == 0 && kO
               "tile bases must stay 128-byte aligned");
 static_assert(kBwdSmem + 2048 <= 232448, "the CTA must fit one SM's shared memory");
 
-constexpr uint32_t kColXA = 0, kColXB = 64, kColD1 = 128, kColD1T = 256, kColDUV = 384, kColDXY = 448;
-constexpr uint32_t kColUV = kColXA, kColOUT1 = kColXB, kColDD = kColD1, kColDDT = kColD1T, kColOUT2 = kColDUV;
+constexpr uint32_t kColXA = 0, kColXB = 64, kColD1 = 128, kColD1T = 256, kColDUV = 384;
+constexpr uint32_t kColOUT1 = kColXB, kColDD = kColD1, kColDDT = kColD1T, kColOUT2 = kColDUV;
 
 template <typename io_t>
 __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
@@ -78,10 +80,10 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
     return;
   }
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ uint64_t mbar[6];
+  __shared__ uint64_t mbar[5];
   __shared__ uint32_t tmem_holder;
   __shared__ float seg_total[8][64];
-  __shared__ float end_part[8][64];  // sum_v G S_L per key channel, one partial per block of eight value columns
+  __shared__ float end_sum[64];  // sum_v G S_L per key channel
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int m = 32 * (warp & 3) + lane;  // tensor-memory lane / operand row of this thread
   const int cg = warp >> 2;              // column group: 16 of 64 columns, 32 of 128
@@ -90,7 +92,7 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
   const int ch0 = 16 * cg;               // this thread's 16 channels
   if (tid == 0) {
 #pragma unroll
-    for (int i = 0; i < 6; ++i) umma::mbar_init(&mbar[i], 1);
+    for (int i = 0; i < 5; ++i) umma::mbar_init(&mbar[i], 1);
     umma::mbar_fence_init();
   }
   if (warp == 0) umma::tmem_alloc(&tmem_holder, 512);
@@ -105,36 +107,41 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
   bool ok = true;
   uint32_t parity = 0;
 
+  // (first token, length, sequence, last chunk of its sequence?) of an item.  The next item's are requested while the
+  // current one is worked on, so that no item starts by waiting for its chunk tables.
+  struct ItemMeta { int t0, len, seq; bool last; };
+  auto item_meta = [&](int item) {
+    ItemMeta im;
+    const int ch = item / num_heads;
+    im.t0 = chunk_starts[ch];
+    im.len = min(max(chunk_ends[ch] - im.t0, 1), kL);
+    int lo = 0, hi = num_sequences;  // largest s with seq_chunk_offsets[s] <= ch
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (seq_chunk_offsets[mid] <= ch) lo = mid; else hi = mid;
+    }
+    im.seq = lo;
+    im.last = ch + 1 == seq_chunk_offsets[lo + 1];
+    return im;
+  };
   // the decay logits of an item travel by cp.async one item ahead (one 16-byte piece per thread)
-  auto stage_w = [&](int item) {
-    const int ch = item / num_heads, hd = item % num_heads;
-    const int tt0 = chunk_starts[ch];
-    const int ln = min(max(chunk_ends[ch] - tt0, 1), kL);
+  auto stage_w = [&](int item, const ItemMeta& im) {
+    const int hd = item % num_heads;
     const int rowi = tid >> 3, part = tid & 7;
     umma::cp_async16(sbase + kOffW + tid * 16,
-                     w_ptr + (long long)(tt0 + min(rowi, ln - 1)) * row_stride + (long long)hd * kD + 8 * part,
-                     rowi < ln ? 16u : 0u);
+                     w_ptr + (long long)(im.t0 + min(rowi, im.len - 1)) * row_stride + (long long)hd * kD + 8 * part,
+                     rowi < im.len ? 16u : 0u);
     umma::cp_async_commit();
   };
-  if ((int)blockIdx.x < num_items) stage_w(blockIdx.x);
+  ItemMeta cur = item_meta(min((int)blockIdx.x, num_items - 1));
+  if ((int)blockIdx.x < num_items) stage_w(blockIdx.x, cur);
 
   for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, parity ^= 1u) {
     const int chunk = item / num_heads, head = item % num_heads;
-    const int t0 = chunk_starts[chunk];
-    const int len = min(max(chunk_ends[chunk] - t0, 1), kL);
+    const int t0 = cur.t0, len = cur.len, seq = cur.seq;
+    const bool last_of_seq = cur.last;
     const long long head_off = (long long)head * kD;
     const bool valid = mt < len;
-    // the sequence this chunk belongs to: its last chunk ends in the final state, the others in the next boundary
-    int seq = 0;
-    {
-      int lo = 0, hi = num_sequences;  // largest s with seq_chunk_offsets[s] <= chunk
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (seq_chunk_offsets[mid] <= chunk) lo = mid; else hi = mid;
-      }
-      seq = lo;
-    }
-    const bool last_of_seq = chunk + 1 == seq_chunk_offsets[seq + 1];
     const float* s_end = last_of_seq ? final_state + ((long long)seq * num_heads + head) * (kD * kD)
                                      : boundary + ((long long)(chunk + 1) * num_heads + head) * (kD * kD);
     const float* s_start = boundary + ((long long)chunk * num_heads + head) * (kD * kD);
@@ -155,7 +162,7 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
         draw[i] = (valid && !low) ? __ldg(dp + i) : zero4;
       }
     }
-
+    const bool has_next = item + (int)gridDim.x < num_items;
     // ---- g[t][k] (as in the forward kernel; threads 0..255 work) ------------------------------------------------
     umma::cp_async_wait_all();
     __syncthreads();
@@ -200,9 +207,8 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
       }
     }
     __syncthreads();
-
     // ---- operands: A forms to tensor memory, row tiles and transposed tiles to shared memory --------------------
-    float dyv[16];  // dY' of this thread's row and channels (lanes 64..127), kept for the [dX;dY'] row tile
+      float dyv[16];  // dY' of this thread's row and channels (lanes 64..127), kept for the [dX;dY'] row tile
     {
       float pf[16], qf[16];
       unpack8<io_t>(praw[0], *reinterpret_cast<float(*)[8]>(&pf[0]));
@@ -238,45 +244,215 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
       umma::tmem_st16(tmem + kColXA + lane_base + ch0, xa);
       umma::tmem_st16(tmem + kColXB + lane_base + ch0, xb);
       if (!low) {
-        uint32_t dq[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           dyv[e] = umma::to_tf32(scale * dyv[e]);
-          dq[e] = __float_as_uint(dyv[e]);
           st1(smem, kOffTDY + tile_off(kCS64, ch0 + e, mt), dyv[e]);  // dY'^T [v][t]
         }
-        umma::tmem_st16(tmem + kColDXY + lane_base + ch0, dq);
       }
     }
-    // G^ = g_L * G in both orientations, S0, and the end term sum_v G S_L: thread (key k, eight value columns)
-    {
-      const int kk = tid & 63, v0 = 8 * (tid >> 6);
-      const float gl = ld1(smem, kOffGT + tile_off(kCS64, 63, kk));
-      const float4 ga = __ldg(reinterpret_cast<const float4*>(g_end + kk * kD + v0));
-      const float4 gb = __ldg(reinterpret_cast<const float4*>(g_end + kk * kD + v0 + 4));
-      const float4 sa = __ldg(reinterpret_cast<const float4*>(s_end + kk * kD + v0));
-      const float4 sb = __ldg(reinterpret_cast<const float4*>(s_end + kk * kD + v0 + 4));
-      const float4 za = __ldg(reinterpret_cast<const float4*>(s_start + kk * kD + v0));
-      const float4 zb = __ldg(reinterpret_cast<const float4*>(s_start + kk * kD + v0 + 4));
-      // partial sums in a table, added later in a fixed order: repeated runs give the same bits
-      end_part[tid >> 6][kk] = ga.x * sa.x + ga.y * sa.y + ga.z * sa.z + ga.w * sa.w + gb.x * sb.x + gb.y * sb.y +
-                               gb.z * sb.z + gb.w * sb.w;
-      const float4 ha = umma::to_tf32(make_float4(gl * ga.x, gl * ga.y, gl * ga.z, gl * ga.w));
-      const float4 hb = umma::to_tf32(make_float4(gl * gb.x, gl * gb.y, gl * gb.z, gl * gb.w));
-      st4(smem, kOffNG + uint32_t(v0 >> 2) * kCS64 + kk * 16, ha);
-      st4(smem, kOffNG + uint32_t((v0 >> 2) + 1) * kCS64 + kk * 16, hb);
-      st4(smem, kOffNS + uint32_t(v0 >> 2) * kCS64 + kk * 16, umma::to_tf32(za));
-      st4(smem, kOffNS + uint32_t((v0 >> 2) + 1) * kCS64 + kk * 16, umma::to_tf32(zb));
-      const uint32_t tg = kOffTG + uint32_t(kk >> 2) * kCS64 + uint32_t(kk & 3) * 4 + uint32_t(v0) * 16;
-      st1(smem, tg, ha.x); st1(smem, tg + 16, ha.y); st1(smem, tg + 32, ha.z); st1(smem, tg + 48, ha.w);
-      st1(smem, tg + 64, hb.x); st1(smem, tg + 80, hb.y); st1(smem, tg + 96, hb.z); st1(smem, tg + 112, hb.w);
+    umma::tmem_st_wait();
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    // ---- D1 = XA B~^T (only its A_ab block is used) and D1T = XB [A~;R~]^T ---------------------------------------
+    if (tid == 0) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ts(tmem + kColD1, tmem + kColXA + 8 * ks,
+                          umma::desc_k_major(sbase + kOffRA + ks * 2 * kCS128, kCS128), idesc64, ks > 0 ? 1u : 0u);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ts(tmem + kColD1T, tmem + kColXB + 8 * ks,
+                          umma::desc_k_major(sbase + kOffRB + ks * 2 * kCS128, kCS128), idesc128, ks > 0 ? 1u : 0u);
+      umma::mma_commit(&mbar[0]);
     }
-    // pull the next item's rows into L2
-    if (item + (int)gridDim.x < num_items) {
+    // meanwhile the three state tiles: G^ = g_L * G in both orientations, S0, and the end term sum_v G S_L.  Warp w
+    // takes keys 4 w .. 4 w + 3: lane (key kq = lane % 4, value chunk c = lane / 4) reads 16 bytes of each tile row
+    // half, so that a load covers whole 128-byte lines; the transposed tile is written as 16-byte pieces after a
+    // 4 x 4 exchange among the four lanes of a value chunk.
+    {
+      const int kq = lane & 3, c = lane >> 2;
+      const int k0 = 4 * warp, kk = k0 + kq;
+      const float gl = ld1(smem, kOffGT + tile_off(kCS64, 63, kk));
+      float4 gv[2], sv[2], zv[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int at = kk * kD + 32 * h + 4 * c;
+        gv[h] = __ldg(reinterpret_cast<const float4*>(g_end + at));
+        sv[h] = __ldg(reinterpret_cast<const float4*>(s_end + at));
+        zv[h] = __ldg(reinterpret_cast<const float4*>(s_start + at));
+      }
+      float e = 0.f;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        e += gv[h].x * sv[h].x + gv[h].y * sv[h].y + gv[h].z * sv[h].z + gv[h].w * sv[h].w;
+        const int vc = 8 * h + c;  // 16-byte column chunk of the value index
+        float4 hg = umma::to_tf32(make_float4(gl * gv[h].x, gl * gv[h].y, gl * gv[h].z, gl * gv[h].w));
+        st4(smem, kOffNG + uint32_t(vc) * kCS64 + kk * 16, hg);
+        st4(smem, kOffNS + uint32_t(vc) * kCS64 + kk * 16, umma::to_tf32(zv[h]));
+        {  // afterwards lane kq holds G^[k0 .. k0 + 3][v] for v = 4 vc + kq
+          const bool odd = (kq & 1) != 0, hi = (kq & 2) != 0;
+          float s0 = odd ? hg.x : hg.y, s1 = odd ? hg.z : hg.w;
+          float r0 = __shfl_xor_sync(0xffffffffu, s0, 1), r1 = __shfl_xor_sync(0xffffffffu, s1, 1);
+          if (odd) { hg.x = r0; hg.z = r1; } else { hg.y = r0; hg.w = r1; }
+          s0 = hi ? hg.x : hg.z; s1 = hi ? hg.y : hg.w;
+          r0 = __shfl_xor_sync(0xffffffffu, s0, 2); r1 = __shfl_xor_sync(0xffffffffu, s1, 2);
+          if (hi) { hg.x = r0; hg.y = r1; } else { hg.z = r0; hg.w = r1; }
+        }
+        st4(smem, kOffTG + uint32_t(k0 >> 2) * kCS64 + uint32_t(4 * vc + kq) * 16, hg);
+      }
+      // the end term of key kk: the eight lanes of the key added in a fixed order
+      e += __shfl_xor_sync(0xffffffffu, e, 4);
+      e += __shfl_xor_sync(0xffffffffu, e, 8);
+      e += __shfl_xor_sync(0xffffffffu, e, 16);
+      if (c == 0) end_sum[kk] = e;
+    }
+    ok = wait_warp(&mbar[0], parity, ok);
+    umma::fence_after_sync();
+    // D1T masked in place: its element [s][t] is kept for t > s (columns 0..63: products with A~) or t >= s (columns
+    // 64..127: with R~).  A_ab -> fp32, as rows 0..63 of the [U;V] tile (B~ rows, consumed); dY' rows -> rows 64..127
+    // of the [dX;dY'] tile ([A~;R~] rows, consumed).
+    if (ok) {
+      const bool mask_d1t = !low || cg >= 2;  // the A_ab^T block (lanes 0..63, columns 0..63) is never used
+      if (mask_d1t) {
+        uint32_t ut[32];
+        const uint32_t taddr = tmem + kColD1T + lane_base + 32 * cg;
+        umma::tmem_ld32(taddr, ut);
+        umma::tmem_ld_wait();
+        const int tbase = (32 * cg) & 63;
+        const int first = cg >= 2 ? mt : mt + 1;  // smallest kept t
+#pragma unroll
+        for (int j = 0; j < 32; ++j) ut[j] = tbase + j >= first ? tf32_bits(__uint_as_float(ut[j])) : 0u;
+        umma::tmem_st32(taddr, ut);
+      }
+      if (low) {
+        uint32_t u[16];
+        umma::tmem_ld16(tmem + kColD1 + lane_base + ch0, u);
+        umma::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          const int s = ch0 + j;
+          st4(smem, kOffRA + uint32_t(s >> 2) * kCS128 + uint32_t(mt) * 16,
+              make_float4(s < mt ? __uint_as_float(u[j]) : 0.f, s + 1 < mt ? __uint_as_float(u[j + 1]) : 0.f,
+                          s + 2 < mt ? __uint_as_float(u[j + 2]) : 0.f, s + 3 < mt ? __uint_as_float(u[j + 3]) : 0.f));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          st4(smem, kOffRB + (4 * cg + j) * kCS128 + m * 16,
+              make_float4(dyv[4 * j], dyv[4 * j + 1], dyv[4 * j + 2], dyv[4 * j + 3]));
+      }
+      umma::tmem_st_wait();
+    }
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    // ---- DUV = D1T[:,64:128] dY' + XB G^  ->  [dU ; A_rk^T dY' + K~ G^] -------------------------------------------------
+    if (tid == 0) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ts(tmem + kColDUV, tmem + kColD1T + 64 + 8 * ks,
+                          umma::desc_k_major(sbase + kOffTDY + ks * 2 * kCS64, kCS64), idesc64, ks > 0 ? 1u : 0u);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma::mma_tf32_ts(tmem + kColDUV, tmem + kColXB + 8 * ks,
+                          umma::desc_k_major(sbase + kOffTG + ks * 2 * kCS64, kCS64), idesc64, 1u);
+      umma::mma_commit(&mbar[1]);
+    }
+    // this thread's 16 channels of its U row (fp32, four pieces) or V row (16-bit, two pieces)
+    uint4 uvraw[4];
+    {
+      const uint4* up = low ? reinterpret_cast<const uint4*>(sda_ptr + row) : reinterpret_cast<const uint4*>(v_ptr + row);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) uvraw[i] = (valid && (low || i < 2)) ? __ldg(up + i) : zero4;
+    }
+    ok = wait_warp(&mbar[1], parity, ok);
+    umma::fence_after_sync();
+    // ---- dU^T -> shared memory (over dY'^T, consumed), unrounded: the solve below works in fp32 -------------------------
+    if (ok && low) {
+      uint32_t u[16];
+      umma::tmem_ld16(tmem + kColDUV + lane_base + ch0, u);
+      umma::tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 16; ++e) st1(smem, kOffTDY + tile_off(kCS64, ch0 + e, mt), __uint_as_float(u[e]));
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    // ---- dX = (I - A_ab)^-T dU by blocked back substitution in fp32, dX_s = dU_s + sum_{t > s} A_ab[t][s] dX_t.
+    //      Thread (column v, block j) of warps 0..7 holds rows 16 j .. 16 j + 15 of column v.  From the last block to
+    //      the first: the owners of block jb finish it (a 16 x 16 triangular solve in registers) and publish it; the
+    //      owners of earlier blocks fold it in (a 16 x 16 update).  The other warps meanwhile pull the next item's
+    //      rows into L2. --------------------------------------------------------------------------------------------------
+    if (warp < 8) {
+      const int v = tid & 63, j = tid >> 6;
+      float x[16];
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const float4 q = ld4(smem, kOffTDY + (4 * j + c4) * kCS64 + v * 16);
+        x[4 * c4] = q.x; x[4 * c4 + 1] = q.y; x[4 * c4 + 2] = q.z; x[4 * c4 + 3] = q.w;
+      }
+#pragma unroll 1
+      for (int jb = 3; jb >= 0; --jb) {
+        if (j == jb) {
+          const uint32_t arow = kOffRA + uint32_t(4 * jb) * kCS128 + uint32_t(16 * jb) * 16;  // A_ab[16 jb][16 jb]
+#pragma unroll
+          for (int tt = 15; tt >= 1; --tt) {
+            const float xt = x[tt];
+#pragma unroll
+            for (int s4 = 0; 4 * s4 < tt; ++s4) {
+              const float4 a4 = ld4(smem, arow + s4 * kCS128 + tt * 16);
+              x[4 * s4] = fmaf(a4.x, xt, x[4 * s4]);
+              if (4 * s4 + 1 < tt) x[4 * s4 + 1] = fmaf(a4.y, xt, x[4 * s4 + 1]);
+              if (4 * s4 + 2 < tt) x[4 * s4 + 2] = fmaf(a4.z, xt, x[4 * s4 + 2]);
+              if (4 * s4 + 3 < tt) x[4 * s4 + 3] = fmaf(a4.w, xt, x[4 * s4 + 3]);
+            }
+          }
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4)
+            st4(smem, kOffTDY + (4 * j + c4) * kCS64 + v * 16, make_float4(x[4 * c4], x[4 * c4 + 1], x[4 * c4 + 2], x[4 * c4 + 3]));
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (j < jb) {
+          float xb[16];
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            const float4 q = ld4(smem, kOffTDY + (4 * jb + c4) * kCS64 + v * 16);
+            xb[4 * c4] = q.x; xb[4 * c4 + 1] = q.y; xb[4 * c4 + 2] = q.z; xb[4 * c4 + 3] = q.w;
+          }
+          const uint32_t arow = kOffRA + uint32_t(4 * j) * kCS128 + uint32_t(16 * jb) * 16;  // A_ab[16 jb][16 j]
+#pragma unroll
+          for (int tt = 0; tt < 16; ++tt) {
+#pragma unroll
+            for (int s4 = 0; s4 < 4; ++s4) {
+              const float4 a4 = ld4(smem, arow + s4 * kCS128 + tt * 16);
+              x[4 * s4] = fmaf(a4.x, xb[tt], x[4 * s4]);
+              x[4 * s4 + 1] = fmaf(a4.y, xb[tt], x[4 * s4 + 1]);
+              x[4 * s4 + 2] = fmaf(a4.z, xb[tt], x[4 * s4 + 2]);
+              x[4 * s4 + 3] = fmaf(a4.w, xb[tt], x[4 * s4 + 3]);
+            }
+          }
+        }
+      }
+      // every block has been read: dX^T, rounded, over dU^T, and the dX rows into rows 0..63 of the [dX;dY'] tile
+#pragma unroll
+      for (int e = 0; e < 16; ++e) x[e] = umma::to_tf32(x[e]);
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4)
+        st4(smem, kOffTDY + (4 * j + c4) * kCS64 + v * 16, make_float4(x[4 * c4], x[4 * c4 + 1], x[4 * c4 + 2], x[4 * c4 + 3]));
+      const uint32_t col = kOffRB + uint32_t(v >> 2) * kCS128 + uint32_t(v & 3) * 4 + uint32_t(16 * j) * 16;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) st1(smem, col + e * 16, x[e]);
+    } else if (warp >= 8 && has_next) {
+      // pull the next item's rows into L2
+      const int u = tid - 256;
       const int nit = item + gridDim.x, nch = nit / num_heads, nhd = nit % num_heads;
       const int num_chunks_total = num_items / num_heads;
       const int nt0 = chunk_starts[nch], nlen = chunk_ends[nch] - nt0;
-      for (int e = tid; e < 8 * kL; e += kBwdThreads) {
+      for (int e = u; e < 8 * kL; e += 256) {
         const int which = e >> 6, rowi = e & 63;
         if (rowi < nlen) {
           const long long at = (long long)(nt0 + rowi) * row_stride + (long long)nhd * kD;
@@ -290,10 +466,10 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
           }
         }
       }
-      // ... and its three 16 KB state tiles (chunk-start state, chunk-end adjoint; the chunk-end state is the next
-      // boundary or the final state, found by the same search the item does): 128 lines of 128 bytes each
-      if (tid < 384) {
-        const int which = tid >> 7, line = tid & 127;
+      // ... and its three 16 KB state tiles (chunk-start state, chunk-end adjoint; the chunk-end state where it is the
+      // next boundary, which is all but the last chunk of a sequence): 128 lines of 128 bytes each
+      for (int e = u; e < 384; e += 256) {
+        const int which = e >> 7, line = e & 127;
         const float* base = nullptr;
         if (which == 0) base = boundary + ((long long)nch * num_heads + nhd) * (kD * kD);
         if (which == 1) base = adjoint + ((long long)nch * num_heads + nhd) * (kD * kD);
@@ -301,104 +477,8 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
         if (base != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + 32 * line));
       }
     }
-    umma::tmem_st_wait();
-    umma::fence_async_smem();
-    umma::fence_before_sync();
-    __syncthreads();
-    umma::fence_after_sync();
-
-    // ---- D1 = XA B~^T (only its A_ab block is used) and D1T = XB [A~;R~]^T ---------------------------------------
-    if (tid == 0) {
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks)
-        umma::mma_tf32_ts(tmem + kColD1, tmem + kColXA + 8 * ks,
-                          umma::desc_k_major(sbase + kOffRA + ks * 2 * kCS128, kCS128), idesc64, ks > 0 ? 1u : 0u);
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks)
-        umma::mma_tf32_ts(tmem + kColD1T, tmem + kColXB + 8 * ks,
-                          umma::desc_k_major(sbase + kOffRB + ks * 2 * kCS128, kCS128), idesc128, ks > 0 ? 1u : 0u);
-      umma::mma_commit(&mbar[0]);
-    }
-    ok = wait_warp(&mbar[0], parity, ok);
-    umma::fence_after_sync();
-    // A_ab -> fp32 scratch (over the [A~;R~] row tile, which both products have consumed); D1T masked in place:
-    // its element [s][t] is kept for t > s (columns 0..63: products with A~) or t >= s (columns 64..127: with R~)
-    if (ok) {
-      if (low) {
-        uint32_t u[16];
-        umma::tmem_ld16(tmem + kColD1 + lane_base + ch0, u);
-        umma::tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; j += 4) {
-          const int s = ch0 + j;
-          const uint32_t o = kOffRB + uint32_t(mt) * 256 + uint32_t((((s >> 2)) ^ ((mt >> 1) & 7)) * 16);
-          st4(smem, o, make_float4(s < mt ? __uint_as_float(u[j]) : 0.f, s + 1 < mt ? __uint_as_float(u[j + 1]) : 0.f,
-                                   s + 2 < mt ? __uint_as_float(u[j + 2]) : 0.f, s + 3 < mt ? __uint_as_float(u[j + 3]) : 0.f));
-        }
-      }
-      if (!low || cg >= 2) {  // the A_ab^T block (lanes 0..63, columns 0..63) is never used
-        uint32_t u[32];
-        const uint32_t taddr = tmem + kColD1T + lane_base + 32 * cg;
-        umma::tmem_ld32(taddr, u);
-        umma::tmem_ld_wait();
-        const int tbase = (32 * cg) & 63;
-        const int first = cg >= 2 ? mt : mt + 1;  // smallest kept t
-#pragma unroll
-        for (int j = 0; j < 32; ++j) u[j] = tbase + j >= first ? tf32_bits(__uint_as_float(u[j])) : 0u;
-        umma::tmem_st32(taddr, u);
-        umma::tmem_st_wait();
-      }
-    }
-    umma::fence_async_smem();
-    umma::fence_before_sync();
-    __syncthreads();
-    umma::fence_after_sync();
-
-    // ---- DUV = D1T[:,64:128] dY' + XB G^  ->  [dU ; A_rk^T dY' + K~ G^]   (runs while the CUDA cores invert) -------
-    if (tid == 0) {
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks)
-        umma::mma_tf32_ts(tmem + kColDUV, tmem + kColD1T + 64 + 8 * ks,
-                          umma::desc_k_major(sbase + kOffTDY + ks * 2 * kCS64, kCS64), idesc64, ks > 0 ? 1u : 0u);
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks)
-        umma::mma_tf32_ts(tmem + kColDUV, tmem + kColXB + 8 * ks,
-                          umma::desc_k_major(sbase + kOffTG + ks * 2 * kCS64, kCS64), idesc64, 1u);
-      umma::mma_commit(&mbar[1]);
-    }
-    // this thread's 16 channels of its U row (fp32, four pieces) or V row (16-bit, two pieces): requested now, used
-    // after the inverse
-    uint4 uvraw[4];
-    {
-      const uint4* up = low ? reinterpret_cast<const uint4*>(sda_ptr + row) : reinterpret_cast<const uint4*>(v_ptr + row);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) uvraw[i] = (valid && (low || i < 2)) ? __ldg(up + i) : zero4;
-    }
-    inverse_blocked<kOffRB, kOffRA, kCS128, true>(smem, tid);  // T'^T, rows 64..127 of the tile zero
-    __syncthreads();
-    ok = wait_warp(&mbar[1], parity, ok);
-    umma::fence_after_sync();
-    // ---- dU^T -> shared memory (over dY'^T, consumed) ------------------------------------------------------------
-    if (ok && low) {
-      uint32_t u[16];
-      umma::tmem_ld16(tmem + kColDUV + lane_base + ch0, u);
-      umma::tmem_ld_wait();
-#pragma unroll
-      for (int e = 0; e < 16; ++e) st1(smem, kOffTDY + tile_off(kCS64, ch0 + e, mt), umma::to_tf32(__uint_as_float(u[e])));
-    }
-    umma::fence_async_smem();
-    umma::fence_before_sync();
-    __syncthreads();
-    umma::fence_after_sync();
-    // ---- dX = dU + T'^T dU: DUV += [T'^T;0] dU ---------------------------------------------------------------------
-    if (tid == 0) {
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks)
-        umma::mma_tf32_ss(tmem + kColDUV, umma::desc_k_major(sbase + kOffRA + ks * 2 * kCS128, kCS128),
-                          umma::desc_k_major(sbase + kOffTDY + ks * 2 * kCS64, kCS64), idesc64, 1u);
-      umma::mma_commit(&mbar[2]);
-    }
-    // meanwhile: this thread's 16 channels of its U row or V row, rounded as operands
+    // this thread's 16 channels of its U row or V row, rounded as operands; the V rows go to rows 64..127 of the
+    // [U;V] tile now, the U rows (over A_ab) once the solve has read it
     float uv[16];
     {
       if (low) {
@@ -413,40 +493,20 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
       }
 #pragma unroll
       for (int e = 0; e < 16; ++e) uv[e] = umma::to_tf32(uv[e]);
-    }
-    ok = wait_warp(&mbar[2], parity, ok);
-    umma::fence_after_sync();
-    // ---- dX: A form (tensor memory), dX^T (over dU^T), [dX;dY'] rows (over the A_ab scratch); [U;V]: A form and rows
-    //      (over [T'^T;0], consumed) ------------------------------------------------------------------------------
-    if (ok) {
-      float dx[16];
-      if (low) {
-        uint32_t u[16];
-        umma::tmem_ld16(tmem + kColDUV + lane_base + ch0, u);
-        umma::tmem_ld_wait();
+      if (!low) {
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          dx[e] = umma::to_tf32(__uint_as_float(u[e]));
-          u[e] = __float_as_uint(dx[e]);
-          st1(smem, kOffTDY + tile_off(kCS64, ch0 + e, mt), dx[e]);
-        }
-        umma::tmem_st16(tmem + kColDXY + lane_base + ch0, u);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 16; ++e) dx[e] = dyv[e];
+        for (int j = 0; j < 4; ++j)
+          st4(smem, kOffRA + (4 * cg + j) * kCS128 + m * 16, make_float4(uv[4 * j], uv[4 * j + 1], uv[4 * j + 2], uv[4 * j + 3]));
       }
-      uint32_t uq[16];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int kc = 4 * cg + j;
-        st4(smem, kOffRB + kc * kCS128 + m * 16, make_float4(dx[4 * j], dx[4 * j + 1], dx[4 * j + 2], dx[4 * j + 3]));
-        st4(smem, kOffRA + kc * kCS128 + m * 16, make_float4(uv[4 * j], uv[4 * j + 1], uv[4 * j + 2], uv[4 * j + 3]));
-      }
-#pragma unroll
-      for (int e = 0; e < 16; ++e) uq[e] = __float_as_uint(uv[e]);
-      umma::tmem_st16(tmem + kColUV + lane_base + ch0, uq);
-      umma::tmem_st_wait();
     }
+    __syncthreads();
+    if (low) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        st4(smem, kOffRA + (4 * cg + j) * kCS128 + m * 16, make_float4(uv[4 * j], uv[4 * j + 1], uv[4 * j + 2], uv[4 * j + 3]));
+    }
+    // the next item's chunk-table entries: requested here, with no other load of this thread in flight, used at the end
+    const ItemMeta nxt = has_next ? item_meta(item + gridDim.x) : cur;
     umma::fence_async_smem();
     umma::fence_before_sync();
     __syncthreads();
@@ -459,41 +519,37 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
                           umma::desc_k_major(sbase + kOffTDY + ks * 2 * kCS64, kCS64), idesc64, 1u);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
-        umma::mma_tf32_ts(tmem + kColDD, tmem + kColDXY + 8 * ks,
+        umma::mma_tf32_ss(tmem + kColDD, umma::desc_k_major(sbase + kOffRB + ks * 2 * kCS128, kCS128),
                           umma::desc_k_major(sbase + kOffRA + ks * 2 * kCS128, kCS128), idesc128, ks > 0 ? 1u : 0u);
-      umma::mma_commit(&mbar[3]);
+      umma::mma_commit(&mbar[2]);
     }
-    ok = wait_warp(&mbar[3], parity, ok);
+    ok = wait_warp(&mbar[2], parity, ok);
     umma::fence_after_sync();
     if (ok) {
-      if (!low) {  // dV rows out
-        uint32_t u[16];
-        umma::tmem_ld16(tmem + kColDUV + lane_base + ch0, u);
-        umma::tmem_ld_wait();
-        if (valid) {
-          uint4 p0, p1;
-          p0.x = IO::pack(__uint_as_float(u[0]), __uint_as_float(u[1])); p0.y = IO::pack(__uint_as_float(u[2]), __uint_as_float(u[3]));
-          p0.z = IO::pack(__uint_as_float(u[4]), __uint_as_float(u[5])); p0.w = IO::pack(__uint_as_float(u[6]), __uint_as_float(u[7]));
-          p1.x = IO::pack(__uint_as_float(u[8]), __uint_as_float(u[9])); p1.y = IO::pack(__uint_as_float(u[10]), __uint_as_float(u[11]));
-          p1.z = IO::pack(__uint_as_float(u[12]), __uint_as_float(u[13])); p1.w = IO::pack(__uint_as_float(u[14]), __uint_as_float(u[15]));
-          uint4* dst = reinterpret_cast<uint4*>(dv_ptr + row);
-          dst[0] = p0;
-          dst[1] = p1;
-        }
-      }
+      uint32_t u[16], ud[32];
+      const uint32_t taddr = tmem + kColDD + lane_base + 32 * cg;
+      if (!low) umma::tmem_ld16(tmem + kColDUV + lane_base + ch0, u);
+      umma::tmem_ld32(taddr, ud);
+      umma::tmem_ld_wait();
       // DD masked in place: element [t][s] kept for s < t (rows of dX) or s <= t (rows of dY')
       {
-        uint32_t u[32];
-        const uint32_t taddr = tmem + kColDD + lane_base + 32 * cg;
-        umma::tmem_ld32(taddr, u);
-        umma::tmem_ld_wait();
         const int sbase_col = (32 * cg) & 63;
         const int limit = low ? mt : mt + 1;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) u[j] = sbase_col + j < limit ? tf32_bits(__uint_as_float(u[j])) : 0u;
-        umma::tmem_st32(taddr, u);
-        umma::tmem_st_wait();
+        for (int j = 0; j < 32; ++j) ud[j] = sbase_col + j < limit ? tf32_bits(__uint_as_float(ud[j])) : 0u;
+        umma::tmem_st32(taddr, ud);
       }
+      if (!low && valid) {  // dV rows out
+        uint4 p0, p1;
+        p0.x = IO::pack(__uint_as_float(u[0]), __uint_as_float(u[1])); p0.y = IO::pack(__uint_as_float(u[2]), __uint_as_float(u[3]));
+        p0.z = IO::pack(__uint_as_float(u[4]), __uint_as_float(u[5])); p0.w = IO::pack(__uint_as_float(u[6]), __uint_as_float(u[7]));
+        p1.x = IO::pack(__uint_as_float(u[8]), __uint_as_float(u[9])); p1.y = IO::pack(__uint_as_float(u[10]), __uint_as_float(u[11]));
+        p1.z = IO::pack(__uint_as_float(u[12]), __uint_as_float(u[13])); p1.w = IO::pack(__uint_as_float(u[14]), __uint_as_float(u[15]));
+        uint4* dst = reinterpret_cast<uint4*>(dv_ptr + row);
+        dst[0] = p0;
+        dst[1] = p1;
+      }
+      umma::tmem_st_wait();
     }
     umma::fence_before_sync();
     __syncthreads();
@@ -502,42 +558,47 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
     if (tid == 0) {
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
-        umma::mma_tf32_ts(tmem + kColDDT, tmem + kColUV + 8 * ks,
+        umma::mma_tf32_ss(tmem + kColDDT, umma::desc_k_major(sbase + kOffRA + ks * 2 * kCS128, kCS128),
                           umma::desc_k_major(sbase + kOffRB + ks * 2 * kCS128, kCS128), idesc128, ks > 0 ? 1u : 0u);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
-        umma::mma_tf32_ts(tmem + kColOUT1, tmem + kColDXY + 8 * ks,
+        umma::mma_tf32_ss(tmem + kColOUT1, umma::desc_k_major(sbase + kOffRB + ks * 2 * kCS128, kCS128),
                           umma::desc_k_major(sbase + kOffNS + ks * 2 * kCS64, kCS64), idesc64, ks > 0 ? 1u : 0u);
 #pragma unroll
       for (int ks = 0; ks < 16; ++ks)
         umma::mma_tf32_ts(tmem + kColOUT1, tmem + kColDD + 8 * ks,
                           umma::desc_k_major(sbase + kOffTBK + ks * 2 * kCS64, kCS64), idesc64, 1u);
-      umma::mma_commit(&mbar[4]);
+      umma::mma_commit(&mbar[3]);
     }
-    ok = wait_warp(&mbar[4], parity, ok);
+    // this thread's a or r channels again (asked for twice rather than held in registers across the solve)
+    uint4 praw2[2];
+    {
+      const uint4* pp = reinterpret_cast<const uint4*>((low ? a_ptr : r_ptr) + row);
+      praw2[0] = valid ? __ldcg(pp) : zero4;
+      praw2[1] = valid ? __ldcg(pp + 1) : zero4;
+    }
+    ok = wait_warp(&mbar[3], parity, ok);
     umma::fence_after_sync();
     // ---- DDT masked in place ([s][t] kept for t > s in the dX columns, t >= s in the dY' columns); da, dr out ------
     if (ok) {
+      uint32_t u[16];
       {
-        uint32_t u[32];
+        uint32_t ut[32];
         const uint32_t taddr = tmem + kColDDT + lane_base + 32 * cg;
-        umma::tmem_ld32(taddr, u);
+        umma::tmem_ld32(taddr, ut);
+        umma::tmem_ld16(tmem + kColOUT1 + lane_base + ch0, u);
         umma::tmem_ld_wait();
         const int tbase = (32 * cg) & 63;
         const int first = cg >= 2 ? mt : mt + 1;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) u[j] = tbase + j >= first ? tf32_bits(__uint_as_float(u[j])) : 0u;
-        umma::tmem_st32(taddr, u);
-        umma::tmem_st_wait();
+        for (int j = 0; j < 32; ++j) ut[j] = tbase + j >= first ? tf32_bits(__uint_as_float(ut[j])) : 0u;
+        umma::tmem_st32(taddr, ut);
       }
       // lanes 0..63: da = dA~ g_{t-1}; lanes 64..127: dr = dR~ g_t; the products da * a and dr * r go to shared memory
       // for the decay gradient, over the S0 tile and the G^^T tile (both read only by products that have completed)
-      uint32_t u[16];
-      umma::tmem_ld16(tmem + kColOUT1 + lane_base + ch0, u);
-      umma::tmem_ld_wait();
       float pf[16];
-      unpack8<io_t>(praw[0], *reinterpret_cast<float(*)[8]>(&pf[0]));
-      unpack8<io_t>(praw[1], *reinterpret_cast<float(*)[8]>(&pf[8]));
+      unpack8<io_t>(praw2[0], *reinterpret_cast<float(*)[8]>(&pf[0]));
+      unpack8<io_t>(praw2[1], *reinterpret_cast<float(*)[8]>(&pf[8]));
       float gr[16];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -559,6 +620,7 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
         dst[0] = p0;
         dst[1] = p1;
       }
+      umma::tmem_st_wait();
     }
     umma::fence_before_sync();
     __syncthreads();
@@ -571,11 +633,17 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
                           umma::desc_k_major(sbase + kOffTAR + ks * 2 * kCS64, kCS64), idesc64, ks > 0 ? 1u : 0u);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
-        umma::mma_tf32_ts(tmem + kColOUT2, tmem + kColUV + 8 * ks,
+        umma::mma_tf32_ss(tmem + kColOUT2, umma::desc_k_major(sbase + kOffRA + ks * 2 * kCS128, kCS128),
                           umma::desc_k_major(sbase + kOffNG + ks * 2 * kCS64, kCS64), idesc64, 1u);
-      umma::mma_commit(&mbar[5]);
+      umma::mma_commit(&mbar[4]);
     }
-    ok = wait_warp(&mbar[5], parity, ok);
+    uint4 qraw2[2];  // ... and its b or k channels
+    {
+      const uint4* qp = reinterpret_cast<const uint4*>((low ? b_ptr : k_ptr) + row);
+      qraw2[0] = valid ? __ldcg(qp) : zero4;
+      qraw2[1] = valid ? __ldcg(qp + 1) : zero4;
+    }
+    ok = wait_warp(&mbar[4], parity, ok);
     umma::fence_after_sync();
     // lanes 0..63: db = dB~ / g_s; lanes 64..127: dk = dK~ / g_s; products db * b, dk * k to shared memory
     if (ok) {
@@ -583,8 +651,8 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
       umma::tmem_ld16(tmem + kColOUT2 + lane_base + ch0, u);
       umma::tmem_ld_wait();
       float qf[16];
-      unpack8<io_t>(qraw[0], *reinterpret_cast<float(*)[8]>(&qf[0]));
-      unpack8<io_t>(qraw[1], *reinterpret_cast<float(*)[8]>(&qf[8]));
+      unpack8<io_t>(qraw2[0], *reinterpret_cast<float(*)[8]>(&qf[0]));
+      unpack8<io_t>(qraw2[1], *reinterpret_cast<float(*)[8]>(&qf[8]));
       float gr[16];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -618,10 +686,7 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
         float d = ld1(smem, kOffTG + col + t * 16) - ld1(smem, kOffTDY + col + t * 16) - ld1(smem, kOffNG + col + t * 16);
         if (t + 1 < kL) d += ld1(smem, kOffNS + col + (t + 1) * 16);
         if (t == len - 1) {
-          float e = end_part[0][kcol];
-#pragma unroll
-          for (int vb = 1; vb < 8; ++vb) e += end_part[vb][kcol];
-          d += e;
+          d += end_sum[kcol];
         }
         dsum[i] = t < len ? d : 0.f;
       }
@@ -654,7 +719,8 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
     umma::fence_before_sync();
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
     umma::fence_after_sync();
-    if (ok && item + (int)gridDim.x < num_items) stage_w(item + gridDim.x);  // the logits have been read
+    if (ok && has_next) stage_w(item + gridDim.x, nxt);  // the logits have been read
+    cur = nxt;
     if (!ok) {
       // fail closed: the gradients of this item's rows read as NaN
       const io_t nan16 = IO::store(quiet_nan());

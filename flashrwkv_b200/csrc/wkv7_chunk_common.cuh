@@ -36,8 +36,7 @@ __device__ __forceinline__ bool wait_warp(uint64_t* mbar, uint32_t parity, bool 
 // T_ii = (I - A_ii)^-1 (one thread per column, 16 right-looking steps), then the off-diagonal blocks in two levels
 // (inside the 32 x 32 halves, then the 32 x 32 block below them).  A block product is done by 32 threads with 2 x 4
 // register tiles and 16-byte operand reads (rows of A and of T, four adjacent columns of T and W).  Ends with T'
-// rounded to tf32 in rows 0..63 of the tile and zeros in rows 64..127 (the second operand half of MMA 3).  Contains barriers: every
-// thread calls it.
+// rounded to tf32 in rows 0..63 of the tile and zeros in rows 64..127 (the second operand half of MMA 3).  Contains barriers.
 __device__ __forceinline__ void fma_2x4(float (&acc)[2][4], const float4& a0, const float4& a1, const float4& t0,
                                         const float4& t1, const float4& t2, const float4& t3) {
   const float a[2][4] = {{a0.x, a0.y, a0.z, a0.w}, {a1.x, a1.y, a1.z, a1.w}};
@@ -51,8 +50,15 @@ __device__ __forceinline__ void fma_2x4(float (&acc)[2][4], const float4& a0, co
       for (int cc = 0; cc < 4; ++cc) acc[r][cc] = fmaf(a[r][k], t[k][cc], acc[r][cc]);
 }
 
-template <uint32_t kScratch, uint32_t kTile, uint32_t kCST, bool kTransposed>
+// kGroupThreads = 0: every thread of the CTA calls it and the barriers are CTA-wide.  kGroupThreads = 256: only
+// threads 0..255 call it (barriers on named barrier 1) and the other warps are free to do something else meanwhile.
+template <uint32_t kScratch, uint32_t kTile, uint32_t kCST, bool kTransposed, int kGroupThreads = 0>
 __device__ __forceinline__ void inverse_blocked(unsigned char* smem, int tid) {
+  static_assert(kGroupThreads == 0 || kGroupThreads == 256, "the last pass uses threads 0..255");
+  const auto group_sync = [] {
+    if (kGroupThreads == 0) __syncthreads();
+    else asm volatile("bar.sync 1, %0;" ::"n"(kGroupThreads) : "memory");
+  };
   // A: fp32 scratch at kScratch, row t = 256 bytes, 16-byte pieces permuted by the row pair (see aab_off);
   // T (then T' or T'^T) in rows 0..63 of the 128-row tile at kTile (chunk stride kCST), scratch W in rows 64..127
   const auto aab_off = [](int t, int s4) { return kScratch + uint32_t(t) * 256 + uint32_t((s4 ^ ((t >> 1) & 7)) * 16); };
@@ -72,7 +78,7 @@ __device__ __forceinline__ void inverse_blocked(unsigned char* smem, int tid) {
       for (int rr = q + 1; rr < 16; ++rr) acc[rr] = fmaf(aab(smem, 16 * blk + rr, 16 * blk + q), xq, acc[rr]);
     }
   }
-  __syncthreads();
+  group_sync();
   const int warp = tid >> 5, sub = tid & 31;
   const int rp = sub >> 2, cq = sub & 3;  // rows 2 rp, 2 rp + 1 and columns 4 cq .. 4 cq + 3 of a 16 x 16 block
   // One 16 x 16 x 16 block product per warp: acc += L[rows lr .. lr + 15][k] * R[k][columns rc .. rc + 15], k = 0..15.
@@ -111,7 +117,7 @@ __device__ __forceinline__ void inverse_blocked(unsigned char* smem, int tid) {
     product(acc, kFromA, j + 16, j, kFromT, j, j);
     store(false, 0, 16 * warp, acc);
   }
-  __syncthreads();
+  group_sync();
   // ---- step 1b: T_10 = T_11 W(0,0), T_32 = T_33 W(0,1) -----------------------------------------------------------
   if (warp < 2) {
     float acc[2][4] = {};
@@ -119,7 +125,7 @@ __device__ __forceinline__ void inverse_blocked(unsigned char* smem, int tid) {
     product(acc, kFromT, j + 16, j + 16, kFromW, 0, 16 * warp);
     store(true, j + 16, j, acc);
   }
-  __syncthreads();
+  group_sync();
   // ---- step 2a: W' = A21' T11': W'_p0 = A_{2+p,0} T_00 + A_{2+p,1} T_10, W'_p1 = A_{2+p,1} T_11; W'_pj in W(1+p, j) ---
   if (warp < 4) {
     float acc[2][4] = {};
@@ -132,7 +138,7 @@ __device__ __forceinline__ void inverse_blocked(unsigned char* smem, int tid) {
     }
     store(false, 16 * (1 + p), 16 * j, acc);
   }
-  __syncthreads();
+  group_sync();
   // ---- step 2b: T_lo = T22' W': T_2j = T_22 W'_0j, T_3j = T_32 W'_0j + T_33 W'_1j ----------------------------------
   if (warp < 4) {
     float acc[2][4] = {};
@@ -145,7 +151,7 @@ __device__ __forceinline__ void inverse_blocked(unsigned char* smem, int tid) {
     }
     store(true, 32 + 16 * i, 16 * j, acc);
   }
-  __syncthreads();
+  group_sync();
   {
     // T' = T - I, rounded; everything on and above the diagonal is zero (the blocks above it were never written).
     // kTransposed: the tile ends as T'^T (rows and columns exchanged through registers, behind a barrier).
@@ -162,7 +168,7 @@ __device__ __forceinline__ void inverse_blocked(unsigned char* smem, int tid) {
         if (col + 3 >= row) v[i].w = 0.f;
       }
     }
-    if (kTransposed) __syncthreads();
+    if (kTransposed) group_sync();
     if (tid < 256) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
