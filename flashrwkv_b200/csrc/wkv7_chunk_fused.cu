@@ -5,24 +5,25 @@
 // Per chunk with start state S0 (K x V), tokens t = 0..L-1, cumulative decay g_t = prod_{s<=t} w_s (g_{-1} = 1):
 //     A~ = a*g_{t-1}   R~ = r*g_t   B~ = b/g_t   K~ = k/g_t   B^ = B~*g_L   K^ = K~*g_L              (L x K)
 //     [A_ab | A_ak ; A_rb | A_rk] = [A~ ; R~] [B~ ; K~]^T, masked (strictly lower for A_a*, lower for A_r*)
-//     T  = (I - A_ab)^-1 = I + T'
-//     X  = A~ S0 + A_ak V          U = X + T' X   (rows u_t = S_{t-1}^T a_t, the reference's state_dot_a)
+//     X  = A~ S0 + A_ak V          U = (I - A_ab)^-1 X   (rows u_t = S_{t-1}^T a_t, the reference's state_dot_a)
 //     Y  = scale * (R~ S0 + A_rk V + A_rb U)
 //     S' = diag(g_L) (S0 + B~^T U + K~^T V)
 //
 // Tensor memory carries the operands from one product to the next (row i of a matrix = lane i):
 //     XA  (64 columns)  lanes 0..63 A~, lanes 64..127 R~            written with tcgen05.st, operand A of MMA 1 and 2
-//     D1  (128 columns) result of MMA 1; masked and rounded in place; the A_ab block (needed only by the inverse)
-//                       is replaced by B~^T, after MMA 2 the A_ak block by K~^T and the A_rk block by zeros, so that
-//                       D1 as a whole is operand A of MMA 4:  [B~^T | K~^T ; A_rb | 0] [U ; V].  B~^T and K~^T are
-//                       columns of the [B~;K~] tile read back from shared memory by the thread that owns the lane.
-//     DA  (64 columns)  MMA 2: XA S0 + D1[:,64:128] V  = [X ; R~ S0 + A_rk V];  MMA 3 adds [T' ; 0] X  ->  [U ; .]
-//     DC  (= XA's columns, free by then)  MMA 4:  [B~^T U + K~^T V ; A_rb U]
+//     D1  (128 columns) result of MMA 1; masked and rounded in place; the A_ab block (needed only by the solve, which
+//                       reads it from shared memory) is replaced by B~^T, after MMA 2 the A_ak block by K~^T and the
+//                       A_rk block by zeros, so that D1 as a whole is operand A of MMA 3:
+//                       [B~^T | K~^T ; A_rb | 0] [U ; V].  B~^T and K~^T are columns of the [B~;K~] tile read back
+//                       from shared memory by the thread that owns the lane.
+//     DA  (64 columns)  MMA 2: XA S0 + D1[:,64:128] V  = [X ; R~ S0 + A_rk V]
+//     DC  (= XA's columns, free by then)  MMA 3:  [B~^T U + K~^T V ; A_rb U]
 // All products are tcgen05.mma kind::tf32 with fp32 accumulation; operands are rounded to tf32 (nearest) once.  The
 // B operands contract over tokens or keys that their producers own as rows, so they are written transposed with
 // 4-byte stores into 64-row tiles whose chunk stride (1040 bytes) keeps those stores free of bank conflicts.  The
-// 64 x 64 unit-triangular inverse runs in fp32 on the CUDA cores (16 x 16 blocks, 2 x 4 register tiles).  The state
-// stays in fp32 registers; only its rounded copy is an operand.
+// unit-triangular system (I - A_ab) U = X is solved in fp32 on the CUDA cores by blocked forward substitution (one
+// thread per value column and block of 16 tokens); the inverse is never formed.  The state stays in fp32 registers;
+// only its rounded copy is an operand.
 //
 // 256 threads, 105 KB of shared memory and 256 tensor-memory columns per CTA: two CTAs share an SM, so one CTA's
 // barrier-separated phases overlap the other's.  The loop body is kept small on purpose (rolled loops, 16-column
@@ -45,12 +46,11 @@ constexpr int kL = 64;
 constexpr int kD = 64;
 constexpr int kThreads = 256;
 constexpr uint32_t kCSB = 2064;   // chunk stride of [B~;K~]  (128 rows, written row-wise, read back column-wise)
-constexpr uint32_t kCST = 2064;   // ... of [T';0]            (128 rows, written column-wise)
 constexpr uint32_t kCS64 = 1040;  // ... of the 64-row transposed tiles and of g
 
 constexpr uint32_t kOffG = 0;                        // g[t][k], chunk-major, 16 x 1040
-constexpr uint32_t kOffX2 = kOffG + 16 * kCS64;      // [B~;K~], later [T';0]
-constexpr uint32_t kOffUV = kOffX2 + 16 * kCST;      // [U^T | V^T]: 32 chunks x 1040; the U half first holds A_ab
+constexpr uint32_t kOffX2 = kOffG + 16 * kCS64;      // [B~;K~], later X^T -> U^T (fp32, 64-row tile) during the solve
+constexpr uint32_t kOffUV = kOffX2 + 16 * kCSB;      // [U^T | V^T]: 32 chunks x 1040; the U half first holds A_ab^T
 constexpr uint32_t kOffS = kOffUV + 32 * kCS64;      // S0^T
 constexpr uint32_t kOffW = kOffS + 16 * kCS64;       // the chunk's decay logits as they are in HBM: [64][64] 16-bit
 constexpr uint32_t kFusedSmem = kOffW + kL * kD * 2; // 107,776 bytes
@@ -60,10 +60,6 @@ static_assert(64 * 256 <= 16 * kCS64, "the A_ab scratch must fit the U half");
 static_assert(2 * (kFusedSmem + 1024) <= 233472, "two CTAs must fit one SM");
 
 constexpr uint32_t kColXA = 0, kColD1 = 64, kColDA = 192, kColDC = 0, kTmemCols = 256;
-
-// A_ab scratch: row t is 256 bytes; its 16-byte pieces are permuted by the row pair so that the inverse's threads,
-// which read the same piece of eight different row pairs at once, hit different banks.
-__device__ __forceinline__ uint32_t aab_off(int t, int s4) { return kOffUV + uint32_t(t) * 256 + uint32_t((s4 ^ ((t >> 1) & 7)) * 16); }
 
 // kAdj = false: the forward recurrence.  kAdj = true: the same kernel walks every sequence BACKWARDS (last chunk
 // first, last token of a chunk first) and takes its key rows from an fp32 tensor: this is how the backward pass gets
@@ -83,7 +79,7 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
     int num_units, long long output_elements, float scale, int* __restrict__ error_flag) {
   using IO = Io16<io_t>;
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ uint64_t mbar[4];
+  __shared__ uint64_t mbar[3];
   __shared__ uint32_t tmem_holder;
   __shared__ float seg_total[4][64];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -103,7 +99,7 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
   const int c0 = 32 * half;
   if (tid == 0) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) umma::mbar_init(&mbar[i], 1);
+    for (int i = 0; i < 3; ++i) umma::mbar_init(&mbar[i], 1);
     umma::mbar_fence_init();
   }
   if (warp == 0) umma::tmem_alloc(&tmem_holder, kTmemCols);
@@ -320,13 +316,10 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
           umma::tmem_ld_wait();
           const int s0 = 16 * hb;
           if (low && half == 0) {
+            // A_ab^T: element [s][t] at 256 s + 4 t bytes (the lanes of a warp are consecutive t: consecutive words)
 #pragma unroll
-            for (int j = 0; j < 16; j += 4)
-              st4(smem, aab_off(mt, (s0 + j) >> 2),
-                  make_float4(s0 + j < limit ? __uint_as_float(u[j]) : 0.f,
-                              s0 + j + 1 < limit ? __uint_as_float(u[j + 1]) : 0.f,
-                              s0 + j + 2 < limit ? __uint_as_float(u[j + 2]) : 0.f,
-                              s0 + j + 3 < limit ? __uint_as_float(u[j + 3]) : 0.f));
+            for (int j = 0; j < 16; ++j)
+              st1(smem, kOffUV + uint32_t(s0 + j) * 256 + uint32_t(mt) * 4, s0 + j < limit ? __uint_as_float(u[j]) : 0.f);
           } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) u[j] = s0 + j < limit ? tf32_bits(__uint_as_float(u[j])) : 0u;
@@ -351,7 +344,7 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
                             umma::desc_k_major(sbase + kOffUV + (16 + 2 * ks) * kCS64, kCS64), idesc64, 1u);
         umma::mma_commit(&mbar[1]);
       }
-      // Meanwhile the key rows of MMA 4's operand: lane k gets column k of the [B~;K~] tile.  B~^T goes over the A_ab
+      // Meanwhile the key rows of MMA 3's operand: lane k gets column k of the [B~;K~] tile.  B~^T goes over the A_ab
       // block at once (every reader of that block passed the barrier above); K~^T waits in registers for MMA 2,
       // which still reads the A_ak block it will replace.
       uint32_t kt[32];
@@ -375,10 +368,8 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
       umma::tmem_st32(tmem + kColD1 + 64 + lane_base + c0, kt);
       umma::tmem_st_wait();
       umma::fence_before_sync();
-      __syncthreads();  // the [B~;K~] tile has been read: the inverse may build T' over it
-      inverse_blocked<kOffUV, kOffX2, kCST, false>(smem, tid);
-      __syncthreads();
-      // ---- epilogue 2: X^T -> shared memory (over the A_ab scratch, which the inverse has consumed) -----------------
+      __syncthreads();  // the [B~;K~] tile has been read: X^T may go over it
+      // ---- epilogue 2: X^T (fp32, unrounded) -> shared memory, over the [B~;K~] tile --------------------------------
       umma::fence_after_sync();
       if (ok && low) {
 #pragma unroll 1
@@ -386,43 +377,78 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
           uint32_t u[16];
           umma::tmem_ld16(tmem + kColDA + lane_base + c0 + 16 * hb, u);
           umma::tmem_ld_wait();
-          const uint32_t o = kOffUV + uint32_t(mt >> 2) * kCS64 + uint32_t(mt & 3) * 4 + (c0 + 16 * hb) * 16;
+          const uint32_t o = kOffX2 + uint32_t(mt >> 2) * kCS64 + uint32_t(mt & 3) * 4 + (c0 + 16 * hb) * 16;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) st1(smem, o + j * 16, umma::to_tf32(__uint_as_float(u[j])));
+          for (int j = 0; j < 16; ++j) st1(smem, o + j * 16, __uint_as_float(u[j]));
         }
       }
-      umma::fence_async_smem();
-      umma::fence_before_sync();
       __syncthreads();
-      umma::fence_after_sync();
-
-      // ---- MMA 3: DA += [T';0] X ----------------------------------------------------------------------------------
-      if (tid == 0) {
+      // ---- U = (I - A_ab)^-1 X by blocked forward substitution in fp32, U_t = X_t + sum_{s < t} A_ab[t][s] U_s.
+      //      Thread (value column v, block j) holds rows 16 j .. 16 j + 15 of column v.  From the first block to the
+      //      last: the owners of block jb finish it (a 16 x 16 triangular solve in registers) and publish it; the owners
+      //      of later blocks fold it in (a 16 x 16 update).  T = (I - A_ab)^-1 is never formed. ---------------------------
+      {
+        const int v = tid & 63, j = tid >> 6;
+        float x[16];
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma::mma_tf32_ss(tmem + kColDA, umma::desc_k_major(sbase + kOffX2 + ks * 2 * kCST, kCST),
-                            umma::desc_k_major(sbase + kOffUV + ks * 2 * kCS64, kCS64), idesc64, 1u);
-        umma::mma_commit(&mbar[2]);
-      }
-      ok = wait_warp(&mbar[2], parity, ok);
-      umma::fence_after_sync();
-      // ---- epilogue 3: U -> state_dot_a (optional) and U^T over X^T ----------------------------------------------
-      if (ok && low) {
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const float4 q = ld4(smem, kOffX2 + (4 * j + c4) * kCS64 + v * 16);
+          x[4 * c4] = q.x; x[4 * c4 + 1] = q.y; x[4 * c4 + 2] = q.z; x[4 * c4 + 3] = q.w;
+        }
 #pragma unroll 1
-        for (int hb = 0; hb < 2; ++hb) {
-          uint32_t u[16];
-          umma::tmem_ld16(tmem + kColDA + lane_base + c0 + 16 * hb, u);
-          umma::tmem_ld_wait();
-          if (sda_ptr != nullptr && valid) {
-            float* dst = sda_ptr + (long long)token_row(t0, len, mt) * row_stride + head_off + c0 + 16 * hb;
+        for (int jb = 0; jb < 4; ++jb) {
+          if (j == jb) {
+            const uint32_t acol = kOffUV + uint32_t(16 * jb) * 256 + uint32_t(16 * jb) * 4;  // A_ab^T[16 jb][16 jb]
 #pragma unroll
-            for (int j = 0; j < 16; j += 4)
-              *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(u[j]), __uint_as_float(u[j + 1]),
-                                                                __uint_as_float(u[j + 2]), __uint_as_float(u[j + 3]));
+            for (int tt = 0; tt < 15; ++tt) {
+              const float xt = x[tt];
+#pragma unroll
+              for (int q4 = (tt + 1) >> 2; q4 < 4; ++q4) {
+                const float4 a4 = ld4(smem, acol + tt * 256 + q4 * 16);  // A_ab[16 jb + 4 q4 ..][16 jb + tt]
+                if (4 * q4 > tt) x[4 * q4] = fmaf(a4.x, xt, x[4 * q4]);
+                if (4 * q4 + 1 > tt) x[4 * q4 + 1] = fmaf(a4.y, xt, x[4 * q4 + 1]);
+                if (4 * q4 + 2 > tt) x[4 * q4 + 2] = fmaf(a4.z, xt, x[4 * q4 + 2]);
+                x[4 * q4 + 3] = fmaf(a4.w, xt, x[4 * q4 + 3]);
+              }
+            }
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4)
+              st4(smem, kOffX2 + (4 * j + c4) * kCS64 + v * 16, make_float4(x[4 * c4], x[4 * c4 + 1], x[4 * c4 + 2], x[4 * c4 + 3]));
           }
-          const uint32_t o = kOffUV + uint32_t(mt >> 2) * kCS64 + uint32_t(mt & 3) * 4 + (c0 + 16 * hb) * 16;
+          __syncthreads();
+          if (j > jb) {
+            float xb[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) st1(smem, o + j * 16, umma::to_tf32(__uint_as_float(u[j])));
+            for (int c4 = 0; c4 < 4; ++c4) {
+              const float4 q = ld4(smem, kOffX2 + (4 * jb + c4) * kCS64 + v * 16);
+              xb[4 * c4] = q.x; xb[4 * c4 + 1] = q.y; xb[4 * c4 + 2] = q.z; xb[4 * c4 + 3] = q.w;
+            }
+            const uint32_t acol = kOffUV + uint32_t(16 * jb) * 256 + uint32_t(16 * j) * 4;  // A_ab^T[16 jb][16 j]
+#pragma unroll
+            for (int tt = 0; tt < 16; ++tt) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                const float4 a4 = ld4(smem, acol + tt * 256 + q4 * 16);
+                x[4 * q4] = fmaf(a4.x, xb[tt], x[4 * q4]);
+                x[4 * q4 + 1] = fmaf(a4.y, xb[tt], x[4 * q4 + 1]);
+                x[4 * q4 + 2] = fmaf(a4.z, xb[tt], x[4 * q4 + 2]);
+                x[4 * q4 + 3] = fmaf(a4.w, xb[tt], x[4 * q4 + 3]);
+              }
+            }
+          }
+        }
+        // every block has been read and A_ab^T with it: U rows -> state_dot_a (optional), U^T rounded over A_ab^T
+        if (ok) {
+          if (sda_ptr != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              if (16 * j + e < len)
+                sda_ptr[(long long)token_row(t0, len, 16 * j + e) * row_stride + head_off + v] = x[e];
+          }
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4)
+            st4(smem, kOffUV + (4 * j + c4) * kCS64 + v * 16,
+                umma::to_tf32(make_float4(x[4 * c4], x[4 * c4 + 1], x[4 * c4 + 2], x[4 * c4 + 3])));
         }
       }
       umma::fence_async_smem();
@@ -430,17 +456,17 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
       __syncthreads();
       umma::fence_after_sync();
 
-      // ---- MMA 4: DC = D1 [U ; V] ---------------------------------------------------------------------------------
+      // ---- MMA 3: DC = D1 [U ; V] ---------------------------------------------------------------------------------
       if (tid == 0) {
 #pragma unroll
         for (int ks = 0; ks < 16; ++ks)
           umma::mma_tf32_ts(tmem + kColDC, tmem + kColD1 + 8 * ks,
                             umma::desc_k_major(sbase + kOffUV + ks * 2 * kCS64, kCS64), idesc64, ks > 0 ? 1u : 0u);
-        umma::mma_commit(&mbar[3]);
+        umma::mma_commit(&mbar[2]);
       }
-      ok = wait_warp(&mbar[3], parity, ok);
+      ok = wait_warp(&mbar[2], parity, ok);
       umma::fence_after_sync();
-      // ---- epilogue 4: Y rows out; S' = g_L (S + DC) -> registers, S0^T, boundary / state pool ----------------------
+      // ---- epilogue 3: Y rows out; S' = g_L (S + DC) -> registers, S0^T, boundary / state pool ----------------------
       if (ok) {
         uint32_t u[32];
         umma::tmem_ld32(tmem + kColDC + lane_base + c0, u);
