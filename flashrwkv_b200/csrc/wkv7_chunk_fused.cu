@@ -57,6 +57,13 @@ constexpr uint32_t kFusedSmem = kOffW + kL * kD * 2; // 107,776 bytes
 static_assert(kOffX2 % 128 == 0 && kOffUV % 128 == 0 && kOffS % 128 == 0 && kOffW % 128 == 0,
               "tile bases must stay 128-byte aligned");
 static_assert(64 * 256 <= 16 * kCS64, "the A_ab scratch must fit the U half");
+// The token rows of the next chunk are staged as they are in HBM over the [B~;K~] and [U^T|V^T] tiles, which are
+// free between a chunk's last product and the next chunk's operand phase: five tiles of 64 rows, rows padded by 16
+// bytes so that the threads of a warp, which read consecutive rows, hit different banks.
+constexpr uint32_t kRawRow16 = 144, kRawRow32 = 272;
+constexpr uint32_t kRawA = kOffX2, kRawR = kRawA + 64 * kRawRow16, kRawB = kRawR + 64 * kRawRow16,
+                   kRawV = kRawB + 64 * kRawRow16, kRawK = kRawV + 64 * kRawRow16;
+static_assert(kRawK + 64 * kRawRow32 <= kOffS, "the staged rows must fit the two free tiles");
 static_assert(2 * (kFusedSmem + 1024) <= 233472, "two CTAs must fit one SM");
 
 constexpr uint32_t kColXA = 0, kColD1 = 64, kColDA = 192, kColDC = 0, kTmemCols = 256;
@@ -132,6 +139,38 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
     umma::cp_async_commit();
   };
 
+  // The a, r, b, k (or, in the adjoint run, fp32 key) and v rows of a chunk, copied as 16-byte pieces with eight (sixteen)
+  // consecutive lanes per row: whole 128-byte lines per request.  Read straight into registers by the thread that owns
+  // a row, the same rows cost a tag lookup per lane and request, which made the loads the longest stall of a chunk.
+  auto stage_rows = [&](int tt0, int ln, long long head_off) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int piece = tid + i * kThreads, which = piece >> 9, rowi = (piece >> 3) & 63, part = piece & 7;
+      const io_t* base = which == 0 ? a_ptr : which == 1 ? r_ptr : which == 2 ? b_ptr : v_ptr;
+      umma::cp_async16(sbase + kRawA + which * (64 * kRawRow16) + rowi * kRawRow16 + part * 16,
+                       base + (long long)token_row(tt0, ln, min(rowi, ln - 1)) * row_stride + head_off + 8 * part,
+                       rowi < ln ? 16u : 0u);
+    }
+    if (!kAdj) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int piece = tid + i * kThreads, rowi = piece >> 3, part = piece & 7;
+        umma::cp_async16(sbase + kRawK + rowi * kRawRow16 + part * 16,
+                         k_ptr + (long long)token_row(tt0, ln, min(rowi, ln - 1)) * row_stride + head_off + 8 * part,
+                         rowi < ln ? 16u : 0u);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int piece = tid + i * kThreads, rowi = piece >> 4, part = piece & 15;
+        umma::cp_async16(sbase + kRawK + rowi * kRawRow32 + part * 16,
+                         khat_ptr + (long long)token_row(tt0, ln, min(rowi, ln - 1)) * row_stride + head_off + 4 * part,
+                         rowi < ln ? 16u : 0u);
+      }
+    }
+    umma::cp_async_commit();
+  };
+
   // g[t][k] of a chunk: (1) thread (token, 16 channels): retention of the staged logits, row-wise into the g tile;
   // (2) thread (key channel, 16-token segment): running product down the column, segment totals, prefix fix-up.
   // Runs one chunk ahead of its use (while the tensor core does MMA 1 of the previous chunk) and starts the copy of
@@ -189,6 +228,10 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
     const long long head_off = (long long)head * kD;
     const int n_chunks = c_end - c_begin, c_step = kAdj ? -1 : 1, c_first = kAdj ? c_end - 1 : c_begin;
     stage_w(c_first, head_off);
+    {
+      const int ft0 = chunk_starts[c_first];
+      stage_rows(ft0, min(max(chunk_ends[c_first] - ft0, 1), kL), head_off);
+    }
 
     // ---- this unit's state: row mt, columns c0..c0+31 in registers (fp32) and, transposed and rounded, in S0^T ----
     float S[32];
@@ -216,27 +259,29 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
         next_t0 = chunk_starts[c + c_step];
         next_end = chunk_ends[c + c_step];
       }
-      // ---- this thread's operand rows leave HBM / L2 now and are used after the decay scan ----------------------
+      // ---- this thread's operand rows, from the staged tiles (rows past the end of a short chunk were zero-filled) --
       const bool valid = mt < len;
       uint4 praw[4], qraw[kAdj ? 8 : 4], vraw[4];
+      umma::cp_async_wait_all();
+      __syncthreads();
       {
-        const long long row = (long long)token_row(t0, len, min(mt, len - 1)) * row_stride + head_off + c0;
-        const uint4* pp = reinterpret_cast<const uint4*>((low ? a_ptr : r_ptr) + row);
-        const uint4* qp = reinterpret_cast<const uint4*>((low ? b_ptr : k_ptr) + row);
-        const uint4* vp = reinterpret_cast<const uint4*>(v_ptr + row);
+        const uint32_t rp = (low ? kRawA : kRawR) + mt * kRawRow16 + c0 * 2;
+        const uint32_t rq = low ? kRawB + mt * kRawRow16 + c0 * 2
+                                : (kAdj ? kRawK + mt * kRawRow32 + c0 * 4 : kRawK + mt * kRawRow16 + c0 * 2);
+        const uint32_t rv = kRawV + mt * kRawRow16 + c0 * 2;
         const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          praw[i] = valid ? __ldg(pp + i) : zero;
-          qraw[i] = valid && (!kAdj || low) ? __ldg(qp + i) : zero;
-          vraw[i] = (valid && !low) ? __ldg(vp + i) : zero;
+          praw[i] = *reinterpret_cast<const uint4*>(smem + rp + 16 * i);
+          qraw[i] = *reinterpret_cast<const uint4*>(smem + rq + 16 * i);
+          vraw[i] = !low ? *reinterpret_cast<const uint4*>(smem + rv + 16 * i) : zero;
         }
-        if (kAdj && !low) {  // the adjoint run's key rows are fp32: 32 channels = eight 16-byte pieces
-          const uint4* kp = reinterpret_cast<const uint4*>(khat_ptr + row);
+        if (kAdj) {  // the adjoint run's key rows are fp32: 32 channels = eight 16-byte pieces
 #pragma unroll
-          for (int i = 0; i < 8; ++i) qraw[i] = valid ? __ldg(kp + i) : zero;
+          for (int i = 4; i < 8; ++i) qraw[kAdj ? i : 0] = !low ? *reinterpret_cast<const uint4*>(smem + rq + 16 * i) : zero;
         }
       }
+      __syncthreads();  // the staged tiles have been read: the operand tiles may go over them
 
       // ---- operands: XA -> tensor memory, [B~;K~] and V^T -> shared memory -------------------------------------
       const float g_last = low ? ld1(smem, kOffG + tile_off(kCS64, 63, mt)) : 0.f;  // g_L of key row mt
@@ -466,6 +511,8 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
       }
       ok = wait_warp(&mbar[2], parity, ok);
       umma::fence_after_sync();
+      // the last product has read its tiles: the next chunk's rows start their way into them
+      if (has_next && ok) stage_rows(next_t0, min(max(next_end - next_t0, 1), kL), head_off);
       // ---- epilogue 3: Y rows out; S' = g_L (S + DC) -> registers, S0^T, boundary / state pool ----------------------
       if (ok) {
         uint32_t u[32];
