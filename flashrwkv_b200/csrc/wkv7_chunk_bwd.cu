@@ -56,6 +56,12 @@ static_assert(kOffRA % 128 == 0 && kOffRB % 128 == 0 && kOffTBK % 128 == 0 && kO
                   kOffTG % 128 == 0 && kOffNG % 128 == 0 && kOffNS % 128 == 0 && kOffW % 128 == 0,
               "tile bases must stay 128-byte aligned");
 static_assert(kBwdSmem + 2048 <= 232448, "the CTA must fit one SM's shared memory");
+// The a, r, b, k and dy rows of the next item are staged as they are in HBM over the [dX;dY'] and [B~^T|K~^T] tiles,
+// which are free from the fourth product group on: five tiles of 64 rows, rows padded by 16 bytes so that the threads
+// of a warp, which read consecutive rows, hit different banks.
+constexpr uint32_t kRawRow = 144;
+constexpr uint32_t kRawBase = kOffRB;
+static_assert(kRawBase + 5 * 64 * kRawRow <= kOffTAR, "the staged rows must fit the two free tiles");
 
 constexpr uint32_t kColXA = 0, kColXB = 64, kColD1 = 128, kColD1T = 256, kColDUV = 384;
 constexpr uint32_t kColOUT1 = kColXB, kColDD = kColD1, kColDDT = kColD1T, kColOUT2 = kColDUV;
@@ -133,8 +139,25 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
                      rowi < im.len ? 16u : 0u);
     umma::cp_async_commit();
   };
+  // ... and so do its a, r, b, k and dy rows, as 16-byte pieces with eight consecutive lanes per row (whole 128-byte
+  // lines per request; read straight into registers by the thread that owns a row they cost a tag lookup per lane)
+  auto stage_rows = [&](int item, const ItemMeta& im) {
+    const long long hoff = (long long)(item % num_heads) * kD;
+#pragma unroll
+    for (int i = 0; i < 5; ++i) {
+      const int rowi = tid >> 3, part = tid & 7;
+      const io_t* base = i == 0 ? a_ptr : i == 1 ? r_ptr : i == 2 ? b_ptr : i == 3 ? k_ptr : dy_ptr;
+      umma::cp_async16(sbase + kRawBase + i * (64 * kRawRow) + rowi * kRawRow + part * 16,
+                       base + (long long)(im.t0 + min(rowi, im.len - 1)) * row_stride + hoff + 8 * part,
+                       rowi < im.len ? 16u : 0u);
+    }
+    umma::cp_async_commit();
+  };
   ItemMeta cur = item_meta(min((int)blockIdx.x, num_items - 1));
-  if ((int)blockIdx.x < num_items) stage_w(blockIdx.x, cur);
+  if ((int)blockIdx.x < num_items) {
+    stage_w(blockIdx.x, cur);
+    stage_rows(blockIdx.x, cur);
+  }
 
   for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, parity ^= 1u) {
     const int chunk = item / num_heads, head = item % num_heads;
@@ -148,24 +171,23 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
     const float* g_end = adjoint + ((long long)chunk * num_heads + head) * (kD * kD);
     const long long row = (long long)(t0 + min(mt, len - 1)) * row_stride + head_off + ch0;
 
-    // ---- this thread's rows: 16 channels of (a, b) or (r, k, dy) ------------------------------------------------
+    // ---- this thread's rows: 16 channels of (a, b) or (r, k, dy), from the staged tiles (rows past the end of a short
+    //      chunk were zero-filled) ----------------------------------------------------------------------------------------
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
     uint4 praw[2], qraw[2], draw[2];
+    umma::cp_async_wait_all();
+    __syncthreads();
     {
-      const uint4* pp = reinterpret_cast<const uint4*>((low ? a_ptr : r_ptr) + row);
-      const uint4* qp = reinterpret_cast<const uint4*>((low ? b_ptr : k_ptr) + row);
-      const uint4* dp = reinterpret_cast<const uint4*>(dy_ptr + row);
+      const uint32_t at = kRawBase + uint32_t(mt) * kRawRow + uint32_t(ch0) * 2;
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        praw[i] = valid ? __ldg(pp + i) : zero4;
-        qraw[i] = valid ? __ldg(qp + i) : zero4;
-        draw[i] = (valid && !low) ? __ldg(dp + i) : zero4;
+        praw[i] = *reinterpret_cast<const uint4*>(smem + at + (low ? 0 : 1) * (64 * kRawRow) + 16 * i);
+        qraw[i] = *reinterpret_cast<const uint4*>(smem + at + (low ? 2 : 3) * (64 * kRawRow) + 16 * i);
+        draw[i] = !low ? *reinterpret_cast<const uint4*>(smem + at + 4 * (64 * kRawRow) + 16 * i) : zero4;
       }
     }
     const bool has_next = item + (int)gridDim.x < num_items;
     // ---- g[t][k] (as in the forward kernel; threads 0..255 work) ------------------------------------------------
-    umma::cp_async_wait_all();
-    __syncthreads();
     if (tid < 256) {
       const int t = tid >> 2, q = tid & 3;
       float x[16];
@@ -579,6 +601,8 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
     }
     ok = wait_warp(&mbar[3], parity, ok);
     umma::fence_after_sync();
+    // the [dX;dY'] and [B~^T|K~^T] tiles have been read for the last time: the next item's rows start their way in
+    if (ok && has_next) stage_rows(item + gridDim.x, nxt);
     // ---- DDT masked in place ([s][t] kept for t > s in the dX columns, t >= s in the dY' columns); da, dr out ------
     if (ok) {
       uint32_t u[16];
