@@ -41,6 +41,14 @@ inline int check_launch(const char* what) {
     if (!(cond)) return ::frwkv::fail(FRWKV_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
   } while (0)
 
+// true when every pointer (null pointers, i.e. absent optional arguments, aside) is a multiple of 32 bytes: the kernels
+// move token rows and state tiles as 16- and 32-byte vectors, and a misaligned one would fault on the device
+inline bool aligned32() { return true; }
+template <typename... Rest>
+inline bool aligned32(const void* p, Rest... rest) {
+  return (reinterpret_cast<uintptr_t>(p) & 31u) == 0 && aligned32(rest...);
+}
+
 // ---- 16-bit io -----------------------------------------------------------------------------
 template <typename T>
 struct Io16;
@@ -141,6 +149,20 @@ inline cudaError_t launch_chained(void (*kernel)(KernelArgs...), dim3 grid, dim3
   cfg.attrs = attr;
   cfg.numAttrs = chained_launch_enabled() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KernelArgs>(args)...);
+}
+
+// 32-byte global accesses (sm_100: one request instead of two).  A thread that owns a token row reads or writes a
+// run of its own row, so the lanes of a warp touch 32 different lines; the tag lookups, one per line and request,
+// are what such accesses cost, and half as many requests cost half as much.  Addresses must be 32-byte aligned.
+__device__ __forceinline__ void ldg256(const void* p, uint4& a, uint4& b) {
+  asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
+               : "l"(p));
+}
+__device__ __forceinline__ void stg256(void* p, const uint4& a, const uint4& b) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+               "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+               : "memory");
 }
 
 }  // namespace frwkv

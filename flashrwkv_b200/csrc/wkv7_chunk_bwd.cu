@@ -389,7 +389,11 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
     {
       const uint4* up = low ? reinterpret_cast<const uint4*>(sda_ptr + row) : reinterpret_cast<const uint4*>(v_ptr + row);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) uvraw[i] = (valid && (low || i < 2)) ? __ldg(up + i) : zero4;
+      for (int i = 0; i < 4; ++i) uvraw[i] = zero4;
+      if (valid) {
+        ldg256(up, uvraw[0], uvraw[1]);
+        if (low) ldg256(up + 2, uvraw[2], uvraw[3]);
+      }
     }
     ok = wait_warp(&mbar[1], parity, ok);
     umma::fence_after_sync();
@@ -568,8 +572,7 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
         p1.x = IO::pack(__uint_as_float(u[8]), __uint_as_float(u[9])); p1.y = IO::pack(__uint_as_float(u[10]), __uint_as_float(u[11]));
         p1.z = IO::pack(__uint_as_float(u[12]), __uint_as_float(u[13])); p1.w = IO::pack(__uint_as_float(u[14]), __uint_as_float(u[15]));
         uint4* dst = reinterpret_cast<uint4*>(dv_ptr + row);
-        dst[0] = p0;
-        dst[1] = p1;
+        stg256(dst, p0, p1);
       }
       umma::tmem_st_wait();
     }
@@ -596,8 +599,8 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
     uint4 praw2[2];
     {
       const uint4* pp = reinterpret_cast<const uint4*>((low ? a_ptr : r_ptr) + row);
-      praw2[0] = valid ? __ldcg(pp) : zero4;
-      praw2[1] = valid ? __ldcg(pp + 1) : zero4;
+      praw2[0] = zero4; praw2[1] = zero4;
+      if (valid) ldg256(pp, praw2[0], praw2[1]);
     }
     ok = wait_warp(&mbar[3], parity, ok);
     umma::fence_after_sync();
@@ -641,8 +644,7 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
         p0.x = IO::pack(gr[0], gr[1]); p0.y = IO::pack(gr[2], gr[3]); p0.z = IO::pack(gr[4], gr[5]); p0.w = IO::pack(gr[6], gr[7]);
         p1.x = IO::pack(gr[8], gr[9]); p1.y = IO::pack(gr[10], gr[11]); p1.z = IO::pack(gr[12], gr[13]); p1.w = IO::pack(gr[14], gr[15]);
         uint4* dst = reinterpret_cast<uint4*>((low ? da_ptr : dr_ptr) + row);
-        dst[0] = p0;
-        dst[1] = p1;
+        stg256(dst, p0, p1);
       }
       umma::tmem_st_wait();
     }
@@ -664,8 +666,8 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
     uint4 qraw2[2];  // ... and its b or k channels
     {
       const uint4* qp = reinterpret_cast<const uint4*>((low ? b_ptr : k_ptr) + row);
-      qraw2[0] = valid ? __ldcg(qp) : zero4;
-      qraw2[1] = valid ? __ldcg(qp + 1) : zero4;
+      qraw2[0] = zero4; qraw2[1] = zero4;
+      if (valid) ldg256(qp, qraw2[0], qraw2[1]);
     }
     ok = wait_warp(&mbar[4], parity, ok);
     umma::fence_after_sync();
@@ -693,8 +695,7 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
         p0.x = IO::pack(gr[0], gr[1]); p0.y = IO::pack(gr[2], gr[3]); p0.z = IO::pack(gr[4], gr[5]); p0.w = IO::pack(gr[6], gr[7]);
         p1.x = IO::pack(gr[8], gr[9]); p1.y = IO::pack(gr[10], gr[11]); p1.z = IO::pack(gr[12], gr[13]); p1.w = IO::pack(gr[14], gr[15]);
         uint4* dst = reinterpret_cast<uint4*>((low ? db_ptr : dk_ptr) + row);
-        dst[0] = p0;
-        dst[1] = p1;
+        stg256(dst, p0, p1);
       }
     }
     __syncthreads();
@@ -810,6 +811,9 @@ extern "C" int frwkv_wkv7_chunk_backward(
                 "wkv7_chunk_backward: null pointer argument");
   FRWKV_REQUIRE(num_sequences > 0 && num_chunks > 0 && num_heads > 0 && total_tokens > 0,
                 "wkv7_chunk_backward: sizes must be positive");
+  FRWKV_REQUIRE(aligned32(final_state, boundary, boundary_adjoint, state_dot_a, r, decay_logits, k, v, a, b, decay_bias,
+                          grad_output, grad_r, grad_decay_logits, grad_k, grad_v, grad_a, grad_b),
+                "wkv7_chunk_backward: tensor pointers must be 32-byte aligned");
   if (head_size != 64)
     return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_chunk_backward: head size %d is not built (only 64)", head_size);
   FRWKV_REQUIRE((long long)num_chunks * num_heads <= 0x7fffffffLL, "wkv7_chunk_backward: too many (chunk, head) pairs");

@@ -528,7 +528,9 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
           for (int j = 0; j < 32; ++j) S[j] = g_last * (S[j] + __uint_as_float(u[j]));
           if (dst != nullptr) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+            for (int j = 0; j < 32; j += 8)
+              stg256(dst + j, make_uint4(__float_as_uint(S[j]), __float_as_uint(S[j + 1]), __float_as_uint(S[j + 2]), __float_as_uint(S[j + 3])),
+                     make_uint4(__float_as_uint(S[j + 4]), __float_as_uint(S[j + 5]), __float_as_uint(S[j + 6]), __float_as_uint(S[j + 7])));
           }
           if (!last) {
 #pragma unroll
@@ -541,18 +543,22 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
           if (valid && y_ptr != nullptr) {
             const long long row = (long long)token_row(t0, len, mt) * row_stride + head_off + c0;
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float o[8];
+            for (int j = 0; j < 32; j += 16) {
+              uint4 packed[2];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) o[e] = scale * (__uint_as_float(u[j + e]) + __uint_as_float(u2[j + e]));
-              uint4 packed;
-              packed.x = IO::pack(o[0], o[1]); packed.y = IO::pack(o[2], o[3]);
-              packed.z = IO::pack(o[4], o[5]); packed.w = IO::pack(o[6], o[7]);
-              *reinterpret_cast<uint4*>(y_ptr + row + j) = packed;
-              if (y32_ptr != nullptr) {
-                *reinterpret_cast<float4*>(y32_ptr + row + j) = make_float4(o[0], o[1], o[2], o[3]);
-                *reinterpret_cast<float4*>(y32_ptr + row + j + 4) = make_float4(o[4], o[5], o[6], o[7]);
+              for (int h8 = 0; h8 < 2; ++h8) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  o[e] = scale * (__uint_as_float(u[j + 8 * h8 + e]) + __uint_as_float(u2[j + 8 * h8 + e]));
+                packed[h8].x = IO::pack(o[0], o[1]); packed[h8].y = IO::pack(o[2], o[3]);
+                packed[h8].z = IO::pack(o[4], o[5]); packed[h8].w = IO::pack(o[6], o[7]);
+                if (y32_ptr != nullptr)
+                  stg256(y32_ptr + row + j + 8 * h8,
+                         make_uint4(__float_as_uint(o[0]), __float_as_uint(o[1]), __float_as_uint(o[2]), __float_as_uint(o[3])),
+                         make_uint4(__float_as_uint(o[4]), __float_as_uint(o[5]), __float_as_uint(o[6]), __float_as_uint(o[7])));
               }
+              stg256(y_ptr + row + j, packed[0], packed[1]);
             }
           }
         }
@@ -647,6 +653,8 @@ extern "C" int frwkv_wkv7_chunk_fused_fp32io16_forward(
                 "wkv7_chunk_fused_forward: null pointer argument");
   FRWKV_REQUIRE(total_tokens > 0 && num_sequences > 0 && num_chunks > 0 && num_heads > 0,
                 "wkv7_chunk_fused_forward: sizes must be positive");
+  FRWKV_REQUIRE(aligned32(state_pool, r, decay_logits, k, v, a, b, decay_bias, y, y_fp32, boundary, state_dot_a),
+                "wkv7_chunk_fused_forward: tensor pointers must be 32-byte aligned");
   if (head_size != 64)
     return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_chunk_fused_forward: head size %d is not built (only 64)", head_size);
   FRWKV_REQUIRE((long long)num_sequences * num_heads <= 0x7fffffffLL,
@@ -713,6 +721,8 @@ extern "C" int frwkv_wkv7_adjoint_scan(const int32_t* seq_chunk_offsets, const i
                 "wkv7_adjoint_scan: null pointer argument");
   FRWKV_REQUIRE(total_tokens > 0 && num_sequences > 0 && num_chunks > 0 && num_heads > 0,
                 "wkv7_adjoint_scan: sizes must be positive");
+  FRWKV_REQUIRE(aligned32(r, decay_logits, a, b, decay_bias, grad_output, grad_state, boundary_adjoint, khat),
+                "wkv7_adjoint_scan: tensor pointers must be 32-byte aligned");
   if (head_size != 64)
     return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_adjoint_scan: head size %d is not built (only 64)", head_size);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

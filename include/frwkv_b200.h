@@ -6,6 +6,10 @@
  * exceptions).  Return value: FRWKV_OK, or a negative FRWKV_ERR_* code with a
  * message available from frwkv_last_error() on the calling thread.  All tensors
  * are contiguous.  "io16" tensors are fp16 or bf16 according to io_dtype.
+ * Tensor pointers are expected on 32-byte boundaries (a device allocation, or an
+ * offset of whole token rows or state tiles into one): the kernels move rows as
+ * 16- and 32-byte vectors.  The chunked entries (fused forward, adjoint scan,
+ * chunk backward) check this and return FRWKV_ERR_INVALID_ARGUMENT otherwise.
  *
  * Each declaration names the interface of the FlashRWKV2 reference it replaces
  * (paths inside the reference project).

@@ -44,6 +44,27 @@ def test_argument_errors_are_reported_without_a_device():
     assert rc == -1 and b"65535" in lib.frwkv_last_error()
 
 
+def test_misaligned_pointers_are_rejected_without_a_device():
+    """The chunk kernels move rows as 16- and 32-byte vectors; a pointer that is not 32-byte aligned is an argument
+    error, reported before any CUDA call, and not a fault on the device."""
+    from flashrwkv_b200 import _ext
+
+    lib = _ext.capi()
+    ok, bad = ctypes.c_void_p(4096), ctypes.c_void_p(4096 + 8)
+    f = ctypes.c_float(1.0)
+    # frwkv_wkv7_chunk_backward(sco, cs, ce, final_state, boundary, adjoint, sda, r, w, k, v, a, b, bias, dy,
+    #                           dr, dw, dk, dv, da, db, error_flag, status, T, B, Cn, H, D, dtype, scale, stream)
+    args = [ok] * 3 + [ok] * 4 + [ok] * 6 + [None, ok] + [ok] * 6 + [None, None, 64, 1, 1, 1, 64, 1, f, None]
+    args[9] = bad  # k
+    assert lib.frwkv_wkv7_chunk_backward(*args) == -1
+    assert b"32-byte aligned" in lib.frwkv_last_error()
+    # frwkv_wkv7_chunk_fused_fp32io16_forward(sco, cs, ce, state_indices, status, pool, r, w, k, v, a, b, bias,
+    #                                         y, y32, boundary, sda, error_flag, T, B, Cn, H, D, dtype, scale, stream)
+    args = [ok] * 3 + [None, None, ok] + [ok] * 6 + [None, bad, None, None, None, None, 64, 1, 1, 1, 64, 1, f, None]
+    assert lib.frwkv_wkv7_chunk_fused_fp32io16_forward(*args) == -1
+    assert b"32-byte aligned" in lib.frwkv_last_error()
+
+
 def test_python_surface_matches_reference_signatures():
     import inspect
 
