@@ -1441,13 +1441,12 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> wkv7_adjoint_scan(
                                                        : torch::zeros({B, H, 64, 64}, f32);
   TORCH_CHECK(g_state.dim() == 4 && g_state.size(0) == B && g_state.size(1) == H, "grad_final_state must be [B,H,64,64]");
   auto boundary_adjoint = torch::empty({Cn, H, 64, 64}, f32);
-  auto khat = torch::empty(r.sizes(), f32);
   auto error_flag = torch::zeros({1}, r.options().dtype(torch::kInt32));
   remember_flag("wkv7_chunk_backward", error_flag);  // the scan and the token-gradient kernel share the word
   check_rc(frwkv_wkv7_adjoint_scan(sco.data_ptr<int>(), cs.data_ptr<int>(), ce.data_ptr<int>(), r.data_ptr(), w.data_ptr(),
                                    a.data_ptr(), b.data_ptr(), decay_bias.has_value() ? decay_bias->data_ptr() : nullptr,
                                    grad_output.data_ptr(), g_state.data_ptr<float>(), boundary_adjoint.data_ptr<float>(),
-                                   khat.data_ptr<float>(), error_flag.data_ptr<int>(),
+                                   error_flag.data_ptr<int>(),
                                    table_status.has_value() ? table_status->data_ptr<int>() : nullptr,
                                    static_cast<int>(r.size(0)), static_cast<int>(B), static_cast<int>(Cn),
                                    static_cast<int>(H), 64, io_dtype_of(r), static_cast<float>(scale), current_stream(r)));

@@ -60,28 +60,29 @@ static_assert(64 * 256 <= 16 * kCS64, "the A_ab scratch must fit the U half");
 // The token rows of the next chunk are staged as they are in HBM over the [B~;K~] and [U^T|V^T] tiles, which are
 // free between a chunk's last product and the next chunk's operand phase: five tiles of 64 rows, rows padded by 16
 // bytes so that the threads of a warp, which read consecutive rows, hit different banks.
-constexpr uint32_t kRawRow16 = 144, kRawRow32 = 272;
+constexpr uint32_t kRawRow16 = 144;
 constexpr uint32_t kRawA = kOffX2, kRawR = kRawA + 64 * kRawRow16, kRawB = kRawR + 64 * kRawRow16,
                    kRawV = kRawB + 64 * kRawRow16, kRawK = kRawV + 64 * kRawRow16;
-static_assert(kRawK + 64 * kRawRow32 <= kOffS, "the staged rows must fit the two free tiles");
+static_assert(kRawK + 64 * kRawRow16 <= kOffS, "the staged rows must fit the two free tiles");
 static_assert(2 * (kFusedSmem + 1024) <= 233472, "two CTAs must fit one SM");
 
 constexpr uint32_t kColXA = 0, kColD1 = 64, kColDA = 192, kColDC = 0, kTmemCols = 256;
 
 // kAdj = false: the forward recurrence.  kAdj = true: the same kernel walks every sequence BACKWARDS (last chunk
-// first, last token of a chunk first) and takes its key rows from an fp32 tensor: this is how the backward pass gets
-// the adjoint of the state at every chunk boundary, because that adjoint obeys a recurrence of the same form
+// first, last token of a chunk first) and makes its key rows itself: this is how the backward pass gets the adjoint of
+// the state at every chunk boundary, because that adjoint obeys a recurrence of the same form
 //     G_{t-1} = diag(w_t) G_t + a_t (G_t^T b_t)^T + k^_t dy_t^T,      k^_t = scale (w_t * r_t + (b_t . r_t) a_t)
 // (the forward one with a and b exchanged, k^ for k, dy for v, run in reverse time).  The launcher passes b as a,
-// a as b, dy as v and k^ as khat; outputs y / state_dot_a are not produced, `boundary[c]` receives the adjoint
-// that enters chunk c from the future and the state slot ends as the gradient of the initial state.
+// a as b and dy as v; k^ comes from the staged r, a and b rows and the decay w_t = g_t / g_{t-1}; outputs y /
+// state_dot_a are not produced, `boundary[c]` receives the adjoint that enters chunk c from the future and the state
+// slot ends as the gradient of the initial state.
 template <typename io_t, bool kAdj>
 __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
     const int* __restrict__ seq_chunk_offsets, const int* __restrict__ chunk_starts, const int* __restrict__ chunk_ends,
     const int* __restrict__ state_indices, const int* __restrict__ metadata_status, float* __restrict__ state_pool,
     const io_t* __restrict__ r_ptr, const io_t* __restrict__ w_ptr, const io_t* __restrict__ k_ptr,
     const io_t* __restrict__ v_ptr, const io_t* __restrict__ a_ptr, const io_t* __restrict__ b_ptr,
-    const io_t* __restrict__ bias_ptr, const float* __restrict__ khat_ptr, io_t* __restrict__ y_ptr,
+    const io_t* __restrict__ bias_ptr, io_t* __restrict__ y_ptr,
     float* __restrict__ y32_ptr, float* __restrict__ boundary, float* __restrict__ sda_ptr, int num_heads,
     int num_units, long long output_elements, float scale, int* __restrict__ error_flag) {
   using IO = Io16<io_t>;
@@ -139,8 +140,8 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
     umma::cp_async_commit();
   };
 
-  // The a, r, b, k (or, in the adjoint run, fp32 key) and v rows of a chunk, copied as 16-byte pieces with eight (sixteen)
-  // consecutive lanes per row: whole 128-byte lines per request.  Read straight into registers by the thread that owns
+  // The a, r, b, k and v rows of a chunk, copied as 16-byte pieces with eight consecutive lanes per row: whole 128-byte
+  // lines per request.  Read straight into registers by the thread that owns
   // a row, the same rows cost a tag lookup per lane and request, which made the loads the longest stall of a chunk.
   auto stage_rows = [&](int tt0, int ln, long long head_off) {
 #pragma unroll
@@ -151,20 +152,12 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
                        base + (long long)token_row(tt0, ln, min(rowi, ln - 1)) * row_stride + head_off + 8 * part,
                        rowi < ln ? 16u : 0u);
     }
-    if (!kAdj) {
+    if (!kAdj) {  // the adjoint run makes its key rows from the r, a and b rows
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         const int piece = tid + i * kThreads, rowi = piece >> 3, part = piece & 7;
         umma::cp_async16(sbase + kRawK + rowi * kRawRow16 + part * 16,
                          k_ptr + (long long)token_row(tt0, ln, min(rowi, ln - 1)) * row_stride + head_off + 8 * part,
-                         rowi < ln ? 16u : 0u);
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int piece = tid + i * kThreads, rowi = piece >> 4, part = piece & 15;
-        umma::cp_async16(sbase + kRawK + rowi * kRawRow32 + part * 16,
-                         khat_ptr + (long long)token_row(tt0, ln, min(rowi, ln - 1)) * row_stride + head_off + 4 * part,
                          rowi < ln ? 16u : 0u);
       }
     }
@@ -261,13 +254,15 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
       }
       // ---- this thread's operand rows, from the staged tiles (rows past the end of a short chunk were zero-filled) --
       const bool valid = mt < len;
-      uint4 praw[4], qraw[kAdj ? 8 : 4], vraw[4];
+      uint4 praw[4], qraw[4], vraw[4];
+      float b_dot_r = 0.f;  // adjoint run, lanes 64..127: (b_t . r_t) over the row's 64 channels
       umma::cp_async_wait_all();
       __syncthreads();
       {
         const uint32_t rp = (low ? kRawA : kRawR) + mt * kRawRow16 + c0 * 2;
-        const uint32_t rq = low ? kRawB + mt * kRawRow16 + c0 * 2
-                                : (kAdj ? kRawK + mt * kRawRow32 + c0 * 4 : kRawK + mt * kRawRow16 + c0 * 2);
+        // q rows: b for lanes 0..63; k for lanes 64..127, or in the adjoint run the row of the a operand again, from
+        // which (with r) the modified key is made
+        const uint32_t rq = (low || kAdj ? kRawB : kRawK) + mt * kRawRow16 + c0 * 2;
         const uint32_t rv = kRawV + mt * kRawRow16 + c0 * 2;
         const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
@@ -276,9 +271,16 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
           qraw[i] = *reinterpret_cast<const uint4*>(smem + rq + 16 * i);
           vraw[i] = !low ? *reinterpret_cast<const uint4*>(smem + rv + 16 * i) : zero;
         }
-        if (kAdj) {  // the adjoint run's key rows are fp32: 32 channels = eight 16-byte pieces
+        if (kAdj && !low) {
+          // the launcher passed the true b as this kernel's a operand: its staged tile times the r tile, whole rows
 #pragma unroll
-          for (int i = 4; i < 8; ++i) qraw[kAdj ? i : 0] = !low ? *reinterpret_cast<const uint4*>(smem + rq + 16 * i) : zero;
+          for (int i = 0; i < 8; ++i) {
+            float bf[8], rf[8];
+            unpack8<io_t>(*reinterpret_cast<const uint4*>(smem + kRawA + mt * kRawRow16 + 16 * i), bf);
+            unpack8<io_t>(*reinterpret_cast<const uint4*>(smem + kRawR + mt * kRawRow16 + 16 * i), rf);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) b_dot_r = fmaf(bf[e], rf[e], b_dot_r);
+          }
         }
       }
       __syncthreads();  // the staged tiles have been read: the operand tiles may go over them
@@ -290,12 +292,6 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
         float pf[8], qf[8];
         unpack8<io_t>(praw[i], pf);
         unpack8<io_t>(qraw[i], qf);
-        if (kAdj && !low) {
-          const uint4 lo4 = qraw[kAdj ? 2 * i : 0], hi4 = qraw[kAdj ? 2 * i + 1 : 0];
-          qf[0] = __uint_as_float(lo4.x); qf[1] = __uint_as_float(lo4.y); qf[2] = __uint_as_float(lo4.z);
-          qf[3] = __uint_as_float(lo4.w); qf[4] = __uint_as_float(hi4.x); qf[5] = __uint_as_float(hi4.y);
-          qf[6] = __uint_as_float(hi4.z); qf[7] = __uint_as_float(hi4.w);
-        }
         uint32_t xa[8];
 #pragma unroll
         for (int hq = 0; hq < 2; ++hq) {
@@ -304,6 +300,14 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
           float4 sc = g;                          // R~ = r * g_t
           if (low) sc = mt > 0 ? ld4(smem, kOffG + kc * kCS64 + (mt - 1) * 16) : make_float4(1.f, 1.f, 1.f, 1.f);
           const int e = 4 * hq;
+          if (kAdj && !low) {
+            // the adjoint run's key k^ = scale (w r + (b . r) a), with w_t = g_t / g_{t-1}; qf holds the a channels
+            const float4 gp = mt > 0 ? ld4(smem, kOffG + kc * kCS64 + (mt - 1) * 16) : make_float4(1.f, 1.f, 1.f, 1.f);
+            qf[e + 0] = scale * fmaf(b_dot_r, qf[e + 0], g.x * rcp_approx(gp.x) * pf[e + 0]);
+            qf[e + 1] = scale * fmaf(b_dot_r, qf[e + 1], g.y * rcp_approx(gp.y) * pf[e + 1]);
+            qf[e + 2] = scale * fmaf(b_dot_r, qf[e + 2], g.z * rcp_approx(gp.z) * pf[e + 2]);
+            qf[e + 3] = scale * fmaf(b_dot_r, qf[e + 3], g.w * rcp_approx(gp.w) * pf[e + 3]);
+          }
           xa[e + 0] = tf32_bits(pf[e + 0] * sc.x);  // rows past the end of a short chunk were loaded as zeros
           xa[e + 1] = tf32_bits(pf[e + 1] * sc.y);
           xa[e + 2] = tf32_bits(pf[e + 2] * sc.z);
@@ -608,7 +612,7 @@ DeviceInfo* device_info() {
 template <typename io_t, bool kAdj>
 int launch_fused(const int* sco, const int* cs, const int* ce, const int* state_indices, const int* status,
                  float* state_pool, const void* r, const void* w, const void* k, const void* v, const void* a,
-                 const void* b, const void* bias, const float* khat, void* y, float* y32, float* boundary, float* sda,
+                 const void* b, const void* bias, void* y, float* y32, float* boundary, float* sda,
                  int* error_flag, int total_tokens, int num_sequences, int num_heads, float scale, int which,
                  cudaStream_t stream) {
   DeviceInfo* info = device_info();
@@ -625,7 +629,7 @@ int launch_fused(const int* sco, const int* cs, const int* ce, const int* state_
   wkv7_chunk_fused_kernel<io_t, kAdj><<<(unsigned)grid, kThreads, kFusedSmem, stream>>>(
       sco, cs, ce, state_indices, status, state_pool, static_cast<const io_t*>(r), static_cast<const io_t*>(w),
       static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),
-      static_cast<const io_t*>(b), static_cast<const io_t*>(bias), khat, static_cast<io_t*>(y), y32, boundary, sda,
+      static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, boundary, sda,
       num_heads, units, (long long)total_tokens * num_heads * kD, scale, error_flag);
   return check_launch("wkv7_chunk_fused_kernel");
 }
@@ -663,92 +667,47 @@ extern "C" int frwkv_wkv7_chunk_fused_fp32io16_forward(
   if (io_dtype == FRWKV_DTYPE_BF16)
     return launch_fused<__nv_bfloat16, false>(seq_chunk_offsets, chunk_starts, chunk_ends, state_indices,
                                               metadata_status, state_pool, r, decay_logits, k, v, a, b, decay_bias,
-                                              nullptr, y, y_fp32, boundary, state_dot_a, error_flag, total_tokens,
+                                              y, y_fp32, boundary, state_dot_a, error_flag, total_tokens,
                                               num_sequences, num_heads, scale, 0, s);
   if (io_dtype == FRWKV_DTYPE_FP16)
     return launch_fused<__half, false>(seq_chunk_offsets, chunk_starts, chunk_ends, state_indices, metadata_status,
-                                       state_pool, r, decay_logits, k, v, a, b, decay_bias, nullptr, y, y_fp32,
+                                       state_pool, r, decay_logits, k, v, a, b, decay_bias, y, y_fp32,
                                        boundary, state_dot_a, error_flag, total_tokens, num_sequences, num_heads,
                                        scale, 1, s);
   return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_chunk_fused_forward: token tensors must be float16 or bfloat16");
 }
 
 // ---- adjoint of the state at every chunk boundary (first stage of the chunked backward) -----------------------------
-namespace frwkv {
-namespace {
-
-// k^_t = scale * (w_t * r_t + (b_t . r_t) a_t) per (token, head), fp32: one warp per row, two channels per lane
-template <typename io_t>
-__global__ void adjoint_key_kernel(const io_t* __restrict__ r, const io_t* __restrict__ w, const io_t* __restrict__ a,
-                                   const io_t* __restrict__ b, const io_t* __restrict__ bias, float* __restrict__ khat,
-                                   long long rows, int num_heads, float scale) {
-  using IO = Io16<io_t>;
-  const int lane = threadIdx.x & 31;
-  for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
-       row += (long long)gridDim.x * (blockDim.x >> 5)) {
-    const long long at = row * kD + 2 * lane;
-    const float2 rv = IO::unpack(*reinterpret_cast<const uint32_t*>(r + at));
-    const float2 av = IO::unpack(*reinterpret_cast<const uint32_t*>(a + at));
-    const float2 bv = IO::unpack(*reinterpret_cast<const uint32_t*>(b + at));
-    float2 wl = IO::unpack(*reinterpret_cast<const uint32_t*>(w + at));
-    if (bias != nullptr) {
-      const float2 bz = IO::unpack(*reinterpret_cast<const uint32_t*>(bias + (row % num_heads) * kD + 2 * lane));
-      wl.x += bz.x;
-      wl.y += bz.y;
-    }
-    float dot = bv.x * rv.x + bv.y * rv.y;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    *reinterpret_cast<float2*>(khat + at) = make_float2(scale * fmaf(dot, av.x, retention(wl.x) * rv.x),
-                                                        scale * fmaf(dot, av.y, retention(wl.y) * rv.y));
-  }
-}
-
-}  // namespace
-}  // namespace frwkv
-
 extern "C" int frwkv_wkv7_adjoint_scan(const int32_t* seq_chunk_offsets, const int32_t* chunk_starts,
                                        const int32_t* chunk_ends, const void* r, const void* decay_logits,
                                        const void* a, const void* b, const void* decay_bias, const void* grad_output,
-                                       float* grad_state, float* boundary_adjoint, float* khat, int32_t* error_flag,
+                                       float* grad_state, float* boundary_adjoint, int32_t* error_flag,
                                        const int32_t* metadata_status, int total_tokens, int num_sequences,
                                        int num_chunks, int num_heads, int head_size, int io_dtype, float scale,
                                        frwkv_stream_t stream) {
   using namespace frwkv;
   clear_error();
   FRWKV_REQUIRE(seq_chunk_offsets && chunk_starts && chunk_ends && r && decay_logits && a && b && grad_output &&
-                    grad_state && boundary_adjoint && khat,
+                    grad_state && boundary_adjoint,
                 "wkv7_adjoint_scan: null pointer argument");
   FRWKV_REQUIRE(total_tokens > 0 && num_sequences > 0 && num_chunks > 0 && num_heads > 0,
                 "wkv7_adjoint_scan: sizes must be positive");
-  FRWKV_REQUIRE(aligned32(r, decay_logits, a, b, decay_bias, grad_output, grad_state, boundary_adjoint, khat),
+  FRWKV_REQUIRE(aligned32(r, decay_logits, a, b, decay_bias, grad_output, grad_state, boundary_adjoint),
                 "wkv7_adjoint_scan: tensor pointers must be 32-byte aligned");
   if (head_size != 64)
     return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_adjoint_scan: head size %d is not built (only 64)", head_size);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const long long rows = (long long)total_tokens * num_heads;
-  const unsigned blocks = (unsigned)((rows + 7) / 8 < 148 * 16 ? (rows + 7) / 8 : 148 * 16);
-  if (io_dtype == FRWKV_DTYPE_BF16) {
-    using T = __nv_bfloat16;
-    adjoint_key_kernel<T><<<blocks, 256, 0, s>>>(static_cast<const T*>(r), static_cast<const T*>(decay_logits),
-                                                 static_cast<const T*>(a), static_cast<const T*>(b),
-                                                 static_cast<const T*>(decay_bias), khat, rows, num_heads, scale);
-    if (int rc = check_launch("adjoint_key_kernel")) return rc;
-    return launch_fused<T, true>(seq_chunk_offsets, chunk_starts, chunk_ends, nullptr, metadata_status, grad_state, r,
-                                 decay_logits, /*k: unused*/ r, grad_output, /*a=*/b, /*b=*/a, decay_bias, khat, nullptr,
-                                 nullptr, boundary_adjoint, nullptr, error_flag, total_tokens, num_sequences, num_heads,
-                                 1.0f, 2, s);
-  }
-  if (io_dtype == FRWKV_DTYPE_FP16) {
-    using T = __half;
-    adjoint_key_kernel<T><<<blocks, 256, 0, s>>>(static_cast<const T*>(r), static_cast<const T*>(decay_logits),
-                                                 static_cast<const T*>(a), static_cast<const T*>(b),
-                                                 static_cast<const T*>(decay_bias), khat, rows, num_heads, scale);
-    if (int rc = check_launch("adjoint_key_kernel")) return rc;
-    return launch_fused<T, true>(seq_chunk_offsets, chunk_starts, chunk_ends, nullptr, metadata_status, grad_state, r,
-                                 decay_logits, /*k: unused*/ r, grad_output, /*a=*/b, /*b=*/a, decay_bias, khat, nullptr,
-                                 nullptr, boundary_adjoint, nullptr, error_flag, total_tokens, num_sequences, num_heads,
-                                 1.0f, 3, s);
-  }
+  // the forward kernel in reverse time with a and b exchanged and dy for v; it makes its key rows
+  // k^ = scale (w r + (b . r) a) itself, from the rows it has staged
+  if (io_dtype == FRWKV_DTYPE_BF16)
+    return launch_fused<__nv_bfloat16, true>(seq_chunk_offsets, chunk_starts, chunk_ends, nullptr, metadata_status,
+                                             grad_state, r, decay_logits, /*k: unused*/ r, grad_output, /*a=*/b,
+                                             /*b=*/a, decay_bias, nullptr, nullptr, boundary_adjoint, nullptr,
+                                             error_flag, total_tokens, num_sequences, num_heads, scale, 2, s);
+  if (io_dtype == FRWKV_DTYPE_FP16)
+    return launch_fused<__half, true>(seq_chunk_offsets, chunk_starts, chunk_ends, nullptr, metadata_status,
+                                      grad_state, r, decay_logits, /*k: unused*/ r, grad_output, /*a=*/b, /*b=*/a,
+                                      decay_bias, nullptr, nullptr, boundary_adjoint, nullptr, error_flag,
+                                      total_tokens, num_sequences, num_heads, scale, 3, s);
   return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_adjoint_scan: token tensors must be float16 or bfloat16");
 }

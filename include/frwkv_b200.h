@@ -200,13 +200,13 @@ int frwkv_wkv7_chunk_fused_fp32io16_forward(
  * csrc/sm90/tmix/wkv7/pretrain_recurrent_bf16_forward.cu:222-282).
  *   grad_output io16 [N,H,64]; grad_state fp32 [B,H,64,64]: in = gradient of the final state (zeros if none), out =
  *   gradient of the initial state;  boundary_adjoint fp32 [Cn,H,64,64]: receives dL/dS at the END of every chunk;
- *   khat fp32 [N,H,64]: scratch for the modified keys scale * (w * r + (b . r) a);
+ *   the modified keys scale * (w * r + (b . r) a) are made inside the kernel: no scratch tensor;
  *   metadata_status (may be NULL): the word of frwkv_validate_chunk_tables; non-zero = the scan does nothing.
  */
 int frwkv_wkv7_adjoint_scan(const int32_t* seq_chunk_offsets, const int32_t* chunk_starts, const int32_t* chunk_ends,
                             const void* r, const void* decay_logits, const void* a, const void* b,
                             const void* decay_bias, const void* grad_output, float* grad_state,
-                            float* boundary_adjoint, float* khat, int32_t* error_flag,
+                            float* boundary_adjoint, int32_t* error_flag,
                             const int32_t* metadata_status, int total_tokens, int num_sequences, int num_chunks,
                             int num_heads, int head_size, int io_dtype, float scale, frwkv_stream_t stream);
 
