@@ -330,9 +330,8 @@ def _extras(dev):
         "workload": f"B={Bc} T={T} H={Ht} D={D}, forward (fused chunk kernel: y, boundary states, state_dot_a) and "
                     "backward (adjoint scan + chunk-parallel tensor-core backward)",
         "tokens_per_s": n_tok / sec, "ms": sec * 1e3, "tensor_frac_of_bf16_peak": n_tok * Ht * 294912 / sec / bf16,
-        "gpu_launches_per_call": 4,
-        "kernels": "wkv7_chunk_fused_kernel, adjoint_key_kernel, wkv7_chunk_fused_kernel<adjoint>, "
-                   "wkv7_chunk_backward_kernel"}
+        "gpu_launches_per_call": 3,
+        "kernels": "wkv7_chunk_fused_kernel, wkv7_chunk_fused_kernel<adjoint>, wkv7_chunk_backward_kernel"}
     del toks, S0, dy
     torch.cuda.empty_cache()
     # ---- TMix layer chain, C = 2048
