@@ -61,7 +61,8 @@ static_assert(kBwdSmem + 2048 <= 232448, "the CTA must fit one SM's shared memor
 // of a warp, which read consecutive rows, hit different banks.
 constexpr uint32_t kRawRow = 144;
 constexpr uint32_t kRawBase = kOffRB;
-static_assert(kRawBase + 5 * 64 * kRawRow <= kOffTAR, "the staged rows must fit the two free tiles");
+constexpr uint32_t kRawW = kRawBase + 5 * 64 * kRawRow;  // the staged decay logits, 128 bytes per row
+static_assert(kRawW + kL * kD * 2 <= kOffTAR, "the staged rows must fit the two free tiles");
 
 constexpr uint32_t kColXA = 0, kColXB = 64, kColD1 = 128, kColD1T = 256, kColDUV = 384;
 constexpr uint32_t kColOUT1 = kColXB, kColDD = kColD1, kColDDT = kColD1T, kColOUT2 = kColDUV;
@@ -130,34 +131,25 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
     im.last = ch + 1 == seq_chunk_offsets[lo + 1];
     return im;
   };
-  // the decay logits of an item travel by cp.async one item ahead (one 16-byte piece per thread)
-  auto stage_w = [&](int item, const ItemMeta& im) {
-    const int hd = item % num_heads;
-    const int rowi = tid >> 3, part = tid & 7;
-    umma::cp_async16(sbase + kOffW + tid * 16,
-                     w_ptr + (long long)(im.t0 + min(rowi, im.len - 1)) * row_stride + (long long)hd * kD + 8 * part,
-                     rowi < im.len ? 16u : 0u);
-    umma::cp_async_commit();
-  };
-  // ... and so do its a, r, b, k and dy rows, as 16-byte pieces with eight consecutive lanes per row (whole 128-byte
-  // lines per request; read straight into registers by the thread that owns a row they cost a tag lookup per lane)
+  // The a, r, b, k, dy rows and the decay logits of an item travel by cp.async one item ahead, as 16-byte pieces with
+  // eight consecutive lanes per row (whole 128-byte lines per request; read straight into registers by the thread
+  // that owns a row they cost a tag lookup per lane).  The logits sit behind the five padded tiles, 128 bytes per row,
+  // and move to their own tile when the item starts (they are read again at its end).
   auto stage_rows = [&](int item, const ItemMeta& im) {
     const long long hoff = (long long)(item % num_heads) * kD;
+    const int rowi = tid >> 3, part = tid & 7;
+    const long long at = (long long)(im.t0 + min(rowi, im.len - 1)) * row_stride + hoff + 8 * part;
+    const uint32_t bytes = rowi < im.len ? 16u : 0u;
 #pragma unroll
     for (int i = 0; i < 5; ++i) {
-      const int rowi = tid >> 3, part = tid & 7;
       const io_t* base = i == 0 ? a_ptr : i == 1 ? r_ptr : i == 2 ? b_ptr : i == 3 ? k_ptr : dy_ptr;
-      umma::cp_async16(sbase + kRawBase + i * (64 * kRawRow) + rowi * kRawRow + part * 16,
-                       base + (long long)(im.t0 + min(rowi, im.len - 1)) * row_stride + hoff + 8 * part,
-                       rowi < im.len ? 16u : 0u);
+      umma::cp_async16(sbase + kRawBase + i * (64 * kRawRow) + rowi * kRawRow + part * 16, base + at, bytes);
     }
+    umma::cp_async16(sbase + kRawW + tid * 16, w_ptr + at, bytes);
     umma::cp_async_commit();
   };
   ItemMeta cur = item_meta(min((int)blockIdx.x, num_items - 1));
-  if ((int)blockIdx.x < num_items) {
-    stage_w(blockIdx.x, cur);
-    stage_rows(blockIdx.x, cur);
-  }
+  if ((int)blockIdx.x < num_items) stage_rows(blockIdx.x, cur);
 
   for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, parity ^= 1u) {
     const int chunk = item / num_heads, head = item % num_heads;
@@ -185,14 +177,17 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
         qraw[i] = *reinterpret_cast<const uint4*>(smem + at + (low ? 2 : 3) * (64 * kRawRow) + 16 * i);
         draw[i] = !low ? *reinterpret_cast<const uint4*>(smem + at + 4 * (64 * kRawRow) + 16 * i) : zero4;
       }
+      // the previous item has read its logits for the last time (the barrier above): this item's take their place
+      // for the decay gradient at the end; the decay tile below reads the staged copy
+      *reinterpret_cast<uint4*>(smem + kOffW + tid * 16) = *reinterpret_cast<const uint4*>(smem + kRawW + tid * 16);
     }
     const bool has_next = item + (int)gridDim.x < num_items;
     // ---- g[t][k] (as in the forward kernel; threads 0..255 work) ------------------------------------------------
     if (tid < 256) {
       const int t = tid >> 2, q = tid & 3;
       float x[16];
-      unpack8<io_t>(*reinterpret_cast<const uint4*>(smem + kOffW + t * 128 + q * 32), *reinterpret_cast<float(*)[8]>(&x[0]));
-      unpack8<io_t>(*reinterpret_cast<const uint4*>(smem + kOffW + t * 128 + q * 32 + 16), *reinterpret_cast<float(*)[8]>(&x[8]));
+      unpack8<io_t>(*reinterpret_cast<const uint4*>(smem + kRawW + t * 128 + q * 32), *reinterpret_cast<float(*)[8]>(&x[0]));
+      unpack8<io_t>(*reinterpret_cast<const uint4*>(smem + kRawW + t * 128 + q * 32 + 16), *reinterpret_cast<float(*)[8]>(&x[8]));
       if (bias_ptr != nullptr) {
         float bz[16];
         unpack8<io_t>(__ldg(reinterpret_cast<const uint4*>(bias_ptr + head_off + 16 * q)), *reinterpret_cast<float(*)[8]>(&bz[0]));
@@ -744,7 +739,6 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
     umma::fence_before_sync();
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
     umma::fence_after_sync();
-    if (ok && has_next) stage_w(item + gridDim.x, nxt);  // the logits have been read
     cur = nxt;
     if (!ok) {
       // fail closed: the gradients of this item's rows read as NaN
