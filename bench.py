@@ -574,7 +574,9 @@ def run_b200(args):
     achieved = loop.bytes_per_launch / launch_s / 1e9
     working_mb = n_local * H * D * D * 4 / 1e6
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_source": f"of {peak_kind}", "kernel": "wkv7_decode_pipelined_kernel",
+                "traffic": None, "peak_source": f"of {peak_kind}",
+                # the library sends batches of at most 4608 (sequence, head) tiles to the register kernel
+                "kernel": "wkv7_decode_pipelined_kernel" if n_local * H > 4608 else "wkv7_recurrent_d64_kernel",
                 "algorithmic_bytes_per_launch": loop.bytes_per_launch, "us_per_launch": launch_s * 1e6,
                 "note": "achieved = algorithmic bytes / time: an effective bandwidth that counts state tiles found in L2 "
                         "(the traversal order alternates between launches) as if they came from HBM"}
