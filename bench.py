@@ -334,6 +334,28 @@ def _extras(dev):
         "kernels": "wkv7_chunk_fused_kernel, wkv7_chunk_fused_kernel<adjoint>, wkv7_chunk_backward_kernel"}
     del toks, S0, dy
     torch.cuda.empty_cache()
+    # ---- training forward + backward at head sizes 128 and 256 (serial CUDA-core recurrences; H * D = 4096)
+    wide = {}
+    Bw, Tw = 8, 1024
+    cu_w, _ = synthetic.equal_length_metadata(Bw, Tw, device=dev)
+    meta_w = make_chunk_metadata(cu_w, 64)
+    for Dw in (128, 256):
+        Hw = 4096 // Dw
+        toks = [t.to(dev).requires_grad_() for t in synthetic.wkv7_inputs(Bw * Tw, Hw, Dw, seed=15)]
+        S0 = synthetic.state_pool(Bw, Hw, Dw, seed=16, device=dev).requires_grad_()
+        dy = torch.randn(Bw * Tw, Hw, Dw, device=dev).to(torch.bfloat16)
+
+        def wide_step():
+            res = F.statetune_recurrent_fp32io16(S0, *meta_w, *toks)
+            res[0].backward(dy)
+            for t in (*toks, S0):
+                t.grad = None
+
+        sec = _time_cuda(wide_step, warmup=1, iters=2)
+        wide[f"D={Dw}"] = {"workload": f"B={Bw} T={Tw} H={Hw} D={Dw}", "tokens_per_s": Bw * Tw / sec, "ms": sec * 1e3}
+        del toks, S0, dy
+    out["training_fwd_bwd_wide_heads"] = wide
+    torch.cuda.empty_cache()
     # ---- TMix layer chain, C = 2048
     C, Hh = 2048, 32
     g = torch.Generator().manual_seed(3)
