@@ -28,6 +28,6 @@ bool chained_launch_enabled() {
 
 }  // namespace frwkv
 
-extern "C" int frwkv_abi_version(void) { return 1; }
+extern "C" int frwkv_abi_version(void) { return 2; }
 
 extern "C" const char* frwkv_last_error(void) { return frwkv::g_error; }

@@ -111,6 +111,38 @@ extern "C" int frwkv_validate_chunk_tables(const int32_t* seq_chunk_offsets, con
   return check_launch("validate_chunk_tables_kernel");
 }
 
+namespace frwkv {
+namespace {
+// *flag stays 1 only if sequence i is token i (cu[i] == i, i = 0..n) and owns slot i (idx[i] == i, i = 0..n-1)
+__global__ void metadata_is_direct_kernel(const int* __restrict__ cu, const int* __restrict__ idx, int n,
+                                          int* __restrict__ flag) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  bool bad = false;
+  if (i <= n) bad = cu[i] != i;
+  if (i < n) bad = bad || idx[i] != i;
+  if (bad) atomicExch(flag, 0);
+}
+__global__ void set_flag_kernel(int* __restrict__ flag) { *flag = 1; }
+}  // namespace
+}  // namespace frwkv
+
+extern "C" int frwkv_recurrent_metadata_is_direct(const int32_t* cu_seqlens, const int32_t* state_indices,
+                                                  int num_sequences, int32_t* flag, frwkv_stream_t stream) {
+  using namespace frwkv;
+  clear_error();
+  FRWKV_REQUIRE(cu_seqlens && state_indices && flag, "recurrent_metadata_is_direct: null pointer argument");
+  FRWKV_REQUIRE(num_sequences > 0 && num_sequences <= 65535,
+                "state_indices must contain at most 65535 sequences");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  constexpr int threads = 128;
+  set_flag_kernel<<<1, 1, 0, s>>>(flag);  // the flag starts as 1, ahead of the kernel that may clear it
+  int rc = check_launch("set_flag_kernel");
+  if (rc != FRWKV_OK) return rc;
+  metadata_is_direct_kernel<<<(num_sequences + 1 + threads - 1) / threads, threads, 0, s>>>(cu_seqlens, state_indices,
+                                                                                          num_sequences, flag);
+  return check_launch("metadata_is_direct_kernel");
+}
+
 extern "C" int frwkv_validate_recurrent_metadata(const int32_t* cu_seqlens, const int32_t* state_indices,
                                                  int num_sequences, int total_tokens, int state_pool_size,
                                                  int32_t* status, int32_t* cu_snapshot,

@@ -105,8 +105,9 @@ PreparedMetadata launch_validation(const torch::Tensor& cu, const torch::Tensor&
 class MetadataTicket {
  public:
   MetadataTicket(torch::Tensor cu, torch::Tensor idx, PreparedMetadata prepared, int64_t total_tokens,
-                 int64_t pool_size, int64_t max_seqlen, cudaStream_t stream)
-      : cu_(std::move(cu)),
+                 int64_t pool_size, int64_t max_seqlen, cudaStream_t stream, bool direct_slots)
+      : direct_slots_(direct_slots),
+        cu_(std::move(cu)),
         idx_(std::move(idx)),
         prepared_(std::move(prepared)),
         cu_version_(tensor_version(cu_)),
@@ -152,8 +153,11 @@ class MetadataTicket {
   const torch::Tensor& idx_snapshot() const { return prepared_.idx; }
   const torch::Tensor& status() const { return prepared_.status; }
   int64_t max_seqlen() const { return max_seqlen_; }
+  // sequence i is token i and owns state slot i (checked on the device and read back when the ticket was made)
+  bool direct_slots() const { return direct_slots_; }
 
  private:
+  bool direct_slots_;
   torch::Tensor cu_, idx_;
   PreparedMetadata prepared_;
   std::optional<uint32_t> cu_version_, idx_version_;
@@ -184,10 +188,17 @@ std::shared_ptr<MetadataTicket> prepare_recurrent_metadata(torch::Tensor cu, tor
   const c10::cuda::CUDAGuard guard(cu.device());
   const cudaStream_t stream = at::cuda::getCurrentCUDAStream(cu.device().index()).stream();
   auto prepared = launch_validation(cu, idx, total_tokens, pool_size);
-  // One 8-byte read back: the status bits and the longest sequence.  This is the
+  // ... and whether every sequence is one token in the slot of its own number (decode launches are then shorter)
+  auto direct_flag = torch::empty({1}, cu.options());
+  check_rc(frwkv_recurrent_metadata_is_direct(prepared.cu.data_ptr<int>(), prepared.idx.data_ptr<int>(),
+                                              static_cast<int>(idx.numel()), direct_flag.data_ptr<int>(), stream));
+  // One read back: the status bits, the longest sequence and that flag.  This is the
   // only synchronisation of the path and happens once per ticket.
   int host_status[2] = {0, 0};
+  int host_direct = 0;
   C10_CUDA_CHECK(cudaMemcpyAsync(host_status, prepared.status.data_ptr<int>(), sizeof(host_status),
+                                 cudaMemcpyDeviceToHost, stream));
+  C10_CUDA_CHECK(cudaMemcpyAsync(&host_direct, direct_flag.data_ptr<int>(), sizeof(host_direct),
                                  cudaMemcpyDeviceToHost, stream));
   C10_CUDA_CHECK(cudaStreamSynchronize(stream));
   const int bits = host_status[0];
@@ -204,7 +215,7 @@ std::shared_ptr<MetadataTicket> prepare_recurrent_metadata(torch::Tensor cu, tor
     TORCH_CHECK(max_seqlen == inferred, "max_seqlen must equal the largest packed sequence length");
   }
   return std::make_shared<MetadataTicket>(std::move(cu), std::move(idx), std::move(prepared), total_tokens,
-                                          pool_size, max_seqlen, stream);
+                                          pool_size, max_seqlen, stream, host_direct == 1);
 }
 
 struct RecurrentDims {
@@ -285,6 +296,7 @@ void recurrent_fp32_from_decay_logits(torch::Tensor cu, torch::Tensor idx, torch
   if (ticket) {
     ticket->check_compatible(cu, idx, r.size(0), state.size(0), max_seqlen);
     flags = ticket->next_launch_parity() ? FRWKV_RECURRENT_REVERSE_ORDER : 0;
+    if (ticket->direct_slots()) flags |= FRWKV_RECURRENT_DIRECT_SLOTS;
     launch_cu = ticket->cu_snapshot();
     launch_idx = ticket->idx_snapshot();
     status = ticket->status();
@@ -1926,7 +1938,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("_query_start_loc_snapshot", [](const MetadataTicket& t) { return t.cu_snapshot(); })
       .def("_state_indices_snapshot", [](const MetadataTicket& t) { return t.idx_snapshot(); })
       .def("_status", [](const MetadataTicket& t) { return t.status().narrow(0, 0, 1); })
-      .def("_max_seqlen", [](const MetadataTicket& t) { return t.max_seqlen(); });
+      .def("_max_seqlen", [](const MetadataTicket& t) { return t.max_seqlen(); })
+      .def("_direct_slots", [](const MetadataTicket& t) { return t.direct_slots(); });
   m.def("prepare_recurrent_metadata", &prepare_recurrent_metadata, py::arg("query_start_loc"),
         py::arg("state_indices"), py::arg("total_tokens"), py::arg("state_pool_size"),
         py::arg("max_seqlen") = -1);

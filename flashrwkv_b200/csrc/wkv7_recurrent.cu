@@ -175,7 +175,11 @@ __device__ __forceinline__ StepOut token_step(float4 (&s)[16], const io_t* __res
 // read from the chunk-start boundary tensor and never written back, and instead of being discarded the per-token
 // S^T a vectors (state_dot_a) and the states after every 16th token of a chunk (checkpoints for the backward
 // pass) are stored.  cu_seqlens / state_indices then hold chunk_starts / chunk_ends.
-template <typename io_t, bool kReplay>
+// kDirect (decode of a batch whose sequence i is token i and owns state slot i, as a host-checked ticket has
+// established): neither table is read, and the status word is asked for together with the state tile instead of one
+// round trip ahead of it; the kernel is then one dependent round trip shorter, which shows when a launch is a few
+// hundred tiles and bound by that chain.
+template <typename io_t, bool kReplay, bool kDirect = false>
 __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
     const int* __restrict__ cu_seqlens, const int* __restrict__ state_indices,
     const int* __restrict__ metadata_status, float* __restrict__ state_pool,
@@ -200,9 +204,15 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
   // the status word and the sequence's metadata are requested together (one round trip, not two in a row: in a decode
   // step of a few hundred tiles the kernel is a chain of dependent loads)
   const int status0 = (!kReplay && metadata_status != nullptr) ? metadata_status[0] : 0;
-  const int t_begin = cu_seqlens[seq];
-  const int t_end = kReplay ? state_indices[seq] : cu_seqlens[seq + 1];
-  const int slot = kReplay ? seq : state_indices[seq];
+  const int t_begin = kDirect ? seq : cu_seqlens[seq];
+  const int t_end = kDirect ? seq + 1 : (kReplay ? state_indices[seq] : cu_seqlens[seq + 1]);
+  const int slot = (kReplay || kDirect) ? seq : state_indices[seq];
+  float4 s[16];
+  float* sbase = state_pool + ((long long)slot * num_heads + head) * (kD * kD) + row0 * kD + col0;
+  if (kDirect) {  // the tile's address needs no table: its loads leave with the status word's
+#pragma unroll
+    for (int i = 0; i < 16; ++i) s[i] = *reinterpret_cast<const float4*>(sbase + i * kD);
+  }
   if (status0 != 0) {
     // fail closed: NaN output, state untouched
     const io_t nan16 = IO::store(quiet_nan());
@@ -215,10 +225,10 @@ __global__ __launch_bounds__(kThreads, 4) void wkv7_recurrent_d64_kernel(
   }
   if (!active) return;
 
-  float* sbase = state_pool + ((long long)slot * num_heads + head) * (kD * kD) + row0 * kD + col0;
-  float4 s[16];
+  if (!kDirect) {
 #pragma unroll
-  for (int i = 0; i < 16; ++i) s[i] = *reinterpret_cast<const float4*>(sbase + i * kD);
+    for (int i = 0; i < 16; ++i) s[i] = *reinterpret_cast<const float4*>(sbase + i * kD);
+  }
 
   for (int t = t_begin; t < t_end; ++t) {
     const long long tb = ((long long)t * num_heads + head) * kD;
@@ -510,9 +520,17 @@ template <typename io_t>
 int launch(const int* cu, const int* idx, const int* status, float* state, const void* r,
            const void* w, const void* k, const void* v, const void* a, const void* b,
            const void* bias, void* y, float* y32, int total_tokens, int num_sequences, int num_heads,
-           float scale, cudaStream_t stream) {
+           float scale, bool direct, cudaStream_t stream) {
   const long long units = (long long)num_sequences * num_heads * 2;
   const long long blocks = (units + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (direct) {
+    launch_chained(wkv7_recurrent_d64_kernel<io_t, false, true>, dim3((unsigned)blocks), dim3(kThreads), 0, stream,
+        cu, idx, status, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w),
+        static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),
+        static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), y32, nullptr, nullptr,
+        units, num_heads, (long long)total_tokens * num_heads * kD, scale);
+    return check_launch("wkv7_recurrent_d64_kernel<direct>");
+  }
   launch_chained(wkv7_recurrent_d64_kernel<io_t, false>, dim3((unsigned)blocks), dim3(kThreads), 0, stream,
       cu, idx, status, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w),
       static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),
@@ -617,14 +635,16 @@ extern "C" int frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex(
   if (decode && io_dtype == FRWKV_DTYPE_FP16)
     return launch_decode<__half>(state_indices, metadata_status, state_pool, r, decay_logits, k, v, a, b, decay_bias,
                                  y, y_fp32, num_sequences, num_heads, scale, flags & 1, s);
+  // one token per sequence, sequence i in slot i, on the caller's word: the register kernel reads neither table
+  const bool direct = (flags & FRWKV_RECURRENT_DIRECT_SLOTS) != 0 && max_seqlen == 1 && total_tokens == num_sequences;
   if (io_dtype == FRWKV_DTYPE_BF16) {
     return launch<__nv_bfloat16>(cu_seqlens, state_indices, metadata_status, state_pool, r, decay_logits, k,
                                  v, a, b, decay_bias, y, y_fp32, total_tokens, num_sequences, num_heads,
-                                 scale, s);
+                                 scale, direct, s);
   }
   if (io_dtype == FRWKV_DTYPE_FP16) {
     return launch<__half>(cu_seqlens, state_indices, metadata_status, state_pool, r, decay_logits, k, v, a,
-                          b, decay_bias, y, y_fp32, total_tokens, num_sequences, num_heads, scale, s);
+                          b, decay_bias, y, y_fp32, total_tokens, num_sequences, num_heads, scale, direct, s);
   }
   return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_recurrent: token tensors must be float16 or bfloat16");
 }

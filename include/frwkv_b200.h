@@ -57,6 +57,11 @@ int frwkv_abi_version(void);
 /* Message of the last error returned on this thread ("" if none). */
 const char* frwkv_last_error(void);
 
+/* *flag (device int32) = 1 when cu_seqlens[i] == i for i = 0..B and state_indices[i] == i for i = 0..B-1, else 0:
+ * every sequence is one token and owns the state slot of its own number.  See FRWKV_RECURRENT_DIRECT_SLOTS. */
+int frwkv_recurrent_metadata_is_direct(const int32_t* cu_seqlens, const int32_t* state_indices, int num_sequences,
+                                       int32_t* flag, frwkv_stream_t stream);
+
 /*
  * Validate packed-sequence metadata on the device and snapshot it.
  * Replaces prepare_recurrent_metadata_cuda / validate_recurrent_metadata_kernel
@@ -107,8 +112,12 @@ int frwkv_wkv7_recurrent_fp32io16_forward_varlen(
 
 /* Same, with flags: bit 0 = FRWKV_RECURRENT_REVERSE_ORDER, walk the (sequence, head) tiles from the far end of the
  * batch.  The result does not depend on it.  A decode loop that alternates the bit between consecutive steps finds
- * the state tiles it wrote last still in L2 (126 MB on B200) when the next step starts with them. */
-enum { FRWKV_RECURRENT_REVERSE_ORDER = 1 };
+ * the state tiles it wrote last still in L2 (126 MB on B200) when the next step starts with them.
+ * bit 1 = FRWKV_RECURRENT_DIRECT_SLOTS: the caller has established (frwkv_recurrent_metadata_is_direct) that
+ * cu_seqlens[i] == i and state_indices[i] == i; with max_seqlen == 1 and total_tokens == num_sequences the register
+ * kernel (batches below the ring kernel's threshold) then reads neither table and is one dependent round trip
+ * shorter per launch.  The status word is still honoured.  Ignored where it does not apply. */
+enum { FRWKV_RECURRENT_REVERSE_ORDER = 1, FRWKV_RECURRENT_DIRECT_SLOTS = 2 };
 int frwkv_wkv7_recurrent_fp32io16_forward_varlen_ex(
     const int32_t* cu_seqlens, const int32_t* state_indices, const int32_t* metadata_status,
     float* state_pool, const void* r, const void* decay_logits, const void* k, const void* v,

@@ -377,3 +377,34 @@ def test_wait_timeout_bit_in_the_status_word_fails_closed(B):
     torch.cuda.synchronize()
     assert torch.isnan(y.float()).all()
     assert torch.equal(pool, before)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_direct_slot_decode_is_bit_identical_to_indexed_decode(dtype):
+    """A ticket made from `cu_seqlens = 0..B` and `state_indices = 0..B-1` knows that sequence i is token i in slot i,
+    and small decode batches then take a kernel that reads neither table.  The same tokens decoded through a shuffled
+    slot table (which takes the indexed kernel) must give the same bits, outputs and states, over several steps."""
+    import flashrwkv_b200 as F
+    from flashrwkv_b200 import synthetic
+
+    B, H, D, steps = 48, 32, 64, 3
+    cu, idx = (t.cuda() for t in synthetic.equal_length_metadata(B, 1))
+    perm = torch.randperm(B, generator=torch.Generator().manual_seed(5)).to(torch.int32).cuda()
+    pool_a = synthetic.state_pool(B, H, D, seed=21, device="cuda")
+    pool_b = torch.empty_like(pool_a)
+    pool_b[perm.long()] = pool_a  # sequence i's state lives in slot perm[i]
+    ticket_a = F.prepare_recurrent_metadata(cu, idx, total_tokens=B, state_pool_size=B, max_seqlen=1)
+    ticket_b = F.prepare_recurrent_metadata(cu, perm, total_tokens=B, state_pool_size=B, max_seqlen=1)
+    assert ticket_a._direct_slots() and not ticket_b._direct_slots()
+    for step in range(steps):
+        toks = [t.cuda() for t in synthetic.wkv7_inputs(B, H, D, seed=300 + step, dtype=dtype)]
+        ya = F.infer_recurrent_fp32io16_forward_varlen(*toks, state_pool=pool_a, cu_seqlens=cu, state_indices=idx,
+                                                       validated_metadata=ticket_a, max_seqlen=1)
+        yb = F.infer_recurrent_fp32io16_forward_varlen(*toks, state_pool=pool_b, cu_seqlens=cu, state_indices=perm,
+                                                       validated_metadata=ticket_b, max_seqlen=1)
+        assert torch.equal(ya, yb)
+    assert torch.equal(pool_a, pool_b[perm.long()])
+    # a batch that is not one token per sequence never gets the flag
+    cu2 = torch.tensor([0, 2, 3], dtype=torch.int32, device="cuda")
+    idx2 = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    assert not F.prepare_recurrent_metadata(cu2, idx2, total_tokens=3, state_pool_size=B)._direct_slots()
