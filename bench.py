@@ -699,6 +699,7 @@ def run_b200(args):
 #   train512   the same at B=8, T=512, H=64: 512 (sequence, head) pairs, as in the training configuration
 #   tmix       one TMix layer's projections at C=2048 for M in (4, 512)
 #   decode     recurrent decode steps at B=256, H=32 (the benchmark's shape, 8 launches)
+#   decode32   the same at B=32: a rank's share of the batch at 8 GPUs (register kernel, tables not read)
 #   decode16   the same on an fp16 state pool
 #   glue       training-side TMix glue, forward + backward of the five operators: B=2, T=4096, C=4096
 def _profile_case(name: str) -> None:
@@ -745,7 +746,7 @@ def _profile_case(name: str) -> None:
                 F.infer_tmix_lowrank_vres_forward_varlen(*feats, w2["w"], w2["a"], w2["g"], w2["v"], xs[4], xs[5], v0)
 
 
-    def case_decode(reps: int = 8):
+    def case_decode(reps: int = 8, B: int = B):
         cu, idx = synthetic.equal_length_metadata(B, 1, device="cuda")
         pool = synthetic.state_pool(B, H, D, seed=5, device="cuda")
         toks = [t.cuda() for t in synthetic.wkv7_inputs(B, H, D, seed=6)]
@@ -804,6 +805,7 @@ def _profile_case(name: str) -> None:
 
     cases = {"layer": case_layer, "layer1": lambda: case_layer(3, 1), "chunk": case_chunk, "chunk2k": lambda: case_chunk(3, 2, 4096, 32, 0), "train": case_train,
              "train512": lambda: case_train(2, 8, 512, 64), "tmix": case_tmix, "decode": case_decode,
+             "decode32": lambda: case_decode(8, 32),
              "decode16": case_decode16, "glue": case_glue}
     if name not in cases:
         raise SystemExit("unknown profile case; one of: " + ", ".join(sorted(cases)))
