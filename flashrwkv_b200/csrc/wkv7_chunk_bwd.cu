@@ -445,17 +445,22 @@ __global__ __launch_bounds__(kBwdThreads, 1) void wkv7_chunk_backward_kernel(
             xb[4 * c4] = q.x; xb[4 * c4 + 1] = q.y; xb[4 * c4 + 2] = q.z; xb[4 * c4 + 3] = q.w;
           }
           const uint32_t arow = kOffRA + uint32_t(4 * j) * kCS128 + uint32_t(16 * jb) * 16;  // A_ab[16 jb][16 j]
+          // two multiply-adds per instruction (fma.rn.f32x2): this fold is bound by instruction issue
+          float2 xp[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) xp[e] = make_float2(x[2 * e], x[2 * e + 1]);
 #pragma unroll
           for (int tt = 0; tt < 16; ++tt) {
+            const float2 bb = make_float2(xb[tt], xb[tt]);
 #pragma unroll
             for (int s4 = 0; s4 < 4; ++s4) {
               const float4 a4 = ld4(smem, arow + s4 * kCS128 + tt * 16);
-              x[4 * s4] = fmaf(a4.x, xb[tt], x[4 * s4]);
-              x[4 * s4 + 1] = fmaf(a4.y, xb[tt], x[4 * s4 + 1]);
-              x[4 * s4 + 2] = fmaf(a4.z, xb[tt], x[4 * s4 + 2]);
-              x[4 * s4 + 3] = fmaf(a4.w, xb[tt], x[4 * s4 + 3]);
+              xp[2 * s4] = __ffma2_rn(make_float2(a4.x, a4.y), bb, xp[2 * s4]);
+              xp[2 * s4 + 1] = __ffma2_rn(make_float2(a4.z, a4.w), bb, xp[2 * s4 + 1]);
             }
           }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { x[2 * e] = xp[e].x; x[2 * e + 1] = xp[e].y; }
         }
       }
       // every block has been read: dX^T, rounded, over dU^T, and the dX rows into rows 0..63 of the [dX;dY'] tile

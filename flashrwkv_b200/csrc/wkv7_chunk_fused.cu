@@ -473,17 +473,22 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
               xb[4 * c4] = q.x; xb[4 * c4 + 1] = q.y; xb[4 * c4 + 2] = q.z; xb[4 * c4 + 3] = q.w;
             }
             const uint32_t acol = kOffUV + uint32_t(16 * jb) * 256 + uint32_t(16 * j) * 4;  // A_ab^T[16 jb][16 j]
+            // two multiply-adds per instruction (fma.rn.f32x2): this fold is bound by instruction issue
+            float2 xp[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) xp[e] = make_float2(x[2 * e], x[2 * e + 1]);
 #pragma unroll
             for (int tt = 0; tt < 16; ++tt) {
+              const float2 bb = make_float2(xb[tt], xb[tt]);
 #pragma unroll
               for (int q4 = 0; q4 < 4; ++q4) {
                 const float4 a4 = ld4(smem, acol + tt * 256 + q4 * 16);
-                x[4 * q4] = fmaf(a4.x, xb[tt], x[4 * q4]);
-                x[4 * q4 + 1] = fmaf(a4.y, xb[tt], x[4 * q4 + 1]);
-                x[4 * q4 + 2] = fmaf(a4.z, xb[tt], x[4 * q4 + 2]);
-                x[4 * q4 + 3] = fmaf(a4.w, xb[tt], x[4 * q4 + 3]);
+                xp[2 * q4] = __ffma2_rn(make_float2(a4.x, a4.y), bb, xp[2 * q4]);
+                xp[2 * q4 + 1] = __ffma2_rn(make_float2(a4.z, a4.w), bb, xp[2 * q4 + 1]);
               }
             }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { x[2 * e] = xp[e].x; x[2 * e + 1] = xp[e].y; }
           }
         }
         // every block has been read and A_ab^T with it: U rows -> state_dot_a (optional), U^T rounded over A_ab^T
