@@ -91,8 +91,9 @@ __device__ __forceinline__ StepOut token_step(float4 (&s)[16], const io_t* __res
     }
   }
 
-  float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f;
-  float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+  // The four value columns of a lane travel as two pairs: fma.rn.f32x2 does two multiply-adds per instruction, each
+  // rounded as the scalar one would be, so the results are the bits of the scalar form.
+  float2 sa01 = make_float2(0.f, 0.f), sa23 = sa01, y01 = sa01, y23 = sa01;
   float br = 0.f, kr = 0.f;
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
@@ -108,25 +109,31 @@ __device__ __forceinline__ StepOut token_step(float4 (&s)[16], const io_t* __res
     }
     {
       const float4 q = s[2 * p];
-      sa0 = fmaf(a2.x, q.x, sa0); sa1 = fmaf(a2.x, q.y, sa1);
-      sa2 = fmaf(a2.x, q.z, sa2); sa3 = fmaf(a2.x, q.w, sa3);
+      const float2 ax = make_float2(a2.x, a2.x);
+      sa01 = __ffma2_rn(ax, make_float2(q.x, q.y), sa01);
+      sa23 = __ffma2_rn(ax, make_float2(q.z, q.w), sa23);
       if (kNeedOutput) {
         const float wr = wv[2 * p] * r2.x;
-        y0 = fmaf(wr, q.x, y0); y1 = fmaf(wr, q.y, y1);
-        y2 = fmaf(wr, q.z, y2); y3 = fmaf(wr, q.w, y3);
+        const float2 wr2 = make_float2(wr, wr);
+        y01 = __ffma2_rn(wr2, make_float2(q.x, q.y), y01);
+        y23 = __ffma2_rn(wr2, make_float2(q.z, q.w), y23);
       }
     }
     {
       const float4 q = s[2 * p + 1];
-      sa0 = fmaf(a2.y, q.x, sa0); sa1 = fmaf(a2.y, q.y, sa1);
-      sa2 = fmaf(a2.y, q.z, sa2); sa3 = fmaf(a2.y, q.w, sa3);
+      const float2 ay = make_float2(a2.y, a2.y);
+      sa01 = __ffma2_rn(ay, make_float2(q.x, q.y), sa01);
+      sa23 = __ffma2_rn(ay, make_float2(q.z, q.w), sa23);
       if (kNeedOutput) {
         const float wr = wv[2 * p + 1] * r2.y;
-        y0 = fmaf(wr, q.x, y0); y1 = fmaf(wr, q.y, y1);
-        y2 = fmaf(wr, q.z, y2); y3 = fmaf(wr, q.w, y3);
+        const float2 wr2 = make_float2(wr, wr);
+        y01 = __ffma2_rn(wr2, make_float2(q.x, q.y), y01);
+        y23 = __ffma2_rn(wr2, make_float2(q.z, q.w), y23);
       }
     }
   }
+  float sa0 = sa01.x, sa1 = sa01.y, sa2 = sa23.x, sa3 = sa23.y;
+  float y0 = y01.x, y1 = y01.y, y2 = y23.x, y3 = y23.y;
   // finish the key-direction sums across the four row groups (lane bits 3 and 4)
 #pragma unroll
   for (int m = 8; m <= 16; m <<= 1) {
@@ -139,27 +146,25 @@ __device__ __forceinline__ StepOut token_step(float4 (&s)[16], const io_t* __res
     }
   }
   const float2 v01 = IO::unpack(vraw.x), v23 = IO::unpack(vraw.y);
+  sa01 = make_float2(sa0, sa1);
+  sa23 = make_float2(sa2, sa3);
 
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
     const float2 b2 = IO::unpack(bb[p]), k2 = IO::unpack(kk[p]);
     {
       float4 q = s[2 * p];
-      const float wi = wv[2 * p];
-      q.x = fmaf(wi, q.x, fmaf(b2.x, sa0, k2.x * v01.x));
-      q.y = fmaf(wi, q.y, fmaf(b2.x, sa1, k2.x * v01.y));
-      q.z = fmaf(wi, q.z, fmaf(b2.x, sa2, k2.x * v23.x));
-      q.w = fmaf(wi, q.w, fmaf(b2.x, sa3, k2.x * v23.y));
-      s[2 * p] = q;
+      const float2 wi = make_float2(wv[2 * p], wv[2 * p]), bx = make_float2(b2.x, b2.x), kx = make_float2(k2.x, k2.x);
+      const float2 lo = __ffma2_rn(wi, make_float2(q.x, q.y), __ffma2_rn(bx, sa01, __fmul2_rn(kx, v01)));
+      const float2 hi = __ffma2_rn(wi, make_float2(q.z, q.w), __ffma2_rn(bx, sa23, __fmul2_rn(kx, v23)));
+      s[2 * p] = make_float4(lo.x, lo.y, hi.x, hi.y);
     }
     {
       float4 q = s[2 * p + 1];
-      const float wi = wv[2 * p + 1];
-      q.x = fmaf(wi, q.x, fmaf(b2.y, sa0, k2.y * v01.x));
-      q.y = fmaf(wi, q.y, fmaf(b2.y, sa1, k2.y * v01.y));
-      q.z = fmaf(wi, q.z, fmaf(b2.y, sa2, k2.y * v23.x));
-      q.w = fmaf(wi, q.w, fmaf(b2.y, sa3, k2.y * v23.y));
-      s[2 * p + 1] = q;
+      const float2 wi = make_float2(wv[2 * p + 1], wv[2 * p + 1]), by = make_float2(b2.y, b2.y), ky = make_float2(k2.y, k2.y);
+      const float2 lo = __ffma2_rn(wi, make_float2(q.x, q.y), __ffma2_rn(by, sa01, __fmul2_rn(ky, v01)));
+      const float2 hi = __ffma2_rn(wi, make_float2(q.z, q.w), __ffma2_rn(by, sa23, __fmul2_rn(ky, v23)));
+      s[2 * p + 1] = make_float4(lo.x, lo.y, hi.x, hi.y);
     }
   }
   StepOut out;
