@@ -308,13 +308,16 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
             qf[e + 2] = scale * fmaf(b_dot_r, qf[e + 2], g.z * rcp_approx(gp.z) * pf[e + 2]);
             qf[e + 3] = scale * fmaf(b_dot_r, qf[e + 3], g.w * rcp_approx(gp.w) * pf[e + 3]);
           }
-          xa[e + 0] = tf32_bits(pf[e + 0] * sc.x);  // rows past the end of a short chunk were loaded as zeros
-          xa[e + 1] = tf32_bits(pf[e + 1] * sc.y);
-          xa[e + 2] = tf32_bits(pf[e + 2] * sc.z);
-          xa[e + 3] = tf32_bits(pf[e + 3] * sc.w);
-          st4(smem, kOffX2 + kc * kCSB + m * 16,
-              umma::to_tf32(make_float4(qf[e + 0] * rcp_approx(g.x), qf[e + 1] * rcp_approx(g.y),
-                                        qf[e + 2] * rcp_approx(g.z), qf[e + 3] * rcp_approx(g.w))));
+          // products in pairs (mul.rn.f32x2: two per instruction, the scalar bits)
+          const float2 p01 = __fmul2_rn(make_float2(pf[e + 0], pf[e + 1]), make_float2(sc.x, sc.y));
+          const float2 p23 = __fmul2_rn(make_float2(pf[e + 2], pf[e + 3]), make_float2(sc.z, sc.w));
+          xa[e + 0] = tf32_bits(p01.x);  // rows past the end of a short chunk were loaded as zeros
+          xa[e + 1] = tf32_bits(p01.y);
+          xa[e + 2] = tf32_bits(p23.x);
+          xa[e + 3] = tf32_bits(p23.y);
+          const float2 q01 = __fmul2_rn(make_float2(qf[e + 0], qf[e + 1]), make_float2(rcp_approx(g.x), rcp_approx(g.y)));
+          const float2 q23 = __fmul2_rn(make_float2(qf[e + 2], qf[e + 3]), make_float2(rcp_approx(g.z), rcp_approx(g.w)));
+          st4(smem, kOffX2 + kc * kCSB + m * 16, umma::to_tf32(make_float4(q01.x, q01.y, q23.x, q23.y)));
         }
         umma::tmem_st8(tmem + kColXA + lane_base + c0 + 8 * i, xa);
         if (!low) {
@@ -534,7 +537,13 @@ __global__ __launch_bounds__(kThreads, 2) void wkv7_chunk_fused_kernel(
                                    ? boundary + ((long long)(c + c_step) * num_heads + head) * (kD * kD) + mt * kD + c0
                                    : nullptr);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) S[j] = g_last * (S[j] + __uint_as_float(u[j]));
+          for (int j = 0; j < 32; j += 2) {  // two state values per instruction, the scalar bits
+            const float2 t = __fmul2_rn(make_float2(g_last, g_last),
+                                        __fadd2_rn(make_float2(S[j], S[j + 1]),
+                                                   make_float2(__uint_as_float(u[j]), __uint_as_float(u[j + 1]))));
+            S[j] = t.x;
+            S[j + 1] = t.y;
+          }
           if (dst != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8)
