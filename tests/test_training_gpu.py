@@ -344,3 +344,52 @@ def test_native_training_entries_fail_closed_on_bad_chunk_tables(head_size):
         torch.cuda.synchronize()
         for g in grads:
             assert torch.isnan(g.float()).all()
+
+
+def test_c_abi_chunked_backward_with_decay_bias_vs_oracle(oracle):
+    """The three native stages (fused forward with saved tensors, adjoint scan, chunk-parallel backward) called with
+    raw pointers and a per-head decay bias, which the Python training operators never pass: the adjoint scan makes its
+    keys from the decay tile, so the bias must reach them through it.  All seven gradients against the oracle."""
+    import ctypes
+
+    from flashrwkv_b200 import _ext, synthetic
+    from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata, wkv7_chunk_forward
+
+    lib = _ext.capi()
+    lengths = (130, 64, 200)
+    H, D, B, N = 2, 64, len(lengths), sum(lengths)
+    toks = synthetic.wkv7_inputs(N, H, D, seed=77)
+    gen = torch.Generator().manual_seed(9)
+    bias = (torch.randn(H, D, generator=gen) * 0.5).to(torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32)
+    S0 = synthetic.state_pool(B, H, D, seed=6)
+    dy = torch.randn(N, H, D, generator=gen).to(torch.bfloat16)
+    dSf = torch.randn(B, H, D, D, generator=gen) * 0.1
+    want = oracle.backward(*toks, initial_state=S0, cu_seqlens=cu, grad_output=dy, grad_final_state=dSf, scale=0.9,
+                           decay_bias=bias)
+    dt = [t.cuda() for t in toks]
+    sco, cs, ce = make_chunk_metadata(cu.cuda(), 64)
+    state = S0.cuda().clone()
+    sda = torch.empty(N, H, D, device="cuda")
+    _, boundary, flag = wkv7_chunk_forward(*dt, state=state, chunk_metadata=(sco, cs, ce), scale=0.9,
+                                           decay_bias=bias.cuda(), want_boundary=True, state_dot_a=sda, path=1)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    r, w, k, v, a, b = dt
+    bias_d, dy_d = bias.cuda(), dy.cuda()
+    g_state = dSf.cuda().clone()
+    adjoint = torch.empty(cs.numel(), H, D, D, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = lib.frwkv_wkv7_adjoint_scan(p(sco), p(cs), p(ce), p(r), p(w), p(a), p(b), p(bias_d), p(dy_d), p(g_state),
+                                     p(adjoint), p(err), None, N, B, cs.numel(), H, D, 1, ctypes.c_float(0.9), stream)
+    assert rc == 0, lib.frwkv_last_error()
+    grads = [torch.empty_like(r) for _ in range(6)]  # dr, dw, dk, dv, da, db
+    rc = lib.frwkv_wkv7_chunk_backward(p(sco), p(cs), p(ce), p(state), p(boundary), p(adjoint), p(sda), p(r), p(w),
+                                       p(k), p(v), p(a), p(b), p(bias_d), p(dy_d), *(p(t) for t in grads), p(err), None,
+                                       N, B, cs.numel(), H, D, 1, ctypes.c_float(0.9), stream)
+    assert rc == 0, lib.frwkv_last_error()
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0 and int(err.item()) == 0
+    for got, name in zip(grads, ("r", "decay_logits", "k", "v", "a", "b")):
+        assert rel_rmse(got.float().cpu(), want[name]) <= 8e-3, name
+    assert rel_rmse(g_state.cpu(), want["initial_state"]) <= 8e-3
