@@ -52,21 +52,22 @@ def test_golden_pretrain_forward_and_gradients():
         F.pretrain_recurrent_bf16(*(v.half() for v in vals))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("lengths", [(256, 256), (1, 17, 64, 100, 130)])
-def test_gradients_vs_oracle_backward(oracle, lengths):
+def test_gradients_vs_oracle_backward(oracle, lengths, dtype):
     """B200 gradients against the oracle's float64 backward at T up to 256, ragged chunking, non-zero S0,
-    upstream gradients on both the output and the final state."""
+    upstream gradients on both the output and the final state; both 16-bit token types."""
     import flashrwkv_b200 as F
     from flashrwkv_b200 import synthetic
     from flashrwkv_b200.tmix.wkv7 import make_chunk_metadata
 
     H, D, B = 2, 64, len(lengths)
     N = sum(lengths)
-    toks = synthetic.wkv7_inputs(N, H, D, seed=31 + B)
+    toks = synthetic.wkv7_inputs(N, H, D, seed=31 + B, dtype=dtype)
     cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32)
     S0 = synthetic.state_pool(B, H, D, seed=5)
     gen = torch.Generator().manual_seed(8)
-    dy = torch.randn(N, H, D, generator=gen).to(torch.bfloat16)
+    dy = torch.randn(N, H, D, generator=gen).to(dtype)
     dSf = torch.randn(B, H, D, D, generator=gen) * 0.1
     want = oracle.backward(*toks, initial_state=S0, cu_seqlens=cu, grad_output=dy, grad_final_state=dSf, scale=0.8)
     dS0 = S0.cuda().requires_grad_()
