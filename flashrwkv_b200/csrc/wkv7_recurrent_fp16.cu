@@ -161,6 +161,7 @@ __global__ __launch_bounds__(kRegWarps * 32, 4) void wkv7_fp16_register_kernel(
     const io_t* __restrict__ a_ptr, const io_t* __restrict__ b_ptr, const io_t* __restrict__ bias_ptr,
     io_t* __restrict__ y_ptr, long long num_units, int num_heads, long long output_elements, float scale) {
   using IO = Io16<io_t>;
+  chain_begin();
   if (metadata_status != nullptr && metadata_status[0] != 0) {  // fail closed: NaN output, state untouched
     fill_nan(y_ptr, output_elements, kRegWarps * 32);
     return;
@@ -236,6 +237,7 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_fp16_decode_kernel(
   constexpr int kStages = R::kStages, kStageBytes = R::kStageBytes;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full_bar[kStages], done_bar[kStages], empty_bar[kStages];
+  chain_begin();  // the counter kernel of the step before may still be running: nothing is read before this returns
   // state slot and elapsed counter of this CTA's first kMetaUnits units, fetched by all threads before the pipeline
   // starts: the loader, the storer and the consumers would otherwise each wait for two dependent global loads per unit
   __shared__ int slot_s[kMetaUnits], elapsed_s[kMetaUnits];
@@ -365,12 +367,14 @@ __global__ __launch_bounds__(kDecodeThreads, 1) void wkv7_fp16_decode_kernel(
 
 // ---- elapsed counters ---------------------------------------------------------------------------------------------------
 __global__ void advance_all_kernel(int* __restrict__ elapsed, long long n, int amount) {
+  chain_begin();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     elapsed[i] = (int)((unsigned)elapsed[i] + (unsigned)amount);  // wraps like the 32-bit phase
 }
 __global__ void advance_varlen_kernel(int* __restrict__ elapsed_pool, const int* __restrict__ cu_seqlens,
                                       const int* __restrict__ state_indices, const int* __restrict__ metadata_status,
                                       int num_sequences) {
+  chain_begin();
   if (metadata_status != nullptr && metadata_status[0] != 0) return;  // fail closed: counters untouched
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < num_sequences; i += gridDim.x * blockDim.x) {
     const int slot = state_indices[i];
@@ -396,11 +400,11 @@ int launch_fp16(const int* cu, const int* idx, const int* status, const int* ela
     if (e != cudaSuccess) return fail(FRWKV_ERR_CUDA, "wkv7_recurrent_fp16: %s", cudaGetErrorString(e));          \
     const int units = tiles / KT;                                                                                 \
     const int grid = sm_count > 0 && sm_count < units ? sm_count : units;                                         \
-    wkv7_fp16_decode_kernel<io_t, KT><<<grid, kDecodeThreads, RingCfg<KT>::kSmem, stream>>>(                      \
-        idx, status, elapsed, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w),                    \
-        static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a),                    \
-        static_cast<const io_t*>(b), static_cast<const io_t*>(bias), static_cast<io_t*>(y), units, num_heads,     \
-        out_elems, scale, reverse, const_cast<int*>(status));                                                     \
+    launch_chained(wkv7_fp16_decode_kernel<io_t, KT>, dim3((unsigned)grid), dim3(kDecodeThreads),                 \
+                   (size_t)RingCfg<KT>::kSmem, stream, idx, status, elapsed, state, static_cast<const io_t*>(r),  \
+                   static_cast<const io_t*>(w), static_cast<const io_t*>(k), static_cast<const io_t*>(v),         \
+                   static_cast<const io_t*>(a), static_cast<const io_t*>(b), static_cast<const io_t*>(bias),      \
+                   static_cast<io_t*>(y), units, num_heads, out_elems, scale, reverse, const_cast<int*>(status)); \
   }
     // two adjacent heads per stage (16 KB copies, twelve stages); four per stage (32 KB copies, six stages) measured
     // slower at 256 x 32 tiles: 29.8 us per launch against 24.4 us
@@ -411,10 +415,10 @@ int launch_fp16(const int* cu, const int* idx, const int* status, const int* ela
   }
   const long long units = (long long)tiles * 2;
   const long long blocks = (units + kRegWarps - 1) / kRegWarps;
-  wkv7_fp16_register_kernel<io_t><<<(unsigned)blocks, kRegWarps * 32, 0, stream>>>(
-      cu, idx, status, elapsed, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w),
-      static_cast<const io_t*>(k), static_cast<const io_t*>(v), static_cast<const io_t*>(a), static_cast<const io_t*>(b),
-      static_cast<const io_t*>(bias), static_cast<io_t*>(y), units, num_heads, out_elems, scale);
+  launch_chained(wkv7_fp16_register_kernel<io_t>, dim3((unsigned)blocks), dim3(kRegWarps * 32), 0, stream, cu, idx, status,
+                 elapsed, state, static_cast<const io_t*>(r), static_cast<const io_t*>(w), static_cast<const io_t*>(k),
+                 static_cast<const io_t*>(v), static_cast<const io_t*>(a), static_cast<const io_t*>(b),
+                 static_cast<const io_t*>(bias), static_cast<io_t*>(y), units, num_heads, out_elems, scale);
   return check_launch("wkv7_fp16_register_kernel");
 }
 
@@ -461,8 +465,8 @@ extern "C" int frwkv_recurrent_fp16_advance_i32(int32_t* elapsed_state, long lon
   clear_error();
   FRWKV_REQUIRE(elapsed_state != nullptr && count > 0, "recurrent_fp16_advance: a non-empty counter array is required");
   const long long blocks = (count + 255) / 256;
-  advance_all_kernel<<<(unsigned)(blocks > 1024 ? 1024 : blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      elapsed_state, count, amount);
+  launch_chained(advance_all_kernel, dim3((unsigned)(blocks > 1024 ? 1024 : blocks)), dim3(256), 0,
+                 reinterpret_cast<cudaStream_t>(stream), elapsed_state, count, amount);
   return check_launch("advance_all_kernel");
 }
 
@@ -474,7 +478,7 @@ extern "C" int frwkv_recurrent_fp16_advance_i32_varlen(int32_t* elapsed_state_po
   FRWKV_REQUIRE(elapsed_state_pool && cu_seqlens && state_indices, "recurrent_fp16_advance_varlen: null pointer argument");
   FRWKV_REQUIRE(num_sequences > 0, "recurrent_fp16_advance_varlen: sizes must be positive");
   const int blocks = (num_sequences + 255) / 256;
-  advance_varlen_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      elapsed_state_pool, cu_seqlens, state_indices, metadata_status, num_sequences);
+  launch_chained(advance_varlen_kernel, dim3((unsigned)blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                 elapsed_state_pool, cu_seqlens, state_indices, metadata_status, num_sequences);
   return check_launch("advance_varlen_kernel");
 }
